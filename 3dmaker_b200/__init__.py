@@ -1,0 +1,148 @@
+"""B200-native NeRF hot path: loader for libnerf_b200.so and thin ctypes bindings.
+
+The package name starts with a digit, so import it with
+``importlib.import_module("3dmaker_b200")``.
+
+The product is the shared library (hand-written sm_100a CUDA behind a C ABI, ``include/nerf_b200.h``)
+and the C++ host classes built into it.  This module only loads the library, declares the argument
+types of its entry points and offers helpers that take torch CUDA tensors (torch is used for device
+memory and streams, nothing else).  There is no CPU fallback: if the library is missing, or a call
+returns a non-zero status, an exception is raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libnerf_b200.so")
+
+NB_MAX_LEVELS = 16
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_int64 = ctypes.c_int64
+c_float = ctypes.c_float
+
+
+class GridDesc(ctypes.Structure):
+    """nb_grid_desc of include/nerf_b200.h."""
+    _fields_ = [
+        ("num_levels", ctypes.c_int32),
+        ("table_size", ctypes.c_int32),
+        ("base_resolution", ctypes.c_int32),
+        ("dense_level_start", ctypes.c_int32),
+        ("growth", ctypes.c_float),
+        ("scales", ctypes.c_float * NB_MAX_LEVELS),
+    ]
+
+
+class MlpDesc(ctypes.Structure):
+    """nb_mlp_desc of include/nerf_b200.h."""
+    _fields_ = [
+        ("input_dim", ctypes.c_int32),
+        ("hidden_dim", ctypes.c_int32),
+        ("output_dim", ctypes.c_int32),
+        ("num_layers", ctypes.c_int32),
+        ("output_activation", ctypes.c_int32),
+    ]
+
+    def layer_dims(self):
+        dims = []
+        for l in range(self.num_layers):
+            i = self.input_dim if l == 0 else self.hidden_dim
+            o = self.output_dim if l == self.num_layers - 1 else self.hidden_dim
+            dims.append((i, o))
+        return dims
+
+    @property
+    def weight_count(self):
+        return sum(i * o for i, o in self.layer_dims())
+
+    @property
+    def bias_count(self):
+        return sum(o for _, o in self.layer_dims())
+
+
+class NerfB200Error(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    "nb_last_error": (ctypes.c_char_p, []),
+    "nb_version": (c_int, []),
+    "nb_built_arch": (c_int, []),
+    "nb_launch_count": (ctypes.c_uint64, []),
+    "nb_zero_async": (c_int, [c_void_p, c_int64, c_void_p]),
+    "nb_grid_setup": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int, c_int, c_float, c_void_p]),
+    "nb_hash_indices": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_int64, c_int, c_void_p, c_void_p]),
+    "nb_hash_encode_forward": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "nb_grid_mlp_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_hash_scatter_backward": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "nb_mlp_forward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "nb_mlp_backward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                c_void_p, c_void_p, c_void_p]),
+    "nb_mse_loss_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_int, c_void_p]),
+    "nb_adam_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_float,
+                             c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]),
+    "nb_sh_gather": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_density_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+def declared_symbols():
+    """Names of every entry point this module binds (a subset check against include/*.h lives in tests)."""
+    return sorted(_SIGNATURES)
+
+
+def load():
+    """Loads libnerf_b200.so (once).  Raises if it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise NerfB200Error(
+            "libnerf_b200.so is missing (%s): build it with `python 3dmaker_b200/build.py`; "
+            "there is no CPU or PyTorch fallback" % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status, what=""):
+    if status != 0:
+        msg = load().nb_last_error().decode("utf-8", "replace")
+        raise NerfB200Error("%s failed with status %d: %s" % (what or "libnerf_b200 call", status, msg))
+
+
+def ptr(t):
+    """Device pointer of a torch tensor (None -> NULL)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise NerfB200Error("expected a CUDA tensor")
+    if not t.is_contiguous():
+        raise NerfB200Error("expected a contiguous tensor")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+def grid_setup(num_levels, table_size, base_resolution, growth, stream=None):
+    d = GridDesc()
+    check(load().nb_grid_setup(ctypes.byref(d), num_levels, table_size, base_resolution, growth, stream_ptr(stream)),
+          "nb_grid_setup")
+    return d
+
+
+def mlp_desc(input_dim, hidden_dim, output_dim, num_layers, output_activation=0):
+    return MlpDesc(input_dim, hidden_dim, output_dim, num_layers, output_activation)

@@ -1,0 +1,393 @@
+// Multiresolution hash grid: geometry set-up, index dump, encode forward (stand-alone and fused with the
+// MLP), gradient scatter.
+//
+// Replaces the encode body and launchers of modules/TinyMLP/networkFusionHashtable.cu and the
+// hashTableScatter_Backward kernel of modules/TinyMLP/networkFusionBackwardHashtable.cu:783-910.
+//
+// Thread mapping of the encode (differs from the reference, which gives each thread 4 levels of one
+// point): a CTA owns 128 points; thread t works on point (t & 127) and on one half of the levels, so a
+// warp always works on 32 consecutive points of ONE level at a time.  Coarse dense levels then hit a
+// handful of cache lines per warp, and the 8 corner loads of two levels are issued back to back before
+// either blend starts (16 independent 4-byte gathers in flight per thread).
+#include <atomic>
+
+#include "mlp_core.cuh"
+
+namespace nb {
+
+extern std::atomic<uint64_t> g_launch_count;
+
+struct GridParams {
+    int L, T, dls;
+    float scales[NB_MAX_LEVELS];
+};
+
+static GridParams make_params(const nb_grid_desc* d) {
+    GridParams p;
+    p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start;
+    for (int i = 0; i < NB_MAX_LEVELS; i++) p.scales[i] = d->scales[i];
+    return p;
+}
+
+// Resolution of every level, with the forward kernel's expression sequence: a power at levels 0,4,8,12 and
+// repeated multiplication by b in between (modules/TinyMLP/networkFusionHashtable.cu:124-128,218).
+__global__ void level_scales_kernel(int lowestSize, float b, int L, float* out) {
+    int l = threadIdx.x;
+    if (l >= L) return;
+    int levelStart = (l / 4) * 4;
+    float N_l_float = lowestSize * __powf(b, levelStart);
+    for (int i = levelStart; i < l; i++) N_l_float *= b;
+    out[l] = N_l_float;
+}
+
+__device__ __forceinline__ uint32_t hash_coords(int cx, int cy, int cz, int T) {
+    return ((static_cast<uint32_t>(cx) * 1U) ^ (static_cast<uint32_t>(cy) * 2654435761U) ^
+            (static_cast<uint32_t>(cz) * 805459861U)) & static_cast<uint32_t>(T - 1);
+}
+__device__ __forceinline__ uint32_t dense_index(int cx, int cy, int cz, int N_l) {
+    return cx + cy * (N_l + 1) + cz * (N_l + 1) * (N_l + 1);
+}
+
+struct Corners {
+    uint32_t idx[8];  // entry index inside the level (pairs of features), corner order 000,100,010,110,001,101,011,111
+    float wx1, wy1, wz1;
+};
+
+// BWD_CLAMP = false: low corner clamped to [0, N_l] (forward); true: to [0, N_l - 1] (backward).
+template <bool BWD_CLAMP>
+__device__ __forceinline__ void corners_of(float px, float py, float pz, float scale, bool dense, int T, Corners& c) {
+    int N_l = __float2int_rd(scale);
+    float x_l = px * scale, y_l = py * scale, z_l = pz * scale;
+    int x0 = __float2int_rd(x_l), y0 = __float2int_rd(y_l), z0 = __float2int_rd(z_l);
+    const int hi = BWD_CLAMP ? N_l - 1 : N_l;
+    x0 = max(0, min(x0, hi)); y0 = max(0, min(y0, hi)); z0 = max(0, min(z0, hi));
+    int x1 = min(x0 + 1, N_l), y1 = min(y0 + 1, N_l), z1 = min(z0 + 1, N_l);
+    c.wx1 = 1.0f - x_l + floorf(x_l);
+    c.wy1 = 1.0f - y_l + floorf(y_l);
+    c.wz1 = 1.0f - z_l + floorf(z_l);
+    if (dense) {
+        c.idx[0] = dense_index(x0, y0, z0, N_l); c.idx[1] = dense_index(x1, y0, z0, N_l);
+        c.idx[2] = dense_index(x0, y1, z0, N_l); c.idx[3] = dense_index(x1, y1, z0, N_l);
+        c.idx[4] = dense_index(x0, y0, z1, N_l); c.idx[5] = dense_index(x1, y0, z1, N_l);
+        c.idx[6] = dense_index(x0, y1, z1, N_l); c.idx[7] = dense_index(x1, y1, z1, N_l);
+    } else {
+        c.idx[0] = hash_coords(x0, y0, z0, T); c.idx[1] = hash_coords(x1, y0, z0, T);
+        c.idx[2] = hash_coords(x0, y1, z0, T); c.idx[3] = hash_coords(x1, y1, z0, T);
+        c.idx[4] = hash_coords(x0, y0, z1, T); c.idx[5] = hash_coords(x1, y0, z1, T);
+        c.idx[6] = hash_coords(x0, y1, z1, T); c.idx[7] = hash_coords(x1, y1, z1, T);
+    }
+}
+
+__device__ __forceinline__ void corner_weights(const Corners& c, float (&w)[8]) {
+    const float wx1 = c.wx1, wy1 = c.wy1, wz1 = c.wz1;
+    w[0] = wx1 * wy1 * wz1;                   w[1] = (1 - wx1) * wy1 * wz1;
+    w[2] = wx1 * (1 - wy1) * wz1;             w[3] = (1 - wx1) * (1 - wy1) * wz1;
+    w[4] = wx1 * wy1 * (1 - wz1);             w[5] = (1 - wx1) * wy1 * (1 - wz1);
+    w[6] = wx1 * (1 - wy1) * (1 - wz1);       w[7] = (1 - wx1) * (1 - wy1) * (1 - wz1);
+}
+
+// Fixed-order blend of the reference (networkFusionHashtable.cu:185-201), both features.
+__device__ __forceinline__ uint32_t blend(const uint32_t (&f)[8], const float (&w)[8]) {
+    float2 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = unpack_half2(f[k]);
+    float rx = v[7].x * w[7], ry = v[7].y * w[7];
+#pragma unroll
+    for (int k = 6; k >= 0; k--) {
+        rx = __fmaf_rn(v[k].x, w[k], rx);
+        ry = __fmaf_rn(v[k].y, w[k], ry);
+    }
+    return pack_half2(rx, ry);
+}
+
+// Encodes the CTA's 128 points into the shared tile: tile[r][2l .. 2l+1].
+template <int TILE_STRIDE>
+__device__ __forceinline__ void encode_tile(const GridParams& gp, const float* __restrict__ pos4, const uint32_t* __restrict__ table2,
+                                            int64_t row_base, int64_t n, __half* tile, int tid) {
+    const int r = tid & (TILE_ROWS - 1);
+    const int half_sel = tid >> 7;  // 0 or 1: which half of the levels
+    const int lpt = gp.L >> 1;      // levels per thread
+    const int64_t row = row_base + r;
+    if (row < n) {
+        float4 p = ld_nc_f4(pos4 + row * 4);
+        for (int li = 0; li < lpt; li += 2) {
+            const int la = half_sel * lpt + li, lb = la + 1;
+            const bool has_b = (li + 1) < lpt;
+            Corners ca, cb;
+            corners_of<false>(p.x, p.y, p.z, gp.scales[la], la < gp.dls, gp.T, ca);
+            corners_of<false>(p.x, p.y, p.z, gp.scales[has_b ? lb : la], (has_b ? lb : la) < gp.dls, gp.T, cb);
+            const uint32_t* ta = table2 + (size_t)la * gp.T;
+            const uint32_t* tb = table2 + (size_t)(has_b ? lb : la) * gp.T;
+            uint32_t fa[8], fb[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) fa[k] = __ldg(ta + ca.idx[k]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) fb[k] = __ldg(tb + cb.idx[k]);
+            float wa[8], wb[8];
+            corner_weights(ca, wa);
+            corner_weights(cb, wb);
+            *reinterpret_cast<uint32_t*>(&tile[r * TILE_STRIDE + 2 * la]) = blend(fa, wa);
+            if (has_b) *reinterpret_cast<uint32_t*>(&tile[r * TILE_STRIDE + 2 * lb]) = blend(fb, wb);
+        }
+    } else {
+        for (int li = 0; li < lpt; li++)
+            *reinterpret_cast<uint32_t*>(&tile[r * TILE_STRIDE + 2 * (half_sel * lpt + li)]) = 0u;
+    }
+}
+
+// Coalesced write of the encoded tile (128 x 2L halves) to global memory.
+template <int TILE_STRIDE>
+__device__ __forceinline__ void store_enc_tile(const __half* tile, __half* __restrict__ enc_out, int L, int64_t row_base, int64_t n,
+                                               int tid) {
+    const int cpr = (2 * L) / 8;
+    for (int c = tid; c < TILE_ROWS * cpr; c += CTA_THREADS) {
+        int r = c / cpr, c8 = c % cpr;
+        if (row_base + r < n) {
+            uint4 v = *reinterpret_cast<const uint4*>(&tile[r * TILE_STRIDE + c8 * 8]);
+            st_cs_v4(&enc_out[(row_base + r) * (2 * L) + c8 * 8], v);
+        }
+    }
+}
+
+constexpr int ENC_STRIDE = 2 * NB_MAX_LEVELS + 8;
+
+__global__ void __launch_bounds__(CTA_THREADS) encode_forward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
+                                                                     const uint32_t* __restrict__ table2, int64_t n,
+                                                                     __half* __restrict__ enc_out) {
+    __shared__ __align__(16) __half tile[TILE_ROWS * ENC_STRIDE];
+    const int64_t row_base = (int64_t)blockIdx.x * TILE_ROWS;
+    encode_tile<ENC_STRIDE>(gp, pos4, table2, row_base, n, tile, threadIdx.x);
+    __syncthreads();
+    store_enc_tile<ENC_STRIDE>(tile, enc_out, gp.L, row_base, n, threadIdx.x);
+}
+
+__global__ void hash_indices_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4, int64_t n, int clamp_mode,
+                                    uint32_t* __restrict__ idx_out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * gp.L) return;
+    int64_t p = i / gp.L;
+    int l = (int)(i % gp.L);
+    float4 pt = ld_nc_f4(pos4 + p * 4);
+    Corners c;
+    if (clamp_mode == 0) corners_of<false>(pt.x, pt.y, pt.z, gp.scales[l], l < gp.dls, gp.T, c);
+    else corners_of<true>(pt.x, pt.y, pt.z, gp.scales[l], l < gp.dls, gp.T, c);
+#pragma unroll
+    for (int k = 0; k < 8; k++) idx_out[i * 8 + k] = (uint32_t)l * (uint32_t)gp.T * 2u + c.idx[k] * 2u;
+}
+
+// Encode fused with the MLP: the encoded 128 x 2L tile is built in shared memory, optionally saved, then
+// every warp runs all layers for its 16 rows out of registers.
+template <class S, bool SAVE>
+__global__ void __launch_bounds__(CTA_THREADS) grid_mlp_forward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
+                                                                       const uint32_t* __restrict__ table2,
+                                                                       const __half* __restrict__ W, const float* __restrict__ bias,
+                                                                       int64_t n, float* __restrict__ out,
+                                                                       __half* __restrict__ save_enc, __half* __restrict__ save_acts) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half* sW = reinterpret_cast<__half*>(smem_raw);
+    float* sBias = reinterpret_cast<float*>(sW + S::SW_TOTAL);
+    __half* tile = reinterpret_cast<__half*>(sBias + S::B_TOTAL);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    load_weights_to_smem<S>(W, bias, sW, sBias, tid);
+    cp_async_commit();
+
+    const int64_t row_base = (int64_t)blockIdx.x * TILE_ROWS;
+    encode_tile<S::TILE_STRIDE>(gp, pos4, table2, row_base, n, tile, tid);
+    cp_async_wait_all();
+    __syncthreads();
+    if (SAVE && save_enc != nullptr) {
+        store_enc_tile<S::TILE_STRIDE>(tile, save_enc, gp.L, row_base, n, tid);
+        __syncthreads();
+    }
+    FwdCtx cx;
+    cx.sW = sW; cx.sBias = sBias;
+    cx.tile_rows = tile + warp * 16 * S::TILE_STRIDE;
+    cx.out = out; cx.acts = SAVE ? save_acts : nullptr;
+    cx.row0 = row_base + warp * 16; cx.n = n; cx.lane = lane;
+    if (cx.row0 < n) mlp_forward_warp<S, 0>(cx);
+}
+
+// Gradient scatter, one thread per (sample, level), level = blockIdx.y so that all CTAs resident at one
+// time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector
+// reduction.  Dense levels first merge lanes that hit the same entry (as the reference does,
+// networkFusionBackwardHashtable.cu:843-887) because neighbouring samples share coarse cells.
+__global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
+                                                               const __half* __restrict__ dEnc, int64_t n,
+                                                               float* __restrict__ grads) {
+    const int level = blockIdx.y;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int lane = threadIdx.x & 31;
+    float4 p = ld_nc_f4(pos4 + i * 4);
+    const bool dense = level < gp.dls;
+    Corners c;
+    corners_of<true>(p.x, p.y, p.z, gp.scales[level], dense, gp.T, c);
+    float w[8];
+    corner_weights(c, w);
+    float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * (2 * gp.L) + 2 * level]));
+    float* base = grads + (size_t)level * gp.T * 2;
+    if (dense) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            float vx = g.x * w[k], vy = g.y * w[k];
+            unsigned active = __activemask();
+            unsigned group = __match_any_sync(active, c.idx[k]);
+            int leader = __ffs(group) - 1;
+            float sx = 0.f, sy = 0.f;
+            unsigned tmp = group;
+            while (tmp) {
+                int src = __ffs(tmp) - 1;
+                sx += __shfl_sync(group, vx, src);
+                sy += __shfl_sync(group, vy, src);
+                tmp &= tmp - 1;
+            }
+            if (lane == leader) red_add_v2(base + (size_t)c.idx[k] * 2, sx, sy);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; k++) red_add_v2(base + (size_t)c.idx[k] * 2, g.x * w[k], g.y * w[k]);
+    }
+}
+
+template <class S>
+static int launch_grid_mlp(const GridParams& gp, const float* pos4, const void* table, const void* W, const float* bias, int64_t n,
+                           float* out, void* save_enc, void* save_acts, cudaStream_t st) {
+    size_t smem = (size_t)S::SW_TOTAL * 2 + (size_t)S::B_TOTAL * 4 + (size_t)TILE_ROWS * S::TILE_STRIDE * 2;
+    int grid = (int)((n + TILE_ROWS - 1) / TILE_ROWS);
+    if (save_enc != nullptr || save_acts != nullptr) {
+        NB_CUDA(cudaFuncSetAttribute(grid_mlp_forward_kernel<S, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        grid_mlp_forward_kernel<S, true><<<grid, CTA_THREADS, smem, st>>>(gp, pos4, (const uint32_t*)table, (const __half*)W, bias, n,
+                                                                          out, (__half*)save_enc, (__half*)save_acts);
+    } else {
+        NB_CUDA(cudaFuncSetAttribute(grid_mlp_forward_kernel<S, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        grid_mlp_forward_kernel<S, false><<<grid, CTA_THREADS, smem, st>>>(gp, pos4, (const uint32_t*)table, (const __half*)W, bias, n,
+                                                                           out, nullptr, nullptr);
+    }
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+static int check_desc(const nb_grid_desc* d, const char* who) {
+    if (!d) return nb_set_error(NB_ERR_INVALID, who);
+    if (d->num_levels < 2 || d->num_levels > NB_MAX_LEVELS || (d->num_levels & 1))
+        return nb_set_error(NB_ERR_UNSUPPORTED, "hash grid: num_levels must be even and between 2 and 16");
+    if (d->table_size < 2 || (d->table_size & (d->table_size - 1)))
+        return nb_set_error(NB_ERR_UNSUPPORTED, "hash grid: table_size must be a power of two");
+    if ((int64_t)d->num_levels * d->table_size * 2 > 0xffffffffLL)
+        return nb_set_error(NB_ERR_LIMIT, "hash grid: table beyond 2^32 elements");
+    return NB_OK;
+}
+
+}  // namespace nb
+
+using namespace nb;
+
+extern "C" int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size, int base_resolution, float growth, void* stream) {
+    if (!desc) return nb_set_error(NB_ERR_INVALID, "nb_grid_setup: null descriptor");
+    desc->num_levels = num_levels;
+    desc->table_size = table_size;
+    desc->base_resolution = base_resolution;
+    desc->growth = growth;
+    desc->dense_level_start = 0;
+    for (int i = 0; i < NB_MAX_LEVELS; i++) desc->scales[i] = 0.f;
+    int rc = check_desc(desc, "nb_grid_setup");
+    if (rc != NB_OK) return rc;
+    if (base_resolution < 1 || !(growth > 1.0f)) return nb_set_error(NB_ERR_INVALID, "nb_grid_setup: base_resolution >= 1 and growth > 1 required");
+    // first hashed level, host float math as in the reference's launchers (networkFusionHashtable.cu:367-377)
+    float inner_term = (std::cbrt(static_cast<float>(table_size)) - 1.0f) / base_resolution;
+    float continuous_level = std::log2(inner_term) / std::log2(growth);
+    int dls = static_cast<int>(std::floor(continuous_level)) + 1;
+    dls = std::max(0, std::min(dls, num_levels));
+    desc->dense_level_start = dls;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    float* d_scales = nullptr;
+    NB_CUDA(cudaMalloc(&d_scales, NB_MAX_LEVELS * sizeof(float)));
+    level_scales_kernel<<<1, 32, 0, st>>>(base_resolution, growth, num_levels, d_scales);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(desc->scales, d_scales, num_levels * sizeof(float), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_scales);
+    if (e != cudaSuccess) return nb_set_cuda_error(e);
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_hash_indices(const nb_grid_desc* desc, const float* d_pos4, int64_t n, int clamp_mode, uint32_t* d_idx_out,
+                               void* stream) {
+    int rc = check_desc(desc, "nb_hash_indices: null descriptor");
+    if (rc != NB_OK) return rc;
+    if (!d_pos4 || !d_idx_out || n < 0) return nb_set_error(NB_ERR_INVALID, "nb_hash_indices: null pointer or negative count");
+    if (n == 0) return NB_OK;
+    GridParams gp = make_params(desc);
+    int64_t total = n * gp.L;
+    hash_indices_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gp, d_pos4, n, clamp_mode, d_idx_out);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_hash_encode_forward(const nb_grid_desc* desc, const float* d_pos4, const void* d_table_h, int64_t n,
+                                      void* d_enc_out_h, void* stream) {
+    int rc = check_desc(desc, "nb_hash_encode_forward: null descriptor");
+    if (rc != NB_OK) return rc;
+    if (!d_pos4 || !d_table_h || !d_enc_out_h || n < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_hash_encode_forward: null pointer or negative count");
+    if ((reinterpret_cast<uintptr_t>(d_pos4) & 15u) || (reinterpret_cast<uintptr_t>(d_enc_out_h) & 15u) ||
+        (reinterpret_cast<uintptr_t>(d_table_h) & 3u) || (desc->num_levels % 4))
+        return nb_set_error(NB_ERR_INVALID, "nb_hash_encode_forward: positions/output must be 16-byte aligned, levels a multiple of 4");
+    if (n == 0) return NB_OK;
+    GridParams gp = make_params(desc);
+    encode_forward_kernel<<<(unsigned)((n + TILE_ROWS - 1) / TILE_ROWS), CTA_THREADS, 0, (cudaStream_t)stream>>>(
+        gp, d_pos4, (const uint32_t*)d_table_h, n, (__half*)d_enc_out_h);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_grid_mlp_forward(const nb_grid_desc* desc, const nb_mlp_desc* mlp, const float* d_pos4, const void* d_table_h,
+                                   const void* d_weights_h, const float* d_biases, int64_t n, float* d_out, void* d_save_enc_h,
+                                   void* d_save_acts_h, void* stream) {
+    int rc = check_desc(desc, "nb_grid_mlp_forward: null descriptor");
+    if (rc != NB_OK) return rc;
+    if (!mlp || !d_pos4 || !d_table_h || !d_weights_h || !d_biases || !d_out || n < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_grid_mlp_forward: null pointer or negative count");
+    if (mlp->input_dim != 2 * desc->num_levels)
+        return nb_set_error(NB_ERR_INVALID, "nb_grid_mlp_forward: mlp input_dim must equal 2 * num_levels");
+    if (mlp->output_activation != 0) return nb_set_error(NB_ERR_UNSUPPORTED, "nb_grid_mlp_forward: the grid network has a linear output");
+    uintptr_t bits = reinterpret_cast<uintptr_t>(d_pos4) | reinterpret_cast<uintptr_t>(d_weights_h) | reinterpret_cast<uintptr_t>(d_out) |
+                     reinterpret_cast<uintptr_t>(d_save_enc_h) | reinterpret_cast<uintptr_t>(d_save_acts_h);
+    if (bits & 15u) return nb_set_error(NB_ERR_INVALID, "nb_grid_mlp_forward: device pointers must be 16-byte aligned");
+    if (n == 0) return NB_OK;
+    GridParams gp = make_params(desc);
+    cudaStream_t st = (cudaStream_t)stream;
+#define X(K0, H, OUT, NL)                                                                                         \
+    if (mlp->input_dim == K0 && (mlp->hidden_dim == H || NL == 1) && mlp->output_dim == OUT && mlp->num_layers == NL) \
+        return launch_grid_mlp<MlpShape<K0, H, OUT, NL>>(gp, d_pos4, d_table_h, d_weights_h, d_biases, n, d_out, d_save_enc_h, d_save_acts_h, st);
+    X(32, 64, 16, 2)
+    X(32, 32, 16, 2)
+    X(32, 64, 16, 3)
+    X(32, 64, 16, 1)
+    X(16, 16, 16, 2)
+#undef X
+    return nb_set_error(NB_ERR_UNSUPPORTED, "nb_grid_mlp_forward: no kernel built for this (levels, hidden, output, layers) shape");
+}
+
+extern "C" int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d_pos4, const void* d_denc_h, int64_t n,
+                                        float* d_table_grads, void* stream) {
+    int rc = check_desc(desc, "nb_hash_scatter_backward: null descriptor");
+    if (rc != NB_OK) return rc;
+    if (!d_pos4 || !d_denc_h || !d_table_grads || n < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_hash_scatter_backward: null pointer or negative count");
+    if ((reinterpret_cast<uintptr_t>(d_pos4) & 15u) || (reinterpret_cast<uintptr_t>(d_table_grads) & 7u))
+        return nb_set_error(NB_ERR_INVALID, "nb_hash_scatter_backward: misaligned device pointer");
+    if (n == 0) return NB_OK;
+    GridParams gp = make_params(desc);
+    dim3 grid((unsigned)((n + 255) / 256), gp.L, 1);
+    scatter_backward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gp, d_pos4, (const __half*)d_denc_h, n, d_table_grads);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}

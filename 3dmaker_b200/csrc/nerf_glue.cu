@@ -1,0 +1,120 @@
+// Per-sample glue between the density and the colour network.
+//
+// nb_sh_gather replaces compute_SH_gather (modules/NeRF/otherKernels.cu:156-273): clamps the 16 density
+// logits to +-64 (NaN -> 0), sigma = expf(min(logit0 - bias, 8)), evaluates the 16 real spherical
+// harmonics of the sample's ray direction and packs logits ++ SH as the colour network's fp16 input.
+// nb_density_grad replaces compute_density_grad (otherKernels.cu:497-562).
+#include <atomic>
+
+#include "common.cuh"
+
+namespace nb {
+
+extern std::atomic<uint64_t> g_launch_count;
+
+__device__ __forceinline__ float sanitize_logit(float v) {
+    v = fmaxf(-64.0f, fminf(64.0f, v));
+    return (v != v) ? 0.0f : v;
+}
+
+__global__ void __launch_bounds__(256) sh_gather_kernel(const float* __restrict__ dirs3, const uint32_t* __restrict__ ray_indices,
+                                                        int64_t offset, int64_t n, float density_bias,
+                                                        const float* __restrict__ density_out, __half* __restrict__ color_in,
+                                                        float* __restrict__ sigma_out) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const float* dp = dirs3 + 3 * (int64_t)ray_indices[idx + offset];
+    float x = dp[0], y = dp[1], z = dp[2];
+    float x2 = x * x, y2 = y * y, z2 = z * z;
+    float sh[16];
+    sh[0] = 0.28209479f;
+    sh[1] = -0.48860251f * y;
+    sh[2] = 0.48860251f * z;
+    sh[3] = -0.48860251f * x;
+    sh[4] = 1.09254843f * x * y;
+    sh[5] = -1.09254843f * y * z;
+    sh[6] = 0.31539156f * (3.0f * z2 - 1.0f);
+    sh[7] = -1.09254843f * x * z;
+    sh[8] = 0.54627421f * (x2 - y2);
+    sh[9] = -0.59004359f * y * (3.0f * x2 - y2);
+    sh[10] = 2.89061144f * x * y * z;
+    sh[11] = -0.45704580f * y * (5.0f * z2 - 1.0f);
+    sh[12] = 0.37317633f * z * (5.0f * z2 - 3.0f);
+    sh[13] = -0.45704580f * x * (5.0f * z2 - 1.0f);
+    sh[14] = 1.44530572f * z * (x2 - y2);
+    sh[15] = -0.59004359f * x * (x2 - 3.0f * y2);
+
+    const float4* dv = reinterpret_cast<const float4*>(density_out + idx * 16);
+    float lg[16];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        float4 v = dv[q];
+        lg[4 * q + 0] = sanitize_logit(v.x); lg[4 * q + 1] = sanitize_logit(v.y);
+        lg[4 * q + 2] = sanitize_logit(v.z); lg[4 * q + 3] = sanitize_logit(v.w);
+    }
+    sigma_out[idx] = expf(fminf(lg[0] - density_bias, 8.0f));
+    uint4* dst = reinterpret_cast<uint4*>(color_in + idx * 32);
+    uint4 o;
+    o = make_uint4(pack_half2(lg[0], lg[1]), pack_half2(lg[2], lg[3]), pack_half2(lg[4], lg[5]), pack_half2(lg[6], lg[7]));
+    st_cs_v4(&dst[0], o);
+    o = make_uint4(pack_half2(lg[8], lg[9]), pack_half2(lg[10], lg[11]), pack_half2(lg[12], lg[13]), pack_half2(lg[14], lg[15]));
+    st_cs_v4(&dst[1], o);
+    o = make_uint4(pack_half2(sh[0], sh[1]), pack_half2(sh[2], sh[3]), pack_half2(sh[4], sh[5]), pack_half2(sh[6], sh[7]));
+    st_cs_v4(&dst[2], o);
+    o = make_uint4(pack_half2(sh[8], sh[9]), pack_half2(sh[10], sh[11]), pack_half2(sh[12], sh[13]), pack_half2(sh[14], sh[15]));
+    st_cs_v4(&dst[3], o);
+}
+
+__device__ __forceinline__ uint32_t sanitize_pair(uint32_t v, float add_lo) {
+    float2 f = unpack_half2(v);
+    f.x += add_lo;
+    f.x = fmaxf(-65504.0f, fminf(65504.0f, f.x));
+    if (f.x != f.x) f.x = 0.0f;
+    f.y = fmaxf(-65504.0f, fminf(65504.0f, f.y));
+    if (f.y != f.y) f.y = 0.0f;
+    return pack_half2(f.x, f.y);
+}
+
+__global__ void __launch_bounds__(256) density_grad_kernel(int64_t n, const float* __restrict__ tmp_dsigma,
+                                                           const __half* __restrict__ color_dx, __half* __restrict__ density_grad) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint4* src = reinterpret_cast<const uint4*>(color_dx + i * 32);
+    uint4 a = src[0], b = src[1];
+    float ds = tmp_dsigma != nullptr ? tmp_dsigma[i] : 0.0f;
+    a.x = sanitize_pair(a.x, ds); a.y = sanitize_pair(a.y, 0.f); a.z = sanitize_pair(a.z, 0.f); a.w = sanitize_pair(a.w, 0.f);
+    b.x = sanitize_pair(b.x, 0.f); b.y = sanitize_pair(b.y, 0.f); b.z = sanitize_pair(b.z, 0.f); b.w = sanitize_pair(b.w, 0.f);
+    uint4* dst = reinterpret_cast<uint4*>(density_grad + i * 16);
+    st_cs_v4(&dst[0], a);
+    st_cs_v4(&dst[1], b);
+}
+
+}  // namespace nb
+
+using namespace nb;
+
+extern "C" int nb_sh_gather(const float* d_dirs3, const uint32_t* d_ray_indices, int64_t offset, int64_t n, float density_bias,
+                            const float* d_density_out, void* d_color_in_h, float* d_sigma, void* stream) {
+    if (!d_dirs3 || !d_ray_indices || !d_density_out || !d_color_in_h || !d_sigma || n < 0 || offset < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_sh_gather: null pointer or negative count");
+    if ((reinterpret_cast<uintptr_t>(d_density_out) & 15u) || (reinterpret_cast<uintptr_t>(d_color_in_h) & 15u))
+        return nb_set_error(NB_ERR_INVALID, "nb_sh_gather: density output and colour input must be 16-byte aligned");
+    if (n == 0) return NB_OK;
+    sh_gather_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_dirs3, d_ray_indices, offset, n, density_bias,
+                                                                                    d_density_out, (__half*)d_color_in_h, d_sigma);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_density_grad(int64_t n, const float* d_tmp_dsigma, const void* d_color_dx_h, void* d_density_grad_h, void* stream) {
+    if (!d_color_dx_h || !d_density_grad_h || n < 0) return nb_set_error(NB_ERR_INVALID, "nb_density_grad: null pointer or negative count");
+    if ((reinterpret_cast<uintptr_t>(d_color_dx_h) & 15u) || (reinterpret_cast<uintptr_t>(d_density_grad_h) & 15u))
+        return nb_set_error(NB_ERR_INVALID, "nb_density_grad: buffers must be 16-byte aligned");
+    if (n == 0) return NB_OK;
+    density_grad_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, d_tmp_dsigma, (const __half*)d_color_dx_h,
+                                                                                       (__half*)d_density_grad_h);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}

@@ -1,0 +1,170 @@
+// Loss gradient and the fused Adam update.
+//
+// nb_adam_step walks ONE flat parameter arena (hash table first, MLP weights and biases behind it) in a
+// single launch.  It replaces fusedAdamHashGridOptim, fusedAdamWeightsOptim, fusedAdamBiasOptim and
+// zeroGradientsKernel of modules/TinyMLP/optimizerKernel.cu (three launches per network there).
+// The element rules are the reference's: the hash part skips entries whose gradient is exactly zero
+// (their moments do not decay) and zeroes the gradient it consumed; the dense part always updates;
+// non-finite gradients, moments and weights are replaced by zero.
+#include <atomic>
+
+#include "common.cuh"
+
+namespace nb {
+
+extern std::atomic<uint64_t> g_launch_count;
+
+__device__ __forceinline__ float finite_or_zero(float x) { return isfinite(x) ? x : 0.0f; }
+
+struct AdamHyper {
+    float lr, beta1, beta2, eps, bc1, bc2, inv_loss_scale;
+};
+
+// optimizerKernel.cu:142-166
+__device__ __forceinline__ bool adam_sparse(float g_raw, float& m, float& v, float& w, const AdamHyper& h) {
+    if (g_raw == 0.0f) return false;
+    float g = finite_or_zero(g_raw * h.inv_loss_scale);
+    float m_val = h.beta1 * finite_or_zero(m) + (1.0f - h.beta1) * g;
+    float v_val = h.beta2 * finite_or_zero(v) + (1.0f - h.beta2) * g * g;
+    float m_hat = m_val / h.bc1;
+    float v_hat = v_val / h.bc2;
+    float w_val = w;
+    if (!isfinite(w_val)) w_val = 0.0f;
+    w_val = w_val - h.lr * m_hat / (sqrtf(v_hat) + h.eps);
+    if (!isfinite(w_val)) w_val = 0.0f;
+    m = m_val; v = v_val; w = w_val;
+    return true;
+}
+
+// optimizerKernel.cu:41-63
+__device__ __forceinline__ void adam_dense(float g_raw, float& m, float& v, float& w, const AdamHyper& h) {
+    float g = finite_or_zero(g_raw * h.inv_loss_scale);
+    float m_val = finite_or_zero(m);
+    float v_val = finite_or_zero(v);
+    float w_val = w;
+    if (!isfinite(w_val)) w_val = 0.0f;
+    m_val = h.beta1 * m_val + (1.0f - h.beta1) * g;
+    v_val = h.beta2 * v_val + (1.0f - h.beta2) * g * g;
+    float m_hat = m_val / h.bc1;
+    float v_hat = v_val / h.bc2;
+    w_val = w_val - (h.lr * m_hat / (sqrtf(v_hat) + h.eps));
+    if (!isfinite(w_val)) w_val = 0.0f;
+    m = m_val; v = v_val; w = w_val;
+}
+
+// Four consecutive parameters per thread (16-byte loads).  sparse4 / total4 are counts of such groups.
+__global__ void __launch_bounds__(256) adam_arena_kernel(float4* __restrict__ w, uint2* __restrict__ w_h, float4* __restrict__ g,
+                                                         float4* __restrict__ m, float4* __restrict__ v, int64_t sparse4,
+                                                         int64_t total4, AdamHyper h, int zero_dense) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 gv = g[i];
+        if (i < sparse4) {
+            if (gv.x == 0.f && gv.y == 0.f && gv.z == 0.f && gv.w == 0.f) continue;  // untouched group: 16 bytes read, nothing else
+            float4 mv = m[i], vv = v[i], wv = w[i];
+            uint2 hv = w_h[i];
+            __half2 h01 = *reinterpret_cast<__half2*>(&hv.x), h23 = *reinterpret_cast<__half2*>(&hv.y);
+            if (adam_sparse(gv.x, mv.x, vv.x, wv.x, h)) h01 = __halves2half2(__float2half(wv.x), __high2half(h01));
+            if (adam_sparse(gv.y, mv.y, vv.y, wv.y, h)) h01 = __halves2half2(__low2half(h01), __float2half(wv.y));
+            if (adam_sparse(gv.z, mv.z, vv.z, wv.z, h)) h23 = __halves2half2(__float2half(wv.z), __high2half(h23));
+            if (adam_sparse(gv.w, mv.w, vv.w, wv.w, h)) h23 = __halves2half2(__low2half(h23), __float2half(wv.w));
+            m[i] = mv; v[i] = vv; w[i] = wv;
+            hv.x = *reinterpret_cast<uint32_t*>(&h01); hv.y = *reinterpret_cast<uint32_t*>(&h23);
+            w_h[i] = hv;
+            g[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            float4 mv = m[i], vv = v[i], wv = w[i];
+            adam_dense(gv.x, mv.x, vv.x, wv.x, h);
+            adam_dense(gv.y, mv.y, vv.y, wv.y, h);
+            adam_dense(gv.z, mv.z, vv.z, wv.z, h);
+            adam_dense(gv.w, mv.w, vv.w, wv.w, h);
+            m[i] = mv; v[i] = vv; w[i] = wv;
+            __half2 h01 = __floats2half2_rn(wv.x, wv.y), h23 = __floats2half2_rn(wv.z, wv.w);
+            uint2 hv;
+            hv.x = *reinterpret_cast<uint32_t*>(&h01); hv.y = *reinterpret_cast<uint32_t*>(&h23);
+            w_h[i] = hv;
+            if (zero_dense) g[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+}
+
+// MSE loss and its gradient, two elements per thread.  optimizerKernel.cu:169-224.
+template <int OUT_ACT>
+__global__ void __launch_bounds__(256) mse_loss_grad_kernel(const float* __restrict__ pred, const __half* __restrict__ target,
+                                                            __half* __restrict__ grad, float* __restrict__ total_loss,
+                                                            int64_t num_elements, int padded_dim, int valid_dim, float grad_scale) {
+    float local = 0.f;
+    for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2; i < num_elements; i += (int64_t)gridDim.x * blockDim.x * 2) {
+        int c1 = (int)(i % padded_dim), c2 = c1 + 1;
+        float2 p = *reinterpret_cast<const float2*>(&pred[i]);
+        float2 t = __half22float2(*reinterpret_cast<const __half2*>(&target[i]));
+        float dx = (c1 < valid_dim) ? (p.x - t.x) : 0.0f;
+        float dy = (c2 < valid_dim) ? (p.y - t.y) : 0.0f;
+        local += (dx * dx) + (dy * dy);
+        float gx = dx * grad_scale, gy = dy * grad_scale;
+        if (OUT_ACT == 1) {
+            gx *= p.x * (1.0f - p.x);
+            gy *= p.y * (1.0f - p.y);
+        }
+        *reinterpret_cast<__half2*>(&grad[i]) = __floats2half2_rn(gx, gy);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_down_sync(0xffffffffu, local, o);
+    __shared__ float warp_sums[8];
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0 && total_loss != nullptr) {
+        float s = 0.f;
+        for (int k = 0; k < 8; k++) s += warp_sums[k];
+        atomicAdd(total_loss, s);
+    }
+}
+
+}  // namespace nb
+
+using namespace nb;
+
+extern "C" int nb_adam_step(float* d_w, void* d_w_h, float* d_g, float* d_m, float* d_v, int64_t sparse_count, int64_t total_count,
+                            float lr, float beta1, float beta2, float eps, float bias_correction1, float bias_correction2,
+                            float inv_loss_scale, int zero_dense_grads, void* stream) {
+    if (!d_w || !d_w_h || !d_g || !d_m || !d_v || sparse_count < 0 || total_count < sparse_count)
+        return nb_set_error(NB_ERR_INVALID, "nb_adam_step: null pointer or bad counts");
+    if ((sparse_count & 3) || (total_count & 3))
+        return nb_set_error(NB_ERR_INVALID, "nb_adam_step: sparse_count and total_count must be multiples of 4");
+    uintptr_t bits = reinterpret_cast<uintptr_t>(d_w) | reinterpret_cast<uintptr_t>(d_g) | reinterpret_cast<uintptr_t>(d_m) |
+                     reinterpret_cast<uintptr_t>(d_v);
+    if ((bits & 15u) || (reinterpret_cast<uintptr_t>(d_w_h) & 7u))
+        return nb_set_error(NB_ERR_INVALID, "nb_adam_step: arrays must be 16-byte aligned (fp16 copy 8-byte)");
+    if (total_count == 0) return NB_OK;
+    AdamHyper h{lr, beta1, beta2, eps, bias_correction1, bias_correction2, inv_loss_scale};
+    int64_t total4 = total_count / 4;
+    int64_t blocks = (total4 + 255) / 256;
+    int64_t cap = (int64_t)nb_num_sms() * 32;
+    if (blocks > cap) blocks = cap;
+    adam_arena_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float4*)d_w, (uint2*)d_w_h, (float4*)d_g, (float4*)d_m,
+                                                                          (float4*)d_v, sparse_count / 4, total4, h, zero_dense_grads);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_mse_loss_grad(const float* d_pred, const void* d_target_h, void* d_grad_h, float* d_total_loss, int64_t n,
+                                int padded_dim, int valid_dim, float loss_scale, int output_activation, void* stream) {
+    if (!d_pred || !d_target_h || !d_grad_h || n < 0 || padded_dim < 2 || (padded_dim & 1) || valid_dim < 1 || valid_dim > padded_dim)
+        return nb_set_error(NB_ERR_INVALID, "nb_mse_loss_grad: null pointer or bad dims (padded_dim even, 1 <= valid_dim <= padded_dim)");
+    if (n == 0) return NB_OK;
+    int64_t num = n * padded_dim;
+    // (2 / (batch * validDim)) * loss_scale, optimizerKernel.cu:388
+    float grad_scale = (2.0f / (float)(n * valid_dim)) * loss_scale;
+    int64_t blocks = ((num + 1) / 2 + 255) / 256;
+    int64_t cap = (int64_t)nb_num_sms() * 16;
+    if (blocks > cap) blocks = cap;
+    if (output_activation == 1)
+        mse_loss_grad_kernel<1><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(d_pred, (const __half*)d_target_h, (__half*)d_grad_h,
+                                                                                    d_total_loss, num, padded_dim, valid_dim, grad_scale);
+    else
+        mse_loss_grad_kernel<0><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(d_pred, (const __half*)d_target_h, (__half*)d_grad_h,
+                                                                                    d_total_loss, num, padded_dim, valid_dim, grad_scale);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}

@@ -1,0 +1,163 @@
+"""Host-side driver of the field-training hot path (encode -> density MLP -> SH -> colour MLP -> loss ->
+backward -> scatter -> Adam) over the C ABI.
+
+This is the orchestration the reference spreads over TinyMLPHashGrid::forward/backward/step,
+TinyMLP::forward/calculate_loss_and_grad/backward/step and the glue kernels of InstantNerf::trainWithRaysHit
+(modules/NeRF/InstantNerf.cu:506-571), restated for one flat parameter arena:
+
+    arena = [ hash table L*T*2 | density W, b | colour W, b ]     (fp32 master, fp16 copy, grad, m, v)
+
+so the gradient of the whole model is one contiguous buffer (one allreduce under data parallelism) and one
+Adam launch updates everything.  torch is used for device memory, streams and the process group only; every
+kernel on the path is launched through libnerf_b200.so.
+"""
+import ctypes
+import importlib
+
+import numpy as np
+
+nb = importlib.import_module("3dmaker_b200")
+
+
+def _pad4(x):
+    return (x + 3) // 4 * 4
+
+
+class FieldModel:
+    """Parameters of hash grid + density network + colour network in one arena, with Adam state."""
+
+    def __init__(self, torch, num_levels=16, table_size=1 << 19, base_resolution=16, growth=1.3819, density_hidden=64,
+                 density_layers=2, color_hidden=64, color_layers=3, training=True, stream=None):
+        self.torch = torch
+        self.lib = nb.load()
+        self.grid = nb.grid_setup(num_levels, table_size, base_resolution, growth, stream)
+        self.density = nb.mlp_desc(2 * num_levels, density_hidden, 16, density_layers, 0)
+        self.color = nb.mlp_desc(32, color_hidden, 8, color_layers, 1)
+        self.hash_count = num_levels * table_size * 2
+        # arena offsets (elements)
+        o = self.hash_count
+        self.off_dw = o; o += self.density.weight_count
+        self.off_db = o; o += self.density.bias_count
+        self.off_cw = o; o += self.color.weight_count
+        self.off_cb = o; o += self.color.bias_count
+        self.total = _pad4(o)
+        dev = "cuda"
+        self.w = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.w_h = torch.zeros(self.total, dtype=torch.float16, device=dev)
+        self.training = training
+        if training:
+            self.g = torch.zeros(self.total, dtype=torch.float32, device=dev)
+            self.m = torch.zeros(self.total, dtype=torch.float32, device=dev)
+            self.v = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.step_count = 0
+
+    # ---- parameter I/O (host numpy <-> arena), mirrors loadHashgrid / loadWeights of the reference classes
+    def load_hashgrid(self, table_f32):
+        t = self.torch.from_numpy(np.ascontiguousarray(table_f32, np.float32).ravel()).cuda()
+        assert t.numel() == self.hash_count
+        self.w[:self.hash_count].copy_(t)
+        self.w_h[:self.hash_count].copy_(t.half())
+
+    def load_density_weights(self, W, b):
+        self._load(self.off_dw, self.density.weight_count, W)
+        self._load(self.off_db, self.density.bias_count, b)
+
+    def load_color_weights(self, W, b):
+        self._load(self.off_cw, self.color.weight_count, W)
+        self._load(self.off_cb, self.color.bias_count, b)
+
+    def _load(self, off, count, arr):
+        t = self.torch.from_numpy(np.ascontiguousarray(arr, np.float32).ravel()).cuda()
+        assert t.numel() == count
+        self.w[off:off + count].copy_(t)
+        self.w_h[off:off + count].copy_(t.half())
+
+    def view(self, which, off, count):
+        return getattr(self, which)[off:off + count]
+
+    def ptr(self, which, off):
+        t = getattr(self, which)
+        return ctypes.c_void_p(t.data_ptr() + off * t.element_size())
+
+
+class SampleTrainer:
+    """One optimizer step on explicit samples (position, view direction, target colour):
+    the 'encode + MLP fwd/bwd + Adam' step of the benchmark.  Buffers are sized once for max_batch."""
+
+    def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0):
+        torch = model.torch
+        self.model, self.torch, self.lib = model, torch, model.lib
+        self.max_batch = max_batch
+        self.lr, self.beta1, self.beta2, self.eps, self.loss_scale, self.density_bias = lr, beta1, beta2, eps, loss_scale, density_bias
+        n, dev = max_batch, "cuda"
+        d, c = model.density, model.color
+        f16, f32 = torch.float16, torch.float32
+        self.pos = torch.zeros((n, 4), dtype=f32, device=dev)
+        self.dirs = torch.zeros((n, 3), dtype=f32, device=dev)
+        self.target = torch.zeros((n, 8), dtype=f16, device=dev)
+        self.ray_idx = torch.arange(n, dtype=torch.int32, device=dev)
+        self.enc = torch.zeros((n, d.input_dim), dtype=f16, device=dev)
+        self.d_acts = torch.zeros((max(d.num_layers - 1, 1), n, d.hidden_dim), dtype=f16, device=dev)
+        self.d_out = torch.zeros((n, 16), dtype=f32, device=dev)
+        self.c_in = torch.zeros((n, 32), dtype=f16, device=dev)
+        self.sigma = torch.zeros(n, dtype=f32, device=dev)
+        self.c_acts = torch.zeros((max(c.num_layers - 1, 1), n, c.hidden_dim), dtype=f16, device=dev)
+        self.c_out = torch.zeros((n, 8), dtype=f32, device=dev)
+        self.c_grad = torch.zeros((n, 8), dtype=f16, device=dev)
+        self.c_dx = torch.zeros((n, 32), dtype=f16, device=dev)
+        self.d_grad = torch.zeros((n, 16), dtype=f16, device=dev)
+        self.d_enc = torch.zeros((n, d.input_dim), dtype=f16, device=dev)
+        self.loss = torch.zeros(1, dtype=f32, device=dev)
+
+    def forward_backward(self, n, stream=None):
+        """Everything of a step except the optimizer, on inputs already in self.pos / dirs / target."""
+        m, lib, P = self.model, self.lib, nb.ptr
+        st = nb.stream_ptr(stream)
+        if n > self.max_batch:
+            raise nb.NerfB200Error("batch exceeds max_batch")
+        nb.check(lib.nb_zero_async(P(self.loss), 4, st), "nb_zero_async")
+        nb.check(lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(self.pos), m.ptr("w_h", 0),
+                                         m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), n, P(self.d_out), P(self.enc), P(self.d_acts),
+                                         st), "nb_grid_mlp_forward")
+        nb.check(lib.nb_sh_gather(P(self.dirs), P(self.ray_idx), 0, n, self.density_bias, P(self.d_out), P(self.c_in), P(self.sigma),
+                                  st), "nb_sh_gather")
+        nb.check(lib.nb_mlp_forward(ctypes.byref(m.color), P(self.c_in), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
+                                    P(self.c_out), P(self.c_acts), st), "nb_mlp_forward")
+        nb.check(lib.nb_mse_loss_grad(P(self.c_out), P(self.target), P(self.c_grad), P(self.loss), n, 8, 3, self.loss_scale, 1, st),
+                 "nb_mse_loss_grad")
+        nb.check(lib.nb_mlp_backward(ctypes.byref(m.color), P(self.c_grad), m.ptr("w_h", m.off_cw), P(self.c_in), P(self.c_acts), n,
+                                     m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(self.c_dx), st), "nb_mlp_backward(colour)")
+        nb.check(lib.nb_density_grad(n, None, P(self.c_dx), P(self.d_grad), st), "nb_density_grad")
+        nb.check(lib.nb_mlp_backward(ctypes.byref(m.density), P(self.d_grad), m.ptr("w_h", m.off_dw), P(self.enc), P(self.d_acts), n,
+                                     m.ptr("g", m.off_dw), m.ptr("g", m.off_db), P(self.d_enc), st), "nb_mlp_backward(density)")
+        nb.check(lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(self.pos), P(self.d_enc), n, m.ptr("g", 0), st),
+                 "nb_hash_scatter_backward")
+
+    def optimizer_step(self, stream=None):
+        """Fused Adam over the whole arena; bias corrections as TinyMLPHashGrid::step (step counter capped at 50000)."""
+        m = self.model
+        if m.step_count < 50000:
+            m.step_count += 1
+        bc1 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta1), np.float32(m.step_count)))
+        bc2 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta2), np.float32(m.step_count)))
+        nb.check(self.lib.nb_adam_step(m.ptr("w", 0), m.ptr("w_h", 0), m.ptr("g", 0), m.ptr("m", 0), m.ptr("v", 0), m.hash_count,
+                                       m.total, self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2),
+                                       1.0 / self.loss_scale, 1, nb.stream_ptr(stream)), "nb_adam_step")
+
+    def step_device(self, n, stream=None, grad_sync=None):
+        """One full step on device-resident inputs.  grad_sync(grad_tensor), if given, runs between backward and
+        Adam (the data-parallel allreduce)."""
+        self.forward_backward(n, stream)
+        if grad_sync is not None:
+            grad_sync(self.model.g)
+        self.optimizer_step(stream)
+
+    def step_host(self, pos4, dirs3, target_h8, stream=None, grad_sync=None):
+        """One full step from pinned host tensors: copies inputs in, runs the step, returns the mean squared error
+        (a device->host read of one float, which also synchronises)."""
+        n = pos4.shape[0]
+        self.pos[:n].copy_(pos4, non_blocking=True)
+        self.dirs[:n].copy_(dirs3, non_blocking=True)
+        self.target[:n].copy_(target_h8, non_blocking=True)
+        self.step_device(n, stream, grad_sync)
+        return float(self.loss.item()) / (n * 3)

@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Benchmark of the NeRF field-training hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = hash-grid encode + density MLP + SH + colour MLP forward, MSE loss, both MLPs backward, gradient
+scatter and the fused Adam update, on one batch of 2^20 synthetic samples per GPU (grid L=16, F=2, T=2^19,
+base 16, growth 1.447; density 32->64->16, colour 32->64->64->3(pad 8), fp16 weights/activations with fp32
+accumulation).  Prints ONE JSON line (rank 0).  Under torchrun each rank trains on its own batch and the
+gradient arena is all-reduced with NCCL before Adam (weak scaling).
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+BATCH = 1 << 20
+L, T, BASE, GROWTH = 16, 1 << 19, 16, 1.447
+DENSITY = (32, 64, 16, 2)
+COLOR = (32, 64, 8, 3)
+HYPER = dict(lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0)
+METRIC = "train samples/s (encode+MLP fwd/bwd+Adam)"
+WORKLOAD = "cfg2+encode+Adam: 2^20 samples/GPU, L16 F2 T2^19 b1.447, density 32-64-16, colour 32-64-64-3, MSE, Adam"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_batch(n, seed):
+    rng = np.random.default_rng(seed)
+    pos = np.zeros((n, 4), np.float32)
+    pos[:, :3] = rng.random((n, 3), dtype=np.float32)
+    d = rng.normal(size=(n, 3)).astype(np.float32)
+    d /= np.linalg.norm(d, axis=1, keepdims=True)
+    tgt = np.zeros((n, 8), np.float16)
+    tgt[:, :3] = rng.random((n, 3), dtype=np.float32).astype(np.float16)
+    return pos, d, tgt
+
+
+def init_params(seed_table=0):
+    from helpers import make_mlp
+    rng = np.random.default_rng(seed_table)
+    table = rng.uniform(-1e-4, 1e-4, size=L * T * 2).astype(np.float32)
+    dW, db = make_mlp(*DENSITY, seed=1)
+    cW, cb = make_mlp(*COLOR, seed=1)
+    return table, dW, db, cW, cb
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for k, nm in enumerate(names):
+                if f[5 + k].lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": float(max(mx)) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(sample, repeats=1):
+    """The oracle's restatement of the same step on `sample` samples, OpenMP over all host cores."""
+    import oracle as orc
+    from oracle_pipeline import OracleField
+    table, dW, db, cW, cb = init_params()
+    scales = orc.level_scales(BASE, GROWTH, L)
+    dls = orc.dense_level_start(T, BASE, GROWTH, L)
+    field = OracleField(L, T, BASE, GROWTH, scales, dls, DENSITY, COLOR, table, dW, db, cW, cb)
+    pos, dirs, tgt = make_batch(sample, 123)
+    tgt_bits = tgt.view(np.uint16)
+    H = L * T * 2
+    m, v = np.zeros(H, np.float32), np.zeros(H, np.float32)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        r = field.forward_backward(pos, dirs, tgt_bits, HYPER["loss_scale"])
+        bc1, bc2 = orc.adam_bias_corrections(1, HYPER["beta1"], HYPER["beta2"])
+        wh = orc.half_bits(field.table).copy()
+        orc.adam_hash(field.table, wh, r["g_table"], m, v, HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"], bc1, bc2,
+                      1.0 / HYPER["loss_scale"])
+        for w, g in ((field.dW, r["g_dW"]), (field.db, r["g_db"]), (field.cW, r["g_cW"]), (field.cb, r["g_cb"])):
+            orc.adam_dense(w, g, np.zeros_like(w), np.zeros_like(w), HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"], bc1, bc2,
+                           1.0 / HYPER["loss_scale"])
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample / best, best
+
+
+def run_reference(args, rank):
+    """Reference arm: the reference has no CPU implementation of this path; the timed code is the oracle's CPU
+    restatement of its kernels (kind "port") on all host cores, each step a bounded sample of the workload."""
+    if rank != 0:
+        return
+    total = args.steps + args.warmup
+    sample = 1 << 16 if total <= 8 else (1 << 15 if total <= 20 else 1 << 14)
+    cores = os.cpu_count() or 1
+    times = []
+    for i in range(total):
+        _, dt = cpu_baseline(sample)
+        if i >= args.warmup:
+            times.append(dt)
+    ms = 1000.0 * float(np.mean(times))
+    value = sample / (ms / 1000.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample_per_step": sample},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port",
+                         "sample": "%d samples per step of the 2^20-sample workload, full T=2^19 table and Adam over it" % sample},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def time_kernels(torch, tr, n, iters=5):
+    """Per-kernel device time of one step (CUDA events around each launch on the launching stream)."""
+    import ctypes
+    nb = importlib.import_module("3dmaker_b200")
+    m, lib, P = tr.model, tr.lib, nb.ptr
+    st = nb.stream_ptr()
+    calls = {
+        "grid_mlp_forward": lambda: lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(tr.pos), m.ptr("w_h", 0),
+                                                            m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), n, P(tr.d_out), P(tr.enc),
+                                                            P(tr.d_acts), st),
+        "sh_gather": lambda: lib.nb_sh_gather(P(tr.dirs), P(tr.ray_idx), 0, n, tr.density_bias, P(tr.d_out), P(tr.c_in), P(tr.sigma), st),
+        "mlp_forward_color": lambda: lib.nb_mlp_forward(ctypes.byref(m.color), P(tr.c_in), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb),
+                                                        n, P(tr.c_out), P(tr.c_acts), st),
+        "mse_loss_grad": lambda: lib.nb_mse_loss_grad(P(tr.c_out), P(tr.target), P(tr.c_grad), P(tr.loss), n, 8, 3, tr.loss_scale, 1, st),
+        "mlp_backward_color": lambda: lib.nb_mlp_backward(ctypes.byref(m.color), P(tr.c_grad), m.ptr("w_h", m.off_cw), P(tr.c_in),
+                                                          P(tr.c_acts), n, m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.c_dx), st),
+        "density_grad": lambda: lib.nb_density_grad(n, None, P(tr.c_dx), P(tr.d_grad), st),
+        "mlp_backward_density": lambda: lib.nb_mlp_backward(ctypes.byref(m.density), P(tr.d_grad), m.ptr("w_h", m.off_dw), P(tr.enc),
+                                                            P(tr.d_acts), n, m.ptr("g", m.off_dw), m.ptr("g", m.off_db), P(tr.d_enc), st),
+        "scatter_backward": lambda: lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(tr.pos), P(tr.d_enc), n, m.ptr("g", 0), st),
+    }
+    out = {}
+    for name, fn in calls.items():
+        ts = []
+        for _ in range(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            nb.check(fn(), name)
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        out[name] = float(np.median(ts))
+    # Adam on the gradient the calls above left behind (first call touches everything, later ones nothing:
+    # time the first)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    tr.optimizer_step()
+    b.record()
+    b.synchronize()
+    out["adam_step"] = float(a.elapsed_time(b))
+    return out
+
+
+# algorithmic bytes per sample of the HBM/L2-bound kernels (encode: 16 B position + 16 levels x 8 corners x 4 B
+# gathers + 64 B features out; scatter: 16 B + 64 B gradient in + 16 x 8 x 2 x 4 B adds counted once)
+ALGO_BYTES = {"grid_mlp_forward": 592.0, "scatter_backward": 1104.0}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    nb = importlib.import_module("3dmaker_b200")
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    nb.load()
+
+    model = pl.FieldModel(torch, L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3])
+    table, dW, db, cW, cb = init_params()
+    model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
+    tr = pl.SampleTrainer(model, BATCH, **HYPER)
+
+    # two distinct seeded batches per rank, pinned on the host and resident on the device
+    host, dev = [], []
+    for k in range(2):
+        pos, dirs, tgt = make_batch(BATCH, 1000 + 10 * rank + k)
+        hp = tuple(torch.from_numpy(a).pin_memory() for a in (pos, dirs, tgt))
+        host.append(hp)
+        dev.append(tuple(t.cuda() for t in hp))
+    own = (tr.pos, tr.dirs, tr.target)
+
+    grad_sync = None
+    if world > 1:
+        def grad_sync(g):
+            dist.all_reduce(g, op=dist.ReduceOp.SUM)
+
+    def step_resident(i):
+        tr.pos, tr.dirs, tr.target = dev[i % 2]
+        tr.step_device(BATCH, None, grad_sync)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: inputs resident in HBM ------------------------------------------------------------------
+    for i in range(max(args.warmup, 3)):
+        step_resident(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = nb.load().nb_launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step_resident(i)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = nb.load().nb_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = world * BATCH / (ms_step / 1000.0)
+
+    # ---- e2e: pinned host inputs copied in every step, loss read back every step ---------------------------
+    tr.pos, tr.dirs, tr.target = own
+    for i in range(2):
+        tr.step_host(*host[i % 2], None, grad_sync)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    loss = 0.0
+    for i in range(args.steps):
+        loss = tr.step_host(*host[i % 2], None, grad_sync)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    e2e_value = world * BATCH / (e2e_ms / 1000.0)
+    h2d = sum(a.numel() * a.element_size() for a in host[0])
+
+    line = None
+    if rank == 0:
+        peak, peak_src = load_peaks()
+        kt = time_kernels(torch, tr, BATCH)
+        dom = max(ALGO_BYTES, key=lambda k: kt[k])
+        achieved = ALGO_BYTES[dom] * BATCH / (kt[dom] / 1000.0) / 1e9
+        roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                    "frac": achieved / peak, "traffic": None,
+                    "note": "achieved = %.0f algorithmic B/sample x 2^20 samples / %.3f ms (CUDA events); the fp16 table (32 MiB) and "
+                            "its fp32 gradient (64 MiB) are L2-resident, so this is L2 + HBM traffic against the HBM copy peak"
+                            % (ALGO_BYTES[dom], kt[dom])}
+        line = {
+            "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "l2": "inputs and activations of one step (>1 GB) exceed the 126 MB L2; two input batches alternate",
+                       "parallelism": "dp%d" % world},
+            "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "last_loss": loss},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernel_ms": kt,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            sample = 1 << 16
+            v, dt = cpu_baseline(sample)
+            line["cpu_baseline"] = {"value": v, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": "one step on %d samples (%.1f s) of the 2^20-sample workload, full T=2^19 table" % (sample, dt)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,146 @@
+/*
+ * C ABI of the B200 (sm_100a) NeRF hot-path library, libnerf_b200.so.
+ *
+ * Plain pointers and sizes only.  Every pointer named d_* is a device pointer owned by the caller;
+ * `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Every entry point
+ * enqueues on that stream and returns an int status (NB_OK = 0); nothing aborts and nothing is a
+ * silent no-op: an unsupported shape returns NB_ERR_UNSUPPORTED and nb_last_error() says why.
+ *
+ * Each declaration cites the interface of the reference (Ajitesh-07/3DMaker) that it replaces.
+ * Parameter layout differs from the reference's launchers in one way: per-layer weights, biases,
+ * activations and gradients are flat, layer after layer, instead of device arrays of device
+ * pointers, so that one allreduce and one optimizer launch cover everything.
+ *
+ *   weights  fp16  layer l is [out_l][in_l] row-major, layers back to back
+ *   biases   fp32  layer l is [out_l], layers back to back
+ *   in_0 = input_dim, in_l = hidden_dim; out_l = hidden_dim, out_last = output_dim
+ *   hidden activations fp16: layer 1 .. num_layers-1 inputs, each [n][hidden_dim], back to back
+ */
+#ifndef NERF_B200_H
+#define NERF_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB_OK 0
+#define NB_ERR_INVALID 1      /* bad argument (null pointer, negative size, misaligned) */
+#define NB_ERR_UNSUPPORTED 2  /* shape outside what the kernels are built for */
+#define NB_ERR_CUDA 3         /* a CUDA runtime call or launch failed */
+#define NB_ERR_LIMIT 4        /* size beyond a fixed capacity */
+
+#define NB_MAX_LEVELS 16
+#define NB_MAX_LAYERS 8
+
+/* Multiresolution hash grid geometry.  Mirrors the grid fields of MLPGridOptions
+ * (modules/TinyMLP/TinyMLPHashGrid.h:11-23); features per level is fixed to 2 as the reference's
+ * constructor requires (TinyMLPHashGrid.cu:39). */
+typedef struct nb_grid_desc {
+    int32_t num_levels;        /* numLevels, even, <= NB_MAX_LEVELS */
+    int32_t table_size;        /* tableSize: entries per level, power of two */
+    int32_t base_resolution;   /* lowestSize */
+    int32_t dense_level_start; /* first hashed level (levels below use dense indexing) */
+    float growth;              /* b */
+    float scales[NB_MAX_LEVELS]; /* per-level resolution N_l as the forward kernel computes it */
+} nb_grid_desc;
+
+/* Mirrors MLPOption (modules/TinyMLP/TinyMLP.h:26-33) with dims already padded the way the
+ * reference pads them (powers of two, minimum 8). */
+typedef struct nb_mlp_desc {
+    int32_t input_dim;
+    int32_t hidden_dim;
+    int32_t output_dim;
+    int32_t num_layers;
+    int32_t output_activation; /* 0 none, 1 sigmoid (OUT_ACT_SIGMOID) */
+} nb_mlp_desc;
+
+/* Text of the last error on this thread ("" if none). */
+const char* nb_last_error(void);
+/* Library version and the SM architecture the kernels were built for (100 = sm_100a). */
+int nb_version(void);
+int nb_built_arch(void);
+/* Number of kernel launches this library has issued since load (bench accounting). */
+uint64_t nb_launch_count(void);
+
+/* cudaMemsetAsync(d_ptr, 0, bytes) on the caller's stream (the reference's classes call
+ * cudaMemsetAsync directly, e.g. TinyMLPHashGrid.cu:312). */
+int nb_zero_async(void* d_ptr, int64_t bytes, void* stream);
+
+/* ---- hash grid --------------------------------------------------------------------------- */
+
+/* Fills dense_level_start (host float math of networkFusionHashtable.cu:367-377) and scales[]
+ * (computed on the device with the forward kernel's own expression sequence, restarted every four
+ * levels, networkFusionHashtable.cu:124-128,218).  Synchronises the stream once. */
+int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size, int base_resolution, float growth, void* stream);
+
+/* Element offsets (feature 0) of the 8 corners of every (point, level): d_idx_out[n][L][8].
+ * clamp_mode 0 = forward clamp, 1 = backward clamp (networkFusionHashtable.cu:134-156,
+ * networkFusionBackwardHashtable.cu:812-834).  For bit-exact index parity tests. */
+int nb_hash_indices(const nb_grid_desc* desc, const float* d_pos4, int64_t n, int clamp_mode, uint32_t* d_idx_out,
+                    void* stream);
+
+/* Encode only: d_enc_out[n][2L] fp16.  The encode body of networkFusionHashTableMMA_2d_vector3
+ * (networkFusionHashtable.cu:111-222).  d_pos4 is float4 per point, w ignored. */
+int nb_hash_encode_forward(const nb_grid_desc* desc, const float* d_pos4, const void* d_table_h, int64_t n,
+                           void* d_enc_out_h, void* stream);
+
+/* Encode fused with the MLP.  Replaces launchNetworkFusionHashTableKernel (d_save_* NULL) and
+ * launchNetworkFusionHashTableGradKernel (TinyMLPHashGrid.h:172-194).  d_out is fp32 [n][output_dim].
+ * d_save_enc_h [n][2L] and d_save_acts_h (hidden activations) may be NULL. */
+int nb_grid_mlp_forward(const nb_grid_desc* desc, const nb_mlp_desc* mlp, const float* d_pos4, const void* d_table_h,
+                        const void* d_weights_h, const float* d_biases, int64_t n, float* d_out, void* d_save_enc_h,
+                        void* d_save_acts_h, void* stream);
+
+/* Gradient scatter into the fp32 table gradient.  Replaces the hashTableScatter_Backward half of
+ * launchNetworkFusionScatterBackwardKernel (TinyMLPHashGrid.h:213-226).  d_denc_h is [n][2L] fp16. */
+int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d_pos4, const void* d_denc_h, int64_t n,
+                             float* d_table_grads, void* stream);
+
+/* ---- fused MLP ---------------------------------------------------------------------------- */
+
+/* Replaces launchNetworkFusionKernel / launchNetworkFusionGradKernel (TinyMLP.h:172-206). */
+int nb_mlp_forward(const nb_mlp_desc* mlp, const void* d_in_h, const void* d_weights_h, const float* d_biases, int64_t n,
+                   float* d_out, void* d_save_acts_h, void* stream);
+
+/* Replaces launchNetworkFusionBackwardKernel (TinyMLP.h:183-194) and the MLP half of
+ * launchNetworkFusionScatterBackwardKernel.  d_dloss_h [n][output_dim] fp16; d_act0_h the layer-0
+ * input [n][input_dim]; gradients are ADDED into d_grad_w / d_grad_b; d_dx_h [n][input_dim] may be NULL. */
+int nb_mlp_backward(const nb_mlp_desc* mlp, const void* d_dloss_h, const void* d_weights_h, const void* d_act0_h,
+                    const void* d_acts_h, int64_t n, float* d_grad_w, float* d_grad_b, void* d_dx_h, void* stream);
+
+/* ---- loss and optimizer ------------------------------------------------------------------- */
+
+/* Replaces launchMSELossGrad (TinyMLP.h:244-255).  d_total_loss: one float, the summed squared
+ * error is ADDED to it. */
+int nb_mse_loss_grad(const float* d_pred, const void* d_target_h, void* d_grad_h, float* d_total_loss, int64_t n,
+                     int padded_dim, int valid_dim, float loss_scale, int output_activation, void* stream);
+
+/* One Adam launch over a flat parameter arena.  Elements [0, sparse_count) follow the hash-table
+ * rule of fusedAdamHashGridOptim (optimizerKernel.cu:116-167: skip when the gradient is exactly 0,
+ * zero the gradient after reading); elements [sparse_count, total_count) follow the dense rule of
+ * fusedAdamWeightsOptim / fusedAdamBiasOptim (optimizerKernel.cu:16-113).  Replaces
+ * launchAdamHashGridOptim + launchAdamWeightsOptim + launchAdamBiasOptim (+ launchZeroGradients when
+ * zero_dense_grads != 0).  d_w_h receives the fp16 copy of every element. */
+int nb_adam_step(float* d_w, void* d_w_h, float* d_g, float* d_m, float* d_v, int64_t sparse_count, int64_t total_count,
+                 float lr, float beta1, float beta2, float eps, float bias_correction1, float bias_correction2,
+                 float inv_loss_scale, int zero_dense_grads, void* stream);
+
+/* ---- NeRF glue between the two networks ------------------------------------------------------ */
+
+/* Replaces compute_SH_gather (modules/NeRF/otherKernels.cu:156-273).  d_dirs3: float3 per ray;
+ * d_ray_indices[offset + i] = ray of sample i; d_density_out fp32 [n][16] (read only);
+ * d_color_in_h fp16 [n][32] = 16 clamped logits ++ 16 SH; d_sigma[n] = expf(min(logit0 - bias, 8)). */
+int nb_sh_gather(const float* d_dirs3, const uint32_t* d_ray_indices, int64_t offset, int64_t n, float density_bias,
+                 const float* d_density_out, void* d_color_in_h, float* d_sigma, void* stream);
+
+/* Replaces compute_density_grad (modules/NeRF/otherKernels.cu:497-562).  d_color_dx_h fp16 [n][32]
+ * (only the first 16 channels are read), d_tmp_dsigma[n] added to channel 0 (NULL = zeros),
+ * d_density_grad_h fp16 [n][16], clamped to +-65504, NaN -> 0. */
+int nb_density_grad(int64_t n, const float* d_tmp_dsigma, const void* d_color_dx_h, void* d_density_grad_h, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NERF_B200_H */

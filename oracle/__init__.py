@@ -1,0 +1,186 @@
+"""ctypes front end of the CPU oracle (oracle/nerf_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by the cpu_baseline /
+reference legs of bench.py, never by the product package.  All arrays are numpy; fp16 data travels as
+uint16 bit patterns (``arr.view(np.uint16)``).
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liboracle.so")
+SRC = os.path.join(_HERE, "nerf_oracle.c")
+
+# x86-64-v3 (AVX2, FMA, F16C) instead of -march=native so the prebuilt library also runs on the GPU
+# box's host CPU.  -ffp-contract=off: fused multiply-adds only where the source says fmaf.
+CFLAGS = ["-O3", "-march=x86-64-v3", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", "-std=gnu11", "-Wall"]
+
+
+def build(force=False):
+    if (not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= os.path.getmtime(SRC)):
+        return LIB_PATH
+    cmd = ["gcc"] + CFLAGS + [SRC, "-o", LIB_PATH, "-lm"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("oracle build failed:\n" + r.stderr)
+    return LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.orc_mse_loss_grad.restype = ctypes.c_double
+        _lib.orc_dense_level_start.restype = ctypes.c_int
+        _lib.orc_mlp_weight_count.restype = ctypes.c_long
+        _lib.orc_mlp_bias_count.restype = ctypes.c_long
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _f(x):
+    return ctypes.c_float(float(x))
+
+
+def _c(a, dtype):
+    a = np.ascontiguousarray(a, dtype=dtype)
+    return a
+
+
+def dense_level_start(table_size, base, growth, num_levels):
+    return int(lib().orc_dense_level_start(int(table_size), int(base), _f(growth), int(num_levels)))
+
+
+def level_scales(base, growth, num_levels):
+    out = np.zeros(num_levels, np.float32)
+    lib().orc_level_scales(int(base), _f(growth), int(num_levels), _p(out))
+    return out
+
+
+def hash_indices(pos4, scales, table_size, dls, clamp_mode=0, want_weights=False):
+    pos4 = _c(pos4, np.float32)
+    scales = _c(scales, np.float32)
+    n, L = pos4.shape[0], scales.shape[0]
+    idx = np.zeros((n, L, 8), np.uint32)
+    w = np.zeros((n, L, 8), np.float32) if want_weights else None
+    lib().orc_hash_indices(_p(pos4), ctypes.c_long(n), _p(scales), L, int(table_size), int(dls), int(clamp_mode), _p(idx), _p(w))
+    return (idx, w) if want_weights else idx
+
+
+def encode_forward(pos4, table_h, scales, table_size, dls):
+    """table_h: uint16 view of the fp16 table [L][T][2]; returns uint16 [n][2L]."""
+    pos4 = _c(pos4, np.float32)
+    table_h = _c(table_h, np.uint16)
+    scales = _c(scales, np.float32)
+    n, L = pos4.shape[0], scales.shape[0]
+    out = np.zeros((n, 2 * L), np.uint16)
+    lib().orc_encode_forward(_p(pos4), ctypes.c_long(n), _p(table_h), _p(scales), L, int(table_size), int(dls), _p(out))
+    return out
+
+
+def scatter_backward(pos4, denc_h, scales, table_size, dls, grads=None):
+    pos4 = _c(pos4, np.float32)
+    denc_h = _c(denc_h, np.uint16)
+    scales = _c(scales, np.float32)
+    n, L = pos4.shape[0], scales.shape[0]
+    if grads is None:
+        grads = np.zeros(L * table_size * 2, np.float32)
+    lib().orc_scatter_backward(_p(pos4), ctypes.c_long(n), _p(denc_h), _p(scales), L, int(table_size), int(dls), _p(grads))
+    return grads
+
+
+def mlp_forward(in_h, dims, W_h, bias, out_act=0, save_acts=False):
+    """dims = (input, hidden, output, layers).  Returns (out fp32 [n][out], acts uint16 or None)."""
+    i, h, o, nl = dims
+    in_h = _c(in_h, np.uint16)
+    W_h = _c(W_h, np.uint16)
+    bias = _c(bias, np.float32)
+    n = in_h.shape[0]
+    out = np.zeros((n, o), np.float32)
+    acts = np.zeros((max(nl - 1, 0), n, h), np.uint16) if save_acts else None
+    lib().orc_mlp_forward(_p(in_h), ctypes.c_long(n), i, h, o, nl, _p(W_h), _p(bias), int(out_act), _p(out), _p(acts))
+    return out, acts
+
+
+def mlp_backward(dL_h, dims, W_h, act0_h, acts_h, want_dx=False):
+    i, h, o, nl = dims
+    dL_h = _c(dL_h, np.uint16)
+    W_h = _c(W_h, np.uint16)
+    act0_h = _c(act0_h, np.uint16)
+    acts_h = _c(acts_h, np.uint16) if acts_h is not None else np.zeros(1, np.uint16)
+    n = dL_h.shape[0]
+    dW = np.zeros(int(lib().orc_mlp_weight_count(i, h, o, nl)), np.float32)
+    db = np.zeros(int(lib().orc_mlp_bias_count(h, o, nl)), np.float32)
+    dX = np.zeros((n, i), np.uint16) if want_dx else None
+    lib().orc_mlp_backward(ctypes.c_long(n), i, h, o, nl, _p(dL_h), _p(W_h), _p(act0_h), _p(acts_h), _p(dW), _p(db), _p(dX))
+    return dW, db, dX
+
+
+def mse_loss_grad(pred, target_h, valid, loss_scale, out_act=0):
+    pred = _c(pred, np.float32)
+    target_h = _c(target_h, np.uint16)
+    n, padded = pred.shape
+    grad = np.zeros((n, padded), np.uint16)
+    total = lib().orc_mse_loss_grad(_p(pred), _p(target_h), _p(grad), ctypes.c_long(n), int(padded), int(valid),
+                                    _f(loss_scale), int(out_act))
+    return float(total), grad
+
+
+def adam_dense(w, g, m, v, lr, b1, b2, eps, bc1, bc2, ils, want_half=True):
+    """In place on w, m, v; returns the fp16 copy (uint16) or None."""
+    wh = np.zeros(w.shape, np.uint16) if want_half else None
+    lib().orc_adam_dense(_p(w), _p(wh), _p(_c(g, np.float32)), _p(m), _p(v), ctypes.c_long(w.size), _f(lr), _f(b1), _f(b2),
+                         _f(eps), _f(bc1), _f(bc2), _f(ils))
+    return wh
+
+
+def adam_hash(w, wh, g, m, v, lr, b1, b2, eps, bc1, bc2, ils):
+    """In place on w, wh, g (zeroed where consumed), m, v."""
+    lib().orc_adam_hash(_p(w), _p(wh), _p(g), _p(m), _p(v), ctypes.c_long(w.size), _f(lr), _f(b1), _f(b2), _f(eps), _f(bc1),
+                        _f(bc2), _f(ils))
+
+
+def adam_bias_corrections(step, b1, b2):
+    a, b = ctypes.c_float(), ctypes.c_float()
+    lib().orc_adam_bias_corrections(int(step), _f(b1), _f(b2), ctypes.byref(a), ctypes.byref(b))
+    return a.value, b.value
+
+
+def half_bits(x):
+    """float32 array -> uint16 bit patterns of its fp16 rounding (round to nearest even)."""
+    return np.asarray(x, np.float32).astype(np.float16).view(np.uint16)
+
+
+def half_values(bits):
+    return np.asarray(bits, np.uint16).view(np.float16).astype(np.float32)
+
+
+def sh_gather(dirs3, ray_indices, density_out16, density_bias, offset=0):
+    dirs3 = _c(dirs3, np.float32)
+    ray_indices = _c(ray_indices, np.uint32)
+    density_out16 = _c(density_out16, np.float32)
+    n = density_out16.shape[0]
+    color_in = np.zeros((n, 32), np.uint16)
+    sigma = np.zeros(n, np.float32)
+    lib().orc_sh_gather(_p(dirs3), _p(ray_indices), ctypes.c_long(offset), ctypes.c_long(n), _f(density_bias), _p(density_out16),
+                        _p(color_in), _p(sigma))
+    return color_in, sigma
+
+
+def density_grad(tmp_dsigma, color_dx32_h):
+    tmp_dsigma = _c(tmp_dsigma, np.float32)
+    color_dx32_h = _c(color_dx32_h, np.uint16)
+    n = tmp_dsigma.shape[0]
+    out = np.zeros((n, 16), np.uint16)
+    lib().orc_density_grad(ctypes.c_long(n), _p(tmp_dsigma), _p(color_dx32_h), _p(out))
+    return out
