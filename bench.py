@@ -62,49 +62,73 @@ def init_params(seed_table=0):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Reads SM clock and throttle reasons through NVML (read-only queries) every few milliseconds from a
+    thread while the timed region runs; falls back to polling nvidia-smi when NVML is not importable."""
 
     def __init__(self, gpu_index):
-        self.gpu, self.proc, self.lines = gpu_index, None, []
+        self.gpu, self.samples, self.stop_flag, self.thread = gpu_index, [], threading.Event(), None
+        self.max_mhz = None
+
+    def _loop_nvml(self):
+        import pynvml
+        pynvml.nvmlInit()
+        phys = self.gpu
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            try:
+                phys = int(vis.split(",")[self.gpu])
+            except (ValueError, IndexError):
+                phys = self.gpu
+        h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+        self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+        while not self.stop_flag.is_set():
+            mhz = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+            try:
+                r = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+            except Exception:
+                r = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+            self.samples.append((mhz, [k for k, b in bits.items() if r & b]))
+            time.sleep(0.002)
+
+    def _loop_smi(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=10).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                self.max_mhz = float(f[1])
+                self.samples.append((float(f[0]), [nm for k, nm in enumerate(names) if f[2 + k].lower().startswith("active")]))
+            except Exception:
+                return
+
+    def _loop(self):
+        try:
+            self._loop_nvml()
+        except Exception:
+            self._loop_smi()
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def mark(self):
+        """Index of the next sample: brackets the timed region inside a longer sampling window."""
+        return len(self.samples)
 
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for k, nm in enumerate(names):
-                if f[5 + k].lower().startswith("active"):
-                    reasons.add(nm)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": float(max(mx)) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+    def stop(self, lo=0, hi=None):
+        self.stop_flag.set()
+        if self.thread is not None:
+            self.thread.join(timeout=15)
+        window = self.samples[lo:hi] if self.samples[lo:hi] else self.samples
+        if not window:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no clock samples"], "samples": 0}
+        reasons = sorted({r for _, rs in window for r in rs})
+        return {"sm_mhz": float(np.median([m for m, _ in window])), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(window)}
 
 
 def cpu_baseline(sample, repeats=1):
@@ -258,8 +282,12 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.05)
+        for i in range(3):      # keep the GPU under load while the sampler spins up
+            step_resident(i)
     launches0 = nb.load().nb_launch_count()
     barrier()
+    mark0 = sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
@@ -268,7 +296,7 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms_total = e0.elapsed_time(e1)
     launches = nb.load().nb_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(mark0, sampler.mark()) if rank == 0 else None
     t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -328,8 +356,8 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
