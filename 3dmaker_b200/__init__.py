@@ -73,6 +73,7 @@ _SIGNATURES = {
     "nb_launch_count": (ctypes.c_uint64, []),
     "nb_zero_async": (c_int, [c_void_p, c_int64, c_void_p]),
     "nb_grid_setup": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int, c_int, c_float, c_void_p]),
+    "nb_grid_setup_noalloc": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int, c_int, c_float, c_void_p]),
     "nb_hash_indices": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "nb_hash_encode_forward": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "nb_grid_mlp_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,

@@ -315,6 +315,62 @@ extern "C" int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size,
     return NB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// nb_grid_setup_noalloc: the same set-up without any allocation.
+//
+// Some host programs may not allocate device memory at the point where they configure a grid: a renderer
+// plug-in that was handed a fixed memory budget by its host application, a process whose allocator is
+// locked while a CUDA graph is being recorded, or a real-time loop that forbids cudaMalloc because it
+// synchronises the whole device.  For them the 16-float scratch that nb_grid_setup allocates and frees lives
+// in the library image instead: every GPU that loads the library holds these 256 bytes until exit.
+// ---------------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_static_level_scales[NB_MAX_LEVELS];
+
+// Device address of g_static_level_scales on each device, looked up on the first call made with that
+// device current.  In host code the array's name is only a handle for cudaGetSymbolAddress, never a pointer
+// a kernel could use.
+static float* g_static_level_scales_addr[64] = {nullptr};
+
+extern "C" int nb_grid_setup_noalloc(nb_grid_desc* desc, int num_levels, int table_size, int base_resolution, float growth,
+                                     void* stream) {
+    if (!desc) return nb_set_error(NB_ERR_INVALID, "nb_grid_setup_noalloc: null descriptor");
+    if (num_levels > NB_MAX_LEVELS)
+        return nb_set_error(NB_ERR_LIMIT, "nb_grid_setup_noalloc: num_levels exceeds the 16 levels the static scratch holds");
+    desc->num_levels = num_levels;
+    desc->table_size = table_size;
+    desc->base_resolution = base_resolution;
+    desc->growth = growth;
+    desc->dense_level_start = 0;
+    for (int i = 0; i < NB_MAX_LEVELS; i++) desc->scales[i] = 0.f;
+    int rc = check_desc(desc, "nb_grid_setup_noalloc");
+    if (rc != NB_OK) return rc;
+    if (base_resolution < 1 || !(growth > 1.0f))
+        return nb_set_error(NB_ERR_INVALID, "nb_grid_setup_noalloc: base_resolution >= 1 and growth > 1 required");
+    float inner_term = (std::cbrt(static_cast<float>(table_size)) - 1.0f) / base_resolution;
+    float continuous_level = std::log2(inner_term) / std::log2(growth);
+    int dls = static_cast<int>(std::floor(continuous_level)) + 1;
+    desc->dense_level_start = std::max(0, std::min(dls, num_levels));
+
+    int dev = -1;
+    NB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return nb_set_error(NB_ERR_LIMIT, "nb_grid_setup_noalloc: device ordinal beyond 63");
+    if (g_static_level_scales_addr[dev] == nullptr) {
+        float* p = nullptr;
+        NB_CUDA(cudaGetSymbolAddress((void**)&p, g_static_level_scales));
+        if (p == nullptr) return nb_set_error(NB_ERR_CUDA, "nb_grid_setup_noalloc: cudaGetSymbolAddress returned a null address");
+        g_static_level_scales_addr[dev] = p;
+    }
+    float* d_scales = g_static_level_scales_addr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+    // the kernel writes entries [0, num_levels) and only those are read back, so nothing has to start at zero
+    level_scales_kernel<<<1, 32, 0, st>>>(base_resolution, growth, num_levels, d_scales);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    NB_CUDA(cudaMemcpyAsync(desc->scales, d_scales, num_levels * sizeof(float), cudaMemcpyDeviceToHost, st));
+    NB_CUDA(cudaStreamSynchronize(st));
+    return NB_OK;
+}
+
 extern "C" int nb_hash_indices(const nb_grid_desc* desc, const float* d_pos4, int64_t n, int clamp_mode, uint32_t* d_idx_out,
                                void* stream) {
     int rc = check_desc(desc, "nb_hash_indices: null descriptor");

@@ -75,6 +75,21 @@ int nb_zero_async(void* d_ptr, int64_t bytes, void* stream);
  * levels, networkFusionHashtable.cu:124-128,218).  Synchronises the stream once. */
 int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size, int base_resolution, float growth, void* stream);
 
+/* nb_grid_setup for callers that must not allocate device memory (no counterpart in the reference,
+ * whose launchers recompute the geometry inside every kernel).  Think of a plug-in running inside a
+ * host application's fixed memory budget, or a loop that cannot afford the device-wide synchronisation
+ * of cudaMalloc/cudaFree.  Same inputs, same results as nb_grid_setup; the 16-float scratch the set-up
+ * kernel writes is a static device array inside the library (256 bytes per GPU, held until the process
+ * exits) instead of a cudaMalloc'd buffer, and no cudaMalloc, cudaFree or other allocating call is made.
+ * Limits and rules:
+ *   - num_levels > 16 (NB_MAX_LEVELS) is rejected with NB_ERR_LIMIT;
+ *   - the first call on each device (with that device current) looks up the array's device address;
+ *     make that first call before starting any stream capture;
+ *   - all calls on one GPU share the array, which keeps the previous call's values (each call overwrites
+ *     exactly the entries it reads back, so nothing needs clearing); two calls that overlap on the GPU
+ *     (different streams or threads) race on it - serialise them. */
+int nb_grid_setup_noalloc(nb_grid_desc* desc, int num_levels, int table_size, int base_resolution, float growth, void* stream);
+
 /* Element offsets (feature 0) of the 8 corners of every (point, level): d_idx_out[n][L][8].
  * clamp_mode 0 = forward clamp, 1 = backward clamp (networkFusionHashtable.cu:134-156,
  * networkFusionBackwardHashtable.cu:812-834).  For bit-exact index parity tests. */
