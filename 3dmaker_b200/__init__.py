@@ -62,6 +62,38 @@ class MlpDesc(ctypes.Structure):
         return sum(o for _, o in self.layer_dims())
 
 
+class SceneDesc(ctypes.Structure):
+    """nb_scene_desc of include/nerf_b200.h."""
+    _fields_ = [
+        ("grid_res", ctypes.c_uint32 * 3),
+        ("aabb_min", ctypes.c_float * 3),
+        ("aabb_max", ctypes.c_float * 3),
+        ("num_cascades", ctypes.c_int32),
+        ("mip_levels", ctypes.c_int32),
+        ("samples_per_voxel", ctypes.c_int32),
+    ]
+
+    @property
+    def cells_per_cascade(self):
+        return int(self.grid_res[0]) * int(self.grid_res[1]) * int(self.grid_res[2])
+
+    @property
+    def pyramid_cells(self):
+        x, y, z, s = int(self.grid_res[0]), int(self.grid_res[1]), int(self.grid_res[2]), 0
+        for _ in range(self.mip_levels):
+            s += x * y * z
+            x, y, z = x >> 1, y >> 1, z >> 1
+        return s
+
+
+def scene_desc(grid_res, aabb_min, aabb_max, num_cascades=1, mip_levels=4, samples_per_voxel=1):
+    d = SceneDesc()
+    for a in range(3):
+        d.grid_res[a] = int(grid_res[a]); d.aabb_min[a] = float(aabb_min[a]); d.aabb_max[a] = float(aabb_max[a])
+    d.num_cascades, d.mip_levels, d.samples_per_voxel = num_cascades, mip_levels, samples_per_voxel
+    return d
+
+
 class NerfB200Error(RuntimeError):
     pass
 
@@ -87,6 +119,26 @@ _SIGNATURES = {
                              c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]),
     "nb_sh_gather": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_density_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_ray_aabb": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_march_count": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                               c_void_p]),
+    "nb_march_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, ctypes.c_uint32, c_void_p, c_void_p]),
+    "nb_march_cutoff": (c_int, [c_void_p, c_void_p, c_int64, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p]),
+    "nb_march_emit": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                              ctypes.c_uint32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_composite_infer": (c_int, [c_int64, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), c_void_p]),
+    "nb_composite_train": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, ctypes.POINTER(c_float), c_void_p]),
+    "nb_color_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_int, c_void_p, c_float, c_float, ctypes.c_uint32, c_void_p]),
+    "nb_occ_sample_cells": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_int, c_int, c_int, ctypes.c_uint64, c_void_p]),
+    "nb_occ_sample_occupied": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_int, ctypes.c_uint64, c_void_p]),
+    "nb_occ_update_tmp_grid": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p]),
+    "nb_occ_scratch_bytes": (c_int64, [c_int]),
+    "nb_occ_update_master_grid": (c_int, [c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p]),
+    "nb_occ_update_bitfield": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
+    "nb_occ_extract_active": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
 }
 
 _lib = None

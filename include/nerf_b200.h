@@ -155,6 +155,94 @@ int nb_sh_gather(const float* d_dirs3, const uint32_t* d_ray_indices, int64_t of
  * d_density_grad_h fp16 [n][16], clamped to +-65504, NaN -> 0. */
 int nb_density_grad(int64_t n, const float* d_tmp_dsigma, const void* d_color_dx_h, void* d_density_grad_h, void* stream);
 
+/* ---- rays, occupancy march, compaction ------------------------------------------------------- */
+
+/* Scene geometry of the marcher: the fields of NerfOptions it reads (modules/NeRF/InstantNerf.h:35-42). */
+typedef struct nb_scene_desc {
+    uint32_t grid_res[3];      /* gridResolution (level 0 of each cascade) */
+    float aabb_min[3];         /* aabbMin; must be negative, aabb_max positive (get_cascade divides by both) */
+    float aabb_max[3];
+    int32_t num_cascades;
+    int32_t mip_levels;        /* levelsMipmap */
+    int32_t samples_per_voxel; /* samplesPerVoxel */
+} nb_scene_desc;
+
+/* Replaces compute_ray_aabb_inv_kernel (modules/NeRF/otherKernels.cu:91-154). float3 per ray in and out. */
+int nb_ray_aabb(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, int64_t num_rays, float* d_rays_d_inv,
+                float* d_nears, float* d_fars, void* stream);
+
+/* Pass 1 of the march, samples per ray (cap 1024).  Replaces march_rays_dda_calc_hits
+ * (modules/NeRF/processRays.cu:626-737). */
+int nb_march_count(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, const float* d_rays_d_inv,
+                   const float* d_nears, const float* d_fars, const uint8_t* d_bitfield, int64_t num_rays, uint32_t* d_num_steps,
+                   void* stream);
+
+/* Exclusive scan of the counts + sample-budget cutoff from ray 0.  Replaces custom_exclusive_sum and
+ * find_cutoff_ray_kernel (processRays.cu:486-549,739-769) and the three host read-backs of
+ * processRaysHitLinear (:979-1013).  d_block_sums: scratch of ceil(num_rays/1024) uint32.  d_plan[4]:
+ * [0] rays that fit, [1] their sample total, [2] first sample of the batch (0), [3] samples of all rays. */
+int nb_march_scan(const uint32_t* d_num_steps, uint32_t* d_ray_offsets, uint32_t* d_block_sums, int64_t num_rays, uint32_t batch_size,
+                  uint32_t* d_plan, void* stream);
+
+/* Cutoff for the next batch of an already scanned chunk, starting at rays_done.  Replaces
+ * find_cutoff_ray_from_kernel (processRays.cu:771-799).  d_plan as above, [0] absolute end ray. */
+int nb_march_cutoff(const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, int64_t num_rays, uint32_t rays_done, uint32_t batch_size,
+                    uint32_t* d_plan, void* stream);
+
+/* Pass 2: t, ray id (relative to rays_done) and contracted float4 position of every sample of rays
+ * [rays_done, d_plan[0]), written at ray_offsets[i] - d_plan[2].  Replaces march_rays_dda_offset
+ * (processRays.cu:801-929).  The plan is read on the device; max_rays_in_batch bounds the launch. */
+int nb_march_emit(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, const float* d_rays_d_inv,
+                  const float* d_nears, const float* d_fars, const uint8_t* d_bitfield, int64_t num_rays, uint32_t rays_done,
+                  int64_t max_rays_in_batch, const uint32_t* d_ray_offsets, const uint32_t* d_plan, float* d_t_out,
+                  uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
+
+/* ---- compositing and loss gradients ---------------------------------------------------------- */
+
+/* Replaces render_rays_kernel via launchVolumeRendering with d_dw_out == NULL (modules/NeRF/compositing.cu:5-78,
+ * InstantNerf.h launchVolumeRendering).  d_rgb rows are rgb_stride floats apart (3 valid). */
+int nb_composite_infer(int64_t num_rays, uint32_t base, uint32_t rays_done, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps,
+                       const float* d_t_sorted, const float* d_sigma, const float* d_rgb, int rgb_stride, const float* d_rgb_true,
+                       float* d_final_rgb, float* d_final_depth, float* d_phi, const float* bg_color3, void* stream);
+
+/* Replaces render_rays_distortion_kernel via launchVolumeRendering with d_dw_out != NULL
+ * (modules/NeRF/compositing.cu:84-213).  d_depth_prior / d_sigma_prior may be NULL (depth supervision off). */
+int nb_composite_train(int64_t num_rays, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps, const float* d_t_sorted,
+                       const float* d_sigma, const float* d_depth_prior, const float* d_sigma_prior, const float* d_rgb, int rgb_stride,
+                       const float* d_rgb_true, float* d_final_rgb, float* d_final_depth, float* d_phi, float* d_dw_out,
+                       float* d_weight_sum, float lambda_dist, float lambda_depth, const float* bg_color3, void* stream);
+
+/* Replaces compute_color_grad (modules/NeRF/otherKernels.cu:303-409) with initialOffset 0.  d_color_out rows are
+ * color_stride floats apart; gradient rows are grad_stride (3 or 8) halves, channels 3..7 written as zero. */
+int nb_color_grad(int64_t num_rays, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, const float* d_t_sorted,
+                  const float* d_density_out16, const float* d_color_out, int color_stride, const float* d_phi, const float* d_final_rgb,
+                  const float* d_dw_out, const float* d_weight_sum, void* d_color_grad_h, int grad_stride, float* d_tmp_dsigma,
+                  float loss_scale, float density_bias, uint32_t total_rays_batch, void* stream);
+
+/* ---- occupancy grid ------------------------------------------------------------------------------ */
+
+/* Replaces sampleAABB (modules/NeRF/otherKernels.cu:591-648): one Philox-jittered, contracted sample per thread,
+ * cell id in .w; n == total_cells covers every cell of [cell_offset, cell_offset + n). */
+int nb_occ_sample_cells(const nb_scene_desc* scene, float* d_samples4, int n, int total_cells, int cell_offset, uint64_t seed,
+                        void* stream);
+/* Replaces sampleOccupiedAABB (otherKernels.cu:836-888). */
+int nb_occ_sample_occupied(const nb_scene_desc* scene, float* d_samples4, const int* d_active_cells, const int* d_num_active, int n,
+                           uint64_t seed, void* stream);
+/* Replaces updateTmpGrid (otherKernels.cu:657-678). */
+int nb_occ_update_tmp_grid(const float* d_samples4, const float* d_density_out16, float* d_tmp_grid, float density_bias, int n,
+                           void* stream);
+/* Bytes of scratch nb_occ_update_master_grid needs for total_cells cells. */
+int64_t nb_occ_scratch_bytes(int total_cells);
+/* Replaces updateMasterGrid + the CUB sum of the master grid (otherKernels.cu:680-698): d_sum[0] = sum of the
+ * updated grid. */
+int nb_occ_update_master_grid(const float* d_tmp_grid, float* d_master_grid, float decay, int total_cells, void* d_scratch,
+                              float* d_sum, void* stream);
+/* Replaces updateOccupancyGrid + buildMipmaps / bitfield_max_pool (otherKernels.cu:700-807, InstantNerf.cu:1177-1204). */
+int nb_occ_update_bitfield(const nb_scene_desc* scene, uint8_t* d_bitfield, const float* d_master_grid, const float* d_sum,
+                           float min_optical_thickness, void* stream);
+/* Replaces extractActiveCells (otherKernels.cu:809-834); zeroes *d_num_active first. */
+int nb_occ_extract_active(const nb_scene_desc* scene, const uint8_t* d_bitfield, int* d_active_cells, int* d_num_active, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

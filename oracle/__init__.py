@@ -184,3 +184,146 @@ def density_grad(tmp_dsigma, color_dx32_h):
     out = np.zeros((n, 16), np.uint16)
     lib().orc_density_grad(ctypes.c_long(n), _p(tmp_dsigma), _p(color_dx32_h), _p(out))
     return out
+
+
+# ---- rays, march, compositing, occupancy ------------------------------------------------------------------
+
+def _u32x3(res):
+    return np.ascontiguousarray(res, np.uint32)
+
+
+def _f3(v):
+    return np.ascontiguousarray(v, np.float32)
+
+
+def ray_aabb(rays_o, rays_d, aabb_min, aabb_max, num_cascades):
+    rays_o, rays_d = _c(rays_o, np.float32), _c(rays_d, np.float32)
+    n = rays_o.shape[0]
+    d_inv = np.zeros((n, 3), np.float32); nears = np.zeros(n, np.float32); fars = np.zeros(n, np.float32)
+    lib().orc_ray_aabb(ctypes.c_long(n), _p(rays_o), _p(rays_d), _p(_f3(aabb_min)), _p(_f3(aabb_max)), int(num_cascades), _p(d_inv),
+                       _p(nears), _p(fars))
+    return d_inv, nears, fars
+
+
+def contract_pos(pos3, aabb_min, aabb_max):
+    pos3 = _c(pos3, np.float32)
+    out = np.zeros_like(pos3)
+    lib().orc_contract_pos(ctypes.c_long(pos3.shape[0]), _p(pos3), _p(_f3(aabb_min)), _p(_f3(aabb_max)), _p(out))
+    return out
+
+
+def pyramid_cells(res, levels):
+    lib().orc_pyramid_cells.restype = ctypes.c_uint32
+    return int(lib().orc_pyramid_cells(_p(_u32x3(res)), int(levels)))
+
+
+def march_count(rays_o, rays_d, d_inv, nears, fars, grid, res, aabb_min, aabb_max, num_cascades, levels, spv):
+    n = rays_o.shape[0]
+    out = np.zeros(n, np.uint32)
+    lib().orc_march_count(ctypes.c_long(n), _p(_c(rays_o, np.float32)), _p(_c(rays_d, np.float32)), _p(_c(d_inv, np.float32)),
+                          _p(_c(nears, np.float32)), _p(_c(fars, np.float32)), _p(_c(grid, np.uint8)), _p(_u32x3(res)), _p(_f3(aabb_min)),
+                          _p(_f3(aabb_max)), int(num_cascades), int(levels), int(spv), _p(out))
+    return out
+
+
+def march_emit(rays_o, rays_d, d_inv, nears, fars, grid, res, aabb_min, aabb_max, num_cascades, levels, spv, ray_offsets, base, total):
+    n = rays_o.shape[0]
+    t = np.zeros(total, np.float32); ray = np.zeros(total, np.uint32); pos = np.zeros((total, 4), np.float32)
+    lib().orc_march_emit(ctypes.c_long(n), _p(_c(rays_o, np.float32)), _p(_c(rays_d, np.float32)), _p(_c(d_inv, np.float32)),
+                         _p(_c(nears, np.float32)), _p(_c(fars, np.float32)), _p(_c(grid, np.uint8)), _p(_u32x3(res)), _p(_f3(aabb_min)),
+                         _p(_f3(aabb_max)), int(num_cascades), int(levels), int(spv), _p(_c(ray_offsets, np.uint32)), ctypes.c_uint32(base),
+                         _p(t), _p(ray), _p(pos))
+    return t, ray, pos
+
+
+def exclusive_sum(counts):
+    counts = _c(counts, np.uint32)
+    out = np.zeros_like(counts)
+    lib().orc_exclusive_sum(ctypes.c_long(counts.size), _p(counts), _p(out))
+    return out
+
+
+def find_cutoff(ray_offsets, num_steps, batch_size, rays_done=0):
+    lib().orc_find_cutoff.restype = ctypes.c_uint32
+    return int(lib().orc_find_cutoff(ctypes.c_long(len(num_steps)), _p(_c(ray_offsets, np.uint32)), _p(_c(num_steps, np.uint32)),
+                                     ctypes.c_uint32(batch_size), ctypes.c_uint32(rays_done)))
+
+
+def render_rays(num_rays, base, rays_done, ray_offsets, num_steps, t_sorted, sigma, rgb3, rgb_true, bg):
+    rgb = np.zeros((num_rays, 3), np.float32); depth = np.zeros(num_rays, np.float32)
+    phi = np.zeros((num_rays, 3), np.float32) if rgb_true is not None else None
+    lib().orc_render_rays(ctypes.c_long(num_rays), ctypes.c_uint32(base), ctypes.c_uint32(rays_done), _p(_c(ray_offsets, np.uint32)),
+                          _p(_c(num_steps, np.uint32)), _p(_c(t_sorted, np.float32)), _p(_c(sigma, np.float32)), _p(_c(rgb3, np.float32)),
+                          _p(_c(rgb_true, np.float32)) if rgb_true is not None else None, _p(rgb), _p(depth), _p(phi), _p(_f3(bg)))
+    return rgb, depth, phi
+
+
+def render_rays_distortion(num_rays, ray_offsets, num_steps, t_sorted, sigma, rgb3, rgb_true, lambda_dist, lambda_depth, bg,
+                           depth_prior=None, sigma_prior=None):
+    n = len(t_sorted)
+    rgb = np.zeros((num_rays, 3), np.float32); depth = np.zeros(num_rays, np.float32); phi = np.zeros((num_rays, 3), np.float32)
+    dw = np.zeros(n, np.float32); wsum = np.zeros(num_rays, np.float32)
+    lib().orc_render_rays_distortion(ctypes.c_long(num_rays), _p(_c(ray_offsets, np.uint32)), _p(_c(num_steps, np.uint32)),
+                                     _p(_c(t_sorted, np.float32)), _p(_c(sigma, np.float32)),
+                                     _p(_c(depth_prior, np.float32)) if depth_prior is not None else None,
+                                     _p(_c(sigma_prior, np.float32)) if sigma_prior is not None else None, _p(_c(rgb3, np.float32)),
+                                     _p(_c(rgb_true, np.float32)), _p(rgb), _p(depth), _p(phi), _p(dw), _p(wsum), _f(lambda_dist),
+                                     _f(lambda_depth), _p(_f3(bg)))
+    return rgb, depth, phi, dw, wsum
+
+
+def color_grad(num_rays, num_steps, ray_offsets, t_sorted, density_out16, color_out, phi, final_rgb, dw, wsum, loss_scale, density_bias,
+               total_rays, grad_stride=8):
+    color_out = _c(color_out, np.float32)
+    n = len(t_sorted)
+    grad = np.zeros((n, grad_stride), np.uint16); dsig = np.zeros(n, np.float32)
+    lib().orc_color_grad(ctypes.c_long(num_rays), _p(_c(num_steps, np.uint32)), _p(_c(ray_offsets, np.uint32)), _p(_c(t_sorted, np.float32)),
+                         _p(_c(density_out16, np.float32)), _p(color_out), int(color_out.shape[1]), _p(_c(phi, np.float32)),
+                         _p(_c(final_rgb, np.float32)), _p(_c(dw, np.float32)), _p(_c(wsum, np.float32)), _p(grad), int(grad_stride), _p(dsig),
+                         _f(loss_scale), _f(density_bias), ctypes.c_uint32(total_rays))
+    return grad, dsig
+
+
+def philox_uniform4(seed, subsequence):
+    out = np.zeros(4, np.float32)
+    lib().orc_philox_uniform4(ctypes.c_uint64(seed), ctypes.c_uint64(subsequence), _p(out))
+    return out
+
+
+def sample_aabb(aabb_min, aabb_max, res, n, total_cells, cell_offset, seed):
+    out = np.zeros((n, 4), np.float32)
+    lib().orc_sample_aabb(_p(out), _p(_f3(aabb_min)), _p(_f3(aabb_max)), _p(_u32x3(res)), int(n), int(total_cells), int(cell_offset),
+                          ctypes.c_uint64(seed))
+    return out
+
+
+def sample_occupied(active, aabb_min, aabb_max, res, n, seed):
+    active = _c(active, np.int32)
+    out = np.zeros((n, 4), np.float32)
+    lib().orc_sample_occupied(_p(out), _p(active), int(active.size), _p(_f3(aabb_min)), _p(_f3(aabb_max)), _p(_u32x3(res)), int(n),
+                              ctypes.c_uint64(seed))
+    return out
+
+
+def update_tmp_grid(samples4, density_out16, tmp_grid, density_bias):
+    samples4 = _c(samples4, np.float32)
+    lib().orc_update_tmp_grid(_p(samples4), _p(_c(density_out16, np.float32)), _p(tmp_grid), _f(density_bias), int(samples4.shape[0]))
+
+
+def update_master_grid(tmp_grid, master, decay):
+    lib().orc_update_master_grid(_p(_c(tmp_grid, np.float32)), _p(master), _f(decay), int(master.size))
+
+
+def update_occupancy_bits(bitfield, master, total_sum, cells_per_cascade, pyramid, min_optical_thickness, base_voxel):
+    lib().orc_update_occupancy_bits(_p(bitfield), _p(_c(master, np.float32)), _f(total_sum), int(master.size), int(cells_per_cascade),
+                                    int(pyramid), _f(min_optical_thickness), _f(base_voxel))
+
+
+def build_mipmaps(bitfield, res, levels, num_cascades):
+    lib().orc_build_mipmaps(_p(bitfield), _p(_u32x3(res)), int(levels), int(num_cascades))
+
+
+def extract_active_cells(bitfield, total_cells, cells_per_cascade, pyramid):
+    out = np.zeros(total_cells, np.int32)
+    n = lib().orc_extract_active_cells(_p(_c(bitfield, np.uint8)), _p(out), int(total_cells), int(cells_per_cascade), int(pyramid))
+    return out[:n].copy()

@@ -1,0 +1,235 @@
+"""GPU parity of the NeRF-level kernels (ray slab test, DDA march, scan + cutoff, compositing, loss
+gradients, occupancy grid) against the CPU oracle, through the C ABI.
+
+The march kernels use the device's approximate division / log2 / exp2 (the reference is built with
+--use_fast_math); the oracle uses IEEE and libm.  Floats therefore agree to a few ulp, and a ray that grazes a
+voxel face within that error may gain or lose a sample: counts are compared per ray with a small allowance
+(MARCH_MISMATCH), everything downstream is compared on the rays whose counts agree."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from helpers import ABS_RGB, REL_MLP, Uploader, dev_half_bits, half_vals, rel_err
+from test_oracle_nerf_cpu import camera_rays, sphere_bitfield
+
+pytestmark = pytest.mark.gpu
+
+MARCH_MISMATCH = 5e-3   # fraction of rays whose sample count may differ from the IEEE restatement
+
+
+def _scene(nb, res, cascades, levels, spv, aabb=0.5):
+    return nb.scene_desc(res, [-aabb] * 3, [aabb] * 3, cascades, levels, spv)
+
+
+def _march_gpu(torch, nb, up, sc, o, d, bits, batch):
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    n = o.shape[0]
+    f32, u32 = torch.float32, torch.int32
+    d_o, d_d = up.f(o), up.f(d)
+    d_inv = torch.zeros((n, 3), dtype=f32, device="cuda"); nears = torch.zeros(n, dtype=f32, device="cuda"); fars = torch.zeros_like(nears)
+    nb.check(lib.nb_ray_aabb(ctypes.byref(sc), d_o, d_d, n, P(d_inv), P(nears), P(fars), st), "nb_ray_aabb")
+    d_bits = torch.from_numpy(bits).cuda()
+    steps = torch.zeros(n, dtype=u32, device="cuda"); offs = torch.zeros_like(steps)
+    nb.check(lib.nb_march_count(ctypes.byref(sc), d_o, d_d, P(d_inv), P(nears), P(fars), P(d_bits), n, P(steps), st), "nb_march_count")
+    bsums = torch.zeros((n + 1023) // 1024 + 1, dtype=u32, device="cuda"); plan = torch.zeros(4, dtype=u32, device="cuda")
+    nb.check(lib.nb_march_scan(P(steps), P(offs), P(bsums), n, batch, P(plan), st), "nb_march_scan")
+    torch.cuda.synchronize()
+    return dict(d_o=d_o, d_d=d_d, d_inv=d_inv, nears=nears, fars=fars, bits=d_bits, steps=steps, offs=offs, plan=plan)
+
+
+@pytest.mark.parametrize("cascades,spv,res", [(1, 1, 128), (3, 1, 128), (1, 2, 64)])
+def test_march_count_scan_emit(cuda, nb, orc, cascades, spv, res):
+    torch = cuda
+    up = Uploader(torch, nb)
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    levels, R = 4, 20000
+    r3 = (res, res, res)
+    sc = _scene(nb, r3, cascades, levels, spv)
+    bits = sphere_bitfield(orc, r3, levels, cascades)
+    o, d = camera_rays(R, seed=2)
+    batch = 1 << 18
+    g = _march_gpu(torch, nb, up, sc, o, d, bits, batch)
+    amin, amax = [-.5] * 3, [.5] * 3
+    # slab test: same formulas, device reciprocal is approximate
+    d_inv_ref, n_ref, f_ref = orc.ray_aabb(o, d, amin, amax, cascades)
+    d_inv, nears, fars = (g[k].cpu().numpy() for k in ("d_inv", "nears", "fars"))
+    assert np.allclose(d_inv, d_inv_ref, rtol=2e-6) and np.allclose(nears, n_ref, rtol=1e-5, atol=1e-6) and np.allclose(fars, f_ref, rtol=1e-5)
+    # counts: the oracle walks with the GPU's own d_inv / near / far
+    cnt = g["steps"].cpu().numpy().view(np.uint32)
+    cnt_ref = orc.march_count(o, d, d_inv, nears, fars, bits, r3, amin, amax, cascades, levels, spv)
+    mism = np.mean(cnt != cnt_ref)
+    assert mism <= MARCH_MISMATCH, "sample counts differ on %.3f%% of rays" % (100 * mism)
+    assert np.max(np.abs(cnt.astype(np.int64) - cnt_ref.astype(np.int64))) <= 2 * spv
+    assert cnt.sum() > 100000
+    # scan and cutoff are integer work on the GPU's own counts: bit-exact
+    offs = g["offs"].cpu().numpy().view(np.uint32)
+    assert np.array_equal(offs, orc.exclusive_sum(cnt))
+    plan = g["plan"].cpu().numpy().view(np.uint32)
+    active = orc.find_cutoff(offs, cnt, batch)
+    assert plan[0] == active and plan[1] == (offs[active - 1] + cnt[active - 1] if active else 0) and plan[2] == 0 and plan[3] == cnt.sum()
+    assert 0 < active < R                               # the budget cuts the chunk: the cutoff path is exercised
+    # emit
+    total = int(plan[1])
+    t = torch.zeros(batch, dtype=torch.float32, device="cuda"); ray = torch.zeros(batch, dtype=torch.int32, device="cuda")
+    pos = torch.zeros((batch, 4), dtype=torch.float32, device="cuda")
+    nb.check(lib.nb_march_emit(ctypes.byref(sc), g["d_o"], g["d_d"], P(g["d_inv"]), P(g["nears"]), P(g["fars"]), P(g["bits"]), R, 0, R,
+                               P(g["offs"]), P(g["plan"]), P(t), P(ray), P(pos), st), "nb_march_emit")
+    torch.cuda.synchronize()
+    t, ray, pos = t.cpu().numpy()[:total], ray.cpu().numpy().view(np.uint32)[:total], pos.cpu().numpy()[:total]
+    assert np.array_equal(ray, np.repeat(np.arange(active, dtype=np.uint32), cnt[:active]))      # ray-ordered, ids exact
+    good = np.nonzero(cnt[:active] == cnt_ref[:active])[0]
+    offs_ref = orc.exclusive_sum(cnt_ref)
+    t_ref, _, pos_ref = orc.march_emit(o, d, d_inv, nears, fars, bits, r3, amin, amax, cascades, levels, spv, offs_ref, 0, int(cnt_ref.sum()))
+    idx = np.concatenate([np.arange(offs[r], offs[r] + cnt[r]) for r in good])
+    idx_ref = np.concatenate([np.arange(offs_ref[r], offs_ref[r] + cnt_ref[r]) for r in good])
+    assert np.allclose(t[idx], t_ref[idx_ref], rtol=2e-5, atol=2e-6)
+    assert np.allclose(pos[idx], pos_ref[idx_ref], atol=2e-6)
+    # second batch of the same chunk: cutoff from rays_done, emit relative to it
+    nb.check(lib.nb_march_cutoff(P(g["steps"]), P(g["offs"]), R, active, batch, P(g["plan"]), st), "nb_march_cutoff")
+    torch.cuda.synchronize()
+    plan2 = g["plan"].cpu().numpy().view(np.uint32)
+    nxt = orc.find_cutoff(offs, cnt, batch, rays_done=active)
+    assert plan2[0] == nxt and plan2[2] == offs[active] and plan2[1] == offs[nxt - 1] + cnt[nxt - 1] - offs[active]
+    ray2 = torch.full((batch,), -1, dtype=torch.int32, device="cuda")
+    nb.check(lib.nb_march_emit(ctypes.byref(sc), g["d_o"], g["d_d"], P(g["d_inv"]), P(g["nears"]), P(g["fars"]), P(g["bits"]), R, active, R,
+                               P(g["offs"]), P(g["plan"]), P(t := torch.zeros(batch, dtype=torch.float32, device="cuda")), P(ray2),
+                               P(pos := torch.zeros((batch, 4), dtype=torch.float32, device="cuda")), st), "nb_march_emit")
+    torch.cuda.synchronize()
+    r2 = ray2.cpu().numpy()[:int(plan2[1])]
+    assert np.array_equal(r2, np.repeat(np.arange(nxt - active), cnt[active:nxt]))
+
+
+def test_march_edge_cases(cuda, nb, orc):
+    torch = cuda
+    up = Uploader(torch, nb)
+    sc = _scene(nb, (32, 32, 32), 1, 3, 1)
+    bits = sphere_bitfield(orc, (32, 32, 32), 3, 1)
+    o = np.array([[0, 0, -1.5], [3, 3, 3], [0, 0, 0]], np.float32); d = np.array([[0, 0, 1], [0, 1, 0], [0, 0, 1]], np.float32)
+    g = _march_gpu(torch, nb, up, sc, o, d, bits, 10)              # budget smaller than the first ray: nothing fits
+    cnt = g["steps"].cpu().numpy()
+    assert cnt[0] >= 18 and cnt[1] == 0 and cnt[2] > 0
+    assert g["plan"].cpu().numpy()[0] == 0
+    g = _march_gpu(torch, nb, up, sc, o, d, np.zeros_like(bits), 10)   # empty grid: all rays fit with zero samples
+    p = g["plan"].cpu().numpy()
+    assert p[0] == 3 and p[1] == 0 and p[3] == 0
+
+
+def _random_ray_samples(R, seed, max_count=60):
+    rng = np.random.default_rng(seed)
+    counts = rng.integers(0, max_count, R).astype(np.uint32)
+    counts[:3] = [0, 1, max_count]
+    n = int(counts.sum())
+    off = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.uint32)
+    t = np.concatenate([np.sort(rng.uniform(0.5, 3.0, c)) for c in counts]).astype(np.float32)
+    dens = rng.normal(1.5, 1.5, (n, 16)).astype(np.float32)
+    col = np.zeros((n, 8), np.float32); col[:, :3] = rng.random((n, 3), dtype=np.float32)
+    target = rng.random((R, 3), dtype=np.float32)
+    return counts, off, t, dens, col, target
+
+
+@pytest.mark.parametrize("R", [1, 5000])
+def test_compositing_and_color_grad(cuda, nb, orc, R):
+    torch = cuda
+    up = Uploader(torch, nb)
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    counts, off, t, dens, col, target = _random_ray_samples(max(R, 3), 5)
+    R = len(counts)
+    n = len(t)
+    bias, lam, scale = 1.0, 0.1, 128.0
+    sigma = np.exp(np.minimum(dens[:, 0] - np.float32(bias), 8)).astype(np.float32)
+    bg = (ctypes.c_float * 3)(1.0, 0.5, 0.25)
+    bg_np = np.array([1.0, 0.5, 0.25], np.float32)
+    f32 = torch.float32
+    rgb = torch.zeros((R, 3), dtype=f32, device="cuda"); depth = torch.zeros(R, dtype=f32, device="cuda"); phi = torch.zeros((R, 3), dtype=f32, device="cuda")
+    dw = torch.zeros(n, dtype=f32, device="cuda"); wsum = torch.zeros(R, dtype=f32, device="cuda")
+    d_off, d_cnt, d_t, d_sig, d_col, d_tgt = up.f(off.view(np.int32)), up.f(counts.view(np.int32)), up.f(t), up.f(sigma), up.f(col), up.f(target)
+    nb.check(lib.nb_composite_train(R, d_off, d_cnt, d_t, d_sig, None, None, d_col, 8, d_tgt, P(rgb), P(depth), P(phi), P(dw), P(wsum), lam, 0.0,
+                                    bg, st), "nb_composite_train")
+    torch.cuda.synchronize()
+    r_rgb, r_depth, r_phi, r_dw, r_wsum = orc.render_rays_distortion(R, off, counts, t, sigma, col[:, :3].copy(), target, lam, 0.0, bg_np)
+    assert np.max(np.abs(rgb.cpu().numpy() - r_rgb)) <= ABS_RGB
+    assert np.allclose(depth.cpu().numpy(), r_depth, rtol=1e-4, atol=1e-4) and np.max(np.abs(phi.cpu().numpy() - r_phi)) <= 2 * ABS_RGB
+    assert rel_err(dw.cpu().numpy(), r_dw) <= REL_MLP and rel_err(wsum.cpu().numpy(), r_wsum) <= REL_MLP
+    # inference variant (early termination) agrees on colour within the termination threshold
+    rgb2 = torch.zeros_like(rgb)
+    nb.check(lib.nb_composite_infer(R, 0, 0, d_off, d_cnt, d_t, d_sig, d_col, 8, None, P(rgb2), None, None, bg, st), "nb_composite_infer")
+    torch.cuda.synchronize()
+    i_rgb, _, _ = orc.render_rays(R, 0, 0, off, counts, t, sigma, col[:, :3].copy(), None, bg_np)
+    assert np.max(np.abs(rgb2.cpu().numpy() - i_rgb)) <= ABS_RGB
+    # loss gradients from the GPU's own forward results
+    grad = torch.full((n, 8), 9.0, dtype=torch.float16, device="cuda"); dsig = torch.zeros(n, dtype=f32, device="cuda")
+    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, up.f(dens), d_col, 8, P(phi), P(rgb), P(dw), P(wsum), P(grad), 8, P(dsig), scale, bias, R,
+                               st), "nb_color_grad")
+    torch.cuda.synchronize()
+    g_ref, ds_ref = orc.color_grad(R, counts, off, t, dens, col, phi.cpu().numpy(), rgb.cpu().numpy(), dw.cpu().numpy(), wsum.cpu().numpy(),
+                                   scale, bias, R, 8)
+    got = half_vals(dev_half_bits(grad))
+    assert np.all(got[:, 3:] == 0)
+    assert rel_err(got, half_vals(g_ref)) <= REL_MLP and rel_err(dsig.cpu().numpy(), ds_ref) <= REL_MLP
+
+
+def test_occupancy_kernels(cuda, nb, orc):
+    torch = cuda
+    up = Uploader(torch, nb)
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    res, levels, casc = (32, 32, 32), 4, 2
+    sc = _scene(nb, res, casc, levels, 1)
+    G, S = sc.cells_per_cascade, sc.pyramid_cells
+    N = casc * G
+    amin, amax = [-.5] * 3, [.5] * 3
+    f32, i32 = torch.float32, torch.int32
+    # full-coverage samples of cascade 1 and random samples of the whole grid: cell ids exact, positions to float error
+    smp = torch.zeros((G, 4), dtype=f32, device="cuda")
+    nb.check(lib.nb_occ_sample_cells(ctypes.byref(sc), P(smp), G, G, G, 77, st), "nb_occ_sample_cells")
+    torch.cuda.synchronize()
+    ref = orc.sample_aabb(amin, amax, res, G, G, G, 77)
+    got = smp.cpu().numpy()
+    assert np.array_equal(got[:, 3].copy().view(np.int32), ref[:, 3].copy().view(np.int32))
+    assert np.allclose(got[:, :3], ref[:, :3], atol=2e-6)
+    smp2 = torch.zeros((5000, 4), dtype=f32, device="cuda")
+    nb.check(lib.nb_occ_sample_cells(ctypes.byref(sc), P(smp2), 5000, N, 0, 78, st), "nb_occ_sample_cells")
+    torch.cuda.synchronize()
+    ref2 = orc.sample_aabb(amin, amax, res, 5000, N, 0, 78)
+    got2 = smp2.cpu().numpy()
+    assert np.mean(got2[:, 3].copy().view(np.int32) != ref2[:, 3].copy().view(np.int32)) < 1e-3      # (int)(u * N) at a boundary
+    # density maximum per cell, master grid decay + sum
+    rng = np.random.default_rng(1)
+    dens = np.zeros((G, 16), np.float32); dens[:, 0] = rng.normal(0, 2, G)
+    tmp = torch.zeros(N, dtype=f32, device="cuda")
+    nb.check(lib.nb_occ_update_tmp_grid(P(smp), up.f(dens), P(tmp), 1.0, G, st), "nb_occ_update_tmp_grid")
+    master0 = np.abs(rng.normal(0, 1, N)).astype(np.float32); master0[3] = -1.0
+    master = torch.from_numpy(master0.copy()).cuda()
+    scratch = torch.zeros(int(lib.nb_occ_scratch_bytes(N)) // 8 + 1, dtype=torch.float64, device="cuda"); dsum = torch.zeros(1, dtype=f32, device="cuda")
+    nb.check(lib.nb_occ_update_master_grid(P(tmp), P(master), 0.95, N, P(scratch), P(dsum), st), "nb_occ_update_master_grid")
+    torch.cuda.synchronize()
+    tmp_ref = np.zeros(N, np.float32); orc.update_tmp_grid(got, dens, tmp_ref, 1.0)
+    assert np.allclose(tmp.cpu().numpy(), tmp_ref, rtol=1e-5)
+    m_ref = master0.copy(); orc.update_master_grid(tmp.cpu().numpy(), m_ref, 0.95)
+    m_got = master.cpu().numpy()
+    assert np.allclose(m_got, m_ref, rtol=1e-6) and m_got[3] == -1.0
+    assert abs(dsum.item() - m_got.astype(np.float64).sum()) <= 1e-6 * abs(m_got.astype(np.float64).sum())
+    # bits and pyramid from the GPU's own master grid and sum: bit-exact
+    bits = torch.zeros(casc * S // 8, dtype=torch.uint8, device="cuda")
+    nb.check(lib.nb_occ_update_bitfield(ctypes.byref(sc), P(bits), P(master), P(dsum), 0.01, st), "nb_occ_update_bitfield")
+    torch.cuda.synchronize()
+    b_ref = np.zeros(casc * S // 8, np.uint8)
+    orc.update_occupancy_bits(b_ref, m_got, dsum.item(), G, S, 0.01, 1.0 / 32)
+    orc.build_mipmaps(b_ref, res, levels, casc)
+    b_got = bits.cpu().numpy()
+    assert np.array_equal(b_got, b_ref), "%d of %d occupancy bytes differ" % ((b_got != b_ref).sum(), b_ref.size)
+    assert 0 < np.unpackbits(b_got).sum() < 8 * b_got.size
+    # occupied-cell list: same set
+    act = torch.zeros(N, dtype=i32, device="cuda"); nact = torch.zeros(1, dtype=i32, device="cuda")
+    nb.check(lib.nb_occ_extract_active(ctypes.byref(sc), P(bits), P(act), P(nact), st), "nb_occ_extract_active")
+    torch.cuda.synchronize()
+    a_ref = orc.extract_active_cells(b_got, N, G, S)
+    a_got = act.cpu().numpy()[:nact.item()]
+    assert nact.item() == len(a_ref) and np.array_equal(np.sort(a_got), a_ref)
+    smp3 = torch.zeros((4096, 4), dtype=f32, device="cuda")
+    nb.check(lib.nb_occ_sample_occupied(ctypes.byref(sc), P(smp3), P(act), P(nact), 4096, 79, st), "nb_occ_sample_occupied")
+    torch.cuda.synchronize()
+    ref3 = orc.sample_occupied(a_got, amin, amax, res, 4096, 79)
+    got3 = smp3.cpu().numpy()
+    same = got3[:, 3].copy().view(np.int32) == ref3[:, 3].copy().view(np.int32)
+    assert same.mean() > 0.999 and np.allclose(got3[same, :3], ref3[same, :3], atol=2e-6)
