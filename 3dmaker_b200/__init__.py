@@ -94,6 +94,41 @@ def scene_desc(grid_res, aabb_min, aabb_max, num_cascades=1, mip_levels=4, sampl
     return d
 
 
+class NerfOptions(ctypes.Structure):
+    """nb_nerf_options of include/nerf_b200.h (mirror of the reference's NerfOptions)."""
+    _fields_ = [
+        ("grid_resolution", ctypes.c_uint32 * 3), ("aabb_min", ctypes.c_float * 3), ("aabb_max", ctypes.c_float * 3),
+        ("levels_mipmap", ctypes.c_int32), ("num_cascades", ctypes.c_int32), ("samples_per_voxel", ctypes.c_int32),
+        ("density_hidden_dim", ctypes.c_int32), ("density_num_layers", ctypes.c_int32),
+        ("color_hidden_dim", ctypes.c_int32), ("color_num_layers", ctypes.c_int32),
+        ("hash_table_size", ctypes.c_int32), ("num_levels", ctypes.c_int32), ("growth_factor", ctypes.c_float),
+        ("base_resolution", ctypes.c_int32), ("features_per_level", ctypes.c_int32),
+        ("render_batch_size", ctypes.c_int32), ("batch_size", ctypes.c_int32), ("ray_chunk_size", ctypes.c_int32),
+        ("lambda_depth", ctypes.c_float), ("lambda_dist", ctypes.c_float), ("learning_rate", ctypes.c_float),
+        ("beta1", ctypes.c_float), ("beta2", ctypes.c_float), ("epsilon", ctypes.c_float), ("loss_scale", ctypes.c_float),
+        ("bg_color", ctypes.c_float * 3),
+        ("min_density_threshold", ctypes.c_float), ("decay_value", ctypes.c_float), ("density_bias", ctypes.c_float),
+        ("legacy_render_flag", ctypes.c_uint8), ("is_profiling", ctypes.c_uint8),
+    ]
+
+
+class ArenaView(ctypes.Structure):
+    _fields_ = [("w", c_void_p), ("w_h", c_void_p), ("g", c_void_p), ("m", c_void_p), ("v", c_void_p),
+                ("total", c_int64), ("sparse_count", c_int64),
+                ("density_weight_offset", c_int64), ("density_bias_offset", c_int64), ("color_weight_offset", c_int64),
+                ("color_bias_offset", c_int64), ("density_weight_count", c_int64), ("density_bias_count", c_int64),
+                ("color_weight_count", c_int64), ("color_bias_count", c_int64)]
+
+
+class StepView(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in ("num_steps", "ray_offsets", "ray_indices", "t_sorted", "positions", "density_out", "sigma",
+                                        "color_out", "render_rgb", "phi", "dw", "weight_sum", "tmp_dsigma", "color_in", "color_grad",
+                                        "density_grad")] + [("last_total_hits", ctypes.c_uint32), ("train_steps", ctypes.c_int32)]
+
+
+GRAD_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
+
+
 class NerfB200Error(RuntimeError):
     pass
 
@@ -139,6 +174,26 @@ _SIGNATURES = {
     "nb_occ_update_master_grid": (c_int, [c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "nb_occ_update_bitfield": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "nb_occ_extract_active": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_nerf_default_options": (c_int, [ctypes.POINTER(NerfOptions)]),
+    "nb_nerf_create": (c_void_p, [ctypes.POINTER(NerfOptions), c_int]),
+    "nb_nerf_destroy": (None, [c_void_p]),
+    "nb_nerf_train_rays": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, ctypes.POINTER(c_int),
+                                   c_void_p, c_void_p, c_void_p]),
+    "nb_nerf_render": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_uint32, c_void_p, c_void_p]),
+    "nb_nerf_set_learning_rate": (c_int, [c_void_p, c_float]),
+    "nb_nerf_set_bg_color": (c_int, [c_void_p, c_float, c_float, c_float]),
+    "nb_nerf_set_profiling": (c_int, [c_void_p, c_int]),
+    "nb_nerf_set_memory_mode": (c_int, [c_void_p, c_int]),
+    "nb_nerf_set_global_ray_scale": (c_int, [c_void_p, ctypes.c_uint32]),
+    "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
+    "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),
+    "nb_nerf_load_params": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_nerf_occupancy": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), ctypes.POINTER(c_void_p)]),
+    "nb_nerf_rebuild_occupancy": (c_int, [c_void_p, c_void_p]),
+    "nb_nerf_get_step_view": (c_int, [c_void_p, ctypes.POINTER(StepView)]),
+    "nb_nerf_phase_times": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int64)]),
+    "nb_nerf_save": (c_int, [c_void_p, ctypes.c_char_p]),
+    "nb_nerf_load": (c_int, [c_void_p, ctypes.c_char_p]),
 }
 
 _lib = None

@@ -1,0 +1,164 @@
+// Scene engine: owns the occupancy grid, both networks (in ONE parameter arena) and all scratch buffers, and
+// runs the optimizer step and the frame render.  Source-compatible with the reference's InstantNerf
+// (modules/NeRF/InstantNerf.h:35-76 NerfOptions, :279-334 class): same option struct (field order is part of
+// the .inerf file format), same public methods and argument meaning.
+//
+// What differs underneath (see InstantNerf.cu): one forward pass per step instead of two, one 16-byte read-back
+// per step instead of three, no pad/unpad copies between the networks, one Adam launch for everything, and a
+// hook between backward and optimizer for the data-parallel gradient all-reduce.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "TinyMLPHashGrid.h"
+
+#define MAX_HITS 1024  // per-ray sample cap
+
+enum MemoryMode { TRAINING, INFERENCE };
+
+struct NerfOptions {
+    uint3 gridResolution = make_uint3(128, 128, 128);
+    float3 aabbMin = make_float3(-1.0f, -1.0f, -1.0f);
+    float3 aabbMax = make_float3(1.0f, 1.0f, 1.0f);
+    int levelsMipmap = 4;
+    int numCascades = 1;
+    int samplesPerVoxel = 1;
+
+    int densityHiddenDim = 64;
+    int densityNumLayers = 2;
+
+    int colorHiddenDim = 64;
+    int colorNumLayers = 2;
+
+    int hashTableSize = 1 << 19;
+    int numLevels = 16;
+    float growthFactor = 1.3819f;
+    int baseResolution = 16;
+    int featuresPerLevel = 2;
+
+    int renderBatchSize = 2048 * 1024;
+    int batchSize = 256 * 1024;
+    int rayChunkSize = 256 * 1024;
+
+    float lambdaDepth = 0.02882f;
+    float lambdaDist = 0.0362781f;
+    float learningRate = 1e-3f;
+    float beta1 = 0.9f;
+    float beta2 = 0.999f;
+    float epsilon = 1e-8f;
+    float lossScale = 1.0f;
+
+    float3 bgColor = make_float3(1.0f, 1.0f, 1.0f);
+    float minDensityThreshold = 0.01;
+    float decayValue = 0.95f;
+    float densityBias = 1.0f;
+
+    bool legacyRenderFlag = false;
+    bool isProfiling = false;
+};
+
+// Per-phase device time of the last training steps / rendered frames (milliseconds, summed), filled when
+// NerfOptions.isProfiling is set.  Plays the role of the reference's GPUStats (InstantNerf.h:128-277).
+struct NerfPhaseTimes {
+    double march = 0, occupancy = 0, densityFwd = 0, shGather = 0, colorFwd = 0, compositing = 0, lossGrad = 0, colorBwd = 0,
+           densityGrad = 0, densityBwd = 0, scatter = 0, optimizer = 0;
+    long steps = 0;
+};
+
+class InstantNerf {
+public:
+    InstantNerf() = default;
+    ~InstantNerf();
+    InstantNerf(const InstantNerf&) = delete;
+    InstantNerf& operator=(const InstantNerf&) = delete;
+
+    void init(const NerfOptions& opts, MemoryMode memMode = TRAINING);
+    void printStats();
+    void resetStats();
+    void setLearningRate(float lr) { m_opts.learningRate = lr; }
+    void setBgColor(float3 c) { m_opts.bgColor = c; }
+    void setProfiling(bool p) { m_opts.isProfiling = p; }
+    void setMemoryMode(MemoryMode mode);
+
+    // One optimizer step per batch of whole rays that fits batchSize samples, until all numRays are consumed.
+    // d_rays_depth / d_rays_sigma (depth priors) and d_rgb_out / hitCounts may be null.
+    void trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_d, const float* d_rays_depth, const float* d_rays_sigma,
+                          const float* d_rgb_true, uint32_t numRays, int& trainStepCount, uint32_t* hitCounts, float* d_rgb_out,
+                          cudaStream_t stream);
+    void renderImageHit(const float3* d_rays_o, const float3* d_rays_d, uint32_t numRays, float* d_rgb_out, cudaStream_t stream);
+    // The reference keeps an older sparse-layout renderer under this name; here it is the same path as renderImageHit.
+    void renderImage(const float3* d_rays_o, const float3* d_rays_d, uint32_t numRays, float* d_rgb_out = nullptr, cudaStream_t stream = 0) {
+        renderImageHit(d_rays_o, d_rays_d, numRays, d_rgb_out, stream);
+    }
+
+    const NerfOptions& options() const { return m_opts; }
+    const uint8_t* occupancyGrid() { return d_occupancyGrid.as<uint8_t>(); }
+    size_t occupancyBytes() { return d_occupancyGrid.bytes(); }
+
+    void save(const std::string& filename);
+    void load(const std::string& filename);
+
+    // ---- additions (not in the reference) -------------------------------------------------------------
+    // Called on the gradient arena between backward and the optimizer of every step (data-parallel all-reduce).
+    using GradSync = std::function<void(float* d_grads, int64_t count, cudaStream_t stream)>;
+    void setGradSync(GradSync fn) { m_gradSync = std::move(fn); }
+    // Loss gradients are normalised by numRays * scale (the global ray count when ranks split a batch).
+    void setGlobalRayScale(uint32_t scale) { m_rayScale = scale ? scale : 1u; }
+    nb::ParamArena& arena() { return m_arena; }
+    TinyMLPHashGrid* densityNetwork() { return m_densityMLP; }
+    TinyMLP* colorNetwork() { return m_colorMLP; }
+    uint8_t* occupancyGridMutable() { return d_occupancyGrid.as<uint8_t>(); }
+    float* masterOccupancyGrid() { return d_masterOccupancyGrid.as<float>(); }
+    void rebuildOccupancy(cudaStream_t stream = 0) { earlyOccupancyGridUpdate(stream); }
+    int trainSteps() const { return m_trainSteps; }
+    uint32_t lastTotalHits() const { return m_lastTotalHits; }
+    const NerfPhaseTimes& phaseTimes() const { return m_times; }
+    // Buffers of the last step, for parity tests (valid until the next call).
+    struct StepView {
+        const uint32_t *num_steps, *ray_offsets, *ray_indices;
+        const float *t_sorted, *positions, *density_out, *sigma, *color_out, *render_rgb, *phi, *dw, *weight_sum, *tmp_dsigma;
+        const half *color_in, *color_grad, *density_grad;
+    };
+    StepView stepView() const;
+
+private:
+    void initRenderBuffers();
+    void freeBuffers();
+    void earlyOccupancyGridUpdate(cudaStream_t stream = 0);
+    void lateOccupancyGridUpdate(cudaStream_t stream = 0);
+    void finishOccupancyUpdate(cudaStream_t stream);
+    nb_scene_desc scene() const;
+    template <class F> void timed(cudaStream_t stream, double& acc, F&& f);
+
+    NerfOptions m_opts;
+    MemoryMode m_memMode = TRAINING;
+    nb::ParamArena m_arena;
+    TinyMLP* m_colorMLP = nullptr;
+    TinyMLPHashGrid* m_densityMLP = nullptr;
+    GradSync m_gradSync;
+    uint32_t m_rayScale = 1;
+    NerfPhaseTimes m_times;
+
+    nb::DeviceMem d_occupancyGrid, d_masterOccupancyGrid;
+    // per ray chunk
+    nb::DeviceMem d_rays_d_inv, d_nears, d_fars, d_num_steps, d_ray_offsets, d_block_sums, d_plan, d_render_rgb, d_render_depth, d_phi,
+        d_weight_sum;
+    // per sample batch
+    nb::DeviceMem d_positions, d_ray_indices, d_t_sorted, d_density_out, d_sigma, d_color_in, d_color_out, d_color_acts, d_enc, d_density_acts,
+        d_color_grad, d_color_dx, d_density_grad, d_denc, d_tmpsigma, d_dw;
+    // occupancy
+    nb::DeviceMem d_occ_samples, d_tmp_grid, d_sum, d_occ_scratch, d_active_cells, d_num_active;
+    uint32_t* h_plan = nullptr;  // pinned, 4 words
+
+    bool m_traininit = false;
+    bool m_renderinit = false;
+    int m_trainSteps = 0;
+    int m_optSteps = 0;  // Adam step counter (capped at 50000 for the bias corrections)
+    uint32_t m_lastTotalHits = 0;
+};

@@ -1,0 +1,145 @@
+"""Python handle on the C++ InstantNerf scene engine (include/nerf_b200.h, nb_nerf_*), used by the tests and
+the benchmark.  torch tensors supply device memory; all work happens inside libnerf_b200.so."""
+import ctypes
+import importlib
+
+import numpy as np
+
+nb = importlib.import_module("3dmaker_b200")
+
+PHASES = ("march", "occupancy", "density_fwd", "sh_gather", "color_fwd", "compositing", "loss_grad", "color_bwd", "density_grad",
+          "density_bwd", "scatter", "optimizer")
+
+
+def default_options(**overrides):
+    o = nb.NerfOptions()
+    nb.check(nb.load().nb_nerf_default_options(ctypes.byref(o)), "nb_nerf_default_options")
+    for k, v in overrides.items():
+        cur = getattr(o, k)
+        if hasattr(cur, "__len__"):
+            for i in range(len(cur)):
+                cur[i] = v[i]
+        else:
+            setattr(o, k, v)
+    return o
+
+
+class InstantNerf:
+    def __init__(self, torch, options, inference=False):
+        self.torch, self.lib, self.options = torch, nb.load(), options
+        self.h = self.lib.nb_nerf_create(ctypes.byref(options), 1 if inference else 0)
+        if not self.h:
+            raise nb.NerfB200Error("nb_nerf_create failed: " + self.lib.nb_last_error().decode())
+        self._cb = None
+        self.steps = ctypes.c_int(0)
+
+    def close(self):
+        if self.h:
+            self.lib.nb_nerf_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def train_rays(self, rays_o, rays_d, rgb_true, rgb_out=None, depth=None, sigma=None, stream=None):
+        n = rays_o.shape[0]
+        nb.check(self.lib.nb_nerf_train_rays(self.h, nb.ptr(rays_o), nb.ptr(rays_d), nb.ptr(depth), nb.ptr(sigma), nb.ptr(rgb_true), n,
+                                             ctypes.byref(self.steps), None, nb.ptr(rgb_out), nb.stream_ptr(stream)), "nb_nerf_train_rays")
+        return self.steps.value
+
+    def render(self, rays_o, rays_d, rgb_out, stream=None):
+        nb.check(self.lib.nb_nerf_render(self.h, nb.ptr(rays_o), nb.ptr(rays_d), rays_o.shape[0], nb.ptr(rgb_out), nb.stream_ptr(stream)),
+                 "nb_nerf_render")
+
+    def set_learning_rate(self, lr):
+        nb.check(self.lib.nb_nerf_set_learning_rate(self.h, lr))
+
+    def set_bg_color(self, r, g, b):
+        nb.check(self.lib.nb_nerf_set_bg_color(self.h, r, g, b))
+
+    def set_profiling(self, on):
+        nb.check(self.lib.nb_nerf_set_profiling(self.h, int(on)))
+
+    def set_memory_mode(self, inference):
+        nb.check(self.lib.nb_nerf_set_memory_mode(self.h, 1 if inference else 0), "nb_nerf_set_memory_mode")
+
+    def set_global_ray_scale(self, scale):
+        nb.check(self.lib.nb_nerf_set_global_ray_scale(self.h, scale))
+
+    def set_grad_sync(self, fn):
+        """fn(grad_tensor) is called between backward and Adam with a float32 view of the gradient arena."""
+        if fn is None:
+            self._cb = None
+            nb.check(self.lib.nb_nerf_set_grad_sync(self.h, nb.GRAD_SYNC_FN(0), None))
+            return
+        grad = self.arena_tensor("g")
+
+        def trampoline(user, ptr, count, stream):
+            fn(grad)
+        self._cb = nb.GRAD_SYNC_FN(trampoline)
+        nb.check(self.lib.nb_nerf_set_grad_sync(self.h, self._cb, None))
+
+    def arena(self):
+        v = nb.ArenaView()
+        nb.check(self.lib.nb_nerf_get_arena(self.h, ctypes.byref(v)), "nb_nerf_get_arena")
+        return v
+
+    def arena_tensor(self, which):
+        """Zero-copy torch view of one arena array ('w', 'g', 'm', 'v' float32; 'w_h' float16)."""
+        v = self.arena()
+        return _wrap(self.torch, getattr(v, which), v.total, np.float16 if which == "w_h" else np.float32)
+
+    def load_params(self, hash_f32=None, density=None, color=None):
+        P = lambda a: None if a is None else np.ascontiguousarray(a, np.float32).ctypes.data_as(ctypes.c_void_p)
+        keep = [None if a is None else np.ascontiguousarray(a, np.float32) for a in
+                (hash_f32, density[0] if density else None, density[1] if density else None, color[0] if color else None,
+                 color[1] if color else None)]
+        nb.check(self.lib.nb_nerf_load_params(self.h, *[None if a is None else a.ctypes.data_as(ctypes.c_void_p) for a in keep]),
+                 "nb_nerf_load_params")
+
+    def occupancy(self):
+        """(bitfield uint8 tensor view, master grid float32 tensor view)."""
+        bits, nbytes, master = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_void_p()
+        nb.check(self.lib.nb_nerf_occupancy(self.h, ctypes.byref(bits), ctypes.byref(nbytes), ctypes.byref(master)))
+        o = self.options
+        cells = o.num_cascades * o.grid_resolution[0] * o.grid_resolution[1] * o.grid_resolution[2]
+        return _wrap(self.torch, bits.value, nbytes.value, np.uint8), _wrap(self.torch, master.value, cells, np.float32)
+
+    def rebuild_occupancy(self, stream=None):
+        nb.check(self.lib.nb_nerf_rebuild_occupancy(self.h, nb.stream_ptr(stream)), "nb_nerf_rebuild_occupancy")
+
+    def step_view(self):
+        v = nb.StepView()
+        nb.check(self.lib.nb_nerf_get_step_view(self.h, ctypes.byref(v)))
+        return v
+
+    def phase_times(self):
+        arr = (ctypes.c_double * 12)()
+        steps = ctypes.c_int64()
+        nb.check(self.lib.nb_nerf_phase_times(self.h, arr, ctypes.byref(steps)))
+        return dict(zip(PHASES, list(arr))), steps.value
+
+    def save(self, path):
+        nb.check(self.lib.nb_nerf_save(self.h, path.encode()), "nb_nerf_save")
+
+    def load(self, path):
+        nb.check(self.lib.nb_nerf_load(self.h, path.encode()), "nb_nerf_load")
+
+
+class _CudaArrayView:
+    """Minimal __cuda_array_interface__ holder so torch can alias library-owned device memory."""
+
+    def __init__(self, ptr, count, dtype):
+        self.__cuda_array_interface__ = {"shape": (int(count),), "typestr": np.dtype(dtype).str, "data": (int(ptr), False), "version": 3,
+                                         "strides": None}
+
+
+def _wrap(torch, ptr, count, dtype):
+    return torch.as_tensor(_CudaArrayView(ptr, count, dtype), device="cuda")
+
+
+def view_tensor(torch, ptr, count, dtype):
+    return _wrap(torch, ptr, count, dtype)

@@ -243,6 +243,83 @@ int nb_occ_update_bitfield(const nb_scene_desc* scene, uint8_t* d_bitfield, cons
 /* Replaces extractActiveCells (otherKernels.cu:809-834); zeroes *d_num_active first. */
 int nb_occ_extract_active(const nb_scene_desc* scene, const uint8_t* d_bitfield, int* d_active_cells, int* d_num_active, void* stream);
 
+/* ---- scene engine (C handle over the InstantNerf host class) ------------------------------------- */
+
+/* Byte-for-byte mirror of NerfOptions (modules/NeRF/InstantNerf.h:35-76); the raw struct is also what the
+ * .inerf file stores after its magic. */
+typedef struct nb_nerf_options {
+    uint32_t grid_resolution[3];
+    float aabb_min[3];
+    float aabb_max[3];
+    int32_t levels_mipmap, num_cascades, samples_per_voxel;
+    int32_t density_hidden_dim, density_num_layers;
+    int32_t color_hidden_dim, color_num_layers;
+    int32_t hash_table_size, num_levels;
+    float growth_factor;
+    int32_t base_resolution, features_per_level;
+    int32_t render_batch_size, batch_size, ray_chunk_size;
+    float lambda_depth, lambda_dist, learning_rate, beta1, beta2, epsilon, loss_scale;
+    float bg_color[3];
+    float min_density_threshold, decay_value, density_bias;
+    uint8_t legacy_render_flag, is_profiling;
+} nb_nerf_options;
+
+typedef struct nb_nerf nb_nerf;
+typedef void (*nb_grad_sync_fn)(void* user, float* d_grads, int64_t count, void* stream);
+
+typedef struct nb_nerf_arena_view {
+    float* w; void* w_h; float* g; float* m; float* v;
+    int64_t total, sparse_count;
+    int64_t density_weight_offset, density_bias_offset, color_weight_offset, color_bias_offset;
+    int64_t density_weight_count, density_bias_count, color_weight_count, color_bias_count;
+} nb_nerf_arena_view;
+
+typedef struct nb_nerf_step_view {
+    const uint32_t *num_steps, *ray_offsets, *ray_indices;
+    const float *t_sorted, *positions, *density_out, *sigma, *color_out, *render_rgb, *phi, *dw, *weight_sum, *tmp_dsigma;
+    const void *color_in, *color_grad, *density_grad;
+    uint32_t last_total_hits;
+    int32_t train_steps;
+} nb_nerf_step_view;
+
+/* NerfOptions defaults (InstantNerf.h:35-76). */
+int nb_nerf_default_options(nb_nerf_options* out);
+/* InstantNerf::init (InstantNerf.cu:282-339); memory_mode 0 = TRAINING, 1 = INFERENCE.  NULL on failure. */
+nb_nerf* nb_nerf_create(const nb_nerf_options* options, int memory_mode);
+void nb_nerf_destroy(nb_nerf* h);
+/* InstantNerf::trainWithRaysHit (InstantNerf.cu:359-583): float3 rays, optional depth priors, float3 targets. */
+int nb_nerf_train_rays(nb_nerf* h, const float* d_rays_o, const float* d_rays_d, const float* d_rays_depth, const float* d_rays_sigma,
+                       const float* d_rgb_true, uint32_t num_rays, int* step_count, uint32_t* hit_counts, float* d_rgb_out, void* stream);
+/* InstantNerf::renderImageHit (InstantNerf.cu:713-864). */
+int nb_nerf_render(nb_nerf* h, const float* d_rays_o, const float* d_rays_d, uint32_t num_rays, float* d_rgb_out, void* stream);
+/* setLearningRate / setBgColor / setProfiling / setMemoryMode (InstantNerf.h:289-293). */
+int nb_nerf_set_learning_rate(nb_nerf* h, float lr);
+int nb_nerf_set_bg_color(nb_nerf* h, float r, float g, float b);
+int nb_nerf_set_profiling(nb_nerf* h, int on);
+int nb_nerf_set_memory_mode(nb_nerf* h, int memory_mode);
+/* Data parallelism (no counterpart in the reference, which is single-GPU): loss gradients are normalised by
+ * num_rays * scale, and fn runs on the gradient arena between backward and the optimizer of every step. */
+int nb_nerf_set_global_ray_scale(nb_nerf* h, uint32_t scale);
+int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user);
+/* Device pointers of the parameter arena [hash | density W,b | colour W,b] and the slice offsets. */
+int nb_nerf_get_arena(nb_nerf* h, nb_nerf_arena_view* out);
+/* loadHashgrid / loadWeights of both networks from host fp32 arrays (any may be NULL);
+ * TinyMLPHashGrid.cu:457-497, TinyMLP.cu:483-512. */
+int nb_nerf_load_params(nb_nerf* h, const float* hash, const float* density_w, const float* density_b, const float* color_w,
+                        const float* color_b);
+/* occupancyGrid() / occupancyBytes() (InstantNerf.h:327-328) and the fp32 master grid. */
+int nb_nerf_occupancy(nb_nerf* h, uint8_t** d_bitfield, int64_t* bitfield_bytes, float** d_master_grid);
+/* earlyOccupancyGridUpdate (InstantNerf.cu:1108-1171) on demand, e.g. after nb_nerf_load_params. */
+int nb_nerf_rebuild_occupancy(nb_nerf* h, void* stream);
+/* Buffers of the last step (parity tests). */
+int nb_nerf_get_step_view(nb_nerf* h, nb_nerf_step_view* out);
+/* Summed per-phase device milliseconds when profiling is on: march, occupancy, density fwd, SH, colour fwd,
+ * compositing, loss grad, colour bwd, density grad, density bwd, scatter, optimizer (GPUStats, InstantNerf.h:128-277). */
+int nb_nerf_phase_times(nb_nerf* h, double* out_ms12, int64_t* steps);
+/* InstantNerf::save / load, the .inerf format (InstantNerf.cu:1206-1352). */
+int nb_nerf_save(nb_nerf* h, const char* path);
+int nb_nerf_load(nb_nerf* h, const char* path);
+
 #ifdef __cplusplus
 }
 #endif

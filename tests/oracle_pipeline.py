@@ -26,3 +26,23 @@ class OracleField:
         g_table = orc.scatter_backward(pos4, d_enc, self.scales, self.T, self.dls)
         return dict(loss_sum=total, enc=enc, d_out=d_out, c_in=c_in, c_out=c_out, c_grad=c_grad, c_dx=c_dx, d_grad=d_grad,
                     d_enc=d_enc, g_table=g_table, g_dW=g_dW, g_db=g_db, g_cW=g_cW, g_cb=g_cb, sigma=sigma)
+
+
+def oracle_ray_step(field, march, dirs3, rgb_true, bg, lambda_dist, loss_scale, density_bias, total_rays):
+    """Everything of one NeRF optimizer step after the march, restated with oracle calls.
+    march = dict(num_steps, ray_offsets, ray_indices, t, pos4) for the rays of the step (ray order)."""
+    cnt, off, ridx, t, pos4 = (march[k] for k in ("num_steps", "ray_offsets", "ray_indices", "t", "pos4"))
+    R, n = len(cnt), len(t)
+    th = orc.half_bits(field.table)
+    enc = orc.encode_forward(pos4, th, field.scales, field.T, field.dls)
+    d_out, d_acts = orc.mlp_forward(enc, field.density_dims, orc.half_bits(field.dW), field.db, save_acts=True)
+    c_in, sigma = orc.sh_gather(dirs3, ridx, d_out, density_bias)
+    c_out, c_acts = orc.mlp_forward(c_in, field.color_dims, orc.half_bits(field.cW), field.cb, out_act=1, save_acts=True)
+    rgb, depth, phi, dw, wsum = orc.render_rays_distortion(R, off, cnt, t, sigma, c_out[:, :3].copy(), rgb_true, lambda_dist, 0.0, bg)
+    c_grad, dsig = orc.color_grad(R, cnt, off, t, d_out, c_out, phi, rgb, dw, wsum, loss_scale, density_bias, total_rays, grad_stride=8)
+    g_cW, g_cb, c_dx = orc.mlp_backward(c_grad, field.color_dims, orc.half_bits(field.cW), c_in, c_acts, want_dx=True)
+    d_grad = orc.density_grad(dsig, c_dx)
+    g_dW, g_db, d_enc = orc.mlp_backward(d_grad, field.density_dims, orc.half_bits(field.dW), enc, d_acts, want_dx=True)
+    g_table = orc.scatter_backward(pos4, d_enc, field.scales, field.T, field.dls)
+    return dict(d_out=d_out, sigma=sigma, c_in=c_in, c_out=c_out, rgb=rgb, phi=phi, dw=dw, wsum=wsum, c_grad=c_grad, dsig=dsig, d_grad=d_grad,
+                g_table=g_table, g_dW=g_dW, g_db=g_db, g_cW=g_cW, g_cb=g_cb)
