@@ -1,0 +1,269 @@
+"""GPU-vs-GPU parity against the reference's OWN CUDA code (oracle/_ref/libref3dmaker.so, built from the
+reference sources for sm_100a by oracle/build_ref.py).  Both libraries run in this process on the same seeded
+inputs.  Skipped when the reference build is not present.
+
+Bars: integer pipelines (ray counts, offsets, ray ids, occupancy samples' cell ids) bit-exact; sample positions
+and t bitwise equal where the two builds make the same contraction choices, else to float error; encoded
+features / network outputs / gradients within the stated relative tolerances; PSNR after a fixed number of
+steps within 0.2 dB."""
+import ctypes
+import importlib
+
+import numpy as np
+import pytest
+
+from helpers import ABS_RGB, REL_MLP, Uploader, dev_half_bits, half_bits, half_vals, make_mlp, make_positions, make_table, mlp_dims, rel_err
+from test_oracle_nerf_cpu import camera_rays, sphere_bitfield
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ref():
+    from oracle import ref_cuda
+    if not ref_cuda.available():
+        pytest.skip("reference CUDA build (oracle/_ref) not present")
+    ref_cuda.lib()
+    return ref_cuda
+
+
+def _dirs(n, seed):
+    rng = np.random.default_rng(seed)
+    d = rng.normal(size=(n, 3)).astype(np.float32)
+    return d / np.linalg.norm(d, axis=1, keepdims=True)
+
+
+def _field_pair(torch, nb, ref, L, T, b, n, seed=0):
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    table = make_table(L, T, seed=seed, amp=0.1)
+    dW, db = make_mlp(32, 64, 16, 2, seed=seed, bias_amp=0.02)
+    cW, cb = make_mlp(32, 64, 8, 3, seed=seed + 1, bias_amp=0.02)
+    model = pl.FieldModel(torch, L, T, 16, b, 64, 2, 64, 3)
+    model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
+    tr = pl.SampleTrainer(model, n, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=1.0)
+    rf = ref.lib().ref_field_create(L, T, 16, b, 64, 2, 64, 3, n)
+    flat = np.ascontiguousarray(table.ravel())
+    ref.lib().ref_field_load(rf, ref.hptr(flat), ref.hptr(dW), ref.hptr(db), ref.hptr(cW), ref.hptr(cb))
+    return model, tr, rf, (table, dW, db, cW, cb)
+
+
+@pytest.mark.parametrize("b", [1.3819, 1.447])
+def test_field_forward_backward_against_reference_kernels(cuda, nb, ref, b):
+    torch = cuda
+    nm = importlib.import_module("3dmaker_b200.nerf")
+    L, T, n = 16, 1 << 17, 20000
+    model, tr, rf, _ = _field_pair(torch, nb, ref, L, T, b, n)
+    rng = np.random.default_rng(3)
+    pos = make_positions(n, 3); dirs = _dirs(n, 4)
+    tgt3 = rng.random((n, 3), dtype=np.float32)
+    tgt8 = np.zeros((n, 8), np.float32); tgt8[:, :3] = tgt3
+    tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(half_bits(tgt8).view(np.float16)))
+    tr.forward_backward(n)
+    d_t3 = torch.from_numpy(half_bits(tgt3).view(np.float16)).cuda()
+    st = nb.stream_ptr()
+    ref.lib().ref_field_forward_backward(rf, nb.ptr(tr.pos), nb.ptr(tr.dirs), nb.ptr(d_t3), n, 1.0, 128.0, st)
+    torch.cuda.synchronize()
+    V = lambda p, cnt, dt=np.float32: nm.view_tensor(torch, p, cnt, dt).cpu().numpy()
+    r_dout = V(ref.lib().ref_field_density_out(rf), n * 16).reshape(n, 16)
+    r_cout = V(ref.lib().ref_field_color_out(rf), n * 3).reshape(n, 3)
+    r_cin = V(ref.lib().ref_field_color_in(rf), n * 32, np.float16).view(np.uint16).reshape(n, 32)
+    assert rel_err(tr.d_out.cpu().numpy(), r_dout) <= REL_MLP
+    assert np.max(np.abs(tr.c_out.cpu().numpy()[:, :3] - r_cout)) <= 1e-2
+    # SH half of the colour input: same formula, same rounding -> identical bits
+    assert np.array_equal(dev_half_bits(tr.c_in)[:, 16:], r_cin[:, 16:])
+    g = model.g.cpu().numpy()
+    H = model.hash_count
+    r_hash = V(ref.lib().ref_field_hash_grads(rf), H)
+    assert rel_err(g[:H], r_hash) <= 3 * REL_MLP
+    # touched sets agree except where a weight underflows on one side
+    assert np.mean((g[:H] != 0) != (r_hash != 0)) < 1e-3
+    for net, (off_w, off_b, dims) in enumerate(((model.off_dw, model.off_db, mlp_dims(32, 64, 16, 2)), (model.off_cw, model.off_cb, mlp_dims(32, 64, 8, 3)))):
+        wo, bo = off_w, off_b
+        for l, (ki, ko) in enumerate(dims):
+            rw = V(ref.lib().ref_field_layer_grads(rf, net, l, 0), ki * ko)
+            rb = V(ref.lib().ref_field_layer_grads(rf, net, l, 1), ko)
+            assert rel_err(g[wo:wo + ki * ko], rw) <= 3 * REL_MLP, ("dW", net, l)
+            assert rel_err(g[bo:bo + ko], rb) <= 3 * REL_MLP, ("db", net, l)
+            wo += ki * ko; bo += ko
+    ref.lib().ref_field_destroy(rf)
+
+
+def test_training_steps_track_the_reference(cuda, nb, ref):
+    """30 optimizer steps from identical parameters on identical batches: the losses of the two implementations
+    stay together."""
+    torch = cuda
+    nm = importlib.import_module("3dmaker_b200.nerf")
+    L, T, n = 16, 1 << 17, 16384
+    model, tr, rf, _ = _field_pair(torch, nb, ref, L, T, 1.3819, n, seed=5)
+    st = nb.stream_ptr()
+    ours, theirs = [], []
+    for it in range(30):
+        rng = np.random.default_rng(100 + it)
+        pos = make_positions(n, 200 + it); dirs = _dirs(n, 300 + it)
+        tgt3 = pos[:, :3].copy()                                    # learn colour = position
+        tgt8 = np.zeros((n, 8), np.float32); tgt8[:, :3] = tgt3
+        tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(half_bits(tgt8).view(np.float16)))
+        d_t3 = torch.from_numpy(half_bits(tgt3).view(np.float16)).cuda()
+        ref.lib().ref_field_forward(rf, nb.ptr(tr.pos), nb.ptr(tr.dirs), n, 1.0, st)
+        torch.cuda.synchronize()
+        r_c = nm.view_tensor(torch, ref.lib().ref_field_color_out(rf), n * 3, np.float32).cpu().numpy().reshape(n, 3)
+        theirs.append(float(((r_c - tgt3) ** 2).mean()))
+        ref.lib().ref_field_train_step(rf, nb.ptr(tr.pos), nb.ptr(tr.dirs), nb.ptr(d_t3), n, 1.0, 128.0, 1e-2, 0.9, 0.99, 1e-15, st)
+        tr.step_device(n)
+        torch.cuda.synchronize()
+        ours.append(tr.loss.item() / (n * 3))
+    ours, theirs = np.array(ours), np.array(theirs)
+    assert ours[-1] < 0.5 * ours[0] and theirs[-1] < 0.5 * theirs[0]
+    assert np.max(np.abs(ours - theirs) / theirs) < 0.05, (ours, theirs)
+    ref.lib().ref_field_destroy(rf)
+
+
+@pytest.mark.parametrize("cascades,spv", [(1, 1), (3, 1), (1, 2)])
+def test_march_is_bit_exact_against_reference(cuda, nb, ref, orc, cascades, spv):
+    torch = cuda
+    up = Uploader(torch, nb)
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    res, levels, R, batch = (128, 128, 128), 4, 30000, 1 << 18
+    sc = nb.scene_desc(res, [-.5] * 3, [.5] * 3, cascades, levels, spv)
+    bits = sphere_bitfield(orc, res, levels, cascades)
+    o, d = camera_rays(R, seed=7)
+    d_o, d_d = up.f(o), up.f(d)
+    d_bits = torch.from_numpy(bits).cuda()
+    f32, i32 = torch.float32, torch.int32
+    Z = lambda *shape, dt=f32: torch.zeros(shape, dtype=dt, device="cuda")
+    mine = dict(dinv=Z(R, 3), near=Z(R), far=Z(R), steps=Z(R, dt=i32), offs=Z(R, dt=i32), t=Z(batch), ray=Z(batch, dt=i32), pos=Z(batch, 4),
+                bs=Z(64, dt=i32), plan=Z(4, dt=i32))
+    theirs = dict(dinv=Z(R, 3), near=Z(R), far=Z(R), steps=Z(R, dt=i32), offs=Z(R, dt=i32), t=Z(batch), ray=Z(batch, dt=i32), pos=Z(batch, 4),
+                  bs=Z(64, dt=i32), act=Z(1, dt=i32))
+    nb.check(lib.nb_ray_aabb(ctypes.byref(sc), d_o, d_d, R, P(mine["dinv"]), P(mine["near"]), P(mine["far"]), st))
+    nb.check(lib.nb_march_count(ctypes.byref(sc), d_o, d_d, P(mine["dinv"]), P(mine["near"]), P(mine["far"]), P(d_bits), R, P(mine["steps"]), st))
+    nb.check(lib.nb_march_scan(P(mine["steps"]), P(mine["offs"]), P(mine["bs"]), R, batch, P(mine["plan"]), st))
+    nb.check(lib.nb_march_emit(ctypes.byref(sc), d_o, d_d, P(mine["dinv"]), P(mine["near"]), P(mine["far"]), P(d_bits), R, 0, R, P(mine["offs"]),
+                               P(mine["plan"]), P(mine["t"]), P(mine["ray"]), P(mine["pos"]), st))
+    amin = np.array([-.5] * 3, np.float32); amax = np.array([.5] * 3, np.float32); r3 = np.array(res, np.uint32)
+    ref.lib().ref_ray_aabb(R, d_o, d_d, ref.hptr(amin), ref.hptr(amax), cascades, P(theirs["dinv"]), P(theirs["near"]), P(theirs["far"]), st)
+    total = ctypes.c_uint(0)
+    active = ref.lib().ref_process_rays_hit_linear(R, d_o, d_d, P(theirs["dinv"]), P(theirs["near"]), P(theirs["far"]), P(d_bits), ref.hptr(r3),
+                                                   ref.hptr(amin), ref.hptr(amax), cascades, levels, spv, batch, ctypes.byref(total), P(theirs["act"]),
+                                                   P(theirs["steps"]), P(theirs["offs"]), P(theirs["pos"]), P(theirs["ray"]), P(theirs["t"]),
+                                                   P(theirs["bs"]), st)
+    torch.cuda.synchronize()
+    plan = mine["plan"].cpu().numpy()
+    for k in ("dinv", "near", "far"):
+        assert torch.equal(mine[k], theirs[k]), k
+    assert torch.equal(mine["steps"], theirs["steps"]) and torch.equal(mine["offs"], theirs["offs"])
+    assert plan[0] == active and plan[1] == total.value and 0 < active < R
+    n = total.value
+    assert torch.equal(mine["ray"][:n], theirs["ray"][:n])
+    same_t = torch.equal(mine["t"][:n], theirs["t"][:n]); same_p = torch.equal(mine["pos"][:n], theirs["pos"][:n])
+    if not (same_t and same_p):
+        dt = (mine["t"][:n] - theirs["t"][:n]).abs().max().item(); dp = (mine["pos"][:n] - theirs["pos"][:n]).abs().max().item()
+        assert dt <= 2e-6 and dp <= 2e-7, "t / positions differ beyond float error: %g %g" % (dt, dp)
+
+
+def test_compositing_and_loss_gradients_against_reference_kernels(cuda, nb, ref):
+    torch = cuda
+    up = Uploader(torch, nb)
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    from test_gpu_nerf import _random_ray_samples
+    counts, off, t, dens, col, target = _random_ray_samples(6000, 9)
+    R, n = len(counts), len(t)
+    bias, lam, scale = 1.0, 0.1, 128.0
+    sigma = np.exp(np.minimum(dens[:, 0] - np.float32(bias), 8)).astype(np.float32)
+    bgn = np.array([1.0, 0.5, 0.25], np.float32); bg = (ctypes.c_float * 3)(*bgn)
+    f32 = torch.float32
+    Z = lambda *shape, dt=f32: torch.zeros(shape, dtype=dt, device="cuda")
+    d_off, d_cnt, d_t, d_sig, d_col8, d_col3, d_tgt, d_dens = (up.f(off.view(np.int32)), up.f(counts.view(np.int32)), up.f(t), up.f(sigma), up.f(col),
+                                                              up.f(np.ascontiguousarray(col[:, :3])), up.f(target), up.f(dens))
+    m = dict(rgb=Z(R, 3), depth=Z(R), phi=Z(R, 3), dw=Z(n), ws=Z(R), grad=Z(n, 8, dt=torch.float16), dsig=Z(n))
+    r = dict(rgb=Z(R, 3), depth=Z(R), phi=Z(R, 3), dw=Z(n), ws=Z(R), grad=Z(n, 3, dt=torch.float16), dsig=Z(n))
+    nb.check(lib.nb_composite_train(R, d_off, d_cnt, d_t, d_sig, None, None, d_col8, 8, d_tgt, P(m["rgb"]), P(m["depth"]), P(m["phi"]), P(m["dw"]),
+                                    P(m["ws"]), lam, 0.0, bg, st))
+    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, d_dens, d_col8, 8, P(m["phi"]), P(m["rgb"]), P(m["dw"]), P(m["ws"]), P(m["grad"]), 8, P(m["dsig"]),
+                               scale, bias, R, st))
+    ref.lib().ref_volume_rendering(R, d_off, d_cnt, d_t, d_sig, d_col3, d_tgt, P(r["rgb"]), P(r["depth"]), P(r["phi"]), P(r["dw"]), P(r["ws"]), lam, 0.0,
+                                   ref.hptr(bgn), 0, 0, st)
+    ref.lib().ref_color_grad(R, d_cnt, d_off, d_t, d_dens, d_col3, P(r["phi"]), P(r["rgb"]), P(r["dw"]), P(r["ws"]), P(r["grad"]), P(r["dsig"]), scale,
+                             bias, R, st)
+    torch.cuda.synchronize()
+    assert (m["rgb"] - r["rgb"]).abs().max().item() <= 1e-5 and (m["phi"] - r["phi"]).abs().max().item() <= 2e-5
+    assert rel_err(m["dw"].cpu().numpy(), r["dw"].cpu().numpy()) <= 1e-4 and rel_err(m["ws"].cpu().numpy(), r["ws"].cpu().numpy()) <= 1e-4
+    assert rel_err(half_vals(dev_half_bits(m["grad"]))[:, :3], half_vals(dev_half_bits(r["grad"]))) <= 1e-3
+    assert rel_err(m["dsig"].cpu().numpy(), r["dsig"].cpu().numpy()) <= 1e-3
+    # inference compositing (early termination)
+    rgb_m, rgb_r = Z(R, 3), Z(R, 3)
+    nb.check(lib.nb_composite_infer(R, 0, 0, d_off, d_cnt, d_t, d_sig, d_col8, 8, None, P(rgb_m), None, None, bg, st))
+    dep = Z(R)
+    ref.lib().ref_volume_rendering(R, d_off, d_cnt, d_t, d_sig, d_col3, None, P(rgb_r), P(dep), None, None, None, 0.0, 0.0, ref.hptr(bgn), 0, 0, st)
+    torch.cuda.synchronize()
+    assert (rgb_m - rgb_r).abs().max().item() <= 1e-5
+
+
+def test_occupancy_samples_are_bit_identical(cuda, nb, ref):
+    torch = cuda
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    res = (64, 64, 64)
+    sc = nb.scene_desc(res, [-.5] * 3, [.5] * 3, 2, 3, 1)
+    G = 64 ** 3
+    a, b = torch.zeros((G, 4), device="cuda"), torch.zeros((G, 4), device="cuda")
+    amin = np.array([-.5] * 3, np.float32); amax = np.array([.5] * 3, np.float32); r3 = np.array(res, np.uint32)
+    for (n, total, offset, seed) in ((G, G, G, 5), (50000, 2 * G, 0, 6)):
+        nb.check(lib.nb_occ_sample_cells(ctypes.byref(sc), P(a), n, total, offset, seed, st))
+        ref.lib().ref_sample_aabb(P(b), ref.hptr(amin), ref.hptr(amax), ref.hptr(r3), n, total, offset, seed, st)
+        torch.cuda.synchronize()
+        assert torch.equal(a[:n].view(torch.int32), b[:n].view(torch.int32))
+
+
+def test_scene_engines_agree(cuda, nb, ref):
+    """Same options, same parameters, same rays: occupancy bits, a rendered frame, and PSNR after 300 steps."""
+    torch = cuda
+    nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
+    T = 1 << 19
+    opts = nm.default_options(grid_resolution=(128,) * 3, aabb_min=(-.5,) * 3, aabb_max=(.5,) * 3, levels_mipmap=4, hash_table_size=T,
+                              growth_factor=1.3819, color_hidden_dim=64, color_num_layers=3, batch_size=1 << 18, render_batch_size=1 << 18,
+                              ray_chunk_size=1 << 16, lambda_dist=0.01, lambda_depth=0.0, learning_rate=1e-2, beta2=0.99, epsilon=1e-15,
+                              loss_scale=128.0, density_bias=1.0, bg_color=(1.0, 1.0, 1.0))
+    assert ref.lib().ref_nerf_options_size() == ctypes.sizeof(opts)
+    eng = nm.InstantNerf(torch, opts)
+    rh = ref.lib().ref_nerf_create(ctypes.byref(opts), 0)
+    # identical starting parameters: take ours (seed 42 as the reference's constructors) and push them into the reference
+    a = eng.arena()
+    w = eng.arena_tensor("w").cpu().numpy()
+    H = a.sparse_count
+    sl = lambda o, c: np.ascontiguousarray(w[o:o + c])
+    hash_w, dW, db = sl(0, H), sl(a.density_weight_offset, a.density_weight_count), sl(a.density_bias_offset, a.density_bias_count)
+    cW, cb = sl(a.color_weight_offset, a.color_weight_count), sl(a.color_bias_offset, a.color_bias_count)
+    r_hash, r_dW, r_db, r_cW, r_cb = (np.zeros_like(x) for x in (hash_w, dW, db, cW, cb))
+    ref.lib().ref_nerf_save_params(rh, ref.hptr(r_hash), ref.hptr(r_dW), ref.hptr(r_db), ref.hptr(r_cW), ref.hptr(r_cb))
+    # both constructors draw from std::mt19937(42) in the same order: the initial parameters are identical already
+    assert np.array_equal(r_hash, hash_w) and np.array_equal(r_dW, dW) and np.array_equal(r_cW, cW)
+    bits, _ = eng.occupancy()
+    nbytes = ctypes.c_long()
+    r_bits = nm.view_tensor(torch, ref.lib().ref_nerf_bitfield(rh, ctypes.byref(nbytes)), bits.numel(), np.uint8)
+    assert nbytes.value == bits.numel()
+    dis = np.unpackbits((bits ^ r_bits).cpu().numpy()).mean()
+    print("initial occupancy bit disagreement rate: %.2e" % dis)
+    assert dis < 2e-3
+    scene = syn.SoftSphereScene(); poses = syn.sphere_cameras(100); bg = (1.0, 1.0, 1.0)
+    R = 1 << 16
+    depth = torch.full((R,), -1.0, device="cuda"); sig = torch.ones(R, device="cuda")
+    st = nb.stream_ptr()
+    it = 0
+    while eng.steps.value < 300:
+        o, d = syn.random_training_rays(torch, poses, R, 800, 800, 50.0, seed=500 + it)
+        tgt = syn.ground_truth(torch, scene, o, d, bg)
+        eng.train_rays(o, d, tgt)
+        ref.lib().ref_nerf_train(rh, nb.ptr(o), nb.ptr(d), nb.ptr(depth), nb.ptr(sig), nb.ptr(tgt), R, None, None, st)
+        it += 1
+    torch.cuda.synchronize()
+    o, d = syn.frame_rays(torch, syn.orbit_c2w(33.0, 20.0, 1.5), 200, 200, 50.0)
+    gt = syn.ground_truth(torch, scene, o, d, bg)
+    img, r_img = torch.zeros_like(gt), torch.zeros_like(gt)
+    eng.render(o, d, img)
+    ref.lib().ref_nerf_render(rh, nb.ptr(o), nb.ptr(d), o.shape[0], nb.ptr(r_img), st)
+    torch.cuda.synchronize()
+    p, rp = syn.psnr(torch, img, gt), syn.psnr(torch, r_img, gt)
+    print("PSNR after ~300 steps: ours %.2f dB, reference %.2f dB" % (p, rp))
+    assert abs(p - rp) <= 0.2 or p > rp
+    ref.lib().ref_nerf_destroy(rh)
+    eng.close()
