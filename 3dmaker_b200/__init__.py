@@ -32,6 +32,7 @@ class GridDesc(ctypes.Structure):
         ("dense_level_start", ctypes.c_int32),
         ("growth", ctypes.c_float),
         ("scales", ctypes.c_float * NB_MAX_LEVELS),
+        ("scatter_scales", ctypes.c_float * NB_MAX_LEVELS),
     ]
 
 

@@ -19,25 +19,29 @@ extern std::atomic<uint64_t> g_launch_count;
 
 struct GridParams {
     int L, T, dls;
-    float scales[NB_MAX_LEVELS];
+    float scales[NB_MAX_LEVELS];   // forward (encode) resolutions
+    float sscales[NB_MAX_LEVELS];  // resolutions of the gradient scatter
 };
 
 static GridParams make_params(const nb_grid_desc* d) {
     GridParams p;
     p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start;
-    for (int i = 0; i < NB_MAX_LEVELS; i++) p.scales[i] = d->scales[i];
+    for (int i = 0; i < NB_MAX_LEVELS; i++) { p.scales[i] = d->scales[i]; p.sscales[i] = d->scatter_scales[i]; }
     return p;
 }
 
-// Resolution of every level, with the forward kernel's expression sequence: a power at levels 0,4,8,12 and
+// Resolution of every level.  out[l]: the forward kernel's expression sequence, a power at levels 0,4,8,12 and
 // repeated multiplication by b in between (modules/TinyMLP/networkFusionHashtable.cu:124-128,218).
-__global__ void level_scales_kernel(int lowestSize, float b, int L, float* out) {
+// out[NB_MAX_LEVELS + l]: the split scatter kernel's expression (networkFusionBackwardHashtable.cu:805).
+__global__ void level_scales_kernel(int lowestSize, float b, float log2b, int L, float* out) {
     int l = threadIdx.x;
     if (l >= L) return;
     int levelStart = (l / 4) * 4;
     float N_l_float = lowestSize * __powf(b, levelStart);
     for (int i = levelStart; i < l; i++) N_l_float *= b;
     out[l] = N_l_float;
+    int level = l;
+    out[NB_MAX_LEVELS + l] = lowestSize * exp2f(level * log2b);
 }
 
 __device__ __forceinline__ uint32_t hash_coords(int cx, int cy, int cz, int T) {
@@ -170,7 +174,7 @@ __global__ void hash_indices_kernel(const __grid_constant__ GridParams gp, const
     float4 pt = ld_nc_f4(pos4 + p * 4);
     Corners c;
     if (clamp_mode == 0) corners_of<false>(pt.x, pt.y, pt.z, gp.scales[l], l < gp.dls, gp.T, c);
-    else corners_of<true>(pt.x, pt.y, pt.z, gp.scales[l], l < gp.dls, gp.T, c);
+    else corners_of<true>(pt.x, pt.y, pt.z, gp.sscales[l], l < gp.dls, gp.T, c);
 #pragma unroll
     for (int k = 0; k < 8; k++) idx_out[i * 8 + k] = (uint32_t)l * (uint32_t)gp.T * 2u + c.idx[k] * 2u;
 }
@@ -222,7 +226,7 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
     float4 p = ld_nc_f4(pos4 + i * 4);
     const bool dense = level < gp.dls;
     Corners c;
-    corners_of<true>(p.x, p.y, p.z, gp.scales[level], dense, gp.T, c);
+    corners_of<true>(p.x, p.y, p.z, gp.sscales[level], dense, gp.T, c);
     float w[8];
     corner_weights(c, w);
     float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * (2 * gp.L) + 2 * level]));
@@ -291,7 +295,7 @@ extern "C" int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size,
     desc->base_resolution = base_resolution;
     desc->growth = growth;
     desc->dense_level_start = 0;
-    for (int i = 0; i < NB_MAX_LEVELS; i++) desc->scales[i] = 0.f;
+    for (int i = 0; i < NB_MAX_LEVELS; i++) desc->scales[i] = desc->scatter_scales[i] = 0.f;
     int rc = check_desc(desc, "nb_grid_setup");
     if (rc != NB_OK) return rc;
     if (base_resolution < 1 || !(growth > 1.0f)) return nb_set_error(NB_ERR_INVALID, "nb_grid_setup: base_resolution >= 1 and growth > 1 required");
@@ -304,10 +308,12 @@ extern "C" int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size,
 
     cudaStream_t st = (cudaStream_t)stream;
     float* d_scales = nullptr;
-    NB_CUDA(cudaMalloc(&d_scales, NB_MAX_LEVELS * sizeof(float)));
-    level_scales_kernel<<<1, 32, 0, st>>>(base_resolution, growth, num_levels, d_scales);
+    NB_CUDA(cudaMalloc(&d_scales, 2 * NB_MAX_LEVELS * sizeof(float)));
+    level_scales_kernel<<<1, 32, 0, st>>>(base_resolution, growth, std::log2(growth), num_levels, d_scales);
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaMemcpyAsync(desc->scales, d_scales, num_levels * sizeof(float), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(desc->scatter_scales, d_scales + NB_MAX_LEVELS, num_levels * sizeof(float), cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     cudaFree(d_scales);
     if (e != cudaSuccess) return nb_set_cuda_error(e);
@@ -321,10 +327,10 @@ extern "C" int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size,
 // Some host programs may not allocate device memory at the point where they configure a grid: a renderer
 // plug-in that was handed a fixed memory budget by its host application, a process whose allocator is
 // locked while a CUDA graph is being recorded, or a real-time loop that forbids cudaMalloc because it
-// synchronises the whole device.  For them the 16-float scratch that nb_grid_setup allocates and frees lives
-// in the library image instead: every GPU that loads the library holds these 256 bytes until exit.
+// synchronises the whole device.  For them the 32-float scratch that nb_grid_setup allocates and frees lives
+// in the library image instead: every GPU that loads the library holds these 128 bytes (one 256-byte aligned slot) until exit.
 // ---------------------------------------------------------------------------------------------------
-static __device__ __align__(256) float g_static_level_scales[NB_MAX_LEVELS];
+static __device__ __align__(256) float g_static_level_scales[2 * NB_MAX_LEVELS];
 
 // Device address of g_static_level_scales on each device, looked up on the first call made with that
 // device current.  In host code the array's name is only a handle for cudaGetSymbolAddress, never a pointer
@@ -341,7 +347,7 @@ extern "C" int nb_grid_setup_noalloc(nb_grid_desc* desc, int num_levels, int tab
     desc->base_resolution = base_resolution;
     desc->growth = growth;
     desc->dense_level_start = 0;
-    for (int i = 0; i < NB_MAX_LEVELS; i++) desc->scales[i] = 0.f;
+    for (int i = 0; i < NB_MAX_LEVELS; i++) desc->scales[i] = desc->scatter_scales[i] = 0.f;
     int rc = check_desc(desc, "nb_grid_setup_noalloc");
     if (rc != NB_OK) return rc;
     if (base_resolution < 1 || !(growth > 1.0f))
@@ -363,10 +369,11 @@ extern "C" int nb_grid_setup_noalloc(nb_grid_desc* desc, int num_levels, int tab
     float* d_scales = g_static_level_scales_addr[dev];
     cudaStream_t st = (cudaStream_t)stream;
     // the kernel writes entries [0, num_levels) and only those are read back, so nothing has to start at zero
-    level_scales_kernel<<<1, 32, 0, st>>>(base_resolution, growth, num_levels, d_scales);
+    level_scales_kernel<<<1, 32, 0, st>>>(base_resolution, growth, std::log2(growth), num_levels, d_scales);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     NB_CUDA(cudaMemcpyAsync(desc->scales, d_scales, num_levels * sizeof(float), cudaMemcpyDeviceToHost, st));
+    NB_CUDA(cudaMemcpyAsync(desc->scatter_scales, d_scales + NB_MAX_LEVELS, num_levels * sizeof(float), cudaMemcpyDeviceToHost, st));
     NB_CUDA(cudaStreamSynchronize(st));
     return NB_OK;
 }

@@ -44,6 +44,8 @@ typedef struct nb_grid_desc {
     int32_t dense_level_start; /* first hashed level (levels below use dense indexing) */
     float growth;              /* b */
     float scales[NB_MAX_LEVELS]; /* per-level resolution N_l as the forward kernel computes it */
+    float scatter_scales[NB_MAX_LEVELS]; /* N_l as the reference's gradient scatter computes it:
+                                            lowestSize * exp2f(level * log2(b)), a few ulp away from scales[] */
 } nb_grid_desc;
 
 /* Mirrors MLPOption (modules/TinyMLP/TinyMLP.h:26-33) with dims already padded the way the
@@ -70,15 +72,18 @@ int nb_zero_async(void* d_ptr, int64_t bytes, void* stream);
 
 /* ---- hash grid --------------------------------------------------------------------------- */
 
-/* Fills dense_level_start (host float math of networkFusionHashtable.cu:367-377) and scales[]
+/* Fills dense_level_start (host float math of networkFusionHashtable.cu:367-377), scales[]
  * (computed on the device with the forward kernel's own expression sequence, restarted every four
- * levels, networkFusionHashtable.cu:124-128,218).  Synchronises the stream once. */
+ * levels, networkFusionHashtable.cu:124-128,218) and scatter_scales[] (the expression of the split
+ * scatter kernel, networkFusionBackwardHashtable.cu:805, with log2(b) taken on the host as its launcher
+ * does, :994).  The reference encodes with the first and scatters with the second; so do we.
+ * Synchronises the stream once. */
 int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size, int base_resolution, float growth, void* stream);
 
 /* nb_grid_setup for callers that must not allocate device memory (no counterpart in the reference,
  * whose launchers recompute the geometry inside every kernel).  Think of a plug-in running inside a
  * host application's fixed memory budget, or a loop that cannot afford the device-wide synchronisation
- * of cudaMalloc/cudaFree.  Same inputs, same results as nb_grid_setup; the 16-float scratch the set-up
+ * of cudaMalloc/cudaFree.  Same inputs, same results as nb_grid_setup; the 32-float scratch the set-up
  * kernel writes is a static device array inside the library (256 bytes per GPU, held until the process
  * exits) instead of a cudaMalloc'd buffer, and no cudaMalloc, cudaFree or other allocating call is made.
  * Limits and rules:

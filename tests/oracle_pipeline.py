@@ -6,8 +6,10 @@ import oracle as orc
 
 
 class OracleField:
-    def __init__(self, L, T, base, growth, scales, dls, density_dims, color_dims, table_f32, dW, db, cW, cb):
+    def __init__(self, L, T, base, growth, scales, dls, density_dims, color_dims, table_f32, dW, db, cW, cb, scatter_scales=None):
         self.L, self.T, self.scales, self.dls = L, T, np.asarray(scales, np.float32), dls
+        # the reference scatters with its own expression of the level resolutions (a few ulp from the forward's)
+        self.scatter_scales = self.scales if scatter_scales is None else np.asarray(scatter_scales, np.float32)
         self.density_dims, self.color_dims = density_dims, color_dims
         self.table = np.ascontiguousarray(table_f32, np.float32).ravel().copy()
         self.dW, self.db, self.cW, self.cb = (np.asarray(a, np.float32).copy() for a in (dW, db, cW, cb))
@@ -23,7 +25,7 @@ class OracleField:
         g_cW, g_cb, c_dx = orc.mlp_backward(c_grad, self.color_dims, orc.half_bits(self.cW), c_in, c_acts, want_dx=True)
         d_grad = orc.density_grad(np.zeros(n, np.float32), c_dx)
         g_dW, g_db, d_enc = orc.mlp_backward(d_grad, self.density_dims, orc.half_bits(self.dW), enc, d_acts, want_dx=True)
-        g_table = orc.scatter_backward(pos4, d_enc, self.scales, self.T, self.dls)
+        g_table = orc.scatter_backward(pos4, d_enc, self.scatter_scales, self.T, self.dls)
         return dict(loss_sum=total, enc=enc, d_out=d_out, c_in=c_in, c_out=c_out, c_grad=c_grad, c_dx=c_dx, d_grad=d_grad,
                     d_enc=d_enc, g_table=g_table, g_dW=g_dW, g_db=g_db, g_cW=g_cW, g_cb=g_cb, sigma=sigma)
 
@@ -43,6 +45,6 @@ def oracle_ray_step(field, march, dirs3, rgb_true, bg, lambda_dist, loss_scale, 
     g_cW, g_cb, c_dx = orc.mlp_backward(c_grad, field.color_dims, orc.half_bits(field.cW), c_in, c_acts, want_dx=True)
     d_grad = orc.density_grad(dsig, c_dx)
     g_dW, g_db, d_enc = orc.mlp_backward(d_grad, field.density_dims, orc.half_bits(field.dW), enc, d_acts, want_dx=True)
-    g_table = orc.scatter_backward(pos4, d_enc, field.scales, field.T, field.dls)
+    g_table = orc.scatter_backward(pos4, d_enc, field.scatter_scales, field.T, field.dls)
     return dict(d_out=d_out, sigma=sigma, c_in=c_in, c_out=c_out, rgb=rgb, phi=phi, dw=dw, wsum=wsum, c_grad=c_grad, dsig=dsig, d_grad=d_grad,
                 g_table=g_table, g_dW=g_dW, g_db=g_db, g_cW=g_cW, g_cb=g_cb)

@@ -58,7 +58,8 @@ def test_one_step_matches_oracle_chain(cuda, nb, orc):
     assert march["num_steps"].sum() == n
     grid = nb.grid_setup(L, T, 16, 1.447)
     scales = np.array(list(grid.scales)[:L], np.float32)
-    field = OracleField(L, T, 16, 1.447, scales, grid.dense_level_start, (32, 64, 16, 2), (32, 64, 8, 3), table, dW, db, cW, cb)
+    sscales = np.array(list(grid.scatter_scales)[:L], np.float32)
+    field = OracleField(L, T, 16, 1.447, scales, grid.dense_level_start, (32, 64, 16, 2), (32, 64, 8, 3), table, dW, db, cW, cb, sscales)
     bg = np.ones(3, np.float32)
     r = oracle_ray_step(field, march, d.cpu().numpy(), tgt.cpu().numpy(), bg, 0.1, 128.0, 1.0, R)
     assert rel_err(_np(torch, nm, v.density_out, 16 * n, np.float32).reshape(n, 16), r["d_out"]) <= REL_MLP

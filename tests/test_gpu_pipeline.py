@@ -38,7 +38,8 @@ def test_sample_training_step_matches_oracle(cuda, nb, orc, n):
     torch.cuda.synchronize()
 
     scales = np.array(list(model.grid.scales)[:L], np.float32)
-    ref = OracleField(L, T, 16, 1.447, scales, model.grid.dense_level_start, (32, 64, 16, 2), (32, 64, 8, 3), table, dW, db, cW, cb)
+    sscales = np.array(list(model.grid.scatter_scales)[:L], np.float32)
+    ref = OracleField(L, T, 16, 1.447, scales, model.grid.dense_level_start, (32, 64, 16, 2), (32, 64, 8, 3), table, dW, db, cW, cb, sscales)
     r = ref.forward_backward(pos, dirs, tgt, 128.0)
     assert np.array_equal(dev_half_bits(tr.enc), r["enc"])
     assert rel_err(tr.d_out.cpu().numpy(), r["d_out"]) <= REL_MLP

@@ -16,6 +16,7 @@ pytestmark = pytest.mark.gpu
 def _grid(nb, L=16, T=1 << 14, base=16, b=1.447):
     d = nb.grid_setup(L, T, base, b)
     scales = np.array(list(d.scales)[:L], np.float32)
+    d.np_scatter_scales = np.array(list(d.scatter_scales)[:L], np.float32)
     return d, scales
 
 
@@ -28,6 +29,8 @@ def test_grid_setup_matches_oracle(cuda, nb, orc, b, T):
     # the device evaluates the power with its approximate intrinsic: a few ulp from libm, same integer part
     assert np.allclose(scales, ref, rtol=2e-6)
     assert np.array_equal(np.floor(scales), np.floor(ref))
+    # the scatter's own expression lands within a few ulp of the same values
+    assert np.allclose(d.np_scatter_scales, ref, rtol=4e-6) and np.array_equal(np.floor(d.np_scatter_scales), np.floor(ref))
 
 
 @pytest.mark.parametrize("clamp_mode", [0, 1])
@@ -44,7 +47,7 @@ def test_hash_indices_bit_exact(cuda, nb, orc, clamp_mode, n):
                                        nb.ptr(out), nb.stream_ptr()), "nb_hash_indices")
     torch.cuda.synchronize()
     got = out.cpu().numpy().view(np.uint32)[:n]
-    ref = orc.hash_indices(pos, scales, 1 << 19, d.dense_level_start, clamp_mode)
+    ref = orc.hash_indices(pos, d.np_scatter_scales if clamp_mode else scales, 1 << 19, d.dense_level_start, clamp_mode)
     assert np.array_equal(got, ref)
 
 
@@ -185,7 +188,7 @@ def test_scatter_backward(cuda, nb, orc, n, T):
     nb.check(nb.load().nb_hash_scatter_backward(ctypes.byref(d), up.f(pos), up.h(denc), n,
                                                 nb.ptr(grads), nb.stream_ptr()), "nb_hash_scatter_backward")
     torch.cuda.synchronize()
-    ref = orc.scatter_backward(pos, denc, scales, T, d.dense_level_start)
+    ref = orc.scatter_backward(pos, denc, d.np_scatter_scales, T, d.dense_level_start)
     got = grads.cpu().numpy()
     assert rel_err(got, ref) <= REL_MLP
     assert np.array_equal(got != 0, ref != 0) or n > 1000   # same touched set (tiny products may cancel at scale)

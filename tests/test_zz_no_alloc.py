@@ -28,6 +28,7 @@ def test_noalloc_grid_setup_matches_allocating_setup_twice_in_a_row(cuda, nb):
         assert (b.num_levels, b.table_size, b.base_resolution, b.dense_level_start) == \
                (a.num_levels, a.table_size, a.base_resolution, a.dense_level_start)
         assert list(b.scales) == list(a.scales)          # same kernel, same expression: identical bits
+        assert list(b.scatter_scales) == list(a.scatter_scales)
         assert all(s > 0 for s in list(b.scales)[:L]) and all(s == 0 for s in list(b.scales)[L:])
 
 
