@@ -147,6 +147,7 @@ _SIGNATURES = {
     "nb_grid_mlp_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_hash_scatter_backward": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "nb_set_tuning": (c_int, [ctypes.c_char_p, c_int]),
     "nb_mlp_forward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "nb_mlp_backward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                 c_void_p, c_void_p, c_void_p]),
@@ -155,6 +156,8 @@ _SIGNATURES = {
                              c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]),
     "nb_sh_gather": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_density_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_generate_rays": (c_int, [c_int, c_int, c_float, ctypes.POINTER(c_float), c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "nb_mse_rays": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "nb_ray_aabb": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_march_count": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                c_void_p]),

@@ -9,7 +9,9 @@
 // warp always works on 32 consecutive points of ONE level at a time.  Coarse dense levels then hit a
 // handful of cache lines per warp, and the 8 corner loads of two levels are issued back to back before
 // either blend starts (16 independent 4-byte gathers in flight per thread).
+#include <algorithm>
 #include <atomic>
+#include <string>
 
 #include "mlp_core.cuh"
 
@@ -212,14 +214,25 @@ __global__ void __launch_bounds__(CTA_THREADS) grid_mlp_forward_kernel(const __g
     if (cx.row0 < n) mlp_forward_warp<S, 0>(cx);
 }
 
-// Gradient scatter, one thread per (sample, level), level = blockIdx.y so that all CTAs resident at one
-// time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector
-// reduction.  Dense levels first merge lanes that hit the same entry (as the reference does,
-// networkFusionBackwardHashtable.cu:843-887) because neighbouring samples share coarse cells.
+// Tunables of the scatter (nb_set_tuning): levels below `dedupe_levels` that are dense merge equal addresses inside
+// a warp before the reduction; levels below `smem_levels` whose dense grid fits shared memory are accumulated per CTA
+// in shared memory and flushed once; [level_begin, level_end) restricts the launch (profiling experiments).
+struct ScatterTuning {
+    int dedupe_levels = 2;
+    int smem_levels = 2;
+    int level_begin = 0;
+    int level_end = NB_MAX_LEVELS;
+};
+static ScatterTuning g_scatter_tuning;
+
+// Gradient scatter, one thread per (sample, level), level = level_base + blockIdx.y so that all CTAs resident at one
+// time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector reduction.
+// Dense levels below dedupe_levels first merge lanes that hit the same entry (as the reference does on every dense
+// level, networkFusionBackwardHashtable.cu:843-887): neighbouring samples of a ray share coarse cells.
 __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
                                                                const __half* __restrict__ dEnc, int64_t n,
-                                                               float* __restrict__ grads) {
-    const int level = blockIdx.y;
+                                                               float* __restrict__ grads, int level_base, int dedupe_levels) {
+    const int level = level_base + blockIdx.y;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int lane = threadIdx.x & 31;
@@ -231,7 +244,7 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
     corner_weights(c, w);
     float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * (2 * gp.L) + 2 * level]));
     float* base = grads + (size_t)level * gp.T * 2;
-    if (dense) {
+    if (dense && level < dedupe_levels) {
 #pragma unroll
         for (int k = 0; k < 8; k++) {
             float vx = g.x * w[k], vy = g.y * w[k];
@@ -251,6 +264,41 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
     } else {
 #pragma unroll
         for (int k = 0; k < 8; k++) red_add_v2(base + (size_t)c.idx[k] * 2, g.x * w[k], g.y * w[k]);
+    }
+}
+
+// Coarse dense levels whose whole grid fits shared memory: every CTA accumulates its share of the samples into a
+// private copy of the level with shared-memory atomics and adds the non-zero entries to global memory once, so the
+// heavily contended coarse entries see (#CTAs) global reductions instead of (#samples x 8).
+__global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
+                                                           const __half* __restrict__ dEnc, int64_t n, float* __restrict__ grads,
+                                                           int level_base) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float2* acc = reinterpret_cast<float2*>(smem_raw);
+    const int level = level_base + blockIdx.y;
+    const float scale = gp.sscales[level];
+    const int N_l = __float2int_rd(scale);
+    const int cells = (N_l + 1) * (N_l + 1) * (N_l + 1);
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) acc[c] = make_float2(0.f, 0.f);
+    __syncthreads();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 p = ld_nc_f4(pos4 + i * 4);
+        Corners c;
+        corners_of<true>(p.x, p.y, p.z, scale, true, gp.T, c);
+        float w[8];
+        corner_weights(c, w);
+        float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * (2 * gp.L) + 2 * level]));
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            atomicAdd(&acc[c.idx[k]].x, g.x * w[k]);
+            atomicAdd(&acc[c.idx[k]].y, g.y * w[k]);
+        }
+    }
+    __syncthreads();
+    float* base = grads + (size_t)level * gp.T * 2;
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+        float2 v = acc[c];
+        if (v.x != 0.f || v.y != 0.f) red_add_v2(base + (size_t)c * 2, v.x, v.y);
     }
 }
 
@@ -438,6 +486,17 @@ extern "C" int nb_grid_mlp_forward(const nb_grid_desc* desc, const nb_mlp_desc* 
     return nb_set_error(NB_ERR_UNSUPPORTED, "nb_grid_mlp_forward: no kernel built for this (levels, hidden, output, layers) shape");
 }
 
+extern "C" int nb_set_tuning(const char* key, int value) {
+    if (!key) return nb_set_error(NB_ERR_INVALID, "nb_set_tuning: null key");
+    std::string k(key);
+    if (k == "scatter_dedupe_levels") g_scatter_tuning.dedupe_levels = value;
+    else if (k == "scatter_smem_levels") g_scatter_tuning.smem_levels = value;
+    else if (k == "scatter_level_begin") g_scatter_tuning.level_begin = value;
+    else if (k == "scatter_level_end") g_scatter_tuning.level_end = value;
+    else return nb_set_error(NB_ERR_INVALID, "nb_set_tuning: unknown key");
+    return NB_OK;
+}
+
 extern "C" int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d_pos4, const void* d_denc_h, int64_t n,
                                         float* d_table_grads, void* stream) {
     int rc = check_desc(desc, "nb_hash_scatter_backward: null descriptor");
@@ -448,9 +507,33 @@ extern "C" int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d
         return nb_set_error(NB_ERR_INVALID, "nb_hash_scatter_backward: misaligned device pointer");
     if (n == 0) return NB_OK;
     GridParams gp = make_params(desc);
-    dim3 grid((unsigned)((n + 255) / 256), gp.L, 1);
-    scatter_backward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gp, d_pos4, (const __half*)d_denc_h, n, d_table_grads);
+    cudaStream_t st = (cudaStream_t)stream;
+    const ScatterTuning tn = g_scatter_tuning;
+    const int lb = std::max(0, tn.level_begin), le = std::min(gp.L, tn.level_end);
+    // leading dense levels whose (N+1)^3 float2 grid fits shared memory
+    constexpr size_t SMEM_CAP = 112 * 1024;
+    int smem_end = lb;
+    size_t smem_bytes = 0;
+    while (smem_end < le && smem_end < gp.dls && smem_end < tn.smem_levels && n >= 16384) {
+        int N_l = (int)std::floor(gp.sscales[smem_end]);
+        size_t bytes = (size_t)(N_l + 1) * (N_l + 1) * (N_l + 1) * sizeof(float2);
+        if (bytes > SMEM_CAP) break;
+        smem_bytes = std::max(smem_bytes, bytes);
+        smem_end++;
+    }
+    if (smem_end > lb) {
+        NB_CUDA(cudaFuncSetAttribute(scatter_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+        int per_level = std::max(1, nb_num_sms() * 2 / (smem_end - lb));
+        int64_t need = (n + 255) / 256;
+        dim3 grid((unsigned)std::min<int64_t>(per_level, need), smem_end - lb, 1);
+        scatter_smem_kernel<<<grid, 256, smem_bytes, st>>>(gp, d_pos4, (const __half*)d_denc_h, n, d_table_grads, lb);
+        g_launch_count++;
+    }
+    if (le > smem_end) {
+        dim3 grid((unsigned)((n + 255) / 256), le - smem_end, 1);
+        scatter_backward_kernel<<<grid, 256, 0, st>>>(gp, d_pos4, (const __half*)d_denc_h, n, d_table_grads, smem_end, tn.dedupe_levels);
+        g_launch_count++;
+    }
     NB_CHECK_LAUNCH();
-    g_launch_count++;
     return NB_OK;
 }

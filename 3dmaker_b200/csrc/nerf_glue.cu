@@ -89,9 +89,76 @@ __global__ void __launch_bounds__(256) density_grad_kernel(int64_t n, const floa
     st_cs_v4(&dst[1], b);
 }
 
+// Pinhole rays of a camera-to-world matrix, pixel (first_pixel + idx).  generate_custom_rays_kernel,
+// modules/NeRF/NerfTrainer.cu:25-47; the pixel offset lets ranks render disjoint tile ranges of one frame.
+__global__ void __launch_bounds__(256) generate_rays_kernel(int width, int height, float focal, float c00, float c01, float c02, float c03,
+                                                            float c10, float c11, float c12, float c13, float c20, float c21, float c22,
+                                                            float c23, int64_t first_pixel, int64_t count, float3* __restrict__ rays_o,
+                                                            float3* __restrict__ rays_d) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    int64_t idx = first_pixel + i;
+    int px = (int)(idx % width);
+    int py = (int)(idx / width);
+    float dx = (px - width * 0.5f) / focal;
+    float dy = -(py - height * 0.5f) / focal;
+    float dz = -1.0f;
+    float inv = rsqrtf(dx * dx + dy * dy + dz * dz);
+    dx *= inv; dy *= inv; dz *= inv;
+    rays_o[i] = make_float3(c03, c13, c23);
+    rays_d[i] = make_float3(c00 * dx + c01 * dy + c02 * dz, c10 * dx + c11 * dy + c12 * dz, c20 * dx + c21 * dy + c22 * dz);
+}
+
+// Sum over rays of the mean squared colour error (mse_kernel, modules/NeRF/NerfTrainer.cu:15-23), one atomic per block.
+__global__ void __launch_bounds__(256) mse_rays_kernel(const float* __restrict__ pred, const float* __restrict__ target,
+                                                       float* __restrict__ loss_out, int64_t n) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    float v = 0.f;
+    if (idx < n) {
+        float r = pred[idx * 3 + 0] - target[idx * 3 + 0];
+        float g = pred[idx * 3 + 1] - target[idx * 3 + 1];
+        float b = pred[idx * 3 + 2] - target[idx * 3 + 2];
+        v = (r * r + g * g + b * b) / 3.0f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    __shared__ float ws[8];
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int k = 0; k < 8; k++) s += ws[k];
+        atomicAdd(loss_out, s);
+    }
+}
+
 }  // namespace nb
 
 using namespace nb;
+
+extern "C" int nb_generate_rays(int width, int height, float focal, const float* c2w_3x4, int64_t first_pixel, int64_t count, float* d_rays_o,
+                                float* d_rays_d, void* stream) {
+    if (!c2w_3x4 || !d_rays_o || !d_rays_d || width <= 0 || height <= 0 || first_pixel < 0 || count < 0 ||
+        first_pixel + count > (int64_t)width * height || !(focal > 0.f))
+        return nb_set_error(NB_ERR_INVALID, "nb_generate_rays: null pointer or pixel range outside the frame");
+    if (count == 0) return NB_OK;
+    const float* c = c2w_3x4;
+    generate_rays_kernel<<<(unsigned)((count + 255) / 256), 256, 0, (cudaStream_t)stream>>>(width, height, focal, c[0], c[1], c[2], c[3], c[4], c[5],
+                                                                                            c[6], c[7], c[8], c[9], c[10], c[11], first_pixel,
+                                                                                            count, (float3*)d_rays_o, (float3*)d_rays_d);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_mse_rays(const float* d_pred3, const float* d_target3, float* d_loss_sum, int64_t n, void* stream) {
+    if (!d_pred3 || !d_target3 || !d_loss_sum || n < 0) return nb_set_error(NB_ERR_INVALID, "nb_mse_rays: null pointer or negative count");
+    if (n == 0) return NB_OK;
+    mse_rays_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_pred3, d_target3, d_loss_sum, n);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
 
 extern "C" int nb_sh_gather(const float* d_dirs3, const uint32_t* d_ray_indices, int64_t offset, int64_t n, float density_bias,
                             const float* d_density_out, void* d_color_in_h, float* d_sigma, void* stream) {

@@ -159,13 +159,103 @@ def cpu_baseline(sample, repeats=1):
     return sample / best, best
 
 
-def run_reference(args, rank):
-    """Reference arm: the reference has no CPU implementation of this path; the timed code is the oracle's CPU
-    restatement of its kernels (kind "port") on all host cores, each step a bounded sample of the workload."""
+def run_reference_cuda(args, rank, world, local_rank):
+    """Reference arm, CUDA: the reference's own TinyMLPHashGrid / TinyMLP classes and kernels, compiled unmodified
+    for sm_100a into oracle/_ref (oracle/build_ref.py), driven through the same step on the same workload:
+    zero_grad, grid forward, SH gather, colour forward, MSE loss, colour backward (dX), density gradient, grid
+    backward + scatter, Adam of both networks.  The reference is single-GPU: under torchrun rank 0 measures one
+    GPU and reports N ideal replicas."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import ref_cuda as ref
+    nb = importlib.import_module("3dmaker_b200")
+    torch.cuda.set_device(local_rank)
+    lib = ref.lib()
+    rf = lib.ref_field_create(L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3], BATCH)
+    table, dW, db, cW, cb = init_params()
+    lib.ref_field_load(rf, ref.hptr(table), ref.hptr(dW), ref.hptr(db), ref.hptr(cW), ref.hptr(cb))
+    host, dev = [], []
+    for k in range(2):
+        pos, dirs, tgt = make_batch(BATCH, 1000 + k)
+        t3 = np.ascontiguousarray(tgt[:, :3])
+        hp = tuple(torch.from_numpy(a).pin_memory() for a in (pos, dirs, t3))
+        host.append(hp)
+        dev.append(tuple(t.cuda() for t in hp))
+    st = nb.stream_ptr()
+    P = nb.ptr
+
+    def step(bufs):
+        lib.ref_field_train_step(rf, P(bufs[0]), P(bufs[1]), P(bufs[2]), BATCH, 0.0, HYPER["loss_scale"], HYPER["lr"], HYPER["beta1"],
+                                 HYPER["beta2"], HYPER["eps"], st)
+
+    warm = max(args.warmup, 3)
+    for i in range(warm):
+        step(dev[i % 2])
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.05)
+    for i in range(3):
+        step(dev[i % 2])
+    torch.cuda.synchronize()
+    mark0 = sampler.mark()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(dev[i % 2])
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop(mark0, sampler.mark())
+    ms = e0.elapsed_time(e1) / args.steps
+    own = tuple(torch.empty_like(t) for t in dev[0])
+    probe = nm_view(torch, lib.ref_field_color_out(rf), 1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        for dst, src in zip(own, host[i % 2]):
+            dst.copy_(src, non_blocking=True)
+        step(own)
+        probe.cpu()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    h2d = sum(a.numel() * a.element_size() for a in host[0])
+    value = world * BATCH / (ms / 1000.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH,
+                   "reference": "reference CUDA classes/kernels recompiled for sm_100a (oracle/_ref); single-GPU code, value = %d ideal replicas" % world},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 0, "kind": "reference",
+                         "sample": "full 2^20-sample step on the GPU: the reference has no CPU implementation of this path"},
+        "e2e": {"value": world * BATCH / (e2e_ms / 1000.0), "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": 0, "clocks": clocks,
+    }
+    print(json.dumps(line))
+    lib.ref_field_destroy(rf)
+
+
+def nm_view(torch, ptr, count):
+    nm = importlib.import_module("3dmaker_b200.nerf")
+    return nm.view_tensor(torch, ptr, count, np.float32)
+
+
+def run_reference(args, rank, world=1, local_rank=0):
+    """Reference arm.  With the reference's CUDA build present (oracle/_ref) and a GPU, its own kernels are timed;
+    otherwise the oracle's CPU restatement of them (kind "port") on all host cores, each step a bounded sample."""
+    try:
+        import torch
+        from oracle import ref_cuda
+        if ref_cuda.available() and torch.cuda.is_available() and not args.reference_cpu:
+            return run_reference_cuda(args, rank, world, local_rank)
+    except ImportError:
+        pass
     if rank != 0:
         return
     total = args.steps + args.warmup
-    sample = 1 << 16 if total <= 8 else (1 << 15 if total <= 20 else 1 << 14)
+    sample = 1 << 16 if total <= 8 else (1 << 15 if total <= 20 else (1 << 14 if total <= 60 else 1 << 13))
     cores = os.cpu_count() or 1
     times = []
     for i in range(total):
@@ -360,12 +450,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -118,6 +118,13 @@ int nb_grid_mlp_forward(const nb_grid_desc* desc, const nb_mlp_desc* mlp, const 
 int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d_pos4, const void* d_denc_h, int64_t n,
                              float* d_table_grads, void* stream);
 
+/* A/B switches for benchmarking, in the spirit of the reference's TinyMLPHashGrid::setSplitScatter
+ * (TinyMLPHashGrid.h:60-63).  Keys: "scatter_dedupe_levels" (dense levels below it merge equal addresses inside a
+ * warp before the reduction), "scatter_smem_levels" (dense levels below it that fit shared memory are accumulated
+ * per CTA), "scatter_level_begin" / "scatter_level_end" (restrict the scatter to a level range).  Results do not
+ * depend on the first two beyond fp32 summation order. */
+int nb_set_tuning(const char* key, int value);
+
 /* ---- fused MLP ---------------------------------------------------------------------------- */
 
 /* Replaces launchNetworkFusionKernel / launchNetworkFusionGradKernel (TinyMLP.h:172-206). */
@@ -159,6 +166,14 @@ int nb_sh_gather(const float* d_dirs3, const uint32_t* d_ray_indices, int64_t of
  * (only the first 16 channels are read), d_tmp_dsigma[n] added to channel 0 (NULL = zeros),
  * d_density_grad_h fp16 [n][16], clamped to +-65504, NaN -> 0. */
 int nb_density_grad(int64_t n, const float* d_tmp_dsigma, const void* d_color_dx_h, void* d_density_grad_h, void* stream);
+
+/* Replaces generate_custom_rays_kernel (modules/NeRF/NerfTrainer.cu:25-47): pinhole rays of pixels
+ * [first_pixel, first_pixel + count) of a width x height frame; c2w_3x4 is a HOST pointer to the row-major 3x4
+ * camera-to-world matrix.  The pixel range is what pixel-sharded rendering splits across ranks. */
+int nb_generate_rays(int width, int height, float focal, const float* c2w_3x4, int64_t first_pixel, int64_t count, float* d_rays_o,
+                     float* d_rays_d, void* stream);
+/* Replaces mse_kernel (modules/NeRF/NerfTrainer.cu:15-23): ADDS sum over rays of mean((pred - target)^2) to *d_loss_sum. */
+int nb_mse_rays(const float* d_pred3, const float* d_target3, float* d_loss_sum, int64_t n, void* stream);
 
 /* ---- rays, occupancy march, compaction ------------------------------------------------------- */
 
