@@ -13,24 +13,11 @@
 #include <atomic>
 #include <string>
 
-#include "mlp_core.cuh"
+#include "hashgrid_core.cuh"
 
 namespace nb {
 
 extern std::atomic<uint64_t> g_launch_count;
-
-struct GridParams {
-    int L, T, dls;
-    float scales[NB_MAX_LEVELS];   // forward (encode) resolutions
-    float sscales[NB_MAX_LEVELS];  // resolutions of the gradient scatter
-};
-
-static GridParams make_params(const nb_grid_desc* d) {
-    GridParams p;
-    p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start;
-    for (int i = 0; i < NB_MAX_LEVELS; i++) { p.scales[i] = d->scales[i]; p.sscales[i] = d->scatter_scales[i]; }
-    return p;
-}
 
 // Resolution of every level.  out[l]: the forward kernel's expression sequence, a power at levels 0,4,8,12 and
 // repeated multiplication by b in between (modules/TinyMLP/networkFusionHashtable.cu:124-128,218).
@@ -44,115 +31,6 @@ __global__ void level_scales_kernel(int lowestSize, float b, float log2b, int L,
     out[l] = N_l_float;
     int level = l;
     out[NB_MAX_LEVELS + l] = lowestSize * exp2f(level * log2b);
-}
-
-__device__ __forceinline__ uint32_t hash_coords(int cx, int cy, int cz, int T) {
-    return ((static_cast<uint32_t>(cx) * 1U) ^ (static_cast<uint32_t>(cy) * 2654435761U) ^
-            (static_cast<uint32_t>(cz) * 805459861U)) & static_cast<uint32_t>(T - 1);
-}
-__device__ __forceinline__ uint32_t dense_index(int cx, int cy, int cz, int N_l) {
-    return cx + cy * (N_l + 1) + cz * (N_l + 1) * (N_l + 1);
-}
-
-struct Corners {
-    uint32_t idx[8];  // entry index inside the level (pairs of features), corner order 000,100,010,110,001,101,011,111
-    float wx1, wy1, wz1;
-};
-
-// BWD_CLAMP = false: low corner clamped to [0, N_l] (forward); true: to [0, N_l - 1] (backward).
-template <bool BWD_CLAMP>
-__device__ __forceinline__ void corners_of(float px, float py, float pz, float scale, bool dense, int T, Corners& c) {
-    int N_l = __float2int_rd(scale);
-    float x_l = px * scale, y_l = py * scale, z_l = pz * scale;
-    int x0 = __float2int_rd(x_l), y0 = __float2int_rd(y_l), z0 = __float2int_rd(z_l);
-    const int hi = BWD_CLAMP ? N_l - 1 : N_l;
-    x0 = max(0, min(x0, hi)); y0 = max(0, min(y0, hi)); z0 = max(0, min(z0, hi));
-    int x1 = min(x0 + 1, N_l), y1 = min(y0 + 1, N_l), z1 = min(z0 + 1, N_l);
-    c.wx1 = 1.0f - x_l + floorf(x_l);
-    c.wy1 = 1.0f - y_l + floorf(y_l);
-    c.wz1 = 1.0f - z_l + floorf(z_l);
-    if (dense) {
-        c.idx[0] = dense_index(x0, y0, z0, N_l); c.idx[1] = dense_index(x1, y0, z0, N_l);
-        c.idx[2] = dense_index(x0, y1, z0, N_l); c.idx[3] = dense_index(x1, y1, z0, N_l);
-        c.idx[4] = dense_index(x0, y0, z1, N_l); c.idx[5] = dense_index(x1, y0, z1, N_l);
-        c.idx[6] = dense_index(x0, y1, z1, N_l); c.idx[7] = dense_index(x1, y1, z1, N_l);
-    } else {
-        c.idx[0] = hash_coords(x0, y0, z0, T); c.idx[1] = hash_coords(x1, y0, z0, T);
-        c.idx[2] = hash_coords(x0, y1, z0, T); c.idx[3] = hash_coords(x1, y1, z0, T);
-        c.idx[4] = hash_coords(x0, y0, z1, T); c.idx[5] = hash_coords(x1, y0, z1, T);
-        c.idx[6] = hash_coords(x0, y1, z1, T); c.idx[7] = hash_coords(x1, y1, z1, T);
-    }
-}
-
-__device__ __forceinline__ void corner_weights(const Corners& c, float (&w)[8]) {
-    const float wx1 = c.wx1, wy1 = c.wy1, wz1 = c.wz1;
-    w[0] = wx1 * wy1 * wz1;                   w[1] = (1 - wx1) * wy1 * wz1;
-    w[2] = wx1 * (1 - wy1) * wz1;             w[3] = (1 - wx1) * (1 - wy1) * wz1;
-    w[4] = wx1 * wy1 * (1 - wz1);             w[5] = (1 - wx1) * wy1 * (1 - wz1);
-    w[6] = wx1 * (1 - wy1) * (1 - wz1);       w[7] = (1 - wx1) * (1 - wy1) * (1 - wz1);
-}
-
-// Fixed-order blend of the reference (networkFusionHashtable.cu:185-201), both features.
-__device__ __forceinline__ uint32_t blend(const uint32_t (&f)[8], const float (&w)[8]) {
-    float2 v[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) v[k] = unpack_half2(f[k]);
-    float rx = v[7].x * w[7], ry = v[7].y * w[7];
-#pragma unroll
-    for (int k = 6; k >= 0; k--) {
-        rx = __fmaf_rn(v[k].x, w[k], rx);
-        ry = __fmaf_rn(v[k].y, w[k], ry);
-    }
-    return pack_half2(rx, ry);
-}
-
-// Encodes the CTA's 128 points into the shared tile: tile[r][2l .. 2l+1].
-template <int TILE_STRIDE>
-__device__ __forceinline__ void encode_tile(const GridParams& gp, const float* __restrict__ pos4, const uint32_t* __restrict__ table2,
-                                            int64_t row_base, int64_t n, __half* tile, int tid) {
-    const int r = tid & (TILE_ROWS - 1);
-    const int half_sel = tid >> 7;  // 0 or 1: which half of the levels
-    const int lpt = gp.L >> 1;      // levels per thread
-    const int64_t row = row_base + r;
-    if (row < n) {
-        float4 p = ld_nc_f4(pos4 + row * 4);
-        for (int li = 0; li < lpt; li += 2) {
-            const int la = half_sel * lpt + li, lb = la + 1;
-            const bool has_b = (li + 1) < lpt;
-            Corners ca, cb;
-            corners_of<false>(p.x, p.y, p.z, gp.scales[la], la < gp.dls, gp.T, ca);
-            corners_of<false>(p.x, p.y, p.z, gp.scales[has_b ? lb : la], (has_b ? lb : la) < gp.dls, gp.T, cb);
-            const uint32_t* ta = table2 + (size_t)la * gp.T;
-            const uint32_t* tb = table2 + (size_t)(has_b ? lb : la) * gp.T;
-            uint32_t fa[8], fb[8];
-#pragma unroll
-            for (int k = 0; k < 8; k++) fa[k] = __ldg(ta + ca.idx[k]);
-#pragma unroll
-            for (int k = 0; k < 8; k++) fb[k] = __ldg(tb + cb.idx[k]);
-            float wa[8], wb[8];
-            corner_weights(ca, wa);
-            corner_weights(cb, wb);
-            *reinterpret_cast<uint32_t*>(&tile[r * TILE_STRIDE + 2 * la]) = blend(fa, wa);
-            if (has_b) *reinterpret_cast<uint32_t*>(&tile[r * TILE_STRIDE + 2 * lb]) = blend(fb, wb);
-        }
-    } else {
-        for (int li = 0; li < lpt; li++)
-            *reinterpret_cast<uint32_t*>(&tile[r * TILE_STRIDE + 2 * (half_sel * lpt + li)]) = 0u;
-    }
-}
-
-// Coalesced write of the encoded tile (128 x 2L halves) to global memory.
-template <int TILE_STRIDE>
-__device__ __forceinline__ void store_enc_tile(const __half* tile, __half* __restrict__ enc_out, int L, int64_t row_base, int64_t n,
-                                               int tid) {
-    const int cpr = (2 * L) / 8;
-    for (int c = tid; c < TILE_ROWS * cpr; c += CTA_THREADS) {
-        int r = c / cpr, c8 = c % cpr;
-        if (row_base + r < n) {
-            uint4 v = *reinterpret_cast<const uint4*>(&tile[r * TILE_STRIDE + c8 * 8]);
-            st_cs_v4(&enc_out[(row_base + r) * (2 * L) + c8 * 8], v);
-        }
-    }
 }
 
 constexpr int ENC_STRIDE = 2 * NB_MAX_LEVELS + 8;
@@ -206,10 +84,10 @@ __global__ void __launch_bounds__(CTA_THREADS) grid_mlp_forward_kernel(const __g
         store_enc_tile<S::TILE_STRIDE>(tile, save_enc, gp.L, row_base, n, tid);
         __syncthreads();
     }
-    FwdCtx cx;
+    FwdCtx cx{};
     cx.sW = sW; cx.sBias = sBias;
     cx.tile_rows = tile + warp * 16 * S::TILE_STRIDE;
-    cx.out = out; cx.acts = SAVE ? save_acts : nullptr;
+    cx.out = out; cx.out_stride = S::OUT; cx.out_valid = S::OUT; cx.acts = SAVE ? save_acts : nullptr;
     cx.row0 = row_base + warp * 16; cx.n = n; cx.lane = lane;
     if (cx.row0 < n) mlp_forward_warp<S, 0>(cx);
 }

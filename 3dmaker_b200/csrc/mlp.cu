@@ -43,10 +43,10 @@ __global__ void __launch_bounds__(CTA_THREADS) mlp_forward_kernel(const __half* 
     cp_async_wait_all();
     __syncthreads();
 
-    FwdCtx cx;
+    FwdCtx cx{};
     cx.sW = sW; cx.sBias = sBias;
     cx.tile_rows = tile + warp * 16 * S::TILE_STRIDE;
-    cx.out = out; cx.acts = acts;
+    cx.out = out; cx.out_stride = S::OUT; cx.out_valid = S::OUT; cx.acts = acts;
     cx.row0 = row_base + warp * 16; cx.n = n; cx.lane = lane;
     if (cx.row0 < n) mlp_forward_warp<S, OUT_ACT>(cx);
 }

@@ -75,15 +75,21 @@ struct FwdCtx {
     const __half* sW;
     const float* sBias;
     __half* tile_rows;  // this warp's 16 rows of the CTA tile (input on entry, staging afterwards)
-    float* out;         // [n][OUT] fp32
-    __half* acts;       // hidden activations, nullable
+    float* out;         // fp32 output rows, out_stride floats apart; only columns < out_valid are written
+    int out_stride;
+    int out_valid;      // even
+    __half* acts;       // hidden activations in global memory, nullable
+    __half* smem_act[NB_MAX_LAYERS];  // per hidden layer: this warp's 16 rows of a shared-memory tile to receive the
+    int smem_act_stride;              // activation (nullable), rows smem_act_stride halves apart
     int64_t row0;       // global row of the warp's first row
     int64_t n;
     int lane;
 };
 
-template <class S, int L, int OUT_ACT>
-__device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) / 16][4], const FwdCtx& cx) {
+// TO_REGS: the last layer's accumulators (bias added, output activation applied) are handed back in fin[OUT/8][4]
+// instead of being written to cx.out.
+template <class S, int L, int OUT_ACT, bool TO_REGS = false>
+__device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) / 16][4], const FwdCtx& cx, float (*fin)[4] = nullptr) {
     constexpr int K = S::in_dim(L), N = S::out_dim(L);
     const __half* sWl = cx.sW + S::sw_off(L);
     const int lane = cx.lane, g = lane >> 2, t = lane & 3;
@@ -109,6 +115,17 @@ __device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) 
             an[q][2] = pack_half2(fmaxf(c[2 * q + 1][0], 0.f), fmaxf(c[2 * q + 1][1], 0.f));
             an[q][3] = pack_half2(fmaxf(c[2 * q + 1][2], 0.f), fmaxf(c[2 * q + 1][3], 0.f));
         }
+        if (cx.smem_act[L] != nullptr) {
+            __half* st = cx.smem_act[L];
+            const int sd = cx.smem_act_stride;
+#pragma unroll
+            for (int q = 0; q < N / 16; q++) {
+                *reinterpret_cast<uint32_t*>(&st[g * sd + 16 * q + 2 * t]) = an[q][0];
+                *reinterpret_cast<uint32_t*>(&st[(g + 8) * sd + 16 * q + 2 * t]) = an[q][1];
+                *reinterpret_cast<uint32_t*>(&st[g * sd + 16 * q + 8 + 2 * t]) = an[q][2];
+                *reinterpret_cast<uint32_t*>(&st[(g + 8) * sd + 16 * q + 8 + 2 * t]) = an[q][3];
+            }
+        }
         if (cx.acts != nullptr) {
             // stage the 16 x N fp16 block in the warp's own tile rows, then write 16-byte chunks coalesced
             __half* st = cx.tile_rows;
@@ -133,7 +150,7 @@ __device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) 
             }
             __syncwarp();
         }
-        forward_layers<S, L + 1, OUT_ACT>(an, cx);
+        forward_layers<S, L + 1, OUT_ACT, TO_REGS>(an, cx, fin);
     } else {
 #pragma unroll
         for (int j = 0; j < N / 8; j++) {
@@ -141,9 +158,17 @@ __device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) 
 #pragma unroll
                 for (int e = 0; e < 4; e++) c[j][e] = 1.0f / (1.0f + expf(-c[j][e]));
             }
+            if constexpr (TO_REGS) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) fin[j][e] = c[j][e];
+                continue;
+            }
             int64_t r0 = cx.row0 + g, r1 = r0 + 8;
-            if (r0 < cx.n) *reinterpret_cast<float2*>(&cx.out[r0 * N + 8 * j + 2 * t]) = make_float2(c[j][0], c[j][1]);
-            if (r1 < cx.n) *reinterpret_cast<float2*>(&cx.out[r1 * N + 8 * j + 2 * t]) = make_float2(c[j][2], c[j][3]);
+            const int col = 8 * j + 2 * t;
+            if (col < cx.out_valid) {
+                if (r0 < cx.n) *reinterpret_cast<float2*>(&cx.out[r0 * cx.out_stride + col]) = make_float2(c[j][0], c[j][1]);
+                if (r1 < cx.n) *reinterpret_cast<float2*>(&cx.out[r1 * cx.out_stride + col]) = make_float2(c[j][2], c[j][3]);
+            }
         }
     }
 }

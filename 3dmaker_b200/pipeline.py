@@ -152,6 +152,38 @@ class SampleTrainer:
             grad_sync(self.model.g)
         self.optimizer_step(stream)
 
+    # ---- pipelined host input: the copy of the next batch overlaps the step on the current one -----------------
+    def prefetch(self, pos4, dirs3, target_h8):
+        """Enqueues the host->device copy of one batch (pinned tensors) on a copy stream into the input slot that
+        the running step is not using.  Pair every call with one step_prefetched()."""
+        torch = self.torch
+        if not hasattr(self, "_slots"):
+            self._copy_stream = torch.cuda.Stream()
+            self._slots = [(self.pos, self.dirs, self.target),
+                           (torch.empty_like(self.pos), torch.empty_like(self.dirs), torch.empty_like(self.target))]
+            self._ready = [torch.cuda.Event(), torch.cuda.Event()]
+            self._free = [torch.cuda.Event(), torch.cuda.Event()]
+            self._next, self._queued = 0, []
+        k = self._next
+        n = pos4.shape[0]
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(self._free[k])      # the step that last read this slot has finished
+            p, d, t = self._slots[k]
+            p[:n].copy_(pos4, non_blocking=True); d[:n].copy_(dirs3, non_blocking=True); t[:n].copy_(target_h8, non_blocking=True)
+            self._ready[k].record(self._copy_stream)
+        self._queued.append((k, n))
+        self._next = 1 - k
+
+    def step_prefetched(self, stream=None, grad_sync=None):
+        """Runs one full step on the oldest prefetched batch and returns its mean squared error (4-byte read-back)."""
+        k, n = self._queued.pop(0)
+        cur = self.torch.cuda.current_stream()
+        cur.wait_event(self._ready[k])
+        self.pos, self.dirs, self.target = self._slots[k]
+        self.step_device(n, stream, grad_sync)
+        self._free[k].record(cur)
+        return float(self.loss.item()) / (n * 3)
+
     def step_host(self, pos4, dirs3, target_h8, stream=None, grad_sync=None):
         """One full step from pinned host tensors: copies inputs in, runs the step, returns the mean squared error
         (a device->host read of one float, which also synchronises)."""
