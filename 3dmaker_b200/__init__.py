@@ -124,7 +124,8 @@ class ArenaView(ctypes.Structure):
 class StepView(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in ("num_steps", "ray_offsets", "ray_indices", "t_sorted", "positions", "density_out", "sigma",
                                         "color_out", "render_rgb", "phi", "dw", "weight_sum", "tmp_dsigma", "color_in", "color_grad",
-                                        "density_grad")] + [("last_total_hits", ctypes.c_uint32), ("train_steps", ctypes.c_int32)]
+                                        "density_grad")] + [("last_total_hits", ctypes.c_uint32), ("train_steps", ctypes.c_int32),
+                                                            ("logit_stride", ctypes.c_int32), ("color_stride", ctypes.c_int32)]
 
 
 GRAD_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
@@ -148,6 +149,13 @@ _SIGNATURES = {
                                     c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_hash_scatter_backward": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "nb_set_tuning": (c_int, [ctypes.c_char_p, c_int]),
+    "nb_field_supported": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc)]),
+    "nb_field_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_void_p]),
+    "nb_field_backward": (c_int, [ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p]),
     "nb_mlp_forward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "nb_mlp_backward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                 c_void_p, c_void_p, c_void_p]),
@@ -169,7 +177,7 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), c_void_p]),
     "nb_composite_train": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, ctypes.POINTER(c_float), c_void_p]),
-    "nb_color_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+    "nb_color_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_int, c_void_p, c_float, c_float, ctypes.c_uint32, c_void_p]),
     "nb_occ_sample_cells": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_int, c_int, c_int, ctypes.c_uint64, c_void_p]),
     "nb_occ_sample_occupied": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_int, ctypes.c_uint64, c_void_p]),
@@ -189,6 +197,7 @@ _SIGNATURES = {
     "nb_nerf_set_profiling": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_memory_mode": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_global_ray_scale": (c_int, [c_void_p, ctypes.c_uint32]),
+    "nb_nerf_set_fused_field": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),
     "nb_nerf_load_params": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

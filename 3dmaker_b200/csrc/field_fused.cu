@@ -155,4 +155,396 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid
     forward_layers<CS, 0, 1, false>(ca, cx);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------
+// Block-level pieces; every tile involved has 128 rows.  "dZ" is the gradient tile (stride DZS halves), "A" the
+// input-activation tile of the layer (stride AS halves).
+
+__host__ __device__ constexpr int dw_tiles(int K, int NP) { return (NP / 16) * (K / 8); }
+__host__ __device__ constexpr int dw_tpw(int K, int NP) { return (dw_tiles(K, NP) + 7) / 8; }
+
+// dW (NP x K, 16 x 8 register tiles dealt round-robin to the 8 warps) += dZ^T x A
+template <int K, int NP, int DZS, int AS>
+__device__ __forceinline__ void accumulate_dw(float (*acc)[4], const __half* sDZ, const __half* sA, int warp, int lane) {
+    const int lq = lane >> 3, lr = lane & 7;
+    constexpr int N8 = K / 8;
+#pragma unroll
+    for (int s = 0; s < dw_tpw(K, NP); s++) {
+        int id = warp + 8 * s;
+        if (id < dw_tiles(K, NP)) {
+            int mi = id / N8, ni = id % N8;
+            float(&c)[4] = acc[s];
+#pragma unroll
+            for (int ks = 0; ks < TILE_ROWS / 16; ks++) {
+                uint32_t a[4], b0, b1;
+                ldmatrix_x4_trans(a, &sDZ[(16 * ks + (lq >> 1) * 8 + lr) * DZS + 16 * mi + (lq & 1) * 8]);
+                ldmatrix_x2_trans(b0, b1, &sA[(16 * ks + (lq & 1) * 8 + lr) * AS + 8 * ni]);
+                mma_16816(c, a, b0, b1);
+            }
+        }
+    }
+}
+
+template <int K, int N, int NP>
+__device__ __forceinline__ void flush_dw(const float (*acc)[4], float* __restrict__ dW, int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int N8 = K / 8;
+#pragma unroll
+    for (int s = 0; s < dw_tpw(K, NP); s++) {
+        int id = warp + 8 * s;
+        if (id < dw_tiles(K, NP)) {
+            int mi = id / N8, ni = id % N8;
+            int m0 = 16 * mi + g, m1 = m0 + 8, nn = 8 * ni + 2 * t;
+            if (m0 < N) red_add_v2(&dW[m0 * K + nn], acc[s][0], acc[s][1]);
+            if (m1 < N) red_add_v2(&dW[m1 * K + nn], acc[s][2], acc[s][3]);
+        }
+    }
+}
+
+template <int N, int DZS>
+__device__ __forceinline__ void accumulate_db(float& db, const __half* sDZ, int tid) {
+    constexpr int PARTS = CTA_THREADS / N;
+    int col = tid % N, part = tid / N;
+    float s = 0.f;
+    for (int r = part; r < TILE_ROWS; r += PARTS) s += __half2float(sDZ[r * DZS + col]);
+    db += s;
+}
+
+// dA[:, 0 .. KOUT) = dZ x W_l for the warp's 16 rows, rounded to fp16; MASK zeroes entries whose activation in
+// sMask (the layer's input, this warp's rows) is not positive.
+template <int K, int KOUT, int NP, int DZS, int AS, bool MASK>
+__device__ __forceinline__ void compute_da(const __half* sWl, const __half* sDZ, const __half* sMask, int warp, int lane,
+                                           uint32_t (&packed)[KOUT / 8][2]) {
+    const int lq = lane >> 3, lr = lane & 7, g = lane >> 2, t = lane & 3;
+    uint32_t a[NP / 16][4];
+#pragma unroll
+    for (int kc = 0; kc < NP / 16; kc++)
+        ldmatrix_x4(a[kc], &sDZ[(16 * warp + lr + (lq & 1) * 8) * DZS + 16 * kc + (lq >> 1) * 8]);
+#pragma unroll
+    for (int j = 0; j < KOUT / 8; j++) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int kc = 0; kc < NP / 16; kc++) {
+            uint32_t b0, b1;
+            ldmatrix_x2_trans(b0, b1, &sWl[(16 * kc + (lq & 1) * 8 + lr) * (K + 8) + 8 * j]);
+            mma_16816(c, a[kc], b0, b1);
+        }
+        __half2 v0 = __floats2half2_rn(c[0], c[1]);  // row g
+        __half2 v1 = __floats2half2_rn(c[2], c[3]);  // row g + 8
+        if constexpr (MASK) {
+            __half2 a0 = *reinterpret_cast<const __half2*>(&sMask[(16 * warp + g) * AS + 8 * j + 2 * t]);
+            __half2 a1 = *reinterpret_cast<const __half2*>(&sMask[(16 * warp + g + 8) * AS + 8 * j + 2 * t]);
+            const __half z = __float2half(0.f);
+            if (!(__low2float(a0) > 0.f)) v0 = __halves2half2(z, __high2half(v0));
+            if (!(__high2float(a0) > 0.f)) v0 = __halves2half2(__low2half(v0), z);
+            if (!(__low2float(a1) > 0.f)) v1 = __halves2half2(z, __high2half(v1));
+            if (!(__high2float(a1) > 0.f)) v1 = __halves2half2(__low2half(v1), z);
+        }
+        packed[j][0] = *reinterpret_cast<uint32_t*>(&v0);
+        packed[j][1] = *reinterpret_cast<uint32_t*>(&v1);
+    }
+}
+
+template <int KOUT, int DZS>
+__device__ __forceinline__ void store_da(const uint32_t (&packed)[KOUT / 8][2], __half* sDZ, int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int j = 0; j < KOUT / 8; j++) {
+        *reinterpret_cast<uint32_t*>(&sDZ[(16 * warp + g) * DZS + 8 * j + 2 * t]) = packed[j][0];
+        *reinterpret_cast<uint32_t*>(&sDZ[(16 * warp + g + 8) * DZS + 8 * j + 2 * t]) = packed[j][1];
+    }
+}
+
+// fp16 pair + optional fp32 addend on the low half, clamped to the fp16 range, NaN -> 0 (compute_density_grad,
+// modules/NeRF/otherKernels.cu:497-562)
+__device__ __forceinline__ uint32_t sanitize_grad_pair(uint32_t v, float add_lo) {
+    float2 f = unpack_half2(v);
+    f.x += add_lo;
+    f.x = fmaxf(-65504.0f, fminf(65504.0f, f.x));
+    if (f.x != f.x) f.x = 0.0f;
+    f.y = fmaxf(-65504.0f, fminf(65504.0f, f.y));
+    if (f.y != f.y) f.y = 0.0f;
+    return pack_half2(f.x, f.y);
+}
+
+struct FieldGradIO {
+    const __half* enc;        // [n][K0] saved by the forward
+    const __half* dcolor;     // [n][8] dL/d(colour pre-activation), channels 3..7 zero
+    const float* dsigma;      // [n] dL/d(logit 0) through sigma, nullable
+    float* dWd; float* dbd;   // density network gradients (accumulated)
+    float* dWc; float* dbc;   // colour network gradients (accumulated)
+    __half* denc;             // [n][K0] dL/d(encoding)
+};
+
+template <class DS, class CS>
+struct FieldBwd {
+    static_assert(DS::NL == 2 && CS::NL == 3 && DS::H == CS::H && DS::K0 == 32 && CS::K0 == 32 && DS::OUT == 16 && CS::OUT == 8,
+                  "fused backward is written for the 32-H-16 density and 32-H-H-8 colour networks");
+    static constexpr int H = DS::H;
+    static constexpr int IS = 32 + 8;  // stride of the 32-wide tiles (encoding, colour input)
+    static constexpr int HS = H + 8;   // stride of the H-wide tiles
+    // register slots of the dW accumulators
+    static constexpr int S_C2 = 0;
+    static constexpr int S_C1 = S_C2 + dw_tpw(H, 16);
+    static constexpr int S_C0 = S_C1 + dw_tpw(H, H);
+    static constexpr int S_D1 = S_C0 + dw_tpw(32, H);
+    static constexpr int S_D0 = S_D1 + dw_tpw(H, 16);
+    static constexpr int SLOTS = S_D0 + dw_tpw(32, H);
+    static constexpr size_t smem_bytes() {
+        return (size_t)(DS::SW_TOTAL + CS::SW_TOTAL) * 2 + (size_t)(DS::B_TOTAL + CS::B_TOTAL) * 4 +
+               (size_t)TILE_ROWS * (2 * IS + 3 * HS) * 2;
+    }
+};
+
+template <class DS, class CS>
+__global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(FieldIO io, FieldGradIO gio) {
+    using FB = FieldBwd<DS, CS>;
+    constexpr int H = FB::H, IS = FB::IS, HS = FB::HS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half* sWd = reinterpret_cast<__half*>(smem_raw);
+    __half* sWc = sWd + DS::SW_TOTAL;
+    float* sBd = reinterpret_cast<float*>(sWc + CS::SW_TOTAL);
+    float* sBc = sBd + DS::B_TOTAL;
+    __half* sE = reinterpret_cast<__half*>(sBc + CS::B_TOTAL);  // encoding            [128][IS]
+    __half* sCI = sE + TILE_ROWS * IS;                          // colour input        [128][IS]
+    __half* sC1 = sCI + TILE_ROWS * IS;                         // colour hidden 1, later density hidden [128][HS]
+    __half* sC2 = sC1 + TILE_ROWS * HS;                         // colour hidden 2     [128][HS]
+    __half* sDZ = sC2 + TILE_ROWS * HS;                         // gradient tile       [128][HS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+
+    load_weights_to_smem<DS>(io.Wd, io.bd, sWd, sBd, tid);
+    load_weights_to_smem<CS>(io.Wc, io.bc, sWc, sBc, tid);
+    cp_async_commit();
+
+    float acc[FB::SLOTS][4];
+#pragma unroll
+    for (int s = 0; s < FB::SLOTS; s++) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
+    float db_c2 = 0.f, db_c1 = 0.f, db_c0 = 0.f, db_d1 = 0.f, db_d0 = 0.f;
+
+    const int64_t ntiles = (io.n + TILE_ROWS - 1) / TILE_ROWS;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t row_base = tile * TILE_ROWS;
+        const int64_t row0 = row_base + 16 * warp;
+        // ---- stage the encoding and the colour gradient (zero rows past n; columns 8..15 of dZ zero) -----------
+        for (int c = tid; c < TILE_ROWS * 4; c += CTA_THREADS) {
+            int r = c >> 2, c8 = c & 3;
+            bool valid = row_base + r < io.n;
+            cp_async16(&sE[r * IS + c8 * 8], valid ? &gio.enc[(row_base + r) * 32 + c8 * 8] : gio.enc, valid);
+        }
+        {
+            int r = tid >> 1, c8 = tid & 1;
+            bool valid = (row_base + r < io.n) && c8 == 0;
+            cp_async16(&sDZ[r * HS + c8 * 8], valid ? &gio.dcolor[(row_base + r) * 8] : gio.dcolor, valid);
+        }
+        cp_async_commit();
+        cp_async_wait_all();
+        __syncthreads();
+
+        // ---- re-derive the activations of the warp's 16 rows ------------------------------------------------------
+        {
+            uint32_t a0[2][4];
+            load_frag_rows<32>(a0, sE + 16 * warp * IS, IS, lane);
+            float c1[H / 8][4];
+            layer_accumulate<32, H>(a0, sWd + DS::sw_off(0), sBd + DS::b_off(0), lane, c1);
+            uint32_t d1[H / 16][4];
+            relu_pack<H>(c1, d1);
+            float dout[2][4];
+            layer_accumulate<H, 16>(d1, sWd + DS::sw_off(1), sBd + DS::b_off(1), lane, dout);
+            uint32_t ci[2][4];
+            float raw0, raw1;
+            build_color_input(dout, io, row0, lane, ci, raw0, raw1);
+            store_frag_rows<32>(ci, sCI + 16 * warp * IS, IS, lane);
+            float c2[H / 8][4];
+            layer_accumulate<32, H>(ci, sWc + CS::sw_off(0), sBc + CS::b_off(0), lane, c2);
+            uint32_t h1[H / 16][4];
+            relu_pack<H>(c2, h1);
+            store_frag_rows<H>(h1, sC1 + 16 * warp * HS, HS, lane);
+            layer_accumulate<H, H>(h1, sWc + CS::sw_off(1), sBc + CS::b_off(1), lane, c2);
+            relu_pack<H>(c2, h1);
+            store_frag_rows<H>(h1, sC2 + 16 * warp * HS, HS, lane);
+        }
+        __syncthreads();
+
+        // ---- colour layer 2: dZ = dcolor (8 valid of 16 columns), input C2 ---------------------------------------
+        {
+            accumulate_dw<H, 16, HS, HS>(&acc[FB::S_C2], sDZ, sC2, warp, lane);
+            accumulate_db<8, HS>(db_c2, sDZ, tid);
+            uint32_t pk[H / 8][2];
+            compute_da<H, H, 16, HS, HS, true>(sWc + CS::sw_off(2), sDZ, sC2, warp, lane, pk);
+            __syncthreads();
+            store_da<H, HS>(pk, sDZ, warp, lane);
+            __syncthreads();
+        }
+        // ---- colour layer 1: input C1 ------------------------------------------------------------------------------
+        {
+            accumulate_dw<H, H, HS, HS>(&acc[FB::S_C1], sDZ, sC1, warp, lane);
+            accumulate_db<H, HS>(db_c1, sDZ, tid);
+            uint32_t pk[H / 8][2];
+            compute_da<H, H, H, HS, HS, true>(sWc + CS::sw_off(1), sDZ, sC1, warp, lane, pk);
+            __syncthreads();
+            store_da<H, HS>(pk, sDZ, warp, lane);
+            __syncthreads();
+        }
+        // ---- colour layer 0: input CI; only the 16 density features carry a gradient further ----------------------
+        {
+            accumulate_dw<32, H, HS, IS>(&acc[FB::S_C0], sDZ, sCI, warp, lane);
+            accumulate_db<H, HS>(db_c0, sDZ, tid);
+            uint32_t pk[2][2];
+            compute_da<32, 16, H, HS, IS, false>(sWc + CS::sw_off(0), sDZ, nullptr, warp, lane, pk);
+            float ds0 = 0.f, ds1 = 0.f;
+            if (t == 0 && gio.dsigma != nullptr) {
+                if (row0 + g < io.n) ds0 = gio.dsigma[row0 + g];
+                if (row0 + g + 8 < io.n) ds1 = gio.dsigma[row0 + g + 8];
+            }
+            pk[0][0] = sanitize_grad_pair(pk[0][0], ds0);
+            pk[0][1] = sanitize_grad_pair(pk[0][1], ds1);
+            pk[1][0] = sanitize_grad_pair(pk[1][0], 0.f);
+            pk[1][1] = sanitize_grad_pair(pk[1][1], 0.f);
+            // the density network's hidden activation, derived again into the tile colour hidden 1 no longer needs
+            uint32_t a0[2][4];
+            load_frag_rows<32>(a0, sE + 16 * warp * IS, IS, lane);
+            float c1[H / 8][4];
+            layer_accumulate<32, H>(a0, sWd + DS::sw_off(0), sBd + DS::b_off(0), lane, c1);
+            uint32_t d1[H / 16][4];
+            relu_pack<H>(c1, d1);
+            __syncthreads();
+            store_da<16, HS>(pk, sDZ, warp, lane);
+            store_frag_rows<H>(d1, sC1 + 16 * warp * HS, HS, lane);
+            __syncthreads();
+        }
+        // ---- density layer 1: dZ 16 wide, input D1 (in the C1 tile) -----------------------------------------------
+        {
+            accumulate_dw<H, 16, HS, HS>(&acc[FB::S_D1], sDZ, sC1, warp, lane);
+            accumulate_db<16, HS>(db_d1, sDZ, tid);
+            uint32_t pk[H / 8][2];
+            compute_da<H, H, 16, HS, HS, true>(sWd + DS::sw_off(1), sDZ, sC1, warp, lane, pk);
+            __syncthreads();
+            store_da<H, HS>(pk, sDZ, warp, lane);
+            __syncthreads();
+        }
+        // ---- density layer 0: input E; dA is the gradient of the encoding -----------------------------------------
+        {
+            accumulate_dw<32, H, HS, IS>(&acc[FB::S_D0], sDZ, sE, warp, lane);
+            accumulate_db<H, HS>(db_d0, sDZ, tid);
+            uint32_t pk[4][2];
+            compute_da<32, 32, H, HS, IS, false>(sWd + DS::sw_off(0), sDZ, nullptr, warp, lane, pk);
+            __syncthreads();
+            store_da<32, HS>(pk, sDZ, warp, lane);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                int ch = lane + 32 * i;
+                int r = ch >> 2, c8 = ch & 3;
+                int64_t gr = row0 + r;
+                if (gr < io.n) {
+                    uint4 v = *reinterpret_cast<const uint4*>(&sDZ[(16 * warp + r) * HS + c8 * 8]);
+                    st_cs_v4(&gio.denc[gr * 32 + c8 * 8], v);
+                }
+            }
+            __syncthreads();
+        }
+    }
+    cp_async_wait_all();
+    flush_dw<H, 8, 16>(&acc[FB::S_C2], gio.dWc + CS::w_off(2), warp, lane);
+    flush_dw<H, H, H>(&acc[FB::S_C1], gio.dWc + CS::w_off(1), warp, lane);
+    flush_dw<32, H, H>(&acc[FB::S_C0], gio.dWc + CS::w_off(0), warp, lane);
+    flush_dw<H, 16, 16>(&acc[FB::S_D1], gio.dWd + DS::w_off(1), warp, lane);
+    flush_dw<32, H, H>(&acc[FB::S_D0], gio.dWd + DS::w_off(0), warp, lane);
+    red_add(&gio.dbc[CS::b_off(2) + tid % 8], db_c2);
+    red_add(&gio.dbc[CS::b_off(1) + tid % H], db_c1);
+    red_add(&gio.dbc[CS::b_off(0) + tid % H], db_c0);
+    red_add(&gio.dbd[DS::b_off(1) + tid % 16], db_d1);
+    red_add(&gio.dbd[DS::b_off(0) + tid % H], db_d0);
+}
+
 }  // namespace nb
+
+namespace {
+
+using DensityNet = nb::MlpShape<32, 64, 16, 2>;
+using ColorNet = nb::MlpShape<32, 64, 8, 3>;
+
+bool is_shape(const nb_mlp_desc* d, int k0, int h, int out, int nl) {
+    return d->input_dim == k0 && d->hidden_dim == h && d->output_dim == out && d->num_layers == nl;
+}
+bool misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
+
+}  // namespace
+
+extern "C" int nb_field_supported(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color) {
+    if (!grid || !density || !color) return 0;
+    if (grid->num_levels != 16) return 0;
+    return is_shape(density, 32, 64, 16, 2) && is_shape(color, 32, 64, 8, 3) && density->output_activation == 0 &&
+           color->output_activation == 1;
+}
+
+extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                                const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                                const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
+                                int64_t n, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
+                                int rgb_stride, void* stream) {
+    if (!grid || !density || !color || !d_pos4 || !d_table_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b ||
+        !d_rgb || n < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_field_forward: null pointer or negative count");
+    if (!nb_field_supported(grid, density, color))
+        return nb_set_error(NB_ERR_UNSUPPORTED, "nb_field_forward: built for 16 levels, density 32-64-16 and colour 32-64-64-8 (sigmoid)");
+    if (rgb_stride != 4 && rgb_stride != 8) return nb_set_error(NB_ERR_INVALID, "nb_field_forward: rgb_stride must be 4 or 8");
+    if (misaligned(d_pos4, 16) || misaligned(d_table_h, 4) || misaligned(d_density_w_h, 16) || misaligned(d_color_w_h, 16) ||
+        misaligned(d_enc_save_h, 16) || misaligned(d_rgb, 8) || misaligned(d_density_b, 8) || misaligned(d_color_b, 8))
+        return nb_set_error(NB_ERR_INVALID, "nb_field_forward: misaligned device pointer");
+    if (n == 0) return NB_OK;
+    nb::FieldIO io{};
+    io.pos4 = d_pos4; io.table2 = (const uint32_t*)d_table_h; io.dirs3 = d_dirs3; io.ray_idx = d_ray_indices;
+    io.ray_idx_offset = ray_index_offset;
+    io.Wd = (const __half*)d_density_w_h; io.bd = d_density_b; io.Wc = (const __half*)d_color_w_h; io.bc = d_color_b;
+    io.n = n; io.density_bias = density_bias;
+    auto kern = nb::field_forward_kernel<DensityNet, ColorNet>;
+    size_t smem = nb::FieldSmem<DensityNet, ColorNet>::fwd_bytes();
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
+    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(nb::make_params(grid), io, (__half*)d_enc_save_h, d_sigma, d_logit0,
+                                                                             d_rgb, rgb_stride);
+    NB_CHECK_LAUNCH();
+    nb::g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
+                                 const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
+                                 const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
+                                 const void* d_dcolor_h, const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b,
+                                 float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h, void* stream) {
+    if (!density || !color || !d_enc_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b || !d_dcolor_h ||
+        !d_grad_density_w || !d_grad_density_b || !d_grad_color_w || !d_grad_color_b || !d_denc_h || n < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_field_backward: null pointer or negative count");
+    if (!is_shape(density, 32, 64, 16, 2) || !is_shape(color, 32, 64, 8, 3))
+        return nb_set_error(NB_ERR_UNSUPPORTED, "nb_field_backward: built for density 32-64-16 and colour 32-64-64-8");
+    if (misaligned(d_enc_h, 16) || misaligned(d_dcolor_h, 16) || misaligned(d_denc_h, 16) || misaligned(d_density_w_h, 16) ||
+        misaligned(d_color_w_h, 16) || misaligned(d_grad_density_w, 8) || misaligned(d_grad_color_w, 8) || misaligned(d_density_b, 8) ||
+        misaligned(d_color_b, 8))
+        return nb_set_error(NB_ERR_INVALID, "nb_field_backward: misaligned device pointer");
+    if (n == 0) return NB_OK;
+    nb::FieldIO io{};
+    io.dirs3 = d_dirs3; io.ray_idx = d_ray_indices; io.ray_idx_offset = ray_index_offset;
+    io.Wd = (const __half*)d_density_w_h; io.bd = d_density_b; io.Wc = (const __half*)d_color_w_h; io.bc = d_color_b;
+    io.n = n;
+    nb::FieldGradIO gio{};
+    gio.enc = (const __half*)d_enc_h; gio.dcolor = (const __half*)d_dcolor_h; gio.dsigma = d_dsigma;
+    gio.dWd = d_grad_density_w; gio.dbd = d_grad_density_b; gio.dWc = d_grad_color_w; gio.dbc = d_grad_color_b;
+    gio.denc = (__half*)d_denc_h;
+    auto kern = nb::field_backward_kernel<DensityNet, ColorNet>;
+    size_t smem = nb::FieldBwd<DensityNet, ColorNet>::smem_bytes();
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int per_sm = 0;
+    NB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, nb::CTA_THREADS, smem));
+    if (per_sm < 1) per_sm = 1;
+    int64_t ntiles = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
+    int64_t grid_dim = (int64_t)nb_num_sms() * per_sm;
+    if (grid_dim > ntiles) grid_dim = ntiles;
+    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(io, gio);
+    NB_CHECK_LAUNCH();
+    nb::g_launch_count++;
+    return NB_OK;
+}

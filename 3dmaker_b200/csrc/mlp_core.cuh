@@ -86,14 +86,11 @@ struct FwdCtx {
     int lane;
 };
 
-// TO_REGS: the last layer's accumulators (bias added, output activation applied) are handed back in fin[OUT/8][4]
-// instead of being written to cx.out.
-template <class S, int L, int OUT_ACT, bool TO_REGS = false>
-__device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) / 16][4], const FwdCtx& cx, float (*fin)[4] = nullptr) {
-    constexpr int K = S::in_dim(L), N = S::out_dim(L);
-    const __half* sWl = cx.sW + S::sw_off(L);
-    const int lane = cx.lane, g = lane >> 2, t = lane & 3;
-    float c[N / 8][4];
+// c[j][.] = (A x W_l^T)[:, 8j .. 8j+7] + bias for the warp's 16 rows; sWl has rows K + 8 halves apart.
+template <int K, int N>
+__device__ __forceinline__ void layer_accumulate(const uint32_t (&a)[K / 16][4], const __half* sWl, const float* sBl, int lane,
+                                                 float (&c)[N / 8][4]) {
+    const int t = lane & 3;
 #pragma unroll
     for (int j = 0; j < N / 8; j++) {
         c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.0f;
@@ -103,39 +100,62 @@ __device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) 
             ldmatrix_x2(b0, b1, &sWl[(8 * j + (lane & 7)) * (K + 8) + 16 * kc + ((lane >> 3) & 1) * 8]);
             mma_16816(c[j], a[kc], b0, b1);
         }
-        float2 bb = *reinterpret_cast<const float2*>(&cx.sBias[S::b_off(L) + 8 * j + 2 * t]);
+        float2 bb = *reinterpret_cast<const float2*>(&sBl[8 * j + 2 * t]);
         c[j][0] += bb.x; c[j][1] += bb.y; c[j][2] += bb.x; c[j][3] += bb.y;
     }
+}
+
+// ReLU + fp16 rounding of accumulator tiles = the A fragments of the next layer.
+template <int N>
+__device__ __forceinline__ void relu_pack(const float (&c)[N / 8][4], uint32_t (&an)[N / 16][4]) {
+#pragma unroll
+    for (int q = 0; q < N / 16; q++) {
+        an[q][0] = pack_half2(fmaxf(c[2 * q][0], 0.f), fmaxf(c[2 * q][1], 0.f));
+        an[q][1] = pack_half2(fmaxf(c[2 * q][2], 0.f), fmaxf(c[2 * q][3], 0.f));
+        an[q][2] = pack_half2(fmaxf(c[2 * q + 1][0], 0.f), fmaxf(c[2 * q + 1][1], 0.f));
+        an[q][3] = pack_half2(fmaxf(c[2 * q + 1][2], 0.f), fmaxf(c[2 * q + 1][3], 0.f));
+    }
+}
+
+// A-fragment layout -> 16 rows of a shared tile (rows `stride` halves apart).
+template <int N>
+__device__ __forceinline__ void store_frag_rows(const uint32_t (&an)[N / 16][4], __half* st, int stride, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int q = 0; q < N / 16; q++) {
+        *reinterpret_cast<uint32_t*>(&st[g * stride + 16 * q + 2 * t]) = an[q][0];
+        *reinterpret_cast<uint32_t*>(&st[(g + 8) * stride + 16 * q + 2 * t]) = an[q][1];
+        *reinterpret_cast<uint32_t*>(&st[g * stride + 16 * q + 8 + 2 * t]) = an[q][2];
+        *reinterpret_cast<uint32_t*>(&st[(g + 8) * stride + 16 * q + 8 + 2 * t]) = an[q][3];
+    }
+}
+
+// A fragments of the warp's 16 rows from a shared tile.
+template <int K>
+__device__ __forceinline__ void load_frag_rows(uint32_t (&a)[K / 16][4], const __half* rows, int stride, int lane) {
+#pragma unroll
+    for (int kc = 0; kc < K / 16; kc++) {
+        int q = lane >> 3, r = lane & 7;
+        ldmatrix_x4(a[kc], &rows[(r + (q & 1) * 8) * stride + 16 * kc + (q >> 1) * 8]);
+    }
+}
+
+// TO_REGS: the last layer's accumulators (bias added, output activation applied) are handed back in fin[OUT/8][4]
+// instead of being written to cx.out.
+template <class S, int L, int OUT_ACT, bool TO_REGS = false>
+__device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) / 16][4], const FwdCtx& cx, float (*fin)[4] = nullptr) {
+    constexpr int K = S::in_dim(L), N = S::out_dim(L);
+    const int lane = cx.lane, g = lane >> 2, t = lane & 3;
+    float c[N / 8][4];
+    layer_accumulate<K, N>(a, cx.sW + S::sw_off(L), cx.sBias + S::b_off(L), lane, c);
     if constexpr (L < S::NL - 1) {
         uint32_t an[N / 16][4];
-#pragma unroll
-        for (int q = 0; q < N / 16; q++) {
-            an[q][0] = pack_half2(fmaxf(c[2 * q][0], 0.f), fmaxf(c[2 * q][1], 0.f));
-            an[q][1] = pack_half2(fmaxf(c[2 * q][2], 0.f), fmaxf(c[2 * q][3], 0.f));
-            an[q][2] = pack_half2(fmaxf(c[2 * q + 1][0], 0.f), fmaxf(c[2 * q + 1][1], 0.f));
-            an[q][3] = pack_half2(fmaxf(c[2 * q + 1][2], 0.f), fmaxf(c[2 * q + 1][3], 0.f));
-        }
-        if (cx.smem_act[L] != nullptr) {
-            __half* st = cx.smem_act[L];
-            const int sd = cx.smem_act_stride;
-#pragma unroll
-            for (int q = 0; q < N / 16; q++) {
-                *reinterpret_cast<uint32_t*>(&st[g * sd + 16 * q + 2 * t]) = an[q][0];
-                *reinterpret_cast<uint32_t*>(&st[(g + 8) * sd + 16 * q + 2 * t]) = an[q][1];
-                *reinterpret_cast<uint32_t*>(&st[g * sd + 16 * q + 8 + 2 * t]) = an[q][2];
-                *reinterpret_cast<uint32_t*>(&st[(g + 8) * sd + 16 * q + 8 + 2 * t]) = an[q][3];
-            }
-        }
+        relu_pack<N>(c, an);
+        if (cx.smem_act[L] != nullptr) store_frag_rows<N>(an, cx.smem_act[L], cx.smem_act_stride, lane);
         if (cx.acts != nullptr) {
             // stage the 16 x N fp16 block in the warp's own tile rows, then write 16-byte chunks coalesced
             __half* st = cx.tile_rows;
-#pragma unroll
-            for (int q = 0; q < N / 16; q++) {
-                *reinterpret_cast<uint32_t*>(&st[g * S::TILE_STRIDE + 16 * q + 2 * t]) = an[q][0];
-                *reinterpret_cast<uint32_t*>(&st[(g + 8) * S::TILE_STRIDE + 16 * q + 2 * t]) = an[q][1];
-                *reinterpret_cast<uint32_t*>(&st[g * S::TILE_STRIDE + 16 * q + 8 + 2 * t]) = an[q][2];
-                *reinterpret_cast<uint32_t*>(&st[(g + 8) * S::TILE_STRIDE + 16 * q + 8 + 2 * t]) = an[q][3];
-            }
+            store_frag_rows<N>(an, st, S::TILE_STRIDE, lane);
             __syncwarp();
             __half* dst = cx.acts + (int64_t)L * cx.n * N;
             constexpr int CPR = N / 8;
@@ -177,12 +197,7 @@ __device__ __forceinline__ void forward_layers(const uint32_t (&a)[S::in_dim(L) 
 template <class S, int OUT_ACT>
 __device__ __forceinline__ void mlp_forward_warp(const FwdCtx& cx) {
     uint32_t a[S::K0 / 16][4];
-    const int lane = cx.lane;
-#pragma unroll
-    for (int kc = 0; kc < S::K0 / 16; kc++) {
-        int q = lane >> 3, r = lane & 7;
-        ldmatrix_x4(a[kc], &cx.tile_rows[(r + (q & 1) * 8) * S::TILE_STRIDE + 16 * kc + (q >> 1) * 8]);
-    }
+    load_frag_rows<S::K0>(a, cx.tile_rows, S::TILE_STRIDE, cx.lane);
     __syncwarp();
     forward_layers<S, 0, OUT_ACT>(a, cx);
 }

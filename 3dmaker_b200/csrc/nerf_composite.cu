@@ -150,8 +150,8 @@ __global__ void __launch_bounds__(256) render_rays_distortion_kernel(
 template <bool GRAD8>
 __global__ void __launch_bounds__(256) color_grad_kernel(const uint32_t numRays, const uint32_t* __restrict__ num_steps,
                                                          const uint32_t* __restrict__ ray_offsets, const float* __restrict__ t_sorted,
-                                                         const float* __restrict__ density_mlp_out, const float* __restrict__ color_mlp_out,
-                                                         const int color_stride, const float* __restrict__ phi_chunk,
+                                                         const float* __restrict__ density_mlp_out, const int logit_stride,
+                                                         const float* __restrict__ color_mlp_out, const int color_stride, const float* __restrict__ phi_chunk,
                                                          const float* __restrict__ final_rgb, const float* __restrict__ dw_out,
                                                          const float* __restrict__ weight_sum, __half* __restrict__ custom_color_grad,
                                                          float* __restrict__ tmp_dsigma, float loss_scale, const float densityBias,
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(256) color_grad_kernel(const uint32_t numRays,
         float t_current = t_sorted[i];
         if (depth_idx == maxDepth - 1) delta_t = 1e-3f;
         else delta_t = fmaxf(t_sorted[i + 1] - t_current, 0.0f);
-        float sigma = expf(fminf(density_mlp_out[(size_t)i * 16] - densityBias, 8.0f));
+        float sigma = expf(fminf(density_mlp_out[(size_t)i * logit_stride] - densityBias, 8.0f));
         float alpha = 1.0f - expf(-sigma * delta_t);
         float weight = currentT * alpha;
         float c_r = color_mlp_out[(size_t)i * color_stride + 0];
@@ -255,11 +255,11 @@ extern "C" int nb_composite_train(int64_t num_rays, const uint32_t* d_ray_offset
 }
 
 extern "C" int nb_color_grad(int64_t num_rays, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, const float* d_t_sorted,
-                             const float* d_density_out16, const float* d_color_out, int color_stride, const float* d_phi,
+                             const float* d_logit0, int logit_stride, const float* d_color_out, int color_stride, const float* d_phi,
                              const float* d_final_rgb, const float* d_dw_out, const float* d_weight_sum, void* d_color_grad_h,
                              int grad_stride, float* d_tmp_dsigma, float loss_scale, float density_bias, uint32_t total_rays_batch,
                              void* stream) {
-    if (!d_num_steps || !d_ray_offsets || !d_t_sorted || !d_density_out16 || !d_color_out || !d_phi || !d_final_rgb || !d_dw_out ||
+    if (!d_num_steps || !d_ray_offsets || !d_t_sorted || !d_logit0 || logit_stride < 1 || !d_color_out || !d_phi || !d_final_rgb || !d_dw_out ||
         !d_weight_sum || !d_color_grad_h || !d_tmp_dsigma || num_rays < 0 || num_rays > 0x7fffffff || color_stride < 3)
         return nb_set_error(NB_ERR_INVALID, "nb_color_grad: null pointer, bad ray count or colour stride < 3");
     if (grad_stride != 3 && grad_stride != 8) return nb_set_error(NB_ERR_UNSUPPORTED, "nb_color_grad: gradient row stride must be 3 or 8 halves");
@@ -269,12 +269,12 @@ extern "C" int nb_color_grad(int64_t num_rays, const uint32_t* d_num_steps, cons
     if (num_rays == 0) return NB_OK;
     unsigned grid = (unsigned)((num_rays + 255) / 256);
     if (grad_stride == 8)
-        color_grad_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t)num_rays, d_num_steps, d_ray_offsets, d_t_sorted, d_density_out16,
+        color_grad_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t)num_rays, d_num_steps, d_ray_offsets, d_t_sorted, d_logit0, logit_stride,
                                                                         d_color_out, color_stride, d_phi, d_final_rgb, d_dw_out, d_weight_sum,
                                                                         (__half*)d_color_grad_h, d_tmp_dsigma, loss_scale, density_bias,
                                                                         total_rays_batch);
     else
-        color_grad_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t)num_rays, d_num_steps, d_ray_offsets, d_t_sorted, d_density_out16,
+        color_grad_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t)num_rays, d_num_steps, d_ray_offsets, d_t_sorted, d_logit0, logit_stride,
                                                                          d_color_out, color_stride, d_phi, d_final_rgb, d_dw_out, d_weight_sum,
                                                                          (__half*)d_color_grad_h, d_tmp_dsigma, loss_scale, density_bias,
                                                                          total_rays_batch);

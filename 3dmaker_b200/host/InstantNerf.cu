@@ -152,6 +152,7 @@ void InstantNerf::initRenderBuffers() {
     d_occ_samples.allocate(((size_t)G + 16) * 4 * sizeof(float)); d_tmp_grid.allocate(N * sizeof(float), true); d_sum.allocate(sizeof(float), true);
     d_occ_scratch.allocate((size_t)nb_occ_scratch_bytes((int)N) + 8); d_active_cells.allocate(N * sizeof(int)); d_num_active.allocate(sizeof(int), true);
     m_traininit = true;
+    setFusedField(true);
 }
 
 void InstantNerf::freeBuffers() { m_traininit = false; }
@@ -230,7 +231,14 @@ InstantNerf::StepView InstantNerf::stepView() const {
     v.sigma = d_sigma.as<float>(); v.color_out = d_color_out.as<float>(); v.render_rgb = d_render_rgb.as<float>(); v.phi = d_phi.as<float>();
     v.dw = d_dw.as<float>(); v.weight_sum = d_weight_sum.as<float>(); v.tmp_dsigma = d_tmpsigma.as<float>();
     v.color_in = d_color_in.as<half>(); v.color_grad = d_color_grad.as<half>(); v.density_grad = d_density_grad.as<half>();
+    v.logit_stride = m_fused ? 1 : 16;
+    v.color_stride = m_fused ? 4 : 8;
     return v;
+}
+
+bool InstantNerf::setFusedField(bool on) {
+    m_fused = on && m_densityMLP && m_colorMLP && nb_field_supported(&m_densityMLP->grid(), &m_densityMLP->desc(), &m_colorMLP->desc());
+    return m_fused;
 }
 
 void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_d, const float* d_rays_depth, const float* d_rays_sigma,
@@ -285,7 +293,16 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
             });
         }
 
-        if (n > 0) {
+        const int logitStride = m_fused ? 1 : 16, colorStride = m_fused ? 4 : 8;
+        if (n > 0 && m_fused) {
+            timed(stream, m_times.densityFwd, [&]() {
+                throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()), chunk_d,
+                                                d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()),
+                                                m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()), n, m_opts.densityBias, d_enc.as<half>(),
+                                                d_sigma.as<float>(), d_density_out.as<float>(), d_color_out.as<float>(), colorStride, stream),
+                               "field forward");
+            });
+        } else if (n > 0) {
             timed(stream, m_times.densityFwd, [&]() {
                 throw_on_error(nb_grid_mlp_forward(&dn->grid(), &dn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
                                                    m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), n, d_density_out.as<float>(),
@@ -302,7 +319,7 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
         }
         timed(stream, m_times.compositing, [&]() {
             throw_on_error(nb_composite_train(currentChunkRays, d_ray_offsets.as<uint32_t>(), d_num_steps.as<uint32_t>(), d_t_sorted.as<float>(),
-                                              d_sigma.as<float>(), chunk_depth, chunk_sigma, d_color_out.as<float>(), 8,
+                                              d_sigma.as<float>(), chunk_depth, chunk_sigma, d_color_out.as<float>(), colorStride,
                                               d_rgb_true ? d_rgb_true + (size_t)raysDone * 3 : nullptr, d_render_rgb.as<float>(),
                                               d_render_depth.as<float>(), d_phi.as<float>(), d_dw.as<float>(), d_weight_sum.as<float>(),
                                               m_opts.lambdaDist, m_opts.lambdaDepth, bg, stream), "compositing");
@@ -313,23 +330,34 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
         if (n > 0) {
             timed(stream, m_times.lossGrad, [&]() {
                 throw_on_error(nb_color_grad(currentChunkRays, d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), d_t_sorted.as<float>(),
-                                             d_density_out.as<float>(), d_color_out.as<float>(), 8, d_phi.as<float>(), d_render_rgb.as<float>(),
+                                             d_density_out.as<float>(), logitStride, d_color_out.as<float>(), colorStride, d_phi.as<float>(),
+                                             d_render_rgb.as<float>(),
                                              d_dw.as<float>(), d_weight_sum.as<float>(), d_color_grad.as<half>(), 8, d_tmpsigma.as<float>(),
                                              m_opts.lossScale, m_opts.densityBias, numRays * m_rayScale, stream), "loss gradients");
             });
-            timed(stream, m_times.colorBwd, [&]() {
-                throw_on_error(nb_mlp_backward(&cn->desc(), d_color_grad.as<half>(), m_arena.Wh(cn->weightOffset()), d_color_in.as<half>(),
-                                               d_color_acts.as<half>(), n, m_arena.G(cn->weightOffset()), m_arena.G(cn->biasOffset()),
-                                               d_color_dx.as<half>(), stream), "colour backward");
-            });
-            timed(stream, m_times.densityGrad, [&]() {
-                throw_on_error(nb_density_grad(n, d_tmpsigma.as<float>(), d_color_dx.as<half>(), d_density_grad.as<half>(), stream), "density gradient");
-            });
-            timed(stream, m_times.densityBwd, [&]() {
-                throw_on_error(nb_mlp_backward(&dn->desc(), d_density_grad.as<half>(), m_arena.Wh(dn->weightOffset()), d_enc.as<half>(),
-                                               d_density_acts.as<half>(), n, m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()),
-                                               d_denc.as<half>(), stream), "density backward");
-            });
+            if (m_fused) {
+                timed(stream, m_times.colorBwd, [&]() {
+                    throw_on_error(nb_field_backward(&dn->desc(), &cn->desc(), d_enc.as<half>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
+                                                     m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
+                                                     m_arena.W(cn->biasOffset()), n, d_color_grad.as<half>(), d_tmpsigma.as<float>(),
+                                                     m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()), m_arena.G(cn->weightOffset()),
+                                                     m_arena.G(cn->biasOffset()), d_denc.as<half>(), stream), "field backward");
+                });
+            } else {
+                timed(stream, m_times.colorBwd, [&]() {
+                    throw_on_error(nb_mlp_backward(&cn->desc(), d_color_grad.as<half>(), m_arena.Wh(cn->weightOffset()), d_color_in.as<half>(),
+                                                   d_color_acts.as<half>(), n, m_arena.G(cn->weightOffset()), m_arena.G(cn->biasOffset()),
+                                                   d_color_dx.as<half>(), stream), "colour backward");
+                });
+                timed(stream, m_times.densityGrad, [&]() {
+                    throw_on_error(nb_density_grad(n, d_tmpsigma.as<float>(), d_color_dx.as<half>(), d_density_grad.as<half>(), stream), "density gradient");
+                });
+                timed(stream, m_times.densityBwd, [&]() {
+                    throw_on_error(nb_mlp_backward(&dn->desc(), d_density_grad.as<half>(), m_arena.Wh(dn->weightOffset()), d_enc.as<half>(),
+                                                   d_density_acts.as<half>(), n, m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()),
+                                                   d_denc.as<half>(), stream), "density backward");
+                });
+            }
             timed(stream, m_times.scatter, [&]() {
                 throw_on_error(nb_hash_scatter_backward(&dn->grid(), d_positions.as<float>(), d_denc.as<half>(), n, m_arena.G(dn->hashOffset()), stream),
                                "gradient scatter");
@@ -389,16 +417,24 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
                                              d_occupancyGrid.as<uint8_t>(), chunkRays, raysDone, crrRays, d_ray_offsets.as<uint32_t>(),
                                              d_plan.as<uint32_t>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
                                "march: emit");
-                throw_on_error(nb_grid_mlp_forward(&dn->grid(), &dn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
-                                                   m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), n, d_density_out.as<float>(), nullptr,
-                                                   nullptr, stream), "density inference");
-                throw_on_error(nb_sh_gather(chunk_d + (size_t)raysDone * 3, d_ray_indices.as<uint32_t>(), 0, n, m_opts.densityBias,
-                                            d_density_out.as<float>(), d_color_in.as<half>(), d_sigma.as<float>(), stream), "SH gather");
-                throw_on_error(nb_mlp_forward(&cn->desc(), d_color_in.as<half>(), m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()), n,
-                                              d_color_out.as<float>(), nullptr, stream), "colour inference");
+                if (m_fused) {
+                    throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
+                                                    chunk_d + (size_t)raysDone * 3, d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()),
+                                                    m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()), n,
+                                                    m_opts.densityBias, nullptr, d_sigma.as<float>(), nullptr, d_color_out.as<float>(), 4, stream),
+                                   "field inference");
+                } else {
+                    throw_on_error(nb_grid_mlp_forward(&dn->grid(), &dn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
+                                                       m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), n, d_density_out.as<float>(), nullptr,
+                                                       nullptr, stream), "density inference");
+                    throw_on_error(nb_sh_gather(chunk_d + (size_t)raysDone * 3, d_ray_indices.as<uint32_t>(), 0, n, m_opts.densityBias,
+                                                d_density_out.as<float>(), d_color_in.as<half>(), d_sigma.as<float>(), stream), "SH gather");
+                    throw_on_error(nb_mlp_forward(&cn->desc(), d_color_in.as<half>(), m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()), n,
+                                                  d_color_out.as<float>(), nullptr, stream), "colour inference");
+                }
             }
             throw_on_error(nb_composite_infer(crrRays, base, raysDone, d_ray_offsets.as<uint32_t>(), d_num_steps.as<uint32_t>() + raysDone,
-                                              d_t_sorted.as<float>(), d_sigma.as<float>(), d_color_out.as<float>(), 8, nullptr,
+                                              d_t_sorted.as<float>(), d_sigma.as<float>(), d_color_out.as<float>(), m_fused ? 4 : 8, nullptr,
                                               d_render_rgb.as<float>(), d_render_depth.as<float>(), nullptr, bg, stream), "compositing");
             if (d_rgb_out != nullptr)
                 throw_on_cuda(cudaMemcpyAsync(d_rgb_out + (size_t)(ray_offset + raysDone) * 3, d_render_rgb.as<float>(),

@@ -110,6 +110,10 @@ public:
     void setGradSync(GradSync fn) { m_gradSync = std::move(fn); }
     // Loss gradients are normalised by numRays * scale (the global ray count when ranks split a batch).
     void setGlobalRayScale(uint32_t scale) { m_rayScale = scale ? scale : 1u; }
+    // One kernel each way for the whole field (encode + both networks) instead of the reference's kernel sequence;
+    // on by default when the network shapes allow it.  Returns the mode now in effect.
+    bool setFusedField(bool on);
+    bool fusedField() const { return m_fused; }
     nb::ParamArena& arena() { return m_arena; }
     TinyMLPHashGrid* densityNetwork() { return m_densityMLP; }
     TinyMLP* colorNetwork() { return m_colorMLP; }
@@ -124,6 +128,8 @@ public:
         const uint32_t *num_steps, *ray_offsets, *ray_indices;
         const float *t_sorted, *positions, *density_out, *sigma, *color_out, *render_rgb, *phi, *dw, *weight_sum, *tmp_dsigma;
         const half *color_in, *color_grad, *density_grad;
+        int logit_stride;  // density_out[i * logit_stride] = raw logit 0 of sample i (16: full density output rows)
+        int color_stride;  // floats between colour rows
     };
     StepView stepView() const;
 
@@ -143,6 +149,7 @@ private:
     TinyMLPHashGrid* m_densityMLP = nullptr;
     GradSync m_gradSync;
     uint32_t m_rayScale = 1;
+    bool m_fused = false;
     NerfPhaseTimes m_times;
 
     nb::DeviceMem d_occupancyGrid, d_masterOccupancyGrid;

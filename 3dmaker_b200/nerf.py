@@ -69,6 +69,10 @@ class InstantNerf:
     def set_global_ray_scale(self, scale):
         nb.check(self.lib.nb_nerf_set_global_ray_scale(self.h, scale))
 
+    def set_fused_field(self, on):
+        """One kernel each way for the whole field (default) or the kernel-by-kernel sequence; returns the mode in effect."""
+        return bool(self.lib.nb_nerf_set_fused_field(self.h, 1 if on else 0))
+
     def set_grad_sync(self, fn):
         """fn(grad_tensor) is called between backward and Adam with a float32 view of the gradient arena."""
         if fn is None:

@@ -84,30 +84,39 @@ class SampleTrainer:
     """One optimizer step on explicit samples (position, view direction, target colour):
     the 'encode + MLP fwd/bwd + Adam' step of the benchmark.  Buffers are sized once for max_batch."""
 
-    def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0):
+    def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0, fused=None):
+        """fused=None picks the two-kernel field path (nb_field_forward / nb_field_backward) when it is built for
+        the model's shapes, else the kernel-by-kernel sequence; True / False force one of them."""
         torch = model.torch
         self.model, self.torch, self.lib = model, torch, model.lib
         self.max_batch = max_batch
         self.lr, self.beta1, self.beta2, self.eps, self.loss_scale, self.density_bias = lr, beta1, beta2, eps, loss_scale, density_bias
+        supported = bool(self.lib.nb_field_supported(ctypes.byref(model.grid), ctypes.byref(model.density), ctypes.byref(model.color)))
+        if fused and not supported:
+            raise nb.NerfB200Error("the fused field kernels are not built for these network shapes")
+        self.fused = supported if fused is None else bool(fused)
         n, dev = max_batch, "cuda"
         d, c = model.density, model.color
         f16, f32 = torch.float16, torch.float32
         self.pos = torch.zeros((n, 4), dtype=f32, device=dev)
         self.dirs = torch.zeros((n, 3), dtype=f32, device=dev)
         self.target = torch.zeros((n, 8), dtype=f16, device=dev)
-        self.ray_idx = torch.arange(n, dtype=torch.int32, device=dev)
         self.enc = torch.zeros((n, d.input_dim), dtype=f16, device=dev)
-        self.d_acts = torch.zeros((max(d.num_layers - 1, 1), n, d.hidden_dim), dtype=f16, device=dev)
-        self.d_out = torch.zeros((n, 16), dtype=f32, device=dev)
-        self.c_in = torch.zeros((n, 32), dtype=f16, device=dev)
         self.sigma = torch.zeros(n, dtype=f32, device=dev)
-        self.c_acts = torch.zeros((max(c.num_layers - 1, 1), n, c.hidden_dim), dtype=f16, device=dev)
         self.c_out = torch.zeros((n, 8), dtype=f32, device=dev)
         self.c_grad = torch.zeros((n, 8), dtype=f16, device=dev)
-        self.c_dx = torch.zeros((n, 32), dtype=f16, device=dev)
-        self.d_grad = torch.zeros((n, 16), dtype=f16, device=dev)
         self.d_enc = torch.zeros((n, d.input_dim), dtype=f16, device=dev)
         self.loss = torch.zeros(1, dtype=f32, device=dev)
+        if self.fused:
+            self.logit0 = torch.zeros(n, dtype=f32, device=dev)
+        else:
+            self.ray_idx = torch.arange(n, dtype=torch.int32, device=dev)
+            self.d_acts = torch.zeros((max(d.num_layers - 1, 1), n, d.hidden_dim), dtype=f16, device=dev)
+            self.d_out = torch.zeros((n, 16), dtype=f32, device=dev)
+            self.c_in = torch.zeros((n, 32), dtype=f16, device=dev)
+            self.c_acts = torch.zeros((max(c.num_layers - 1, 1), n, c.hidden_dim), dtype=f16, device=dev)
+            self.c_dx = torch.zeros((n, 32), dtype=f16, device=dev)
+            self.d_grad = torch.zeros((n, 16), dtype=f16, device=dev)
 
     def forward_backward(self, n, stream=None):
         """Everything of a step except the optimizer, on inputs already in self.pos / dirs / target."""
@@ -116,20 +125,32 @@ class SampleTrainer:
         if n > self.max_batch:
             raise nb.NerfB200Error("batch exceeds max_batch")
         nb.check(lib.nb_zero_async(P(self.loss), 4, st), "nb_zero_async")
-        nb.check(lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(self.pos), m.ptr("w_h", 0),
-                                         m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), n, P(self.d_out), P(self.enc), P(self.d_acts),
-                                         st), "nb_grid_mlp_forward")
-        nb.check(lib.nb_sh_gather(P(self.dirs), P(self.ray_idx), 0, n, self.density_bias, P(self.d_out), P(self.c_in), P(self.sigma),
-                                  st), "nb_sh_gather")
-        nb.check(lib.nb_mlp_forward(ctypes.byref(m.color), P(self.c_in), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
-                                    P(self.c_out), P(self.c_acts), st), "nb_mlp_forward")
-        nb.check(lib.nb_mse_loss_grad(P(self.c_out), P(self.target), P(self.c_grad), P(self.loss), n, 8, 3, self.loss_scale, 1, st),
-                 "nb_mse_loss_grad")
-        nb.check(lib.nb_mlp_backward(ctypes.byref(m.color), P(self.c_grad), m.ptr("w_h", m.off_cw), P(self.c_in), P(self.c_acts), n,
-                                     m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(self.c_dx), st), "nb_mlp_backward(colour)")
-        nb.check(lib.nb_density_grad(n, None, P(self.c_dx), P(self.d_grad), st), "nb_density_grad")
-        nb.check(lib.nb_mlp_backward(ctypes.byref(m.density), P(self.d_grad), m.ptr("w_h", m.off_dw), P(self.enc), P(self.d_acts), n,
-                                     m.ptr("g", m.off_dw), m.ptr("g", m.off_db), P(self.d_enc), st), "nb_mlp_backward(density)")
+        if self.fused:
+            nb.check(lib.nb_field_forward(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(self.pos), m.ptr("w_h", 0),
+                                          P(self.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
+                                          m.ptr("w", m.off_cb), n, self.density_bias, P(self.enc), P(self.sigma), P(self.logit0),
+                                          P(self.c_out), 8, st), "nb_field_forward")
+            nb.check(lib.nb_mse_loss_grad(P(self.c_out), P(self.target), P(self.c_grad), P(self.loss), n, 8, 3, self.loss_scale, 1, st),
+                     "nb_mse_loss_grad")
+            nb.check(lib.nb_field_backward(ctypes.byref(m.density), ctypes.byref(m.color), P(self.enc), P(self.dirs), None, 0,
+                                           m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
+                                           P(self.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db), m.ptr("g", m.off_cw),
+                                           m.ptr("g", m.off_cb), P(self.d_enc), st), "nb_field_backward")
+        else:
+            nb.check(lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(self.pos), m.ptr("w_h", 0),
+                                             m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), n, P(self.d_out), P(self.enc), P(self.d_acts),
+                                             st), "nb_grid_mlp_forward")
+            nb.check(lib.nb_sh_gather(P(self.dirs), P(self.ray_idx), 0, n, self.density_bias, P(self.d_out), P(self.c_in), P(self.sigma),
+                                      st), "nb_sh_gather")
+            nb.check(lib.nb_mlp_forward(ctypes.byref(m.color), P(self.c_in), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
+                                        P(self.c_out), P(self.c_acts), st), "nb_mlp_forward")
+            nb.check(lib.nb_mse_loss_grad(P(self.c_out), P(self.target), P(self.c_grad), P(self.loss), n, 8, 3, self.loss_scale, 1, st),
+                     "nb_mse_loss_grad")
+            nb.check(lib.nb_mlp_backward(ctypes.byref(m.color), P(self.c_grad), m.ptr("w_h", m.off_cw), P(self.c_in), P(self.c_acts), n,
+                                         m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(self.c_dx), st), "nb_mlp_backward(colour)")
+            nb.check(lib.nb_density_grad(n, None, P(self.c_dx), P(self.d_grad), st), "nb_density_grad")
+            nb.check(lib.nb_mlp_backward(ctypes.byref(m.density), P(self.d_grad), m.ptr("w_h", m.off_dw), P(self.enc), P(self.d_acts), n,
+                                         m.ptr("g", m.off_dw), m.ptr("g", m.off_db), P(self.d_enc), st), "nb_mlp_backward(density)")
         nb.check(lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(self.pos), P(self.d_enc), n, m.ptr("g", 0), st),
                  "nb_hash_scatter_backward")
 

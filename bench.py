@@ -282,21 +282,35 @@ def time_kernels(torch, tr, n, iters=5):
     nb = importlib.import_module("3dmaker_b200")
     m, lib, P = tr.model, tr.lib, nb.ptr
     st = nb.stream_ptr()
-    calls = {
-        "grid_mlp_forward": lambda: lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(tr.pos), m.ptr("w_h", 0),
-                                                            m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), n, P(tr.d_out), P(tr.enc),
-                                                            P(tr.d_acts), st),
-        "sh_gather": lambda: lib.nb_sh_gather(P(tr.dirs), P(tr.ray_idx), 0, n, tr.density_bias, P(tr.d_out), P(tr.c_in), P(tr.sigma), st),
-        "mlp_forward_color": lambda: lib.nb_mlp_forward(ctypes.byref(m.color), P(tr.c_in), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb),
-                                                        n, P(tr.c_out), P(tr.c_acts), st),
-        "mse_loss_grad": lambda: lib.nb_mse_loss_grad(P(tr.c_out), P(tr.target), P(tr.c_grad), P(tr.loss), n, 8, 3, tr.loss_scale, 1, st),
-        "mlp_backward_color": lambda: lib.nb_mlp_backward(ctypes.byref(m.color), P(tr.c_grad), m.ptr("w_h", m.off_cw), P(tr.c_in),
-                                                          P(tr.c_acts), n, m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.c_dx), st),
-        "density_grad": lambda: lib.nb_density_grad(n, None, P(tr.c_dx), P(tr.d_grad), st),
-        "mlp_backward_density": lambda: lib.nb_mlp_backward(ctypes.byref(m.density), P(tr.d_grad), m.ptr("w_h", m.off_dw), P(tr.enc),
-                                                            P(tr.d_acts), n, m.ptr("g", m.off_dw), m.ptr("g", m.off_db), P(tr.d_enc), st),
-        "scatter_backward": lambda: lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(tr.pos), P(tr.d_enc), n, m.ptr("g", 0), st),
-    }
+    if tr.fused:
+        calls = {
+            "field_forward": lambda: lib.nb_field_forward(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(tr.pos),
+                                                          m.ptr("w_h", 0), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db),
+                                                          m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, tr.density_bias, P(tr.enc),
+                                                          P(tr.sigma), P(tr.logit0), P(tr.c_out), 8, st),
+            "mse_loss_grad": lambda: lib.nb_mse_loss_grad(P(tr.c_out), P(tr.target), P(tr.c_grad), P(tr.loss), n, 8, 3, tr.loss_scale, 1, st),
+            "field_backward": lambda: lib.nb_field_backward(ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0,
+                                                            m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
+                                                            m.ptr("w", m.off_cb), n, P(tr.c_grad), None, m.ptr("g", m.off_dw),
+                                                            m.ptr("g", m.off_db), m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc), st),
+            "scatter_backward": lambda: lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(tr.pos), P(tr.d_enc), n, m.ptr("g", 0), st),
+        }
+    else:
+        calls = {
+            "grid_mlp_forward": lambda: lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(tr.pos), m.ptr("w_h", 0),
+                                                                m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), n, P(tr.d_out), P(tr.enc),
+                                                                P(tr.d_acts), st),
+            "sh_gather": lambda: lib.nb_sh_gather(P(tr.dirs), P(tr.ray_idx), 0, n, tr.density_bias, P(tr.d_out), P(tr.c_in), P(tr.sigma), st),
+            "mlp_forward_color": lambda: lib.nb_mlp_forward(ctypes.byref(m.color), P(tr.c_in), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb),
+                                                            n, P(tr.c_out), P(tr.c_acts), st),
+            "mse_loss_grad": lambda: lib.nb_mse_loss_grad(P(tr.c_out), P(tr.target), P(tr.c_grad), P(tr.loss), n, 8, 3, tr.loss_scale, 1, st),
+            "mlp_backward_color": lambda: lib.nb_mlp_backward(ctypes.byref(m.color), P(tr.c_grad), m.ptr("w_h", m.off_cw), P(tr.c_in),
+                                                              P(tr.c_acts), n, m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.c_dx), st),
+            "density_grad": lambda: lib.nb_density_grad(n, None, P(tr.c_dx), P(tr.d_grad), st),
+            "mlp_backward_density": lambda: lib.nb_mlp_backward(ctypes.byref(m.density), P(tr.d_grad), m.ptr("w_h", m.off_dw), P(tr.enc),
+                                                                P(tr.d_acts), n, m.ptr("g", m.off_dw), m.ptr("g", m.off_db), P(tr.d_enc), st),
+            "scatter_backward": lambda: lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(tr.pos), P(tr.d_enc), n, m.ptr("g", 0), st),
+        }
     out = {}
     for name, fn in calls.items():
         ts = []
@@ -320,8 +334,9 @@ def time_kernels(torch, tr, n, iters=5):
 
 
 # algorithmic bytes per sample of the HBM/L2-bound kernels (encode: 16 B position + 16 levels x 8 corners x 4 B
-# gathers + 64 B features out; scatter: 16 B + 64 B gradient in + 16 x 8 x 2 x 4 B adds counted once)
-ALGO_BYTES = {"grid_mlp_forward": 592.0, "scatter_backward": 1104.0}
+# gathers + 64 B features out; field forward: the same + 12 B direction + 4 B sigma + 4 B logit + 32 B colour row;
+# scatter: 16 B + 64 B gradient in + 16 x 8 x 2 x 4 B adds counted once)
+ALGO_BYTES = {"grid_mlp_forward": 592.0, "field_forward": 644.0, "scatter_backward": 1104.0}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -340,7 +355,7 @@ def run_ours(args, rank, world, local_rank):
     model = pl.FieldModel(torch, L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3])
     table, dW, db, cW, cb = init_params()
     model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
-    tr = pl.SampleTrainer(model, BATCH, **HYPER)
+    tr = pl.SampleTrainer(model, BATCH, fused=False if args.unfused else None, **HYPER)
 
     # two distinct seeded batches per rank, pinned on the host and resident on the device
     host, dev = [], []
@@ -422,7 +437,7 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         peak, peak_src = load_peaks()
         kt = time_kernels(torch, tr, BATCH)
-        dom = max(ALGO_BYTES, key=lambda k: kt[k])
+        dom = max((k for k in ALGO_BYTES if k in kt), key=lambda k: kt[k])
         achieved = ALGO_BYTES[dom] * BATCH / (kt[dom] / 1000.0) / 1e9
         roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                     "frac": achieved / peak, "traffic": None,
@@ -433,7 +448,7 @@ def run_ours(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "l2": "inputs and activations of one step (>1 GB) exceed the 126 MB L2; two input batches alternate",
-                       "parallelism": "dp%d" % world},
+                       "parallelism": "dp%d" % world, "field_kernels": "fused" if tr.fused else "sequence"},
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "last_loss": loss},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernel_ms": kt,
@@ -456,6 +471,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

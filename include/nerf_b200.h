@@ -175,6 +175,36 @@ int nb_generate_rays(int width, int height, float focal, const float* c2w_3x4, i
 /* Replaces mse_kernel (modules/NeRF/NerfTrainer.cu:15-23): ADDS sum over rays of mean((pred - target)^2) to *d_loss_sum. */
 int nb_mse_rays(const float* d_pred3, const float* d_target3, float* d_loss_sum, int64_t n, void* stream);
 
+/* ---- the whole field in one launch each way ------------------------------------------------------ */
+
+/* 1 when nb_field_forward / nb_field_backward are built for this (grid, density, colour) combination: 16 levels,
+ * density 32-64-16 (linear), colour 32-64-64-8 (sigmoid) - the shapes of NerfOptions' defaults
+ * (modules/NeRF/InstantNerf.h:20-33).  Other shapes run the separate kernels above. */
+int nb_field_supported(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color);
+
+/* Positions -> (sigma, logit 0, rgb) of n samples.  Replaces, in one launch, the sequence
+ * TinyMLPHashGrid::forward / inference -> compute_SH_gather -> TinyMLP::forward / inference that InstantNerf runs per
+ * chunk (modules/NeRF/InstantNerf.cu:436-459 training, 930-960 rendering).  Ray of sample i =
+ * d_ray_indices[ray_index_offset + i] (NULL: ray i).  d_enc_save_h fp16 [n][32] is all the backward needs
+ * (NULL when rendering); d_sigma[n] = expf(min(clamp(logit0) - density_bias, 8)); d_logit0[n] the raw first output
+ * of the density network; d_rgb rows are rgb_stride (4 or 8) floats apart, sigmoid applied, columns >= 3 padding. */
+int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                     const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                     const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
+                     float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb, int rgb_stride,
+                     void* stream);
+
+/* Gradients of both networks and of the encoding from the colour gradient.  Replaces TinyMLP::backward (colour) ->
+ * compute_density_grad -> the network half of TinyMLPHashGrid::backward (modules/NeRF/InstantNerf.cu:506-561).
+ * Hidden activations are derived again from d_enc_h inside the kernel.  d_dcolor_h fp16 [n][8] = dL/d(colour
+ * pre-activation) as nb_color_grad / nb_mse_loss_grad write it; d_dsigma[n] (NULL = zeros) is added to the gradient
+ * of logit 0.  d_grad_* are ACCUMULATED (fp32); d_denc_h fp16 [n][32] feeds nb_hash_scatter_backward. */
+int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
+                      const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h, const float* d_density_b,
+                      const void* d_color_w_h, const float* d_color_b, int64_t n, const void* d_dcolor_h, const float* d_dsigma,
+                      float* d_grad_density_w, float* d_grad_density_b, float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h,
+                      void* stream);
+
 /* ---- rays, occupancy march, compaction ------------------------------------------------------- */
 
 /* Scene geometry of the marcher: the fields of NerfOptions it reads (modules/NeRF/InstantNerf.h:35-42). */
@@ -232,10 +262,12 @@ int nb_composite_train(int64_t num_rays, const uint32_t* d_ray_offsets, const ui
                        const float* d_rgb_true, float* d_final_rgb, float* d_final_depth, float* d_phi, float* d_dw_out,
                        float* d_weight_sum, float lambda_dist, float lambda_depth, const float* bg_color3, void* stream);
 
-/* Replaces compute_color_grad (modules/NeRF/otherKernels.cu:303-409) with initialOffset 0.  d_color_out rows are
- * color_stride floats apart; gradient rows are grad_stride (3 or 8) halves, channels 3..7 written as zero. */
+/* Replaces compute_color_grad (modules/NeRF/otherKernels.cu:303-409) with initialOffset 0.  d_logit0 holds the raw
+ * first density output of sample i at d_logit0[i * logit_stride] (16 for a full density-output matrix, 1 for the
+ * compact array of nb_field_forward); d_color_out rows are color_stride floats apart; gradient rows are grad_stride
+ * (3 or 8) halves, channels 3..7 written as zero. */
 int nb_color_grad(int64_t num_rays, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, const float* d_t_sorted,
-                  const float* d_density_out16, const float* d_color_out, int color_stride, const float* d_phi, const float* d_final_rgb,
+                  const float* d_logit0, int logit_stride, const float* d_color_out, int color_stride, const float* d_phi, const float* d_final_rgb,
                   const float* d_dw_out, const float* d_weight_sum, void* d_color_grad_h, int grad_stride, float* d_tmp_dsigma,
                   float loss_scale, float density_bias, uint32_t total_rays_batch, void* stream);
 
@@ -300,6 +332,8 @@ typedef struct nb_nerf_step_view {
     const void *color_in, *color_grad, *density_grad;
     uint32_t last_total_hits;
     int32_t train_steps;
+    int32_t logit_stride; /* density_out[i * logit_stride] = raw logit 0 of sample i: 16 (full rows) or 1 (fused field) */
+    int32_t color_stride; /* floats between rows of color_out: 8 or 4 (fused field) */
 } nb_nerf_step_view;
 
 /* NerfOptions defaults (InstantNerf.h:35-76). */
@@ -321,6 +355,10 @@ int nb_nerf_set_memory_mode(nb_nerf* h, int memory_mode);
  * num_rays * scale, and fn runs on the gradient arena between backward and the optimizer of every step. */
 int nb_nerf_set_global_ray_scale(nb_nerf* h, uint32_t scale);
 int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user);
+/* Switches between nb_field_forward / nb_field_backward (default when nb_field_supported) and the reference's
+ * kernel-by-kernel sequence; returns 1 when the fused kernels are in effect afterwards, 0 otherwise.  Results agree
+ * to the fp32 summation order of the weight gradients.  No counterpart in the reference. */
+int nb_nerf_set_fused_field(nb_nerf* h, int on);
 /* Device pointers of the parameter arena [hash | density W,b | colour W,b] and the slice offsets. */
 int nb_nerf_get_arena(nb_nerf* h, nb_nerf_arena_view* out);
 /* loadHashgrid / loadWeights of both networks from host fp32 arrays (any may be NULL);

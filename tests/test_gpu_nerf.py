@@ -159,7 +159,7 @@ def test_compositing_and_color_grad(cuda, nb, orc, R):
     assert np.max(np.abs(rgb2.cpu().numpy() - i_rgb)) <= ABS_RGB
     # loss gradients from the GPU's own forward results
     grad = torch.full((n, 8), 9.0, dtype=torch.float16, device="cuda"); dsig = torch.zeros(n, dtype=f32, device="cuda")
-    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, up.f(dens), d_col, 8, P(phi), P(rgb), P(dw), P(wsum), P(grad), 8, P(dsig), scale, bias, R,
+    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, up.f(dens), 16, d_col, 8, P(phi), P(rgb), P(dw), P(wsum), P(grad), 8, P(dsig), scale, bias, R,
                                st), "nb_color_grad")
     torch.cuda.synchronize()
     g_ref, ds_ref = orc.color_grad(R, counts, off, t, dens, col, phi.cpu().numpy(), rgb.cpu().numpy(), dw.cpu().numpy(), wsum.cpu().numpy(),

@@ -21,8 +21,9 @@ def _inputs(n, seed):
     return pos, d, half_bits(tgt)
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("n", [300, 8192])
-def test_sample_training_step_matches_oracle(cuda, nb, orc, n):
+def test_sample_training_step_matches_oracle(cuda, nb, orc, n, fused):
     torch = cuda
     pl = importlib.import_module("3dmaker_b200.pipeline")
     L, T = 16, 1 << 15
@@ -31,7 +32,8 @@ def test_sample_training_step_matches_oracle(cuda, nb, orc, n):
     dW, db = make_mlp(32, 64, 16, 2, seed=0)
     cW, cb = make_mlp(32, 64, 8, 3, seed=1)
     model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
-    tr = pl.SampleTrainer(model, n, lr=1e-2, loss_scale=128.0)
+    tr = pl.SampleTrainer(model, n, lr=1e-2, loss_scale=128.0, fused=fused)
+    assert tr.fused == fused
     pos, dirs, tgt = _inputs(n, 5)
     tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
     tr.forward_backward(n)
@@ -42,8 +44,12 @@ def test_sample_training_step_matches_oracle(cuda, nb, orc, n):
     ref = OracleField(L, T, 16, 1.447, scales, model.grid.dense_level_start, (32, 64, 16, 2), (32, 64, 8, 3), table, dW, db, cW, cb, sscales)
     r = ref.forward_backward(pos, dirs, tgt, 128.0)
     assert np.array_equal(dev_half_bits(tr.enc), r["enc"])
-    assert rel_err(tr.d_out.cpu().numpy(), r["d_out"]) <= REL_MLP
-    assert rel_err(half_vals(dev_half_bits(tr.c_in)), half_vals(r["c_in"])) <= REL_MLP
+    if fused:
+        assert rel_err(tr.logit0.cpu().numpy(), r["d_out"][:, 0]) <= REL_MLP
+    else:
+        assert rel_err(tr.d_out.cpu().numpy(), r["d_out"]) <= REL_MLP
+        assert rel_err(half_vals(dev_half_bits(tr.c_in)), half_vals(r["c_in"])) <= REL_MLP
+    assert rel_err(tr.sigma.cpu().numpy(), r["sigma"]) <= 2 * REL_MLP
     assert np.max(np.abs(tr.c_out.cpu().numpy()[:, :3] - r["c_out"][:, :3])) <= 1e-2
     assert abs(tr.loss.item() - r["loss_sum"]) <= 1e-2 * r["loss_sum"]
     assert rel_err(half_vals(dev_half_bits(tr.c_grad)), half_vals(r["c_grad"])) <= 2 * REL_MLP
@@ -91,3 +97,50 @@ def test_training_reduces_loss(cuda, nb):
     losses = [tr.step_host(P(pos), P(dirs), P(half_bits(tgt_f).view(np.float16))) for _ in range(60)]
     assert np.isfinite(losses).all()
     assert losses[-1] < 0.5 * losses[0]
+
+
+@pytest.mark.parametrize("n", [1, 127, 128, 129, 5000, 40000])
+def test_fused_field_kernels_agree_with_the_kernel_sequence(cuda, nb, n):
+    """The two-kernel field path against the kernel-by-kernel one on the same parameters and inputs: every fp16
+    intermediate has the same rounding points, so the encoding, the outputs and the encoding gradient are
+    bit-identical; weight gradients differ by fp32 summation order only."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    L, T = 16, 1 << 15
+    model = pl.FieldModel(torch, L, T, 16, 1.3819, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    pos, dirs, tgt = _inputs(n, 11)
+    out = {}
+    for fused in (False, True):
+        tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=fused)
+        tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+        model.g.zero_()
+        tr.forward_backward(n)
+        torch.cuda.synchronize()
+        out[fused] = dict(enc=dev_half_bits(tr.enc), sigma=tr.sigma.cpu().numpy(), c_out=tr.c_out.cpu().numpy()[:, :3].copy(),
+                          logit=(tr.logit0 if fused else tr.d_out[:, 0]).cpu().numpy(), d_enc=dev_half_bits(tr.d_enc), g=model.g.cpu().numpy().copy(),
+                          loss=tr.loss.item())
+    a, b = out[False], out[True]
+    assert np.array_equal(a["enc"], b["enc"])
+    assert np.array_equal(a["logit"], b["logit"])
+    assert np.array_equal(a["sigma"], b["sigma"])
+    assert np.array_equal(a["c_out"], b["c_out"])
+    assert a["loss"] == b["loss"]
+    assert np.array_equal(a["d_enc"], b["d_enc"])
+    H = model.hash_count
+    assert np.allclose(a["g"][:H], b["g"][:H], rtol=1e-4, atol=1e-7 * np.abs(a["g"][:H]).max())
+    for off, cnt in ((model.off_dw, model.density.weight_count), (model.off_db, model.density.bias_count),
+                     (model.off_cw, model.color.weight_count), (model.off_cb, model.color.bias_count)):
+        ga, gb = a["g"][off:off + cnt], b["g"][off:off + cnt]
+        assert rel_err(gb, ga) <= 1e-4
+    model.g.zero_()
+
+
+def test_fused_field_rejects_other_shapes(cuda, nb):
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    model = pl.FieldModel(torch, 16, 1 << 14, 16, 1.3819, 32, 2, 32, 3)
+    assert pl.SampleTrainer(model, 64).fused is False
+    with pytest.raises(nb.NerfB200Error):
+        pl.SampleTrainer(model, 64, fused=True)

@@ -33,26 +33,27 @@ def _dirs(n, seed):
     return d / np.linalg.norm(d, axis=1, keepdims=True)
 
 
-def _field_pair(torch, nb, ref, L, T, b, n, seed=0):
+def _field_pair(torch, nb, ref, L, T, b, n, seed=0, fused=None):
     pl = importlib.import_module("3dmaker_b200.pipeline")
     table = make_table(L, T, seed=seed, amp=0.1)
     dW, db = make_mlp(32, 64, 16, 2, seed=seed, bias_amp=0.02)
     cW, cb = make_mlp(32, 64, 8, 3, seed=seed + 1, bias_amp=0.02)
     model = pl.FieldModel(torch, L, T, 16, b, 64, 2, 64, 3)
     model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
-    tr = pl.SampleTrainer(model, n, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=1.0)
+    tr = pl.SampleTrainer(model, n, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=1.0, fused=fused)
     rf = ref.lib().ref_field_create(L, T, 16, b, 64, 2, 64, 3, n)
     flat = np.ascontiguousarray(table.ravel())
     ref.lib().ref_field_load(rf, ref.hptr(flat), ref.hptr(dW), ref.hptr(db), ref.hptr(cW), ref.hptr(cb))
     return model, tr, rf, (table, dW, db, cW, cb)
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("b", [1.3819, 1.447])
-def test_field_forward_backward_against_reference_kernels(cuda, nb, ref, b):
+def test_field_forward_backward_against_reference_kernels(cuda, nb, ref, b, fused):
     torch = cuda
     nm = importlib.import_module("3dmaker_b200.nerf")
     L, T, n = 16, 1 << 17, 20000
-    model, tr, rf, _ = _field_pair(torch, nb, ref, L, T, b, n)
+    model, tr, rf, _ = _field_pair(torch, nb, ref, L, T, b, n, fused=fused)
     rng = np.random.default_rng(3)
     pos = make_positions(n, 3); dirs = _dirs(n, 4)
     tgt3 = rng.random((n, 3), dtype=np.float32)
@@ -67,10 +68,13 @@ def test_field_forward_backward_against_reference_kernels(cuda, nb, ref, b):
     r_dout = V(ref.lib().ref_field_density_out(rf), n * 16).reshape(n, 16)
     r_cout = V(ref.lib().ref_field_color_out(rf), n * 3).reshape(n, 3)
     r_cin = V(ref.lib().ref_field_color_in(rf), n * 32, np.float16).view(np.uint16).reshape(n, 32)
-    assert rel_err(tr.d_out.cpu().numpy(), r_dout) <= REL_MLP
     assert np.max(np.abs(tr.c_out.cpu().numpy()[:, :3] - r_cout)) <= 1e-2
-    # SH half of the colour input: same formula, same rounding -> identical bits
-    assert np.array_equal(dev_half_bits(tr.c_in)[:, 16:], r_cin[:, 16:])
+    if fused:
+        assert rel_err(tr.logit0.cpu().numpy(), r_dout[:, 0]) <= REL_MLP
+    else:
+        assert rel_err(tr.d_out.cpu().numpy(), r_dout) <= REL_MLP
+        # SH half of the colour input: same formula, same rounding -> identical bits
+        assert np.array_equal(dev_half_bits(tr.c_in)[:, 16:], r_cin[:, 16:])
     g = model.g.cpu().numpy()
     H = model.hash_count
     r_hash = V(ref.lib().ref_field_hash_grads(rf), H)
@@ -179,7 +183,7 @@ def test_compositing_and_loss_gradients_against_reference_kernels(cuda, nb, ref)
     r = dict(rgb=Z(R, 3), depth=Z(R), phi=Z(R, 3), dw=Z(n), ws=Z(R), grad=Z(n, 3, dt=torch.float16), dsig=Z(n))
     nb.check(lib.nb_composite_train(R, d_off, d_cnt, d_t, d_sig, None, None, d_col8, 8, d_tgt, P(m["rgb"]), P(m["depth"]), P(m["phi"]), P(m["dw"]),
                                     P(m["ws"]), lam, 0.0, bg, st))
-    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, d_dens, d_col8, 8, P(m["phi"]), P(m["rgb"]), P(m["dw"]), P(m["ws"]), P(m["grad"]), 8, P(m["dsig"]),
+    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, d_dens, 16, d_col8, 8, P(m["phi"]), P(m["rgb"]), P(m["dw"]), P(m["ws"]), P(m["grad"]), 8, P(m["dsig"]),
                                scale, bias, R, st))
     ref.lib().ref_volume_rendering(R, d_off, d_cnt, d_t, d_sig, d_col3, d_tgt, P(r["rgb"]), P(r["depth"]), P(r["phi"]), P(r["dw"]), P(r["ws"]), lam, 0.0,
                                    ref.hptr(bgn), 0, 0, st)
