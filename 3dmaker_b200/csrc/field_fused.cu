@@ -504,8 +504,9 @@ extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* den
     size_t smem = nb::FieldSmem<DensityNet, ColorNet>::fwd_bytes();
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
-    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(nb::make_params(grid), io, (__half*)d_enc_save_h, d_sigma, d_logit0,
-                                                                             d_rgb, rgb_stride);
+    nb::GridParams gp = nb::make_params(grid);
+    if (misaligned(d_table_h, 8)) gp.pair_ops = 0;
+    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride);
     NB_CHECK_LAUNCH();
     nb::g_launch_count++;
     return NB_OK;

@@ -102,6 +102,7 @@ struct ScatterTuning {
     int level_end = NB_MAX_LEVELS;
 };
 static ScatterTuning g_scatter_tuning;
+std::atomic<int> g_pair_ops{1};
 
 // Gradient scatter, one thread per (sample, level), level = level_base + blockIdx.y so that all CTAs resident at one
 // time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector reduction.
@@ -140,8 +141,21 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
             if (lane == leader) red_add_v2(base + (size_t)c.idx[k] * 2, sx, sy);
         }
     } else {
+        const bool pair_ops = gp.pair_ops != 0;
 #pragma unroll
-        for (int k = 0; k < 8; k++) red_add_v2(base + (size_t)c.idx[k] * 2, g.x * w[k], g.y * w[k]);
+        for (int j = 0; j < 4; j++) {
+            const uint32_t a = c.idx[2 * j], b = c.idx[2 * j + 1];
+            const float wa = w[2 * j], wb = w[2 * j + 1];
+            if (pair_ops && ((a ^ b) == 1u)) {
+                // x-neighbours in one aligned slot pair: one 16-byte reduction instead of two 8-byte ones
+                const bool a_hi = (a & 1u) != 0;
+                const float wl = a_hi ? wb : wa, wh = a_hi ? wa : wb;
+                red_add_v4(base + (size_t)(a & ~1u) * 2, g.x * wl, g.y * wl, g.x * wh, g.y * wh);
+            } else {
+                red_add_v2(base + (size_t)a * 2, g.x * wa, g.y * wa);
+                red_add_v2(base + (size_t)b * 2, g.x * wb, g.y * wb);
+            }
+        }
     }
 }
 
@@ -329,6 +343,7 @@ extern "C" int nb_hash_encode_forward(const nb_grid_desc* desc, const float* d_p
         return nb_set_error(NB_ERR_INVALID, "nb_hash_encode_forward: positions/output must be 16-byte aligned, levels a multiple of 4");
     if (n == 0) return NB_OK;
     GridParams gp = make_params(desc);
+    if (reinterpret_cast<uintptr_t>(d_table_h) & 7u) gp.pair_ops = 0;
     encode_forward_kernel<<<(unsigned)((n + TILE_ROWS - 1) / TILE_ROWS), CTA_THREADS, 0, (cudaStream_t)stream>>>(
         gp, d_pos4, (const uint32_t*)d_table_h, n, (__half*)d_enc_out_h);
     NB_CHECK_LAUNCH();
@@ -351,6 +366,7 @@ extern "C" int nb_grid_mlp_forward(const nb_grid_desc* desc, const nb_mlp_desc* 
     if (bits & 15u) return nb_set_error(NB_ERR_INVALID, "nb_grid_mlp_forward: device pointers must be 16-byte aligned");
     if (n == 0) return NB_OK;
     GridParams gp = make_params(desc);
+    if (reinterpret_cast<uintptr_t>(d_table_h) & 7u) gp.pair_ops = 0;
     cudaStream_t st = (cudaStream_t)stream;
 #define X(K0, H, OUT, NL)                                                                                         \
     if (mlp->input_dim == K0 && (mlp->hidden_dim == H || NL == 1) && mlp->output_dim == OUT && mlp->num_layers == NL) \
@@ -369,6 +385,7 @@ extern "C" int nb_set_tuning(const char* key, int value) {
     std::string k(key);
     if (k == "scatter_dedupe_levels") g_scatter_tuning.dedupe_levels = value;
     else if (k == "scatter_smem_levels") g_scatter_tuning.smem_levels = value;
+    else if (k == "pair_ops") g_pair_ops = value;
     else if (k == "scatter_level_begin") g_scatter_tuning.level_begin = value;
     else if (k == "scatter_level_end") g_scatter_tuning.level_end = value;
     else return nb_set_error(NB_ERR_INVALID, "nb_set_tuning: unknown key");
@@ -385,6 +402,7 @@ extern "C" int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d
         return nb_set_error(NB_ERR_INVALID, "nb_hash_scatter_backward: misaligned device pointer");
     if (n == 0) return NB_OK;
     GridParams gp = make_params(desc);
+    if (reinterpret_cast<uintptr_t>(d_table_grads) & 15u) gp.pair_ops = 0;
     cudaStream_t st = (cudaStream_t)stream;
     const ScatterTuning tn = g_scatter_tuning;
     const int lb = std::max(0, tn.level_begin), le = std::min(gp.L, tn.level_end);

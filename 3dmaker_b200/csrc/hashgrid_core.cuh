@@ -3,19 +3,24 @@
 // 128-point tile into shared memory.  Arithmetic follows modules/TinyMLP/networkFusionHashtable.cu:62-70,111-222.
 #pragma once
 
+#include <atomic>
+
 #include "mlp_core.cuh"
 
 namespace nb {
 
+extern std::atomic<int> g_pair_ops;  // nb_set_tuning("pair_ops", ...)
+
 struct GridParams {
     int L, T, dls;
+    int pair_ops;  // non-zero: the two x-neighbours of a corner pair that share an aligned slot pair move as one access
     float scales[NB_MAX_LEVELS];   // forward (encode) resolutions
     float sscales[NB_MAX_LEVELS];  // resolutions of the gradient scatter
 };
 
 inline GridParams make_params(const nb_grid_desc* d) {
     GridParams p;
-    p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start;
+    p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start; p.pair_ops = g_pair_ops.load();
     for (int i = 0; i < NB_MAX_LEVELS; i++) { p.scales[i] = d->scales[i]; p.sscales[i] = d->scatter_scales[i]; }
     return p;
 }
@@ -66,6 +71,25 @@ __device__ __forceinline__ void corner_weights(const Corners& c, float (&w)[8]) 
     w[6] = wx1 * (1 - wy1) * (1 - wz1);       w[7] = (1 - wx1) * (1 - wy1) * (1 - wz1);
 }
 
+// The 8 corner entries (feature pairs) of one level.  Corners 2j and 2j+1 differ in x only; whenever their indices
+// differ in the lowest bit only (every even x0 on a hashed level, since the x prime is 1; every even low index on a
+// dense level) both sit in one aligned 8-byte slot pair and are fetched with one load.
+__device__ __forceinline__ void gather_corners(const uint32_t* __restrict__ tl, const Corners& c, bool pair_ops, uint32_t (&f)[8]) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t a = c.idx[2 * j], b = c.idx[2 * j + 1];
+        if (pair_ops && ((a ^ b) == 1u)) {
+            uint2 v = __ldg(reinterpret_cast<const uint2*>(tl + (a & ~1u)));
+            const bool a_hi = (a & 1u) != 0;
+            f[2 * j] = a_hi ? v.y : v.x;
+            f[2 * j + 1] = a_hi ? v.x : v.y;
+        } else {
+            f[2 * j] = __ldg(tl + a);
+            f[2 * j + 1] = __ldg(tl + b);
+        }
+    }
+}
+
 // Fixed-order blend of the reference (networkFusionHashtable.cu:185-201), both features.
 __device__ __forceinline__ uint32_t blend(const uint32_t (&f)[8], const float (&w)[8]) {
     float2 v[8];
@@ -99,10 +123,8 @@ __device__ __forceinline__ void encode_tile(const GridParams& gp, const float* _
             const uint32_t* ta = table2 + (size_t)la * gp.T;
             const uint32_t* tb = table2 + (size_t)(has_b ? lb : la) * gp.T;
             uint32_t fa[8], fb[8];
-#pragma unroll
-            for (int k = 0; k < 8; k++) fa[k] = __ldg(ta + ca.idx[k]);
-#pragma unroll
-            for (int k = 0; k < 8; k++) fb[k] = __ldg(tb + cb.idx[k]);
+            gather_corners(ta, ca, gp.pair_ops != 0, fa);
+            gather_corners(tb, cb, gp.pair_ops != 0, fb);
             float wa[8], wb[8];
             corner_weights(ca, wa);
             corner_weights(cb, wb);

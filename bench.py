@@ -351,6 +351,9 @@ def run_ours(args, rank, world, local_rank):
     nb = importlib.import_module("3dmaker_b200")
     pl = importlib.import_module("3dmaker_b200.pipeline")
     nb.load()
+    for kv in args.tune:
+        k, v = kv.split("=")
+        nb.check(nb.load().nb_set_tuning(k.encode(), int(v)), "nb_set_tuning")
 
     model = pl.FieldModel(torch, L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3])
     table, dW, db, cW, cb = init_params()
@@ -448,7 +451,8 @@ def run_ours(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "l2": "inputs and activations of one step (>1 GB) exceed the 126 MB L2; two input batches alternate",
-                       "parallelism": "dp%d" % world, "field_kernels": "fused" if tr.fused else "sequence"},
+                       "parallelism": "dp%d" % world, "field_kernels": "fused" if tr.fused else "sequence",
+                       "tuning": args.tune},
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "last_loss": loss},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernel_ms": kt,
@@ -471,6 +475,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()
