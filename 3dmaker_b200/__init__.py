@@ -155,7 +155,7 @@ _SIGNATURES = {
                                  c_void_p, c_void_p, c_int, c_void_p]),
     "nb_field_backward": (c_int, [ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_void_p, c_void_p]),
+                                  c_void_p, ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_void_p]),
     "nb_mlp_forward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "nb_mlp_backward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                 c_void_p, c_void_p, c_void_p]),

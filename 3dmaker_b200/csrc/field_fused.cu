@@ -275,7 +275,12 @@ struct FieldGradIO {
     const float* dsigma;      // [n] dL/d(logit 0) through sigma, nullable
     float* dWd; float* dbd;   // density network gradients (accumulated)
     float* dWc; float* dbc;   // colour network gradients (accumulated)
-    __half* denc;             // [n][K0] dL/d(encoding)
+    __half* denc;             // dL/d(encoding): the first denc_cols columns of every row, rows denc_cols halves apart
+    int denc_cols;            // 32 = the full matrix; 4 * k = only the k levels the stand-alone scatter handles; 0 = nothing
+    // gradient scatter done by this kernel for levels [scatter_begin, 16) when table_grads is set
+    const float* pos4;
+    float* table_grads;
+    int scatter_begin;
 };
 
 template <class DS, class CS>
@@ -299,7 +304,7 @@ struct FieldBwd {
 };
 
 template <class DS, class CS>
-__global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(FieldIO io, FieldGradIO gio) {
+__global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(const __grid_constant__ GridParams gp, FieldIO io, FieldGradIO gio) {
     using FB = FieldBwd<DS, CS>;
     constexpr int H = FB::H, IS = FB::IS, HS = FB::HS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -433,14 +438,30 @@ __global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(FieldIO 
             __syncthreads();
             store_da<32, HS>(pk, sDZ, warp, lane);
             __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                int ch = lane + 32 * i;
-                int r = ch >> 2, c8 = ch & 3;
-                int64_t gr = row0 + r;
-                if (gr < io.n) {
-                    uint4 v = *reinterpret_cast<const uint4*>(&sDZ[(16 * warp + r) * HS + c8 * 8]);
-                    st_cs_v4(&gio.denc[gr * 32 + c8 * 8], v);
+            if (gio.denc_cols > 0) {
+                // leading columns of the warp's 16 rows, 8-byte chunks
+                const int cpr = gio.denc_cols >> 2;
+                for (int ch = lane; ch < 16 * cpr; ch += 32) {
+                    int r = ch / cpr, c4 = ch % cpr;
+                    int64_t gr = row0 + r;
+                    if (gr < io.n) {
+                        uint2 v = *reinterpret_cast<const uint2*>(&sDZ[(16 * warp + r) * HS + c4 * 4]);
+                        *reinterpret_cast<uint2*>(&gio.denc[gr * gio.denc_cols + c4 * 4]) = v;
+                    }
+                }
+            }
+            if (gio.table_grads != nullptr) {
+                // Gradient scatter of this tile, fire-and-forget reductions that drain through L2 while the tensor
+                // work of the next tile (and of the other CTA on this SM) goes on: thread = (row, every other level).
+                __syncthreads();
+                const int r = tid & (TILE_ROWS - 1), hsel = tid >> 7;
+                const int64_t row = row_base + r;
+                if (row < io.n) {
+                    const float4 p = ld_nc_f4(gio.pos4 + row * 4);
+                    for (int level = gio.scatter_begin + hsel; level < gp.L; level += 2) {
+                        const float2 gq = __half22float2(*reinterpret_cast<const __half2*>(&sDZ[r * HS + 2 * level]));
+                        if (gq.x != 0.f || gq.y != 0.f) scatter_sample_level(gp, level, p.x, p.y, p.z, gq, gio.table_grads);
+                    }
                 }
             }
             __syncthreads();
@@ -516,7 +537,8 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
                                  const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
                                  const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
                                  const void* d_dcolor_h, const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b,
-                                 float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h, void* stream) {
+                                 float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h, const nb_grid_desc* grid,
+                                 const float* d_pos4, float* d_table_grads, void* stream) {
     if (!density || !color || !d_enc_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b || !d_dcolor_h ||
         !d_grad_density_w || !d_grad_density_b || !d_grad_color_w || !d_grad_color_b || !d_denc_h || n < 0)
         return nb_set_error(NB_ERR_INVALID, "nb_field_backward: null pointer or negative count");
@@ -534,7 +556,21 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
     nb::FieldGradIO gio{};
     gio.enc = (const __half*)d_enc_h; gio.dcolor = (const __half*)d_dcolor_h; gio.dsigma = d_dsigma;
     gio.dWd = d_grad_density_w; gio.dbd = d_grad_density_b; gio.dWc = d_grad_color_w; gio.dbc = d_grad_color_b;
-    gio.denc = (__half*)d_denc_h;
+    gio.denc = (__half*)d_denc_h; gio.denc_cols = 32;
+    nb::GridParams gp{};
+    int shared_levels = 0;
+    const bool scatter = d_table_grads != nullptr;
+    if (scatter) {
+        if (!grid || !d_pos4) return nb_set_error(NB_ERR_INVALID, "nb_field_backward: the fused scatter needs the grid descriptor and positions");
+        if (grid->num_levels != 16) return nb_set_error(NB_ERR_UNSUPPORTED, "nb_field_backward: built for 16 levels");
+        if (misaligned(d_pos4, 16) || misaligned(d_table_grads, 8))
+            return nb_set_error(NB_ERR_INVALID, "nb_field_backward: misaligned positions or table gradient");
+        gp = nb::make_params(grid);
+        if (misaligned(d_table_grads, 16)) gp.pair_ops = 0;
+        shared_levels = nb::scatter_shared_levels(gp, n);
+        gio.pos4 = d_pos4; gio.table_grads = d_table_grads; gio.scatter_begin = shared_levels;
+        gio.denc_cols = 4 * shared_levels;   // only what the shared-memory scatter kernel below reads
+    }
     auto kern = nb::field_backward_kernel<DensityNet, ColorNet>;
     size_t smem = nb::FieldBwd<DensityNet, ColorNet>::smem_bytes();
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -544,8 +580,10 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
     int64_t ntiles = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
     int64_t grid_dim = (int64_t)nb_num_sms() * per_sm;
     if (grid_dim > ntiles) grid_dim = ntiles;
-    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(io, gio);
+    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, gio);
     NB_CHECK_LAUNCH();
     nb::g_launch_count++;
+    if (scatter && shared_levels > 0)
+        return nb::scatter_launch(gp, d_pos4, (const __half*)d_denc_h, 4 * shared_levels, n, d_table_grads, 0, shared_levels, (cudaStream_t)stream);
     return NB_OK;
 }

@@ -109,7 +109,7 @@ std::atomic<int> g_pair_ops{1};
 // Dense levels below dedupe_levels first merge lanes that hit the same entry (as the reference does on every dense
 // level, networkFusionBackwardHashtable.cu:843-887): neighbouring samples of a ray share coarse cells.
 __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
-                                                               const __half* __restrict__ dEnc, int64_t n,
+                                                               const __half* __restrict__ dEnc, int denc_stride, int64_t n,
                                                                float* __restrict__ grads, int level_base, int dedupe_levels) {
     const int level = level_base + blockIdx.y;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -117,13 +117,13 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
     const int lane = threadIdx.x & 31;
     float4 p = ld_nc_f4(pos4 + i * 4);
     const bool dense = level < gp.dls;
-    Corners c;
-    corners_of<true>(p.x, p.y, p.z, gp.sscales[level], dense, gp.T, c);
-    float w[8];
-    corner_weights(c, w);
-    float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * (2 * gp.L) + 2 * level]));
-    float* base = grads + (size_t)level * gp.T * 2;
+    float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
     if (dense && level < dedupe_levels) {
+        Corners c;
+        corners_of<true>(p.x, p.y, p.z, gp.sscales[level], dense, gp.T, c);
+        float w[8];
+        corner_weights(c, w);
+        float* base = grads + (size_t)level * gp.T * 2;
 #pragma unroll
         for (int k = 0; k < 8; k++) {
             float vx = g.x * w[k], vy = g.y * w[k];
@@ -141,21 +141,7 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
             if (lane == leader) red_add_v2(base + (size_t)c.idx[k] * 2, sx, sy);
         }
     } else {
-        const bool pair_ops = gp.pair_ops != 0;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint32_t a = c.idx[2 * j], b = c.idx[2 * j + 1];
-            const float wa = w[2 * j], wb = w[2 * j + 1];
-            if (pair_ops && ((a ^ b) == 1u)) {
-                // x-neighbours in one aligned slot pair: one 16-byte reduction instead of two 8-byte ones
-                const bool a_hi = (a & 1u) != 0;
-                const float wl = a_hi ? wb : wa, wh = a_hi ? wa : wb;
-                red_add_v4(base + (size_t)(a & ~1u) * 2, g.x * wl, g.y * wl, g.x * wh, g.y * wh);
-            } else {
-                red_add_v2(base + (size_t)a * 2, g.x * wa, g.y * wa);
-                red_add_v2(base + (size_t)b * 2, g.x * wb, g.y * wb);
-            }
-        }
+        scatter_sample_level(gp, level, p.x, p.y, p.z, g, grads);
     }
 }
 
@@ -163,8 +149,8 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
 // private copy of the level with shared-memory atomics and adds the non-zero entries to global memory once, so the
 // heavily contended coarse entries see (#CTAs) global reductions instead of (#samples x 8).
 __global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
-                                                           const __half* __restrict__ dEnc, int64_t n, float* __restrict__ grads,
-                                                           int level_base) {
+                                                           const __half* __restrict__ dEnc, int denc_stride, int64_t n,
+                                                           float* __restrict__ grads, int level_base) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* acc = reinterpret_cast<float2*>(smem_raw);
     const int level = level_base + blockIdx.y;
@@ -179,7 +165,7 @@ __global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant
         corners_of<true>(p.x, p.y, p.z, scale, true, gp.T, c);
         float w[8];
         corner_weights(c, w);
-        float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * (2 * gp.L) + 2 * level]));
+        float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
 #pragma unroll
         for (int k = 0; k < 8; k++) {
             atomicAdd(&acc[c.idx[k]].x, g.x * w[k]);
@@ -221,6 +207,49 @@ static int check_desc(const nb_grid_desc* d, const char* who) {
         return nb_set_error(NB_ERR_UNSUPPORTED, "hash grid: table_size must be a power of two");
     if ((int64_t)d->num_levels * d->table_size * 2 > 0xffffffffLL)
         return nb_set_error(NB_ERR_LIMIT, "hash grid: table beyond 2^32 elements");
+    return NB_OK;
+}
+
+// Leading dense levels whose (N+1)^3 float2 grid fits shared memory.
+static constexpr size_t SCATTER_SMEM_CAP = 112 * 1024;
+
+int scatter_shared_levels(const GridParams& gp, int64_t n) {
+    const ScatterTuning tn = g_scatter_tuning;
+    int k = 0;
+    while (k < gp.L && k < gp.dls && k < tn.smem_levels && n >= 16384) {
+        int N_l = (int)std::floor(gp.sscales[k]);
+        if ((size_t)(N_l + 1) * (N_l + 1) * (N_l + 1) * sizeof(float2) > SCATTER_SMEM_CAP) break;
+        k++;
+    }
+    return k;
+}
+
+int scatter_launch(const GridParams& gp, const float* d_pos4, const __half* d_denc, int denc_stride, int64_t n, float* d_table_grads,
+                   int level_begin, int level_end, cudaStream_t st) {
+    const ScatterTuning tn = g_scatter_tuning;
+    const int lb = std::max(level_begin, std::max(0, tn.level_begin)), le = std::min(level_end, std::min(gp.L, tn.level_end));
+    if (le <= lb) return NB_OK;
+    const int smem_end = std::max(lb, std::min(le, scatter_shared_levels(gp, n)));
+    if (smem_end > lb) {
+        size_t smem_bytes = 0;
+        for (int l = lb; l < smem_end; l++) {
+            int N_l = (int)std::floor(gp.sscales[l]);
+            smem_bytes = std::max(smem_bytes, (size_t)(N_l + 1) * (N_l + 1) * (N_l + 1) * sizeof(float2));
+        }
+        NB_CUDA(cudaFuncSetAttribute(scatter_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+        int per_level = std::max(1, nb_num_sms() * 2 / (smem_end - lb));
+        int64_t need = (n + 255) / 256;
+        dim3 grid((unsigned)std::min<int64_t>(per_level, need), smem_end - lb, 1);
+        scatter_smem_kernel<<<grid, 256, smem_bytes, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, lb);
+        NB_CHECK_LAUNCH();
+        g_launch_count++;
+    }
+    if (le > smem_end) {
+        dim3 grid((unsigned)((n + 255) / 256), le - smem_end, 1);
+        scatter_backward_kernel<<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end, tn.dedupe_levels);
+        NB_CHECK_LAUNCH();
+        g_launch_count++;
+    }
     return NB_OK;
 }
 
@@ -403,33 +432,5 @@ extern "C" int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d
     if (n == 0) return NB_OK;
     GridParams gp = make_params(desc);
     if (reinterpret_cast<uintptr_t>(d_table_grads) & 15u) gp.pair_ops = 0;
-    cudaStream_t st = (cudaStream_t)stream;
-    const ScatterTuning tn = g_scatter_tuning;
-    const int lb = std::max(0, tn.level_begin), le = std::min(gp.L, tn.level_end);
-    // leading dense levels whose (N+1)^3 float2 grid fits shared memory
-    constexpr size_t SMEM_CAP = 112 * 1024;
-    int smem_end = lb;
-    size_t smem_bytes = 0;
-    while (smem_end < le && smem_end < gp.dls && smem_end < tn.smem_levels && n >= 16384) {
-        int N_l = (int)std::floor(gp.sscales[smem_end]);
-        size_t bytes = (size_t)(N_l + 1) * (N_l + 1) * (N_l + 1) * sizeof(float2);
-        if (bytes > SMEM_CAP) break;
-        smem_bytes = std::max(smem_bytes, bytes);
-        smem_end++;
-    }
-    if (smem_end > lb) {
-        NB_CUDA(cudaFuncSetAttribute(scatter_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-        int per_level = std::max(1, nb_num_sms() * 2 / (smem_end - lb));
-        int64_t need = (n + 255) / 256;
-        dim3 grid((unsigned)std::min<int64_t>(per_level, need), smem_end - lb, 1);
-        scatter_smem_kernel<<<grid, 256, smem_bytes, st>>>(gp, d_pos4, (const __half*)d_denc_h, n, d_table_grads, lb);
-        g_launch_count++;
-    }
-    if (le > smem_end) {
-        dim3 grid((unsigned)((n + 255) / 256), le - smem_end, 1);
-        scatter_backward_kernel<<<grid, 256, 0, st>>>(gp, d_pos4, (const __half*)d_denc_h, n, d_table_grads, smem_end, tn.dedupe_levels);
-        g_launch_count++;
-    }
-    NB_CHECK_LAUNCH();
-    return NB_OK;
+    return scatter_launch(gp, d_pos4, (const __half*)d_denc_h, 2 * gp.L, n, d_table_grads, 0, gp.L, (cudaStream_t)stream);
 }

@@ -137,6 +137,39 @@ __device__ __forceinline__ void encode_tile(const GridParams& gp, const float* _
     }
 }
 
+// Adds one sample's gradient of one level (feature pair g) to the 8 corner entries of the fp32 table gradient.
+// Backward clamp and scatter resolution as hashTableScatter_Backward (networkFusionBackwardHashtable.cu:797-900).
+__device__ __forceinline__ void scatter_sample_level(const GridParams& gp, int level, float px, float py, float pz, float2 g,
+                                                     float* __restrict__ grads) {
+    Corners c;
+    corners_of<true>(px, py, pz, gp.sscales[level], level < gp.dls, gp.T, c);
+    float w[8];
+    corner_weights(c, w);
+    float* base = grads + (size_t)level * gp.T * 2;
+    const bool pair_ops = gp.pair_ops != 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t a = c.idx[2 * j], b = c.idx[2 * j + 1];
+        const float wa = w[2 * j], wb = w[2 * j + 1];
+        if (pair_ops && ((a ^ b) == 1u)) {
+            // x-neighbours in one aligned slot pair: one 16-byte reduction instead of two 8-byte ones
+            const bool a_hi = (a & 1u) != 0;
+            const float wl = a_hi ? wb : wa, wh = a_hi ? wa : wb;
+            red_add_v4(base + (size_t)(a & ~1u) * 2, g.x * wl, g.y * wl, g.x * wh, g.y * wh);
+        } else {
+            red_add_v2(base + (size_t)a * 2, g.x * wa, g.y * wa);
+            red_add_v2(base + (size_t)b * 2, g.x * wb, g.y * wb);
+        }
+    }
+}
+
+// Host side of the stand-alone scatter (hashgrid.cu): levels [level_begin, level_end) from a gradient matrix whose
+// rows are denc_stride halves apart.  scatter_shared_levels = how many leading levels of a launch over n samples go
+// through the shared-memory accumulation kernel.
+int scatter_shared_levels(const GridParams& gp, int64_t n);
+int scatter_launch(const GridParams& gp, const float* d_pos4, const __half* d_denc, int denc_stride, int64_t n, float* d_table_grads,
+                   int level_begin, int level_end, cudaStream_t st);
+
 // Coalesced write of the encoded tile (128 x 2L halves) to global memory.
 template <int TILE_STRIDE>
 __device__ __forceinline__ void store_enc_tile(const __half* tile, __half* __restrict__ enc_out, int L, int64_t row_base, int64_t n,

@@ -341,7 +341,8 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                                                      m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
                                                      m_arena.W(cn->biasOffset()), n, d_color_grad.as<half>(), d_tmpsigma.as<float>(),
                                                      m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()), m_arena.G(cn->weightOffset()),
-                                                     m_arena.G(cn->biasOffset()), d_denc.as<half>(), stream), "field backward");
+                                                     m_arena.G(cn->biasOffset()), d_denc.as<half>(), &dn->grid(), d_positions.as<float>(),
+                                                     m_arena.G(dn->hashOffset()), stream), "field backward");
                 });
             } else {
                 timed(stream, m_times.colorBwd, [&]() {
@@ -358,10 +359,12 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                                                    d_denc.as<half>(), stream), "density backward");
                 });
             }
-            timed(stream, m_times.scatter, [&]() {
-                throw_on_error(nb_hash_scatter_backward(&dn->grid(), d_positions.as<float>(), d_denc.as<half>(), n, m_arena.G(dn->hashOffset()), stream),
-                               "gradient scatter");
-            });
+            if (!m_fused) {
+                timed(stream, m_times.scatter, [&]() {
+                    throw_on_error(nb_hash_scatter_backward(&dn->grid(), d_positions.as<float>(), d_denc.as<half>(), n, m_arena.G(dn->hashOffset()), stream),
+                                   "gradient scatter");
+                });
+            }
         }
         if (m_gradSync) m_gradSync(m_arena.G(0), m_arena.total, stream);
         timed(stream, m_times.optimizer, [&]() {

@@ -84,9 +84,10 @@ class SampleTrainer:
     """One optimizer step on explicit samples (position, view direction, target colour):
     the 'encode + MLP fwd/bwd + Adam' step of the benchmark.  Buffers are sized once for max_batch."""
 
-    def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0, fused=None):
+    def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0, fused=None, fused_scatter=None):
         """fused=None picks the two-kernel field path (nb_field_forward / nb_field_backward) when it is built for
-        the model's shapes, else the kernel-by-kernel sequence; True / False force one of them."""
+        the model's shapes, else the kernel-by-kernel sequence; True / False force one of them.  fused_scatter
+        (default: on with the fused path) lets the backward kernel scatter the table gradient itself."""
         torch = model.torch
         self.model, self.torch, self.lib = model, torch, model.lib
         self.max_batch = max_batch
@@ -95,6 +96,7 @@ class SampleTrainer:
         if fused and not supported:
             raise nb.NerfB200Error("the fused field kernels are not built for these network shapes")
         self.fused = supported if fused is None else bool(fused)
+        self.fused_scatter = self.fused if fused_scatter is None else (bool(fused_scatter) and self.fused)
         n, dev = max_batch, "cuda"
         d, c = model.density, model.color
         f16, f32 = torch.float16, torch.float32
@@ -135,7 +137,11 @@ class SampleTrainer:
             nb.check(lib.nb_field_backward(ctypes.byref(m.density), ctypes.byref(m.color), P(self.enc), P(self.dirs), None, 0,
                                            m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
                                            P(self.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db), m.ptr("g", m.off_cw),
-                                           m.ptr("g", m.off_cb), P(self.d_enc), st), "nb_field_backward")
+                                           m.ptr("g", m.off_cb), P(self.d_enc), ctypes.byref(m.grid) if self.fused_scatter else None,
+                                           P(self.pos) if self.fused_scatter else None, m.ptr("g", 0) if self.fused_scatter else None,
+                                           st), "nb_field_backward")
+            if self.fused_scatter:
+                return
         else:
             nb.check(lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(self.pos), m.ptr("w_h", 0),
                                              m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), n, P(self.d_out), P(self.enc), P(self.d_acts),

@@ -292,9 +292,15 @@ def time_kernels(torch, tr, n, iters=5):
             "field_backward": lambda: lib.nb_field_backward(ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0,
                                                             m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
                                                             m.ptr("w", m.off_cb), n, P(tr.c_grad), None, m.ptr("g", m.off_dw),
-                                                            m.ptr("g", m.off_db), m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc), st),
+                                                            m.ptr("g", m.off_db), m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc),
+                                                            None, None, None, st),
             "scatter_backward": lambda: lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(tr.pos), P(tr.d_enc), n, m.ptr("g", 0), st),
         }
+        if tr.fused_scatter:
+            calls["field_backward_scatter"] = lambda: lib.nb_field_backward(
+                ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db),
+                m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, P(tr.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db),
+                m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc), ctypes.byref(m.grid), P(tr.pos), m.ptr("g", 0), st)
     else:
         calls = {
             "grid_mlp_forward": lambda: lib.nb_grid_mlp_forward(ctypes.byref(m.grid), ctypes.byref(m.density), P(tr.pos), m.ptr("w_h", 0),
@@ -358,7 +364,7 @@ def run_ours(args, rank, world, local_rank):
     model = pl.FieldModel(torch, L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3])
     table, dW, db, cW, cb = init_params()
     model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
-    tr = pl.SampleTrainer(model, BATCH, fused=False if args.unfused else None, **HYPER)
+    tr = pl.SampleTrainer(model, BATCH, fused=False if args.unfused else None, fused_scatter=False if args.separate_scatter else None, **HYPER)
 
     # two distinct seeded batches per rank, pinned on the host and resident on the device
     host, dev = [], []
@@ -451,7 +457,7 @@ def run_ours(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "l2": "inputs and activations of one step (>1 GB) exceed the 126 MB L2; two input batches alternate",
-                       "parallelism": "dp%d" % world, "field_kernels": "fused" if tr.fused else "sequence",
+                       "parallelism": "dp%d" % world, "field_kernels": ("fused+scatter" if tr.fused_scatter else "fused") if tr.fused else "sequence",
                        "tuning": args.tune},
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "last_loss": loss},
@@ -476,6 +482,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
+    ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()

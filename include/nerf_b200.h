@@ -195,16 +195,20 @@ int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const
                      float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb, int rgb_stride,
                      void* stream);
 
-/* Gradients of both networks and of the encoding from the colour gradient.  Replaces TinyMLP::backward (colour) ->
- * compute_density_grad -> the network half of TinyMLPHashGrid::backward (modules/NeRF/InstantNerf.cu:506-561).
+/* Gradients of both networks, of the encoding and (optionally) of the hash table from the colour gradient.  Replaces
+ * TinyMLP::backward (colour) -> compute_density_grad -> TinyMLPHashGrid::backward (modules/NeRF/InstantNerf.cu:506-561).
  * Hidden activations are derived again from d_enc_h inside the kernel.  d_dcolor_h fp16 [n][8] = dL/d(colour
  * pre-activation) as nb_color_grad / nb_mse_loss_grad write it; d_dsigma[n] (NULL = zeros) is added to the gradient
- * of logit 0.  d_grad_* are ACCUMULATED (fp32); d_denc_h fp16 [n][32] feeds nb_hash_scatter_backward. */
+ * of logit 0.  d_grad_* are ACCUMULATED (fp32).
+ *   d_table_grads == NULL: d_denc_h receives fp16 [n][32] for nb_hash_scatter_backward (grid, d_pos4 unused).
+ *   d_table_grads != NULL: the kernel also scatters into the table gradient as nb_hash_scatter_backward would (its
+ *     reductions drain through L2 underneath the tensor work); d_denc_h is then scratch of at least n * 8 bytes whose
+ *     content is unspecified, grid and d_pos4 (float4 per sample) are required. */
 int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
                       const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h, const float* d_density_b,
                       const void* d_color_w_h, const float* d_color_b, int64_t n, const void* d_dcolor_h, const float* d_dsigma,
                       float* d_grad_density_w, float* d_grad_density_b, float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h,
-                      void* stream);
+                      const nb_grid_desc* grid, const float* d_pos4, float* d_table_grads, void* stream);
 
 /* ---- rays, occupancy march, compaction ------------------------------------------------------- */
 
