@@ -125,7 +125,8 @@ class StepView(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in ("num_steps", "ray_offsets", "ray_indices", "t_sorted", "positions", "density_out", "sigma",
                                         "color_out", "render_rgb", "phi", "dw", "weight_sum", "tmp_dsigma", "color_in", "color_grad",
                                         "density_grad")] + [("last_total_hits", ctypes.c_uint32), ("train_steps", ctypes.c_int32),
-                                                            ("logit_stride", ctypes.c_int32), ("color_stride", ctypes.c_int32)]
+                                                            ("logit_stride", ctypes.c_int32), ("color_stride", ctypes.c_int32),
+                                                            ("rays_consumed", ctypes.c_uint32)]
 
 
 GRAD_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
@@ -198,6 +199,7 @@ _SIGNATURES = {
     "nb_nerf_set_memory_mode": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_global_ray_scale": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_fused_field": (c_int, [c_void_p, c_int]),
+    "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),
     "nb_nerf_load_params": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

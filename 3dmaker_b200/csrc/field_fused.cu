@@ -165,23 +165,33 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid
 __host__ __device__ constexpr int dw_tiles(int K, int NP) { return (NP / 16) * (K / 8); }
 __host__ __device__ constexpr int dw_tpw(int K, int NP) { return (dw_tiles(K, NP) + 7) / 8; }
 
-// dW (NP x K, 16 x 8 register tiles dealt round-robin to the 8 warps) += dZ^T x A
+// dW (NP x K) += dZ^T x A in 16 x 8 register tiles.  Warp w owns the tpw consecutive tiles w*tpw .. w*tpw+tpw-1 of
+// the row-major (mi, ni) tile grid; tpw divides the tiles of a row, so all of them share mi and one dZ^T fragment
+// per 16-row step serves the whole group, and neighbouring ni pairs share one 4-matrix load of A.
 template <int K, int NP, int DZS, int AS>
 __device__ __forceinline__ void accumulate_dw(float (*acc)[4], const __half* sDZ, const __half* sA, int warp, int lane) {
     const int lq = lane >> 3, lr = lane & 7;
-    constexpr int N8 = K / 8;
+    constexpr int N8 = K / 8, TPW = dw_tpw(K, NP);
+    static_assert(dw_tiles(K, NP) == 8 * TPW && N8 % TPW == 0 && (TPW == 1 || TPW % 2 == 0), "tile grid must split evenly over 8 warps");
+    const int id0 = warp * TPW;
+    const int mi = id0 / N8, ni0 = id0 % N8;
 #pragma unroll
-    for (int s = 0; s < dw_tpw(K, NP); s++) {
-        int id = warp + 8 * s;
-        if (id < dw_tiles(K, NP)) {
-            int mi = id / N8, ni = id % N8;
-            float(&c)[4] = acc[s];
+    for (int ks = 0; ks < TILE_ROWS / 16; ks++) {
+        uint32_t a[4];
+        // A operand = dZ^T: element (m, k) = sDZ[16ks + k][16mi + m]
+        ldmatrix_x4_trans(a, &sDZ[(16 * ks + (lq >> 1) * 8 + lr) * DZS + 16 * mi + (lq & 1) * 8]);
+        if constexpr (TPW == 1) {
+            uint32_t b0, b1;
+            // B operand = the layer input: element (k, nn) = sA[16ks + k][8ni + nn]
+            ldmatrix_x2_trans(b0, b1, &sA[(16 * ks + (lq & 1) * 8 + lr) * AS + 8 * ni0]);
+            mma_16816(acc[0], a, b0, b1);
+        } else {
 #pragma unroll
-            for (int ks = 0; ks < TILE_ROWS / 16; ks++) {
-                uint32_t a[4], b0, b1;
-                ldmatrix_x4_trans(a, &sDZ[(16 * ks + (lq >> 1) * 8 + lr) * DZS + 16 * mi + (lq & 1) * 8]);
-                ldmatrix_x2_trans(b0, b1, &sA[(16 * ks + (lq & 1) * 8 + lr) * AS + 8 * ni]);
-                mma_16816(c, a, b0, b1);
+            for (int s = 0; s < TPW; s += 2) {
+                uint32_t b[4];  // matrices: (k 0-7, ni), (k 8-15, ni), (k 0-7, ni+1), (k 8-15, ni+1)
+                ldmatrix_x4_trans(b, &sA[(16 * ks + (lq & 1) * 8 + lr) * AS + 8 * (ni0 + s) + (lq >> 1) * 8]);
+                mma_16816(acc[s], a, b[0], b[1]);
+                mma_16816(acc[s + 1], a, b[2], b[3]);
             }
         }
     }
@@ -190,16 +200,14 @@ __device__ __forceinline__ void accumulate_dw(float (*acc)[4], const __half* sDZ
 template <int K, int N, int NP>
 __device__ __forceinline__ void flush_dw(const float (*acc)[4], float* __restrict__ dW, int warp, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    constexpr int N8 = K / 8;
+    constexpr int N8 = K / 8, TPW = dw_tpw(K, NP);
+    const int id0 = warp * TPW;
+    const int mi = id0 / N8, ni0 = id0 % N8;
 #pragma unroll
-    for (int s = 0; s < dw_tpw(K, NP); s++) {
-        int id = warp + 8 * s;
-        if (id < dw_tiles(K, NP)) {
-            int mi = id / N8, ni = id % N8;
-            int m0 = 16 * mi + g, m1 = m0 + 8, nn = 8 * ni + 2 * t;
-            if (m0 < N) red_add_v2(&dW[m0 * K + nn], acc[s][0], acc[s][1]);
-            if (m1 < N) red_add_v2(&dW[m1 * K + nn], acc[s][2], acc[s][3]);
-        }
+    for (int s = 0; s < TPW; s++) {
+        int m0 = 16 * mi + g, m1 = m0 + 8, nn = 8 * (ni0 + s) + 2 * t;
+        if (m0 < N) red_add_v2(&dW[m0 * K + nn], acc[s][0], acc[s][1]);
+        if (m1 < N) red_add_v2(&dW[m1 * K + nn], acc[s][2], acc[s][3]);
     }
 }
 

@@ -1,0 +1,150 @@
+"""One process per GPU: data-parallel training and pixel-sharded rendering over torch.distributed.
+
+The reference is single-GPU.  Its training step normalises the loss gradients by the number of rays of the whole batch
+(compute_color_grad, modules/NeRF/otherKernels.cu:370) and sums sample gradients into one table, so splitting the rays
+of a batch over ranks and SUM-allreducing the flat gradient arena before the optimizer reproduces the single-GPU
+gradient; every rank then applies the same Adam update to its replica.  Rendering needs no exchange at all: pixels are
+independent, each rank renders its tiles and the frame is gathered once.
+
+Nothing here launches a kernel: the engine (3dmaker_b200.nerf.InstantNerf, or any object with the same few methods)
+does.  The partitioning, the step agreement and the gather are host logic and run on any backend (NCCL on GPUs, gloo
+on CPU).
+"""
+
+def ray_shard(num_rays, rank, world):
+    """Rays [start, start + count) of a global batch that `rank` trains on: contiguous, sizes differ by at most one."""
+    start = rank * num_rays // world
+    end = (rank + 1) * num_rays // world
+    return start, end - start
+
+
+def pixel_tiles(num_pixels, rank, world, tile=4096):
+    """Runs of `tile` consecutive pixels dealt round-robin to the ranks: [(first_pixel, count), ...] of `rank`.
+    Interleaving balances frames whose cost per pixel varies smoothly over the image (empty sky vs the object)."""
+    out = []
+    num_tiles = (num_pixels + tile - 1) // tile
+    for t in range(rank, num_tiles, world):
+        first = t * tile
+        out.append((first, min(tile, num_pixels - first)))
+    return out
+
+
+class DataParallelTrainer:
+    """Wraps a scene engine so that train_rays() takes the GLOBAL ray batch.
+
+    engine needs: set_global_ray_scale(int), set_single_step(bool), set_grad_sync(fn), train_rays(o, d, rgb) -> total
+    optimizer steps so far, rays_consumed(), arena_tensor(name).  dist is torch.distributed (already initialised) or
+    None for a single process."""
+
+    def __init__(self, torch, engine, dist=None):
+        self.torch, self.engine, self.dist = torch, engine, dist
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.world = dist.get_world_size() if dist is not None else 1
+        self._steps_seen = 0
+        self.sync_calls = 0
+        if self.world > 1:
+            engine.set_grad_sync(self._allreduce)
+            # one optimizer step, hence one allreduce, per call on every rank, whatever the local sample count is
+            engine.set_single_step(True)
+        # with equal shards (num_rays a multiple of world) local_rays * world is exactly the global ray count
+        engine.set_global_ray_scale(self.world)
+
+    def _allreduce(self, grad):
+        self.sync_calls += 1
+        self.dist.all_reduce(grad, op=self.dist.ReduceOp.SUM)
+
+    def train_rays(self, rays_o, rays_d, rgb_true):
+        """One optimizer step on the global batch (which must split evenly over the ranks); returns the number of
+        local rays that fitted this rank's sample batch and were trained on (normally all of its shard)."""
+        n = rays_o.shape[0]
+        if n % self.world != 0:
+            raise ValueError("global ray batch (%d) must be a multiple of the number of ranks (%d)" % (n, self.world))
+        start, count = ray_shard(n, self.rank, self.world)
+        before = self._steps_seen
+        self._steps_seen = self.engine.train_rays(rays_o[start:start + count], rays_d[start:start + count], rgb_true[start:start + count])
+        if self.world > 1 and self._steps_seen - before != 1:
+            raise RuntimeError("the engine took %d optimizer steps in single-step mode" % (self._steps_seen - before))
+        return self.engine.rays_consumed() if self.world > 1 else count
+
+    def replicas_in_sync(self):
+        """True when every rank holds bit-identical parameters: compares the 64-bit sum of the raw parameter bits."""
+        w = self.engine.arena_tensor("w")
+        s = w.view(self.torch.int32).to(self.torch.int64).sum().reshape(1)
+        if self.world == 1:
+            return True
+        t = self.torch.stack([s[0], -s[0]])
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return int(t[0].item()) == -int(t[1].item())
+
+
+class ShardedRenderer:
+    """Renders one frame with the pixels split over the ranks and gathers it on rank 0.
+
+    engine needs render(rays_o, rays_d, rgb_out); ray_fn(first_pixel, count, rays_o_out, rays_d_out) writes the rays of
+    a pixel run into [count, 3] slices (nb_generate_rays on a GPU).  No collective touches the data path except the
+    final gather."""
+
+    def __init__(self, torch, engine, ray_fn, dist=None, tile=4096):
+        self.torch, self.engine, self.ray_fn, self.dist, self.tile = torch, engine, ray_fn, dist, tile
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.world = dist.get_world_size() if dist is not None else 1
+        self._rays = None
+
+    def local_pixels(self, num_pixels):
+        return sum(c for _, c in pixel_tiles(num_pixels, self.rank, self.world, self.tile))
+
+    def render_local(self, num_pixels, device):
+        """Renders this rank's tiles into one [local_pixels, 3] tensor (tile order): the rays of all its tiles are
+        generated into one buffer and rendered by ONE engine call, so the engine batches samples across tiles."""
+        torch = self.torch
+        tiles = pixel_tiles(num_pixels, self.rank, self.world, self.tile)
+        total = sum(c for _, c in tiles)
+        if self._rays is None or self._rays[0].shape[0] < max(1, total):
+            self._rays = (torch.empty((max(1, total), 3), dtype=torch.float32, device=device),
+                          torch.empty((max(1, total), 3), dtype=torch.float32, device=device))
+        o, d = self._rays
+        at = 0
+        for first, count in tiles:
+            self.ray_fn(first, count, o[at:at + count], d[at:at + count])
+            at += count
+        out = torch.zeros((max(1, total), 3), dtype=torch.float32, device=device)
+        if total > 0:
+            self.engine.render(o[:total], d[:total], out[:total])
+        return out, tiles
+
+    def render_frame(self, num_pixels, device):
+        """Returns the [num_pixels, 3] frame on rank 0 (None elsewhere)."""
+        torch = self.torch
+        local, tiles = self.render_local(num_pixels, device)
+        if self.world == 1:
+            frame = torch.empty((num_pixels, 3), dtype=torch.float32, device=device)
+            self._place(frame, local, tiles)
+            return frame
+        # equal-size gather: pad every rank's block to the largest one
+        num_tiles = (num_pixels + self.tile - 1) // self.tile
+        max_tiles = (num_tiles + self.world - 1) // self.world
+        padded = torch.zeros((max_tiles * self.tile, 3), dtype=torch.float32, device=device)
+        padded[:sum(c for _, c in tiles)] = local[:sum(c for _, c in tiles)]
+        if self.rank == 0:
+            blocks = [torch.empty_like(padded) for _ in range(self.world)]
+            self.dist.gather(padded, blocks, dst=0)
+            frame = torch.empty((num_pixels, 3), dtype=torch.float32, device=device)
+            for r in range(self.world):
+                self._place(frame, blocks[r], pixel_tiles(num_pixels, r, self.world, self.tile))
+            return frame
+        self.dist.gather(padded, None, dst=0)
+        return None
+
+    @staticmethod
+    def _place(frame, block, tiles):
+        at = 0
+        for first, count in tiles:
+            frame[first:first + count] = block[at:at + count]
+            at += count
+
+
+def gathered_bytes(num_pixels, world, tile=4096):
+    """Bytes rank 0 receives per frame in render_frame (the only traffic of sharded rendering)."""
+    num_tiles = (num_pixels + tile - 1) // tile
+    max_tiles = (num_tiles + world - 1) // world
+    return (world - 1) * max_tiles * tile * 3 * 4 if world > 1 else 0

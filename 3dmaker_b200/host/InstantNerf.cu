@@ -380,6 +380,8 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
         m_times.steps++;
         raysDone += currentChunkRays;
         i++;
+        m_lastRaysConsumed = raysDone;
+        if (m_singleStep) break;
     }
 }
 

@@ -122,6 +122,10 @@ public:
     void rebuildOccupancy(cudaStream_t stream = 0) { earlyOccupancyGridUpdate(stream); }
     int trainSteps() const { return m_trainSteps; }
     uint32_t lastTotalHits() const { return m_lastTotalHits; }
+    // Data parallelism: exactly one optimizer step (hence one gradient exchange) per trainWithRaysHit call; rays of
+    // the call that do not fit the sample batch are left untrained instead of starting a second step.
+    void setSingleStep(bool on) { m_singleStep = on; }
+    uint32_t lastRaysConsumed() const { return m_lastRaysConsumed; }
     const NerfPhaseTimes& phaseTimes() const { return m_times; }
     // Buffers of the last step, for parity tests (valid until the next call).
     struct StepView {
@@ -168,4 +172,6 @@ private:
     int m_trainSteps = 0;
     int m_optSteps = 0;  // Adam step counter (capped at 50000 for the bias corrections)
     uint32_t m_lastTotalHits = 0;
+    uint32_t m_lastRaysConsumed = 0;
+    bool m_singleStep = false;
 };

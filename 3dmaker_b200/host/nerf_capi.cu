@@ -91,6 +91,12 @@ extern "C" int nb_nerf_set_global_ray_scale(nb_nerf* h, uint32_t scale) {
     return NB_OK;
 }
 
+extern "C" int nb_nerf_set_single_step(nb_nerf* h, int on) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    h->impl.setSingleStep(on != 0);
+    return NB_OK;
+}
+
 extern "C" int nb_nerf_set_fused_field(nb_nerf* h, int on) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     return h->impl.setFusedField(on != 0) ? 1 : 0;
@@ -147,7 +153,7 @@ extern "C" int nb_nerf_get_step_view(nb_nerf* h, nb_nerf_step_view* out) {
     out->render_rgb = v.render_rgb; out->phi = v.phi; out->dw = v.dw; out->weight_sum = v.weight_sum; out->tmp_dsigma = v.tmp_dsigma;
     out->color_in = v.color_in; out->color_grad = v.color_grad; out->density_grad = v.density_grad;
     out->last_total_hits = h->impl.lastTotalHits(); out->train_steps = h->impl.trainSteps();
-    out->logit_stride = v.logit_stride; out->color_stride = v.color_stride;
+    out->logit_stride = v.logit_stride; out->color_stride = v.color_stride; out->rays_consumed = h->impl.lastRaysConsumed();
     return NB_OK;
 }
 

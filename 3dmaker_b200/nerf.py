@@ -32,6 +32,7 @@ class InstantNerf:
             raise nb.NerfB200Error("nb_nerf_create failed: " + self.lib.nb_last_error().decode())
         self._cb = None
         self.steps = ctypes.c_int(0)
+        self._hits = np.zeros(4096, np.uint32)      # samples of every optimizer step of the last train_rays() call
 
     def close(self):
         if self.h:
@@ -46,9 +47,16 @@ class InstantNerf:
 
     def train_rays(self, rays_o, rays_d, rgb_true, rgb_out=None, depth=None, sigma=None, stream=None):
         n = rays_o.shape[0]
+        before = self.steps.value
         nb.check(self.lib.nb_nerf_train_rays(self.h, nb.ptr(rays_o), nb.ptr(rays_d), nb.ptr(depth), nb.ptr(sigma), nb.ptr(rgb_true), n,
-                                             ctypes.byref(self.steps), None, nb.ptr(rgb_out), nb.stream_ptr(stream)), "nb_nerf_train_rays")
+                                             ctypes.byref(self.steps), self._hits.ctypes.data_as(ctypes.c_void_p), nb.ptr(rgb_out),
+                                             nb.stream_ptr(stream)), "nb_nerf_train_rays")
+        self._last_steps = self.steps.value - before
         return self.steps.value
+
+    def samples_last_call(self):
+        """Samples (ray-march hits) the last train_rays() call trained on, over all its optimizer steps."""
+        return int(self._hits[:min(self._last_steps, self._hits.size)].astype(np.int64).sum())
 
     def render(self, rays_o, rays_d, rgb_out, stream=None):
         nb.check(self.lib.nb_nerf_render(self.h, nb.ptr(rays_o), nb.ptr(rays_d), rays_o.shape[0], nb.ptr(rgb_out), nb.stream_ptr(stream)),
@@ -68,6 +76,13 @@ class InstantNerf:
 
     def set_global_ray_scale(self, scale):
         nb.check(self.lib.nb_nerf_set_global_ray_scale(self.h, scale))
+
+    def set_single_step(self, on):
+        """Exactly one optimizer step per train_rays() call (data parallelism); see rays_consumed()."""
+        nb.check(self.lib.nb_nerf_set_single_step(self.h, 1 if on else 0))
+
+    def rays_consumed(self):
+        return self.step_view().rays_consumed
 
     def set_fused_field(self, on):
         """One kernel each way for the whole field (default) or the kernel-by-kernel sequence; returns the mode in effect."""

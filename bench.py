@@ -474,12 +474,229 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------------
+# Secondary workloads (not the driver's line): the full NeRF step on the analytic soft-sphere scene and
+# frame rendering along an orbit, both through the scene engine, with the reference's engine as the other arm.
+# ---------------------------------------------------------------------------------------------------------
+SCENE_OPTS = dict(grid_resolution=(128,) * 3, aabb_min=(-.5,) * 3, aabb_max=(.5,) * 3, levels_mipmap=4, hash_table_size=1 << 19,
+                  growth_factor=1.3819, color_hidden_dim=64, color_num_layers=3, batch_size=1 << 18, render_batch_size=1 << 20,
+                  ray_chunk_size=1 << 16, lambda_dist=0.01, lambda_depth=0.0, learning_rate=1e-2, beta2=0.99, epsilon=1e-15,
+                  loss_scale=128.0, density_bias=1.0, bg_color=(1.0, 1.0, 1.0))
+SCENE_WORKLOAD = ("cfg3: analytic soft sphere, 100 cameras 800x800, 128^3 occupancy x1 cascade, L16 F2 T2^19, batch 2^18 samples, "
+                  "ray chunk 65536, distortion loss, Adam")
+RENDER_WORKLOAD = "cfg4: 1920x1080 orbit frames of the cfg3 model after %d training steps, <=1024 samples/ray, early termination"
+
+
+class _RefEngine:
+    """The reference's InstantNerf (oracle/_ref build) behind the few methods the workloads call."""
+
+    def __init__(self, torch, opts):
+        import ctypes
+        from oracle import ref_cuda as ref
+        self.torch, self.ref, self.nb = torch, ref, importlib.import_module("3dmaker_b200")
+        self.h = ref.lib().ref_nerf_create(ctypes.byref(opts), 0)
+        self.steps = 0
+        self._depth = self._sig = None
+        self.hits = torch.zeros(64, dtype=torch.int32).numpy()
+
+    def train_rays(self, o, d, rgb):
+        n = o.shape[0]
+        if self._depth is None or self._depth.shape[0] < n:
+            self._depth = self.torch.full((n,), -1.0, device="cuda"); self._sig = self.torch.ones(n, device="cuda")
+        P = self.nb.ptr
+        self.hits[:] = 0
+        k = self.ref.lib().ref_nerf_train(self.h, P(o), P(d), P(self._depth), P(self._sig), P(rgb), n, None, self.ref.hptr(self.hits),
+                                          self.nb.stream_ptr())
+        self.steps += k
+        return self.steps
+
+    def samples_last_call(self):
+        return int(self.hits.astype("int64").sum())
+
+    def render(self, o, d, out):
+        self.ref.lib().ref_nerf_render(self.h, self.nb.ptr(o), self.nb.ptr(d), o.shape[0], self.nb.ptr(out), self.nb.stream_ptr())
+
+    def close(self):
+        self.ref.lib().ref_nerf_destroy(self.h)
+
+
+def _scene_batches(torch, syn, count, rays, seed0):
+    scene, poses, bg = syn.SoftSphereScene(), syn.sphere_cameras(100), (1.0, 1.0, 1.0)
+    out = []
+    for k in range(count):
+        o, d = syn.random_training_rays(torch, poses, rays, 800, 800, 50.0, seed=seed0 + k)
+        out.append((o, d, syn.ground_truth(torch, scene, o, d, bg)))
+    return out
+
+
+def run_scene(args, rank, world, local_rank):
+    """Full training step (march + field + compositing + loss + backward + scatter + Adam) on the analytic scene.
+    --gpus N: the global ray batch is N x 65536 rays, data-parallel with one gradient allreduce per step."""
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    reference = args.impl == "reference"
+    if reference and rank != 0:
+        return
+    if world > 1 and not reference:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    nb = importlib.import_module("3dmaker_b200")
+    nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
+    D = importlib.import_module("3dmaker_b200.distributed")
+    opts = nm.default_options(**SCENE_OPTS)
+    rays = 1 << 16
+    if reference:
+        from oracle import ref_cuda as ref
+        if not ref.available():
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref3dmaker.so not built (no reference tree at build time)"}))
+            return
+        eng, trainer, nranks = _RefEngine(torch, opts), None, 1
+    else:
+        eng = nm.InstantNerf(torch, opts)
+        trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None)
+        nranks = world
+    batches = _scene_batches(torch, syn, 8, rays * nranks, 9000)
+
+    def step(i):
+        o, d, c = batches[i % len(batches)]
+        if trainer is not None:
+            trainer.train_rays(o, d, c)
+        else:
+            eng.train_rays(o, d, c)
+        return eng.samples_last_call()
+
+    warm = max(args.warmup, 272)          # past the 256 steps of whole-grid occupancy updates
+    for i in range(warm):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1 and not reference:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    samples = 0
+    steps_before = eng.steps if reference else eng.steps.value
+    e0.record()
+    for i in range(args.steps):
+        samples += step(warm + i)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1), float(samples)], dtype=torch.float64, device="cuda")
+    if world > 1 and not reference:
+        tm = t[:1].clone(); dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ts = t[1:].clone(); dist.all_reduce(ts, op=dist.ReduceOp.SUM)
+        t = torch.cat([tm, ts])
+    ms, total = float(t[0].item()), float(t[1].item())
+    opt_steps = (eng.steps if reference else eng.steps.value) - steps_before
+    if rank == 0:
+        line = {"metric": "train samples/s (full NeRF step)", "value": total / (ms / 1000.0), "unit": "samples/s", "n_gpus": nranks,
+                "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": SCENE_WORKLOAD, "rays_per_step_per_gpu": rays, "optimizer_steps": opt_steps,
+                           "samples_per_call": total / args.steps, "rays_per_s": rays * nranks * args.steps / (ms / 1000.0)}}
+        if reference:
+            line["impl"] = "reference"
+        elif trainer is not None:
+            line["config"]["replicas_in_sync"] = None
+        print(json.dumps(line))
+    if trainer is not None and world > 1:
+        ok = trainer.replicas_in_sync()
+        if rank == 0:
+            print(json.dumps({"replicas_in_sync": bool(ok)}))
+        dist.barrier(); dist.destroy_process_group()
+    eng.close()
+
+
+def run_render(args, rank, world, local_rank):
+    """Frames of the trained scene along an orbit, pixels sharded over the ranks, one gather per frame."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    reference = args.impl == "reference"
+    if reference and rank != 0:
+        return
+    if world > 1 and not reference:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    nb = importlib.import_module("3dmaker_b200")
+    nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
+    D = importlib.import_module("3dmaker_b200.distributed")
+    lib = nb.load()
+    opts = nm.default_options(**SCENE_OPTS)
+    train_steps = 400
+    if reference:
+        from oracle import ref_cuda as ref
+        if not ref.available():
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref3dmaker.so not built (no reference tree at build time)"}))
+            return
+        eng = _RefEngine(torch, opts)
+    else:
+        eng = nm.InstantNerf(torch, opts)
+    # every rank trains the same model from the same seeded batches (replicated, no exchange needed for the benchmark)
+    batches = _scene_batches(torch, syn, 8, 1 << 16, 9000)
+    i = 0
+    while (eng.steps if reference else eng.steps.value) < train_steps:
+        eng.train_rays(*batches[i % 8]); i += 1
+    torch.cuda.synchronize()
+    W, H = 1920, 1080
+    focal = syn.focal_from_fov(W, 50.0)
+    pose = {}
+
+    def ray_fn(first, count, o, d):
+        c2w = np.ascontiguousarray(pose["c2w"], np.float32)
+        nb.check(lib.nb_generate_rays(W, H, focal, c2w.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), first, count, nb.ptr(o), nb.ptr(d),
+                                      nb.stream_ptr()), "nb_generate_rays")
+
+    r = D.ShardedRenderer(torch, eng, ray_fn, dist if (world > 1 and not reference) else None, tile=1 << 14)
+    nranks = 1 if reference else world
+
+    def frame(k):
+        pose["c2w"] = syn.orbit_c2w(3.0 * k, 20.0, 1.5)
+        return r.render_frame(W * H, "cuda")
+
+    for k in range(max(args.warmup, 3)):
+        img = frame(k)
+    torch.cuda.synchronize()
+    if nranks > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        img = frame(10 + k)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if nranks > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    if rank == 0:
+        scene = syn.SoftSphereScene()
+        o, d = syn.frame_rays(torch, pose["c2w"], W // 4, H // 4, 50.0)
+        gt = syn.ground_truth(torch, scene, o, d, (1.0, 1.0, 1.0))
+        small = torch.zeros_like(gt)
+        eng.render(o, d, small)
+        torch.cuda.synchronize()
+        line = {"metric": "render Mrays/s", "value": W * H / (ms / 1000.0) / 1e6, "unit": "Mrays/s", "n_gpus": nranks, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic",
+                "config": {"workload": RENDER_WORKLOAD % train_steps, "frame": [W, H], "tile_pixels": 1 << 14,
+                           "gather_bytes_per_frame": D.gathered_bytes(W * H, nranks, 1 << 14),
+                           "psnr_quarter_res_db": float(syn.psnr(torch, small, gt)), "frame_mean": float(img.mean().item())}}
+        if reference:
+            line["impl"] = "reference"
+        print(json.dumps(line))
+    if nranks > 1:
+        dist.barrier(); dist.destroy_process_group()
+    eng.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="field", choices=["field", "scene", "render"],
+                    help="field: the headline step on explicit samples (default, the driver's line); scene: full NeRF training step on the "
+                         "analytic scene; render: 1920x1080 orbit frames, pixels sharded over the ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
@@ -489,7 +706,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.workload == "scene":
+        run_scene(args, rank, world, local_rank)
+    elif args.workload == "render":
+        run_render(args, rank, world, local_rank)
+    elif args.impl == "reference":
         run_reference(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)

@@ -339,6 +339,7 @@ typedef struct nb_nerf_step_view {
     int32_t train_steps;
     int32_t logit_stride; /* density_out[i * logit_stride] = raw logit 0 of sample i: 16 (full rows) or 1 (fused field) */
     int32_t color_stride; /* floats between rows of color_out: 8 or 4 (fused field) */
+    uint32_t rays_consumed; /* rays of the last nb_nerf_train_rays call that were trained on */
 } nb_nerf_step_view;
 
 /* NerfOptions defaults (InstantNerf.h:35-76). */
@@ -360,6 +361,10 @@ int nb_nerf_set_memory_mode(nb_nerf* h, int memory_mode);
  * num_rays * scale, and fn runs on the gradient arena between backward and the optimizer of every step. */
 int nb_nerf_set_global_ray_scale(nb_nerf* h, uint32_t scale);
 int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user);
+/* on != 0: nb_nerf_train_rays runs exactly one optimizer step (one fn call) per call; rays that do not fit the sample
+ * batch are left untrained (nb_nerf_step_view.rays_consumed says how many were used) instead of starting a second
+ * step, so that every rank of a data-parallel job issues the same number of gradient exchanges. */
+int nb_nerf_set_single_step(nb_nerf* h, int on);
 /* Switches between nb_field_forward / nb_field_backward (default when nb_field_supported) and the reference's
  * kernel-by-kernel sequence; returns 1 when the fused kernels are in effect afterwards, 0 otherwise.  Results agree
  * to the fp32 summation order of the weight gradients.  No counterpart in the reference. */

@@ -1,0 +1,178 @@
+"""Data-parallel training and pixel-sharded rendering logic (3dmaker_b200/distributed.py) on two CPU ranks over gloo,
+with a stand-in engine: the partitioning, the one-exchange-per-step rule, replica agreement and the frame gather are
+host logic that needs no GPU."""
+import importlib
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+D = importlib.import_module("3dmaker_b200.distributed")
+
+
+class FakeEngine:
+    """A linear 'field': prediction = P[3, 6] @ [o, d]; squared error against the target; the gradient is normalised
+    by (local rays x global scale) the way the scene engine normalises by the global ray count, summed over rays,
+    handed to the sync hook, then applied with plain SGD.  max_rays mimics the sample batch that bounds one step."""
+
+    def __init__(self, max_rays=1 << 30):
+        self.w = torch.linspace(-0.5, 0.5, 18, dtype=torch.float32)
+        self.g = torch.zeros(18, dtype=torch.float32)
+        self.scale, self.sync, self.single, self.steps, self.max_rays, self.consumed = 1, None, False, 0, max_rays, 0
+
+    def set_global_ray_scale(self, s):
+        self.scale = s
+
+    def set_single_step(self, on):
+        self.single = on
+
+    def set_grad_sync(self, fn):
+        self.sync = fn
+
+    def rays_consumed(self):
+        return self.consumed
+
+    def arena_tensor(self, name):
+        return {"w": self.w, "g": self.g}[name]
+
+    def train_rays(self, o, d, rgb):
+        n, done = o.shape[0], 0
+        while done < n:
+            k = min(self.max_rays, n - done)
+            x = torch.cat([o[done:done + k], d[done:done + k]], dim=1)
+            err = x @ self.w.view(3, 6).t() - rgb[done:done + k]
+            self.g += (2.0 * err.t() @ x / (n * self.scale)).reshape(-1)
+            if self.sync is not None:
+                self.sync(self.g)
+            self.w -= 0.1 * self.g
+            self.g.zero_()
+            self.steps += 1
+            done += k
+            self.consumed = done
+            if self.single:
+                break
+        return self.steps
+
+    def render(self, o, d, out):
+        out.copy_(o * 0.25 + d)
+
+
+def _batch(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.rand((n, 3), generator=g), torch.rand((n, 3), generator=g), torch.rand((n, 3), generator=g)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir, case):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        if case == "train":
+            eng = FakeEngine()
+            tr = D.DataParallelTrainer(torch, eng, dist)
+            used = []
+            for step in range(5):
+                o, d, c = _batch(64, 100 + step)
+                used.append(tr.train_rays(o, d, c))
+            np.save(os.path.join(out_dir, "w%d.npy" % rank), eng.w.numpy())
+            np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([tr.sync_calls, eng.steps, int(tr.replicas_in_sync())] + used))
+        elif case == "overflow":
+            # rank 1's sample batch holds only 20 of its 32 rays: it still takes ONE step and ONE exchange
+            eng = FakeEngine(max_rays=20 if rank == 1 else 1 << 30)
+            tr = D.DataParallelTrainer(torch, eng, dist)
+            o, d, c = _batch(64, 7)
+            used = tr.train_rays(o, d, c)
+            np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([tr.sync_calls, eng.steps, int(tr.replicas_in_sync()), used]))
+        elif case == "drift":
+            eng = FakeEngine()
+            tr = D.DataParallelTrainer(torch, eng, dist)
+            if rank == 1:
+                eng.w[3] += 1e-7
+            np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([int(tr.replicas_in_sync())]))
+        elif case == "render":
+            W, H = 50, 37                                     # 1850 pixels, tile 128 -> 15 tiles, ragged last tile
+            def ray_fn(first, count, o, d):
+                idx = torch.arange(first, first + count, dtype=torch.float32)
+                o.copy_(torch.stack([idx, idx * 2, idx * 3], dim=1))
+                d.copy_(torch.stack([idx % W, idx // W, torch.ones_like(idx)], dim=1))
+            r = D.ShardedRenderer(torch, FakeEngine(), ray_fn, dist, tile=128)
+            frame = r.render_frame(W * H, "cpu")
+            assert (frame is None) == (rank != 0)
+            if rank == 0:
+                np.save(os.path.join(out_dir, "frame.npy"), frame.numpy())
+            np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([r.local_pixels(W * H)]))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(case, tmp_path, world=2):
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), case), nprocs=world, join=True)
+
+
+def test_ray_and_pixel_partitions_cover_everything_once():
+    for n, world in ((64, 2), (65537, 8), (7, 8), (0, 4)):
+        spans = [D.ray_shard(n, r, world) for r in range(world)]
+        assert spans[0][0] == 0 and sum(c for _, c in spans) == n
+        assert all(spans[i][0] + spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+        assert max(c for _, c in spans) - min(c for _, c in spans) <= 1
+    for n, world, tile in ((1850, 2, 128), (1920 * 1080, 8, 4096), (5, 4, 4096), (4096 * 3, 3, 4096)):
+        seen = np.zeros(n, np.int32)
+        for r in range(world):
+            for first, count in D.pixel_tiles(n, r, world, tile):
+                seen[first:first + count] += 1
+        assert np.all(seen == 1)
+    assert D.gathered_bytes(1920 * 1080, 1) == 0
+    assert D.gathered_bytes(1920 * 1080, 8) == 7 * 64 * 4096 * 12
+
+
+def test_two_ranks_reproduce_the_single_process_gradient(tmp_path):
+    _run("train", tmp_path)
+    single = FakeEngine()
+    tr = D.DataParallelTrainer(torch, single, None)
+    for step in range(5):
+        tr.train_rays(*_batch(64, 100 + step))
+    w0, w1 = np.load(tmp_path / "w0.npy"), np.load(tmp_path / "w1.npy")
+    assert np.array_equal(w0, w1)                                   # replicas bit-identical after every rank's update
+    assert np.allclose(w0, single.w.numpy(), rtol=1e-5, atol=1e-6)  # and equal to the one-GPU result (fp32 sum order aside)
+    for r in range(2):
+        meta = np.load(tmp_path / ("meta%d.npy" % r))
+        assert meta[0] == 5 and meta[1] == 5 and meta[2] == 1       # one exchange per step
+        assert list(meta[3:]) == [32] * 5
+
+
+def test_a_rank_that_overflows_its_batch_still_exchanges_once(tmp_path):
+    _run("overflow", tmp_path)
+    m0, m1 = np.load(tmp_path / "meta0.npy"), np.load(tmp_path / "meta1.npy")
+    assert list(m0) == [1, 1, 1, 32]
+    assert list(m1) == [1, 1, 1, 20]
+
+
+def test_replica_drift_is_detected(tmp_path):
+    _run("drift", tmp_path)
+    assert np.load(tmp_path / "meta0.npy")[0] == 0 and np.load(tmp_path / "meta1.npy")[0] == 0
+
+
+def test_sharded_frame_equals_the_single_process_frame(tmp_path):
+    _run("render", tmp_path)
+    W, H = 50, 37
+    idx = np.arange(W * H, dtype=np.float32)
+    o = np.stack([idx, idx * 2, idx * 3], axis=1)
+    d = np.stack([idx % W, idx // W, np.ones_like(idx)], axis=1)
+    assert np.array_equal(np.load(tmp_path / "frame.npy"), o * 0.25 + d)
+    assert np.load(tmp_path / "meta0.npy")[0] + np.load(tmp_path / "meta1.npy")[0] == W * H
+
+
+def test_uneven_global_batch_is_rejected():
+    tr = D.DataParallelTrainer(torch, FakeEngine(), None)
+    tr.world = 2
+    with pytest.raises(ValueError):
+        tr.train_rays(*_batch(63, 1))
