@@ -126,7 +126,7 @@ class StepView(ctypes.Structure):
                                         "color_out", "render_rgb", "phi", "dw", "weight_sum", "tmp_dsigma", "color_in", "color_grad",
                                         "density_grad")] + [("last_total_hits", ctypes.c_uint32), ("train_steps", ctypes.c_int32),
                                                             ("logit_stride", ctypes.c_int32), ("color_stride", ctypes.c_int32),
-                                                            ("rays_consumed", ctypes.c_uint32)]
+                                                            ("rays_consumed", ctypes.c_uint32), ("sample_base", ctypes.c_uint32)]
 
 
 GRAD_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
@@ -172,13 +172,18 @@ _SIGNATURES = {
                                c_void_p]),
     "nb_march_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, ctypes.c_uint32, c_void_p, c_void_p]),
     "nb_march_cutoff": (c_int, [c_void_p, c_void_p, c_int64, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p]),
+    "nb_march_row_stride": (c_int, []),
+    "nb_march_fill": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_march_compact": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p,
+                                 ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_march_emit": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                               ctypes.c_uint32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_composite_infer": (c_int, [c_int64, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                    c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), c_void_p]),
-    "nb_composite_train": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+    "nb_composite_train": (c_int, [c_int64, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, ctypes.POINTER(c_float), c_void_p]),
-    "nb_color_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+    "nb_color_grad": (c_int, [c_int64, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_int, c_void_p, c_float, c_float, ctypes.c_uint32, c_void_p]),
     "nb_occ_sample_cells": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_int, c_int, c_int, ctypes.c_uint64, c_void_p]),
     "nb_occ_sample_occupied": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_int, ctypes.c_uint64, c_void_p]),

@@ -3,9 +3,18 @@
 //
 // Replaces render_rays_kernel and render_rays_distortion_kernel (modules/NeRF/compositing.cu:5-213, launcher
 // launchVolumeRendering :215-279) and compute_color_grad (modules/NeRF/otherKernels.cu:303-409).
-// One thread per ray, samples of a ray contiguous in ray order, exactly the reference's arithmetic.
-// Colour buffers carry a row stride so the colour network's padded [n][8] output and gradient are used in
-// place (the reference un-pads to [n][3] and pads back with two extra kernels, TinyMLP.cu:276-284,361-367).
+//
+// The reference gives every ray to one thread that walks the ray's samples in a loop: neighbouring lanes read
+// addresses a whole ray apart and the loop is a chain of dependent loads, exponentials and multiplies.  Here a WARP
+// owns a ray and lane k owns sample k of the current 32-sample window, so loads are contiguous and everything that
+// the reference carries from sample to sample - transmittance, accumulated colour, the distortion loss's prefix
+// sums, the suffix terms of the gradients - becomes a warp scan with a carry between windows:
+//     T_i      = prod_{j<i} (1 - alpha_j)                       exclusive product scan
+//     W_<i     = sum_{j<i} w_j ,  WM_<i = sum_{j<i} w_j m_j      exclusive sum scans (distortion loss)
+//     C_<=i    = sum_{j<=i} w_j c_j , G_<=i = sum_{j<=i} w_j g_j   inclusive sum scans (gradient suffix terms)
+// The formulas are the reference's; sums are associated differently, so results agree to fp32 rounding, not bitwise.
+// Colour buffers carry a row stride so the colour network's padded output and gradient are used in place (the
+// reference un-pads to [n][3] and pads back with two extra kernels, TinyMLP.cu:276-284,361-367).
 #include <atomic>
 
 #include "common.cuh"
@@ -14,205 +23,272 @@ namespace nb {
 
 extern std::atomic<uint64_t> g_launch_count;
 
-__global__ void __launch_bounds__(256) render_rays_kernel(const uint32_t num_rays, const uint32_t base, const uint32_t raysDone,
-                                                          const uint32_t* __restrict__ ray_offsets, const uint32_t* __restrict__ num_steps,
-                                                          const float* __restrict__ t_sorted, const float* __restrict__ density_sigma,
-                                                          const float* __restrict__ rgb_output, const int rgb_stride,
-                                                          const float* __restrict__ rgb_true, float* __restrict__ final_rgb,
-                                                          float* __restrict__ final_depth, float* __restrict__ phi_out, float3 bg_color) {
-    int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= num_rays) return;
-    uint32_t offset = ray_offsets[r + raysDone] - base;
-    uint32_t count = num_steps[r];
-    float T = 1.0f;
-    float r_c = 0.0f, g_c = 0.0f, b_c = 0.0f;
-    float depth = 0.0f;
-    for (uint32_t i = 0; i < count; ++i) {
-        uint32_t idx = offset + i;
-        float t = t_sorted[idx];
-        float delta_t = 0.0f;
-        if (i < count - 1) delta_t = t_sorted[idx + 1] - t;
-        else delta_t = 1e-3f;
-        if (delta_t < 0.0f) delta_t = 0.0f;
-        float sigma = density_sigma[idx];
-        float alpha = 1.0f - expf(-sigma * delta_t);
-        float weight = alpha * T;
-        r_c += weight * rgb_output[(size_t)idx * rgb_stride + 0];
-        g_c += weight * rgb_output[(size_t)idx * rgb_stride + 1];
-        b_c += weight * rgb_output[(size_t)idx * rgb_stride + 2];
-        depth += weight * t;
-        T *= (1.0f - alpha);
-        if (T < 1e-4f) break;
+constexpr unsigned FULL = 0xffffffffu;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_incl_sum(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float n = __shfl_up_sync(FULL, v, o);
+        if (lane >= o) v += n;
     }
-    r_c += T * bg_color.x;
-    g_c += T * bg_color.y;
-    b_c += T * bg_color.z;
-    final_rgb[r * 3 + 0] = r_c;
-    final_rgb[r * 3 + 1] = g_c;
-    final_rgb[r * 3 + 2] = b_c;
-    if (final_depth != nullptr) final_depth[r] = depth;
-    if (rgb_true != nullptr && phi_out != nullptr) {
-        phi_out[r * 3 + 0] = 2.0f * (r_c - rgb_true[r * 3 + 0]);
-        phi_out[r * 3 + 1] = 2.0f * (g_c - rgb_true[r * 3 + 1]);
-        phi_out[r * 3 + 2] = 2.0f * (b_c - rgb_true[r * 3 + 2]);
+    return v;
+}
+__device__ __forceinline__ float warp_incl_prod(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float n = __shfl_up_sync(FULL, v, o);
+        if (lane >= o) v *= n;
+    }
+    return v;
+}
+// value of the lane below (identity for lane 0): turns an inclusive scan into an exclusive one
+__device__ __forceinline__ float from_lane_below(float incl, int lane, float identity) {
+    float n = __shfl_up_sync(FULL, incl, 1);
+    return lane == 0 ? identity : n;
+}
+
+// Sample i of a ray with `count` samples starting at `first`: distance, distance of the next sample, interval clamped
+// at zero.  The last sample has no successor and gets a 1e-3 interval: as the literal where NOMINAL_LAST (the
+// inference and gradient kernels of the reference), as (t + 1e-3) - t otherwise (its training kernel) - the two differ
+// in the last bits and each kernel keeps its own form.
+struct Interval {
+    float t, t_next, dt;
+};
+template <bool NOMINAL_LAST>
+__device__ __forceinline__ Interval load_interval(const float* __restrict__ t_sorted, uint32_t first, uint32_t i, uint32_t count) {
+    Interval v;
+    v.t = t_sorted[first + i];
+    v.t_next = (i + 1 < count) ? t_sorted[first + i + 1] : v.t + 1e-3f;
+    v.dt = (NOMINAL_LAST && i + 1 >= count) ? 1e-3f : v.t_next - v.t;
+    if (v.dt < 0.0f) { v.dt = 0.0f; v.t_next = v.t; }
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// inference: colour and depth of a ray, stopping once the transmittance has dropped below 1e-4
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) composite_infer_kernel(const uint32_t num_rays, const uint32_t sample_base,
+                                                              const uint32_t* __restrict__ ray_offsets, const uint32_t* __restrict__ num_steps,
+                                                              const float* __restrict__ t_sorted, const float* __restrict__ sigma_in,
+                                                              const float* __restrict__ rgb_in, const int rgb_stride,
+                                                              const float* __restrict__ rgb_true, float* __restrict__ final_rgb,
+                                                              float* __restrict__ final_depth, float* __restrict__ phi_out, float3 bg) {
+    const uint32_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= num_rays) return;
+    const uint32_t first = ray_offsets[r] - sample_base;
+    const uint32_t count = num_steps[r];
+    float T = 1.0f;  // transmittance in front of the current window
+    float cr = 0.f, cg = 0.f, cb = 0.f, depth = 0.f;
+    for (uint32_t w0 = 0; w0 < count; w0 += 32) {
+        const uint32_t i = w0 + lane;
+        const bool valid = i < count;
+        float alpha = 0.f, t = 0.f;
+        if (valid) {
+            Interval iv = load_interval<true>(t_sorted, first, i, count);
+            t = iv.t;
+            alpha = 1.0f - expf(-sigma_in[first + i] * iv.dt);
+        }
+        const float incl = warp_incl_prod(1.0f - alpha, lane);
+        const float T_before = T * from_lane_below(incl, lane, 1.0f);
+        // the reference leaves its loop after the first sample that takes T below 1e-4: sample i counts exactly when
+        // the transmittance in front of it is still at least 1e-4
+        const bool live = valid && T_before >= 1e-4f;
+        if (live) {
+            const float w = alpha * T_before;
+            const float* c = rgb_in + (size_t)(first + i) * rgb_stride;
+            cr += w * c[0]; cg += w * c[1]; cb += w * c[2];
+            depth += w * t;
+        }
+        const unsigned live_mask = __ballot_sync(FULL, live);
+        const int last = 31 - __clz((int)live_mask);            // live_mask != 0: lane 0 of a window is live or the loop ended
+        const float T_after_last = __shfl_sync(FULL, T * incl, last);
+        T = T_after_last;
+        if (live_mask != __ballot_sync(FULL, valid) || T < 1e-4f) break;
+    }
+    cr = warp_sum(cr); cg = warp_sum(cg); cb = warp_sum(cb); depth = warp_sum(depth);
+    if (lane == 0) {
+        cr += T * bg.x; cg += T * bg.y; cb += T * bg.z;
+        final_rgb[r * 3 + 0] = cr; final_rgb[r * 3 + 1] = cg; final_rgb[r * 3 + 2] = cb;
+        if (final_depth != nullptr) final_depth[r] = depth;
+        if (rgb_true != nullptr && phi_out != nullptr) {
+            phi_out[r * 3 + 0] = 2.0f * (cr - rgb_true[r * 3 + 0]);
+            phi_out[r * 3 + 1] = 2.0f * (cg - rgb_true[r * 3 + 1]);
+            phi_out[r * 3 + 2] = 2.0f * (cb - rgb_true[r * 3 + 2]);
+        }
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// training: colour, depth, dL/dw of the distortion (and depth-prior) loss per sample, sum_i w_i dL/dw_i per ray
+// ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float disparity_warp(float t, float t_near, float inv_g_range) {
     return (1.0f - t_near / fmaxf(t, 1e-4f)) * inv_g_range;
 }
 
-__global__ void __launch_bounds__(256) render_rays_distortion_kernel(
-    const uint32_t num_rays, const uint32_t* __restrict__ ray_offsets, const uint32_t* __restrict__ num_steps,
-    const float* __restrict__ t_sorted, const float* __restrict__ density_sigma, const float* __restrict__ depth_chunk,
-    const float* __restrict__ sigma_chunk, const float* __restrict__ rgb_output, const int rgb_stride, const float* __restrict__ rgb_true,
+__global__ void __launch_bounds__(256) composite_train_kernel(
+    const uint32_t num_rays, const uint32_t sample_base, const uint32_t* __restrict__ ray_offsets, const uint32_t* __restrict__ num_steps,
+    const float* __restrict__ t_sorted, const float* __restrict__ sigma_in, const float* __restrict__ depth_prior,
+    const float* __restrict__ sigma_prior_in, const float* __restrict__ rgb_in, const int rgb_stride, const float* __restrict__ rgb_true,
     float* __restrict__ final_rgb, float* __restrict__ final_depth, float* __restrict__ phi_out, float* __restrict__ dw_out,
-    float* __restrict__ weight_sum, float lambda_dist, float lambda_depth, float3 bg_color) {
-    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    float* __restrict__ weight_sum, float lambda_dist, float lambda_depth, float3 bg) {
+    const uint32_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
     if (r >= num_rays) return;
-    uint32_t offset = ray_offsets[r];
-    uint32_t count = num_steps[r];
-    float d_prior = depth_chunk ? depth_chunk[r] : -1.0f;
-    float sigma_prior = sigma_chunk ? sigma_chunk[r] : -1.0f;
-    float depth_weight_loss = (d_prior >= 0) ? lambda_depth : 0.0f;
-    float t_near = (count > 0) ? fmaxf(t_sorted[offset], 1e-4f) : 1.0f;
-    float t_far_ray = (count > 0) ? t_sorted[offset + count - 1] : 1.0f;
-    float g_far = 1.0f - t_near / fmaxf(t_far_ray, t_near + 1e-4f);
-    float inv_g_range = (g_far > 1e-6f) ? (1.0f / g_far) : 0.0f;
+    const uint32_t first = ray_offsets[r] - sample_base;
+    const uint32_t count = num_steps[r];
+    const float d_prior = depth_prior ? depth_prior[r] : -1.0f;
+    const float s_prior = sigma_prior_in ? sigma_prior_in[r] : -1.0f;
+    const float depth_lambda = (d_prior >= 0) ? lambda_depth : 0.0f;
+    // normalised disparity s(t) = (1 - t_near / t) / g_far over the ray's own sample range
+    const float t_near = (count > 0) ? fmaxf(t_sorted[first], 1e-4f) : 1.0f;
+    const float t_far = (count > 0) ? t_sorted[first + count - 1] : 1.0f;
+    const float g_far = 1.0f - t_near / fmaxf(t_far, t_near + 1e-4f);
+    const float inv_g = (g_far > 1e-6f) ? (1.0f / g_far) : 0.0f;
+
+    // pass 1: weights (staged in dw_out), colour, depth, W = sum w, WM = sum w m, depth-prior normaliser
     float T = 1.0f;
-    float r_c = 0.0f, g_c = 0.0f, b_c = 0.0f;
-    float depth = 0.0f;
-    float c = 2.0f / 3;
-    float dw_global_sum = 0.0f, dwm_global_sum = 0.0f, dw_sum = 0.0f, dwm_sum = 0.0f, depth_loss_sum = 0.0f;
-    for (uint32_t i = 0; i < count; i++) {
-        uint32_t idx = offset + i;
-        float t = t_sorted[idx];
-        float t_next = (i < count - 1) ? t_sorted[idx + 1] : (t + 1e-3f);
-        float delta_t = t_next - t;
-        if (delta_t < 0.0f) { delta_t = 0.0f; t_next = t; }
-        float s = disparity_warp(t, t_near, inv_g_range);
-        float s_next = disparity_warp(t_next, t_near, inv_g_range);
-        float m = 0.5f * (s + s_next);
-        float sigma = density_sigma[idx];
-        float alpha = 1.0f - expf(-sigma * delta_t);
-        float weight = alpha * T;
-        r_c += weight * rgb_output[(size_t)idx * rgb_stride + 0];
-        g_c += weight * rgb_output[(size_t)idx * rgb_stride + 1];
-        b_c += weight * rgb_output[(size_t)idx * rgb_stride + 2];
-        depth += weight * t;
-        T *= (1.0f - alpha);
-        dw_global_sum += weight;
-        dwm_global_sum += weight * m;
-        float tx = (t - d_prior) / sigma_prior;
-        float depthWeight = expf(-0.5f * tx * tx) * delta_t;
-        depth_loss_sum += depthWeight;
-        dw_out[idx] = weight;
+    float cr = 0.f, cg = 0.f, cb = 0.f, depth = 0.f, W = 0.f, WM = 0.f, DN = 0.f;
+    float w_keep = 0.f;  // this lane's weight when the ray fits one window (the common case): pass 2 skips the re-read
+    for (uint32_t w0 = 0; w0 < count; w0 += 32) {
+        const uint32_t i = w0 + lane;
+        const bool valid = i < count;
+        float alpha = 0.f, t = 0.f, m = 0.f, dterm = 0.f;
+        if (valid) {
+            Interval iv = load_interval<false>(t_sorted, first, i, count);
+            t = iv.t;
+            m = 0.5f * (disparity_warp(iv.t, t_near, inv_g) + disparity_warp(iv.t_next, t_near, inv_g));
+            alpha = 1.0f - expf(-sigma_in[first + i] * iv.dt);
+            const float tx = (iv.t - d_prior) / s_prior;
+            dterm = expf(-0.5f * tx * tx) * iv.dt;
+        }
+        const float incl = warp_incl_prod(1.0f - alpha, lane);
+        const float w = alpha * (T * from_lane_below(incl, lane, 1.0f));
+        if (valid) {
+            const float* c = rgb_in + (size_t)(first + i) * rgb_stride;
+            cr += w * c[0]; cg += w * c[1]; cb += w * c[2];
+            depth += w * t; W += w; WM += w * m; DN += dterm;
+            dw_out[first + i] = w;
+        }
+        w_keep = w;
+        T *= __shfl_sync(FULL, incl, 31);
     }
-    depth_loss_sum = 1.0f / fmaxf(depth_loss_sum, 1e-8f);
-    float weight_g_sum = 0.0f;
-    for (uint32_t i = 0; i < count; i++) {
-        uint32_t idx = offset + i;
-        float t = t_sorted[idx];
-        float t_next = (i < count - 1) ? t_sorted[idx + 1] : (t + 1e-3f);
-        float delta_t = t_next - t;
-        if (delta_t < 0.0f) { delta_t = 0.0f; t_next = t; }
-        float s = disparity_warp(t, t_near, inv_g_range);
-        float s_next = disparity_warp(t_next, t_near, inv_g_range);
-        float m = 0.5f * (s + s_next);
-        float delta_s = s_next - s;
-        if (delta_s < 0.0f) delta_s = 0.0f;
-        float crrWeight = dw_out[idx];
-        float tx = (t - d_prior) / sigma_prior;
-        float depthWeight = expf(-0.5f * tx * tx) * delta_t * depth_loss_sum;
-        float depthLoss = -depthWeight * (1.0f / fmaxf(crrWeight, 1e-6));
-        float dl_bilinear = m * (2 * dw_sum - dw_global_sum) + (dwm_global_sum - 2 * dwm_sum);
-        dw_out[idx] = lambda_dist * (2 * (dl_bilinear) + c * crrWeight * delta_s) + depth_weight_loss * depthLoss;
-        weight_g_sum += crrWeight * (lambda_dist * (2 * (dl_bilinear) + c * crrWeight * delta_s) + depth_weight_loss * depthLoss);
-        dw_sum += crrWeight;
-        dwm_sum += crrWeight * m;
+    cr = warp_sum(cr); cg = warp_sum(cg); cb = warp_sum(cb); depth = warp_sum(depth);
+    W = warp_sum(W); WM = warp_sum(WM); DN = warp_sum(DN);
+    const float depth_norm = 1.0f / fmaxf(DN, 1e-8f);
+
+    // pass 2: dL/dw_i = lambda (2 (m_i (2 W_<i - W) + (WM - 2 WM_<i)) + (2/3) w_i ds_i) + depth term
+    float W_lt = 0.f, WM_lt = 0.f, wg = 0.f;
+    const float two_thirds = 2.0f / 3;
+    for (uint32_t w0 = 0; w0 < count; w0 += 32) {
+        const uint32_t i = w0 + lane;
+        const bool valid = i < count;
+        float w = 0.f, m = 0.f, ds = 0.f, dloss = 0.f;
+        if (valid) {
+            Interval iv = load_interval<false>(t_sorted, first, i, count);
+            const float s = disparity_warp(iv.t, t_near, inv_g), s_next = disparity_warp(iv.t_next, t_near, inv_g);
+            m = 0.5f * (s + s_next);
+            ds = fmaxf(s_next - s, 0.0f);
+            w = (count <= 32) ? w_keep : dw_out[first + i];
+            const float tx = (iv.t - d_prior) / s_prior;
+            dloss = -(expf(-0.5f * tx * tx) * iv.dt * depth_norm) * (1.0f / fmaxf(w, 1e-6));
+        }
+        const float w_incl = warp_incl_sum(w, lane), wm_incl = warp_incl_sum(w * m, lane);
+        const float w_before = W_lt + (w_incl - w), wm_before = WM_lt + (wm_incl - w * m);
+        if (valid) {
+            const float bilinear = m * (2 * w_before - W) + (WM - 2 * wm_before);
+            const float g = lambda_dist * (2 * bilinear + two_thirds * w * ds) + depth_lambda * dloss;
+            dw_out[first + i] = g;
+            wg += w * g;
+        }
+        W_lt += __shfl_sync(FULL, w_incl, 31);
+        WM_lt += __shfl_sync(FULL, wm_incl, 31);
     }
-    weight_sum[r] = weight_g_sum;
-    r_c += T * bg_color.x;
-    g_c += T * bg_color.y;
-    b_c += T * bg_color.z;
-    final_rgb[r * 3 + 0] = r_c;
-    final_rgb[r * 3 + 1] = g_c;
-    final_rgb[r * 3 + 2] = b_c;
-    if (final_depth != nullptr) final_depth[r] = depth;
-    if (rgb_true != nullptr && phi_out != nullptr) {
-        phi_out[r * 3 + 0] = 2.0f * (r_c - rgb_true[r * 3 + 0]);
-        phi_out[r * 3 + 1] = 2.0f * (g_c - rgb_true[r * 3 + 1]);
-        phi_out[r * 3 + 2] = 2.0f * (b_c - rgb_true[r * 3 + 2]);
+    wg = warp_sum(wg);
+    if (lane == 0) {
+        weight_sum[r] = wg;
+        cr += T * bg.x; cg += T * bg.y; cb += T * bg.z;
+        final_rgb[r * 3 + 0] = cr; final_rgb[r * 3 + 1] = cg; final_rgb[r * 3 + 2] = cb;
+        if (final_depth != nullptr) final_depth[r] = depth;
+        if (rgb_true != nullptr && phi_out != nullptr) {
+            phi_out[r * 3 + 0] = 2.0f * (cr - rgb_true[r * 3 + 0]);
+            phi_out[r * 3 + 1] = 2.0f * (cg - rgb_true[r * 3 + 1]);
+            phi_out[r * 3 + 2] = 2.0f * (cb - rgb_true[r * 3 + 2]);
+        }
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// loss gradients per sample: dL/d(colour pre-activation) in fp16 and dL/d(logit 0) through sigma
+// ---------------------------------------------------------------------------------------------------------
 // GRAD8: the gradient row is 8 halves wide (16-byte store, channels 3..7 zero); otherwise 3 halves.
 template <bool GRAD8>
-__global__ void __launch_bounds__(256) color_grad_kernel(const uint32_t numRays, const uint32_t* __restrict__ num_steps,
-                                                         const uint32_t* __restrict__ ray_offsets, const float* __restrict__ t_sorted,
-                                                         const float* __restrict__ density_mlp_out, const int logit_stride,
-                                                         const float* __restrict__ color_mlp_out, const int color_stride, const float* __restrict__ phi_chunk,
-                                                         const float* __restrict__ final_rgb, const float* __restrict__ dw_out,
-                                                         const float* __restrict__ weight_sum, __half* __restrict__ custom_color_grad,
-                                                         float* __restrict__ tmp_dsigma, float loss_scale, const float densityBias,
-                                                         const uint32_t totalRaysBatch) {
-    int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= numRays) return;
-    float currentT = 1.0f;
-    float3 currentRgb = make_float3(0.0f, 0.0f, 0.0f);
-    float currentWeightG = 0.0f;
-    uint32_t rayIdx = ray_offsets[idx];
-    float crrWeightGSum = weight_sum[idx];
-    uint32_t maxDepth = num_steps[idx];
-    float phi_r = phi_chunk[idx * 3], phi_g = phi_chunk[idx * 3 + 1], phi_b = phi_chunk[idx * 3 + 2];
-    float final_r = final_rgb[idx * 3], final_g = final_rgb[idx * 3 + 1], final_b = final_rgb[idx * 3 + 2];
-    float delta_t;
-    for (int depth_idx = 0; depth_idx < maxDepth; depth_idx++) {
-        uint32_t i = rayIdx + depth_idx;
-        float t_current = t_sorted[i];
-        if (depth_idx == maxDepth - 1) delta_t = 1e-3f;
-        else delta_t = fmaxf(t_sorted[i + 1] - t_current, 0.0f);
-        float sigma = expf(fminf(density_mlp_out[(size_t)i * logit_stride] - densityBias, 8.0f));
-        float alpha = 1.0f - expf(-sigma * delta_t);
-        float weight = currentT * alpha;
-        float c_r = color_mlp_out[(size_t)i * color_stride + 0];
-        float c_g = color_mlp_out[(size_t)i * color_stride + 1];
-        float c_b = color_mlp_out[(size_t)i * color_stride + 2];
-        currentRgb.x += weight * c_r;
-        currentRgb.y += weight * c_g;
-        currentRgb.z += weight * c_b;
-        float batch_scale = 1.0f / (float)totalRaysBatch;
-        float cg_r = phi_r * weight * c_r * (1.0f - c_r) * loss_scale * batch_scale;
-        float cg_g = phi_g * weight * c_g * (1.0f - c_g) * loss_scale * batch_scale;
-        float cg_b = phi_b * weight * c_b * (1.0f - c_b) * loss_scale * batch_scale;
-        cg_r = fmaxf(-65504.0f, fminf(65504.0f, cg_r));
-        cg_g = fmaxf(-65504.0f, fminf(65504.0f, cg_g));
-        cg_b = fmaxf(-65504.0f, fminf(65504.0f, cg_b));
-        if (cg_r != cg_r || cg_g != cg_g || cg_b != cg_b) { cg_r = 0.0f; cg_g = 0.0f; cg_b = 0.0f; }
-        if (GRAD8) {
-            uint4 v = make_uint4(pack_half2(cg_r, cg_g), pack_half2(cg_b, 0.0f), 0u, 0u);
-            *reinterpret_cast<uint4*>(custom_color_grad + (size_t)i * 8) = v;
-        } else {
-            custom_color_grad[(size_t)i * 3 + 0] = __float2half(cg_r);
-            custom_color_grad[(size_t)i * 3 + 1] = __float2half(cg_g);
-            custom_color_grad[(size_t)i * 3 + 2] = __float2half(cg_b);
+__global__ void __launch_bounds__(256) loss_grad_kernel(const uint32_t num_rays, const uint32_t sample_base, const uint32_t* __restrict__ num_steps,
+                                                        const uint32_t* __restrict__ ray_offsets, const float* __restrict__ t_sorted,
+                                                        const float* __restrict__ logit0, const int logit_stride,
+                                                        const float* __restrict__ rgb_in, const int rgb_stride, const float* __restrict__ phi_in,
+                                                        const float* __restrict__ final_rgb, const float* __restrict__ dw_in,
+                                                        const float* __restrict__ weight_sum, __half* __restrict__ color_grad,
+                                                        float* __restrict__ dsigma_out, float loss_scale, const float density_bias,
+                                                        const uint32_t total_rays) {
+    const uint32_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= num_rays) return;
+    const uint32_t first = ray_offsets[r] - sample_base;
+    const uint32_t count = num_steps[r];
+    const float wg_total = weight_sum[r];
+    const float phi_r = phi_in[r * 3], phi_g = phi_in[r * 3 + 1], phi_b = phi_in[r * 3 + 2];
+    const float fin_r = final_rgb[r * 3], fin_g = final_rgb[r * 3 + 1], fin_b = final_rgb[r * 3 + 2];
+    const float scale = loss_scale * (1.0f / (float)total_rays);
+    float T = 1.0f, acc_r = 0.f, acc_g = 0.f, acc_b = 0.f, acc_wg = 0.f;  // carries: everything up to the current window
+    for (uint32_t w0 = 0; w0 < count; w0 += 32) {
+        const uint32_t i = w0 + lane;
+        const bool valid = i < count;
+        float alpha = 0.f, sigma = 0.f, dt = 0.f, c_r = 0.f, c_g = 0.f, c_b = 0.f, g = 0.f;
+        if (valid) {
+            Interval iv = load_interval<true>(t_sorted, first, i, count);
+            dt = iv.dt;
+            sigma = expf(fminf(logit0[(size_t)(first + i) * logit_stride] - density_bias, 8.0f));
+            alpha = 1.0f - expf(-sigma * dt);
+            const float* c = rgb_in + (size_t)(first + i) * rgb_stride;
+            c_r = c[0]; c_g = c[1]; c_b = c[2];
+            g = dw_in[first + i];
         }
-        float suff_r = final_r - currentRgb.x;
-        float suff_g = final_g - currentRgb.y;
-        float suff_b = final_b - currentRgb.z;
-        float ds_r = currentT * c_r * (1.0f - alpha) - suff_r;
-        float ds_g = currentT * c_g * (1.0f - alpha) - suff_g;
-        float ds_b = currentT * c_b * (1.0f - alpha) - suff_b;
-        float g_i = dw_out[i];
-        currentWeightG += weight * g_i;
-        float suffix_weight = crrWeightGSum - currentWeightG;
-        float d_sigma_i = delta_t * (ds_r * phi_r + ds_g * phi_g + ds_b * phi_b);
-        d_sigma_i += delta_t * (g_i * currentT * (1.0f - alpha) - suffix_weight);
-        float ds = d_sigma_i * sigma * loss_scale * batch_scale;
-        ds = fmaxf(-65504.0f, fminf(65504.0f, ds));
-        if (ds != ds) ds = 0.0f;
-        tmp_dsigma[i] = ds;
-        currentT = currentT * (1.0f - alpha);
+        const float incl = warp_incl_prod(1.0f - alpha, lane);
+        const float T_before = T * from_lane_below(incl, lane, 1.0f);
+        const float w = T_before * alpha;
+        // colour composited up to and including this sample, and the same for w g
+        const float cum_r = acc_r + warp_incl_sum(w * c_r, lane), cum_g = acc_g + warp_incl_sum(w * c_g, lane);
+        const float cum_b = acc_b + warp_incl_sum(w * c_b, lane), cum_wg = acc_wg + warp_incl_sum(w * g, lane);
+        if (valid) {
+            float gr = phi_r * w * c_r * (1.0f - c_r) * scale, gg = phi_g * w * c_g * (1.0f - c_g) * scale, gb = phi_b * w * c_b * (1.0f - c_b) * scale;
+            gr = fmaxf(-65504.0f, fminf(65504.0f, gr)); gg = fmaxf(-65504.0f, fminf(65504.0f, gg)); gb = fmaxf(-65504.0f, fminf(65504.0f, gb));
+            if (gr != gr || gg != gg || gb != gb) { gr = 0.0f; gg = 0.0f; gb = 0.0f; }
+            if (GRAD8) {
+                *reinterpret_cast<uint4*>(color_grad + (size_t)(first + i) * 8) = make_uint4(pack_half2(gr, gg), pack_half2(gb, 0.0f), 0u, 0u);
+            } else {
+                __half* o = color_grad + (size_t)(first + i) * 3;
+                o[0] = __float2half(gr); o[1] = __float2half(gg); o[2] = __float2half(gb);
+            }
+            // d/d sigma_i of the colour loss: this sample's own term minus everything composited behind it
+            const float keep = T_before * (1.0f - alpha);
+            const float ds_r = keep * c_r - (fin_r - cum_r), ds_g = keep * c_g - (fin_g - cum_g), ds_b = keep * c_b - (fin_b - cum_b);
+            float d = dt * (ds_r * phi_r + ds_g * phi_g + ds_b * phi_b);
+            // ... and of the distortion / depth loss through the weights
+            d += dt * (g * keep - (wg_total - cum_wg));
+            d = d * sigma * scale;
+            d = fmaxf(-65504.0f, fminf(65504.0f, d));
+            if (d != d) d = 0.0f;
+            dsigma_out[first + i] = d;
+        }
+        T *= __shfl_sync(FULL, incl, 31);
+        acc_r = __shfl_sync(FULL, cum_r, 31); acc_g = __shfl_sync(FULL, cum_g, 31);
+        acc_b = __shfl_sync(FULL, cum_b, 31); acc_wg = __shfl_sync(FULL, cum_wg, 31);
     }
 }
 
@@ -220,64 +296,66 @@ __global__ void __launch_bounds__(256) color_grad_kernel(const uint32_t numRays,
 
 using namespace nb;
 
+static unsigned warp_grid(int64_t rays) { return (unsigned)((rays * 32 + 255) / 256); }
+
 extern "C" int nb_composite_infer(int64_t num_rays, uint32_t base, uint32_t rays_done, const uint32_t* d_ray_offsets,
                                   const uint32_t* d_num_steps, const float* d_t_sorted, const float* d_sigma, const float* d_rgb,
                                   int rgb_stride, const float* d_rgb_true, float* d_final_rgb, float* d_final_depth, float* d_phi,
                                   const float* bg_color3, void* stream) {
     if (!d_ray_offsets || !d_num_steps || !d_t_sorted || !d_sigma || !d_rgb || !d_final_rgb || !bg_color3 || num_rays < 0 ||
-        num_rays > 0x7fffffff || rgb_stride < 3)
+        num_rays > 0x3ffffff || rgb_stride < 3)
         return nb_set_error(NB_ERR_INVALID, "nb_composite_infer: null pointer, bad ray count or rgb stride < 3");
     if (num_rays == 0) return NB_OK;
-    render_rays_kernel<<<(unsigned)((num_rays + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        (uint32_t)num_rays, base, rays_done, d_ray_offsets, d_num_steps, d_t_sorted, d_sigma, d_rgb, rgb_stride, d_rgb_true, d_final_rgb,
+    composite_infer_kernel<<<warp_grid(num_rays), 256, 0, (cudaStream_t)stream>>>(
+        (uint32_t)num_rays, base, d_ray_offsets + rays_done, d_num_steps, d_t_sorted, d_sigma, d_rgb, rgb_stride, d_rgb_true, d_final_rgb,
         d_final_depth, d_phi, make_float3(bg_color3[0], bg_color3[1], bg_color3[2]));
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;
 }
 
-extern "C" int nb_composite_train(int64_t num_rays, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps, const float* d_t_sorted,
-                                  const float* d_sigma, const float* d_depth_prior, const float* d_sigma_prior, const float* d_rgb,
-                                  int rgb_stride, const float* d_rgb_true, float* d_final_rgb, float* d_final_depth, float* d_phi,
-                                  float* d_dw_out, float* d_weight_sum, float lambda_dist, float lambda_depth, const float* bg_color3,
-                                  void* stream) {
+extern "C" int nb_composite_train(int64_t num_rays, uint32_t sample_base, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps,
+                                  const float* d_t_sorted, const float* d_sigma, const float* d_depth_prior, const float* d_sigma_prior,
+                                  const float* d_rgb, int rgb_stride, const float* d_rgb_true, float* d_final_rgb, float* d_final_depth,
+                                  float* d_phi, float* d_dw_out, float* d_weight_sum, float lambda_dist, float lambda_depth,
+                                  const float* bg_color3, void* stream) {
     if (!d_ray_offsets || !d_num_steps || !d_t_sorted || !d_sigma || !d_rgb || !d_final_rgb || !d_dw_out || !d_weight_sum || !bg_color3 ||
-        num_rays < 0 || num_rays > 0x7fffffff || rgb_stride < 3)
+        num_rays < 0 || num_rays > 0x3ffffff || rgb_stride < 3)
         return nb_set_error(NB_ERR_INVALID, "nb_composite_train: null pointer, bad ray count or rgb stride < 3");
     if (num_rays == 0) return NB_OK;
-    render_rays_distortion_kernel<<<(unsigned)((num_rays + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        (uint32_t)num_rays, d_ray_offsets, d_num_steps, d_t_sorted, d_sigma, d_depth_prior, d_sigma_prior, d_rgb, rgb_stride, d_rgb_true,
-        d_final_rgb, d_final_depth, d_phi, d_dw_out, d_weight_sum, lambda_dist, lambda_depth,
+    composite_train_kernel<<<warp_grid(num_rays), 256, 0, (cudaStream_t)stream>>>(
+        (uint32_t)num_rays, sample_base, d_ray_offsets, d_num_steps, d_t_sorted, d_sigma, d_depth_prior, d_sigma_prior, d_rgb, rgb_stride,
+        d_rgb_true, d_final_rgb, d_final_depth, d_phi, d_dw_out, d_weight_sum, lambda_dist, lambda_depth,
         make_float3(bg_color3[0], bg_color3[1], bg_color3[2]));
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;
 }
 
-extern "C" int nb_color_grad(int64_t num_rays, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, const float* d_t_sorted,
-                             const float* d_logit0, int logit_stride, const float* d_color_out, int color_stride, const float* d_phi,
-                             const float* d_final_rgb, const float* d_dw_out, const float* d_weight_sum, void* d_color_grad_h,
-                             int grad_stride, float* d_tmp_dsigma, float loss_scale, float density_bias, uint32_t total_rays_batch,
-                             void* stream) {
+extern "C" int nb_color_grad(int64_t num_rays, uint32_t sample_base, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets,
+                             const float* d_t_sorted, const float* d_logit0, int logit_stride, const float* d_color_out, int color_stride,
+                             const float* d_phi, const float* d_final_rgb, const float* d_dw_out, const float* d_weight_sum,
+                             void* d_color_grad_h, int grad_stride, float* d_tmp_dsigma, float loss_scale, float density_bias,
+                             uint32_t total_rays_batch, void* stream) {
     if (!d_num_steps || !d_ray_offsets || !d_t_sorted || !d_logit0 || logit_stride < 1 || !d_color_out || !d_phi || !d_final_rgb || !d_dw_out ||
-        !d_weight_sum || !d_color_grad_h || !d_tmp_dsigma || num_rays < 0 || num_rays > 0x7fffffff || color_stride < 3)
+        !d_weight_sum || !d_color_grad_h || !d_tmp_dsigma || num_rays < 0 || num_rays > 0x3ffffff || color_stride < 3)
         return nb_set_error(NB_ERR_INVALID, "nb_color_grad: null pointer, bad ray count or colour stride < 3");
     if (grad_stride != 3 && grad_stride != 8) return nb_set_error(NB_ERR_UNSUPPORTED, "nb_color_grad: gradient row stride must be 3 or 8 halves");
     if (grad_stride == 8 && (reinterpret_cast<uintptr_t>(d_color_grad_h) & 15u))
         return nb_set_error(NB_ERR_INVALID, "nb_color_grad: 8-wide gradient rows must be 16-byte aligned");
     if (total_rays_batch == 0) return nb_set_error(NB_ERR_INVALID, "nb_color_grad: total_rays_batch must be positive");
     if (num_rays == 0) return NB_OK;
-    unsigned grid = (unsigned)((num_rays + 255) / 256);
+    cudaStream_t st = (cudaStream_t)stream;
     if (grad_stride == 8)
-        color_grad_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t)num_rays, d_num_steps, d_ray_offsets, d_t_sorted, d_logit0, logit_stride,
-                                                                        d_color_out, color_stride, d_phi, d_final_rgb, d_dw_out, d_weight_sum,
-                                                                        (__half*)d_color_grad_h, d_tmp_dsigma, loss_scale, density_bias,
-                                                                        total_rays_batch);
+        loss_grad_kernel<true><<<warp_grid(num_rays), 256, 0, st>>>((uint32_t)num_rays, sample_base, d_num_steps, d_ray_offsets, d_t_sorted, d_logit0,
+                                                                    logit_stride, d_color_out, color_stride, d_phi, d_final_rgb, d_dw_out,
+                                                                    d_weight_sum, (__half*)d_color_grad_h, d_tmp_dsigma, loss_scale, density_bias,
+                                                                    total_rays_batch);
     else
-        color_grad_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t)num_rays, d_num_steps, d_ray_offsets, d_t_sorted, d_logit0, logit_stride,
-                                                                         d_color_out, color_stride, d_phi, d_final_rgb, d_dw_out, d_weight_sum,
-                                                                         (__half*)d_color_grad_h, d_tmp_dsigma, loss_scale, density_bias,
-                                                                         total_rays_batch);
+        loss_grad_kernel<false><<<warp_grid(num_rays), 256, 0, st>>>((uint32_t)num_rays, sample_base, d_num_steps, d_ray_offsets, d_t_sorted, d_logit0,
+                                                                     logit_stride, d_color_out, color_stride, d_phi, d_final_rgb, d_dw_out,
+                                                                     d_weight_sum, (__half*)d_color_grad_h, d_tmp_dsigma, loss_scale, density_bias,
+                                                                     total_rays_batch);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

@@ -1,17 +1,21 @@
-// Rays: slab test against the outermost cascade, hierarchical DDA march over the occupancy bitfield
-// (count pass and emit pass), exclusive scan of the per-ray counts and the sample-budget cutoff.
+// Rays: slab test against the outermost cascade, the walk over the cascaded occupancy pyramid, exclusive scan of the
+// per-ray sample counts and the compaction of the samples of a ray range into the field kernels' input.
 //
 // Replaces compute_ray_aabb_inv_kernel (modules/NeRF/otherKernels.cu:91-154), march_rays_dda_calc_hits,
 // custom_exclusive_sum, find_cutoff_ray_kernel / find_cutoff_ray_from_kernel and march_rays_dda_offset
 // (modules/NeRF/processRays.cu:486-549, 626-929) and the host orchestration processRaysHitLinear /
 // processRaysHitData / processRaysHitPositions (processRays.cu:931-1173).
 //
-// What differs from the reference: the cutoff (how many whole rays fit the sample budget), the batch's first
-// sample and its sample total are written to a small device-side "plan" by the scan itself, and the emit
-// kernel reads the plan from device memory.  The reference reads those numbers back to the host between
-// kernels (three blocking copies per optimizer step); here the host needs them only to size the following
-// launches and can read the 16-byte plan once.  The sample list itself (counts, offsets, ray ids, t,
-// contracted positions, all in ray order) is the reference's, expression for expression.
+// The sample list (counts, offsets, ray ids, t, contracted positions, all in ray order) is the reference's, bit for
+// bit; how it is produced is not:
+//   * ONE walk per ray.  The reference walks every ray twice per batch (count, then emit) and, when training, walks
+//     all remaining rays of the chunk again for every optimizer step.  Here the walk stores the sample distances of a
+//     ray in that ray's row of a scratch matrix [ray][1024] (HBM is plentiful: 4 KB per ray) together with the count;
+//     a batch is then cut out of the rows by a warp-per-ray copy that also evaluates the contracted positions.
+//   * Where to cut is decided by the host from the scanned offsets, read back once per walk instead of once (the
+//     reference: three times) per batch.
+//   * A probe order that skips the pyramid descent inside solid regions (see walk_ray).
+// The two-pass entry points (count / scan / cutoff / emit) remain for callers that want the reference's sequence.
 #include <atomic>
 
 #include "common.cuh"
@@ -21,11 +25,15 @@ namespace nb {
 extern std::atomic<uint64_t> g_launch_count;
 
 constexpr uint32_t MAX_HITS = 1024;  // per-ray sample cap, modules/NeRF/InstantNerf.h:24
+constexpr int MAX_MIP_LEVELS = 8;
 
 struct Scene {
     uint3 res;
     float3 aabb_min, aabb_max;
     int num_cascades, levels, spv;
+    uint32_t level_offset[MAX_MIP_LEVELS];  // first cell of every pyramid level inside a cascade
+    uint32_t pyramid_cells;                 // cells of one cascade's whole pyramid
+    int nested;                             // every level halves the one below exactly (resolution divisible by 2^(levels-1))
 };
 
 static Scene make_scene(const nb_scene_desc* d) {
@@ -34,6 +42,15 @@ static Scene make_scene(const nb_scene_desc* d) {
     s.aabb_min = make_float3(d->aabb_min[0], d->aabb_min[1], d->aabb_min[2]);
     s.aabb_max = make_float3(d->aabb_max[0], d->aabb_max[1], d->aabb_max[2]);
     s.num_cascades = d->num_cascades; s.levels = d->mip_levels; s.spv = d->samples_per_voxel;
+    uint32_t off = 0;
+    uint3 r = s.res;
+    for (int l = 0; l < MAX_MIP_LEVELS; l++) {
+        s.level_offset[l] = off;
+        if (l < s.levels) { off += r.x * r.y * r.z; r.x >>= 1; r.y >>= 1; r.z >>= 1; }
+    }
+    s.pyramid_cells = off;
+    const uint32_t m = (1u << (s.levels - 1)) - 1u;
+    s.nested = ((s.res.x & m) == 0 && (s.res.y & m) == 0 && (s.res.z & m) == 0) ? 1 : 0;
     return s;
 }
 
@@ -43,172 +60,222 @@ __global__ void __launch_bounds__(256) ray_aabb_kernel(const uint32_t num_rays, 
                                                        float* __restrict__ nears, float* __restrict__ fars) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= num_rays) return;
-    float scale = exp2f((float)(num_cascades - 1));
-    float3 min_bound = make_float3(aabb_min.x * scale, aabb_min.y * scale, aabb_min.z * scale);
-    float3 max_bound = make_float3(aabb_max.x * scale, aabb_max.y * scale, aabb_max.z * scale);
-    float3 o = rays_o[i];
-    float3 d = rays_d[i];
-    if (fabsf(d.x) < 1e-8f) d.x = 1e-8f;
-    if (fabsf(d.y) < 1e-8f) d.y = 1e-8f;
-    if (fabsf(d.z) < 1e-8f) d.z = 1e-8f;
-    float3 d_inv;
-    d_inv.x = 1.0f / d.x;
-    d_inv.y = 1.0f / d.y;
-    d_inv.z = 1.0f / d.z;
-    rays_d_inv[i] = d_inv;
-    float t1x = (min_bound.x - o.x) * d_inv.x, t2x = (max_bound.x - o.x) * d_inv.x;
-    if (t1x > t2x) { float tmp = t1x; t1x = t2x; t2x = tmp; }
-    float t1y = (min_bound.y - o.y) * d_inv.y, t2y = (max_bound.y - o.y) * d_inv.y;
-    if (t1y > t2y) { float tmp = t1y; t1y = t2y; t2y = tmp; }
-    float t1z = (min_bound.z - o.z) * d_inv.z, t2z = (max_bound.z - o.z) * d_inv.z;
-    if (t1z > t2z) { float tmp = t1z; t1z = t2z; t2z = tmp; }
-    float t_enter = fmaxf(fmaxf(t1x, t1y), t1z);
-    float t_exit = fminf(fminf(t2x, t2y), t2z);
-    if (t_enter > t_exit || t_exit < 0.0f) {
-        nears[i] = 0.0f;
-        fars[i] = 0.0f;
-    } else {
-        nears[i] = fmaxf(t_enter, 0.0f);
-        fars[i] = t_exit;
+    const float scale = exp2f((float)(num_cascades - 1));
+    const float lo[3] = {aabb_min.x * scale, aabb_min.y * scale, aabb_min.z * scale};
+    const float hi[3] = {aabb_max.x * scale, aabb_max.y * scale, aabb_max.z * scale};
+    const float3 o3 = rays_o[i], d3 = rays_d[i];
+    const float o[3] = {o3.x, o3.y, o3.z};
+    float d[3] = {d3.x, d3.y, d3.z};
+    float inv[3];
+    float t_enter = -INFINITY, t_exit = INFINITY;
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+        if (fabsf(d[a]) < 1e-8f) d[a] = 1e-8f;
+        inv[a] = 1.0f / d[a];
+        const float ta = (lo[a] - o[a]) * inv[a], tb = (hi[a] - o[a]) * inv[a];
+        t_enter = fmaxf(t_enter, fminf(ta, tb));
+        t_exit = fminf(t_exit, fmaxf(ta, tb));
     }
+    rays_d_inv[i] = make_float3(inv[0], inv[1], inv[2]);
+    const bool miss = t_enter > t_exit || t_exit < 0.0f;
+    nears[i] = miss ? 0.0f : fmaxf(t_enter, 0.0f);
+    fars[i] = miss ? 0.0f : t_exit;
 }
 
-// modules/NeRF/processRays.cu:11-19
+// Which cascade a point belongs to: ceil(log2(largest |p| / box half-extent ratio)), modules/NeRF/processRays.cu:11-19.
 __device__ __forceinline__ int get_cascade(float3 pos, float3 aabb_min, float3 aabb_max, int num_cascades) {
-    float rx = fmaxf(pos.x / aabb_max.x, pos.x / aabb_min.x);
-    float ry = fmaxf(pos.y / aabb_max.y, pos.y / aabb_min.y);
-    float rz = fmaxf(pos.z / aabb_max.z, pos.z / aabb_min.z);
-    float max_scale = fmaxf(rx, fmaxf(ry, rz));
+    const float rx = fmaxf(pos.x / aabb_max.x, pos.x / aabb_min.x);
+    const float ry = fmaxf(pos.y / aabb_max.y, pos.y / aabb_min.y);
+    const float rz = fmaxf(pos.z / aabb_max.z, pos.z / aabb_min.z);
+    const float max_scale = fmaxf(rx, fmaxf(ry, rz));
     if (max_scale <= 1.0f) return 0;
-    int cascade = (int)ceilf(log2f(max_scale));
-    return max(0, min(cascade, num_cascades - 1));
+    return max(0, min((int)ceilf(log2f(max_scale)), num_cascades - 1));
 }
 
-// modules/NeRF/processRays.cu:21-46
+__device__ __forceinline__ float contract_axis(float v) {
+    return fabsf(v) <= 1.0f ? v : (2.0f - 1.0f / fabsf(v)) * copysignf(1.0f, v);
+}
+
+// World position -> the unit cube the hash grid is defined on: [-1, 1] of the inner box maps linearly, everything
+// outside is folded into (1, 2) per axis, then (c + 2) / 4.  modules/NeRF/processRays.cu:21-46.
 __device__ __forceinline__ float3 contract_pos(float3 pos, float3 aabb_min, float3 aabb_max) {
-    float3 aabb_extent = make_float3(aabb_max.x - aabb_min.x, aabb_max.y - aabb_min.y, aabb_max.z - aabb_min.z);
-    float3 rel_pos = make_float3((pos.x - aabb_min.x) / aabb_extent.x, (pos.y - aabb_min.y) / aabb_extent.y,
-                                 (pos.z - aabb_min.z) / aabb_extent.z);
-    float3 norm_pos = make_float3(rel_pos.x * 2.0f - 1.0f, rel_pos.y * 2.0f - 1.0f, rel_pos.z * 2.0f - 1.0f);
-    float3 contracted;
-    contracted.x = fabsf(norm_pos.x) <= 1.0f ? norm_pos.x : (2.0f - 1.0f / fabsf(norm_pos.x)) * copysignf(1.0f, norm_pos.x);
-    contracted.y = fabsf(norm_pos.y) <= 1.0f ? norm_pos.y : (2.0f - 1.0f / fabsf(norm_pos.y)) * copysignf(1.0f, norm_pos.y);
-    contracted.z = fabsf(norm_pos.z) <= 1.0f ? norm_pos.z : (2.0f - 1.0f / fabsf(norm_pos.z)) * copysignf(1.0f, norm_pos.z);
-    return make_float3(fmaxf(0.0f, fminf((contracted.x + 2.0f) * 0.25f, 1.0f)), fmaxf(0.0f, fminf((contracted.y + 2.0f) * 0.25f, 1.0f)),
-                       fmaxf(0.0f, fminf((contracted.z + 2.0f) * 0.25f, 1.0f)));
+    const float ex = aabb_max.x - aabb_min.x, ey = aabb_max.y - aabb_min.y, ez = aabb_max.z - aabb_min.z;
+    const float rx = (pos.x - aabb_min.x) / ex, ry = (pos.y - aabb_min.y) / ey, rz = (pos.z - aabb_min.z) / ez;
+    const float cx = contract_axis(rx * 2.0f - 1.0f), cy = contract_axis(ry * 2.0f - 1.0f), cz = contract_axis(rz * 2.0f - 1.0f);
+    return make_float3(fmaxf(0.0f, fminf((cx + 2.0f) * 0.25f, 1.0f)), fmaxf(0.0f, fminf((cy + 2.0f) * 0.25f, 1.0f)),
+                       fmaxf(0.0f, fminf((cz + 2.0f) * 0.25f, 1.0f)));
 }
 
-// modules/NeRF/processRays.cu:83-93
-__device__ __forceinline__ uint32_t get_mipmap_offset(uint3 base_res, int target_level) {
-    uint32_t offset = 0;
-    uint3 res = base_res;
-    for (int l = 0; l < target_level; ++l) {
-        offset += res.x * res.y * res.z;
-        res.x >>= 1; res.y >>= 1; res.z >>= 1;
-    }
-    return offset;
+// The voxel of pyramid level `level` that holds the point at relative position `rel` of its cascade box: is it
+// occupied, and at which ray distance does the ray leave it.
+struct Probe {
+    bool occupied;
+    float exit_t;
+};
+
+struct RayConst {
+    float3 o, d_inv;
+    float3 ahead;  // 1 where the ray moves towards +axis, else 0: selects the far face of a voxel
+};
+
+__device__ __forceinline__ Probe probe_level(const Scene& sc, const RayConst& rc, const uint8_t* __restrict__ bits, int level, uint32_t cascade_base,
+                                             float3 box_min, float3 box_extent, float3 rel) {
+    const uint32_t rx = sc.res.x >> level, ry = sc.res.y >> level, rz = sc.res.z >> level;
+    const float sx = box_extent.x / rx, sy = box_extent.y / ry, sz = box_extent.z / rz;  // voxel size
+    const int vx = max(0, min((int)floorf(rel.x * rx), (int)rx - 1));
+    const int vy = max(0, min((int)floorf(rel.y * ry), (int)ry - 1));
+    const int vz = max(0, min((int)floorf(rel.z * rz), (int)rz - 1));
+    const uint32_t cell = cascade_base + sc.level_offset[level] + vz * (rx * ry) + vy * rx + vx;
+    Probe p;
+    p.occupied = (bits[cell >> 3] >> (cell & 7u)) & 1u;
+    const float fx = box_min.x + (vx + rc.ahead.x) * sx, fy = box_min.y + (vy + rc.ahead.y) * sy, fz = box_min.z + (vz + rc.ahead.z) * sz;
+    p.exit_t = fminf(fminf((fx - rc.o.x) * rc.d_inv.x, (fy - rc.o.y) * rc.d_inv.y), (fz - rc.o.z) * rc.d_inv.z);
+    return p;
 }
 
-// The DDA walk shared by the count pass (EMIT = false) and the emit pass.  One thread per ray.
-template <bool EMIT>
-__device__ __forceinline__ uint32_t march_ray(const Scene& sc, float3 o, float3 d, float3 d_inv, float t_min, float t_max_ray,
-                                              const uint8_t* __restrict__ occupancy_grid, uint32_t ray_id, uint32_t out_base_idx,
-                                              float* __restrict__ t_hits_out, uint32_t* __restrict__ ray_indices_out,
-                                              float4* __restrict__ mlp_pos_vec) {
-    const float3 aabb_min = sc.aabb_min, aabb_max = sc.aabb_max;
-    const uint3 grid_resolution = sc.res;
-    const int levelsMipmap = sc.levels;
-    float3 aabb_extent = make_float3(aabb_max.x - aabb_min.x, aabb_max.y - aabb_min.y, aabb_max.z - aabb_min.z);
-    int3 step = make_int3((d.x >= 0.0f) ? 1 : -1, (d.y >= 0.0f) ? 1 : -1, (d.z >= 0.0f) ? 1 : -1);
-    const uint32_t total_mipmap_cells = get_mipmap_offset(grid_resolution, levelsMipmap);
-
-    uint32_t hit_count = 0;
-    float current_t = t_min;
-    int current_level = levelsMipmap - 1;
-
-    while (current_t < t_max_ray && hit_count < MAX_HITS) {
-        float3 current_pos = make_float3(o.x + current_t * d.x, o.y + current_t * d.y, o.z + current_t * d.z);
-        int cascade = get_cascade(current_pos, aabb_min, aabb_max, sc.num_cascades);
-        float cascade_scale = exp2f((float)cascade);
-        float3 c_aabb_min = make_float3(aabb_min.x * cascade_scale, aabb_min.y * cascade_scale, aabb_min.z * cascade_scale);
-        float3 c_aabb_extent = make_float3(aabb_extent.x * cascade_scale, aabb_extent.y * cascade_scale, aabb_extent.z * cascade_scale);
-        uint3 res_l = make_uint3(grid_resolution.x >> current_level, grid_resolution.y >> current_level, grid_resolution.z >> current_level);
-        float3 voxel_size_l = make_float3(c_aabb_extent.x / res_l.x, c_aabb_extent.y / res_l.y, c_aabb_extent.z / res_l.z);
-        float3 rel_pos = make_float3((current_pos.x - c_aabb_min.x) / c_aabb_extent.x, (current_pos.y - c_aabb_min.y) / c_aabb_extent.y,
-                                     (current_pos.z - c_aabb_min.z) / c_aabb_extent.z);
-        int3 voxel_index = make_int3(max(0, min((int)floorf(rel_pos.x * res_l.x), (int)res_l.x - 1)),
-                                     max(0, min((int)floorf(rel_pos.y * res_l.y), (int)res_l.y - 1)),
-                                     max(0, min((int)floorf(rel_pos.z * res_l.z), (int)res_l.z - 1)));
-        uint32_t level_offset = get_mipmap_offset(grid_resolution, current_level);
-        uint32_t cascade_offset = cascade * total_mipmap_cells;
-        uint32_t flat_idx = cascade_offset + level_offset + voxel_index.z * (res_l.x * res_l.y) + voxel_index.y * res_l.x + voxel_index.x;
-        uint32_t byte_idx = flat_idx >> 3;
-        uint32_t bit_idx = flat_idx & 7;
-        bool is_occupied = (occupancy_grid[byte_idx] >> bit_idx) & 1;
-
-        float3 next_boundary = make_float3(c_aabb_min.x + (voxel_index.x + (step.x > 0 ? 1.0f : 0.0f)) * voxel_size_l.x,
-                                           c_aabb_min.y + (voxel_index.y + (step.y > 0 ? 1.0f : 0.0f)) * voxel_size_l.y,
-                                           c_aabb_min.z + (voxel_index.z + (step.z > 0 ? 1.0f : 0.0f)) * voxel_size_l.z);
-        float3 t_max_axis = make_float3((next_boundary.x - o.x) * d_inv.x, (next_boundary.y - o.y) * d_inv.y, (next_boundary.z - o.z) * d_inv.z);
-        float next_t = fminf(fminf(t_max_axis.x, t_max_axis.y), t_max_axis.z);
-
-        if (is_occupied) {
-            if (current_level > 0) {
-                current_level--;
-                continue;
-            }
-            if (!EMIT) {
-                int n = sc.spv;
-                int remaining = (int)MAX_HITS - (int)hit_count;
-                if (n > remaining) n = remaining;
-                hit_count += n;
-            } else {
-                const int K = sc.spv;
-                float span = next_t - current_t;
-                for (int k = 0; k < K; ++k) {
-                    if (hit_count >= MAX_HITS) break;
-                    float t_k = current_t + (k + 0.5f) / (float)K * span;
-                    uint32_t write_idx = out_base_idx + hit_count;
-                    t_hits_out[write_idx] = t_k;
-                    ray_indices_out[write_idx] = ray_id;
-                    float3 pos = make_float3(o.x + t_k * d.x, o.y + t_k * d.y, o.z + t_k * d.z);
-                    pos = contract_pos(pos, aabb_min, aabb_max);
-                    st_cs_v4(&mlp_pos_vec[write_idx], make_uint4(__float_as_uint(pos.x), __float_as_uint(pos.y), __float_as_uint(pos.z), 0u));
-                    hit_count++;
+// One ray through the occupancy pyramid.  sink(k, t) receives sample k at ray distance t; returns the sample count.
+//
+// The reference (march_rays_dda_calc_hits / _offset) restarts every advance at the coarsest level and descends while
+// the voxel is occupied; it then either samples the occupied finest voxel or jumps to the exit of the first empty
+// voxel it met.  Because a parent bit is the OR of its children, "first empty level from the top" is the same level
+// whichever order the levels are looked at, so inside solid regions - where the last advance ended in an occupied
+// finest voxel and the next one most likely does too - the finest level is probed first and the descent is skipped.
+// That needs parent and child voxels to nest exactly (sc.nested); otherwise the reference's order is kept.
+template <class Sink>
+__device__ __forceinline__ uint32_t walk_ray(const Scene& sc, float3 o, float3 d, float3 d_inv, float t_begin, float t_end,
+                                             const uint8_t* __restrict__ bits, Sink&& sink) {
+    const float3 extent = make_float3(sc.aabb_max.x - sc.aabb_min.x, sc.aabb_max.y - sc.aabb_min.y, sc.aabb_max.z - sc.aabb_min.z);
+    RayConst rc;
+    rc.o = o; rc.d_inv = d_inv;
+    rc.ahead = make_float3(d.x >= 0.0f ? 1.0f : 0.0f, d.y >= 0.0f ? 1.0f : 0.0f, d.z >= 0.0f ? 1.0f : 0.0f);
+    const int top = sc.levels - 1;
+    uint32_t count = 0;
+    float t = t_begin;
+    bool in_solid = false;
+    while (t < t_end && count < MAX_HITS) {
+        const float3 pos = make_float3(o.x + t * d.x, o.y + t * d.y, o.z + t * d.z);
+        const int cascade = get_cascade(pos, sc.aabb_min, sc.aabb_max, sc.num_cascades);
+        const float cs = exp2f((float)cascade);
+        const float3 box_min = make_float3(sc.aabb_min.x * cs, sc.aabb_min.y * cs, sc.aabb_min.z * cs);
+        const float3 box_extent = make_float3(extent.x * cs, extent.y * cs, extent.z * cs);
+        const float3 rel = make_float3((pos.x - box_min.x) / box_extent.x, (pos.y - box_min.y) / box_extent.y, (pos.z - box_min.z) / box_extent.z);
+        const uint32_t cascade_base = cascade * sc.pyramid_cells;
+        Probe p;
+        if (in_solid && sc.nested) {
+            p = probe_level(sc, rc, bits, 0, cascade_base, box_min, box_extent, rel);
+            if (!p.occupied) {
+                for (int l = top; l > 0; l--) {
+                    const Probe q = probe_level(sc, rc, bits, l, cascade_base, box_min, box_extent, rel);
+                    if (!q.occupied) { p = q; break; }
                 }
             }
+        } else {
+            for (int l = top;; l--) {
+                p = probe_level(sc, rc, bits, l, cascade_base, box_min, box_extent, rel);
+                if (!p.occupied || l == 0) break;
+            }
         }
-        current_t = fmaxf(current_t + 1e-5f, next_t + 1e-6f);
-        current_level = levelsMipmap - 1;
+        in_solid = p.occupied;
+        if (p.occupied) {
+            // samples_per_voxel points at the centres of equal sub-spans of [t, exit)
+            const int K = sc.spv;
+            const float span = p.exit_t - t;
+            for (int k = 0; k < K && count < MAX_HITS; ++k) {
+                sink(count, t + (k + 0.5f) / (float)K * span);
+                count++;
+            }
+        }
+        t = fmaxf(t + 1e-5f, p.exit_t + 1e-6f);
     }
-    return hit_count;
+    return count;
 }
 
-__global__ void __launch_bounds__(256) march_count_kernel(const __grid_constant__ Scene sc, const uint32_t num_rays,
-                                                          const float3* __restrict__ rays_o, const float3* __restrict__ rays_d,
-                                                          const float3* __restrict__ rays_d_inv, const float* __restrict__ nears,
-                                                          const float* __restrict__ fars, const uint8_t* __restrict__ grid,
-                                                          uint32_t* __restrict__ num_steps) {
+struct CountOnly {
+    __device__ __forceinline__ void operator()(uint32_t, float) const {}
+};
+struct RowSink {
+    float* row;
+    __device__ __forceinline__ void operator()(uint32_t k, float t) const { row[k] = t; }
+};
+// Writes a sample straight into the compacted arrays (the two-pass entry point).
+struct CompactSink {
+    const Scene* sc;
+    float3 o, d;
+    uint32_t ray_id, base;
+    float* t_out;
+    uint32_t* ray_out;
+    float4* pos_out;
+    __device__ __forceinline__ void operator()(uint32_t k, float t) const {
+        const uint32_t w = base + k;
+        t_out[w] = t;
+        ray_out[w] = ray_id;
+        const float3 p = contract_pos(make_float3(o.x + t * d.x, o.y + t * d.y, o.z + t * d.z), sc->aabb_min, sc->aabb_max);
+        st_cs_v4(&pos_out[w], make_uint4(__float_as_uint(p.x), __float_as_uint(p.y), __float_as_uint(p.z), 0u));
+    }
+};
+
+struct RayArrays {
+    const float3* o;
+    const float3* d;
+    const float3* d_inv;
+    const float* nears;
+    const float* fars;
+};
+
+__global__ void __launch_bounds__(256) march_count_kernel(const __grid_constant__ Scene sc, const uint32_t num_rays, RayArrays r,
+                                                          const uint8_t* __restrict__ bits, uint32_t* __restrict__ num_steps) {
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= num_rays) return;
-    num_steps[i] = march_ray<false>(sc, rays_o[i], rays_d[i], rays_d_inv[i], nears[i], fars[i], grid, i, 0u, nullptr, nullptr, nullptr);
+    num_steps[i] = walk_ray(sc, r.o[i], r.d[i], r.d_inv[i], r.nears[i], r.fars[i], bits, CountOnly{});
+}
+
+// The single walk: sample distances of ray i into rows[i * row_stride ...], count into num_steps[i].
+__global__ void __launch_bounds__(256) march_fill_kernel(const __grid_constant__ Scene sc, const uint32_t num_rays, RayArrays r,
+                                                         const uint8_t* __restrict__ bits, uint32_t* __restrict__ num_steps,
+                                                         float* __restrict__ rows, uint32_t row_stride) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_rays) return;
+    num_steps[i] = walk_ray(sc, r.o[i], r.d[i], r.d_inv[i], r.nears[i], r.fars[i], bits, RowSink{rows + (size_t)i * row_stride});
 }
 
 // plan[0] = one past the last ray of the batch (absolute index), plan[2] = first sample of the batch.
-// Rays [rays_done, plan[0]) are marched; ray ids are written relative to rays_done.
+// Rays [rays_done, plan[0]) are walked; ray ids are written relative to rays_done.
 __global__ void __launch_bounds__(256) march_emit_kernel(const __grid_constant__ Scene sc, const uint32_t num_rays, const uint32_t rays_done,
-                                                         const float3* __restrict__ rays_o, const float3* __restrict__ rays_d,
-                                                         const float3* __restrict__ rays_d_inv, const float* __restrict__ nears,
-                                                         const float* __restrict__ fars, const uint8_t* __restrict__ grid,
-                                                         const uint32_t* __restrict__ ray_offsets, const uint32_t* __restrict__ plan,
-                                                         float* __restrict__ t_out, uint32_t* __restrict__ ray_idx_out,
-                                                         float4* __restrict__ pos_out) {
+                                                         RayArrays r, const uint8_t* __restrict__ bits, const uint32_t* __restrict__ ray_offsets,
+                                                         const uint32_t* __restrict__ plan, float* __restrict__ t_out,
+                                                         uint32_t* __restrict__ ray_idx_out, float4* __restrict__ pos_out) {
     uint32_t local = blockIdx.x * blockDim.x + threadIdx.x;
     uint32_t i = local + rays_done;
     uint32_t end = min(plan[0], num_rays);
     if (i >= end) return;
-    uint32_t base = plan[2];
-    march_ray<true>(sc, rays_o[i], rays_d[i], rays_d_inv[i], nears[i], fars[i], grid, local, ray_offsets[i] - base, t_out, ray_idx_out, pos_out);
+    CompactSink s{&sc, r.o[i], r.d[i], local, ray_offsets[i] - plan[2], t_out, ray_idx_out, pos_out};
+    walk_ray(sc, s.o, s.d, r.d_inv[i], r.nears[i], r.fars[i], bits, s);
+}
+
+// Cuts rays [ray_begin, ray_begin + ray_count) out of the scratch rows: one warp per ray, lane k copies sample k and
+// evaluates its contracted position; ray ids are relative to ray_begin, samples land at offsets[ray] - sample_base.
+__global__ void __launch_bounds__(256) march_compact_kernel(const float3 aabb_min, const float3 aabb_max, const float3* __restrict__ rays_o,
+                                                            const float3* __restrict__ rays_d, uint32_t ray_begin, uint32_t ray_count,
+                                                            const uint32_t* __restrict__ num_steps, const uint32_t* __restrict__ offsets,
+                                                            uint32_t sample_base, const float* __restrict__ rows, uint32_t row_stride,
+                                                            float* __restrict__ t_out, uint32_t* __restrict__ ray_idx_out,
+                                                            float4* __restrict__ pos_out) {
+    const uint32_t local = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    if (local >= ray_count) return;
+    const uint32_t i = ray_begin + local;
+    const uint32_t count = num_steps[i];
+    if (count == 0) return;
+    const uint32_t dst = offsets[i] - sample_base;
+    const float3 o = rays_o[i], d = rays_d[i];
+    const float* row = rows + (size_t)i * row_stride;
+    for (uint32_t k = lane; k < count; k += 32) {
+        const float t = row[k];
+        t_out[dst + k] = t;
+        ray_idx_out[dst + k] = local;
+        const float3 p = contract_pos(make_float3(o.x + t * d.x, o.y + t * d.y, o.z + t * d.z), aabb_min, aabb_max);
+        st_cs_v4(&pos_out[dst + k], make_uint4(__float_as_uint(p.x), __float_as_uint(p.y), __float_as_uint(p.z), 0u));
+    }
 }
 
 // ---- exclusive scan + cutoff --------------------------------------------------------------------------
@@ -268,12 +335,13 @@ __global__ void __launch_bounds__(SCAN_BLOCK) scan_block_sums_kernel(uint32_t* _
 // first ray) still fits the budget.  Inclusive counts never decrease, so exactly one ray is that boundary.
 __global__ void __launch_bounds__(SCAN_BLOCK) scan_finish_kernel(uint32_t* __restrict__ offsets, const uint32_t* __restrict__ num_steps,
                                                                  const uint32_t* __restrict__ block_sums, uint32_t n,
-                                                                 uint32_t batch_size, uint32_t* __restrict__ plan) {
+                                                                 uint32_t batch_size, uint32_t* __restrict__ plan, int write_total) {
     uint32_t gid = blockIdx.x * SCAN_BLOCK + threadIdx.x;
     if (gid >= n) return;
     uint32_t off = offsets[gid] + block_sums[blockIdx.x];
     offsets[gid] = off;
     uint32_t steps = num_steps[gid];
+    if (write_total && gid == n - 1) offsets[n] = off + steps;  // offsets has n + 1 entries: the last one is the sample total
     uint32_t incl = off + steps;  // base is 0: the scan starts at ray 0
     if (incl <= batch_size) {
         bool boundary = true;
@@ -312,7 +380,7 @@ using namespace nb;
 
 static int check_scene(const nb_scene_desc* s, const char* who) {
     if (!s) return nb_set_error(NB_ERR_INVALID, who);
-    if (s->num_cascades < 1 || s->mip_levels < 1 || s->mip_levels > 8 || s->samples_per_voxel < 1)
+    if (s->num_cascades < 1 || s->mip_levels < 1 || s->mip_levels > MAX_MIP_LEVELS || s->samples_per_voxel < 1)
         return nb_set_error(NB_ERR_INVALID, "scene: cascades >= 1, 1 <= mip levels <= 8, samples per voxel >= 1 required");
     for (int a = 0; a < 3; a++)
         if (s->grid_res[a] == 0 || (s->grid_res[a] >> (s->mip_levels - 1)) == 0)
@@ -345,9 +413,8 @@ extern "C" int nb_march_count(const nb_scene_desc* scene, const float* d_rays_o,
         return nb_set_error(NB_ERR_INVALID, "nb_march_count: null pointer or bad ray count");
     if (num_rays == 0) return NB_OK;
     Scene sc = make_scene(scene);
-    march_count_kernel<<<(unsigned)((num_rays + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        sc, (uint32_t)num_rays, (const float3*)d_rays_o, (const float3*)d_rays_d, (const float3*)d_rays_d_inv, d_nears, d_fars, d_bitfield,
-        d_num_steps);
+    RayArrays r{(const float3*)d_rays_o, (const float3*)d_rays_d, (const float3*)d_rays_d_inv, d_nears, d_fars};
+    march_count_kernel<<<(unsigned)((num_rays + 255) / 256), 256, 0, (cudaStream_t)stream>>>(sc, (uint32_t)num_rays, r, d_bitfield, d_num_steps);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;
@@ -364,7 +431,7 @@ extern "C" int nb_march_scan(const uint32_t* d_num_steps, uint32_t* d_ray_offset
     uint32_t blocks = (n + SCAN_BLOCK - 1) / SCAN_BLOCK;
     if (n > 0) scan_blocks_kernel<<<blocks, SCAN_BLOCK, 0, st>>>(d_num_steps, d_ray_offsets, d_block_sums, n);
     scan_block_sums_kernel<<<1, SCAN_BLOCK, 0, st>>>(d_block_sums, blocks, d_plan, 0u);
-    if (n > 0) scan_finish_kernel<<<blocks, SCAN_BLOCK, 0, st>>>(d_ray_offsets, d_num_steps, d_block_sums, n, batch_size, d_plan);
+    if (n > 0) scan_finish_kernel<<<blocks, SCAN_BLOCK, 0, st>>>(d_ray_offsets, d_num_steps, d_block_sums, n, batch_size, d_plan, 0);
     NB_CHECK_LAUNCH();
     g_launch_count += (n > 0 ? 3 : 1);
     return NB_OK;
@@ -398,9 +465,55 @@ extern "C" int nb_march_emit(const nb_scene_desc* scene, const float* d_rays_o, 
     if (max_rays_in_batch < span) span = max_rays_in_batch;
     if (span == 0) return NB_OK;
     Scene sc = make_scene(scene);
-    march_emit_kernel<<<(unsigned)((span + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        sc, (uint32_t)num_rays, rays_done, (const float3*)d_rays_o, (const float3*)d_rays_d, (const float3*)d_rays_d_inv, d_nears, d_fars,
-        d_bitfield, d_ray_offsets, d_plan, d_t_out, d_ray_idx_out, (float4*)d_pos4_out);
+    RayArrays r{(const float3*)d_rays_o, (const float3*)d_rays_d, (const float3*)d_rays_d_inv, d_nears, d_fars};
+    march_emit_kernel<<<(unsigned)((span + 255) / 256), 256, 0, (cudaStream_t)stream>>>(sc, (uint32_t)num_rays, rays_done, r, d_bitfield, d_ray_offsets,
+                                                                                         d_plan, d_t_out, d_ray_idx_out, (float4*)d_pos4_out);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_march_row_stride(void) { return (int)MAX_HITS; }
+
+extern "C" int nb_march_fill(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, const float* d_rays_d_inv,
+                             const float* d_nears, const float* d_fars, const uint8_t* d_bitfield, int64_t num_rays, uint32_t* d_num_steps,
+                             float* d_t_rows, uint32_t* d_ray_offsets, uint32_t* d_block_sums, void* stream) {
+    int rc = check_scene(scene, "nb_march_fill: null scene");
+    if (rc) return rc;
+    if (!d_rays_o || !d_rays_d || !d_rays_d_inv || !d_nears || !d_fars || !d_bitfield || !d_num_steps || !d_t_rows || !d_ray_offsets ||
+        !d_block_sums || num_rays < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_march_fill: null pointer or negative ray count");
+    if (num_rays > (int64_t)SCAN_BLOCK * SCAN_BLOCK) return nb_set_error(NB_ERR_LIMIT, "nb_march_fill: at most 1048576 rays per call");
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t n = (uint32_t)num_rays;
+    if (n == 0) return nb_zero_async(d_ray_offsets, sizeof(uint32_t), stream);
+    Scene sc = make_scene(scene);
+    RayArrays r{(const float3*)d_rays_o, (const float3*)d_rays_d, (const float3*)d_rays_d_inv, d_nears, d_fars};
+    march_fill_kernel<<<(n + 255) / 256, 256, 0, st>>>(sc, n, r, d_bitfield, d_num_steps, d_t_rows, MAX_HITS);
+    const uint32_t blocks = (n + SCAN_BLOCK - 1) / SCAN_BLOCK;
+    scan_blocks_kernel<<<blocks, SCAN_BLOCK, 0, st>>>(d_num_steps, d_ray_offsets, d_block_sums, n);
+    // the plan words these kernels maintain live behind the block sums (the scratch holds 1024 + 4 words)
+    scan_block_sums_kernel<<<1, SCAN_BLOCK, 0, st>>>(d_block_sums, blocks, d_block_sums + SCAN_BLOCK, 0u);
+    scan_finish_kernel<<<blocks, SCAN_BLOCK, 0, st>>>(d_ray_offsets, d_num_steps, d_block_sums, n, 0xffffffffu, d_block_sums + SCAN_BLOCK, 1);
+    NB_CHECK_LAUNCH();
+    g_launch_count += 4;
+    return NB_OK;
+}
+
+extern "C" int nb_march_compact(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, uint32_t ray_begin,
+                                uint32_t ray_count, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, uint32_t sample_base,
+                                const float* d_t_rows, float* d_t_out, uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream) {
+    int rc = check_scene(scene, "nb_march_compact: null scene");
+    if (rc) return rc;
+    if (!d_rays_o || !d_rays_d || !d_num_steps || !d_ray_offsets || !d_t_rows || !d_t_out || !d_ray_idx_out || !d_pos4_out)
+        return nb_set_error(NB_ERR_INVALID, "nb_march_compact: null pointer");
+    if (reinterpret_cast<uintptr_t>(d_pos4_out) & 15u) return nb_set_error(NB_ERR_INVALID, "nb_march_compact: positions must be 16-byte aligned");
+    if (ray_count == 0) return NB_OK;
+    Scene sc = make_scene(scene);
+    const uint64_t threads = (uint64_t)ray_count * 32;
+    march_compact_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        sc.aabb_min, sc.aabb_max, (const float3*)d_rays_o, (const float3*)d_rays_d, ray_begin, ray_count, d_num_steps, d_ray_offsets, sample_base,
+        d_t_rows, MAX_HITS, d_t_out, d_ray_idx_out, (float4*)d_pos4_out);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

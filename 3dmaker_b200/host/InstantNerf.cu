@@ -30,6 +30,7 @@ InstantNerf::~InstantNerf() {
     delete m_colorMLP;
     delete m_densityMLP;
     if (h_plan) cudaFreeHost(h_plan);
+    if (h_offsets) cudaFreeHost(h_offsets);
 }
 
 nb_scene_desc InstantNerf::scene() const {
@@ -130,8 +131,16 @@ void InstantNerf::initRenderBuffers() {
     const nb_mlp_desc& cd = m_colorMLP->desc();
 
     d_rays_d_inv.allocate(R * 3 * sizeof(float)); d_nears.allocate(R * sizeof(float)); d_fars.allocate(R * sizeof(float));
-    d_num_steps.allocate(R * sizeof(uint32_t)); d_ray_offsets.allocate(R * sizeof(uint32_t));
-    d_block_sums.allocate(((R + 1023) / 1024 + 1) * sizeof(uint32_t)); d_plan.allocate(4 * sizeof(uint32_t), true);
+    if (R > (size_t)1 << 20) throw std::runtime_error("rayChunkSize above 1048576 is not supported");
+    d_num_steps.allocate(R * sizeof(uint32_t)); d_ray_offsets.allocate((R + 1) * sizeof(uint32_t));
+    d_block_sums.allocate((1024 + 4) * sizeof(uint32_t)); d_plan.allocate(4 * sizeof(uint32_t), true);
+    // sample distances of every ray of a chunk, one row per ray (see nb_march_fill)
+    d_t_rows.allocate(R * (size_t)nb_march_row_stride() * sizeof(float));
+    if (h_offsets_capacity < R + 1) {
+        if (h_offsets) cudaFreeHost(h_offsets);
+        throw_on_cuda(cudaMallocHost(&h_offsets, (R + 1) * sizeof(uint32_t)), "pinned offsets");
+        h_offsets_capacity = R + 1;
+    }
     d_render_rgb.allocate(R * 3 * sizeof(float)); d_render_depth.allocate(R * sizeof(float)); d_phi.allocate(R * 3 * sizeof(float));
     d_weight_sum.allocate(R * sizeof(float));
 
@@ -226,7 +235,8 @@ void InstantNerf::lateOccupancyGridUpdate(cudaStream_t stream) {
 
 InstantNerf::StepView InstantNerf::stepView() const {
     StepView v;
-    v.num_steps = d_num_steps.as<uint32_t>(); v.ray_offsets = d_ray_offsets.as<uint32_t>(); v.ray_indices = d_ray_indices.as<uint32_t>();
+    v.num_steps = d_num_steps.as<uint32_t>() + m_lastStepFirstRay; v.ray_offsets = d_ray_offsets.as<uint32_t>() + m_lastStepFirstRay;
+    v.ray_indices = d_ray_indices.as<uint32_t>(); v.sample_base = m_lastSampleBase;
     v.t_sorted = d_t_sorted.as<float>(); v.positions = d_positions.as<float>(); v.density_out = d_density_out.as<float>();
     v.sigma = d_sigma.as<float>(); v.color_out = d_color_out.as<float>(); v.render_rgb = d_render_rgb.as<float>(); v.phi = d_phi.as<float>();
     v.dw = d_dw.as<float>(); v.weight_sum = d_weight_sum.as<float>(); v.tmp_dsigma = d_tmpsigma.as<float>();
@@ -241,6 +251,28 @@ bool InstantNerf::setFusedField(bool on) {
     return m_fused;
 }
 
+// Walks rays [first, first + count) once (slab test, occupancy walk into the scratch rows, scan) and brings the
+// scanned offsets to the host: h_offsets[i] = first sample of ray first + i, h_offsets[count] = sample total.
+void InstantNerf::walkRays(const float3* d_rays_o, const float3* d_rays_d, uint32_t first, uint32_t count, cudaStream_t stream) {
+    nb_scene_desc sc = scene();
+    const float* o = reinterpret_cast<const float*>(d_rays_o + first);
+    const float* d = reinterpret_cast<const float*>(d_rays_d + first);
+    throw_on_error(nb_ray_aabb(&sc, o, d, count, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(), stream), "ray/box");
+    throw_on_error(nb_march_fill(&sc, o, d, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(), d_occupancyGrid.as<uint8_t>(), count,
+                                 d_num_steps.as<uint32_t>(), d_t_rows.as<float>(), d_ray_offsets.as<uint32_t>(), d_block_sums.as<uint32_t>(), stream),
+                   "march: walk");
+    throw_on_cuda(cudaMemcpyAsync(h_offsets, d_ray_offsets.as<uint32_t>(), ((size_t)count + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream),
+                  "march: offsets");
+    throw_on_cuda(cudaStreamSynchronize(stream), "march: offsets");
+}
+
+// Last ray e >= begin of a walked window of `count` rays such that the samples of rays [begin, e) fit `budget`.
+static uint32_t cutRays(const uint32_t* offsets, uint32_t begin, uint32_t count, uint32_t budget) {
+    const uint64_t limit = (uint64_t)offsets[begin] + budget;
+    const uint32_t* e = std::upper_bound(offsets + begin + 1, offsets + count + 1, limit, [](uint64_t v, uint32_t x) { return v < x; });
+    return (uint32_t)(e - offsets) - 1;
+}
+
 void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_d, const float* d_rays_depth, const float* d_rays_sigma,
                                    const float* d_rgb_true, uint32_t numRays, int& trainStepCount, uint32_t* hitCounts, float* d_rgb_out,
                                    cudaStream_t stream) {
@@ -250,47 +282,68 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
     TinyMLPHashGrid* dn = m_densityMLP;
     TinyMLP* cn = m_colorMLP;
     const float bg[3] = {m_opts.bgColor.x, m_opts.bgColor.y, m_opts.bgColor.z};
+    const uint32_t budget = (uint32_t)m_opts.batchSize;
     uint32_t raysDone = 0;
     int i = 0;
+    // The reference walks the rays left in the chunk again for every optimizer step (InstantNerf.cu:386-407).  The
+    // walk only depends on the rays and the occupancy bits, so one walk serves every step until the bits change
+    // (every 16th step) or the walked window runs out while rays remain beyond it.
+    uint32_t winFirst = 0, winCount = 0;
+    bool walked = false;
     while (raysDone < numRays) {
-        const uint32_t upper = std::min<uint32_t>((uint32_t)m_opts.rayChunkSize, numRays - raysDone);
-        const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + raysDone);
-        const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + raysDone);
-        const float* chunk_depth = d_rays_depth ? d_rays_depth + raysDone : nullptr;
-        const float* chunk_sigma = d_rays_sigma ? d_rays_sigma + raysDone : nullptr;
-        uint32_t currentChunkRays = 0, totalHits = 0;
-
+        uint32_t begin = 0, end = 0;
         timed(stream, m_times.march, [&]() {
-            throw_on_error(nb_ray_aabb(&sc, chunk_o, chunk_d, upper, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(), stream), "ray/box");
-            throw_on_error(nb_march_count(&sc, chunk_o, chunk_d, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(),
-                                          d_occupancyGrid.as<uint8_t>(), upper, d_num_steps.as<uint32_t>(), stream), "march: count");
-            throw_on_error(nb_march_scan(d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), d_block_sums.as<uint32_t>(), upper,
-                                         (uint32_t)m_opts.batchSize, d_plan.as<uint32_t>(), stream), "march: scan");
-            throw_on_cuda(cudaMemcpyAsync(h_plan, d_plan.as<uint32_t>(), 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream), "march: plan");
-            throw_on_cuda(cudaStreamSynchronize(stream), "march: plan");
-            currentChunkRays = h_plan[0];
-            totalHits = h_plan[1];
-            if (currentChunkRays > 0 && totalHits > 0)
-                throw_on_error(nb_march_emit(&sc, chunk_o, chunk_d, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(),
-                                             d_occupancyGrid.as<uint8_t>(), upper, 0, currentChunkRays, d_ray_offsets.as<uint32_t>(),
-                                             d_plan.as<uint32_t>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
-                               "march: emit");
+            for (;;) {
+                if (!walked) {
+                    winFirst = raysDone;
+                    winCount = std::min<uint32_t>((uint32_t)m_opts.rayChunkSize, numRays - raysDone);
+                    walkRays(d_rays_o, d_rays_d, winFirst, winCount, stream);
+                    walked = true;
+                }
+                begin = raysDone - winFirst;
+                end = cutRays(h_offsets, begin, winCount, budget);
+                // budget not exhausted by what is left of the window, but the window does not reach the last ray:
+                // the reference's chunk would start at raysDone and reach further, so walk again from here
+                if (end == winCount && begin > 0 && winFirst + winCount < numRays) { walked = false; continue; }
+                break;
+            }
         });
+        const uint32_t currentChunkRays = end - begin;
+        const uint32_t totalHits = h_offsets[end] - h_offsets[begin];
+        const uint32_t sampleBase = h_offsets[begin];
         if (currentChunkRays == 0) {
             std::fprintf(stderr, "Error: Batch size is too small to fit even a single ray! Increase batchSize.\n");
             return;
         }
+        const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + raysDone);
+        const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + raysDone);
+        const float* chunk_depth = d_rays_depth ? d_rays_depth + raysDone : nullptr;
+        const float* chunk_sigma = d_rays_sigma ? d_rays_sigma + raysDone : nullptr;
+        const uint32_t* steps_b = d_num_steps.as<uint32_t>() + begin;
+        const uint32_t* offs_b = d_ray_offsets.as<uint32_t>() + begin;
+        if (totalHits > 0) {
+            timed(stream, m_times.march, [&]() {
+                throw_on_error(nb_march_compact(&sc, reinterpret_cast<const float*>(d_rays_o + winFirst), reinterpret_cast<const float*>(d_rays_d + winFirst),
+                                                begin, currentChunkRays, d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), sampleBase,
+                                                d_t_rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(),
+                                                stream), "march: compact");
+            });
+        }
         if (hitCounts != nullptr) hitCounts[i] = totalHits;
         m_lastTotalHits = totalHits;
+        m_lastStepFirstRay = begin;
+        m_lastSampleBase = sampleBase;
         const int64_t n = totalHits;
 
         // occupancy schedule of the reference: every 16 steps, all cells for the first 256 steps (InstantNerf.cu:488-494).
-        // It only reads the parameters, which do not change before the optimizer below.
+        // It only reads the parameters, which do not change before the optimizer below; the walk above used the old bits,
+        // as the reference's march of this step does, and the next step walks again.
         if (m_trainSteps % 16 == 0) {
             timed(stream, m_times.occupancy, [&]() {
                 if (m_trainSteps < 256) earlyOccupancyGridUpdate(stream);
                 else lateOccupancyGridUpdate(stream);
             });
+            walked = false;
         }
 
         const int logitStride = m_fused ? 1 : 16, colorStride = m_fused ? 4 : 8;
@@ -318,8 +371,8 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
             });
         }
         timed(stream, m_times.compositing, [&]() {
-            throw_on_error(nb_composite_train(currentChunkRays, d_ray_offsets.as<uint32_t>(), d_num_steps.as<uint32_t>(), d_t_sorted.as<float>(),
-                                              d_sigma.as<float>(), chunk_depth, chunk_sigma, d_color_out.as<float>(), colorStride,
+            throw_on_error(nb_composite_train(currentChunkRays, sampleBase, offs_b, steps_b, d_t_sorted.as<float>(), d_sigma.as<float>(), chunk_depth,
+                                              chunk_sigma, d_color_out.as<float>(), colorStride,
                                               d_rgb_true ? d_rgb_true + (size_t)raysDone * 3 : nullptr, d_render_rgb.as<float>(),
                                               d_render_depth.as<float>(), d_phi.as<float>(), d_dw.as<float>(), d_weight_sum.as<float>(),
                                               m_opts.lambdaDist, m_opts.lambdaDepth, bg, stream), "compositing");
@@ -329,9 +382,8 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                                           cudaMemcpyDeviceToDevice, stream), "rgb out");
         if (n > 0) {
             timed(stream, m_times.lossGrad, [&]() {
-                throw_on_error(nb_color_grad(currentChunkRays, d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), d_t_sorted.as<float>(),
-                                             d_density_out.as<float>(), logitStride, d_color_out.as<float>(), colorStride, d_phi.as<float>(),
-                                             d_render_rgb.as<float>(),
+                throw_on_error(nb_color_grad(currentChunkRays, sampleBase, steps_b, offs_b, d_t_sorted.as<float>(), d_density_out.as<float>(),
+                                             logitStride, d_color_out.as<float>(), colorStride, d_phi.as<float>(), d_render_rgb.as<float>(),
                                              d_dw.as<float>(), d_weight_sum.as<float>(), d_color_grad.as<half>(), 8, d_tmpsigma.as<float>(),
                                              m_opts.lossScale, m_opts.densityBias, numRays * m_rayScale, stream), "loss gradients");
             });
@@ -358,8 +410,6 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                                                    d_density_acts.as<half>(), n, m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()),
                                                    d_denc.as<half>(), stream), "density backward");
                 });
-            }
-            if (!m_fused) {
                 timed(stream, m_times.scatter, [&]() {
                     throw_on_error(nb_hash_scatter_backward(&dn->grid(), d_positions.as<float>(), d_denc.as<half>(), n, m_arena.G(dn->hashOffset()), stream),
                                    "gradient scatter");
@@ -396,32 +446,22 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
         const uint32_t chunkRays = std::min<uint32_t>((uint32_t)m_opts.rayChunkSize, numRays - ray_offset);
         const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + ray_offset);
         const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + ray_offset);
-        throw_on_error(nb_ray_aabb(&sc, chunk_o, chunk_d, chunkRays, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(), stream), "ray/box");
-        throw_on_error(nb_march_count(&sc, chunk_o, chunk_d, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(),
-                                      d_occupancyGrid.as<uint8_t>(), chunkRays, d_num_steps.as<uint32_t>(), stream), "march: count");
-        throw_on_error(nb_march_scan(d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), d_block_sums.as<uint32_t>(), chunkRays, hitBatch,
-                                     d_plan.as<uint32_t>(), stream), "march: scan");
+        // one walk and one read-back per chunk; every sample batch below is cut out of the rows without another sync
+        walkRays(d_rays_o, d_rays_d, ray_offset, chunkRays, stream);
         uint32_t raysDone = 0;
-        bool first = true;
         while (raysDone < chunkRays) {
-            if (!first)
-                throw_on_error(nb_march_cutoff(d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), chunkRays, raysDone, hitBatch,
-                                               d_plan.as<uint32_t>(), stream), "march: cutoff");
-            first = false;
-            throw_on_cuda(cudaMemcpyAsync(h_plan, d_plan.as<uint32_t>(), 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream), "march: plan");
-            throw_on_cuda(cudaStreamSynchronize(stream), "march: plan");
-            const uint32_t next = h_plan[0], totalHits = h_plan[1], base = h_plan[2];
+            const uint32_t next = cutRays(h_offsets, raysDone, chunkRays, hitBatch);
             if (next <= raysDone) {
                 std::fprintf(stderr, "Error: Batch size is too small to fit even a single ray! Increase batchSize.\n");
                 return;
             }
             const uint32_t crrRays = next - raysDone;
-            const int64_t n = totalHits;
+            const uint32_t base = h_offsets[raysDone];
+            const int64_t n = h_offsets[next] - base;
             if (n > 0) {
-                throw_on_error(nb_march_emit(&sc, chunk_o, chunk_d, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(),
-                                             d_occupancyGrid.as<uint8_t>(), chunkRays, raysDone, crrRays, d_ray_offsets.as<uint32_t>(),
-                                             d_plan.as<uint32_t>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
-                               "march: emit");
+                throw_on_error(nb_march_compact(&sc, chunk_o, chunk_d, raysDone, crrRays, d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), base,
+                                                d_t_rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
+                               "march: compact");
                 if (m_fused) {
                     throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
                                                     chunk_d + (size_t)raysDone * 3, d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()),

@@ -134,6 +134,7 @@ public:
         const half *color_in, *color_grad, *density_grad;
         int logit_stride;  // density_out[i * logit_stride] = raw logit 0 of sample i (16: full density output rows)
         int color_stride;  // floats between colour rows
+        uint32_t sample_base;  // ray_offsets[r] - sample_base = first sample of the step's ray r in the sample arrays
     };
     StepView stepView() const;
 
@@ -143,6 +144,7 @@ private:
     void earlyOccupancyGridUpdate(cudaStream_t stream = 0);
     void lateOccupancyGridUpdate(cudaStream_t stream = 0);
     void finishOccupancyUpdate(cudaStream_t stream);
+    void walkRays(const float3* d_rays_o, const float3* d_rays_d, uint32_t first, uint32_t count, cudaStream_t stream);
     nb_scene_desc scene() const;
     template <class F> void timed(cudaStream_t stream, double& acc, F&& f);
 
@@ -166,6 +168,10 @@ private:
     // occupancy
     nb::DeviceMem d_occ_samples, d_tmp_grid, d_sum, d_occ_scratch, d_active_cells, d_num_active;
     uint32_t* h_plan = nullptr;  // pinned, 4 words
+    uint32_t* h_offsets = nullptr;  // pinned: scanned sample offsets of the walked rays (+ total)
+    size_t h_offsets_capacity = 0;
+    nb::DeviceMem d_t_rows;
+    uint32_t m_lastStepFirstRay = 0, m_lastSampleBase = 0;
 
     bool m_traininit = false;
     bool m_renderinit = false;

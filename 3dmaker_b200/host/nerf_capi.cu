@@ -153,7 +153,7 @@ extern "C" int nb_nerf_get_step_view(nb_nerf* h, nb_nerf_step_view* out) {
     out->render_rgb = v.render_rgb; out->phi = v.phi; out->dw = v.dw; out->weight_sum = v.weight_sum; out->tmp_dsigma = v.tmp_dsigma;
     out->color_in = v.color_in; out->color_grad = v.color_grad; out->density_grad = v.density_grad;
     out->last_total_hits = h->impl.lastTotalHits(); out->train_steps = h->impl.trainSteps();
-    out->logit_stride = v.logit_stride; out->color_stride = v.color_stride; out->rays_consumed = h->impl.lastRaysConsumed();
+    out->logit_stride = v.logit_stride; out->color_stride = v.color_stride; out->rays_consumed = h->impl.lastRaysConsumed(); out->sample_base = v.sample_base;
     return NB_OK;
 }
 

@@ -252,29 +252,49 @@ int nb_march_emit(const nb_scene_desc* scene, const float* d_rays_o, const float
                   int64_t max_rays_in_batch, const uint32_t* d_ray_offsets, const uint32_t* d_plan, float* d_t_out,
                   uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
 
+/* The single walk: as nb_march_count, but the sample distances of ray i are also stored in row i of d_t_rows
+ * (nb_march_row_stride() = 1024 floats per ray), and the counts are scanned into d_ray_offsets[num_rays + 1] (exclusive
+ * offsets, last entry = sample total).  d_block_sums: scratch of 1028 uint32.  At most 1048576 rays per call.  A host
+ * that reads d_ray_offsets back can cut any number of sample batches out of the rows with nb_march_compact without
+ * walking a ray again.  No counterpart in the reference, which walks every ray twice per batch. */
+int nb_march_row_stride(void);
+int nb_march_fill(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, const float* d_rays_d_inv, const float* d_nears,
+                  const float* d_fars, const uint8_t* d_bitfield, int64_t num_rays, uint32_t* d_num_steps, float* d_t_rows,
+                  uint32_t* d_ray_offsets, uint32_t* d_block_sums, void* stream);
+/* Samples of rays [ray_begin, ray_begin + ray_count) from the rows into the compact arrays the field kernels read:
+ * sample k of ray i lands at d_ray_offsets[i] - sample_base + k with its t, its ray id relative to ray_begin and its
+ * contracted float4 position - the output of march_rays_dda_offset (processRays.cu:801-929). */
+int nb_march_compact(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, uint32_t ray_begin, uint32_t ray_count,
+                     const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, uint32_t sample_base, const float* d_t_rows,
+                     float* d_t_out, uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
+
 /* ---- compositing and loss gradients ---------------------------------------------------------- */
 
+/* The three compositing entry points give every ray a warp; ray r of the call has num_steps[r] samples starting at
+ * d_ray_offsets[r] - sample_base of the sample arrays. */
+
 /* Replaces render_rays_kernel via launchVolumeRendering with d_dw_out == NULL (modules/NeRF/compositing.cu:5-78,
- * InstantNerf.h launchVolumeRendering).  d_rgb rows are rgb_stride floats apart (3 valid). */
+ * InstantNerf.h launchVolumeRendering).  Ray r reads d_ray_offsets[rays_done + r] - base and d_num_steps[r].
+ * d_rgb rows are rgb_stride floats apart (3 valid). */
 int nb_composite_infer(int64_t num_rays, uint32_t base, uint32_t rays_done, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps,
                        const float* d_t_sorted, const float* d_sigma, const float* d_rgb, int rgb_stride, const float* d_rgb_true,
                        float* d_final_rgb, float* d_final_depth, float* d_phi, const float* bg_color3, void* stream);
 
 /* Replaces render_rays_distortion_kernel via launchVolumeRendering with d_dw_out != NULL
  * (modules/NeRF/compositing.cu:84-213).  d_depth_prior / d_sigma_prior may be NULL (depth supervision off). */
-int nb_composite_train(int64_t num_rays, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps, const float* d_t_sorted,
-                       const float* d_sigma, const float* d_depth_prior, const float* d_sigma_prior, const float* d_rgb, int rgb_stride,
-                       const float* d_rgb_true, float* d_final_rgb, float* d_final_depth, float* d_phi, float* d_dw_out,
-                       float* d_weight_sum, float lambda_dist, float lambda_depth, const float* bg_color3, void* stream);
+int nb_composite_train(int64_t num_rays, uint32_t sample_base, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps,
+                       const float* d_t_sorted, const float* d_sigma, const float* d_depth_prior, const float* d_sigma_prior,
+                       const float* d_rgb, int rgb_stride, const float* d_rgb_true, float* d_final_rgb, float* d_final_depth, float* d_phi,
+                       float* d_dw_out, float* d_weight_sum, float lambda_dist, float lambda_depth, const float* bg_color3, void* stream);
 
-/* Replaces compute_color_grad (modules/NeRF/otherKernels.cu:303-409) with initialOffset 0.  d_logit0 holds the raw
- * first density output of sample i at d_logit0[i * logit_stride] (16 for a full density-output matrix, 1 for the
- * compact array of nb_field_forward); d_color_out rows are color_stride floats apart; gradient rows are grad_stride
- * (3 or 8) halves, channels 3..7 written as zero. */
-int nb_color_grad(int64_t num_rays, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, const float* d_t_sorted,
-                  const float* d_logit0, int logit_stride, const float* d_color_out, int color_stride, const float* d_phi, const float* d_final_rgb,
-                  const float* d_dw_out, const float* d_weight_sum, void* d_color_grad_h, int grad_stride, float* d_tmp_dsigma,
-                  float loss_scale, float density_bias, uint32_t total_rays_batch, void* stream);
+/* Replaces compute_color_grad (modules/NeRF/otherKernels.cu:303-409).  d_logit0 holds the raw first density output of
+ * sample i at d_logit0[i * logit_stride] (16 for a full density-output matrix, 1 for the compact array of
+ * nb_field_forward); d_color_out rows are color_stride floats apart; gradient rows are grad_stride (3 or 8) halves,
+ * channels 3..7 written as zero. */
+int nb_color_grad(int64_t num_rays, uint32_t sample_base, const uint32_t* d_num_steps, const uint32_t* d_ray_offsets,
+                  const float* d_t_sorted, const float* d_logit0, int logit_stride, const float* d_color_out, int color_stride,
+                  const float* d_phi, const float* d_final_rgb, const float* d_dw_out, const float* d_weight_sum, void* d_color_grad_h,
+                  int grad_stride, float* d_tmp_dsigma, float loss_scale, float density_bias, uint32_t total_rays_batch, void* stream);
 
 /* ---- occupancy grid ------------------------------------------------------------------------------ */
 
@@ -340,6 +360,7 @@ typedef struct nb_nerf_step_view {
     int32_t logit_stride; /* density_out[i * logit_stride] = raw logit 0 of sample i: 16 (full rows) or 1 (fused field) */
     int32_t color_stride; /* floats between rows of color_out: 8 or 4 (fused field) */
     uint32_t rays_consumed; /* rays of the last nb_nerf_train_rays call that were trained on */
+    uint32_t sample_base;   /* num_steps / ray_offsets point at the last step's first ray; ray_offsets[r] - sample_base = its first sample */
 } nb_nerf_step_view;
 
 /* NerfOptions defaults (InstantNerf.h:35-76). */

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 from helpers import ABS_RGB, REL_MLP, Uploader, dev_half_bits, half_vals, rel_err
-from test_oracle_nerf_cpu import camera_rays, sphere_bitfield
+from test_oracle_nerf_cpu import camera_rays, speckled_bitfield, sphere_bitfield
 
 pytestmark = pytest.mark.gpu
 
@@ -100,6 +100,52 @@ def test_march_count_scan_emit(cuda, nb, orc, cascades, spv, res):
     assert np.array_equal(r2, np.repeat(np.arange(nxt - active), cnt[active:nxt]))
 
 
+@pytest.mark.parametrize("cascades,spv,res,levels", [(1, 1, 128, 4), (3, 1, 128, 4), (1, 2, 64, 3)])
+def test_single_walk_and_compaction_equal_the_two_pass_march(cuda, nb, orc, cascades, spv, res, levels):
+    """nb_march_fill + nb_march_compact against nb_march_count / scan / cutoff / emit on the same rays: counts,
+    offsets, ray ids, distances and positions are the same bits, batch after batch."""
+    torch = cuda
+    up = Uploader(torch, nb)
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    R, batch = 30000, 1 << 17
+    r3 = (res, res, res)
+    sc = _scene(nb, r3, cascades, levels, spv)
+    bits = speckled_bitfield(orc, r3, levels, cascades)
+    o, d = camera_rays(R, seed=4)
+    g = _march_gpu(torch, nb, up, sc, o, d, bits, batch)
+    i32, f32 = torch.int32, torch.float32
+    steps2 = torch.zeros(R, dtype=i32, device="cuda"); offs2 = torch.zeros(R + 1, dtype=i32, device="cuda")
+    rows = torch.zeros((R, lib.nb_march_row_stride()), dtype=f32, device="cuda"); scratch = torch.zeros(1028, dtype=i32, device="cuda")
+    nb.check(lib.nb_march_fill(ctypes.byref(sc), g["d_o"], g["d_d"], P(g["d_inv"]), P(g["nears"]), P(g["fars"]), P(g["bits"]), R, P(steps2), P(rows),
+                               P(offs2), P(scratch), st), "nb_march_fill")
+    torch.cuda.synchronize()
+    cnt = g["steps"].cpu().numpy().view(np.uint32)
+    assert np.array_equal(steps2.cpu().numpy().view(np.uint32), cnt)
+    offs = offs2.cpu().numpy().view(np.uint32)
+    assert np.array_equal(offs[:R], g["offs"].cpu().numpy().view(np.uint32)) and offs[R] == cnt.sum()
+    assert cnt.sum() > 2 * batch                                                # several batches
+    done, batches = 0, 0
+    while done < R:
+        nb.check(lib.nb_march_cutoff(P(g["steps"]), P(g["offs"]), R, done, batch, P(g["plan"]), st), "nb_march_cutoff")
+        torch.cuda.synchronize()
+        plan = g["plan"].cpu().numpy().view(np.uint32)
+        # the host's cut from the offsets: the last ray whose samples still fit
+        end = int(np.searchsorted(offs[done + 1:], offs[done] + batch, side="right")) + done
+        assert end == plan[0] and offs[end] - offs[done] == plan[1] and end > done
+        total = int(plan[1])
+        a = [torch.zeros(batch, dtype=f32, device="cuda"), torch.full((batch,), -1, dtype=i32, device="cuda"), torch.zeros((batch, 4), dtype=f32, device="cuda")]
+        b = [torch.zeros(batch, dtype=f32, device="cuda"), torch.full((batch,), -1, dtype=i32, device="cuda"), torch.zeros((batch, 4), dtype=f32, device="cuda")]
+        nb.check(lib.nb_march_emit(ctypes.byref(sc), g["d_o"], g["d_d"], P(g["d_inv"]), P(g["nears"]), P(g["fars"]), P(g["bits"]), R, done, R,
+                                   P(g["offs"]), P(g["plan"]), P(a[0]), P(a[1]), P(a[2]), st), "nb_march_emit")
+        nb.check(lib.nb_march_compact(ctypes.byref(sc), g["d_o"], g["d_d"], done, end - done, P(steps2), P(offs2), int(offs[done]), P(rows),
+                                      P(b[0]), P(b[1]), P(b[2]), st), "nb_march_compact")
+        torch.cuda.synchronize()
+        for x, y in zip(a, b):
+            assert torch.equal(x[:total].view(i32), y[:total].view(i32))
+        done, batches = end, batches + 1
+    assert batches >= 3
+
+
 def test_march_edge_cases(cuda, nb, orc):
     torch = cuda
     up = Uploader(torch, nb)
@@ -119,6 +165,8 @@ def _random_ray_samples(R, seed, max_count=60):
     rng = np.random.default_rng(seed)
     counts = rng.integers(0, max_count, R).astype(np.uint32)
     counts[:3] = [0, 1, max_count]
+    if R > 100:
+        counts[3:8] = [31, 32, 33, 300, 1024]          # around the 32-sample window of the warp-per-ray kernels, and the cap
     n = int(counts.sum())
     off = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.uint32)
     t = np.concatenate([np.sort(rng.uniform(0.5, 3.0, c)) for c in counts]).astype(np.float32)
@@ -144,7 +192,7 @@ def test_compositing_and_color_grad(cuda, nb, orc, R):
     rgb = torch.zeros((R, 3), dtype=f32, device="cuda"); depth = torch.zeros(R, dtype=f32, device="cuda"); phi = torch.zeros((R, 3), dtype=f32, device="cuda")
     dw = torch.zeros(n, dtype=f32, device="cuda"); wsum = torch.zeros(R, dtype=f32, device="cuda")
     d_off, d_cnt, d_t, d_sig, d_col, d_tgt = up.f(off.view(np.int32)), up.f(counts.view(np.int32)), up.f(t), up.f(sigma), up.f(col), up.f(target)
-    nb.check(lib.nb_composite_train(R, d_off, d_cnt, d_t, d_sig, None, None, d_col, 8, d_tgt, P(rgb), P(depth), P(phi), P(dw), P(wsum), lam, 0.0,
+    nb.check(lib.nb_composite_train(R, 0, d_off, d_cnt, d_t, d_sig, None, None, d_col, 8, d_tgt, P(rgb), P(depth), P(phi), P(dw), P(wsum), lam, 0.0,
                                     bg, st), "nb_composite_train")
     torch.cuda.synchronize()
     r_rgb, r_depth, r_phi, r_dw, r_wsum = orc.render_rays_distortion(R, off, counts, t, sigma, col[:, :3].copy(), target, lam, 0.0, bg_np)
@@ -159,7 +207,7 @@ def test_compositing_and_color_grad(cuda, nb, orc, R):
     assert np.max(np.abs(rgb2.cpu().numpy() - i_rgb)) <= ABS_RGB
     # loss gradients from the GPU's own forward results
     grad = torch.full((n, 8), 9.0, dtype=torch.float16, device="cuda"); dsig = torch.zeros(n, dtype=f32, device="cuda")
-    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, up.f(dens), 16, d_col, 8, P(phi), P(rgb), P(dw), P(wsum), P(grad), 8, P(dsig), scale, bias, R,
+    nb.check(lib.nb_color_grad(R, 0, d_cnt, d_off, d_t, up.f(dens), 16, d_col, 8, P(phi), P(rgb), P(dw), P(wsum), P(grad), 8, P(dsig), scale, bias, R,
                                st), "nb_color_grad")
     torch.cuda.synchronize()
     g_ref, ds_ref = orc.color_grad(R, counts, off, t, dens, col, phi.cpu().numpy(), rgb.cpu().numpy(), dw.cpu().numpy(), wsum.cpu().numpy(),
@@ -167,6 +215,26 @@ def test_compositing_and_color_grad(cuda, nb, orc, R):
     got = half_vals(dev_half_bits(grad))
     assert np.all(got[:, 3:] == 0)
     assert rel_err(got, half_vals(g_ref)) <= REL_MLP and rel_err(dsig.cpu().numpy(), ds_ref) <= REL_MLP
+    if R < 100:
+        return
+    # the same rays as the second half of a longer sample list: offsets carry a base, results do not change
+    k = R // 2
+    base = int(off[k])
+    sh = lambda a: up.f(np.ascontiguousarray(a[base:]))
+    rgb_b = torch.zeros((R - k, 3), dtype=f32, device="cuda"); phi_b = torch.zeros_like(rgb_b); dw_b = torch.zeros(n - base, dtype=f32, device="cuda")
+    ws_b = torch.zeros(R - k, dtype=f32, device="cuda"); grad_b = torch.zeros((n - base, 8), dtype=torch.float16, device="cuda")
+    dsig_b = torch.zeros(n - base, dtype=f32, device="cuda")
+    o_b, c_b = up.f(off[k:].view(np.int32).copy()), up.f(counts[k:].view(np.int32).copy())
+    t_b, s_b, col_b, dens_b, tgt_b = sh(t), sh(sigma), sh(col), sh(dens), up.f(target[k:].copy())
+    nb.check(lib.nb_composite_train(R - k, base, o_b, c_b, t_b, s_b, None, None, col_b, 8, tgt_b, P(rgb_b), None, P(phi_b), P(dw_b), P(ws_b), lam, 0.0,
+                                    bg, st), "nb_composite_train")
+    nb.check(lib.nb_color_grad(R - k, base, c_b, o_b, t_b, dens_b, 16, col_b, 8, P(phi_b), P(rgb_b), P(dw_b), P(ws_b), P(grad_b), 8, P(dsig_b), scale,
+                               bias, R, st), "nb_color_grad")
+    rgb_i = torch.zeros_like(rgb_b)
+    nb.check(lib.nb_composite_infer(R - k, base, k, d_off, c_b, t_b, s_b, col_b, 8, None, P(rgb_i), None, None, bg, st), "nb_composite_infer")
+    torch.cuda.synchronize()
+    assert torch.equal(rgb_b, rgb[k:]) and torch.equal(dw_b, dw[base:]) and torch.equal(ws_b, wsum[k:])
+    assert torch.equal(grad_b, grad[base:]) and torch.equal(dsig_b, dsig[base:]) and torch.equal(rgb_i, rgb2[k:])
 
 
 def test_occupancy_kernels(cuda, nb, orc):

@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 from helpers import ABS_RGB, REL_MLP, Uploader, dev_half_bits, half_bits, half_vals, make_mlp, make_positions, make_table, mlp_dims, rel_err
-from test_oracle_nerf_cpu import camera_rays, sphere_bitfield
+from test_oracle_nerf_cpu import camera_rays, speckled_bitfield, sphere_bitfield
 
 pytestmark = pytest.mark.gpu
 
@@ -122,14 +122,14 @@ def test_training_steps_track_the_reference(cuda, nb, ref):
     ref.lib().ref_field_destroy(rf)
 
 
-@pytest.mark.parametrize("cascades,spv", [(1, 1), (3, 1), (1, 2)])
-def test_march_is_bit_exact_against_reference(cuda, nb, ref, orc, cascades, spv):
+@pytest.mark.parametrize("cascades,spv,speckle", [(1, 1, False), (3, 1, False), (1, 2, False), (1, 1, True), (2, 1, True)])
+def test_march_is_bit_exact_against_reference(cuda, nb, ref, orc, cascades, spv, speckle):
     torch = cuda
     up = Uploader(torch, nb)
     lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
     res, levels, R, batch = (128, 128, 128), 4, 30000, 1 << 18
     sc = nb.scene_desc(res, [-.5] * 3, [.5] * 3, cascades, levels, spv)
-    bits = sphere_bitfield(orc, res, levels, cascades)
+    bits = speckled_bitfield(orc, res, levels, cascades) if speckle else sphere_bitfield(orc, res, levels, cascades)
     o, d = camera_rays(R, seed=7)
     d_o, d_d = up.f(o), up.f(d)
     d_bits = torch.from_numpy(bits).cuda()
@@ -181,9 +181,9 @@ def test_compositing_and_loss_gradients_against_reference_kernels(cuda, nb, ref)
                                                               up.f(np.ascontiguousarray(col[:, :3])), up.f(target), up.f(dens))
     m = dict(rgb=Z(R, 3), depth=Z(R), phi=Z(R, 3), dw=Z(n), ws=Z(R), grad=Z(n, 8, dt=torch.float16), dsig=Z(n))
     r = dict(rgb=Z(R, 3), depth=Z(R), phi=Z(R, 3), dw=Z(n), ws=Z(R), grad=Z(n, 3, dt=torch.float16), dsig=Z(n))
-    nb.check(lib.nb_composite_train(R, d_off, d_cnt, d_t, d_sig, None, None, d_col8, 8, d_tgt, P(m["rgb"]), P(m["depth"]), P(m["phi"]), P(m["dw"]),
+    nb.check(lib.nb_composite_train(R, 0, d_off, d_cnt, d_t, d_sig, None, None, d_col8, 8, d_tgt, P(m["rgb"]), P(m["depth"]), P(m["phi"]), P(m["dw"]),
                                     P(m["ws"]), lam, 0.0, bg, st))
-    nb.check(lib.nb_color_grad(R, d_cnt, d_off, d_t, d_dens, 16, d_col8, 8, P(m["phi"]), P(m["rgb"]), P(m["dw"]), P(m["ws"]), P(m["grad"]), 8, P(m["dsig"]),
+    nb.check(lib.nb_color_grad(R, 0, d_cnt, d_off, d_t, d_dens, 16, d_col8, 8, P(m["phi"]), P(m["rgb"]), P(m["dw"]), P(m["ws"]), P(m["grad"]), 8, P(m["dsig"]),
                                scale, bias, R, st))
     ref.lib().ref_volume_rendering(R, d_off, d_cnt, d_t, d_sig, d_col3, d_tgt, P(r["rgb"]), P(r["depth"]), P(r["phi"]), P(r["dw"]), P(r["ws"]), lam, 0.0,
                                    ref.hptr(bgn), 0, 0, st)

@@ -22,6 +22,21 @@ def sphere_bitfield(orc, res, levels, cascades, aabb=0.5, radius=0.3):
     return bits
 
 
+def speckled_bitfield(orc, res, levels, cascades, p=0.02, seed=3):
+    """The sphere plus stray finest-level cells set with probability p, pyramid rebuilt: empty-space skips keep
+    running into isolated occupied cells, solid runs into holes' borders."""
+    bits = sphere_bitfield(orc, res, levels, cascades)
+    S = orc.pyramid_cells(res, levels)
+    G = res[0] * res[1] * res[2]
+    rng = np.random.default_rng(seed)
+    for c in range(cascades):
+        lvl0 = np.unpackbits(bits[c * S // 8: c * S // 8 + G // 8], bitorder="little")
+        lvl0 |= (rng.random(G) < p).astype(np.uint8)
+        bits[c * S // 8: c * S // 8 + G // 8] = np.packbits(lvl0, bitorder="little")
+    orc.build_mipmaps(bits, res, levels, cascades)
+    return bits
+
+
 def camera_rays(n, radius=1.5, seed=0, jitter=0.25):
     rng = np.random.default_rng(seed)
     o = rng.normal(size=(n, 3)); o = (radius * o / np.linalg.norm(o, axis=1, keepdims=True)).astype(np.float32)
