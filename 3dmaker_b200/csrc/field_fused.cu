@@ -462,14 +462,14 @@ __global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(const __
                 // Gradient scatter of this tile, fire-and-forget reductions that drain through L2 while the tensor
                 // work of the next tile (and of the other CTA on this SM) goes on: thread = (row, every other level).
                 __syncthreads();
-                const int r = tid & (TILE_ROWS - 1), hsel = tid >> 7;
+                const int r = tid & (TILE_ROWS - 1), hsel = tid >> 7;  // a warp = 32 consecutive samples at one level
                 const int64_t row = row_base + r;
-                if (row < io.n) {
-                    const float4 p = ld_nc_f4(gio.pos4 + row * 4);
-                    for (int level = gio.scatter_begin + hsel; level < gp.L; level += 2) {
-                        const float2 gq = __half22float2(*reinterpret_cast<const __half2*>(&sDZ[r * HS + 2 * level]));
-                        if (gq.x != 0.f || gq.y != 0.f) scatter_sample_level(gp, level, p.x, p.y, p.z, gq, gio.table_grads);
-                    }
+                const bool has = row < io.n;
+                float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (has) p = ld_nc_f4(gio.pos4 + row * 4);
+                for (int level = gio.scatter_begin + hsel; level < gp.L; level += 2) {
+                    const float2 gq = __half22float2(*reinterpret_cast<const __half2*>(&sDZ[r * HS + 2 * level]));
+                    scatter_level_warp(gp, level, p.x, p.y, p.z, gq, has, gio.table_grads, lane);
                 }
             }
             __syncthreads();

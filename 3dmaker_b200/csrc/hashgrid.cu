@@ -92,62 +92,40 @@ __global__ void __launch_bounds__(CTA_THREADS) grid_mlp_forward_kernel(const __g
     if (cx.row0 < n) mlp_forward_warp<S, 0>(cx);
 }
 
-// Tunables of the scatter (nb_set_tuning): levels below `dedupe_levels` that are dense merge equal addresses inside
-// a warp before the reduction; levels below `smem_levels` whose dense grid fits shared memory are accumulated per CTA
-// in shared memory and flushed once; [level_begin, level_end) restricts the launch (profiling experiments).
+// Tunables of the scatter (nb_set_tuning): levels below `smem_levels` whose dense grid fits shared memory are
+// accumulated per CTA in shared memory and flushed once; [level_begin, level_end) restricts the launch (profiling
+// experiments).
 struct ScatterTuning {
-    int dedupe_levels = 2;
     int smem_levels = 2;
     int level_begin = 0;
     int level_end = NB_MAX_LEVELS;
 };
 static ScatterTuning g_scatter_tuning;
 std::atomic<int> g_pair_ops{1};
+std::atomic<int> g_run_merge{1};
 
 // Gradient scatter, one thread per (sample, level), level = level_base + blockIdx.y so that all CTAs resident at one
 // time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector reduction.
-// Dense levels below dedupe_levels first merge lanes that hit the same entry (as the reference does on every dense
-// level, networkFusionBackwardHashtable.cu:843-887): neighbouring samples of a ray share coarse cells.
 __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
                                                                const __half* __restrict__ dEnc, int denc_stride, int64_t n,
-                                                               float* __restrict__ grads, int level_base, int dedupe_levels) {
+                                                               float* __restrict__ grads, int level_base) {
     const int level = level_base + blockIdx.y;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const int lane = threadIdx.x & 31;
-    float4 p = ld_nc_f4(pos4 + i * 4);
-    const bool dense = level < gp.dls;
-    float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
-    if (dense && level < dedupe_levels) {
-        Corners c;
-        corners_of<true>(p.x, p.y, p.z, gp.sscales[level], dense, gp.T, c);
-        float w[8];
-        corner_weights(c, w);
-        float* base = grads + (size_t)level * gp.T * 2;
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            float vx = g.x * w[k], vy = g.y * w[k];
-            unsigned active = __activemask();
-            unsigned group = __match_any_sync(active, c.idx[k]);
-            int leader = __ffs(group) - 1;
-            float sx = 0.f, sy = 0.f;
-            unsigned tmp = group;
-            while (tmp) {
-                int src = __ffs(tmp) - 1;
-                sx += __shfl_sync(group, vx, src);
-                sy += __shfl_sync(group, vy, src);
-                tmp &= tmp - 1;
-            }
-            if (lane == leader) red_add_v2(base + (size_t)c.idx[k] * 2, sx, sy);
-        }
-    } else {
-        scatter_sample_level(gp, level, p.x, p.y, p.z, g, grads);
+    const bool has = i < n;
+    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+    float2 g = make_float2(0.f, 0.f);
+    if (has) {
+        p = ld_nc_f4(pos4 + i * 4);
+        g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
     }
+    scatter_level_warp(gp, level, p.x, p.y, p.z, g, has, grads, threadIdx.x & 31);
 }
 
 // Coarse dense levels whose whole grid fits shared memory: every CTA accumulates its share of the samples into a
 // private copy of the level with shared-memory atomics and adds the non-zero entries to global memory once, so the
-// heavily contended coarse entries see (#CTAs) global reductions instead of (#samples x 8).
+// heavily contended coarse entries see (#CTAs) global reductions instead of (#samples x 8).  Runs of consecutive
+// samples in one cell are merged in the warp first (scatter_level_runs): on these levels a ray spends ten or more
+// samples per cell, and same-address shared-memory atomics serialise.
 __global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
                                                            const __half* __restrict__ dEnc, int denc_stride, int64_t n,
                                                            float* __restrict__ grads, int level_base) {
@@ -159,18 +137,23 @@ __global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant
     const int cells = (N_l + 1) * (N_l + 1) * (N_l + 1);
     for (int c = threadIdx.x; c < cells; c += blockDim.x) acc[c] = make_float2(0.f, 0.f);
     __syncthreads();
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        float4 p = ld_nc_f4(pos4 + i * 4);
-        Corners c;
-        corners_of<true>(p.x, p.y, p.z, scale, true, gp.T, c);
-        float w[8];
-        corner_weights(c, w);
-        float2 g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            atomicAdd(&acc[c.idx[k]].x, g.x * w[k]);
-            atomicAdd(&acc[c.idx[k]].y, g.y * w[k]);
+    const int lane = threadIdx.x & 31;
+    for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x; i0 < n; i0 += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = i0 + threadIdx.x;
+        const bool has = i < n;
+        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+        float2 g = make_float2(0.f, 0.f);
+        if (has) {
+            p = ld_nc_f4(pos4 + i * 4);
+            g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
         }
+        scatter_level_runs(gp, level, p.x, p.y, p.z, g, has, lane, [&](const Corners& c, const float (&v)[16]) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                atomicAdd(&acc[c.idx[k]].x, v[2 * k]);
+                atomicAdd(&acc[c.idx[k]].y, v[2 * k + 1]);
+            }
+        });
     }
     __syncthreads();
     float* base = grads + (size_t)level * gp.T * 2;
@@ -246,7 +229,7 @@ int scatter_launch(const GridParams& gp, const float* d_pos4, const __half* d_de
     }
     if (le > smem_end) {
         dim3 grid((unsigned)((n + 255) / 256), le - smem_end, 1);
-        scatter_backward_kernel<<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end, tn.dedupe_levels);
+        scatter_backward_kernel<<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end);
         NB_CHECK_LAUNCH();
         g_launch_count++;
     }
@@ -412,7 +395,7 @@ extern "C" int nb_grid_mlp_forward(const nb_grid_desc* desc, const nb_mlp_desc* 
 extern "C" int nb_set_tuning(const char* key, int value) {
     if (!key) return nb_set_error(NB_ERR_INVALID, "nb_set_tuning: null key");
     std::string k(key);
-    if (k == "scatter_dedupe_levels") g_scatter_tuning.dedupe_levels = value;
+    if (k == "scatter_run_merge") g_run_merge = value;
     else if (k == "scatter_smem_levels") g_scatter_tuning.smem_levels = value;
     else if (k == "pair_ops") g_pair_ops = value;
     else if (k == "scatter_level_begin") g_scatter_tuning.level_begin = value;

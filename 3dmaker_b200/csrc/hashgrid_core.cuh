@@ -9,10 +9,12 @@
 
 namespace nb {
 
-extern std::atomic<int> g_pair_ops;  // nb_set_tuning("pair_ops", ...)
+extern std::atomic<int> g_pair_ops;   // nb_set_tuning("pair_ops", ...)
+extern std::atomic<int> g_run_merge;  // nb_set_tuning("scatter_run_merge", ...)
 
 struct GridParams {
     int L, T, dls;
+    int run_merge; // non-zero: the gradient scatter sums runs of consecutive samples in one cell before reducing
     int pair_ops;  // non-zero: the two x-neighbours of a corner pair that share an aligned slot pair move as one access
     float scales[NB_MAX_LEVELS];   // forward (encode) resolutions
     float sscales[NB_MAX_LEVELS];  // resolutions of the gradient scatter
@@ -20,7 +22,7 @@ struct GridParams {
 
 inline GridParams make_params(const nb_grid_desc* d) {
     GridParams p;
-    p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start; p.pair_ops = g_pair_ops.load();
+    p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start; p.pair_ops = g_pair_ops.load(); p.run_merge = g_run_merge.load();
     for (int i = 0; i < NB_MAX_LEVELS; i++) { p.scales[i] = d->scales[i]; p.sscales[i] = d->scatter_scales[i]; }
     return p;
 }
@@ -36,6 +38,7 @@ __device__ __forceinline__ uint32_t dense_index(int cx, int cy, int cz, int N_l)
 struct Corners {
     uint32_t idx[8];  // entry index inside the level (pairs of features), corner order 000,100,010,110,001,101,011,111
     float wx1, wy1, wz1;
+    uint32_t cell;    // the low corner (x0 | y0 << 10 | z0 << 20) when the level has fewer than 1024 cells per axis, else ~0
 };
 
 // BWD_CLAMP = false: low corner clamped to [0, N_l] (forward); true: to [0, N_l - 1] (backward).
@@ -47,6 +50,7 @@ __device__ __forceinline__ void corners_of(float px, float py, float pz, float s
     const int hi = BWD_CLAMP ? N_l - 1 : N_l;
     x0 = max(0, min(x0, hi)); y0 = max(0, min(y0, hi)); z0 = max(0, min(z0, hi));
     int x1 = min(x0 + 1, N_l), y1 = min(y0 + 1, N_l), z1 = min(z0 + 1, N_l);
+    c.cell = (N_l < 1024) ? ((uint32_t)x0 | ((uint32_t)y0 << 10) | ((uint32_t)z0 << 20)) : 0xffffffffu;
     c.wx1 = 1.0f - x_l + floorf(x_l);
     c.wy1 = 1.0f - y_l + floorf(y_l);
     c.wz1 = 1.0f - z_l + floorf(z_l);
@@ -137,30 +141,72 @@ __device__ __forceinline__ void encode_tile(const GridParams& gp, const float* _
     }
 }
 
-// Adds one sample's gradient of one level (feature pair g) to the 8 corner entries of the fp32 table gradient.
-// Backward clamp and scatter resolution as hashTableScatter_Backward (networkFusionBackwardHashtable.cu:797-900).
-__device__ __forceinline__ void scatter_sample_level(const GridParams& gp, int level, float px, float py, float pz, float2 g,
-                                                     float* __restrict__ grads) {
+// The 8 reductions of one (sample, level): v[2k], v[2k+1] = the two features' contributions to corner k.
+__device__ __forceinline__ void reduce_corners(const Corners& c, const float (&v)[16], bool pair_ops, float* __restrict__ base) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t a = c.idx[2 * j], b = c.idx[2 * j + 1];
+        if (pair_ops && ((a ^ b) == 1u)) {
+            // x-neighbours in one aligned slot pair: one 16-byte reduction instead of two 8-byte ones
+            const bool a_hi = (a & 1u) != 0;
+            red_add_v4(base + (size_t)(a & ~1u) * 2, a_hi ? v[4 * j + 2] : v[4 * j], a_hi ? v[4 * j + 3] : v[4 * j + 1],
+                       a_hi ? v[4 * j] : v[4 * j + 2], a_hi ? v[4 * j + 1] : v[4 * j + 3]);
+        } else {
+            red_add_v2(base + (size_t)a * 2, v[4 * j], v[4 * j + 1]);
+            red_add_v2(base + (size_t)b * 2, v[4 * j + 2], v[4 * j + 3]);
+        }
+    }
+}
+
+// Adds the gradient of one level (feature pair g) of the warp's 32 samples to the fp32 table gradient: 8 corner
+// entries per sample.  Backward clamp and scatter resolution as hashTableScatter_Backward
+// (networkFusionBackwardHashtable.cu:797-900).  ALL 32 LANES MUST CALL; lanes without a sample pass active = false.
+//
+// Samples arrive in ray order, and on the coarser levels a ray stays inside one cell for many consecutive samples.
+// Lanes that follow each other in the same cell form a run; when the warp has few runs their 16 contributions are
+// summed across the run with shuffles and only the run's first lane issues reductions (the reference merges equal
+// addresses inside a warp on its dense levels for the same reason, networkFusionBackwardHashtable.cu:843-887).
+// Scattered positions (most lanes in different cells) take the direct path.
+// sink(c, v) adds v[2k], v[2k+1] to corner k's entry.
+template <class Sink>
+__device__ __forceinline__ void scatter_level_runs(const GridParams& gp, int level, float px, float py, float pz, float2 g, bool active, int lane,
+                                                   Sink&& sink) {
     Corners c;
     corners_of<true>(px, py, pz, gp.sscales[level], level < gp.dls, gp.T, c);
     float w[8];
     corner_weights(c, w);
-    float* base = grads + (size_t)level * gp.T * 2;
-    const bool pair_ops = gp.pair_ops != 0;
+    active = active && (g.x != 0.f || g.y != 0.f);
+    // inactive lanes and levels too fine for a cell key never merge: a key no other lane has
+    const uint32_t key = (active && c.cell != 0xffffffffu) ? c.cell : (0xc0000000u | (uint32_t)lane);
+    const uint32_t below = __shfl_up_sync(0xffffffffu, key, 1);
+    const bool head = lane == 0 || key != below;
+    const unsigned heads = __ballot_sync(0xffffffffu, head);
+    float v[16];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const uint32_t a = c.idx[2 * j], b = c.idx[2 * j + 1];
-        const float wa = w[2 * j], wb = w[2 * j + 1];
-        if (pair_ops && ((a ^ b) == 1u)) {
-            // x-neighbours in one aligned slot pair: one 16-byte reduction instead of two 8-byte ones
-            const bool a_hi = (a & 1u) != 0;
-            const float wl = a_hi ? wb : wa, wh = a_hi ? wa : wb;
-            red_add_v4(base + (size_t)(a & ~1u) * 2, g.x * wl, g.y * wl, g.x * wh, g.y * wh);
-        } else {
-            red_add_v2(base + (size_t)a * 2, g.x * wa, g.y * wa);
-            red_add_v2(base + (size_t)b * 2, g.x * wb, g.y * wb);
+    for (int k = 0; k < 8; k++) { v[2 * k] = g.x * w[k]; v[2 * k + 1] = g.y * w[k]; }
+    if (!gp.run_merge || __popc(heads) > 20) {
+        if (active) sink(c, v);
+        return;
+    }
+    const int run = __popc(heads & (0xffffffffu >> (31 - lane)));  // index of this lane's run
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int other = __shfl_down_sync(0xffffffffu, run, o);
+        const bool same = (lane + o < 32) && other == run;
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const float n = __shfl_down_sync(0xffffffffu, v[k], o);
+            if (same) v[k] += n;
         }
     }
+    if (head && active) sink(c, v);
+}
+
+__device__ __forceinline__ void scatter_level_warp(const GridParams& gp, int level, float px, float py, float pz, float2 g, bool active,
+                                                   float* __restrict__ grads, int lane) {
+    float* base = grads + (size_t)level * gp.T * 2;
+    const bool pair_ops = gp.pair_ops != 0;
+    scatter_level_runs(gp, level, px, py, pz, g, active, lane, [&](const Corners& c, const float (&v)[16]) { reduce_corners(c, v, pair_ops, base); });
 }
 
 // Host side of the stand-alone scatter (hashgrid.cu): levels [level_begin, level_end) from a gradient matrix whose

@@ -565,7 +565,7 @@ def run_scene(args, rank, world, local_rank):
             eng.train_rays(o, d, c)
         return eng.samples_last_call()
 
-    warm = max(args.warmup, 272)          # past the 256 steps of whole-grid occupancy updates
+    warm = max(args.warmup, args.scene_warm)   # default: past the 256 steps of whole-grid occupancy updates
     for i in range(warm):
         step(i)
     torch.cuda.synchronize()
@@ -621,7 +621,7 @@ def run_render(args, rank, world, local_rank):
     D = importlib.import_module("3dmaker_b200.distributed")
     lib = nb.load()
     opts = nm.default_options(**SCENE_OPTS)
-    train_steps = 400
+    train_steps = args.render_train_steps
     if reference:
         from oracle import ref_cuda as ref
         if not ref.available():
@@ -631,10 +631,9 @@ def run_render(args, rank, world, local_rank):
     else:
         eng = nm.InstantNerf(torch, opts)
     # every rank trains the same model from the same seeded batches (replicated, no exchange needed for the benchmark)
-    batches = _scene_batches(torch, syn, 8, 1 << 16, 9000)
     i = 0
     while (eng.steps if reference else eng.steps.value) < train_steps:
-        eng.train_rays(*batches[i % 8]); i += 1
+        eng.train_rays(*_scene_batches(torch, syn, 1, 1 << 16, 9000 + i)[0]); i += 1
     torch.cuda.synchronize()
     W, H = 1920, 1080
     focal = syn.focal_from_fov(W, 50.0)
@@ -697,6 +696,8 @@ def main():
     ap.add_argument("--workload", default="field", choices=["field", "scene", "render"],
                     help="field: the headline step on explicit samples (default, the driver's line); scene: full NeRF training step on the "
                          "analytic scene; render: 1920x1080 orbit frames, pixels sharded over the ranks")
+    ap.add_argument("--scene-warm", type=int, default=272, help="scene workload: untimed train_rays calls before the timed ones")
+    ap.add_argument("--render-train-steps", type=int, default=400, help="render workload: optimizer steps the model is trained for first")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")

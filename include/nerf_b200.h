@@ -119,11 +119,11 @@ int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d_pos4, cons
                              float* d_table_grads, void* stream);
 
 /* A/B switches for benchmarking, in the spirit of the reference's TinyMLPHashGrid::setSplitScatter
- * (TinyMLPHashGrid.h:60-63).  Keys: "scatter_dedupe_levels" (dense levels below it merge equal addresses inside a
- * warp before the reduction), "scatter_smem_levels" (dense levels below it that fit shared memory are accumulated
- * per CTA), "scatter_level_begin" / "scatter_level_end" (restrict the scatter to a level range), "pair_ops" (x-neighbour
- * corners that share an aligned slot pair are gathered with one 8-byte load and scattered with one 16-byte
- * reduction; default 1).  Results do not depend on these beyond fp32 summation order of the scatter. */
+ * (TinyMLPHashGrid.h:60-63).  Keys: "scatter_run_merge" (consecutive samples in one grid cell are summed inside the
+ * warp before the reduction; default 1), "scatter_smem_levels" (dense levels below it that fit shared memory are
+ * accumulated per CTA; default 2), "scatter_level_begin" / "scatter_level_end" (restrict the scatter to a level range),
+ * "pair_ops" (x-neighbour corners that share an aligned slot pair are gathered with one 8-byte load and scattered with
+ * one 16-byte reduction; default 1).  Results do not depend on these beyond fp32 summation order of the scatter. */
 int nb_set_tuning(const char* key, int value);
 
 /* ---- fused MLP ---------------------------------------------------------------------------- */

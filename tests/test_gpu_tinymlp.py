@@ -197,6 +197,40 @@ def test_scatter_backward(cuda, nb, orc, n, T):
     assert np.allclose(per, half_vals(denc).astype(np.float64).reshape(n, 16, 2).sum(axis=0), rtol=1e-3, atol=1e-5)
 
 
+@pytest.mark.parametrize("n", [4000, 70000])
+def test_scatter_of_ray_ordered_samples(cuda, nb, orc, n):
+    """Samples in ray order (a short step between neighbours, as the marcher emits them): most warps take the path that
+    sums runs of samples in one cell before reducing.  Against the oracle, and against the direct path switched on by
+    nb_set_tuning - the two differ by fp32 summation order only.  Some gradient rows are exactly zero (skipped)."""
+    torch = cuda
+    up = Uploader(torch, nb)
+    T = 1 << 17
+    d, scales = _grid(nb, T=T, b=1.3819)
+    rng = np.random.default_rng(5)
+    per_ray = 40
+    rays = (n + per_ray - 1) // per_ray
+    o = rng.uniform(0.3, 0.7, (rays, 1, 3)); dirs = rng.normal(size=(rays, 1, 3)); dirs /= np.linalg.norm(dirs, axis=2, keepdims=True)
+    pts = (o + dirs * (np.arange(per_ray)[None, :, None] * 0.004)).reshape(-1, 3)[:n]
+    pos = np.zeros((n, 4), np.float32); pos[:, :3] = np.clip(pts, 0.0, 0.999)
+    g = rng.normal(0, 1e-2, size=(n, 32)).astype(np.float32)
+    g[rng.random(n) < 0.1] = 0.0
+    denc = half_bits(g)
+    out = {}
+    lib = nb.load()
+    for merge in (1, 0):
+        nb.check(lib.nb_set_tuning(b"scatter_run_merge", merge), "nb_set_tuning")
+        grads = torch.zeros(16 * T * 2, dtype=torch.float32, device="cuda")
+        nb.check(lib.nb_hash_scatter_backward(ctypes.byref(d), up.f(pos), up.h(denc), n, nb.ptr(grads), nb.stream_ptr()), "nb_hash_scatter_backward")
+        torch.cuda.synchronize()
+        out[merge] = grads.cpu().numpy()
+    nb.check(lib.nb_set_tuning(b"scatter_run_merge", 1), "nb_set_tuning")
+    ref = orc.scatter_backward(pos, denc, d.np_scatter_scales, T, d.dense_level_start)
+    assert rel_err(out[1], ref) <= REL_MLP and rel_err(out[0], ref) <= REL_MLP
+    assert rel_err(out[1], out[0]) <= 1e-5
+    per = out[1].astype(np.float64).reshape(16, T, 2).sum(axis=1)
+    assert np.allclose(per, half_vals(denc).astype(np.float64).reshape(n, 16, 2).sum(axis=0), rtol=1e-3, atol=1e-5)
+
+
 def test_mse_loss_grad(cuda, nb, orc):
     torch = cuda
     up = Uploader(torch, nb)
