@@ -32,7 +32,6 @@ TINY_SRC = ["networkFusion.cu", "networkFusionBackward.cu", "networkFusionHashta
 # includes InstantNerf.cu to reach the kernels that have no launcher of their own.
 NERF_SRC = ["processRays.cu", "compositing.cu"]
 SHIM = os.path.join(HERE, "ref_shim.cu")
-TWINS = ["ref_twin_backprop_hash.cu", "ref_twin_backprop.cu", "ref_twin_forward.cu", "ref_twin_optimizer.cu", "ref_twin_scatter.cu"]
 
 
 def _nvcc():
@@ -66,17 +65,6 @@ def build(verbose=True):
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("reference link failed:\n" + r.stderr[-4000:])
-    for t in TWINS:
-        src = os.path.join(HERE, t)
-        if not os.path.exists(src):
-            continue
-        so = os.path.join(OUT, "lib" + t[:-3] + ".so")
-        if _newer(so, [src]):
-            continue
-        r = subprocess.run([_nvcc()] + FLAGS + ["-shared", src, "-o", so, "-L", OUT, "-lref3dmaker", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"],
-                           capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError("twin build failed for %s:\n%s" % (t, r.stderr[-4000:]))
     if verbose:
         print("reference build in", OUT)
     return OUT
