@@ -205,6 +205,7 @@ _SIGNATURES = {
     "nb_nerf_set_global_ray_scale": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_fused_field": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
+    "nb_nerf_set_steps_per_call": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),
     "nb_nerf_load_params": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

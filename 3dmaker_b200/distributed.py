@@ -32,20 +32,22 @@ def pixel_tiles(num_pixels, rank, world, tile=4096):
 class DataParallelTrainer:
     """Wraps a scene engine so that train_rays() takes the GLOBAL ray batch.
 
-    engine needs: set_global_ray_scale(int), set_single_step(bool), set_grad_sync(fn), train_rays(o, d, rgb) -> total
+    engine needs: set_global_ray_scale(int), set_steps_per_call(int), set_grad_sync(fn), train_rays(o, d, rgb) -> total
     optimizer steps so far, rays_consumed(), arena_tensor(name).  dist is torch.distributed (already initialised) or
     None for a single process."""
 
-    def __init__(self, torch, engine, dist=None):
+    def __init__(self, torch, engine, dist=None, steps_per_call=1):
         self.torch, self.engine, self.dist = torch, engine, dist
+        self.steps_per_call = steps_per_call
         self.rank = dist.get_rank() if dist is not None else 0
         self.world = dist.get_world_size() if dist is not None else 1
         self._steps_seen = 0
         self.sync_calls = 0
         if self.world > 1:
             engine.set_grad_sync(self._allreduce)
-            # one optimizer step, hence one allreduce, per call on every rank, whatever the local sample count is
-            engine.set_single_step(True)
+            # the same number of optimizer steps, hence allreduces, per call on every rank, whatever the local sample
+            # counts are (steps_per_call > 1 lets one occupancy walk of a large ray shard serve several steps)
+            engine.set_steps_per_call(steps_per_call)
         # with equal shards (num_rays a multiple of world) local_rays * world is exactly the global ray count
         engine.set_global_ray_scale(self.world)
 
@@ -54,16 +56,16 @@ class DataParallelTrainer:
         self.dist.all_reduce(grad, op=self.dist.ReduceOp.SUM)
 
     def train_rays(self, rays_o, rays_d, rgb_true):
-        """One optimizer step on the global batch (which must split evenly over the ranks); returns the number of
-        local rays that fitted this rank's sample batch and were trained on (normally all of its shard)."""
+        """steps_per_call optimizer steps on the global batch (which must split evenly over the ranks); returns the
+        number of local rays that fitted this rank's sample batches and were trained on."""
         n = rays_o.shape[0]
         if n % self.world != 0:
             raise ValueError("global ray batch (%d) must be a multiple of the number of ranks (%d)" % (n, self.world))
         start, count = ray_shard(n, self.rank, self.world)
         before = self._steps_seen
         self._steps_seen = self.engine.train_rays(rays_o[start:start + count], rays_d[start:start + count], rgb_true[start:start + count])
-        if self.world > 1 and self._steps_seen - before != 1:
-            raise RuntimeError("the engine took %d optimizer steps in single-step mode" % (self._steps_seen - before))
+        if self.world > 1 and self._steps_seen - before != self.steps_per_call:
+            raise RuntimeError("the engine took %d optimizer steps instead of %d" % (self._steps_seen - before, self.steps_per_call))
         return self.engine.rays_consumed() if self.world > 1 else count
 
     def replicas_in_sync(self):

@@ -290,7 +290,24 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
     // (every 16th step) or the walked window runs out while rays remain beyond it.
     uint32_t winFirst = 0, winCount = 0;
     bool walked = false;
-    while (raysDone < numRays) {
+    // m_stepsPerCall > 0 (data parallelism): exactly that many optimizer steps, hence gradient exchanges, per call on
+    // every rank - rays left over after the last step stay untrained, and a rank that has used up its rays earlier
+    // runs the remaining steps with no samples (it still joins the exchange and applies the common update).
+    while (m_stepsPerCall > 0 ? i < m_stepsPerCall : raysDone < numRays) {
+        if (raysDone >= numRays) {
+            if (hitCounts != nullptr) hitCounts[i] = 0;
+            m_lastTotalHits = 0;
+            if (m_trainSteps % 16 == 0) {
+                timed(stream, m_times.occupancy, [&]() {
+                    if (m_trainSteps < 256) earlyOccupancyGridUpdate(stream);
+                    else lateOccupancyGridUpdate(stream);
+                });
+            }
+            if (m_gradSync) m_gradSync(m_arena.G(0), m_arena.total, stream);
+            optimizerStep(stream);
+            trainStepCount++; m_trainSteps++; m_times.steps++; i++;
+            continue;
+        }
         uint32_t begin = 0, end = 0;
         timed(stream, m_times.march, [&]() {
             for (;;) {
@@ -417,22 +434,25 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
             }
         }
         if (m_gradSync) m_gradSync(m_arena.G(0), m_arena.total, stream);
-        timed(stream, m_times.optimizer, [&]() {
-            if (m_optSteps < 50000) m_optSteps++;
-            float bc1 = 1.0f - std::pow(m_opts.beta1, (float)m_optSteps);
-            float bc2 = 1.0f - std::pow(m_opts.beta2, (float)m_optSteps);
-            throw_on_error(nb_adam_step(m_arena.W(0), m_arena.Wh(0), m_arena.G(0), m_arena.M(0), m_arena.V(0), m_arena.sparse_count, m_arena.total,
-                                        m_opts.learningRate, m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),
-                           "optimizer");
-        });
+        optimizerStep(stream);
         trainStepCount++;
         m_trainSteps++;
         m_times.steps++;
         raysDone += currentChunkRays;
         i++;
         m_lastRaysConsumed = raysDone;
-        if (m_singleStep) break;
     }
+}
+
+void InstantNerf::optimizerStep(cudaStream_t stream) {
+    timed(stream, m_times.optimizer, [&]() {
+        if (m_optSteps < 50000) m_optSteps++;
+        float bc1 = 1.0f - std::pow(m_opts.beta1, (float)m_optSteps);
+        float bc2 = 1.0f - std::pow(m_opts.beta2, (float)m_optSteps);
+        throw_on_error(nb_adam_step(m_arena.W(0), m_arena.Wh(0), m_arena.G(0), m_arena.M(0), m_arena.V(0), m_arena.sparse_count, m_arena.total,
+                                    m_opts.learningRate, m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),
+                       "optimizer");
+    });
 }
 
 void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d, uint32_t numRays, float* d_rgb_out, cudaStream_t stream) {

@@ -122,9 +122,11 @@ public:
     void rebuildOccupancy(cudaStream_t stream = 0) { earlyOccupancyGridUpdate(stream); }
     int trainSteps() const { return m_trainSteps; }
     uint32_t lastTotalHits() const { return m_lastTotalHits; }
-    // Data parallelism: exactly one optimizer step (hence one gradient exchange) per trainWithRaysHit call; rays of
-    // the call that do not fit the sample batch are left untrained instead of starting a second step.
-    void setSingleStep(bool on) { m_singleStep = on; }
+    // Data parallelism: exactly k optimizer steps (hence k gradient exchanges) per trainWithRaysHit call on every rank;
+    // rays left after the k-th step stay untrained, a rank that runs out of rays earlier steps with no samples.
+    // k = 0 restores the reference's loop (as many steps as the rays need).
+    void setStepsPerCall(int k) { m_stepsPerCall = k > 0 ? k : 0; }
+    void setSingleStep(bool on) { m_stepsPerCall = on ? 1 : 0; }
     uint32_t lastRaysConsumed() const { return m_lastRaysConsumed; }
     const NerfPhaseTimes& phaseTimes() const { return m_times; }
     // Buffers of the last step, for parity tests (valid until the next call).
@@ -144,6 +146,7 @@ private:
     void earlyOccupancyGridUpdate(cudaStream_t stream = 0);
     void lateOccupancyGridUpdate(cudaStream_t stream = 0);
     void finishOccupancyUpdate(cudaStream_t stream);
+    void optimizerStep(cudaStream_t stream);
     void walkRays(const float3* d_rays_o, const float3* d_rays_d, uint32_t first, uint32_t count, cudaStream_t stream);
     nb_scene_desc scene() const;
     template <class F> void timed(cudaStream_t stream, double& acc, F&& f);
@@ -179,5 +182,5 @@ private:
     int m_optSteps = 0;  // Adam step counter (capped at 50000 for the bias corrections)
     uint32_t m_lastTotalHits = 0;
     uint32_t m_lastRaysConsumed = 0;
-    bool m_singleStep = false;
+    int m_stepsPerCall = 0;
 };

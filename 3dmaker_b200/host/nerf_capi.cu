@@ -97,6 +97,12 @@ extern "C" int nb_nerf_set_single_step(nb_nerf* h, int on) {
     return NB_OK;
 }
 
+extern "C" int nb_nerf_set_steps_per_call(nb_nerf* h, int steps) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    h->impl.setStepsPerCall(steps);
+    return NB_OK;
+}
+
 extern "C" int nb_nerf_set_fused_field(nb_nerf* h, int on) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     return h->impl.setFusedField(on != 0) ? 1 : 0;

@@ -81,6 +81,10 @@ class InstantNerf:
         """Exactly one optimizer step per train_rays() call (data parallelism); see rays_consumed()."""
         nb.check(self.lib.nb_nerf_set_single_step(self.h, 1 if on else 0))
 
+    def set_steps_per_call(self, steps):
+        """Exactly `steps` optimizer steps per train_rays() call on every rank (0: as many as the rays need)."""
+        nb.check(self.lib.nb_nerf_set_steps_per_call(self.h, int(steps)))
+
     def rays_consumed(self):
         return self.step_view().rays_consumed
 

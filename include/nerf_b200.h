@@ -386,6 +386,10 @@ int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user);
  * batch are left untrained (nb_nerf_step_view.rays_consumed says how many were used) instead of starting a second
  * step, so that every rank of a data-parallel job issues the same number of gradient exchanges. */
 int nb_nerf_set_single_step(nb_nerf* h, int on);
+/* The general form: exactly `steps` optimizer steps per nb_nerf_train_rays call (0 = as many as the rays need, the
+ * reference's loop).  A rank whose rays are used up before the last step takes the remaining steps with no samples
+ * of its own: it still calls fn and applies the update. */
+int nb_nerf_set_steps_per_call(nb_nerf* h, int steps);
 /* Switches between nb_field_forward / nb_field_backward (default when nb_field_supported) and the reference's
  * kernel-by-kernel sequence; returns 1 when the fused kernels are in effect afterwards, 0 otherwise.  Results agree
  * to the fp32 summation order of the weight gradients.  No counterpart in the reference. */

@@ -22,13 +22,13 @@ class FakeEngine:
     def __init__(self, max_rays=1 << 30):
         self.w = torch.linspace(-0.5, 0.5, 18, dtype=torch.float32)
         self.g = torch.zeros(18, dtype=torch.float32)
-        self.scale, self.sync, self.single, self.steps, self.max_rays, self.consumed = 1, None, False, 0, max_rays, 0
+        self.scale, self.sync, self.single, self.steps, self.max_rays, self.consumed = 1, None, 0, 0, max_rays, 0
 
     def set_global_ray_scale(self, s):
         self.scale = s
 
-    def set_single_step(self, on):
-        self.single = on
+    def set_steps_per_call(self, k):
+        self.single = k
 
     def set_grad_sync(self, fn):
         self.sync = fn
@@ -40,8 +40,8 @@ class FakeEngine:
         return {"w": self.w, "g": self.g}[name]
 
     def train_rays(self, o, d, rgb):
-        n, done = o.shape[0], 0
-        while done < n:
+        n, done, taken = o.shape[0], 0, 0
+        while (taken < self.single) if self.single else (done < n):
             k = min(self.max_rays, n - done)
             x = torch.cat([o[done:done + k], d[done:done + k]], dim=1)
             err = x @ self.w.view(3, 6).t() - rgb[done:done + k]
@@ -52,9 +52,8 @@ class FakeEngine:
             self.g.zero_()
             self.steps += 1
             done += k
+            taken += 1
             self.consumed = done
-            if self.single:
-                break
         return self.steps
 
     def render(self, o, d, out):
@@ -92,6 +91,14 @@ def _worker(rank, world, port, out_dir, case):
             o, d, c = _batch(64, 7)
             used = tr.train_rays(o, d, c)
             np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([tr.sync_calls, eng.steps, int(tr.replicas_in_sync()), used]))
+        elif case == "multistep":
+            # three steps per call on every rank: rank 0 needs one step for its 32 rays, rank 1 two (20 + 12); the
+            # steps a rank has no rays left for still exchange and update
+            eng = FakeEngine(max_rays=20 if rank == 1 else 1 << 30)
+            tr = D.DataParallelTrainer(torch, eng, dist, steps_per_call=3)
+            used = [tr.train_rays(*_batch(64, 40 + c)) for c in range(2)]
+            np.save(os.path.join(out_dir, "w%d.npy" % rank), eng.w.numpy())
+            np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([tr.sync_calls, eng.steps, int(tr.replicas_in_sync())] + used))
         elif case == "drift":
             eng = FakeEngine()
             tr = D.DataParallelTrainer(torch, eng, dist)
@@ -154,6 +161,13 @@ def test_a_rank_that_overflows_its_batch_still_exchanges_once(tmp_path):
     m0, m1 = np.load(tmp_path / "meta0.npy"), np.load(tmp_path / "meta1.npy")
     assert list(m0) == [1, 1, 1, 32]
     assert list(m1) == [1, 1, 1, 20]
+
+
+def test_fixed_number_of_steps_per_call_keeps_ranks_in_lock_step(tmp_path):
+    _run("multistep", tmp_path)
+    m0, m1 = np.load(tmp_path / "meta0.npy"), np.load(tmp_path / "meta1.npy")
+    assert list(m0) == [6, 6, 1, 32, 32] and list(m1) == [6, 6, 1, 32, 32]
+    assert np.array_equal(np.load(tmp_path / "w0.npy"), np.load(tmp_path / "w1.npy"))
 
 
 def test_replica_drift_is_detected(tmp_path):
