@@ -171,10 +171,35 @@ class SampleTrainer:
                                        m.total, self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2),
                                        1.0 / self.loss_scale, 1, nb.stream_ptr(stream)), "nb_adam_step")
 
+    def optimizer_step_synced(self, dist, chunks=4, stream=None):
+        """Data-parallel tail of a step: SUM-allreduce of the gradient arena and Adam, pipelined over `chunks` slices of
+        the arena - the allreduce of slice c+1 (NCCL's stream) runs while Adam updates slice c, so only the first
+        exchange and the last update are exposed.  Same result as one allreduce followed by optimizer_step()."""
+        m = self.model
+        if m.step_count < 50000:
+            m.step_count += 1
+        bc1 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta1), np.float32(m.step_count)))
+        bc2 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta2), np.float32(m.step_count)))
+        step = (m.total // chunks + 3) // 4 * 4
+        bounds = [min(c * step, m.total) for c in range(chunks)] + [m.total]
+        works = [dist.all_reduce(m.g[bounds[c]:bounds[c + 1]], op=dist.ReduceOp.SUM, async_op=True) for c in range(chunks)]
+        for c in range(chunks):
+            lo, hi = bounds[c], bounds[c + 1]
+            if hi <= lo:
+                continue
+            works[c].wait()                                 # the current stream waits for this slice's exchange
+            sparse = max(0, min(hi, m.hash_count) - lo)     # the slice's share of the hash table (sparse Adam rule)
+            nb.check(self.lib.nb_adam_step(m.ptr("w", lo), m.ptr("w_h", lo), m.ptr("g", lo), m.ptr("m", lo), m.ptr("v", lo), sparse, hi - lo,
+                                           self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2), 1.0 / self.loss_scale, 1,
+                                           nb.stream_ptr(stream)), "nb_adam_step")
+
     def step_device(self, n, stream=None, grad_sync=None):
-        """One full step on device-resident inputs.  grad_sync(grad_tensor), if given, runs between backward and
-        Adam (the data-parallel allreduce)."""
+        """One full step on device-resident inputs.  grad_sync: a callable grad_sync(grad_tensor) that runs between
+        backward and Adam, or torch.distributed itself (initialised) for the pipelined allreduce + Adam."""
         self.forward_backward(n, stream)
+        if grad_sync is not None and hasattr(grad_sync, "all_reduce"):
+            self.optimizer_step_synced(grad_sync, stream=stream)     # a torch.distributed module: pipelined exchange + Adam
+            return
         if grad_sync is not None:
             grad_sync(self.model.g)
         self.optimizer_step(stream)

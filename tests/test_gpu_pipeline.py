@@ -148,3 +148,37 @@ def test_fused_field_rejects_other_shapes(cuda, nb):
     assert pl.SampleTrainer(model, 64).fused is False
     with pytest.raises(nb.NerfB200Error):
         pl.SampleTrainer(model, 64, fused=True)
+
+
+def test_pipelined_allreduce_and_adam_equal_the_single_launch(cuda, nb):
+    """optimizer_step_synced (allreduce and Adam over slices of the arena) on a one-rank NCCL group against
+    optimizer_step: identical parameters, moments and fp16 copy, and the gradient is consumed."""
+    torch = cuda
+    import socket
+    import torch.distributed as dist
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    if dist.is_initialized():
+        pytest.skip("a process group already exists in this process")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
+    dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % port, rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        n, out = 4096, {}
+        pos, dirs, tgt = _inputs(n, 21)
+        for mode in ("single", "sliced"):
+            model = pl.FieldModel(torch, 16, 1 << 14, 16, 1.3819, 64, 2, 64, 3)
+            model.load_hashgrid(make_table(16, 1 << 14, seed=2, amp=0.1))
+            model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=3)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=4))
+            tr = pl.SampleTrainer(model, n)
+            tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+            for _ in range(2):
+                tr.step_device(n, None, dist if mode == "sliced" else (lambda g: dist.all_reduce(g)))
+            torch.cuda.synchronize()
+            out[mode] = [getattr(model, k).clone() for k in ("w", "w_h", "m", "v", "g")]
+        # the gradient itself differs run to run in its last bits (unordered atomics), so compare loosely but completely
+        for a, b in zip(out["single"][:4], out["sliced"][:4]):
+            assert torch.allclose(a.float(), b.float(), rtol=1e-3, atol=1e-6)
+        assert torch.all(out["sliced"][4] == 0) and torch.all(out["single"][4] == 0)
+        assert (out["sliced"][0] != torch.from_numpy(make_table(16, 1 << 14, seed=2, amp=0.1).ravel()).cuda()[:1].new_zeros(1)).any()
+    finally:
+        dist.destroy_process_group()
