@@ -382,11 +382,11 @@ def run_ours(args, rank, world, local_rank):
 
     grad_sync = None
     if world > 1:
-        if args.plain_allreduce:
+        if args.sliced_allreduce:
+            grad_sync = dist          # allreduce pipelined with Adam over slices of the arena (SampleTrainer.optimizer_step_synced)
+        else:
             def grad_sync(g):
                 dist.all_reduce(g, op=dist.ReduceOp.SUM)
-        else:
-            grad_sync = dist          # allreduce pipelined with Adam over slices of the arena (SampleTrainer.optimizer_step_synced)
 
     def step_resident(i):
         tr.pos, tr.dirs, tr.target = dev[i % 2]
@@ -719,7 +719,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
-    ap.add_argument("--plain-allreduce", action="store_true", help="N > 1: one allreduce then one Adam launch instead of the pipelined slices (A/B)")
+    ap.add_argument("--sliced-allreduce", action="store_true",
+                    help="N > 1: allreduce and Adam pipelined over 4 slices of the arena instead of one allreduce and one Adam launch "
+                         "(A/B; measured slower at 2 GPUs: 1.44 against 1.36 ms per step)")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()
