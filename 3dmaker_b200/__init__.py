@@ -150,6 +150,7 @@ _SIGNATURES = {
                                     c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_hash_scatter_backward": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "nb_set_tuning": (c_int, [ctypes.c_char_p, c_int]),
+    "nb_field_backward_tc_status": (c_int, []),
     "nb_field_supported": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc)]),
     "nb_field_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_void_p,

@@ -17,6 +17,7 @@
 #include <atomic>
 
 #include "hashgrid_core.cuh"
+#include "field_backward_tc.cuh"
 
 namespace nb {
 
@@ -578,6 +579,19 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
         shared_levels = nb::scatter_shared_levels(gp, n);
         gio.pos4 = d_pos4; gio.table_grads = d_table_grads; gio.scatter_begin = shared_levels;
         gio.denc_cols = 4 * shared_levels;   // only what the shared-memory scatter kernel below reads
+    }
+    if (nb::g_backward_tc.load() != 0) {
+        // tensor-memory formulation (field_backward_tc.cu): same inputs, outputs and rounding points
+        nb::tc::BackwardArgs ta{};
+        ta.enc = gio.enc; ta.dcolor = gio.dcolor; ta.dsigma = gio.dsigma; ta.dirs3 = io.dirs3; ta.ray_idx = io.ray_idx;
+        ta.ray_idx_offset = io.ray_idx_offset; ta.Wd = io.Wd; ta.Wc = io.Wc; ta.bd = io.bd; ta.bc = io.bc; ta.n = n;
+        ta.dWd = gio.dWd; ta.dbd = gio.dbd; ta.dWc = gio.dWc; ta.dbc = gio.dbc; ta.denc = gio.denc; ta.denc_cols = gio.denc_cols;
+        ta.pos4 = gio.pos4; ta.table_grads = gio.table_grads; ta.scatter_begin = gio.scatter_begin;
+        int rc = nb::launch_field_backward_tc(gp, ta, (cudaStream_t)stream);
+        if (rc != NB_OK) return rc;
+        if (scatter && shared_levels > 0)
+            return nb::scatter_launch(gp, d_pos4, (const __half*)d_denc_h, 4 * shared_levels, n, d_table_grads, 0, shared_levels, (cudaStream_t)stream);
+        return NB_OK;
     }
     auto kern = nb::field_backward_kernel<DensityNet, ColorNet>;
     size_t smem = nb::FieldBwd<DensityNet, ColorNet>::smem_bytes();

@@ -14,6 +14,7 @@
 #include <string>
 
 #include "hashgrid_core.cuh"
+#include "field_backward_tc.cuh"
 
 namespace nb {
 
@@ -396,6 +397,7 @@ extern "C" int nb_set_tuning(const char* key, int value) {
     if (!key) return nb_set_error(NB_ERR_INVALID, "nb_set_tuning: null key");
     std::string k(key);
     if (k == "scatter_run_merge") g_run_merge = value;
+    else if (k == "backward_tc") g_backward_tc = value;
     else if (k == "scatter_smem_levels") g_scatter_tuning.smem_levels = value;
     else if (k == "pair_ops") g_pair_ops = value;
     else if (k == "scatter_level_begin") g_scatter_tuning.level_begin = value;

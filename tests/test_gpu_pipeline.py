@@ -182,3 +182,40 @@ def test_pipelined_allreduce_and_adam_equal_the_single_launch(cuda, nb):
         assert (out["sliced"][0] != torch.from_numpy(make_table(16, 1 << 14, seed=2, amp=0.1).ravel()).cuda()[:1].new_zeros(1)).any()
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n", [1, 127, 128, 129, 5000, 70000])
+def test_tensor_memory_backward_agrees_with_the_register_formulation(cuda, nb, n):
+    """nb_field_backward with tcgen05.mma / tensor-memory accumulators against the mma.sync formulation: same rounding
+    points, so dL/d(encoding) and every gradient agree to accumulation order (an fp16 value may differ in its last bit
+    where the fp32 sums straddle a rounding boundary)."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    lib = nb.load()
+    L, T = 16, 1 << 15
+    model = pl.FieldModel(torch, L, T, 16, 1.3819, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    pos, dirs, tgt = _inputs(n, 13)
+    out = {}
+    try:
+        for name, tcflag, fs in (("regs", 0, False), ("tc", 1, False), ("regs+scatter", 0, True), ("tc+scatter", 1, True)):
+            nb.check(lib.nb_set_tuning(b"backward_tc", tcflag), "nb_set_tuning")
+            tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=fs)
+            tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+            model.g.zero_()
+            tr.forward_backward(n)
+            nb.check(lib.nb_field_backward_tc_status(), "tensor-memory backward status")
+            out[name] = dict(d_enc=half_vals(dev_half_bits(tr.d_enc)), g=model.g.cpu().numpy().copy())
+    finally:
+        nb.check(lib.nb_set_tuning(b"backward_tc", 0), "nb_set_tuning")
+        model.g.zero_()
+    H = model.hash_count
+    assert rel_err(out["tc"]["d_enc"], out["regs"]["d_enc"]) <= 2e-3
+    assert np.mean(out["tc"]["d_enc"] != out["regs"]["d_enc"]) < 2e-2
+    for name in ("tc", "tc+scatter"):
+        a, b = out["regs+scatter" if "scatter" in name else "regs"]["g"], out[name]["g"]
+        assert rel_err(b[:H], a[:H]) <= 2e-3, name
+        for off, cnt in ((model.off_dw, model.density.weight_count), (model.off_db, model.density.bias_count),
+                         (model.off_cw, model.color.weight_count), (model.off_cb, model.color.bias_count)):
+            assert rel_err(b[off:off + cnt], a[off:off + cnt]) <= 2e-3, (name, off)
