@@ -12,8 +12,17 @@
 //   * a thread owns one sample row: it reads its row of a layer's result from tensor memory, applies bias / ReLU / mask,
 //     rounds to fp16 and writes the row of the next operand tile; after the last layer it holds the 32 encoding gradients
 //     of its sample in registers and scatters them into the hash-table gradient without a round trip through memory.
-// One elected thread issues the MMAs of a stage and commits them to an mbarrier; every wait is bounded.
+// One elected thread issues the MMAs of a stage and commits them to an mbarrier.
+//
+// The CTA is two warpgroups.  Warps 0-3 (thread = row) run the chain of layer GEMMs and epilogues above; that chain is a
+// sequence of dependent stages, each waiting on the tensor core, so its warps are mostly asleep.  Warps 4-7 do nothing but
+// the gradient scatter: they receive a tile's encoding gradients through a double-buffered shared-memory hand-over and
+// issue its reductions while warps 0-3 are already on the next tile.  The scatter's index arithmetic and its L1TEX
+// traffic thus run underneath the tensor-core chain instead of after it.  (A second scatter warpgroup, with the
+// registers split by setmaxnreg, was measured and does not help: the scatter's own L2 reduction rate is the bound by then.)
+// Every wait - MMA barrier, hand-over full / empty - is bounded.
 #include <atomic>
+#include <type_traits>
 
 #include "hashgrid_core.cuh"
 #include "field_backward_tc.cuh"
@@ -25,7 +34,9 @@ extern std::atomic<uint64_t> g_launch_count;
 namespace tc {
 
 constexpr int ROWS = 128;      // rows of a tile = TMEM lanes = threads of the CTA
-constexpr int THREADS = 128;
+constexpr int SCATTER_GROUPS = 1;  // warpgroups that only scatter; a row's levels are dealt round-robin to them
+constexpr int THREADS = 128 * (1 + SCATTER_GROUPS);  // warps 0-3: GEMM chain (thread = row); the rest: gradient scatter
+constexpr int CHAIN_THREADS = 128;
 
 // ---- shared-memory map (bytes); every tile is [rows][cols] fp16 in core-matrix order --------------------------
 __host__ __device__ constexpr uint32_t tile_bytes(int rows, int cols) { return (uint32_t)rows * cols * 2; }
@@ -47,7 +58,8 @@ constexpr uint32_t OFF_B = OFF_A + tile_bytes(ROWS, 64);          // colour hidd
 constexpr uint32_t OFF_C = OFF_B + tile_bytes(ROWS, 64);          // colour hidden 2, later its gradient [128][64]
 constexpr uint32_t OFF_Z = OFF_C + tile_bytes(ROWS, 64);          // 16-wide gradients: colour output, then density output [128][16]
 constexpr uint32_t OFF_BIAS = OFF_Z + tile_bytes(ROWS, 16);       // fp32 biases: density 64 + 16, colour 64 + 64 + 8
-constexpr uint32_t SMEM_BYTES = OFF_BIAS + (64 + 16 + 64 + 64 + 8) * 4;
+constexpr uint32_t OFF_X = OFF_BIAS + (64 + 16 + 64 + 64 + 8) * 4;   // hand-over: 2 buffers x [16 levels][128 rows] fp16 pairs
+constexpr uint32_t SMEM_BYTES = OFF_X + 2 * 16 * ROWS * 4;
 
 // ---- tensor-memory map (32-bit columns) ----------------------------------------------------------------------
 constexpr uint32_t COL_WORK = 0;      // result of the current layer GEMM, up to 64 columns, 128 lanes
@@ -198,23 +210,31 @@ __device__ __forceinline__ float clamp_half_range(float v) {
 }
 
 // All threads: make this thread's shared-memory writes visible to the tensor core, order its tensor-memory reads, meet.
+__device__ __forceinline__ void chain_barrier() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 __device__ __forceinline__ void stage_sync() {
     proxy_fence();
     tc_fence_before();
-    __syncthreads();
+    chain_barrier();
     tc_fence_after();
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __grid_constant__ GridParams gp, const BackwardArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t mbar;
+    __shared__ __align__(8) uint64_t mbar;         // MMAs of the current stage done
+    __shared__ __align__(8) uint64_t x_full[2];    // hand-over buffer written by the 128 chain threads
+    __shared__ __align__(8) uint64_t x_empty[2];   // ... read by the 128 scatter threads
     __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t sbase = smem_u32(smem);
     float* sBias = reinterpret_cast<float*>(smem + OFF_BIAS);
     const float* bD0 = sBias, *bD1 = sBias + 64, *bC0 = sBias + 80, *bC1 = sBias + 144;
 
-    // ---- one-time set-up: weights and the ones tile in core-matrix order, biases, tensor memory, barrier ----------
+    // ---- one-time set-up (all 256 threads): weights and the ones tile in core-matrix order, biases, tensor memory, barriers
     auto stage_weights = [&](uint32_t off, const __half* W, int rows_valid, int rows, int cols) {
         const int cpr = cols >> 3;
         for (int c = tid; c < rows * cpr; c += THREADS) {
@@ -230,7 +250,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
     cp_async_commit();
     for (int i = tid; i < 80; i += THREADS) sBias[i] = a.bd[i];
     for (int i = tid; i < 136; i += THREADS) sBias[80 + i] = a.bc[i];
-    {
+    if (tid < ROWS) {
         const uint32_t one2 = pack_half2(1.0f, 1.0f);
         *reinterpret_cast<uint4*>(smem + OFF_ONES + core_off(tid, 0, 8)) = make_uint4(one2, one2, one2, one2);
     }
@@ -240,284 +260,332 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
     }
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&mbar)), "r"(1u) : "memory");
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&x_full[b])), "r"((uint32_t)CHAIN_THREADS) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&x_empty[b])), "r"((uint32_t)(THREADS - CHAIN_THREADS)) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        abort_flag_s = 0;
     }
     cp_async_wait_all();
-    stage_sync();
+    proxy_fence();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
     const uint32_t tmem = tmem_base_s;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
-    uint32_t phase = 0;
-    bool ok = true;
-    bool first_tile = true;
-    float db_c2 = 0.f, db_d1 = 0.f;  // lane j of every warp: partial bias gradient of output j (colour 8, density 16)
-
-    // wait for the MMAs committed last; uniform verdict over the CTA
-    auto await = [&]() -> bool {
-        bool got = mbar_wait(&mbar, phase & 1);
-        phase++;
-        got = __syncthreads_and(got);
-        tc_fence_after();
-        return got;
-    };
-
     const int64_t ntiles = (a.n + ROWS - 1) / ROWS;
-    for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int64_t row_base = tile * ROWS;
-        const int64_t row = row_base + tid;
-        const bool has = row < a.n;
-        // ---- stage 0: encoding tile and colour gradient (zero rows past n; gradient columns 8..15 zero) -------------
-        for (int c = tid; c < ROWS * 4; c += THREADS) {
-            const int r = c >> 2, c8 = c & 3;
-            const bool v = row_base + r < a.n;
-            cp_async16(smem + OFF_E + core_off(r, c8 * 8, 32), v ? (const void*)(a.enc + (row_base + r) * 32 + c8 * 8) : (const void*)a.enc, v);
-        }
-        cp_async16(smem + OFF_Z + core_off(tid, 0, 16), has ? (const void*)(a.dcolor + row * 8) : (const void*)a.dcolor, has);
-        *reinterpret_cast<uint4*>(smem + OFF_Z + core_off(tid, 8, 16)) = make_uint4(0u, 0u, 0u, 0u);
-        cp_async_commit();
-        // direction of this row's ray, for the SH half of the colour input
-        float sh[16];
-        {
-            int64_t r = has ? row : a.n - 1;
-            int64_t ray = a.ray_idx ? (int64_t)a.ray_idx[r + a.ray_idx_offset] : r;
-            const float* dp = a.dirs3 + 3 * ray;
-            sh16(dp[0], dp[1], dp[2], sh);
-        }
-        cp_async_wait_all();
-        stage_sync();
+    bool ok = true;
 
-        // ---- stage 1: density hidden = relu(E Wd0^T + b) -> tile A ----------------------------------------------------
-        if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_E, sbase + OFF_WD0, 32, 64); umma_commit(&mbar); }
-        if (!(ok = await())) break;
+    if (warp >= 4) {
+        // ================= scatter warpgroup: thread = row of the tile handed over =====================================
+        if constexpr (SCATTER_GROUPS > 1) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n");
+        if (a.table_grads != nullptr) {
+            const int r = (tid - CHAIN_THREADS) & (ROWS - 1), group = (tid - CHAIN_THREADS) >> 7;
+            int it = 0;
+            for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, it++) {
+                const int buf = it & 1, use = it >> 1;
+                const bool got = __all_sync(0xffffffffu, mbar_wait(&x_full[buf], use & 1));
+                if (!got) { ok = false; break; }   // the chain gave up (or never came): leave, every wait here is bounded
+                const uint32_t* x = reinterpret_cast<const uint32_t*>(smem + OFF_X) + buf * 16 * ROWS;
+                uint32_t pk[16];
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v[32];
-            tmem_ld32(lane_base + COL_WORK + 32 * h, v);
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i] + bD0[32 * h + i], 0.f);
-#pragma unroll
-            for (int c = 0; c < 4; c++) store_chunk(smem + OFF_A, tid, 4 * h + c, 64, v + 8 * c);
-        }
-        stage_sync();
-
-        // ---- stage 2: 16 logits = A Wd1^T + b; clamp; with the SH -> colour input tile ---------------------------------
-        if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_A, sbase + OFF_WD1, 64, 16); umma_commit(&mbar); }
-        if (!(ok = await())) break;
-        {
-            float v[16];
-            tmem_ld16(lane_base + COL_WORK, v);
-#pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = clamp_logit(v[i] + bD1[i]);
-            store_chunk(smem + OFF_CI, tid, 0, 32, v);
-            store_chunk(smem + OFF_CI, tid, 1, 32, v + 8);
-            store_chunk(smem + OFF_CI, tid, 2, 32, sh);
-            store_chunk(smem + OFF_CI, tid, 3, 32, sh + 8);
-        }
-        stage_sync();
-
-        // ---- stage 3: colour hidden 1 = relu(CI Wc0^T + b) -> tile B -----------------------------------------------------
-        if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_CI, sbase + OFF_WC0, 32, 64); umma_commit(&mbar); }
-        if (!(ok = await())) break;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v[32];
-            tmem_ld32(lane_base + COL_WORK + 32 * h, v);
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i] + bC0[32 * h + i], 0.f);
-#pragma unroll
-            for (int c = 0; c < 4; c++) store_chunk(smem + OFF_B, tid, 4 * h + c, 64, v + 8 * c);
-        }
-        stage_sync();
-
-        // ---- stage 4: colour hidden 2 = relu(B Wc1^T + b) -> tile C ------------------------------------------------------
-        if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_B, sbase + OFF_WC1, 64, 64); umma_commit(&mbar); }
-        if (!(ok = await())) break;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v[32];
-            tmem_ld32(lane_base + COL_WORK + 32 * h, v);
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i] + bC1[32 * h + i], 0.f);
-#pragma unroll
-            for (int c = 0; c < 4; c++) store_chunk(smem + OFF_C, tid, 4 * h + c, 64, v + 8 * c);
-        }
-        // bias gradient of the colour output layer: column sums of this tile's colour gradient (8 valid columns)
-        {
-            const uint4 q = load_chunk(smem + OFF_Z, tid, 0, 16);
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-            float g8[8];
-#pragma unroll
-            for (int i = 0; i < 4; i++) { const float2 f = unpack_half2(w[i]); g8[2 * i] = f.x; g8[2 * i + 1] = f.y; }
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                float s = g8[j];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == j) db_c2 += s;
-            }
-        }
-        stage_sync();
-
-        // ---- stage 5: colour layer 2 backward: dW2^T += C^T Z ; dA = Z Wc2, masked by C > 0 -> tile C (in place) --------
-        if (tid == 0) {
-            gemm_outer(tmem + COL_DWC2T, sbase + OFF_C, 64, sbase + OFF_Z, 16, 16, !first_tile);
-            gemm_dinput(tmem + COL_WORK, sbase + OFF_Z, 16, sbase + OFF_WC2, 64, 64);
-            umma_commit(&mbar);
-        }
-        if (!(ok = await())) break;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v[32];
-            tmem_ld32(lane_base + COL_WORK + 32 * h, v);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                unsigned char* p = smem + OFF_C + core_off(tid, (4 * h + c) * 8, 64);
-                *reinterpret_cast<uint4*>(p) = masked_chunk(v + 8 * c, *reinterpret_cast<const uint4*>(p));
-            }
-        }
-        stage_sync();
-
-        // ---- stage 6: colour layer 1 backward: dW1 += C^T B ; db1 += C^T 1 ; dA = C Wc1, masked by B > 0 -> tile B --------
-        if (tid == 0) {
-            gemm_outer(tmem + COL_DWC1, sbase + OFF_C, 64, sbase + OFF_B, 64, 64, !first_tile);
-            gemm_outer(tmem + COL_DBC1, sbase + OFF_C, 64, sbase + OFF_ONES, 8, 8, !first_tile);
-            gemm_dinput(tmem + COL_WORK, sbase + OFF_C, 64, sbase + OFF_WC1, 64, 64);
-            umma_commit(&mbar);
-        }
-        if (!(ok = await())) break;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v[32];
-            tmem_ld32(lane_base + COL_WORK + 32 * h, v);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                unsigned char* p = smem + OFF_B + core_off(tid, (4 * h + c) * 8, 64);
-                *reinterpret_cast<uint4*>(p) = masked_chunk(v + 8 * c, *reinterpret_cast<const uint4*>(p));
-            }
-        }
-        stage_sync();
-
-        // ---- stage 7: colour layer 0 backward: dW0 += B^T CI ; db0 += B^T 1 ; gradient of the 16 density outputs ---------
-        if (tid == 0) {
-            gemm_outer(tmem + COL_DWC0, sbase + OFF_B, 64, sbase + OFF_CI, 32, 32, !first_tile);
-            gemm_outer(tmem + COL_DBC0, sbase + OFF_B, 64, sbase + OFF_ONES, 8, 8, !first_tile);
-            gemm_dinput(tmem + COL_WORK, sbase + OFF_B, 64, sbase + OFF_WC0, 32, 16);
-            umma_commit(&mbar);
-        }
-        if (!(ok = await())) break;
-        {
-            float v[16];
-            tmem_ld16(lane_base + COL_WORK, v);
-            // compute_density_grad (modules/NeRF/otherKernels.cu:497-562): fp16 gradient, + dL/dsigma on logit 0, clamp, NaN -> 0
-            const float ds = (has && a.dsigma != nullptr) ? a.dsigma[row] : 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = clamp_half_range(__half2float(__float2half_rn(v[i])) + (i == 0 ? ds : 0.f));
-            store_chunk(smem + OFF_Z, tid, 0, 16, v);
-            store_chunk(smem + OFF_Z, tid, 1, 16, v + 8);
-            // bias gradient of the density output layer: column sums of the fp16 values just written
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                float s = __half2float(__float2half_rn(v[j]));
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == j) db_d1 += s;
-            }
-        }
-        stage_sync();
-
-        // ---- stage 8: density layer 1 backward: dW1^T += A^T Z ; dA = Z Wd1, masked by A > 0 -> tile A ---------------------
-        if (tid == 0) {
-            gemm_outer(tmem + COL_DWD1T, sbase + OFF_A, 64, sbase + OFF_Z, 16, 16, !first_tile);
-            gemm_dinput(tmem + COL_WORK, sbase + OFF_Z, 16, sbase + OFF_WD1, 64, 64);
-            umma_commit(&mbar);
-        }
-        if (!(ok = await())) break;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v[32];
-            tmem_ld32(lane_base + COL_WORK + 32 * h, v);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                unsigned char* p = smem + OFF_A + core_off(tid, (4 * h + c) * 8, 64);
-                *reinterpret_cast<uint4*>(p) = masked_chunk(v + 8 * c, *reinterpret_cast<const uint4*>(p));
-            }
-        }
-        stage_sync();
-
-        // ---- stage 9: density layer 0 backward: dW0 += A^T E ; db0 += A^T 1 ; dL/d(encoding) = A Wd0 -------------------------
-        if (tid == 0) {
-            gemm_outer(tmem + COL_DWD0, sbase + OFF_A, 64, sbase + OFF_E, 32, 32, !first_tile);
-            gemm_outer(tmem + COL_DBD0, sbase + OFF_A, 64, sbase + OFF_ONES, 8, 8, !first_tile);
-            gemm_dinput(tmem + COL_WORK, sbase + OFF_A, 64, sbase + OFF_WD0, 32, 32);
-            umma_commit(&mbar);
-        }
-        if (!(ok = await())) break;
-        {
-            float v[32];
-            tmem_ld32(lane_base + COL_WORK, v);
-            uint32_t pk[16];  // the sample's 16 feature-pair gradients, fp16 as the reference rounds them
-#pragma unroll
-            for (int l = 0; l < 16; l++) pk[l] = pack_half2(v[2 * l], v[2 * l + 1]);
-            if (has && a.denc_cols > 0) {
-                uint2* dst = reinterpret_cast<uint2*>(a.denc + row * a.denc_cols);
-#pragma unroll
-                for (int q = 0; q < 8; q++)
-                    if (4 * q < a.denc_cols) dst[q] = make_uint2(pk[2 * q], pk[2 * q + 1]);
-            }
-            if (a.table_grads != nullptr) {
-                // the scatter, straight from registers: a warp is 32 consecutive samples working on one level at a time
+                for (int l = 0; l < 16; l++) pk[l] = x[l * ROWS + r];
+                mbar_arrive(&x_empty[buf]);
+                const int64_t row = tile * ROWS + r;
+                const bool has = row < a.n;
                 float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (has) p = ld_nc_f4(a.pos4 + row * 4);
+                // a warp is 32 consecutive samples working on one level at a time
 #pragma unroll
                 for (int l = 0; l < 16; l++)
-                    if (l >= a.scatter_begin) scatter_level_warp(gp, l, p.x, p.y, p.z, unpack_half2(pk[l]), has, a.table_grads, lane);
+                    if (l >= a.scatter_begin && (l % SCATTER_GROUPS) == group)
+                        scatter_level_warp(gp, l, p.x, p.y, p.z, unpack_half2(pk[l]), has, a.table_grads, lane);
             }
         }
-        first_tile = false;
-        // the next tile's stage 0 overwrites E and Z: every MMA that read them has completed (awaited above), and all
-        // threads have finished reading tensor memory before the next MMA is issued
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
-    }
+    } else {
+        if constexpr (SCATTER_GROUPS > 1) asm volatile("setmaxnreg.inc.sync.aligned.u32 112;\n");
+        // ================= chain warpgroup: thread = row = tensor-memory lane ============================================
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+        uint32_t phase = 0;
+        bool first_tile = true;
+        int it = 0;
+        float db_c2 = 0.f, db_d1 = 0.f;  // lane j of every warp: partial bias gradient of output j (colour 8, density 16)
 
-    // ---- flush: accumulators of this CTA -> global (fp32 reductions), once -------------------------------------------------
-    if (ok && !first_tile) {
-        // a 64-row accumulator keeps row m in lane (m % 16) of warp (m / 16): lanes 0..15 of every warp hold rows
-        const int m = 16 * warp + lane;
-        const bool holds = lane < 16;
-        float v[32];
+        // wait for the MMAs committed last; uniform verdict over the warpgroup
+        auto await = [&]() -> bool {
+            if (!mbar_wait(&mbar, phase & 1)) *abort_flag = 1;
+            phase++;
+            chain_barrier();
+            tc_fence_after();
+            return *abort_flag == 0;
+        };
+
+        for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, it++) {
+            const int64_t row_base = tile * ROWS;
+            const int64_t row = row_base + tid;
+            const bool has = row < a.n;
+            // ---- stage 0: encoding tile and colour gradient (zero rows past n; gradient columns 8..15 zero) -------------
+            for (int c = tid; c < ROWS * 4; c += CHAIN_THREADS) {
+                const int r = c >> 2, c8 = c & 3;
+                const bool v = row_base + r < a.n;
+                cp_async16(smem + OFF_E + core_off(r, c8 * 8, 32), v ? (const void*)(a.enc + (row_base + r) * 32 + c8 * 8) : (const void*)a.enc, v);
+            }
+            cp_async16(smem + OFF_Z + core_off(tid, 0, 16), has ? (const void*)(a.dcolor + row * 8) : (const void*)a.dcolor, has);
+            *reinterpret_cast<uint4*>(smem + OFF_Z + core_off(tid, 8, 16)) = make_uint4(0u, 0u, 0u, 0u);
+            cp_async_commit();
+            // direction of this row's ray, for the SH half of the colour input
+            float sh[16];
+            {
+                int64_t r = has ? row : a.n - 1;
+                int64_t ray = a.ray_idx ? (int64_t)a.ray_idx[r + a.ray_idx_offset] : r;
+                const float* dp = a.dirs3 + 3 * ray;
+                sh16(dp[0], dp[1], dp[2], sh);
+            }
+            cp_async_wait_all();
+            stage_sync();
+
+            // ---- stage 1: density hidden = relu(E Wd0^T + b) -> tile A ----------------------------------------------------
+            if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_E, sbase + OFF_WD0, 32, 64); umma_commit(&mbar); }
+            if (!(ok = await())) break;
 #pragma unroll
-        for (int h = 0; h < 2; h++) {  // colour layer 1: [64 out][64 in]
-            tmem_ld32(lane_base + COL_DWC1 + 32 * h, v);
+            for (int h = 0; h < 2; h++) {
+                float v[32];
+                tmem_ld32(lane_base + COL_WORK + 32 * h, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i] + bD0[32 * h + i], 0.f);
+#pragma unroll
+                for (int c = 0; c < 4; c++) store_chunk(smem + OFF_A, tid, 4 * h + c, 64, v + 8 * c);
+            }
+            stage_sync();
+
+            // ---- stage 2: 16 logits = A Wd1^T + b; clamp; with the SH -> colour input tile ---------------------------------
+            if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_A, sbase + OFF_WD1, 64, 16); umma_commit(&mbar); }
+            if (!(ok = await())) break;
+            {
+                float v[16];
+                tmem_ld16(lane_base + COL_WORK, v);
+#pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = clamp_logit(v[i] + bD1[i]);
+                store_chunk(smem + OFF_CI, tid, 0, 32, v);
+                store_chunk(smem + OFF_CI, tid, 1, 32, v + 8);
+                store_chunk(smem + OFF_CI, tid, 2, 32, sh);
+                store_chunk(smem + OFF_CI, tid, 3, 32, sh + 8);
+            }
+            stage_sync();
+
+            // ---- stage 3: colour hidden 1 = relu(CI Wc0^T + b) -> tile B -----------------------------------------------------
+            if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_CI, sbase + OFF_WC0, 32, 64); umma_commit(&mbar); }
+            if (!(ok = await())) break;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float v[32];
+                tmem_ld32(lane_base + COL_WORK + 32 * h, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i] + bC0[32 * h + i], 0.f);
+#pragma unroll
+                for (int c = 0; c < 4; c++) store_chunk(smem + OFF_B, tid, 4 * h + c, 64, v + 8 * c);
+            }
+            stage_sync();
+
+            // ---- stage 4: colour hidden 2 = relu(B Wc1^T + b) -> tile C ------------------------------------------------------
+            if (tid == 0) { gemm_layer(tmem + COL_WORK, sbase + OFF_B, sbase + OFF_WC1, 64, 64); umma_commit(&mbar); }
+            if (!(ok = await())) break;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float v[32];
+                tmem_ld32(lane_base + COL_WORK + 32 * h, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i] + bC1[32 * h + i], 0.f);
+#pragma unroll
+                for (int c = 0; c < 4; c++) store_chunk(smem + OFF_C, tid, 4 * h + c, 64, v + 8 * c);
+            }
+            // bias gradient of the colour output layer: column sums of this tile's colour gradient (8 valid columns)
+            {
+                const uint4 q = load_chunk(smem + OFF_Z, tid, 0, 16);
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                float g8[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) { const float2 f = unpack_half2(w[i]); g8[2 * i] = f.x; g8[2 * i + 1] = f.y; }
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float s = g8[j];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                    if (lane == j) db_c2 += s;
+                }
+            }
+            stage_sync();
+
+            // ---- stage 5: colour layer 2 backward: dW2^T += C^T Z ; dA = Z Wc2, masked by C > 0 -> tile C (in place) --------
+            if (tid == 0) {
+                gemm_outer(tmem + COL_DWC2T, sbase + OFF_C, 64, sbase + OFF_Z, 16, 16, !first_tile);
+                gemm_dinput(tmem + COL_WORK, sbase + OFF_Z, 16, sbase + OFF_WC2, 64, 64);
+                umma_commit(&mbar);
+            }
+            if (!(ok = await())) break;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float v[32];
+                tmem_ld32(lane_base + COL_WORK + 32 * h, v);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    unsigned char* p = smem + OFF_C + core_off(tid, (4 * h + c) * 8, 64);
+                    *reinterpret_cast<uint4*>(p) = masked_chunk(v + 8 * c, *reinterpret_cast<const uint4*>(p));
+                }
+            }
+            stage_sync();
+
+            // ---- stage 6: colour layer 1 backward: dW1 += C^T B ; db1 += C^T 1 ; dA = C Wc1, masked by B > 0 -> tile B --------
+            if (tid == 0) {
+                gemm_outer(tmem + COL_DWC1, sbase + OFF_C, 64, sbase + OFF_B, 64, 64, !first_tile);
+                gemm_outer(tmem + COL_DBC1, sbase + OFF_C, 64, sbase + OFF_ONES, 8, 8, !first_tile);
+                gemm_dinput(tmem + COL_WORK, sbase + OFF_C, 64, sbase + OFF_WC1, 64, 64);
+                umma_commit(&mbar);
+            }
+            if (!(ok = await())) break;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float v[32];
+                tmem_ld32(lane_base + COL_WORK + 32 * h, v);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    unsigned char* p = smem + OFF_B + core_off(tid, (4 * h + c) * 8, 64);
+                    *reinterpret_cast<uint4*>(p) = masked_chunk(v + 8 * c, *reinterpret_cast<const uint4*>(p));
+                }
+            }
+            stage_sync();
+
+            // ---- stage 7: colour layer 0 backward: dW0 += B^T CI ; db0 += B^T 1 ; gradient of the 16 density outputs ---------
+            if (tid == 0) {
+                gemm_outer(tmem + COL_DWC0, sbase + OFF_B, 64, sbase + OFF_CI, 32, 32, !first_tile);
+                gemm_outer(tmem + COL_DBC0, sbase + OFF_B, 64, sbase + OFF_ONES, 8, 8, !first_tile);
+                gemm_dinput(tmem + COL_WORK, sbase + OFF_B, 64, sbase + OFF_WC0, 32, 16);
+                umma_commit(&mbar);
+            }
+            if (!(ok = await())) break;
+            {
+                float v[16];
+                tmem_ld16(lane_base + COL_WORK, v);
+                // compute_density_grad (modules/NeRF/otherKernels.cu:497-562): fp16 gradient, + dL/dsigma on logit 0, clamp, NaN -> 0
+                const float ds = (has && a.dsigma != nullptr) ? a.dsigma[row] : 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = clamp_half_range(__half2float(__float2half_rn(v[i])) + (i == 0 ? ds : 0.f));
+                store_chunk(smem + OFF_Z, tid, 0, 16, v);
+                store_chunk(smem + OFF_Z, tid, 1, 16, v + 8);
+                // bias gradient of the density output layer: column sums of the fp16 values just written
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    float s = __half2float(__float2half_rn(v[j]));
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                    if (lane == j) db_d1 += s;
+                }
+            }
+            stage_sync();
+
+            // ---- stage 8: density layer 1 backward: dW1^T += A^T Z ; dA = Z Wd1, masked by A > 0 -> tile A ---------------------
+            if (tid == 0) {
+                gemm_outer(tmem + COL_DWD1T, sbase + OFF_A, 64, sbase + OFF_Z, 16, 16, !first_tile);
+                gemm_dinput(tmem + COL_WORK, sbase + OFF_Z, 16, sbase + OFF_WD1, 64, 64);
+                umma_commit(&mbar);
+            }
+            if (!(ok = await())) break;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float v[32];
+                tmem_ld32(lane_base + COL_WORK + 32 * h, v);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    unsigned char* p = smem + OFF_A + core_off(tid, (4 * h + c) * 8, 64);
+                    *reinterpret_cast<uint4*>(p) = masked_chunk(v + 8 * c, *reinterpret_cast<const uint4*>(p));
+                }
+            }
+            stage_sync();
+
+            // ---- stage 9: density layer 0 backward: dW0 += A^T E ; db0 += A^T 1 ; dL/d(encoding) = A Wd0 -------------------------
+            if (tid == 0) {
+                gemm_outer(tmem + COL_DWD0, sbase + OFF_A, 64, sbase + OFF_E, 32, 32, !first_tile);
+                gemm_outer(tmem + COL_DBD0, sbase + OFF_A, 64, sbase + OFF_ONES, 8, 8, !first_tile);
+                gemm_dinput(tmem + COL_WORK, sbase + OFF_A, 64, sbase + OFF_WD0, 32, 32);
+                umma_commit(&mbar);
+            }
+            if (!(ok = await())) break;
+            {
+                float v[32];
+                tmem_ld32(lane_base + COL_WORK, v);
+                uint32_t pk[16];  // the sample's 16 feature-pair gradients, fp16 as the reference rounds them
+#pragma unroll
+                for (int l = 0; l < 16; l++) pk[l] = pack_half2(v[2 * l], v[2 * l + 1]);
+                if (has && a.denc_cols > 0) {
+                    uint2* dst = reinterpret_cast<uint2*>(a.denc + row * a.denc_cols);
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        if (4 * q < a.denc_cols) dst[q] = make_uint2(pk[2 * q], pk[2 * q + 1]);
+                }
+                if (a.table_grads != nullptr) {
+                    // hand the tile's gradients to the scatter warps: buffer `it & 1`, free again once they have read it
+                    const int buf = it & 1, use = it >> 1;
+                    bool free_now = true;
+                    if (use > 0) free_now = mbar_wait(&x_empty[buf], (use - 1) & 1);
+                    if (free_now) {
+                        uint32_t* x = reinterpret_cast<uint32_t*>(smem + OFF_X) + buf * 16 * ROWS;
+#pragma unroll
+                        for (int l = 0; l < 16; l++) x[l * ROWS + tid] = pk[l];
+                        mbar_arrive(&x_full[buf]);
+                    } else {
+                        *abort_flag = 1;
+                    }
+                }
+            }
+            first_tile = false;
+            // the next tile's stage 0 overwrites E and Z: every MMA that read them has completed (awaited above), and all
+            // threads have finished reading tensor memory before the next MMA is issued
+            tc_fence_before();
+            chain_barrier();
+            tc_fence_after();
+            if (*abort_flag != 0) ok = false;
+        }
+
+        // ---- flush: accumulators of this CTA -> global (fp32 reductions), once ---------------------------------------------
+        if (ok && !first_tile) {
+            // a 64-row accumulator keeps row m in lane (m % 16) of warp (m / 16): lanes 0..15 of every warp hold rows
+            const int m = 16 * warp + lane;
+            const bool holds = lane < 16;
+            float v[32];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {  // colour layer 1: [64 out][64 in]
+                tmem_ld32(lane_base + COL_DWC1 + 32 * h, v);
+                if (holds)
+#pragma unroll
+                    for (int q = 0; q < 8; q++) red_add_v4(a.dWc + 64 * 32 + m * 64 + 32 * h + 4 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            }
+            tmem_ld32(lane_base + COL_DWC0, v);  // colour layer 0: [64 out][32 in]
             if (holds)
 #pragma unroll
-                for (int q = 0; q < 8; q++) red_add_v4(a.dWc + 64 * 32 + m * 64 + 32 * h + 4 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                for (int q = 0; q < 8; q++) red_add_v4(a.dWc + m * 32 + 4 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            tmem_ld32(lane_base + COL_DWD0, v);  // density layer 0: [64 out][32 in]
+            if (holds)
+#pragma unroll
+                for (int q = 0; q < 8; q++) red_add_v4(a.dWd + m * 32 + 4 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            tmem_ld32(lane_base + COL_DWC2T, v);  // columns 0-15: colour layer 2 transposed [64 in][16 out], 16-31: density layer 1 transposed
+            if (holds) {
+#pragma unroll
+                for (int o = 0; o < 8; o++) red_add(a.dWc + 64 * 32 + 64 * 64 + o * 64 + m, v[o]);
+#pragma unroll
+                for (int o = 0; o < 16; o++) red_add(a.dWd + 64 * 32 + o * 64 + m, v[16 + o]);
+            }
+            tmem_ld32(lane_base + COL_DBC1, v);  // columns 0, 8, 16: bias gradients of colour 1, colour 0, density 0
+            if (holds) {
+                red_add(a.dbc + 64 + m, v[0]);
+                red_add(a.dbc + m, v[8]);
+                red_add(a.dbd + m, v[16]);
+            }
+            if (lane < 8) red_add(a.dbc + 128 + lane, db_c2);
+            if (lane < 16) red_add(a.dbd + 64 + lane, db_d1);
         }
-        tmem_ld32(lane_base + COL_DWC0, v);  // colour layer 0: [64 out][32 in]
-        if (holds)
-#pragma unroll
-            for (int q = 0; q < 8; q++) red_add_v4(a.dWc + m * 32 + 4 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        tmem_ld32(lane_base + COL_DWD0, v);  // density layer 0: [64 out][32 in]
-        if (holds)
-#pragma unroll
-            for (int q = 0; q < 8; q++) red_add_v4(a.dWd + m * 32 + 4 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        tmem_ld32(lane_base + COL_DWC2T, v);  // columns 0-15: colour layer 2 transposed [64 in][16 out], 16-31: density layer 1 transposed
-        if (holds) {
-#pragma unroll
-            for (int o = 0; o < 8; o++) red_add(a.dWc + 64 * 32 + 64 * 64 + o * 64 + m, v[o]);
-#pragma unroll
-            for (int o = 0; o < 16; o++) red_add(a.dWd + 64 * 32 + o * 64 + m, v[16 + o]);
-        }
-        tmem_ld32(lane_base + COL_DBC1, v);  // columns 0, 8, 16: bias gradients of colour 1, colour 0, density 0
-        if (holds) {
-            red_add(a.dbc + 64 + m, v[0]);
-            red_add(a.dbc + m, v[8]);
-            red_add(a.dbd + m, v[16]);
-        }
-        if (lane < 8) red_add(a.dbc + 128 + lane, db_c2);
-        if (lane < 16) red_add(a.dbd + 64 + lane, db_d1);
     }
-    if (!ok && tid == 0 && a.error_flag != nullptr) atomicExch(a.error_flag, 1);
+    if (!ok && lane == 0 && a.error_flag != nullptr) atomicExch(a.error_flag, 1);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -528,7 +596,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
 
 namespace nb {
 
-std::atomic<int> g_backward_tc{0};   // nb_set_tuning("backward_tc", ...)
+std::atomic<int> g_backward_tc{1};   // nb_set_tuning("backward_tc", ...)
 static __device__ int g_tc_error_flag;
 
 // Host side: launched by nb_field_backward when the tensor-memory path is selected.

@@ -205,8 +205,8 @@ int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const
  *     reductions drain through L2 underneath the tensor work); d_denc_h is then scratch of at least n * 8 bytes whose
  *     content is unspecified, grid and d_pos4 (float4 per sample) are required. */
 /* The backward kernel exists in two formulations with the same inputs, outputs and fp16 rounding points:
- * nb_set_tuning("backward_tc", 1) selects tcgen05.mma with accumulators in tensor memory, 0 mma.sync with register
- * accumulators.  nb_field_backward_tc_status() synchronises the device and reports (NB_ERR_CUDA) whether a bounded
+ * nb_set_tuning("backward_tc", 1) selects tcgen05.mma with accumulators in tensor memory (default), 0 mma.sync with
+ * register accumulators.  nb_field_backward_tc_status() synchronises the device and reports (NB_ERR_CUDA) whether a bounded
  * wait of the tensor-memory kernel ever ran out; it clears the flag. */
 int nb_field_backward_tc_status(void);
 int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
