@@ -580,7 +580,8 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
         gio.pos4 = d_pos4; gio.table_grads = d_table_grads; gio.scatter_begin = shared_levels;
         gio.denc_cols = 4 * shared_levels;   // only what the shared-memory scatter kernel below reads
     }
-    if (nb::g_backward_tc.load() != 0) {
+    const int tc_mode = nb::g_backward_tc.load();
+    if (tc_mode == 1 || (tc_mode == 2 && d_ray_indices == nullptr)) {
         // tensor-memory formulation (field_backward_tc.cu): same inputs, outputs and rounding points
         nb::tc::BackwardArgs ta{};
         ta.enc = gio.enc; ta.dcolor = gio.dcolor; ta.dsigma = gio.dsigma; ta.dirs3 = io.dirs3; ta.ray_idx = io.ray_idx;

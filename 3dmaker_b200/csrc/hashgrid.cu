@@ -103,7 +103,7 @@ struct ScatterTuning {
 };
 static ScatterTuning g_scatter_tuning;
 std::atomic<int> g_pair_ops{1};
-std::atomic<int> g_run_merge{1};
+std::atomic<int> g_run_merge{20};
 
 // Gradient scatter, one thread per (sample, level), level = level_base + blockIdx.y so that all CTAs resident at one
 // time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector reduction.

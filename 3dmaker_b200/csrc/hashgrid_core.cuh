@@ -14,7 +14,8 @@ extern std::atomic<int> g_run_merge;  // nb_set_tuning("scatter_run_merge", ...)
 
 struct GridParams {
     int L, T, dls;
-    int run_merge; // non-zero: the gradient scatter sums runs of consecutive samples in one cell before reducing
+    int run_merge; // > 0: the gradient scatter sums runs of consecutive samples in one cell before reducing, in warps that
+                   // have at most this many runs (merging costs about 300 instructions per warp and level)
     int pair_ops;  // non-zero: the two x-neighbours of a corner pair that share an aligned slot pair move as one access
     float scales[NB_MAX_LEVELS];   // forward (encode) resolutions
     float sscales[NB_MAX_LEVELS];  // resolutions of the gradient scatter
@@ -184,7 +185,7 @@ __device__ __forceinline__ void scatter_level_runs(const GridParams& gp, int lev
     float v[16];
 #pragma unroll
     for (int k = 0; k < 8; k++) { v[2 * k] = g.x * w[k]; v[2 * k + 1] = g.y * w[k]; }
-    if (!gp.run_merge || __popc(heads) > 20) {
+    if (__popc(heads) > gp.run_merge) {
         if (active) sink(c, v);
         return;
     }

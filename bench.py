@@ -714,6 +714,8 @@ def main():
     ap.add_argument("--workload", default="field", choices=["field", "scene", "render"],
                     help="field: the headline step on explicit samples (default, the driver's line); scene: full NeRF training step on the "
                          "analytic scene; render: 1920x1080 orbit frames, pixels sharded over the ranks")
+    ap.add_argument("--batch-log2", type=int, default=20, help="field workload: log2 of the samples per GPU and step (20 = the benchmark's; "
+                    "smaller values are for profiling small cases, their lines are not benchmark results)")
     ap.add_argument("--scene-warm", type=int, default=272, help="scene workload: untimed train_rays calls before the timed ones")
     ap.add_argument("--render-train-steps", type=int, default=400, help="render workload: optimizer steps the model is trained for first")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -725,6 +727,10 @@ def main():
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()
+    global BATCH, WORKLOAD
+    if args.batch_log2 != 20:
+        BATCH = 1 << args.batch_log2
+        WORKLOAD = WORKLOAD.replace("2^20 samples/GPU", "2^%d samples/GPU (NOT the benchmark size)" % args.batch_log2)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -120,7 +120,7 @@ int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d_pos4, cons
 
 /* A/B switches for benchmarking, in the spirit of the reference's TinyMLPHashGrid::setSplitScatter
  * (TinyMLPHashGrid.h:60-63).  Keys: "scatter_run_merge" (consecutive samples in one grid cell are summed inside the
- * warp before the reduction; default 1), "scatter_smem_levels" (dense levels below it that fit shared memory are
+ * warp before the reduction, in warps with at most this many runs; default 20, 0 = never), "scatter_smem_levels" (dense levels below it that fit shared memory are
  * accumulated per CTA; default 2), "scatter_level_begin" / "scatter_level_end" (restrict the scatter to a level range),
  * "pair_ops" (x-neighbour corners that share an aligned slot pair are gathered with one 8-byte load and scattered with
  * one 16-byte reduction; default 1).  Results do not depend on these beyond fp32 summation order of the scatter. */
@@ -205,8 +205,11 @@ int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const
  *     reductions drain through L2 underneath the tensor work); d_denc_h is then scratch of at least n * 8 bytes whose
  *     content is unspecified, grid and d_pos4 (float4 per sample) are required. */
 /* The backward kernel exists in two formulations with the same inputs, outputs and fp16 rounding points:
- * nb_set_tuning("backward_tc", 1) selects tcgen05.mma with accumulators in tensor memory (default), 0 mma.sync with
- * register accumulators.  nb_field_backward_tc_status() synchronises the device and reports (NB_ERR_CUDA) whether a bounded
+ * nb_set_tuning("backward_tc", 1) selects tcgen05.mma with accumulators in tensor memory, 0 mma.sync with register
+ * accumulators, 2 (default) picks by the sample order the call implies: d_ray_indices == NULL means explicit,
+ * unordered samples, where the scatter's reductions are the long pole and the tensor-memory kernel (its scatter on
+ * warps of their own) is faster (0.63 against 0.74 ms at 2^20 samples); ray-ordered samples from the marcher come with
+ * ray indices, merge into few reductions, and the register kernel is the faster one there (0.21 against 0.23 ms at 2^18).  nb_field_backward_tc_status() synchronises the device and reports (NB_ERR_CUDA) whether a bounded
  * wait of the tensor-memory kernel ever ran out; it clears the flag. */
 int nb_field_backward_tc_status(void);
 int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,

@@ -126,7 +126,7 @@ def test_fused_field_kernels_agree_with_the_kernel_sequence(cuda, nb, n):
                          logit=(tr.logit0 if tr.fused else tr.d_out[:, 0]).cpu().numpy(), d_enc=dev_half_bits(tr.d_enc), g=model.g.cpu().numpy().copy(),
                          loss=tr.loss.item())
     model.g.zero_()
-    nb.check(nb.load().nb_set_tuning(b"backward_tc", 1), "nb_set_tuning")
+    nb.check(nb.load().nb_set_tuning(b"backward_tc", 2), "nb_set_tuning")
     a = out["sequence"]
     H = model.hash_count
     for name in ("fused", "fused+scatter"):
@@ -212,7 +212,7 @@ def test_tensor_memory_backward_agrees_with_the_register_formulation(cuda, nb, n
             nb.check(lib.nb_field_backward_tc_status(), "tensor-memory backward status")
             out[name] = dict(d_enc=half_vals(dev_half_bits(tr.d_enc)), g=model.g.cpu().numpy().copy())
     finally:
-        nb.check(lib.nb_set_tuning(b"backward_tc", 1), "nb_set_tuning")
+        nb.check(lib.nb_set_tuning(b"backward_tc", 2), "nb_set_tuning")
         model.g.zero_()
     H = model.hash_count
     assert rel_err(out["tc"]["d_enc"], out["regs"]["d_enc"]) <= 2e-3

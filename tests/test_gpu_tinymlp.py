@@ -218,12 +218,12 @@ def test_scatter_of_ray_ordered_samples(cuda, nb, orc, n):
     out = {}
     lib = nb.load()
     for merge in (1, 0):
-        nb.check(lib.nb_set_tuning(b"scatter_run_merge", merge), "nb_set_tuning")
+        nb.check(lib.nb_set_tuning(b"scatter_run_merge", 32 if merge else 0), "nb_set_tuning")
         grads = torch.zeros(16 * T * 2, dtype=torch.float32, device="cuda")
         nb.check(lib.nb_hash_scatter_backward(ctypes.byref(d), up.f(pos), up.h(denc), n, nb.ptr(grads), nb.stream_ptr()), "nb_hash_scatter_backward")
         torch.cuda.synchronize()
         out[merge] = grads.cpu().numpy()
-    nb.check(lib.nb_set_tuning(b"scatter_run_merge", 1), "nb_set_tuning")
+    nb.check(lib.nb_set_tuning(b"scatter_run_merge", 20), "nb_set_tuning")
     ref = orc.scatter_backward(pos, denc, d.np_scatter_scales, T, d.dense_level_start)
     assert rel_err(out[1], ref) <= REL_MLP and rel_err(out[0], ref) <= REL_MLP
     assert rel_err(out[1], out[0]) <= 1e-5

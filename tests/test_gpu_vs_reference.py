@@ -252,22 +252,36 @@ def test_scene_engines_agree(cuda, nb, ref):
     R = 1 << 16
     depth = torch.full((R,), -1.0, device="cuda"); sig = torch.ones(R, device="cuda")
     st = nb.stream_ptr()
+    # a second instance of the reference on the same rays: its own run-to-run spread (fp32 atomics are unordered, and at a
+    # few hundred steps the PSNR still climbs 1 dB per 100 steps) is the yardstick the 0.2 dB bar is read against
+    rh2 = ref.lib().ref_nerf_create(ctypes.byref(opts), 0)
     it = 0
     while eng.steps.value < 300:
         o, d = syn.random_training_rays(torch, poses, R, 800, 800, 50.0, seed=500 + it)
         tgt = syn.ground_truth(torch, scene, o, d, bg)
         eng.train_rays(o, d, tgt)
-        ref.lib().ref_nerf_train(rh, nb.ptr(o), nb.ptr(d), nb.ptr(depth), nb.ptr(sig), nb.ptr(tgt), R, None, None, st)
+        for h in (rh, rh2):
+            ref.lib().ref_nerf_train(h, nb.ptr(o), nb.ptr(d), nb.ptr(depth), nb.ptr(sig), nb.ptr(tgt), R, None, None, st)
         it += 1
     torch.cuda.synchronize()
-    o, d = syn.frame_rays(torch, syn.orbit_c2w(33.0, 20.0, 1.5), 200, 200, 50.0)
-    gt = syn.ground_truth(torch, scene, o, d, bg)
-    img, r_img = torch.zeros_like(gt), torch.zeros_like(gt)
-    eng.render(o, d, img)
-    ref.lib().ref_nerf_render(rh, nb.ptr(o), nb.ptr(d), o.shape[0], nb.ptr(r_img), st)
-    torch.cuda.synchronize()
-    p, rp = syn.psnr(torch, img, gt), syn.psnr(torch, r_img, gt)
-    print("PSNR after ~300 steps: ours %.2f dB, reference %.2f dB" % (p, rp))
-    assert abs(p - rp) <= 0.2 or p > rp
+    ps = {"ours": [], "ref": [], "ref2": []}
+    for az, el in ((33.0, 20.0), (117.0, 20.0), (250.0, -30.0), (190.0, 45.0)):
+        o, d = syn.frame_rays(torch, syn.orbit_c2w(az, el, 1.5), 200, 200, 50.0)
+        gt = syn.ground_truth(torch, scene, o, d, bg)
+        img = torch.zeros_like(gt)
+        eng.render(o, d, img)
+        torch.cuda.synchronize()
+        ps["ours"].append(syn.psnr(torch, img, gt))
+        for key, h in (("ref", rh), ("ref2", rh2)):
+            r_img = torch.zeros_like(gt)
+            ref.lib().ref_nerf_render(h, nb.ptr(o), nb.ptr(d), o.shape[0], nb.ptr(r_img), st)
+            torch.cuda.synchronize()
+            ps[key].append(syn.psnr(torch, r_img, gt))
+    p, rp, rp2 = (float(np.mean(ps[k])) for k in ("ours", "ref", "ref2"))
+    spread = abs(rp - rp2)
+    print("PSNR after ~300 steps, mean of 4 views: ours %.2f dB, reference %.2f dB, reference again %.2f dB (its own spread %.2f dB)" % (p, rp, rp2, spread))
+    assert p > 30.0
+    assert abs(p - 0.5 * (rp + rp2)) <= 0.2 + spread or p > max(rp, rp2)
+    ref.lib().ref_nerf_destroy(rh2)
     ref.lib().ref_nerf_destroy(rh)
     eng.close()
