@@ -14,12 +14,14 @@
 //     of its sample in registers and scatters them into the hash-table gradient without a round trip through memory.
 // One elected thread issues the MMAs of a stage and commits them to an mbarrier.
 //
-// The CTA is three warpgroups.  Warps 0-3 (thread = row) run the chain of layer GEMMs and epilogues above; that chain is a
-// sequence of dependent stages, each waiting on the tensor core, so its warps are mostly asleep.  Warps 4-11 do nothing but
+// The CTA is two warpgroups.  Warps 0-3 (thread = row) run the chain of layer GEMMs and epilogues above; that chain is a
+// sequence of dependent stages, each waiting on the tensor core, so its warps are mostly asleep.  Warps 4-7 do nothing but
 // the gradient scatter: they receive a tile's encoding gradients through a double-buffered shared-memory hand-over and
 // issue its reductions while warps 0-3 are already on the next tile.  The scatter's index arithmetic and its L1TEX
-// traffic thus run underneath the tensor-core chain instead of after it.  Two scatter warpgroups (a row's levels dealt
-// alternately to them), registers split by setmaxnreg: 112 per thread for the chain, 64 for the scatter.
+// traffic thus run underneath the tensor-core chain instead of after it.  (SCATTER_GROUPS = 2 adds a second
+// scatter warpgroup, registers split by setmaxnreg; measured at 2^20 unordered samples it is slower, 0.654 against
+// 0.630 ms - the reductions' own rate binds by then - and on ray-ordered samples faster, 0.234 against 0.282 ms, where
+// the register kernel's 0.214 ms is what gets used anyway.)
 // Every wait - MMA barrier, hand-over full / empty - is bounded.
 #include <atomic>
 #include <type_traits>
@@ -34,7 +36,7 @@ extern std::atomic<uint64_t> g_launch_count;
 namespace tc {
 
 constexpr int ROWS = 128;      // rows of a tile = TMEM lanes = threads of the CTA
-constexpr int SCATTER_GROUPS = 2;  // warpgroups that only scatter; a row's levels are dealt round-robin to them
+constexpr int SCATTER_GROUPS = 1;  // warpgroups that only scatter; a row's levels are dealt round-robin to them
 constexpr int THREADS = 128 * (1 + SCATTER_GROUPS);  // warps 0-3: GEMM chain (thread = row); the rest: gradient scatter
 constexpr int CHAIN_THREADS = 128;
 
