@@ -171,6 +171,45 @@ class SampleTrainer:
                                        m.total, self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2),
                                        1.0 / self.loss_scale, 1, nb.stream_ptr(stream)), "nb_adam_step")
 
+    def optimizer_step_sharded(self, dist, stream=None):
+        """Data-parallel tail of a step with the hash table's optimizer state used shard-wise: reduce-scatter of the table
+        gradient (each rank receives the summed gradient of its 1/N slice), Adam on that slice only, all-gather of the
+        updated fp16 slice - the copy the forward reads.  Against allreduce + full Adam this moves 3/4 of the bytes over
+        NVLink (fp32 gradient one way, fp16 parameters back) and divides the Adam launch by N.  The small dense tail
+        (network weights and biases) is allreduced and updated by every rank.  Every rank ends with identical fp16
+        parameters; the fp32 master copy, m and v of a slice are current on its owner only (gather_master() collects them)."""
+        m = self.model
+        world, rank = dist.get_world_size(), dist.get_rank()
+        H = m.hash_count
+        if H % (4 * world) != 0:
+            raise nb.NerfB200Error("hash table size must be divisible by 4 x ranks")
+        shard = H // world
+        lo, hi = rank * shard, (rank + 1) * shard
+        if m.step_count < 50000:
+            m.step_count += 1
+        bc1 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta1), np.float32(m.step_count)))
+        bc2 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta2), np.float32(m.step_count)))
+        hyper = (self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2), 1.0 / self.loss_scale, 1, nb.stream_ptr(stream))
+        dist.reduce_scatter_tensor(m.g[lo:hi], m.g[:H], op=dist.ReduceOp.SUM)      # in place: the output is this rank's slice
+        dist.all_reduce(m.g[H:], op=dist.ReduceOp.SUM)
+        nb.check(self.lib.nb_adam_step(m.ptr("w", lo), m.ptr("w_h", lo), m.ptr("g", lo), m.ptr("m", lo), m.ptr("v", lo), shard, shard, *hyper),
+                 "nb_adam_step(table slice)")
+        nb.check(self.lib.nb_adam_step(m.ptr("w", H), m.ptr("w_h", H), m.ptr("g", H), m.ptr("m", H), m.ptr("v", H), 0, m.total - H, *hyper),
+                 "nb_adam_step(networks)")
+        # the other slices still hold this rank's unreduced gradient: clear them for the next step's accumulation
+        if lo > 0:
+            nb.check(self.lib.nb_zero_async(m.ptr("g", 0), lo * 4, nb.stream_ptr(stream)), "nb_zero_async")
+        if hi < H:
+            nb.check(self.lib.nb_zero_async(m.ptr("g", hi), (H - hi) * 4, nb.stream_ptr(stream)), "nb_zero_async")
+        dist.all_gather_into_tensor(m.w_h[:H], m.w_h[lo:hi])                        # in place as well
+
+    def gather_master(self, dist):
+        """After sharded steps: brings the fp32 master table of every slice to every rank (e.g. before saving)."""
+        m = self.model
+        world, rank = dist.get_world_size(), dist.get_rank()
+        shard = m.hash_count // world
+        dist.all_gather_into_tensor(m.w[:m.hash_count], m.w[rank * shard:(rank + 1) * shard])
+
     def optimizer_step_synced(self, dist, chunks=4, stream=None):
         """Data-parallel tail of a step: SUM-allreduce of the gradient arena and Adam, pipelined over `chunks` slices of
         the arena - the allreduce of slice c+1 (NCCL's stream) runs while Adam updates slice c, so only the first
@@ -198,7 +237,11 @@ class SampleTrainer:
         backward and Adam, or torch.distributed itself (initialised) for the pipelined allreduce + Adam."""
         self.forward_backward(n, stream)
         if grad_sync is not None and hasattr(grad_sync, "all_reduce"):
-            self.optimizer_step_synced(grad_sync, stream=stream)     # a torch.distributed module: pipelined exchange + Adam
+            # a torch.distributed module: sharded optimizer (default) or the pipelined allreduce + Adam
+            if getattr(self, "dp_mode", "sharded") == "sharded":
+                self.optimizer_step_sharded(grad_sync, stream=stream)
+            else:
+                self.optimizer_step_synced(grad_sync, stream=stream)
             return
         if grad_sync is not None:
             grad_sync(self.model.g)

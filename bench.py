@@ -382,11 +382,14 @@ def run_ours(args, rank, world, local_rank):
 
     grad_sync = None
     if world > 1:
-        if args.sliced_allreduce:
-            grad_sync = dist          # allreduce pipelined with Adam over slices of the arena (SampleTrainer.optimizer_step_synced)
-        else:
+        if args.dp == "allreduce":
             def grad_sync(g):
                 dist.all_reduce(g, op=dist.ReduceOp.SUM)
+        else:
+            # "sharded": reduce-scatter, Adam on this rank's slice of the table, all-gather of the fp16 slice;
+            # "sliced": allreduce and Adam pipelined over 4 slices (SampleTrainer.optimizer_step_sharded / _synced)
+            grad_sync = dist
+            tr.dp_mode = args.dp
 
     def step_resident(i):
         tr.pos, tr.dirs, tr.target = dev[i % 2]
@@ -468,7 +471,7 @@ def run_ours(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "l2": "inputs and activations of one step (>1 GB) exceed the 126 MB L2; two input batches alternate",
-                       "parallelism": "dp%d" % world, "field_kernels": ("fused+scatter" if tr.fused_scatter else "fused") if tr.fused else "sequence",
+                       "parallelism": "dp%d" % world if world == 1 else "dp%d/%s" % (world, args.dp), "field_kernels": ("fused+scatter" if tr.fused_scatter else "fused") if tr.fused else "sequence",
                        "tuning": args.tune},
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "last_loss": loss},
@@ -721,9 +724,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
-    ap.add_argument("--sliced-allreduce", action="store_true",
-                    help="N > 1: allreduce and Adam pipelined over 4 slices of the arena instead of one allreduce and one Adam launch "
-                         "(A/B; measured slower at 2 GPUs: 1.44 against 1.36 ms per step)")
+    ap.add_argument("--dp", default="sharded", choices=["sharded", "allreduce", "sliced"],
+                    help="N > 1: how the gradient is exchanged (sharded: reduce-scatter + Adam on a slice + all-gather of fp16 parameters; "
+                         "allreduce: one allreduce + one full Adam; sliced: both pipelined over 4 slices)")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()

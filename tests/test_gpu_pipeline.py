@@ -169,20 +169,25 @@ def test_pipelined_allreduce_and_adam_equal_the_single_launch(cuda, nb):
     try:
         n, out = 4096, {}
         pos, dirs, tgt = _inputs(n, 21)
-        for mode in ("single", "sliced"):
+        for mode in ("single", "sliced", "sharded"):
             model = pl.FieldModel(torch, 16, 1 << 14, 16, 1.3819, 64, 2, 64, 3)
             model.load_hashgrid(make_table(16, 1 << 14, seed=2, amp=0.1))
             model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=3)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=4))
             tr = pl.SampleTrainer(model, n)
+            tr.dp_mode = mode
             tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
             for _ in range(2):
-                tr.step_device(n, None, dist if mode == "sliced" else (lambda g: dist.all_reduce(g)))
+                tr.step_device(n, None, dist if mode != "single" else (lambda g: dist.all_reduce(g)))
+            if mode == "sharded":
+                tr.gather_master(dist)
             torch.cuda.synchronize()
             out[mode] = [getattr(model, k).clone() for k in ("w", "w_h", "m", "v", "g")]
         # the gradient itself differs run to run in its last bits (unordered atomics), so compare loosely but completely
-        for a, b in zip(out["single"][:4], out["sliced"][:4]):
-            assert torch.allclose(a.float(), b.float(), rtol=1e-3, atol=1e-6)
-        assert torch.all(out["sliced"][4] == 0) and torch.all(out["single"][4] == 0)
+        for other in ("sliced", "sharded"):
+            for a, b in zip(out["single"][:4], out[other][:4]):
+                assert torch.allclose(a.float(), b.float(), rtol=1e-3, atol=1e-6), other
+            assert torch.all(out[other][4] == 0)
+        assert torch.all(out["single"][4] == 0)
         assert (out["sliced"][0] != torch.from_numpy(make_table(16, 1 << 14, seed=2, amp=0.1).ravel()).cuda()[:1].new_zeros(1)).any()
     finally:
         dist.destroy_process_group()
