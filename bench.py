@@ -501,6 +501,13 @@ SCENE_WORKLOAD = ("cfg3: analytic soft sphere, 100 cameras 800x800, 128^3 occupa
 RENDER_WORKLOAD = "cfg4: 1920x1080 orbit frames of the cfg3 model after %d training steps, <=1024 samples/ray, early termination"
 
 
+# config 5: 32 seeded soft spheres in a box of scale 4, 3 cascades of 128^3, T = 2^22 per level, 300 cameras 1280x720,
+# 2^21 samples per step over all ranks (2^18 per rank at 8 GPUs; the per-rank batch stays 2^18 at every N: weak scaling)
+SCENE5_OPTS = dict(SCENE_OPTS, hash_table_size=1 << 22, num_cascades=3)
+SCENE5_WORKLOAD = ("cfg5: 32 soft spheres in a scale-4 box, 300 cameras 1280x720, 128^3 occupancy x3 cascades, L16 F2 T2^22, "
+                   "batch 2^18 samples per GPU, ray chunk 65536, distortion loss, Adam")
+
+
 class _RefEngine:
     """The reference's InstantNerf (oracle/_ref build) behind the few methods the workloads call."""
 
@@ -534,12 +541,17 @@ class _RefEngine:
         self.ref.lib().ref_nerf_destroy(self.h)
 
 
-def _scene_batches(torch, syn, count, rays, seed0):
-    scene, poses, bg = syn.SoftSphereScene(), syn.sphere_cameras(100), (1.0, 1.0, 1.0)
+def _scene_batches(torch, syn, count, rays, seed0, config=3):
+    bg = (1.0, 1.0, 1.0)
+    if config == 5:
+        scene, poses, wh = syn.MultiSphereScene(), syn.sphere_cameras(300, radius=4.5), (1280, 720)
+        extent = scene.extent
+    else:
+        scene, poses, wh, extent = syn.SoftSphereScene(), syn.sphere_cameras(100), (800, 800), None
     out = []
     for k in range(count):
-        o, d = syn.random_training_rays(torch, poses, rays, 800, 800, 50.0, seed=seed0 + k)
-        out.append((o, d, syn.ground_truth(torch, scene, o, d, bg)))
+        o, d = syn.random_training_rays(torch, poses, rays, wh[0], wh[1], 50.0, seed=seed0 + k)
+        out.append((o, d, syn.ground_truth(torch, scene, o, d, bg, extent=extent, chunk=(1 << 14) if config == 5 else (1 << 18))))
     return out
 
 
@@ -557,7 +569,8 @@ def run_scene(args, rank, world, local_rank):
     nb = importlib.import_module("3dmaker_b200")
     nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
     D = importlib.import_module("3dmaker_b200.distributed")
-    opts = nm.default_options(**SCENE_OPTS)
+    cfg5 = args.workload == "scene5"
+    opts = nm.default_options(**(SCENE5_OPTS if cfg5 else SCENE_OPTS))
     rays = 1 << 16
     if reference:
         from oracle import ref_cuda as ref
@@ -571,7 +584,7 @@ def run_scene(args, rank, world, local_rank):
         # walk per call); the sphere scene yields about 7 steps' worth of samples per 65536 rays
         trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None, steps_per_call=6)
         nranks = world
-    batches = _scene_batches(torch, syn, 8, rays * nranks, 9000)
+    batches = _scene_batches(torch, syn, 8, rays * nranks, 9000, config=5 if cfg5 else 3)
 
     used = [0]
 
@@ -610,7 +623,7 @@ def run_scene(args, rank, world, local_rank):
         line = {"metric": "train samples/s (full NeRF step)", "value": total / (ms / 1000.0), "unit": "samples/s", "n_gpus": nranks,
                 "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": SCENE_WORKLOAD, "rays_per_step_per_gpu": rays, "optimizer_steps": opt_steps,
+                "config": {"workload": SCENE5_WORKLOAD if cfg5 else SCENE_WORKLOAD, "rays_per_step_per_gpu": rays, "optimizer_steps": opt_steps,
                            "samples_per_call": total / args.steps, "rays_per_s": rays_used / (ms / 1000.0),
                            "ms_per_optimizer_step": ms / max(opt_steps, 1)}}
         if reference:
@@ -714,9 +727,9 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="field", choices=["field", "scene", "render"],
-                    help="field: the headline step on explicit samples (default, the driver's line); scene: full NeRF training step on the "
-                         "analytic scene; render: 1920x1080 orbit frames, pixels sharded over the ranks")
+    ap.add_argument("--workload", default="field", choices=["field", "scene", "scene5", "render"],
+                    help="field: the headline step on explicit samples (default, the driver's line); scene / scene5: full NeRF training step on the "
+                         "analytic scene of config 3 / config 5; render: 1920x1080 orbit frames, pixels sharded over the ranks")
     ap.add_argument("--batch-log2", type=int, default=20, help="field workload: log2 of the samples per GPU and step (20 = the benchmark's; "
                     "smaller values are for profiling small cases, their lines are not benchmark results)")
     ap.add_argument("--scene-warm", type=int, default=272, help="scene workload: untimed train_rays calls before the timed ones")
@@ -737,7 +750,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload == "scene":
+    if args.workload in ("scene", "scene5"):
         run_scene(args, rank, world, local_rank)
     elif args.workload == "render":
         run_render(args, rank, world, local_rank)
