@@ -3,7 +3,7 @@ they lie into oracle/_ref/libref3dmaker.so by oracle/build_ref.py) on small seed
 
 Run on a machine with a CUDA GPU, from the repository root, after the reference build exists:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [copy-to-directory]
 
 The inputs are not stored: tests/test_golden_cpu.py rebuilds them from the same seeded generators (golden_inputs
 below, pure numpy) and checks the CPU oracle against these vectors without a GPU.  The file stays small (a few
@@ -160,10 +160,10 @@ def main():
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote %s (%d arrays, %.0f KB)" % (path, len(out), os.path.getsize(path) / 1024))
-    dst = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(dst):
+    if len(sys.argv) > 1:                      # optional second copy, e.g. into a folder that is collected from the GPU machine
         import shutil
-        shutil.copy(path, os.path.join(dst, "reference_vectors.npz"))
+        os.makedirs(sys.argv[1], exist_ok=True)
+        shutil.copy(path, os.path.join(sys.argv[1], "reference_vectors.npz"))
 
 
 if __name__ == "__main__":
