@@ -113,6 +113,13 @@ class NerfOptions(ctypes.Structure):
     ]
 
 
+class ImageSet(ctypes.Structure):
+    _fields_ = [("d_images_rgba", c_void_p), ("d_transforms", c_void_p), ("num_images", ctypes.c_int32), ("width", ctypes.c_int32),
+                ("height", ctypes.c_int32), ("focal", c_float), ("d_rec_frame", c_void_p), ("d_rec_u", c_void_p), ("d_rec_v", c_void_p),
+                ("d_rec_depth", c_void_p), ("d_rec_sigma", c_void_p), ("num_records", ctypes.c_uint32), ("dense_fraction", c_float),
+                ("prior_width", ctypes.c_int32), ("prior_height", ctypes.c_int32)]
+
+
 class ArenaView(ctypes.Structure):
     _fields_ = [("w", c_void_p), ("w_h", c_void_p), ("g", c_void_p), ("m", c_void_p), ("v", c_void_p),
                 ("total", c_int64), ("sparse_count", c_int64),
@@ -166,6 +173,8 @@ _SIGNATURES = {
                              c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]),
     "nb_sh_gather": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_density_grad": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_fetch_ray_chunk": (c_int, [ctypes.POINTER(ImageSet), c_int, c_int, ctypes.c_uint32, c_int, ctypes.POINTER(c_float), c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_generate_rays": (c_int, [c_int, c_int, c_float, ctypes.POINTER(c_float), c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "nb_mse_rays": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "nb_ray_aabb": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),

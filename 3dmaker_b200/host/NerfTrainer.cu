@@ -74,6 +74,74 @@ void INerfTrainer::setRaySource(RaySource source, uint32_t totalRays, Vec3 scene
     m_lossHistory.clear();
 }
 
+void INerfTrainer::setImageSet(const nb_image_set& set, Vec3 sceneUp, bool randomBackground) {
+    if (!set.d_images_rgba || !set.d_transforms || set.num_images <= 0 || set.width <= 0 || set.height <= 0)
+        throw std::runtime_error("setImageSet: empty image set");
+    m_imageSet = set;
+    m_imageSet.dense_fraction = (set.num_records > 0) ? m_config.depthFraction : 0.0f;
+    m_hasImageSet = true;
+    m_holdoutEvery = m_config.shouldValidate ? 8u : 0u;   // NerfTrainer.cu:88
+    m_cameraAngleX = 2.0f * atanf(0.5f * set.width / set.focal);
+    const uint64_t total = (uint64_t)set.num_images * set.width * set.height;
+    if (total > 0x7fffffffu) throw std::runtime_error("setImageSet: more than 2^31 - 1 pixels");
+    RaySource src = [this](uint32_t cursor, uint32_t count, uint32_t epochSeed, float3 bg, float3* d_o, float3* d_d, float* d_rgb, cudaStream_t st) {
+        const float bgc[3] = {bg.x, bg.y, bg.z};
+        if (m_d_prior_depth.bytes() < count * sizeof(float)) { m_d_prior_depth.allocate(count * sizeof(float)); m_d_prior_sigma.allocate(count * sizeof(float)); }
+        throw_on_error(nb_fetch_ray_chunk(&m_imageSet, (int)cursor, (int)count, epochSeed, 1, bgc, (int)m_holdoutEvery, reinterpret_cast<float*>(d_o),
+                                          reinterpret_cast<float*>(d_d), d_rgb, m_d_prior_depth.as<float>(), m_d_prior_sigma.as<float>(), st),
+                       "ray fetch");
+    };
+    setRaySource(std::move(src), (uint32_t)total, sceneUp, randomBackground);
+}
+
+float INerfTrainer::validate() {
+    if (!m_nerf || !m_hasImageSet) return 0.0f;
+    const int HOLDOUT = 8;
+    const int pixels = m_imageSet.width * m_imageSet.height;
+    const int tile = (int)m_masterConfig.rayChunkSize;
+    ensureChunkBuffers();
+    m_nerf->setMemoryMode(INFERENCE);
+    const float white[3] = {1.0f, 1.0f, 1.0f};
+    m_nerf->setBgColor(make_float3(1.0f, 1.0f, 1.0f));
+    throw_on_error(nb_zero_async(m_d_loss.as<float>(), sizeof(float), 0), "loss reset");
+    long long totalPixels = 0;
+    for (int i = 0; i < m_imageSet.num_images; i += HOLDOUT) {
+        for (int off = 0; off < pixels; off += tile) {
+            const int count = std::min(tile, pixels - off);
+            throw_on_error(nb_fetch_ray_chunk(&m_imageSet, i * pixels + off, count, 0u, 0, white, 0, m_d_rays_o.as<float>(), m_d_rays_d.as<float>(),
+                                              m_d_rgb_true.as<float>(), nullptr, nullptr, 0), "ray fetch");
+            m_nerf->renderImageHit(m_d_rays_o.as<float3>(), m_d_rays_d.as<float3>(), (uint32_t)count, m_d_chunkRgb.as<float>(), 0);
+            throw_on_error(nb_mse_rays(m_d_chunkRgb.as<float>(), m_d_rgb_true.as<float>(), m_d_loss.as<float>(), count, 0), "validation error");
+            totalPixels += count;
+        }
+    }
+    float h_loss = 0.0f;
+    throw_on_cuda(cudaMemcpy(&h_loss, m_d_loss.as<float>(), sizeof(float), cudaMemcpyDeviceToHost), "validation loss");
+    const float mse = h_loss / (float)std::max(1LL, totalPixels);
+    return -10.0f * log10f(fmaxf(mse, 1e-8f));
+}
+
+Image INerfTrainer::renderTrainView(int index, int width, int height) {
+    Image img;
+    if (!m_nerf || !m_hasImageSet || index < 0 || index >= m_imageSet.num_images) return img;
+    if (width <= 0) width = m_imageSet.width;
+    if (height <= 0) height = m_imageSet.height;
+    float m16[16];
+    throw_on_cuda(cudaMemcpy(m16, m_imageSet.d_transforms + (size_t)index * 16, sizeof(m16), cudaMemcpyDeviceToHost), "frame pose");
+    float c2w[12];
+    for (int r = 0; r < 3; r++)
+        for (int c = 0; c < 4; c++) c2w[4 * r + c] = m16[4 * r + c];
+    const float focal = 0.5f * width / tanf(0.5f * m_cameraAngleX);
+    img.width = width; img.height = height;
+    img.rgb.assign((size_t)width * height * 3, 0.0f);
+    nb::DeviceMem d_rgb;
+    d_rgb.allocate(img.rgb.size() * sizeof(float));
+    renderPixels(c2w, focal, width, height, 0, (int64_t)width * height, d_rgb.as<float>(), 0);
+    throw_on_cuda(cudaDeviceSynchronize(), "renderTrainView");
+    throw_on_cuda(cudaMemcpy(img.rgb.data(), d_rgb.as<float>(), img.rgb.size() * sizeof(float), cudaMemcpyDeviceToHost), "renderTrainView");
+    return img;
+}
+
 float INerfTrainer::currentLR() const {
     int anneal = (m_config.annealSteps > 0) ? m_config.annealSteps : std::max(1, m_targetSteps);
     float progress = fminf((float)m_globalStep / (float)anneal, 1.0f);
@@ -95,7 +163,9 @@ float INerfTrainer::trainOneChunk(bool computeLoss) {
     m_source(m_rayCursor, (uint32_t)chunkSize, m_epochSeed, bg, m_d_rays_o.as<float3>(), m_d_rays_d.as<float3>(), m_d_rgb_true.as<float>(), 0);
     if (computeLoss) throw_on_error(nb_zero_async(m_d_loss.as<float>(), sizeof(float), 0), "loss reset");
 
-    m_nerf->trainWithRaysHit(m_d_rays_o.as<float3>(), m_d_rays_d.as<float3>(), nullptr, nullptr, m_d_rgb_true.as<float>(), (uint32_t)chunkSize,
+    const bool priors = m_hasImageSet && m_imageSet.num_records > 0;
+    m_nerf->trainWithRaysHit(m_d_rays_o.as<float3>(), m_d_rays_d.as<float3>(), priors ? m_d_prior_depth.as<float>() : nullptr,
+                             priors ? m_d_prior_sigma.as<float>() : nullptr, m_d_rgb_true.as<float>(), (uint32_t)chunkSize,
                              m_globalStep, nullptr, computeLoss ? m_d_chunkRgb.as<float>() : nullptr, 0);
     m_rayCursor += chunkSize;
     m_raysSeen += chunkSize;

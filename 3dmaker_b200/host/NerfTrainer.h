@@ -62,6 +62,16 @@ public:
     void loadDataset(const std::string& path);  // throws: image datasets are outside this library, use setRaySource
     // Replaces loadDataset for synthetic or externally loaded data (no counterpart in the reference).
     void setRaySource(RaySource source, uint32_t totalRays, Vec3 sceneUp = {0.0f, 1.0f, 0.0f}, bool randomBackground = true);
+    // A posed image set already in device memory (decoding image files stays outside the library): training rays are
+    // drawn from it by nb_fetch_ray_chunk exactly as DataLoader::fetchRayChunk draws them (PCG pick, hold-out of every 8th
+    // image when the config asks for validation, depth-prior slots), and validate() / renderTrainView() work as in the
+    // reference.  The set's device buffers must outlive the trainer.  No counterpart in the reference, where
+    // loadDataset() produces the same state from files.
+    void setImageSet(const nb_image_set& set, Vec3 sceneUp = {0.0f, 1.0f, 0.0f}, bool randomBackground = true);
+    // Hold-out PSNR over every 8th image, white background (NerfTrainer.cu:378-409); 0 without an image set.
+    float validate();
+    // Frame `index` of the image set re-rendered from its own pose (NerfTrainer.cu:368-376).
+    Image renderTrainView(int index, int width = 0, int height = 0);
     // Lets a caller override what init() derives (AABB, network sizes, ...) before the model is built.
     NerfOptions& options() { return m_masterConfig; }
 
@@ -99,6 +109,10 @@ private:
     NerfOptions m_masterConfig;
     InstantNerf* m_nerf = nullptr;
     RaySource m_source;
+    nb_image_set m_imageSet{};
+    bool m_hasImageSet = false;
+    uint32_t m_holdoutEvery = 0;
+    nb::DeviceMem m_d_prior_depth, m_d_prior_sigma;
     bool m_randomBg = true;
     uint32_t m_total_rays = 0;
 

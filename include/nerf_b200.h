@@ -218,6 +218,31 @@ int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, cons
                       float* d_grad_density_w, float* d_grad_density_b, float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h,
                       const nb_grid_desc* grid, const float* d_pos4, float* d_table_grads, void* stream);
 
+/* ---- ray batches from an image set ------------------------------------------------------------------ */
+
+/* A posed image set in device memory: what the reference's DataLoader holds after loading (DataLoader.h), with the
+ * images in HBM instead of mapped host memory.  Depth-prior records are optional (num_records 0). */
+typedef struct nb_image_set {
+    const uint8_t* d_images_rgba;  /* [num_images][height][width][4] */
+    const float* d_transforms;     /* [num_images][16] row-major camera-to-world */
+    int32_t num_images, width, height;
+    float focal;                   /* pixels */
+    const int32_t* d_rec_frame;    /* depth priors: image index, pixel position (in a prior_width x prior_height frame), depth, sigma */
+    const float *d_rec_u, *d_rec_v, *d_rec_depth, *d_rec_sigma;
+    uint32_t num_records;
+    float dense_fraction;          /* share of the random slots redirected to a prior's keypoint */
+    int32_t prior_width, prior_height;
+} nb_image_set;
+
+/* Replaces DataLoader::fetchRayChunk / fetchRayChunkStreamingKernel (modules/NeRF/DataLoader.cu:542-690): `size` rays
+ * and blended target colours for slots [offset, offset + size).  randomize != 0: PCG-hashed image and pixel per slot
+ * (seed = the epoch seed), images 0, N, 2N, ... never drawn when holdout_every = N >= 2; randomize == 0: pixels in
+ * order (validation, INerfTrainer::validate).  d_prior_depth / d_prior_sigma (nullable) receive -1 for plain colour
+ * rays.  float3 rays, float3 colours. */
+int nb_fetch_ray_chunk(const nb_image_set* set, int offset, int size, uint32_t seed, int randomize, const float* bg_color3,
+                       int holdout_every, float* d_rays_o, float* d_rays_d, float* d_rgb, float* d_prior_depth, float* d_prior_sigma,
+                       void* stream);
+
 /* ---- rays, occupancy march, compaction ------------------------------------------------------- */
 
 /* Scene geometry of the marcher: the fields of NerfOptions it reads (modules/NeRF/InstantNerf.h:35-42). */

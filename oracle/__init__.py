@@ -327,3 +327,34 @@ def extract_active_cells(bitfield, total_cells, cells_per_cascade, pyramid):
     out = np.zeros(total_cells, np.int32)
     n = lib().orc_extract_active_cells(_p(_c(bitfield, np.uint8)), _p(out), int(total_cells), int(cells_per_cascade), int(pyramid))
     return out[:n].copy()
+
+
+def pcg_hash(v):
+    lib().orc_pcg.restype = ctypes.c_uint32
+    return int(lib().orc_pcg(ctypes.c_uint32(int(v) & 0xffffffff)))
+
+
+def fetch_ray_chunk(offset, size, seed, randomize, width, height, focal, transforms, images_rgba, bg, holdout_every=0, records=None,
+                    dense_fraction=0.0, prior_wh=(0, 0)):
+    """fetchRayChunkStreamingKernel on the CPU.  images_rgba uint8 [n][h][w][4], transforms float32 [n][16].
+    records = (frame int32, u, v, depth, sigma float32 arrays) or None.  Returns rays_o, rays_d, rgb, depth, sigma, picked."""
+    images_rgba = _c(images_rgba, np.uint8)
+    n = images_rgba.shape[0]
+    total = n * width * height
+    ro, rd, rgb = np.zeros((size, 3), np.float32), np.zeros((size, 3), np.float32), np.zeros((size, 3), np.float32)
+    dep, sig, pick = np.zeros(size, np.float32), np.zeros(size, np.float32), np.zeros(size, np.uint32)
+    if records is None:
+        rf = ru = rv = rD = rs = None
+        nrec = 0
+    else:
+        rf, ru, rv, rD, rs = (_c(records[0], np.int32), _c(records[1], np.float32), _c(records[2], np.float32), _c(records[3], np.float32),
+                              _c(records[4], np.float32))
+        nrec = len(rf)
+    sx = float(width) / prior_wh[0] if prior_wh[0] > 0 else 1.0
+    sy = float(height) / prior_wh[1] if prior_wh[1] > 0 else 1.0
+    P = lambda a: None if a is None else _p(a)
+    lib().orc_fetch_ray_chunk(int(offset), int(size), int(total), ctypes.c_uint32(int(seed)), int(randomize), int(width), int(height), _f(focal),
+                              _p(_c(transforms, np.float32)), _p(images_rgba), _p(ro), _p(rd), _p(rgb), _p(dep), _p(sig), _p(pick), P(rf), P(ru), P(rv),
+                              P(rD), P(rs), ctypes.c_uint32(nrec), _f(dense_fraction), _f(sx), _f(sy), _p(_c(np.asarray(bg, np.float32), np.float32)),
+                              int(holdout_every))
+    return ro, rd, rgb, dep, sig, pick

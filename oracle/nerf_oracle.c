@@ -952,3 +952,86 @@ int orc_extract_active_cells(const uint8_t* bitfield, int* active, int total_cel
     }
     return n;
 }
+
+/* ------------------------------------------------------------------------------------------------
+ * Ray batches from a posed image set: fetchRayChunkStreamingKernel, modules/NeRF/DataLoader.cu:542-662.
+ * PCG hash (:542-546), hold-out aware image / pixel pick (:566-592), depth-prior slots (:606-626), pinhole ray
+ * (:628-646), RGBA over background (:651-664).  Parity unpinned for this function: the reference's loader does not build
+ * without its image-decoding dependencies, so there is no reference vector; the selection is integer arithmetic on a
+ * published hash, the rest a handful of fp32 operations.
+ * ------------------------------------------------------------------------------------------------ */
+static uint32_t orc_pcg_hash(uint32_t input) {
+    uint32_t state = input * 747796405u + 2891336453u;
+    uint32_t word = ((state >> ((state >> 28u) + 4u)) ^ state) * 277803737u;
+    return (word >> 22u) ^ word;
+}
+uint32_t orc_pcg(uint32_t v) { return orc_pcg_hash(v); }
+
+void orc_fetch_ray_chunk(int offset, int size, int total_rays, uint32_t seed, int randomize, int width, int height, float focal,
+                         const float* transforms, const uint8_t* images, float* rays_o, float* rays_d, float* rgb, float* out_depth,
+                         float* out_sigma, uint32_t* picked, const int* rec_frame, const float* rec_u, const float* rec_v, const float* rec_D,
+                         const float* rec_sigma, uint32_t num_records, float dense_fraction, float uv_scale_x, float uv_scale_y,
+                         const float* bg, int holdout_every) {
+    const int pixels = width * height;
+    for (int idx = 0; idx < size; idx++) {
+        uint32_t global_idx;
+        if (randomize) {
+            uint32_t rand_val = orc_pcg_hash((uint32_t)(offset + idx) + seed);
+            if (holdout_every >= 2) {
+                int num_imgs = total_rays / pixels;
+                int num_test = (num_imgs + holdout_every - 1) / holdout_every;
+                int num_train = num_imgs - num_test;
+                if (num_train < 1) {
+                    global_idx = rand_val % (uint32_t)total_rays;
+                } else {
+                    int train_slot = (int)(rand_val % (uint32_t)num_train);
+                    int block = train_slot / (holdout_every - 1);
+                    int within = train_slot % (holdout_every - 1);
+                    int img_idx = block * holdout_every + within + 1;
+                    uint32_t r2 = orc_pcg_hash(rand_val);
+                    global_idx = (uint32_t)img_idx * (uint32_t)pixels + r2 % (uint32_t)pixels;
+                }
+            } else {
+                global_idx = rand_val % (uint32_t)total_rays;
+            }
+        } else {
+            global_idx = (uint32_t)(offset + idx) % (uint32_t)total_rays;
+        }
+        int img_idx = (int)(global_idx / (uint32_t)pixels);
+        int pixel_idx = (int)(global_idx % (uint32_t)pixels);
+        float px = (float)(pixel_idx % width), py = (float)(pixel_idx / width);
+        float oD = -1.0f, oS = -1.0f;
+        if (randomize && dense_fraction > 0.0f && num_records > 0) {
+            uint32_t hsel = orc_pcg_hash((uint32_t)(idx + 0x9E3779B9u) ^ (seed * 2654435761u));
+            if ((float)hsel * (1.0f / 4294967296.0f) < dense_fraction) {
+                uint32_t r = orc_pcg_hash(hsel) % num_records;
+                int f = rec_frame[r];
+                if (!(holdout_every >= 2 && (f % holdout_every == 0))) {
+                    img_idx = f;
+                    px = rec_u[r] * uv_scale_x;
+                    py = rec_v[r] * uv_scale_y;
+                    oD = rec_D[r];
+                    oS = rec_sigma[r];
+                    int px_i = (int)(px + 0.5f), py_i = (int)(py + 0.5f);
+                    px_i = px_i < 0 ? 0 : (px_i > width - 1 ? width - 1 : px_i);
+                    py_i = py_i < 0 ? 0 : (py_i > height - 1 ? height - 1 : py_i);
+                    global_idx = (uint32_t)img_idx * (uint32_t)pixels + (uint32_t)(py_i * width + px_i);
+                }
+            }
+        }
+        float dx = (px - width * 0.5f) / focal, dy = -(py - height * 0.5f) / focal, dz = -1.0f;
+        float inv = 1.0f / sqrtf(dx * dx + dy * dy + dz * dz);
+        dx *= inv; dy *= inv; dz *= inv;
+        const float* m = transforms + (size_t)img_idx * 16;
+        rays_o[3 * idx + 0] = m[3]; rays_o[3 * idx + 1] = m[7]; rays_o[3 * idx + 2] = m[11];
+        rays_d[3 * idx + 0] = m[0] * dx + m[1] * dy + m[2] * dz;
+        rays_d[3 * idx + 1] = m[4] * dx + m[5] * dy + m[6] * dz;
+        rays_d[3 * idx + 2] = m[8] * dx + m[9] * dy + m[10] * dz;
+        const uint8_t* c = images + (size_t)global_idx * 4;
+        float fa = c[3] / 255.0f;
+        for (int k = 0; k < 3; k++) rgb[3 * idx + k] = (c[k] / 255.0f) * fa + bg[k] * (1.0f - fa);
+        if (out_depth) out_depth[idx] = oD;
+        if (out_sigma) out_sigma[idx] = oS;
+        if (picked) picked[idx] = global_idx;
+    }
+}

@@ -154,10 +154,56 @@ static void test_trainer_facade() {
     std::printf("[SUCCESS?] INerfTrainer facade, %d failures so far\n", g_fail);
 }
 
+// An image set in device memory as the source of training rays, hold-out validation and train-view rendering.
+static void test_trainer_image_set() {
+    INerfTrainer trainer;
+    NerfConfig cfg;
+    cfg.batchSize = 1 << 16; cfg.renderBatchSize = 1 << 16; cfg.lambdaDist = 0.0f; cfg.shouldValidate = true;
+    trainer.init(cfg);
+    CHECK(trainer.validate() == 0.0f);                       // no image set yet
+    NerfOptions& o = trainer.options();
+    o.gridResolution = make_uint3(32, 32, 32); o.levelsMipmap = 3; o.hashTableSize = 1 << 14;
+    o.aabbMin = make_float3(-0.5f, -0.5f, -0.5f); o.aabbMax = make_float3(0.5f, 0.5f, 0.5f);
+    const int N = 16, W = 48, H = 48;
+    std::vector<uint8_t> rgba((size_t)N * W * H * 4);
+    for (size_t i = 0; i < rgba.size(); i += 4) { rgba[i] = 204; rgba[i + 1] = 77; rgba[i + 2] = 26; rgba[i + 3] = 255; }
+    std::vector<float> poses((size_t)N * 16, 0.0f);
+    for (int i = 0; i < N; i++) {
+        float c2w[12];
+        trainer.orbitCamera(22.5f * i, 15.0f, 1.5f, c2w);
+        for (int k = 0; k < 12; k++) poses[(size_t)i * 16 + k] = c2w[k];
+        poses[(size_t)i * 16 + 15] = 1.0f;
+    }
+    uint8_t* d_rgba = nullptr; float* d_poses = nullptr;
+    cudaMalloc(&d_rgba, rgba.size()); cudaMalloc(&d_poses, poses.size() * sizeof(float));
+    cudaMemcpy(d_rgba, rgba.data(), rgba.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_poses, poses.data(), poses.size() * sizeof(float), cudaMemcpyHostToDevice);
+    nb_image_set set{};
+    set.d_images_rgba = d_rgba; set.d_transforms = d_poses; set.num_images = N; set.width = W; set.height = H;
+    set.focal = 0.5f * W / std::tan(0.5f * 50.0f * 3.14159265f / 180.0f);
+    nb_image_set empty{};
+    EXPECT_THROW(trainer.setImageSet(empty));
+    EXPECT_NO_THROW(trainer.setImageSet(set, Vec3{0, 1, 0}, /*randomBackground=*/false));
+    const float before = trainer.validate();
+    trainer.beginTraining(80);
+    while (!trainer.isTrainingDone()) trainer.trainSteps(10);
+    const float after = trainer.validate();
+    std::printf("image set: hold-out PSNR %.2f dB -> %.2f dB\n", before, after);
+    CHECK(after > before + 3.0f && after > 12.0f);
+    Image view = trainer.renderTrainView(3);
+    CHECK(view.width == W && view.height == H && view.rgb.size() == (size_t)W * H * 3);
+    Image small = trainer.renderTrainView(3, 24, 24);
+    CHECK(small.width == 24 && small.rgb.size() == (size_t)24 * 24 * 3);
+    CHECK(trainer.renderTrainView(N).rgb.empty());
+    cudaFree(d_rgba); cudaFree(d_poses);
+    std::printf("[SUCCESS?] INerfTrainer image set, %d failures so far\n", g_fail);
+}
+
 int main() {
     test_tinymlp_modes();
     test_hashgrid_modes();
     test_trainer_facade();
+    test_trainer_image_set();
     std::printf(g_fail == 0 ? "[SUCCESS] all host-class checks passed\n" : "[FAILED] %d checks failed\n", g_fail);
     return g_fail;
 }
