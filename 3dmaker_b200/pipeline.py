@@ -269,15 +269,42 @@ class SampleTrainer:
         self._queued.append((k, n))
         self._next = 1 - k
 
-    def step_prefetched(self, stream=None, grad_sync=None):
-        """Runs one full step on the oldest prefetched batch and returns its mean squared error (4-byte read-back)."""
+    def step_prefetched(self, stream=None, grad_sync=None, lag=True):
+        """Runs one full step on the oldest prefetched batch.  The step's loss travels to pinned host memory by an
+        asynchronous 4-byte copy enqueued behind the step; with lag=True (default) the call returns the mean squared error
+        of the PREVIOUS step, whose copy has long finished, so the host never waits for the step it has just enqueued
+        and the device never waits for the host (None on the first call; flush_loss() returns the last one).  lag=False
+        waits for this step's own loss."""
+        torch = self.torch
         k, n = self._queued.pop(0)
-        cur = self.torch.cuda.current_stream()
+        cur = torch.cuda.current_stream()
         cur.wait_event(self._ready[k])
         self.pos, self.dirs, self.target = self._slots[k]
         self.step_device(n, stream, grad_sync)
         self._free[k].record(cur)
-        return float(self.loss.item()) / (n * 3)
+        if not hasattr(self, "_loss_host"):
+            self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._loss_done = [torch.cuda.Event(), torch.cuda.Event()]
+            self._loss_slot, self._loss_pending = 0, None
+        j = self._loss_slot
+        self._loss_host[j].copy_(self.loss, non_blocking=True)       # self.loss is re-zeroed by the next step, after this copy in stream order
+        self._loss_done[j].record(cur)
+        prev, self._loss_pending, self._loss_slot = self._loss_pending, (j, n), 1 - j
+        if not lag:
+            return self.flush_loss()
+        if prev is None:
+            return None
+        self._loss_done[prev[0]].synchronize()
+        return float(self._loss_host[prev[0]].item()) / (prev[1] * 3)
+
+    def flush_loss(self):
+        """Mean squared error of the last step enqueued by step_prefetched (waits for it)."""
+        if getattr(self, "_loss_pending", None) is None:
+            return None
+        j, n = self._loss_pending
+        self._loss_pending = None
+        self._loss_done[j].synchronize()
+        return float(self._loss_host[j].item()) / (n * 3)
 
     def step_host(self, pos4, dirs3, target_h8, stream=None, grad_sync=None):
         """One full step from pinned host tensors: copies inputs in, runs the step, returns the mean squared error

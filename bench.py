@@ -436,16 +436,21 @@ def run_ours(args, rank, world, local_rank):
     for i in range(2):
         tr.prefetch(*host[(i + 1) % 2])
         tr.step_prefetched(None, grad_sync)
+    tr.flush_loss()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    loss = 0.0
+    loss, losses_read = 0.0, 0
     for i in range(args.steps):
         tr.prefetch(*host[(i + 1) % 2])
-        loss = tr.step_prefetched(None, grad_sync)
+        got = tr.step_prefetched(None, grad_sync)      # the loss of the previous step: its 4-byte copy has landed by now
+        if got is not None:
+            loss, losses_read = got, losses_read + 1
+    loss, losses_read = tr.flush_loss(), losses_read + 1   # the last step's loss, still inside the timed region
     e1.record()
-    tr.step_prefetched(None, grad_sync)      # drain the last prefetched batch (outside the timed region)
+    tr.step_prefetched(None, grad_sync, lag=False)      # drain the last prefetched batch (outside the timed region)
     barrier()
+    assert losses_read == args.steps, "every timed step's loss must have been read back"
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
