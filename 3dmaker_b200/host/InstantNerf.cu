@@ -30,7 +30,10 @@ InstantNerf::~InstantNerf() {
     delete m_colorMLP;
     delete m_densityMLP;
     if (h_plan) cudaFreeHost(h_plan);
-    if (h_offsets) cudaFreeHost(h_offsets);
+    for (WalkSet& w : m_walk) {
+        if (w.h_offsets) cudaFreeHost(w.h_offsets);
+        if (w.done) cudaEventDestroy(w.done);
+    }
 }
 
 nb_scene_desc InstantNerf::scene() const {
@@ -132,14 +135,17 @@ void InstantNerf::initRenderBuffers() {
 
     d_rays_d_inv.allocate(R * 3 * sizeof(float)); d_nears.allocate(R * sizeof(float)); d_fars.allocate(R * sizeof(float));
     if (R > (size_t)1 << 20) throw std::runtime_error("rayChunkSize above 1048576 is not supported");
-    d_num_steps.allocate(R * sizeof(uint32_t)); d_ray_offsets.allocate((R + 1) * sizeof(uint32_t));
     d_block_sums.allocate((1024 + 4) * sizeof(uint32_t)); d_plan.allocate(4 * sizeof(uint32_t), true);
-    // sample distances of every ray of a chunk, one row per ray (see nb_march_fill)
-    d_t_rows.allocate(R * (size_t)nb_march_row_stride() * sizeof(float));
-    if (h_offsets_capacity < R + 1) {
-        if (h_offsets) cudaFreeHost(h_offsets);
-        throw_on_cuda(cudaMallocHost(&h_offsets, (R + 1) * sizeof(uint32_t)), "pinned offsets");
-        h_offsets_capacity = R + 1;
+    for (WalkSet& w : m_walk) {
+        w.num_steps.allocate(R * sizeof(uint32_t)); w.offsets.allocate((R + 1) * sizeof(uint32_t));
+        // sample distances of every ray of a chunk, one row per ray (see nb_march_fill)
+        w.rows.allocate(R * (size_t)nb_march_row_stride() * sizeof(float));
+        if (w.capacity < R + 1) {
+            if (w.h_offsets) cudaFreeHost(w.h_offsets);
+            throw_on_cuda(cudaMallocHost(&w.h_offsets, (R + 1) * sizeof(uint32_t)), "pinned offsets");
+            w.capacity = R + 1;
+        }
+        if (!w.done) throw_on_cuda(cudaEventCreateWithFlags(&w.done, cudaEventDisableTiming), "walk event");
     }
     d_render_rgb.allocate(R * 3 * sizeof(float)); d_render_depth.allocate(R * sizeof(float)); d_phi.allocate(R * 3 * sizeof(float));
     d_weight_sum.allocate(R * sizeof(float));
@@ -235,7 +241,7 @@ void InstantNerf::lateOccupancyGridUpdate(cudaStream_t stream) {
 
 InstantNerf::StepView InstantNerf::stepView() const {
     StepView v;
-    v.num_steps = d_num_steps.as<uint32_t>() + m_lastStepFirstRay; v.ray_offsets = d_ray_offsets.as<uint32_t>() + m_lastStepFirstRay;
+    v.num_steps = m_walk[0].num_steps.as<uint32_t>() + m_lastStepFirstRay; v.ray_offsets = m_walk[0].offsets.as<uint32_t>() + m_lastStepFirstRay;
     v.ray_indices = d_ray_indices.as<uint32_t>(); v.sample_base = m_lastSampleBase;
     v.t_sorted = d_t_sorted.as<float>(); v.positions = d_positions.as<float>(); v.density_out = d_density_out.as<float>();
     v.sigma = d_sigma.as<float>(); v.color_out = d_color_out.as<float>(); v.render_rgb = d_render_rgb.as<float>(); v.phi = d_phi.as<float>();
@@ -252,19 +258,25 @@ bool InstantNerf::setFusedField(bool on) {
 }
 
 // Walks rays [first, first + count) once (slab test, occupancy walk into the scratch rows, scan) and brings the
-// scanned offsets to the host: h_offsets[i] = first sample of ray first + i, h_offsets[count] = sample total.
-void InstantNerf::walkRays(const float3* d_rays_o, const float3* d_rays_d, uint32_t first, uint32_t count, cudaStream_t stream) {
+// scanned offsets to the host: offsets[i] = first sample of ray first + i, offsets[count] = sample total.  There are
+// two sets of walk buffers so that a renderer can have the next chunk walked while it still cuts batches out of the
+// current one; wait = false only enqueues (the set's event marks the read-back), finishWalk() waits for it.
+void InstantNerf::walkRays(const float3* d_rays_o, const float3* d_rays_d, uint32_t first, uint32_t count, cudaStream_t stream, int set, bool wait) {
     nb_scene_desc sc = scene();
+    WalkSet& w = m_walk[set];
     const float* o = reinterpret_cast<const float*>(d_rays_o + first);
     const float* d = reinterpret_cast<const float*>(d_rays_d + first);
     throw_on_error(nb_ray_aabb(&sc, o, d, count, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(), stream), "ray/box");
     throw_on_error(nb_march_fill(&sc, o, d, d_rays_d_inv.as<float>(), d_nears.as<float>(), d_fars.as<float>(), d_occupancyGrid.as<uint8_t>(), count,
-                                 d_num_steps.as<uint32_t>(), d_t_rows.as<float>(), d_ray_offsets.as<uint32_t>(), d_block_sums.as<uint32_t>(), stream),
+                                 w.num_steps.as<uint32_t>(), w.rows.as<float>(), w.offsets.as<uint32_t>(), d_block_sums.as<uint32_t>(), stream),
                    "march: walk");
-    throw_on_cuda(cudaMemcpyAsync(h_offsets, d_ray_offsets.as<uint32_t>(), ((size_t)count + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream),
+    throw_on_cuda(cudaMemcpyAsync(w.h_offsets, w.offsets.as<uint32_t>(), ((size_t)count + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream),
                   "march: offsets");
-    throw_on_cuda(cudaStreamSynchronize(stream), "march: offsets");
+    throw_on_cuda(cudaEventRecord(w.done, stream), "march: offsets");
+    if (wait) finishWalk(set);
 }
+
+void InstantNerf::finishWalk(int set) { throw_on_cuda(cudaEventSynchronize(m_walk[set].done), "march: offsets"); }
 
 // Last ray e >= begin of a walked window of `count` rays such that the samples of rays [begin, e) fit `budget`.
 static uint32_t cutRays(const uint32_t* offsets, uint32_t begin, uint32_t count, uint32_t budget) {
@@ -314,11 +326,11 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                 if (!walked) {
                     winFirst = raysDone;
                     winCount = std::min<uint32_t>((uint32_t)m_opts.rayChunkSize, numRays - raysDone);
-                    walkRays(d_rays_o, d_rays_d, winFirst, winCount, stream);
+                    walkRays(d_rays_o, d_rays_d, winFirst, winCount, stream, 0, true);
                     walked = true;
                 }
                 begin = raysDone - winFirst;
-                end = cutRays(h_offsets, begin, winCount, budget);
+                end = cutRays(m_walk[0].h_offsets, begin, winCount, budget);
                 // budget not exhausted by what is left of the window, but the window does not reach the last ray:
                 // the reference's chunk would start at raysDone and reach further, so walk again from here
                 if (end == winCount && begin > 0 && winFirst + winCount < numRays) { walked = false; continue; }
@@ -326,8 +338,8 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
             }
         });
         const uint32_t currentChunkRays = end - begin;
-        const uint32_t totalHits = h_offsets[end] - h_offsets[begin];
-        const uint32_t sampleBase = h_offsets[begin];
+        const uint32_t totalHits = m_walk[0].h_offsets[end] - m_walk[0].h_offsets[begin];
+        const uint32_t sampleBase = m_walk[0].h_offsets[begin];
         if (currentChunkRays == 0) {
             std::fprintf(stderr, "Error: Batch size is too small to fit even a single ray! Increase batchSize.\n");
             return;
@@ -336,13 +348,13 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
         const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + raysDone);
         const float* chunk_depth = d_rays_depth ? d_rays_depth + raysDone : nullptr;
         const float* chunk_sigma = d_rays_sigma ? d_rays_sigma + raysDone : nullptr;
-        const uint32_t* steps_b = d_num_steps.as<uint32_t>() + begin;
-        const uint32_t* offs_b = d_ray_offsets.as<uint32_t>() + begin;
+        const uint32_t* steps_b = m_walk[0].num_steps.as<uint32_t>() + begin;
+        const uint32_t* offs_b = m_walk[0].offsets.as<uint32_t>() + begin;
         if (totalHits > 0) {
             timed(stream, m_times.march, [&]() {
                 throw_on_error(nb_march_compact(&sc, reinterpret_cast<const float*>(d_rays_o + winFirst), reinterpret_cast<const float*>(d_rays_d + winFirst),
-                                                begin, currentChunkRays, d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), sampleBase,
-                                                d_t_rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(),
+                                                begin, currentChunkRays, m_walk[0].num_steps.as<uint32_t>(), m_walk[0].offsets.as<uint32_t>(), sampleBase,
+                                                m_walk[0].rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(),
                                                 stream), "march: compact");
             });
         }
@@ -462,25 +474,33 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
     TinyMLP* cn = m_colorMLP;
     const float bg[3] = {m_opts.bgColor.x, m_opts.bgColor.y, m_opts.bgColor.z};
     const uint32_t hitBatch = (uint32_t)((m_memMode == INFERENCE) ? m_opts.renderBatchSize : m_opts.batchSize);
-    for (uint32_t ray_offset = 0; ray_offset < numRays; ray_offset += m_opts.rayChunkSize) {
-        const uint32_t chunkRays = std::min<uint32_t>((uint32_t)m_opts.rayChunkSize, numRays - ray_offset);
+    // The walk of chunk k + 1 is enqueued before the batches of chunk k: while the host waits for chunk k's offsets and cuts
+    // its batches, the device is already walking the next chunk, so the one read-back per chunk never leaves it idle.
+    const uint32_t chunk = (uint32_t)m_opts.rayChunkSize;
+    const uint32_t numChunks = (numRays + chunk - 1) / chunk;
+    if (numChunks > 0) walkRays(d_rays_o, d_rays_d, 0, std::min(chunk, numRays), stream, 0, false);
+    for (uint32_t k = 0; k < numChunks; k++) {
+        const uint32_t ray_offset = k * chunk;
+        const uint32_t chunkRays = std::min<uint32_t>(chunk, numRays - ray_offset);
+        const int set = (int)(k & 1);
+        if (k + 1 < numChunks) walkRays(d_rays_o, d_rays_d, ray_offset + chunk, std::min(chunk, numRays - ray_offset - chunk), stream, set ^ 1, false);
+        finishWalk(set);
+        const WalkSet& w = m_walk[set];
         const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + ray_offset);
         const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + ray_offset);
-        // one walk and one read-back per chunk; every sample batch below is cut out of the rows without another sync
-        walkRays(d_rays_o, d_rays_d, ray_offset, chunkRays, stream);
         uint32_t raysDone = 0;
         while (raysDone < chunkRays) {
-            const uint32_t next = cutRays(h_offsets, raysDone, chunkRays, hitBatch);
+            const uint32_t next = cutRays(w.h_offsets, raysDone, chunkRays, hitBatch);
             if (next <= raysDone) {
                 std::fprintf(stderr, "Error: Batch size is too small to fit even a single ray! Increase batchSize.\n");
                 return;
             }
             const uint32_t crrRays = next - raysDone;
-            const uint32_t base = h_offsets[raysDone];
-            const int64_t n = h_offsets[next] - base;
+            const uint32_t base = w.h_offsets[raysDone];
+            const int64_t n = w.h_offsets[next] - base;
             if (n > 0) {
-                throw_on_error(nb_march_compact(&sc, chunk_o, chunk_d, raysDone, crrRays, d_num_steps.as<uint32_t>(), d_ray_offsets.as<uint32_t>(), base,
-                                                d_t_rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
+                throw_on_error(nb_march_compact(&sc, chunk_o, chunk_d, raysDone, crrRays, w.num_steps.as<uint32_t>(), w.offsets.as<uint32_t>(), base,
+                                                w.rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
                                "march: compact");
                 if (m_fused) {
                     throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
@@ -498,12 +518,11 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
                                                   d_color_out.as<float>(), nullptr, stream), "colour inference");
                 }
             }
-            throw_on_error(nb_composite_infer(crrRays, base, raysDone, d_ray_offsets.as<uint32_t>(), d_num_steps.as<uint32_t>() + raysDone,
+            // composited straight into the caller's frame when there is one
+            float* rgb_dst = d_rgb_out != nullptr ? d_rgb_out + (size_t)(ray_offset + raysDone) * 3 : d_render_rgb.as<float>();
+            throw_on_error(nb_composite_infer(crrRays, base, raysDone, w.offsets.as<uint32_t>(), w.num_steps.as<uint32_t>() + raysDone,
                                               d_t_sorted.as<float>(), d_sigma.as<float>(), d_color_out.as<float>(), m_fused ? 4 : 8, nullptr,
-                                              d_render_rgb.as<float>(), d_render_depth.as<float>(), nullptr, bg, stream), "compositing");
-            if (d_rgb_out != nullptr)
-                throw_on_cuda(cudaMemcpyAsync(d_rgb_out + (size_t)(ray_offset + raysDone) * 3, d_render_rgb.as<float>(),
-                                              (size_t)crrRays * 3 * sizeof(float), cudaMemcpyDeviceToDevice, stream), "rgb out");
+                                              rgb_dst, d_render_depth.as<float>(), nullptr, bg, stream), "compositing");
             raysDone += crrRays;
         }
     }

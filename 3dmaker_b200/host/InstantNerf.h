@@ -147,7 +147,8 @@ private:
     void lateOccupancyGridUpdate(cudaStream_t stream = 0);
     void finishOccupancyUpdate(cudaStream_t stream);
     void optimizerStep(cudaStream_t stream);
-    void walkRays(const float3* d_rays_o, const float3* d_rays_d, uint32_t first, uint32_t count, cudaStream_t stream);
+    void walkRays(const float3* d_rays_o, const float3* d_rays_d, uint32_t first, uint32_t count, cudaStream_t stream, int set, bool wait);
+    void finishWalk(int set);
     nb_scene_desc scene() const;
     template <class F> void timed(cudaStream_t stream, double& acc, F&& f);
 
@@ -163,7 +164,7 @@ private:
 
     nb::DeviceMem d_occupancyGrid, d_masterOccupancyGrid;
     // per ray chunk
-    nb::DeviceMem d_rays_d_inv, d_nears, d_fars, d_num_steps, d_ray_offsets, d_block_sums, d_plan, d_render_rgb, d_render_depth, d_phi,
+    nb::DeviceMem d_rays_d_inv, d_nears, d_fars, d_block_sums, d_plan, d_render_rgb, d_render_depth, d_phi,
         d_weight_sum;
     // per sample batch
     nb::DeviceMem d_positions, d_ray_indices, d_t_sorted, d_density_out, d_sigma, d_color_in, d_color_out, d_color_acts, d_enc, d_density_acts,
@@ -171,9 +172,14 @@ private:
     // occupancy
     nb::DeviceMem d_occ_samples, d_tmp_grid, d_sum, d_occ_scratch, d_active_cells, d_num_active;
     uint32_t* h_plan = nullptr;  // pinned, 4 words
-    uint32_t* h_offsets = nullptr;  // pinned: scanned sample offsets of the walked rays (+ total)
-    size_t h_offsets_capacity = 0;
-    nb::DeviceMem d_t_rows;
+    // buffers of one occupancy walk over a ray chunk; two sets so that rendering can walk ahead
+    struct WalkSet {
+        nb::DeviceMem num_steps, offsets, rows;
+        uint32_t* h_offsets = nullptr;  // pinned: scanned sample offsets of the walked rays (+ total)
+        size_t capacity = 0;
+        cudaEvent_t done = nullptr;
+    };
+    WalkSet m_walk[2];
     uint32_t m_lastStepFirstRay = 0, m_lastSampleBase = 0;
 
     bool m_traininit = false;

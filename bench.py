@@ -674,6 +674,12 @@ def run_render(args, rank, world, local_rank):
     while (eng.steps if reference else eng.steps.value) < train_steps:
         eng.train_rays(*_scene_batches(torch, syn, 1, 1 << 16, 9000 + i)[0]); i += 1
     torch.cuda.synchronize()
+    # frames are rendered in inference mode, as INerfTrainer::renderC2W does (NerfTrainer.cu:302-328): the sample batch
+    # is renderBatchSize and the training buffers are released
+    if reference:
+        eng.ref.lib().ref_nerf_set_memory_mode(eng.h, 1)
+    else:
+        eng.set_memory_mode(True)
     W, H = 1920, 1080
     focal = syn.focal_from_fov(W, 50.0)
     pose = {}
