@@ -29,6 +29,17 @@ def pixel_tiles(num_pixels, rank, world, tile=4096):
     return out
 
 
+def merge_runs(tiles):
+    """Joins tiles that follow one another in the frame: [(first, count), ...] with as few entries as possible."""
+    out = []
+    for first, count in tiles:
+        if out and out[-1][0] + out[-1][1] == first:
+            out[-1] = (out[-1][0], out[-1][1] + count)
+        else:
+            out.append((first, count))
+    return out
+
+
 class DataParallelTrainer:
     """Wraps a scene engine so that train_rays() takes the GLOBAL ray batch.
 
@@ -106,7 +117,7 @@ class ShardedRenderer:
                           torch.empty((max(1, total), 3), dtype=torch.float32, device=device))
         o, d = self._rays
         at = 0
-        for first, count in tiles:
+        for first, count in merge_runs(tiles):
             self.ray_fn(first, count, o[at:at + count], d[at:at + count])
             at += count
         out = torch.zeros((max(1, total), 3), dtype=torch.float32, device=device)
@@ -122,25 +133,26 @@ class ShardedRenderer:
             frame = torch.empty((num_pixels, 3), dtype=torch.float32, device=device)
             self._place(frame, local, tiles)
             return frame
-        # equal-size gather: pad every rank's block to the largest one
+        # equal-size gather: pad every rank's block to the largest one; rank 0 receives into one [world, tiles, tile, 3]
+        # buffer and un-deals the tiles with ONE strided copy (tile j of rank r is tile j * world + r of the frame)
         num_tiles = (num_pixels + self.tile - 1) // self.tile
         max_tiles = (num_tiles + self.world - 1) // self.world
+        n_local = sum(c for _, c in tiles)
         padded = torch.zeros((max_tiles * self.tile, 3), dtype=torch.float32, device=device)
-        padded[:sum(c for _, c in tiles)] = local[:sum(c for _, c in tiles)]
+        padded[:n_local] = local[:n_local]
         if self.rank == 0:
-            blocks = [torch.empty_like(padded) for _ in range(self.world)]
-            self.dist.gather(padded, blocks, dst=0)
-            frame = torch.empty((num_pixels, 3), dtype=torch.float32, device=device)
-            for r in range(self.world):
-                self._place(frame, blocks[r], pixel_tiles(num_pixels, r, self.world, self.tile))
-            return frame
+            buf = torch.empty((self.world, max_tiles, self.tile, 3), dtype=torch.float32, device=device)
+            self.dist.gather(padded, [buf[r].view(max_tiles * self.tile, 3) for r in range(self.world)], dst=0)
+            frame = torch.empty((max_tiles, self.world, self.tile, 3), dtype=torch.float32, device=device)
+            frame.copy_(buf.permute(1, 0, 2, 3))
+            return frame.view(-1, 3)[:num_pixels]
         self.dist.gather(padded, None, dst=0)
         return None
 
     @staticmethod
     def _place(frame, block, tiles):
         at = 0
-        for first, count in tiles:
+        for first, count in merge_runs(tiles):
             frame[first:first + count] = block[at:at + count]
             at += count
 
