@@ -162,6 +162,9 @@ _SIGNATURES = {
     "nb_field_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int, c_void_p]),
+    "nb_field_forward_counted": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float,
+                                         c_void_p, c_void_p, c_int, c_void_p]),
     "nb_field_backward": (c_int, [ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_void_p]),
@@ -187,10 +190,15 @@ _SIGNATURES = {
                               c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_march_compact": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p,
                                  ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_march_round_emit": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p,
+                                    ctypes.c_uint32, ctypes.c_uint32, c_void_p, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p]),
     "nb_march_emit": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                               ctypes.c_uint32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_composite_infer": (c_int, [c_int64, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                    c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), c_void_p]),
+    "nb_composite_round": (c_int, [ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, ctypes.c_uint32, c_void_p,
+                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), c_void_p]),
     "nb_composite_train": (c_int, [c_int64, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, ctypes.POINTER(c_float), c_void_p]),
     "nb_color_grad": (c_int, [c_int64, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -214,6 +222,7 @@ _SIGNATURES = {
     "nb_nerf_set_memory_mode": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_global_ray_scale": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_fused_field": (c_int, [c_void_p, c_int]),
+    "nb_nerf_set_render_rounds": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_steps_per_call": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),

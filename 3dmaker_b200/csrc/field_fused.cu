@@ -64,6 +64,7 @@ struct FieldIO {
     const __half* Wc; const float* bc;  // colour network
     int64_t n;
     float density_bias;
+    const uint32_t* count;  // nullable: sample count known only on the device (at most n)
 };
 
 // Colour-network input fragments of the warp's 16 rows from the density output fragments (16 logits) and the
@@ -112,10 +113,16 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid
     __half* tile = reinterpret_cast<__half*>(sBc + CS::B_TOTAL);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
 
+    const int64_t row_base = (int64_t)blockIdx.x * TILE_ROWS;
+    if (io.count != nullptr) {
+        // the launch covers an upper bound of the samples; tiles behind the count a kernel before this one left leave at once
+        const int64_t counted = (int64_t)__ldg(io.count);
+        if (counted < io.n) io.n = counted;
+        if (row_base >= io.n) return;
+    }
     load_weights_to_smem<DS>(io.Wd, io.bd, sWd, sBd, tid);
     load_weights_to_smem<CS>(io.Wc, io.bc, sWc, sBc, tid);
     cp_async_commit();
-    const int64_t row_base = (int64_t)blockIdx.x * TILE_ROWS;
     encode_tile<FS::ENC_STRIDE>(gp, io.pos4, io.table2, row_base, io.n, tile, tid);
     cp_async_wait_all();
     __syncthreads();
@@ -510,11 +517,11 @@ extern "C" int nb_field_supported(const nb_grid_desc* grid, const nb_mlp_desc* d
            color->output_activation == 1;
 }
 
-extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
                                 const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
                                 const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
                                 int64_t n, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
-                                int rgb_stride, void* stream) {
+                                int rgb_stride, const uint32_t* d_count, void* stream) {
     if (!grid || !density || !color || !d_pos4 || !d_table_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b ||
         !d_rgb || n < 0)
         return nb_set_error(NB_ERR_INVALID, "nb_field_forward: null pointer or negative count");
@@ -529,7 +536,7 @@ extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* den
     io.pos4 = d_pos4; io.table2 = (const uint32_t*)d_table_h; io.dirs3 = d_dirs3; io.ray_idx = d_ray_indices;
     io.ray_idx_offset = ray_index_offset;
     io.Wd = (const __half*)d_density_w_h; io.bd = d_density_b; io.Wc = (const __half*)d_color_w_h; io.bc = d_color_b;
-    io.n = n; io.density_bias = density_bias;
+    io.n = n; io.density_bias = density_bias; io.count = d_count;
     auto kern = nb::field_forward_kernel<DensityNet, ColorNet>;
     size_t smem = nb::FieldSmem<DensityNet, ColorNet>::fwd_bytes();
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -540,6 +547,25 @@ extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* den
     NB_CHECK_LAUNCH();
     nb::g_launch_count++;
     return NB_OK;
+}
+
+extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                                const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                                const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
+                                int64_t n, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
+                                int rgb_stride, void* stream) {
+    return field_forward_impl(grid, density, color, d_pos4, d_table_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b,
+                              d_color_w_h, d_color_b, n, density_bias, d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride, nullptr, stream);
+}
+
+extern "C" int nb_field_forward_counted(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                                        const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices,
+                                        int64_t ray_index_offset, const void* d_density_w_h, const float* d_density_b,
+                                        const void* d_color_w_h, const float* d_color_b, int64_t n_max, const uint32_t* d_count,
+                                        float density_bias, float* d_sigma, float* d_rgb, int rgb_stride, void* stream) {
+    if (!d_count) return nb_set_error(NB_ERR_INVALID, "nb_field_forward_counted: null count");
+    return field_forward_impl(grid, density, color, d_pos4, d_table_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b,
+                              d_color_w_h, d_color_b, n_max, density_bias, nullptr, d_sigma, nullptr, d_rgb, rgb_stride, d_count, stream);
 }
 
 extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,

@@ -125,6 +125,72 @@ __global__ void __launch_bounds__(256) composite_infer_kernel(const uint32_t num
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// inference in rounds: the same front-to-back sum, cut into rounds of samples so that rays whose transmittance has
+// dropped below 1e-4 are not evaluated any further (the samples the reference's loop never reaches contribute
+// nothing to it either).  State per ray between rounds: transmittance and (r, g, b, depth) composited so far.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) composite_round_kernel(const uint32_t ray_begin, const uint32_t ray_count,
+                                                              const uint32_t* __restrict__ num_steps, const uint32_t* __restrict__ round_off,
+                                                              const float* __restrict__ rows, const uint32_t row_stride,
+                                                              const uint32_t round_begin, const uint32_t round_width,
+                                                              const float* __restrict__ sigma_in, const float* __restrict__ rgb_in,
+                                                              const int rgb_stride, float* __restrict__ transmittance,
+                                                              float4* __restrict__ composited, float* __restrict__ final_rgb,
+                                                              float* __restrict__ final_depth, float3 bg) {
+    const uint32_t local = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (local >= ray_count) return;
+    const uint32_t r = ray_begin + local;
+    const uint32_t n = num_steps[r];
+    float T = round_begin == 0 ? 1.0f : transmittance[r];
+    if (!(T >= 1e-4f && n > round_begin)) {  // the predicate round_emit_kernel planned this round with
+        if (round_begin == 0 && lane == 0) {
+            final_rgb[r * 3 + 0] = bg.x; final_rgb[r * 3 + 1] = bg.y; final_rgb[r * 3 + 2] = bg.z;
+            if (final_depth != nullptr) final_depth[r] = 0.0f;
+        }
+        return;
+    }
+    const uint32_t count = min(n - round_begin, round_width);
+    const uint32_t first = round_off[r];
+    const float* row = rows + (size_t)r * row_stride;
+    float cr = 0.f, cg = 0.f, cb = 0.f, depth = 0.f;
+    for (uint32_t w0 = 0; w0 < count; w0 += 32) {
+        const uint32_t i = w0 + lane;
+        const bool valid = i < count;
+        float alpha = 0.f, t = 0.f;
+        if (valid) {
+            const uint32_t k = round_begin + i;  // index of the sample in its ray
+            t = row[k];
+            float dt = (k + 1 < n) ? row[k + 1] - t : 1e-3f;
+            if (dt < 0.0f) dt = 0.0f;
+            alpha = 1.0f - expf(-sigma_in[first + i] * dt);
+        }
+        const float incl = warp_incl_prod(1.0f - alpha, lane);
+        const float T_before = T * from_lane_below(incl, lane, 1.0f);
+        const bool live = valid && T_before >= 1e-4f;
+        if (live) {
+            const float w = alpha * T_before;
+            const float* c = rgb_in + (size_t)(first + i) * rgb_stride;
+            cr += w * c[0]; cg += w * c[1]; cb += w * c[2];
+            depth += w * t;
+        }
+        const unsigned live_mask = __ballot_sync(FULL, live);
+        const int last = 31 - __clz((int)live_mask);
+        T = __shfl_sync(FULL, T * incl, last);
+        if (live_mask != __ballot_sync(FULL, valid) || T < 1e-4f) break;
+    }
+    cr = warp_sum(cr); cg = warp_sum(cg); cb = warp_sum(cb); depth = warp_sum(depth);
+    if (lane == 0) {
+        float4 acc = round_begin == 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : composited[r];
+        acc.x += cr; acc.y += cg; acc.z += cb; acc.w += depth;
+        composited[r] = acc;
+        transmittance[r] = T;
+        final_rgb[r * 3 + 0] = acc.x + T * bg.x; final_rgb[r * 3 + 1] = acc.y + T * bg.y; final_rgb[r * 3 + 2] = acc.z + T * bg.z;
+        if (final_depth != nullptr) final_depth[r] = acc.w;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // training: colour, depth, dL/dw of the distortion (and depth-prior) loss per sample, sum_i w_i dL/dw_i per ray
 // ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float disparity_warp(float t, float t_near, float inv_g_range) {
@@ -356,6 +422,25 @@ extern "C" int nb_color_grad(int64_t num_rays, uint32_t sample_base, const uint3
                                                                      logit_stride, d_color_out, color_stride, d_phi, d_final_rgb, d_dw_out,
                                                                      d_weight_sum, (__half*)d_color_grad_h, d_tmp_dsigma, loss_scale, density_bias,
                                                                      total_rays_batch);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_composite_round(uint32_t ray_begin, uint32_t ray_count, const uint32_t* d_num_steps, const uint32_t* d_round_offsets,
+                                  const float* d_t_rows, uint32_t round_begin, uint32_t round_width, const float* d_sigma, const float* d_rgb,
+                                  int rgb_stride, float* d_transmittance, float* d_composited4, float* d_final_rgb, float* d_final_depth,
+                                  const float* bg_color3, void* stream) {
+    if (!d_num_steps || !d_round_offsets || !d_t_rows || !d_sigma || !d_rgb || !d_transmittance || !d_composited4 || !d_final_rgb ||
+        !bg_color3 || rgb_stride < 3 || round_width == 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_composite_round: null pointer, empty round or rgb stride < 3");
+    if (reinterpret_cast<uintptr_t>(d_composited4) & 15u)
+        return nb_set_error(NB_ERR_INVALID, "nb_composite_round: the composited state must be 16-byte aligned");
+    if (ray_count > 0x3ffffffu) return nb_set_error(NB_ERR_INVALID, "nb_composite_round: too many rays");
+    if (ray_count == 0) return NB_OK;
+    composite_round_kernel<<<warp_grid(ray_count), 256, 0, (cudaStream_t)stream>>>(
+        ray_begin, ray_count, d_num_steps, d_round_offsets, d_t_rows, (uint32_t)nb_march_row_stride(), round_begin, round_width, d_sigma, d_rgb,
+        rgb_stride, d_transmittance, (float4*)d_composited4, d_final_rgb, d_final_depth, make_float3(bg_color3[0], bg_color3[1], bg_color3[2]));
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

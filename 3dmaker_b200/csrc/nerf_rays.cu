@@ -278,6 +278,66 @@ __global__ void __launch_bounds__(256) march_compact_kernel(const float3 aabb_mi
     }
 }
 
+// One round of front-to-back rendering: samples [round_begin, round_begin + round_width) of every ray of
+// [ray_begin, ray_begin + ray_count) that is still visible (transmittance at least 1e-4 after the rounds before) and
+// has that many samples.  A block plans 256 rays (count per ray, scan, ONE atomic on the round's counter for the
+// block's sample range) and its warps then copy the rays' samples out of the rows.  Sample ranges of different blocks
+// land in arrival order; a ray's own samples are contiguous and in order, which is all compositing needs.
+__global__ void __launch_bounds__(256) round_emit_kernel(const float3 aabb_min, const float3 aabb_max, const float3* __restrict__ rays_o,
+                                                         const float3* __restrict__ rays_d, uint32_t ray_begin, uint32_t ray_count,
+                                                         const uint32_t* __restrict__ num_steps, const float* __restrict__ transmittance,
+                                                         uint32_t round_begin, uint32_t round_width, const float* __restrict__ rows,
+                                                         uint32_t row_stride, uint32_t capacity, uint32_t* __restrict__ counter,
+                                                         uint32_t* __restrict__ round_off, uint32_t* __restrict__ ray_idx_out,
+                                                         float4* __restrict__ pos_out) {
+    __shared__ uint32_t s_warp[8], s_cnt[256], s_off[256], s_base;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t local = blockIdx.x * 256 + threadIdx.x;
+    uint32_t c = 0;
+    if (local < ray_count) {
+        const uint32_t i = ray_begin + local;
+        const uint32_t n = num_steps[i];
+        const bool visible = round_begin == 0 || transmittance[i] >= 1e-4f;
+        if (visible && n > round_begin) c = min(n - round_begin, round_width);
+    }
+    uint32_t incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    uint32_t before = 0, total = 0;
+#pragma unroll
+    for (uint32_t w = 0; w < 8; w++) {
+        const uint32_t v = s_warp[w];
+        if (w < warp) before += v;
+        total += v;
+    }
+    if (threadIdx.x == 0) s_base = total ? atomicAdd(counter, total) : 0u;
+    s_cnt[threadIdx.x] = c;
+    s_off[threadIdx.x] = before + incl - c;
+    __syncthreads();
+    const uint32_t base = s_base;
+    if (c > 0) round_off[ray_begin + local] = base + before + incl - c;
+    for (uint32_t j = warp; j < 256; j += 8) {
+        const uint32_t cj = s_cnt[j];
+        if (cj == 0) continue;
+        const uint32_t i = ray_begin + blockIdx.x * 256 + j;
+        const uint32_t dst = base + s_off[j];
+        if (dst + cj > capacity) continue;  // cannot happen when the caller's bound holds; never write past the arrays
+        const float3 o = rays_o[i], d = rays_d[i];
+        const float* row = rows + (size_t)i * row_stride + round_begin;
+        for (uint32_t k = lane; k < cj; k += 32) {
+            const float t = row[k];
+            ray_idx_out[dst + k] = i;
+            const float3 p = contract_pos(make_float3(o.x + t * d.x, o.y + t * d.y, o.z + t * d.z), aabb_min, aabb_max);
+            st_cs_v4(&pos_out[dst + k], make_uint4(__float_as_uint(p.x), __float_as_uint(p.y), __float_as_uint(p.z), 0u));
+        }
+    }
+}
+
 // ---- exclusive scan + cutoff --------------------------------------------------------------------------
 constexpr int SCAN_BLOCK = 1024;
 
@@ -514,6 +574,29 @@ extern "C" int nb_march_compact(const nb_scene_desc* scene, const float* d_rays_
     march_compact_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         sc.aabb_min, sc.aabb_max, (const float3*)d_rays_o, (const float3*)d_rays_d, ray_begin, ray_count, d_num_steps, d_ray_offsets, sample_base,
         d_t_rows, MAX_HITS, d_t_out, d_ray_idx_out, (float4*)d_pos4_out);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_march_round_emit(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, uint32_t ray_begin,
+                                   uint32_t ray_count, const uint32_t* d_num_steps, const float* d_transmittance, uint32_t round_begin,
+                                   uint32_t round_width, const float* d_t_rows, uint32_t capacity, uint32_t* d_counter,
+                                   uint32_t* d_round_offsets, uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream) {
+    int rc = check_scene(scene, "nb_march_round_emit: null scene");
+    if (rc) return rc;
+    if (!d_rays_o || !d_rays_d || !d_num_steps || !d_t_rows || !d_counter || !d_round_offsets || !d_ray_idx_out || !d_pos4_out ||
+        (round_begin > 0 && !d_transmittance))
+        return nb_set_error(NB_ERR_INVALID, "nb_march_round_emit: null pointer");
+    if (round_width == 0 || round_begin >= (uint32_t)MAX_HITS)
+        return nb_set_error(NB_ERR_INVALID, "nb_march_round_emit: the round must lie inside a row");
+    if (reinterpret_cast<uintptr_t>(d_pos4_out) & 15u)
+        return nb_set_error(NB_ERR_INVALID, "nb_march_round_emit: positions must be 16-byte aligned");
+    if (ray_count == 0) return NB_OK;
+    Scene sc = make_scene(scene);
+    round_emit_kernel<<<(ray_count + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        sc.aabb_min, sc.aabb_max, (const float3*)d_rays_o, (const float3*)d_rays_d, ray_begin, ray_count, d_num_steps, d_transmittance, round_begin,
+        round_width, d_t_rows, MAX_HITS, capacity, d_counter, d_round_offsets, d_ray_idx_out, (float4*)d_pos4_out);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

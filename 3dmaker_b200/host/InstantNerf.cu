@@ -147,6 +147,8 @@ void InstantNerf::initRenderBuffers() {
         }
         if (!w.done) throw_on_cuda(cudaEventCreateWithFlags(&w.done, cudaEventDisableTiming), "walk event");
     }
+    d_round_off.allocate(R * sizeof(uint32_t)); d_transmittance.allocate(R * sizeof(float)); d_composited.allocate(R * 4 * sizeof(float));
+    d_round_counters.allocate(kRoundCounters * sizeof(uint32_t), true);
     d_render_rgb.allocate(R * 3 * sizeof(float)); d_render_depth.allocate(R * sizeof(float)); d_phi.allocate(R * 3 * sizeof(float));
     d_weight_sum.allocate(R * sizeof(float));
 
@@ -467,6 +469,98 @@ void InstantNerf::optimizerStep(cudaStream_t stream) {
     });
 }
 
+// One walked chunk rendered front to back in rounds of samples per ray.  Round r covers samples [b_r, b_r + w_r) of
+// every ray that still has samples there and is not yet opaque; which rays those are is decided on the device
+// (nb_march_round_emit), the host only bounds each launch: a ray with n samples reaches round r when n > b_r, and a
+// round over k such rays holds at most k * w_r samples.  Ray ranges are cut at 1024-ray blocks so that this bound fits
+// the sample arrays (a single block that does not fit is cut ray by ray).
+void InstantNerf::renderChunkRounds(const WalkSet& w, const float* chunk_o, const float* chunk_d, uint32_t chunkRays, uint32_t capacity,
+                                    float* rgb_dst, cudaStream_t stream) {
+    static constexpr int kRounds = 7;
+    static constexpr uint32_t kBegin[kRounds] = {0, 16, 32, 64, 128, 256, 512};
+    static constexpr uint32_t kWidth[kRounds] = {16, 16, 32, 64, 128, 256, 512};
+    static_assert(kBegin[kRounds - 1] + kWidth[kRounds - 1] == 1024, "the rounds cover a whole row");
+    constexpr uint32_t BLOCK = 1024;
+    nb_scene_desc sc = scene();
+    TinyMLPHashGrid* dn = m_densityMLP;
+    TinyMLP* cn = m_colorMLP;
+    const float bg[3] = {m_opts.bgColor.x, m_opts.bgColor.y, m_opts.bgColor.z};
+    const uint32_t* off = w.h_offsets;
+    const uint32_t numBlocks = (chunkRays + BLOCK - 1) / BLOCK;
+    // m_roundRays[block * kRounds + r] = rays of the block with more than kBegin[r] samples
+    m_roundRays.assign((size_t)numBlocks * kRounds, 0u);
+    uint32_t reach[kRounds] = {0, 0, 0, 0, 0, 0, 0};
+    for (uint32_t b = 0; b < numBlocks; b++) {
+        uint32_t hist[kRounds + 1] = {0, 0, 0, 0, 0, 0, 0, 0};  // by the number of rounds a ray reaches
+        const uint32_t end = std::min(chunkRays, (b + 1) * BLOCK);
+        for (uint32_t i = b * BLOCK; i < end; i++) {
+            const uint32_t n = off[i + 1] - off[i];
+            // n in (0, 16] reaches 1 round, (16, 32] 2, (32, 64] 3, ... (512, 1024] 7
+            const uint32_t rounds = n == 0 ? 0u : (n <= 16 ? 1u : std::min<uint32_t>(kRounds, 29u - (uint32_t)__builtin_clz(n - 1)));
+            hist[rounds]++;
+        }
+        uint32_t rays = 0;
+        for (int r = kRounds - 1; r >= 0; r--) {
+            rays += hist[r + 1];
+            m_roundRays[(size_t)b * kRounds + r] = rays;
+            reach[r] += rays;
+        }
+    }
+    int slot = kRoundCounters;  // forces the first clear
+    auto launchRange = [&](int r, uint32_t begin, uint32_t end, uint64_t bound) {
+        if (r > 0 && bound == 0) return;  // nobody reaches the round; round 0 still writes the background
+        if (slot == kRoundCounters) {
+            throw_on_cuda(cudaMemsetAsync(d_round_counters.as<uint32_t>(), 0, kRoundCounters * sizeof(uint32_t), stream), "round counters");
+            slot = 0;
+        }
+        uint32_t* counter = d_round_counters.as<uint32_t>() + slot++;
+        throw_on_error(nb_march_round_emit(&sc, chunk_o, chunk_d, begin, end - begin, w.num_steps.as<uint32_t>(), d_transmittance.as<float>(),
+                                           kBegin[r], kWidth[r], w.rows.as<float>(), capacity, counter, d_round_off.as<uint32_t>(),
+                                           d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream), "march: round");
+        if (bound > 0) {
+            throw_on_error(nb_field_forward_counted(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
+                                                    chunk_d, d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()),
+                                                    m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()),
+                                                    (int64_t)bound, counter, m_opts.densityBias, d_sigma.as<float>(), d_color_out.as<float>(), 4,
+                                                    stream), "field inference");
+        }
+        throw_on_error(nb_composite_round(begin, end - begin, w.num_steps.as<uint32_t>(), d_round_off.as<uint32_t>(), w.rows.as<float>(), kBegin[r],
+                                          kWidth[r], d_sigma.as<float>(), d_color_out.as<float>(), 4, d_transmittance.as<float>(),
+                                          d_composited.as<float>(), rgb_dst, d_render_depth.as<float>(), bg, stream), "compositing");
+    };
+    for (int r = 0; r < kRounds; r++) {
+        if (r > 0 && reach[r] == 0) break;  // round 0 always runs: it writes the background of rays without samples
+        uint32_t rangeBegin = 0;
+        uint64_t bound = 0;
+        for (uint32_t b = 0; b < numBlocks; b++) {
+            const uint32_t blockBegin = b * BLOCK, blockEnd = std::min(chunkRays, (b + 1) * BLOCK);
+            const uint64_t blockBound = (uint64_t)m_roundRays[(size_t)b * kRounds + r] * kWidth[r];
+            if (blockBound > capacity) {
+                // a block that alone exceeds the arrays: flush what is pending, then cut this block ray by ray
+                if (blockBegin > rangeBegin) launchRange(r, rangeBegin, blockBegin, bound);
+                uint32_t begin = blockBegin;
+                uint64_t acc = 0;
+                for (uint32_t i = blockBegin; i < blockEnd; i++) {
+                    const uint32_t n = off[i + 1] - off[i];
+                    const uint32_t c = n > kBegin[r] ? std::min(n - kBegin[r], kWidth[r]) : 0u;
+                    if (c > capacity) throw std::runtime_error("renderImageHit: the sample batch is too small for one round of one ray");
+                    if (acc + c > capacity) { launchRange(r, begin, i, acc); begin = i; acc = 0; }
+                    acc += c;
+                }
+                launchRange(r, begin, blockEnd, acc);
+                rangeBegin = blockEnd; bound = 0;
+                continue;
+            }
+            if (bound + blockBound > capacity) {
+                launchRange(r, rangeBegin, blockBegin, bound);
+                rangeBegin = blockBegin; bound = 0;
+            }
+            bound += blockBound;
+        }
+        if (rangeBegin < chunkRays) launchRange(r, rangeBegin, chunkRays, bound);
+    }
+}
+
 void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d, uint32_t numRays, float* d_rgb_out, cudaStream_t stream) {
     if (!m_traininit) { std::fprintf(stderr, "[InstantNerf] Error: init() must be called before renderImageHit()\n"); return; }
     nb_scene_desc sc = scene();
@@ -488,6 +582,11 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
         const WalkSet& w = m_walk[set];
         const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + ray_offset);
         const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + ray_offset);
+        if (renderRounds()) {
+            renderChunkRounds(w, chunk_o, chunk_d, chunkRays, hitBatch, d_rgb_out != nullptr ? d_rgb_out + (size_t)ray_offset * 3 : d_render_rgb.as<float>(),
+                              stream);
+            continue;
+        }
         uint32_t raysDone = 0;
         while (raysDone < chunkRays) {
             const uint32_t next = cutRays(w.h_offsets, raysDone, chunkRays, hitBatch);

@@ -114,6 +114,11 @@ public:
     // on by default when the network shapes allow it.  Returns the mode now in effect.
     bool setFusedField(bool on);
     bool fusedField() const { return m_fused; }
+    // Rendering in rounds of samples per ray (16, 16, 32, 64, ...): rays are not evaluated behind the point where their
+    // transmittance has dropped below 1e-4, which the reference's compositing never reaches either.  On by default;
+    // needs the fused field kernels, otherwise (or when off) every sample of every ray is evaluated as in the reference.
+    void setRenderRounds(bool on) { m_renderRounds = on; }
+    bool renderRounds() const { return m_renderRounds && m_fused; }
     nb::ParamArena& arena() { return m_arena; }
     TinyMLPHashGrid* densityNetwork() { return m_densityMLP; }
     TinyMLP* colorNetwork() { return m_colorMLP; }
@@ -160,6 +165,7 @@ private:
     GradSync m_gradSync;
     uint32_t m_rayScale = 1;
     bool m_fused = false;
+    bool m_renderRounds = true;
     NerfPhaseTimes m_times;
 
     nb::DeviceMem d_occupancyGrid, d_masterOccupancyGrid;
@@ -180,6 +186,13 @@ private:
         cudaEvent_t done = nullptr;
     };
     WalkSet m_walk[2];
+    // rendering in rounds: per ray of the chunk its place in the round's sample arrays, transmittance and colour so far;
+    // one sample counter per (round, ray range), zeroed per chunk
+    nb::DeviceMem d_round_off, d_transmittance, d_composited, d_round_counters;
+    std::vector<uint32_t> m_roundRays;  // host scratch: per 1024-ray block and round, the rays that reach the round
+    static constexpr int kRoundCounters = 64;
+    void renderChunkRounds(const WalkSet& w, const float* chunk_o, const float* chunk_d, uint32_t chunkRays, uint32_t capacity, float* rgb_dst,
+                           cudaStream_t stream);
     uint32_t m_lastStepFirstRay = 0, m_lastSampleBase = 0;
 
     bool m_traininit = false;

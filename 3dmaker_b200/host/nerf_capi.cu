@@ -108,6 +108,12 @@ extern "C" int nb_nerf_set_fused_field(nb_nerf* h, int on) {
     return h->impl.setFusedField(on != 0) ? 1 : 0;
 }
 
+extern "C" int nb_nerf_set_render_rounds(nb_nerf* h, int on) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    h->impl.setRenderRounds(on != 0);
+    return h->impl.renderRounds() ? 1 : 0;
+}
+
 extern "C" int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     if (!fn) h->impl.setGradSync(nullptr);

@@ -92,6 +92,11 @@ class InstantNerf:
         """One kernel each way for the whole field (default) or the kernel-by-kernel sequence; returns the mode in effect."""
         return bool(self.lib.nb_nerf_set_fused_field(self.h, 1 if on else 0))
 
+    def set_render_rounds(self, on):
+        """Render in rounds of samples per ray, skipping what lies behind an opaque surface (default), or evaluate every
+        sample of every ray; returns the mode in effect."""
+        return bool(self.lib.nb_nerf_set_render_rounds(self.h, 1 if on else 0))
+
     def set_grad_sync(self, fn):
         """fn(grad_tensor) is called between backward and Adam with a float32 view of the gradient arena."""
         if fn is None:

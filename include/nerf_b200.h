@@ -195,6 +195,14 @@ int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const
                      float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb, int rgb_stride,
                      void* stream);
 
+/* nb_field_forward for rendering when the sample count is known only on the device: the launch covers n_max samples
+ * and tiles at or behind *d_count (read when the kernel runs; at most n_max) leave at once. */
+int nb_field_forward_counted(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                             const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                             const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
+                             int64_t n_max, const uint32_t* d_count, float density_bias, float* d_sigma, float* d_rgb, int rgb_stride,
+                             void* stream);
+
 /* Gradients of both networks, of the encoding and (optionally) of the hash table from the colour gradient.  Replaces
  * TinyMLP::backward (colour) -> compute_density_grad -> TinyMLPHashGrid::backward (modules/NeRF/InstantNerf.cu:506-561).
  * Hidden activations are derived again from d_enc_h inside the kernel.  d_dcolor_h fp16 [n][8] = dL/d(colour
@@ -300,6 +308,18 @@ int nb_march_fill(const nb_scene_desc* scene, const float* d_rays_o, const float
 int nb_march_compact(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, uint32_t ray_begin, uint32_t ray_count,
                      const uint32_t* d_num_steps, const uint32_t* d_ray_offsets, uint32_t sample_base, const float* d_t_rows,
                      float* d_t_out, uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
+/* Rendering in rounds (no counterpart in the reference, whose renderImageHit, InstantNerf.cu:880-990, evaluates every
+ * sample of every ray and lets render_rays_kernel skip the ones behind an opaque surface): round [round_begin,
+ * round_begin + round_width) of the rows of rays [ray_begin, ray_begin + ray_count) - all arrays are indexed by the ray's
+ * place in the walked chunk.  A ray takes part when it has more than round_begin samples and (round_begin > 0) its
+ * d_transmittance is still at least 1e-4.  Its samples land contiguously at d_round_offsets[ray] of the compact arrays
+ * (ray id = place in the chunk, contracted float4 position); *d_counter (zero before the call) is advanced by the
+ * round's sample total, which stays on the device: nb_field_forward_counted reads it there.  capacity = size of the
+ * compact arrays in samples; the caller bounds the round (rays x round_width) so that it fits. */
+int nb_march_round_emit(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, uint32_t ray_begin, uint32_t ray_count,
+                        const uint32_t* d_num_steps, const float* d_transmittance, uint32_t round_begin, uint32_t round_width,
+                        const float* d_t_rows, uint32_t capacity, uint32_t* d_counter, uint32_t* d_round_offsets,
+                        uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
 
 /* ---- compositing and loss gradients ---------------------------------------------------------- */
 
@@ -312,6 +332,16 @@ int nb_march_compact(const nb_scene_desc* scene, const float* d_rays_o, const fl
 int nb_composite_infer(int64_t num_rays, uint32_t base, uint32_t rays_done, const uint32_t* d_ray_offsets, const uint32_t* d_num_steps,
                        const float* d_t_sorted, const float* d_sigma, const float* d_rgb, int rgb_stride, const float* d_rgb_true,
                        float* d_final_rgb, float* d_final_depth, float* d_phi, const float* bg_color3, void* stream);
+
+/* One round of nb_composite_infer's sum for the rays nb_march_round_emit planned (same arguments, same predicate):
+ * continues from d_transmittance / d_composited4 (r, g, b, depth per ray; not read when round_begin == 0), stops a ray
+ * for good once its transmittance is below 1e-4 exactly where render_rays_kernel (compositing.cu:5-78) leaves its loop,
+ * and writes colour (+ transmittance x background) and depth so far into d_final_rgb / d_final_depth (nullable) at the
+ * ray's place in the chunk.  Round 0 writes every ray of the range (background for rays without samples). */
+int nb_composite_round(uint32_t ray_begin, uint32_t ray_count, const uint32_t* d_num_steps, const uint32_t* d_round_offsets,
+                       const float* d_t_rows, uint32_t round_begin, uint32_t round_width, const float* d_sigma, const float* d_rgb,
+                       int rgb_stride, float* d_transmittance, float* d_composited4, float* d_final_rgb, float* d_final_depth,
+                       const float* bg_color3, void* stream);
 
 /* Replaces render_rays_distortion_kernel via launchVolumeRendering with d_dw_out != NULL
  * (modules/NeRF/compositing.cu:84-213).  d_depth_prior / d_sigma_prior may be NULL (depth supervision off). */
@@ -427,6 +457,11 @@ int nb_nerf_set_steps_per_call(nb_nerf* h, int steps);
  * kernel-by-kernel sequence; returns 1 when the fused kernels are in effect afterwards, 0 otherwise.  Results agree
  * to the fp32 summation order of the weight gradients.  No counterpart in the reference. */
 int nb_nerf_set_fused_field(nb_nerf* h, int on);
+/* Rendering in rounds of samples per ray (nb_march_round_emit / nb_field_forward_counted / nb_composite_round), so that
+ * nothing is evaluated behind the point where a ray turned opaque: on by default with the fused field kernels; off = every
+ * sample of every ray, as the reference's renderImageHit does.  Returns 1 when rounds are in effect afterwards.  Frames
+ * agree to fp32 rounding (the skipped samples have weight zero in both).  No counterpart in the reference. */
+int nb_nerf_set_render_rounds(nb_nerf* h, int on);
 /* Device pointers of the parameter arena [hash | density W,b | colour W,b] and the slice offsets. */
 int nb_nerf_get_arena(nb_nerf* h, nb_nerf_arena_view* out);
 /* loadHashgrid / loadWeights of both networks from host fp32 arrays (any may be NULL);

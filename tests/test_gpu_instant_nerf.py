@@ -124,6 +124,14 @@ def test_training_converges_and_renders(cuda, nb, tmp_path):
     p = syn.psnr(torch, img, gt)
     print("PSNR after %d steps: %.2f dB" % (eng.steps.value, p))
     assert p > 24.0
+    # the trained sphere is opaque: rendering in rounds (default) stops evaluating rays behind its surface and still gives
+    # the picture that evaluating every sample gives
+    assert eng.set_render_rounds(False) is False
+    full = torch.zeros_like(img)
+    eng.render(o, d, full)
+    torch.cuda.synchronize()
+    assert eng.set_render_rounds(True) is True
+    assert float((img - full).abs().max()) <= 1e-5
     bits, master = eng.occupancy()
     occ = np.unpackbits(bits.cpu().numpy()[:128 ** 3 // 8]).mean()
     assert 0.02 < occ < 0.6                                               # the grid has carved away empty space
@@ -150,20 +158,24 @@ def test_render_batching_is_invisible(cuda, nb):
                 color_hidden_dim=64, color_num_layers=3, batch_size=1 << 16, ray_chunk_size=1 << 12, density_bias=-2.0)
     imgs = []
     o, d = syn.frame_rays(torch, syn.orbit_c2w(10.0, 5.0, 1.5), 96, 96, 50.0)
-    for rb in (1 << 20, 3000):
+    for rb, rounds in ((1 << 20, True), (3000, True), (1 << 20, False), (3000, False)):
         eng = nm.InstantNerf(torch, nm.default_options(render_batch_size=rb, **base), inference=True)
+        assert eng.set_render_rounds(rounds) is rounds
         img = torch.zeros((96 * 96, 3), device="cuda")
         eng.render(o, d, img)
         torch.cuda.synchronize()
         imgs.append(img)
         eng.close()
-    assert torch.equal(imgs[0], imgs[1])
+    assert torch.equal(imgs[0], imgs[1]) and torch.equal(imgs[2], imgs[3])
     assert imgs[0].std() > 1e-3
-    # the kernel-by-kernel sequence renders the same picture as the single field kernel, bit for bit
+    # rendering in rounds sums each ray in pieces: the same picture up to fp32 rounding
+    assert float((imgs[0] - imgs[2]).abs().max()) <= 1e-5
+    # the kernel-by-kernel sequence (which evaluates every sample) renders the same picture as the single field kernel
+    # does on every sample, bit for bit
     eng = nm.InstantNerf(torch, nm.default_options(render_batch_size=1 << 20, **base), inference=True)
     assert eng.set_fused_field(False) is False
     img = torch.zeros((96 * 96, 3), device="cuda")
     eng.render(o, d, img)
     torch.cuda.synchronize()
     eng.close()
-    assert torch.equal(imgs[0], img)
+    assert torch.equal(imgs[2], img)

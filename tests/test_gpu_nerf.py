@@ -237,6 +237,73 @@ def test_compositing_and_color_grad(cuda, nb, orc, R):
     assert torch.equal(grad_b, grad[base:]) and torch.equal(dsig_b, dsig[base:]) and torch.equal(rgb_i, rgb2[k:])
 
 
+@pytest.mark.parametrize("capacity_rays", [None, 700])
+def test_rendering_in_rounds_equals_the_single_pass(cuda, nb, orc, capacity_rays):
+    """nb_march_round_emit + nb_composite_round over the rounds 16, 16, 32, ... against nb_composite_infer on the same
+    rays: same colour and depth to fp32 rounding, and rays that turned opaque are not emitted again."""
+    torch = cuda
+    up = Uploader(torch, nb)
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    counts, off, t, dens, col, _ = _random_ray_samples(5000, 11, max_count=200)
+    R, n = len(counts), len(t)
+    sigma = np.exp(np.minimum(dens[:, 0] - np.float32(1.0), 8)).astype(np.float32)
+    bg = (ctypes.c_float * 3)(1.0, 0.5, 0.25)
+    f32, i32 = torch.float32, torch.int32
+    d_off, d_cnt, d_t, d_sig, d_col = up.f(off.view(np.int32)), up.f(counts.view(np.int32)), up.f(t), up.f(sigma), up.f(col)
+    want = torch.zeros((R, 3), dtype=f32, device="cuda"); want_depth = torch.zeros(R, dtype=f32, device="cuda")
+    nb.check(lib.nb_composite_infer(R, 0, 0, d_off, d_cnt, d_t, d_sig, d_col, 8, None, P(want), P(want_depth), None, bg, st), "nb_composite_infer")
+    # rows as the walk leaves them
+    stride = lib.nb_march_row_stride()
+    rows_np = np.zeros((R, stride), np.float32)
+    for r in range(R):
+        rows_np[r, :counts[r]] = t[off[r]:off[r] + counts[r]]
+    rows = torch.from_numpy(rows_np).cuda()
+    sc = _scene(nb, (32, 32, 32), 1, 3, 1)
+    rng = np.random.default_rng(3)
+    o = torch.from_numpy(rng.normal(0, 0.1, (R, 3)).astype(np.float32)).cuda()
+    dirs = rng.normal(0, 1, (R, 3)).astype(np.float32); dirs /= np.linalg.norm(dirs, axis=1, keepdims=True)
+    d = torch.from_numpy(dirs).cuda()
+    cap = 1 << 20
+    pos = torch.zeros((cap, 4), dtype=f32, device="cuda"); ridx = torch.zeros(cap, dtype=i32, device="cuda")
+    roff = torch.zeros(R, dtype=i32, device="cuda"); T = torch.full((R,), 7.0, dtype=f32, device="cuda")
+    acc = torch.full((R, 4), 7.0, dtype=f32, device="cuda")
+    got = torch.full((R, 3), -1.0, dtype=f32, device="cuda"); got_depth = torch.full((R,), -1.0, dtype=f32, device="cuda")
+    sig_all, col_all, off_all = torch.from_numpy(sigma).cuda(), torch.from_numpy(col).cuda(), torch.from_numpy(off.astype(np.int64)).cuda()
+    begin, emitted, reached = 0, 0, 0
+    for width in (16, 16, 32, 64, 128, 256, 512):
+        step = R if capacity_rays is None else capacity_rays
+        for r0 in range(0, R, step):
+            rc = min(step, R - r0)
+            counter = torch.zeros(1, dtype=i32, device="cuda")
+            nb.check(lib.nb_march_round_emit(ctypes.byref(sc), P(o), P(d), r0, rc, d_cnt, P(T), begin, width, P(rows), cap, P(counter), P(roff),
+                                             P(ridx), P(pos), st), "nb_march_round_emit")
+            torch.cuda.synchronize()
+            m = int(counter.item())
+            reach = np.clip(counts[r0:r0 + rc].astype(np.int64) - begin, 0, width)
+            assert m <= reach.sum()
+            emitted += m; reached += int(reach.sum())
+            # the field's part: sigma and colour of the emitted samples, looked up by (ray, sample index in the ray)
+            ray = ridx[:m].long()
+            assert m == 0 or (int(ray.min()) >= r0 and int(ray.max()) < r0 + rc)
+            k = begin + torch.arange(m, device="cuda") - roff.long()[ray]
+            assert m == 0 or (int(k.min()) >= begin and int(k.max()) < begin + width)
+            src = off_all[ray] + k
+            s_round = sig_all[src].contiguous(); c_round = col_all[src].contiguous()
+            # positions are those of the row entries
+            tt = rows[ray, k]
+            if m:
+                p_want = orc.contract_pos((o[ray] + tt[:, None] * d[ray]).cpu().numpy(), (-0.5,) * 3, (0.5,) * 3)
+                assert np.allclose(pos[:m, :3].cpu().numpy(), p_want, atol=2e-6)
+            nb.check(lib.nb_composite_round(r0, rc, d_cnt, P(roff), P(rows), begin, width, P(s_round), P(c_round), 8, P(T), P(acc), P(got),
+                                            P(got_depth), bg, st), "nb_composite_round")
+            torch.cuda.synchronize()
+        begin += width
+    assert float((got - want).abs().max()) <= 1e-5
+    assert torch.allclose(got_depth, want_depth, rtol=1e-5, atol=1e-5)
+    assert emitted < reached                                       # opaque rays dropped out before their last round
+    assert emitted >= int(np.minimum(counts, 16).sum())            # ... but every ray took part in the first
+
+
 def test_occupancy_kernels(cuda, nb, orc):
     torch = cuda
     up = Uploader(torch, nb)
