@@ -192,7 +192,7 @@ _SIGNATURES = {
                                  ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_march_round_emit": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p,
                                     ctypes.c_uint32, ctypes.c_uint32, c_void_p, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_void_p]),
+                                    c_void_p, c_void_p]),
     "nb_march_emit": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                               ctypes.c_uint32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_composite_infer": (c_int, [c_int64, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -223,6 +223,7 @@ _SIGNATURES = {
     "nb_nerf_set_global_ray_scale": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_fused_field": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_render_rounds": (c_int, [c_void_p, c_int]),
+    "nb_nerf_last_render_samples": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint64)]),
     "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_steps_per_call": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),

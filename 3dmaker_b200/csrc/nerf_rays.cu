@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(256) round_emit_kernel(const float3 aabb_min, 
                                                          const uint32_t* __restrict__ num_steps, const float* __restrict__ transmittance,
                                                          uint32_t round_begin, uint32_t round_width, const float* __restrict__ rows,
                                                          uint32_t row_stride, uint32_t capacity, uint32_t* __restrict__ counter,
-                                                         uint32_t* __restrict__ round_off, uint32_t* __restrict__ ray_idx_out,
+                                                         unsigned long long* __restrict__ emitted_total, uint32_t* __restrict__ round_off, uint32_t* __restrict__ ray_idx_out,
                                                          float4* __restrict__ pos_out) {
     __shared__ uint32_t s_warp[8], s_cnt[256], s_off[256], s_base;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -315,7 +315,10 @@ __global__ void __launch_bounds__(256) round_emit_kernel(const float3 aabb_min, 
         if (w < warp) before += v;
         total += v;
     }
-    if (threadIdx.x == 0) s_base = total ? atomicAdd(counter, total) : 0u;
+    if (threadIdx.x == 0) {
+        s_base = total ? atomicAdd(counter, total) : 0u;
+        if (total && emitted_total != nullptr) atomicAdd(emitted_total, (unsigned long long)total);
+    }
     s_cnt[threadIdx.x] = c;
     s_off[threadIdx.x] = before + incl - c;
     __syncthreads();
@@ -582,7 +585,8 @@ extern "C" int nb_march_compact(const nb_scene_desc* scene, const float* d_rays_
 extern "C" int nb_march_round_emit(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, uint32_t ray_begin,
                                    uint32_t ray_count, const uint32_t* d_num_steps, const float* d_transmittance, uint32_t round_begin,
                                    uint32_t round_width, const float* d_t_rows, uint32_t capacity, uint32_t* d_counter,
-                                   uint32_t* d_round_offsets, uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream) {
+                                   uint64_t* d_emitted_total, uint32_t* d_round_offsets, uint32_t* d_ray_idx_out, float* d_pos4_out,
+                                   void* stream) {
     int rc = check_scene(scene, "nb_march_round_emit: null scene");
     if (rc) return rc;
     if (!d_rays_o || !d_rays_d || !d_num_steps || !d_t_rows || !d_counter || !d_round_offsets || !d_ray_idx_out || !d_pos4_out ||
@@ -596,7 +600,8 @@ extern "C" int nb_march_round_emit(const nb_scene_desc* scene, const float* d_ra
     Scene sc = make_scene(scene);
     round_emit_kernel<<<(ray_count + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
         sc.aabb_min, sc.aabb_max, (const float3*)d_rays_o, (const float3*)d_rays_d, ray_begin, ray_count, d_num_steps, d_transmittance, round_begin,
-        round_width, d_t_rows, MAX_HITS, capacity, d_counter, d_round_offsets, d_ray_idx_out, (float4*)d_pos4_out);
+        round_width, d_t_rows, MAX_HITS, capacity, d_counter, (unsigned long long*)d_emitted_total, d_round_offsets, d_ray_idx_out,
+        (float4*)d_pos4_out);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

@@ -148,7 +148,7 @@ void InstantNerf::initRenderBuffers() {
         if (!w.done) throw_on_cuda(cudaEventCreateWithFlags(&w.done, cudaEventDisableTiming), "walk event");
     }
     d_round_off.allocate(R * sizeof(uint32_t)); d_transmittance.allocate(R * sizeof(float)); d_composited.allocate(R * 4 * sizeof(float));
-    d_round_counters.allocate(kRoundCounters * sizeof(uint32_t), true);
+    d_round_counters.allocate(kRoundCounters * sizeof(uint32_t), true); d_render_samples.allocate(sizeof(uint64_t), true);
     d_render_rgb.allocate(R * 3 * sizeof(float)); d_render_depth.allocate(R * sizeof(float)); d_phi.allocate(R * 3 * sizeof(float));
     d_weight_sum.allocate(R * sizeof(float));
 
@@ -515,7 +515,8 @@ void InstantNerf::renderChunkRounds(const WalkSet& w, const float* chunk_o, cons
         }
         uint32_t* counter = d_round_counters.as<uint32_t>() + slot++;
         throw_on_error(nb_march_round_emit(&sc, chunk_o, chunk_d, begin, end - begin, w.num_steps.as<uint32_t>(), d_transmittance.as<float>(),
-                                           kBegin[r], kWidth[r], w.rows.as<float>(), capacity, counter, d_round_off.as<uint32_t>(),
+                                           kBegin[r], kWidth[r], w.rows.as<float>(), capacity, counter, d_render_samples.as<uint64_t>(),
+                                           d_round_off.as<uint32_t>(),
                                            d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream), "march: round");
         if (bound > 0) {
             throw_on_error(nb_field_forward_counted(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
@@ -572,6 +573,8 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
     // its batches, the device is already walking the next chunk, so the one read-back per chunk never leaves it idle.
     const uint32_t chunk = (uint32_t)m_opts.rayChunkSize;
     const uint32_t numChunks = (numRays + chunk - 1) / chunk;
+    m_renderSamplesHost = 0;
+    throw_on_cuda(cudaMemsetAsync(d_render_samples.as<uint64_t>(), 0, sizeof(uint64_t), stream), "render statistics");
     if (numChunks > 0) walkRays(d_rays_o, d_rays_d, 0, std::min(chunk, numRays), stream, 0, false);
     for (uint32_t k = 0; k < numChunks; k++) {
         const uint32_t ray_offset = k * chunk;
@@ -597,6 +600,7 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
             const uint32_t crrRays = next - raysDone;
             const uint32_t base = w.h_offsets[raysDone];
             const int64_t n = w.h_offsets[next] - base;
+            m_renderSamplesHost += (uint64_t)n;
             if (n > 0) {
                 throw_on_error(nb_march_compact(&sc, chunk_o, chunk_d, raysDone, crrRays, w.num_steps.as<uint32_t>(), w.offsets.as<uint32_t>(), base,
                                                 w.rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
@@ -625,6 +629,13 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
             raysDone += crrRays;
         }
     }
+}
+
+uint64_t InstantNerf::lastRenderSamples() {
+    uint64_t emitted = 0;
+    if (d_render_samples.bytes() >= sizeof(uint64_t))
+        throw_on_cuda(cudaMemcpy(&emitted, d_render_samples.as<uint64_t>(), sizeof(uint64_t), cudaMemcpyDeviceToHost), "render statistics");
+    return emitted + m_renderSamplesHost;
 }
 
 // .inerf: "INERF1", raw NerfOptions, fp32 hash table, density W then b, colour W then b (sized for a 16-wide colour

@@ -115,10 +115,14 @@ public:
     bool setFusedField(bool on);
     bool fusedField() const { return m_fused; }
     // Rendering in rounds of samples per ray (16, 16, 32, 64, ...): rays are not evaluated behind the point where their
-    // transmittance has dropped below 1e-4, which the reference's compositing never reaches either.  On by default;
-    // needs the fused field kernels, otherwise (or when off) every sample of every ray is evaluated as in the reference.
+    // transmittance has dropped below 1e-4, which the reference's compositing never reaches either.  Pays when surfaces
+    // hide much of what the occupancy grid keeps (about half the samples of a many-object scene) and costs a few
+    // launches per chunk when they do not, so it is off by default; needs the fused field kernels.  When off, every
+    // sample of every ray is evaluated as in the reference.
     void setRenderRounds(bool on) { m_renderRounds = on; }
     bool renderRounds() const { return m_renderRounds && m_fused; }
+    // samples the field was evaluated on during the last renderImageHit call (waits for the device)
+    uint64_t lastRenderSamples();
     nb::ParamArena& arena() { return m_arena; }
     TinyMLPHashGrid* densityNetwork() { return m_densityMLP; }
     TinyMLP* colorNetwork() { return m_colorMLP; }
@@ -165,7 +169,7 @@ private:
     GradSync m_gradSync;
     uint32_t m_rayScale = 1;
     bool m_fused = false;
-    bool m_renderRounds = true;
+    bool m_renderRounds = false;
     NerfPhaseTimes m_times;
 
     nb::DeviceMem d_occupancyGrid, d_masterOccupancyGrid;
@@ -188,7 +192,8 @@ private:
     WalkSet m_walk[2];
     // rendering in rounds: per ray of the chunk its place in the round's sample arrays, transmittance and colour so far;
     // one sample counter per (round, ray range), zeroed per chunk
-    nb::DeviceMem d_round_off, d_transmittance, d_composited, d_round_counters;
+    nb::DeviceMem d_round_off, d_transmittance, d_composited, d_round_counters, d_render_samples;
+    uint64_t m_renderSamplesHost = 0;  // the part of the count the host knows (every sample, when not in rounds)
     std::vector<uint32_t> m_roundRays;  // host scratch: per 1024-ray block and round, the rays that reach the round
     static constexpr int kRoundCounters = 64;
     void renderChunkRounds(const WalkSet& w, const float* chunk_o, const float* chunk_d, uint32_t chunkRays, uint32_t capacity, float* rgb_dst,

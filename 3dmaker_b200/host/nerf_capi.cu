@@ -114,6 +114,11 @@ extern "C" int nb_nerf_set_render_rounds(nb_nerf* h, int on) {
     return h->impl.renderRounds() ? 1 : 0;
 }
 
+extern "C" int nb_nerf_last_render_samples(nb_nerf* h, uint64_t* samples) {
+    if (!h || !samples) return nb_set_error(NB_ERR_INVALID, "nb_nerf_last_render_samples: null pointer");
+    NB_GUARD(*samples = h->impl.lastRenderSamples())
+}
+
 extern "C" int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     if (!fn) h->impl.setGradSync(nullptr);

@@ -93,9 +93,15 @@ class InstantNerf:
         return bool(self.lib.nb_nerf_set_fused_field(self.h, 1 if on else 0))
 
     def set_render_rounds(self, on):
-        """Render in rounds of samples per ray, skipping what lies behind an opaque surface (default), or evaluate every
-        sample of every ray; returns the mode in effect."""
+        """Render in rounds of samples per ray, skipping what lies behind an opaque surface, or evaluate every sample of
+        every ray (default); returns the mode in effect."""
         return bool(self.lib.nb_nerf_set_render_rounds(self.h, 1 if on else 0))
+
+    def last_render_samples(self):
+        """Samples the field was evaluated on during the last render() (waits for the device)."""
+        n = ctypes.c_uint64(0)
+        nb.check(self.lib.nb_nerf_last_render_samples(self.h, ctypes.byref(n)), "nb_nerf_last_render_samples")
+        return int(n.value)
 
     def set_grad_sync(self, fn):
         """fn(grad_tensor) is called between backward and Adam with a float32 view of the gradient arena."""

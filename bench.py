@@ -712,6 +712,7 @@ def run_render(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item()) / args.steps
     if rank == 0:
+        frame_samples = None if reference else eng.last_render_samples() * nranks   # this rank's share of the last frame, scaled
         scene = syn.SoftSphereScene()
         o, d = syn.frame_rays(torch, pose["c2w"], W // 4, H // 4, 50.0)
         gt = syn.ground_truth(torch, scene, o, d, (1.0, 1.0, 1.0))
@@ -723,7 +724,8 @@ def run_render(args, rank, world, local_rank):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": RENDER_WORKLOAD % train_steps, "frame": [W, H], "tile_pixels": 1 << 14,
                            "gather_bytes_per_frame": D.gathered_bytes(W * H, nranks, 1 << 14),
-                           "psnr_quarter_res_db": float(syn.psnr(torch, small, gt)), "frame_mean": float(img.mean().item())}}
+                           "psnr_quarter_res_db": float(syn.psnr(torch, small, gt)), "frame_mean": float(img.mean().item()),
+                           "field_samples_per_frame": frame_samples}}
         if reference:
             line["impl"] = "reference"
         print(json.dumps(line))

@@ -315,11 +315,12 @@ int nb_march_compact(const nb_scene_desc* scene, const float* d_rays_o, const fl
  * d_transmittance is still at least 1e-4.  Its samples land contiguously at d_round_offsets[ray] of the compact arrays
  * (ray id = place in the chunk, contracted float4 position); *d_counter (zero before the call) is advanced by the
  * round's sample total, which stays on the device: nb_field_forward_counted reads it there.  capacity = size of the
- * compact arrays in samples; the caller bounds the round (rays x round_width) so that it fits. */
+ * compact arrays in samples; the caller bounds the round (rays x round_width) so that it fits.  d_emitted_total
+ * (nullable) is a running 64-bit sum of the samples emitted, for statistics. */
 int nb_march_round_emit(const nb_scene_desc* scene, const float* d_rays_o, const float* d_rays_d, uint32_t ray_begin, uint32_t ray_count,
                         const uint32_t* d_num_steps, const float* d_transmittance, uint32_t round_begin, uint32_t round_width,
-                        const float* d_t_rows, uint32_t capacity, uint32_t* d_counter, uint32_t* d_round_offsets,
-                        uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
+                        const float* d_t_rows, uint32_t capacity, uint32_t* d_counter, uint64_t* d_emitted_total,
+                        uint32_t* d_round_offsets, uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
 
 /* ---- compositing and loss gradients ---------------------------------------------------------- */
 
@@ -458,10 +459,13 @@ int nb_nerf_set_steps_per_call(nb_nerf* h, int steps);
  * to the fp32 summation order of the weight gradients.  No counterpart in the reference. */
 int nb_nerf_set_fused_field(nb_nerf* h, int on);
 /* Rendering in rounds of samples per ray (nb_march_round_emit / nb_field_forward_counted / nb_composite_round), so that
- * nothing is evaluated behind the point where a ray turned opaque: on by default with the fused field kernels; off = every
- * sample of every ray, as the reference's renderImageHit does.  Returns 1 when rounds are in effect afterwards.  Frames
- * agree to fp32 rounding (the skipped samples have weight zero in both).  No counterpart in the reference. */
+ * nothing is evaluated behind the point where a ray turned opaque.  Off by default (every sample of every ray, as the
+ * reference's renderImageHit does): it pays when surfaces hide much of what the occupancy grid keeps and costs a few
+ * launches per ray chunk when they do not.  Needs the fused field kernels; returns 1 when rounds are in effect afterwards.
+ * Frames agree to fp32 rounding (the skipped samples have weight zero in both).  No counterpart in the reference. */
 int nb_nerf_set_render_rounds(nb_nerf* h, int on);
+/* Samples the field was evaluated on during the last nb_nerf_render call (waits for the device). */
+int nb_nerf_last_render_samples(nb_nerf* h, uint64_t* samples);
 /* Device pointers of the parameter arena [hash | density W,b | colour W,b] and the slice offsets. */
 int nb_nerf_get_arena(nb_nerf* h, nb_nerf_arena_view* out);
 /* loadHashgrid / loadWeights of both networks from host fp32 arrays (any may be NULL);

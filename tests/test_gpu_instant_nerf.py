@@ -124,14 +124,16 @@ def test_training_converges_and_renders(cuda, nb, tmp_path):
     p = syn.psnr(torch, img, gt)
     print("PSNR after %d steps: %.2f dB" % (eng.steps.value, p))
     assert p > 24.0
-    # the trained sphere is opaque: rendering in rounds (default) stops evaluating rays behind its surface and still gives
-    # the picture that evaluating every sample gives
-    assert eng.set_render_rounds(False) is False
-    full = torch.zeros_like(img)
-    eng.render(o, d, full)
-    torch.cuda.synchronize()
+    # rendering in rounds stops evaluating rays behind the point where they turned opaque and still gives the picture that
+    # evaluating every sample gives
+    every = eng.last_render_samples()
     assert eng.set_render_rounds(True) is True
-    assert float((img - full).abs().max()) <= 1e-5
+    part = torch.zeros_like(img)
+    eng.render(o, d, part)
+    torch.cuda.synchronize()
+    assert 0 < eng.last_render_samples() < every
+    assert eng.set_render_rounds(False) is False
+    assert float((img - part).abs().max()) <= 1e-5
     bits, master = eng.occupancy()
     occ = np.unpackbits(bits.cpu().numpy()[:128 ** 3 // 8]).mean()
     assert 0.02 < occ < 0.6                                               # the grid has carved away empty space

@@ -269,13 +269,14 @@ def test_rendering_in_rounds_equals_the_single_pass(cuda, nb, orc, capacity_rays
     acc = torch.full((R, 4), 7.0, dtype=f32, device="cuda")
     got = torch.full((R, 3), -1.0, dtype=f32, device="cuda"); got_depth = torch.full((R,), -1.0, dtype=f32, device="cuda")
     sig_all, col_all, off_all = torch.from_numpy(sigma).cuda(), torch.from_numpy(col).cuda(), torch.from_numpy(off.astype(np.int64)).cuda()
+    total = torch.zeros(1, dtype=torch.int64, device="cuda")
     begin, emitted, reached = 0, 0, 0
     for width in (16, 16, 32, 64, 128, 256, 512):
         step = R if capacity_rays is None else capacity_rays
         for r0 in range(0, R, step):
             rc = min(step, R - r0)
             counter = torch.zeros(1, dtype=i32, device="cuda")
-            nb.check(lib.nb_march_round_emit(ctypes.byref(sc), P(o), P(d), r0, rc, d_cnt, P(T), begin, width, P(rows), cap, P(counter), P(roff),
+            nb.check(lib.nb_march_round_emit(ctypes.byref(sc), P(o), P(d), r0, rc, d_cnt, P(T), begin, width, P(rows), cap, P(counter), P(total), P(roff),
                                              P(ridx), P(pos), st), "nb_march_round_emit")
             torch.cuda.synchronize()
             m = int(counter.item())
@@ -288,7 +289,8 @@ def test_rendering_in_rounds_equals_the_single_pass(cuda, nb, orc, capacity_rays
             k = begin + torch.arange(m, device="cuda") - roff.long()[ray]
             assert m == 0 or (int(k.min()) >= begin and int(k.max()) < begin + width)
             src = off_all[ray] + k
-            s_round = sig_all[src].contiguous(); c_round = col_all[src].contiguous()
+            s_round = sig_all[src].contiguous() if m else torch.zeros(1, device="cuda")
+            c_round = col_all[src].contiguous() if m else torch.zeros((1, 8), device="cuda")
             # positions are those of the row entries
             tt = rows[ray, k]
             if m:
@@ -300,6 +302,7 @@ def test_rendering_in_rounds_equals_the_single_pass(cuda, nb, orc, capacity_rays
         begin += width
     assert float((got - want).abs().max()) <= 1e-5
     assert torch.allclose(got_depth, want_depth, rtol=1e-5, atol=1e-5)
+    assert int(total.item()) == emitted
     assert emitted < reached                                       # opaque rays dropped out before their last round
     assert emitted >= int(np.minimum(counts, 16).sum())            # ... but every ray took part in the first
 
