@@ -12,7 +12,7 @@ def np_hash(cx, cy, cz, T):
                 (cz.astype(np.uint32) * np.uint32(805459861))) & np.uint32(T - 1)
 
 
-def test_dense_level_start_matches_survey_values(orc):
+def test_dense_level_start_matches_known_values(orc):
     # T = 2^19: levels 0..4 are dense for both growth factors; T = 2^22: 7 (b=1.447) and 8 (b=1.3819)
     assert orc.dense_level_start(1 << 19, 16, 1.447, 16) == 5
     assert orc.dense_level_start(1 << 19, 16, 1.3819, 16) == 5
