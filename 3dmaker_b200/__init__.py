@@ -227,6 +227,7 @@ _SIGNATURES = {
     "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_steps_per_call": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
+    "nb_nerf_set_grad_buffer": (c_int, [c_void_p, c_void_p, c_int64]),
     "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),
     "nb_nerf_load_params": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_nerf_occupancy": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), ctypes.POINTER(c_void_p)]),

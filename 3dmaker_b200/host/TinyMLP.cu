@@ -30,10 +30,18 @@ void DeviceMem::allocate(size_t bytes, bool zero) {
     if (zero) throw_on_cuda(cudaMemset(ptr_, 0, bytes), "cudaMemset");
 }
 
+void DeviceMem::adopt(void* ptr, size_t bytes) {
+    release();
+    ptr_ = ptr;
+    bytes_ = ptr ? bytes : 0;
+    owned_ = false;
+}
+
 void DeviceMem::release() {
-    if (ptr_) cudaFree(ptr_);
+    if (ptr_ && owned_) cudaFree(ptr_);
     ptr_ = nullptr;
     bytes_ = 0;
+    owned_ = true;
 }
 
 void ParamArena::allocate(int64_t total_elems, int64_t sparse_elems, bool with_training) {
@@ -45,7 +53,23 @@ void ParamArena::allocate(int64_t total_elems, int64_t sparse_elems, bool with_t
     if (with_training) enable_training();
 }
 
+void ParamArena::set_external_grad(float* ptr) {
+    external_grad = ptr;
+    if (!training) return;
+    g.release();
+    if (ptr) {
+        g.adopt(ptr, (size_t)total * sizeof(float));
+        throw_on_cuda(cudaMemset(ptr, 0, (size_t)total * sizeof(float)), "cudaMemset");
+    } else {
+        g.allocate((size_t)total * sizeof(float), true);
+    }
+}
+
 void ParamArena::enable_training() {
+    if (!g && external_grad) {
+        g.adopt(external_grad, (size_t)total * sizeof(float));
+        throw_on_cuda(cudaMemset(external_grad, 0, (size_t)total * sizeof(float)), "cudaMemset");
+    }
     if (!g) g.allocate((size_t)total * sizeof(float), true);
     if (!m) m.allocate((size_t)total * sizeof(float), true);
     if (!v) v.allocate((size_t)total * sizeof(float), true);

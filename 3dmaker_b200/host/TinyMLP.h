@@ -44,6 +44,8 @@ public:
     DeviceMem(const DeviceMem&) = delete;
     DeviceMem& operator=(const DeviceMem&) = delete;
     void allocate(size_t bytes, bool zero = false);
+    // Uses memory the caller owns (and keeps alive) instead of allocating; release() then only forgets it.
+    void adopt(void* ptr, size_t bytes);
     void release();
     template <class T> T* as() const { return static_cast<T*>(ptr_); }
     size_t bytes() const { return bytes_; }
@@ -51,6 +53,7 @@ public:
 private:
     void* ptr_ = nullptr;
     size_t bytes_ = 0;
+    bool owned_ = true;
 };
 
 // One flat run of parameters with everything the optimizer needs, element i of every array describing the same
@@ -63,6 +66,11 @@ struct ParamArena {
     bool training = false;
     void allocate(int64_t total_elems, int64_t sparse_elems, bool with_training);
     void enable_training();   // allocates g, m, v (zeroed) if missing
+    // The gradient lives in caller-owned memory of at least `total` floats from now on (e.g. a buffer registered with a
+    // collective library); it is zeroed here and used again whenever training is re-enabled.  nullptr returns to an
+    // own allocation.
+    void set_external_grad(float* ptr);
+    float* external_grad = nullptr;
     void disable_training();  // frees g, m, v
     float* W(int64_t off = 0) const { return w.as<float>() + off; }
     half* Wh(int64_t off = 0) const { return w_h.as<half>() + off; }

@@ -126,6 +126,14 @@ extern "C" int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user)
     return NB_OK;
 }
 
+extern "C" int nb_nerf_set_grad_buffer(nb_nerf* h, float* d_grads, int64_t count) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    nb::ParamArena& a = h->impl.arena();
+    if (d_grads && count < a.total) return nb_set_error(NB_ERR_INVALID, "nb_nerf_set_grad_buffer: the buffer is smaller than the parameter arena");
+    if (reinterpret_cast<uintptr_t>(d_grads) & 15u) return nb_set_error(NB_ERR_INVALID, "nb_nerf_set_grad_buffer: the buffer must be 16-byte aligned");
+    NB_GUARD(a.set_external_grad(d_grads))
+}
+
 extern "C" int nb_nerf_get_arena(nb_nerf* h, nb_nerf_arena_view* out) {
     if (!h || !out) return nb_set_error(NB_ERR_INVALID, "nb_nerf_get_arena: null pointer");
     nb::ParamArena& a = h->impl.arena();

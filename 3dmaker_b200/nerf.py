@@ -107,14 +107,31 @@ class InstantNerf:
         """fn(grad_tensor) is called between backward and Adam with a float32 view of the gradient arena."""
         if fn is None:
             self._cb = None
+            self._sync_fn = None
             nb.check(self.lib.nb_nerf_set_grad_sync(self.h, nb.GRAD_SYNC_FN(0), None))
             return
-        grad = self.arena_tensor("g")
+        self._sync_fn = fn
+        grad = self._grad_buffer if getattr(self, "_grad_buffer", None) is not None else self.arena_tensor("g")
 
         def trampoline(user, ptr, count, stream):
             fn(grad)
         self._cb = nb.GRAD_SYNC_FN(trampoline)
         nb.check(self.lib.nb_nerf_set_grad_sync(self.h, self._cb, None))
+
+    def set_grad_buffer(self, tensor):
+        """Moves the gradient arena into `tensor` (float32, CUDA, at least arena().total elements; the engine zeroes it and
+        this object keeps it alive) - e.g. memory registered with the communicator so that the all-reduce of
+        set_grad_sync() works on it in place.  None returns to the engine's own allocation."""
+        if tensor is None:
+            nb.check(self.lib.nb_nerf_set_grad_buffer(self.h, None, 0), "nb_nerf_set_grad_buffer")
+            self._grad_buffer = None
+        else:
+            if tensor.dtype != self.torch.float32 or not tensor.is_cuda or not tensor.is_contiguous():
+                raise ValueError("the gradient buffer must be a contiguous float32 CUDA tensor")
+            nb.check(self.lib.nb_nerf_set_grad_buffer(self.h, nb.ptr(tensor), tensor.numel()), "nb_nerf_set_grad_buffer")
+            self._grad_buffer = tensor[:self.arena().total]
+        if getattr(self, "_sync_fn", None) is not None:
+            self.set_grad_sync(self._sync_fn)
 
     def arena(self):
         v = nb.ArenaView()

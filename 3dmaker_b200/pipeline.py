@@ -27,7 +27,7 @@ class FieldModel:
     """Parameters of hash grid + density network + colour network in one arena, with Adam state."""
 
     def __init__(self, torch, num_levels=16, table_size=1 << 19, base_resolution=16, growth=1.3819, density_hidden=64,
-                 density_layers=2, color_hidden=64, color_layers=3, training=True, stream=None):
+                 density_layers=2, color_hidden=64, color_layers=3, training=True, stream=None, grad_alloc=None):
         self.torch = torch
         self.lib = nb.load()
         self.grid = nb.grid_setup(num_levels, table_size, base_resolution, growth, stream)
@@ -46,7 +46,8 @@ class FieldModel:
         self.w_h = torch.zeros(self.total, dtype=torch.float16, device=dev)
         self.training = training
         if training:
-            self.g = torch.zeros(self.total, dtype=torch.float32, device=dev)
+            # grad_alloc(count, dtype): where the gradient lives, e.g. distributed.CollectiveBuffers.zeros for data parallelism
+            self.g = grad_alloc(self.total, torch.float32) if grad_alloc is not None else torch.zeros(self.total, dtype=torch.float32, device=dev)
             self.m = torch.zeros(self.total, dtype=torch.float32, device=dev)
             self.v = torch.zeros(self.total, dtype=torch.float32, device=dev)
         self.step_count = 0

@@ -366,7 +366,15 @@ def run_ours(args, rank, world, local_rank):
         k, v = kv.split("=")
         nb.check(nb.load().nb_set_tuning(k.encode(), int(v)), "nb_set_tuning")
 
-    model = pl.FieldModel(torch, L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3])
+    buffers = None
+    if world > 1 and args.dp == "allreduce" and not args.plain_buffers:
+        # the gradient lives in memory registered with the communicator: all-reduced in place through NVSwitch
+        D = importlib.import_module("3dmaker_b200.distributed")
+        buffers = D.CollectiveBuffers(torch, dist, "cuda:%d" % local_rank)
+    model = pl.FieldModel(torch, L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3],
+                          grad_alloc=buffers.zeros if buffers is not None else None)
+    if buffers is not None:
+        buffers.register()
     table, dW, db, cW, cb = init_params()
     model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
     tr = pl.SampleTrainer(model, BATCH, fused=False if args.unfused else None, fused_scatter=False if args.separate_scatter else None, **HYPER)
@@ -587,7 +595,7 @@ def run_scene(args, rank, world, local_rank):
         eng = nm.InstantNerf(torch, opts)
         # data parallel: every rank gets 65536 rays per call and takes DP_STEPS optimizer steps on them (one occupancy
         # walk per call); the sphere scene yields about 7 steps' worth of samples per 65536 rays
-        trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None, steps_per_call=6)
+        trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None, steps_per_call=6, registered_gradient=not args.plain_buffers)
         nranks = world
     batches = _scene_batches(torch, syn, 8, rays * nranks, 9000, config=5 if cfg5 else 3)
 
@@ -753,6 +761,8 @@ def main():
     ap.add_argument("--dp", default="sharded", choices=["sharded", "allreduce", "sliced"],
                     help="N > 1: how the gradient is exchanged (sharded: reduce-scatter + Adam on a slice + all-gather of fp16 parameters; "
                          "allreduce: one allreduce + one full Adam; sliced: both pipelined over 4 slices)")
+    ap.add_argument("--plain-buffers", action="store_true", help="N > 1: keep the gradient in ordinary device memory instead of memory "
+                    "registered with the communicator (A/B)")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()

@@ -466,6 +466,11 @@ int nb_nerf_set_fused_field(nb_nerf* h, int on);
 int nb_nerf_set_render_rounds(nb_nerf* h, int on);
 /* Samples the field was evaluated on during the last nb_nerf_render call (waits for the device). */
 int nb_nerf_last_render_samples(nb_nerf* h, uint64_t* samples);
+/* The gradient arena moves into caller-owned device memory of at least `count` >= arena total floats (16-byte aligned;
+ * zeroed by the call; the caller keeps it alive until nb_nerf_destroy or a call with NULL, which returns to an own
+ * allocation).  For data-parallel training: a buffer allocated by the collective library's allocator and registered
+ * with the communicator is all-reduced in place through NVSwitch without staging copies.  Call between steps. */
+int nb_nerf_set_grad_buffer(nb_nerf* h, float* d_grads, int64_t count);
 /* Device pointers of the parameter arena [hash | density W,b | colour W,b] and the slice offsets. */
 int nb_nerf_get_arena(nb_nerf* h, nb_nerf_arena_view* out);
 /* loadHashgrid / loadWeights of both networks from host fp32 arrays (any may be NULL);

@@ -181,3 +181,44 @@ def test_render_batching_is_invisible(cuda, nb):
     torch.cuda.synchronize()
     eng.close()
     assert torch.equal(imgs[2], img)
+
+
+def test_gradient_arena_in_caller_memory(cuda, nb):
+    """set_grad_buffer: the engine accumulates its gradient in a tensor the caller owns (what data-parallel training
+    hands to the communicator), through mode switches, and returns to its own allocation on request."""
+    torch = cuda
+    nm, syn = _mods()
+    opts = nm.default_options(grid_resolution=(64,) * 3, aabb_min=(-.5,) * 3, aabb_max=(.5,) * 3, levels_mipmap=3, hash_table_size=1 << 15,
+                              color_hidden_dim=64, color_num_layers=3, batch_size=1 << 16, ray_chunk_size=1 << 12, density_bias=1.0)
+    eng = nm.InstantNerf(torch, opts)
+    total = eng.arena().total
+    buf = torch.full((total + 8,), 3.0, dtype=torch.float32, device="cuda")
+    seen = []
+
+    def sync(g):
+        seen.append((g.data_ptr(), g.numel(), float(g.abs().sum().item())))
+    eng.set_grad_sync(sync)
+    scene, poses = syn.SoftSphereScene(), syn.sphere_cameras(20)
+
+    def one_call(seed):
+        o, d = syn.random_training_rays(torch, poses, 1 << 12, 200, 200, 50.0, seed=seed)
+        eng.train_rays(o, d, syn.ground_truth(torch, scene, o, d, (1.0, 1.0, 1.0)))
+        torch.cuda.synchronize()
+    one_call(1)
+    own_ptr = seen[-1][0]
+    assert own_ptr != buf.data_ptr() and seen[-1][2] > 0
+    eng.set_grad_buffer(buf)
+    assert float(buf[:total].abs().sum().item()) == 0.0 and float(buf[total:].min().item()) == 3.0   # zeroed, nothing written past the arena
+    one_call(2)
+    assert seen[-1][0] == buf.data_ptr() and seen[-1][1] == total and seen[-1][2] > 0
+    assert float(buf[:total].abs().sum().item()) == 0.0                                              # Adam cleared it again
+    eng.set_memory_mode(True); eng.set_memory_mode(False)                                            # inference and back
+    one_call(3)
+    assert seen[-1][0] == buf.data_ptr() and seen[-1][2] > 0
+    with pytest.raises(nb.NerfB200Error):
+        eng.set_grad_buffer(torch.zeros(total - 4, dtype=torch.float32, device="cuda"))
+    eng.set_grad_buffer(None)
+    one_call(4)
+    assert seen[-1][0] != buf.data_ptr() and seen[-1][2] > 0
+    assert float(buf[total:].min().item()) == 3.0
+    eng.close()
