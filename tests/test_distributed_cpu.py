@@ -190,3 +190,11 @@ def test_uneven_global_batch_is_rejected():
     tr.world = 2
     with pytest.raises(ValueError):
         tr.train_rays(*_batch(63, 1))
+
+
+def test_collective_buffers_fall_back_to_plain_tensors_without_a_nccl_allocator():
+    # no process group / a backend without its own allocator: ordinary tensors, nothing to register
+    b = D.CollectiveBuffers(torch, dist, "cpu")
+    t = b.zeros(12, torch.float32)
+    assert t.shape == (12,) and t.dtype == torch.float32 and float(t.abs().sum()) == 0.0
+    assert b.register() is False
