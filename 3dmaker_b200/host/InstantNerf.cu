@@ -33,7 +33,10 @@ InstantNerf::~InstantNerf() {
     for (WalkSet& w : m_walk) {
         if (w.h_offsets) cudaFreeHost(w.h_offsets);
         if (w.done) cudaEventDestroy(w.done);
+        if (w.freed) cudaEventDestroy(w.freed);
     }
+    if (m_raysReady) cudaEventDestroy(m_raysReady);
+    if (m_walkStream) cudaStreamDestroy(m_walkStream);
 }
 
 nb_scene_desc InstantNerf::scene() const {
@@ -146,7 +149,10 @@ void InstantNerf::initRenderBuffers() {
             w.capacity = R + 1;
         }
         if (!w.done) throw_on_cuda(cudaEventCreateWithFlags(&w.done, cudaEventDisableTiming), "walk event");
+        if (!w.freed) throw_on_cuda(cudaEventCreateWithFlags(&w.freed, cudaEventDisableTiming), "walk event");
     }
+    if (!m_raysReady) throw_on_cuda(cudaEventCreateWithFlags(&m_raysReady, cudaEventDisableTiming), "walk event");
+    if (!m_walkStream) throw_on_cuda(cudaStreamCreateWithFlags(&m_walkStream, cudaStreamNonBlocking), "walk stream");
     d_round_off.allocate(R * sizeof(uint32_t)); d_transmittance.allocate(R * sizeof(float)); d_composited.allocate(R * 4 * sizeof(float));
     d_round_counters.allocate(kRoundCounters * sizeof(uint32_t), true); d_render_samples.allocate(sizeof(uint64_t), true);
     d_render_rgb.allocate(R * 3 * sizeof(float)); d_render_depth.allocate(R * sizeof(float)); d_phi.allocate(R * 3 * sizeof(float));
@@ -569,25 +575,34 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
     TinyMLP* cn = m_colorMLP;
     const float bg[3] = {m_opts.bgColor.x, m_opts.bgColor.y, m_opts.bgColor.z};
     const uint32_t hitBatch = (uint32_t)((m_memMode == INFERENCE) ? m_opts.renderBatchSize : m_opts.batchSize);
-    // The walk of chunk k + 1 is enqueued before the batches of chunk k: while the host waits for chunk k's offsets and cuts
-    // its batches, the device is already walking the next chunk, so the one read-back per chunk never leaves it idle.
+    // Chunks are walked one ahead, on the walk stream: while the host waits for chunk k's offsets and cuts its batches, and
+    // while the field kernels of chunk k run, the device is already walking chunk k + 1.  Events order the two streams:
+    // a walk starts once the caller's rays are there and the batches that read its buffer set are through; the batches
+    // of a chunk start once its walk has finished.
     const uint32_t chunk = (uint32_t)m_opts.rayChunkSize;
     const uint32_t numChunks = (numRays + chunk - 1) / chunk;
     m_renderSamplesHost = 0;
     throw_on_cuda(cudaMemsetAsync(d_render_samples.as<uint64_t>(), 0, sizeof(uint64_t), stream), "render statistics");
-    if (numChunks > 0) walkRays(d_rays_o, d_rays_d, 0, std::min(chunk, numRays), stream, 0, false);
+    throw_on_cuda(cudaEventRecord(m_raysReady, stream), "walk event");
+    throw_on_cuda(cudaStreamWaitEvent(m_walkStream, m_raysReady, 0), "walk event");
+    if (numChunks > 0) walkRays(d_rays_o, d_rays_d, 0, std::min(chunk, numRays), m_walkStream, 0, false);
     for (uint32_t k = 0; k < numChunks; k++) {
         const uint32_t ray_offset = k * chunk;
         const uint32_t chunkRays = std::min<uint32_t>(chunk, numRays - ray_offset);
         const int set = (int)(k & 1);
-        if (k + 1 < numChunks) walkRays(d_rays_o, d_rays_d, ray_offset + chunk, std::min(chunk, numRays - ray_offset - chunk), stream, set ^ 1, false);
+        if (k + 1 < numChunks) {
+            if (k >= 1) throw_on_cuda(cudaStreamWaitEvent(m_walkStream, m_walk[set ^ 1].freed, 0), "walk event");  // batches of chunk k - 1
+            walkRays(d_rays_o, d_rays_d, ray_offset + chunk, std::min(chunk, numRays - ray_offset - chunk), m_walkStream, set ^ 1, false);
+        }
         finishWalk(set);
+        throw_on_cuda(cudaStreamWaitEvent(stream, m_walk[set].done, 0), "walk event");
         const WalkSet& w = m_walk[set];
         const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + ray_offset);
         const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + ray_offset);
         if (renderRounds()) {
             renderChunkRounds(w, chunk_o, chunk_d, chunkRays, hitBatch, d_rgb_out != nullptr ? d_rgb_out + (size_t)ray_offset * 3 : d_render_rgb.as<float>(),
                               stream);
+            throw_on_cuda(cudaEventRecord(m_walk[set].freed, stream), "walk event");
             continue;
         }
         uint32_t raysDone = 0;
@@ -595,6 +610,7 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
             const uint32_t next = cutRays(w.h_offsets, raysDone, chunkRays, hitBatch);
             if (next <= raysDone) {
                 std::fprintf(stderr, "Error: Batch size is too small to fit even a single ray! Increase batchSize.\n");
+                if (k + 1 < numChunks) cudaStreamWaitEvent(stream, m_walk[set ^ 1].done, 0);  // leave no walk behind the caller's stream
                 return;
             }
             const uint32_t crrRays = next - raysDone;
@@ -628,6 +644,7 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
                                               rgb_dst, d_render_depth.as<float>(), nullptr, bg, stream), "compositing");
             raysDone += crrRays;
         }
+        throw_on_cuda(cudaEventRecord(m_walk[set].freed, stream), "walk event");
     }
 }
 
