@@ -33,8 +33,10 @@ InstantNerf::~InstantNerf() {
     for (WalkSet& w : m_walk) {
         if (w.h_offsets) cudaFreeHost(w.h_offsets);
         if (w.done) cudaEventDestroy(w.done);
-        if (w.freed) cudaEventDestroy(w.freed);
+        for (cudaEvent_t e : w.freed) if (e) cudaEventDestroy(e);
     }
+    for (cudaEvent_t e : m_batchDone) if (e) cudaEventDestroy(e);
+    for (cudaStream_t st : m_batchStream) if (st) cudaStreamDestroy(st);
     if (m_raysReady) cudaEventDestroy(m_raysReady);
     if (m_walkStream) cudaStreamDestroy(m_walkStream);
 }
@@ -149,8 +151,10 @@ void InstantNerf::initRenderBuffers() {
             w.capacity = R + 1;
         }
         if (!w.done) throw_on_cuda(cudaEventCreateWithFlags(&w.done, cudaEventDisableTiming), "walk event");
-        if (!w.freed) throw_on_cuda(cudaEventCreateWithFlags(&w.freed, cudaEventDisableTiming), "walk event");
+        for (cudaEvent_t& e : w.freed) if (!e) throw_on_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "walk event");
     }
+    for (cudaEvent_t& e : m_batchDone) if (!e) throw_on_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "batch event");
+    for (cudaStream_t& st : m_batchStream) if (!st) throw_on_cuda(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "batch stream");
     if (!m_raysReady) throw_on_cuda(cudaEventCreateWithFlags(&m_raysReady, cudaEventDisableTiming), "walk event");
     if (!m_walkStream) throw_on_cuda(cudaStreamCreateWithFlags(&m_walkStream, cudaStreamNonBlocking), "walk stream");
     d_round_off.allocate(R * sizeof(uint32_t)); d_transmittance.allocate(R * sizeof(float)); d_composited.allocate(R * 4 * sizeof(float));
@@ -159,6 +163,8 @@ void InstantNerf::initRenderBuffers() {
     d_weight_sum.allocate(R * sizeof(float));
 
     d_positions.allocate(B * 4 * sizeof(float)); d_ray_indices.allocate(B * sizeof(uint32_t)); d_t_sorted.allocate(B * sizeof(float));
+    d_positions2.allocate(B * 4 * sizeof(float)); d_ray_indices2.allocate(B * sizeof(uint32_t)); d_t_sorted2.allocate(B * sizeof(float));
+    d_sigma2.allocate(B * sizeof(float)); d_color_out2.allocate(B * 4 * sizeof(float));
     d_density_out.allocate(std::max(B, (size_t)G + 16) * 16 * sizeof(float));
     d_sigma.allocate(B * sizeof(float)); d_color_in.allocate(B * 32 * sizeof(half)); d_color_out.allocate(B * 8 * sizeof(float));
     if (training) {
@@ -585,67 +591,95 @@ void InstantNerf::renderImageHit(const float3* d_rays_o, const float3* d_rays_d,
     throw_on_cuda(cudaMemsetAsync(d_render_samples.as<uint64_t>(), 0, sizeof(uint64_t), stream), "render statistics");
     throw_on_cuda(cudaEventRecord(m_raysReady, stream), "walk event");
     throw_on_cuda(cudaStreamWaitEvent(m_walkStream, m_raysReady, 0), "walk event");
+    // Sample batches alternate between two streams (each with its own sample arrays) when they write disjoint parts of the
+    // caller's frame; the caller's stream joins them at the end.  The kernel-by-kernel sequence and rendering in rounds
+    // stay on the caller's stream.
+    const bool alternate = m_fused && !renderRounds() && d_rgb_out != nullptr;
+    uint32_t batchIndex = 0;
+    if (alternate)
+        for (cudaStream_t bs : m_batchStream) throw_on_cuda(cudaStreamWaitEvent(bs, m_raysReady, 0), "batch event");
+    auto joinBatches = [&]() {
+        if (!alternate) return;
+        for (int lane = 0; lane < 2; lane++) {
+            throw_on_cuda(cudaEventRecord(m_batchDone[lane], m_batchStream[lane]), "batch event");
+            throw_on_cuda(cudaStreamWaitEvent(stream, m_batchDone[lane], 0), "batch event");
+        }
+    };
     if (numChunks > 0) walkRays(d_rays_o, d_rays_d, 0, std::min(chunk, numRays), m_walkStream, 0, false);
     for (uint32_t k = 0; k < numChunks; k++) {
         const uint32_t ray_offset = k * chunk;
         const uint32_t chunkRays = std::min<uint32_t>(chunk, numRays - ray_offset);
         const int set = (int)(k & 1);
         if (k + 1 < numChunks) {
-            if (k >= 1) throw_on_cuda(cudaStreamWaitEvent(m_walkStream, m_walk[set ^ 1].freed, 0), "walk event");  // batches of chunk k - 1
+            if (k >= 1)  // batches of chunk k - 1 (an event never recorded counts as reached)
+                for (cudaEvent_t e : m_walk[set ^ 1].freed) throw_on_cuda(cudaStreamWaitEvent(m_walkStream, e, 0), "walk event");
             walkRays(d_rays_o, d_rays_d, ray_offset + chunk, std::min(chunk, numRays - ray_offset - chunk), m_walkStream, set ^ 1, false);
         }
         finishWalk(set);
-        throw_on_cuda(cudaStreamWaitEvent(stream, m_walk[set].done, 0), "walk event");
         const WalkSet& w = m_walk[set];
         const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + ray_offset);
         const float* chunk_d = reinterpret_cast<const float*>(d_rays_d + ray_offset);
         if (renderRounds()) {
+            throw_on_cuda(cudaStreamWaitEvent(stream, m_walk[set].done, 0), "walk event");
             renderChunkRounds(w, chunk_o, chunk_d, chunkRays, hitBatch, d_rgb_out != nullptr ? d_rgb_out + (size_t)ray_offset * 3 : d_render_rgb.as<float>(),
                               stream);
-            throw_on_cuda(cudaEventRecord(m_walk[set].freed, stream), "walk event");
+            throw_on_cuda(cudaEventRecord(m_walk[set].freed[0], stream), "walk event");
             continue;
         }
         uint32_t raysDone = 0;
+        bool laneUsed[2] = {false, false};
         while (raysDone < chunkRays) {
             const uint32_t next = cutRays(w.h_offsets, raysDone, chunkRays, hitBatch);
             if (next <= raysDone) {
                 std::fprintf(stderr, "Error: Batch size is too small to fit even a single ray! Increase batchSize.\n");
                 if (k + 1 < numChunks) cudaStreamWaitEvent(stream, m_walk[set ^ 1].done, 0);  // leave no walk behind the caller's stream
+                joinBatches();
                 return;
             }
             const uint32_t crrRays = next - raysDone;
             const uint32_t base = w.h_offsets[raysDone];
             const int64_t n = w.h_offsets[next] - base;
             m_renderSamplesHost += (uint64_t)n;
+            const int lane = alternate ? (int)(batchIndex++ & 1u) : 0;
+            cudaStream_t ls = alternate ? m_batchStream[lane] : stream;
+            if (!laneUsed[lane]) {
+                throw_on_cuda(cudaStreamWaitEvent(ls, m_walk[set].done, 0), "walk event");
+                laneUsed[lane] = true;
+            }
+            float* positions = lane ? d_positions2.as<float>() : d_positions.as<float>();
+            uint32_t* rayIdx = lane ? d_ray_indices2.as<uint32_t>() : d_ray_indices.as<uint32_t>();
+            float* tSorted = lane ? d_t_sorted2.as<float>() : d_t_sorted.as<float>();
+            float* sigma = lane ? d_sigma2.as<float>() : d_sigma.as<float>();
+            float* colorOut = lane ? d_color_out2.as<float>() : d_color_out.as<float>();
             if (n > 0) {
                 throw_on_error(nb_march_compact(&sc, chunk_o, chunk_d, raysDone, crrRays, w.num_steps.as<uint32_t>(), w.offsets.as<uint32_t>(), base,
-                                                w.rows.as<float>(), d_t_sorted.as<float>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
-                               "march: compact");
+                                                w.rows.as<float>(), tSorted, rayIdx, positions, ls), "march: compact");
                 if (m_fused) {
-                    throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
-                                                    chunk_d + (size_t)raysDone * 3, d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()),
+                    throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), positions, m_arena.Wh(dn->hashOffset()),
+                                                    chunk_d + (size_t)raysDone * 3, rayIdx, 0, m_arena.Wh(dn->weightOffset()),
                                                     m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()), n,
-                                                    m_opts.densityBias, nullptr, d_sigma.as<float>(), nullptr, d_color_out.as<float>(), 4, stream),
-                                   "field inference");
+                                                    m_opts.densityBias, nullptr, sigma, nullptr, colorOut, 4, ls), "field inference");
                 } else {
-                    throw_on_error(nb_grid_mlp_forward(&dn->grid(), &dn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
+                    throw_on_error(nb_grid_mlp_forward(&dn->grid(), &dn->desc(), positions, m_arena.Wh(dn->hashOffset()),
                                                        m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), n, d_density_out.as<float>(), nullptr,
-                                                       nullptr, stream), "density inference");
-                    throw_on_error(nb_sh_gather(chunk_d + (size_t)raysDone * 3, d_ray_indices.as<uint32_t>(), 0, n, m_opts.densityBias,
-                                                d_density_out.as<float>(), d_color_in.as<half>(), d_sigma.as<float>(), stream), "SH gather");
+                                                       nullptr, ls), "density inference");
+                    throw_on_error(nb_sh_gather(chunk_d + (size_t)raysDone * 3, rayIdx, 0, n, m_opts.densityBias, d_density_out.as<float>(),
+                                                d_color_in.as<half>(), sigma, ls), "SH gather");
                     throw_on_error(nb_mlp_forward(&cn->desc(), d_color_in.as<half>(), m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()), n,
-                                                  d_color_out.as<float>(), nullptr, stream), "colour inference");
+                                                  colorOut, nullptr, ls), "colour inference");
                 }
             }
             // composited straight into the caller's frame when there is one
             float* rgb_dst = d_rgb_out != nullptr ? d_rgb_out + (size_t)(ray_offset + raysDone) * 3 : d_render_rgb.as<float>();
-            throw_on_error(nb_composite_infer(crrRays, base, raysDone, w.offsets.as<uint32_t>(), w.num_steps.as<uint32_t>() + raysDone,
-                                              d_t_sorted.as<float>(), d_sigma.as<float>(), d_color_out.as<float>(), m_fused ? 4 : 8, nullptr,
-                                              rgb_dst, d_render_depth.as<float>(), nullptr, bg, stream), "compositing");
+            throw_on_error(nb_composite_infer(crrRays, base, raysDone, w.offsets.as<uint32_t>(), w.num_steps.as<uint32_t>() + raysDone, tSorted, sigma,
+                                              colorOut, m_fused ? 4 : 8, nullptr, rgb_dst, d_render_depth.as<float>() + raysDone, nullptr, bg, ls),
+                           "compositing");
             raysDone += crrRays;
         }
-        throw_on_cuda(cudaEventRecord(m_walk[set].freed, stream), "walk event");
+        for (int lane = 0; lane < 2; lane++)
+            if (laneUsed[lane]) throw_on_cuda(cudaEventRecord(m_walk[set].freed[lane], alternate ? m_batchStream[lane] : stream), "walk event");
     }
+    joinBatches();
 }
 
 uint64_t InstantNerf::lastRenderSamples() {

@@ -188,13 +188,18 @@ private:
         uint32_t* h_offsets = nullptr;  // pinned: scanned sample offsets of the walked rays (+ total)
         size_t capacity = 0;
         cudaEvent_t done = nullptr;   // the walk into this set has finished (recorded on the stream that walked)
-        cudaEvent_t freed = nullptr;  // everything that reads this set has been enqueued and, once reached, finished
+        cudaEvent_t freed[2] = {nullptr, nullptr};  // per batch stream: the batches that read this set are through
     };
     WalkSet m_walk[2];
     // Rendering walks on a stream of its own: the walk keeps one thread per ray busy with dependent probes and fills a
     // fraction of the machine, so it runs beside the field kernels of the chunk before instead of in front of them.
     cudaStream_t m_walkStream = nullptr;
     cudaEvent_t m_raysReady = nullptr;
+    // Sample batches of a frame alternate between two streams with a set of sample arrays each, so that the small kernels
+    // and the tail of one batch overlap the field kernel of the next.  Set 0 = the arrays training uses.
+    cudaStream_t m_batchStream[2] = {nullptr, nullptr};
+    cudaEvent_t m_batchDone[2] = {nullptr, nullptr};
+    nb::DeviceMem d_positions2, d_ray_indices2, d_t_sorted2, d_sigma2, d_color_out2;
     // rendering in rounds: per ray of the chunk its place in the round's sample arrays, transmittance and colour so far;
     // one sample counter per (round, ray range), zeroed per chunk
     nb::DeviceMem d_round_off, d_transmittance, d_composited, d_round_counters, d_render_samples;
