@@ -179,6 +179,8 @@ _SIGNATURES = {
     "nb_fetch_ray_chunk": (c_int, [ctypes.POINTER(ImageSet), c_int, c_int, ctypes.c_uint32, c_int, ctypes.POINTER(c_float), c_int, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_generate_rays": (c_int, [c_int, c_int, c_float, ctypes.POINTER(c_float), c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "nb_generate_rays_tiled": (c_int, [c_int, c_int, c_float, ctypes.POINTER(c_float), c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                       c_void_p]),
     "nb_mse_rays": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "nb_ray_aabb": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_march_count": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,

@@ -91,13 +91,16 @@ __global__ void __launch_bounds__(256) density_grad_kernel(int64_t n, const floa
 
 // Pinhole rays of a camera-to-world matrix, pixel (first_pixel + idx).  generate_custom_rays_kernel,
 // modules/NeRF/NerfTrainer.cu:25-47; the pixel offset lets ranks render disjoint tile ranges of one frame.
+// tile == 0: pixels [first_pixel, first_pixel + count).  tile > 0: ray i belongs to the (i / tile)-th of the tiles
+// first_tile, first_tile + tile_stride, ... (tile pixels each) - the tiles one rank of a pixel-sharded frame renders.
 __global__ void __launch_bounds__(256) generate_rays_kernel(int width, int height, float focal, float c00, float c01, float c02, float c03,
                                                             float c10, float c11, float c12, float c13, float c20, float c21, float c22,
-                                                            float c23, int64_t first_pixel, int64_t count, float3* __restrict__ rays_o,
-                                                            float3* __restrict__ rays_d) {
+                                                            float c23, int64_t first_pixel, int64_t count, int64_t tile, int64_t tile_stride,
+                                                            float3* __restrict__ rays_o, float3* __restrict__ rays_d) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     int64_t idx = first_pixel + i;
+    if (tile > 0) idx = (first_pixel + (i / tile) * tile_stride) * tile + i % tile;  // first_pixel holds the first tile here
     int px = (int)(idx % width);
     int py = (int)(idx / width);
     float dx = (px - width * 0.5f) / focal;
@@ -145,7 +148,27 @@ extern "C" int nb_generate_rays(int width, int height, float focal, const float*
     const float* c = c2w_3x4;
     generate_rays_kernel<<<(unsigned)((count + 255) / 256), 256, 0, (cudaStream_t)stream>>>(width, height, focal, c[0], c[1], c[2], c[3], c[4], c[5],
                                                                                             c[6], c[7], c[8], c[9], c[10], c[11], first_pixel,
-                                                                                            count, (float3*)d_rays_o, (float3*)d_rays_d);
+                                                                                            count, 0, 0, (float3*)d_rays_o, (float3*)d_rays_d);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_generate_rays_tiled(int width, int height, float focal, const float* c2w_3x4, int64_t tile, int64_t first_tile,
+                                      int64_t tile_stride, int64_t count, float* d_rays_o, float* d_rays_d, void* stream) {
+    if (!c2w_3x4 || !d_rays_o || !d_rays_d || width <= 0 || height <= 0 || tile <= 0 || first_tile < 0 || tile_stride <= 0 || count < 0 ||
+        !(focal > 0.f))
+        return nb_set_error(NB_ERR_INVALID, "nb_generate_rays_tiled: null pointer or bad tiling");
+    if (count == 0) return NB_OK;
+    // the last ray's pixel must lie inside the frame
+    const int64_t last = count - 1;
+    if ((first_tile + (last / tile) * tile_stride) * tile + last % tile >= (int64_t)width * height)
+        return nb_set_error(NB_ERR_INVALID, "nb_generate_rays_tiled: the tiles reach past the frame");
+    const float* c = c2w_3x4;
+    generate_rays_kernel<<<(unsigned)((count + 255) / 256), 256, 0, (cudaStream_t)stream>>>(width, height, focal, c[0], c[1], c[2], c[3], c[4], c[5],
+                                                                                            c[6], c[7], c[8], c[9], c[10], c[11], first_tile,
+                                                                                            count, tile, tile_stride, (float3*)d_rays_o,
+                                                                                            (float3*)d_rays_d);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

@@ -138,8 +138,11 @@ class ShardedRenderer:
     a pixel run into [count, 3] slices (nb_generate_rays on a GPU).  No collective touches the data path except the
     final gather."""
 
-    def __init__(self, torch, engine, ray_fn, dist=None, tile=4096):
+    def __init__(self, torch, engine, ray_fn, dist=None, tile=4096, tiled_ray_fn=None):
         self.torch, self.engine, self.ray_fn, self.dist, self.tile = torch, engine, ray_fn, dist, tile
+        # optional tiled_ray_fn(tile, first_tile, tile_stride, count, rays_o_out, rays_d_out): all tiles of this rank in one
+        # call (nb_generate_rays_tiled); without it ray_fn runs once per run of consecutive pixels
+        self.tiled_ray_fn = tiled_ray_fn
         self.rank = dist.get_rank() if dist is not None else 0
         self.world = dist.get_world_size() if dist is not None else 1
         self._rays = None
@@ -157,10 +160,14 @@ class ShardedRenderer:
             self._rays = (torch.empty((max(1, total), 3), dtype=torch.float32, device=device),
                           torch.empty((max(1, total), 3), dtype=torch.float32, device=device))
         o, d = self._rays
-        at = 0
-        for first, count in merge_runs(tiles):
-            self.ray_fn(first, count, o[at:at + count], d[at:at + count])
-            at += count
+        if self.tiled_ray_fn is not None and self.world > 1 and total > 0:
+            # the last tile of the frame may be short, and it is the last of whichever rank holds it
+            self.tiled_ray_fn(self.tile, self.rank, self.world, total, o[:total], d[:total])
+        else:
+            at = 0
+            for first, count in merge_runs(tiles):
+                self.ray_fn(first, count, o[at:at + count], d[at:at + count])
+                at += count
         out = torch.zeros((max(1, total), 3), dtype=torch.float32, device=device)
         if total > 0:
             self.engine.render(o[:total], d[:total], out[:total])

@@ -697,7 +697,12 @@ def run_render(args, rank, world, local_rank):
         nb.check(lib.nb_generate_rays(W, H, focal, c2w.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), first, count, nb.ptr(o), nb.ptr(d),
                                       nb.stream_ptr()), "nb_generate_rays")
 
-    r = D.ShardedRenderer(torch, eng, ray_fn, dist if (world > 1 and not reference) else None, tile=1 << 14)
+    def tiled_ray_fn(tile, first_tile, stride, count, o, d):
+        c2w = np.ascontiguousarray(pose["c2w"], np.float32)
+        nb.check(lib.nb_generate_rays_tiled(W, H, focal, c2w.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), tile, first_tile, stride, count,
+                                            nb.ptr(o), nb.ptr(d), nb.stream_ptr()), "nb_generate_rays_tiled")
+
+    r = D.ShardedRenderer(torch, eng, ray_fn, dist if (world > 1 and not reference) else None, tile=1 << 14, tiled_ray_fn=tiled_ray_fn)
     nranks = 1 if reference else world
 
     def frame(k):

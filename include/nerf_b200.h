@@ -173,6 +173,11 @@ int nb_density_grad(int64_t n, const float* d_tmp_dsigma, const void* d_color_dx
  * camera-to-world matrix.  The pixel range is what pixel-sharded rendering splits across ranks. */
 int nb_generate_rays(int width, int height, float focal, const float* c2w_3x4, int64_t first_pixel, int64_t count, float* d_rays_o,
                      float* d_rays_d, void* stream);
+/* The same rays for the tiles first_tile, first_tile + tile_stride, ... of `tile` consecutive pixels each, written one tile
+ * after the other: ray i is pixel (first_tile + (i / tile) * tile_stride) * tile + i % tile.  One launch generates all the
+ * tiles a rank of a pixel-sharded frame renders (distributed.pixel_tiles); only the last tile may be cut short by count. */
+int nb_generate_rays_tiled(int width, int height, float focal, const float* c2w_3x4, int64_t tile, int64_t first_tile, int64_t tile_stride,
+                           int64_t count, float* d_rays_o, float* d_rays_d, void* stream);
 /* Replaces mse_kernel (modules/NeRF/NerfTrainer.cu:15-23): ADDS sum over rays of mean((pred - target)^2) to *d_loss_sum. */
 int nb_mse_rays(const float* d_pred3, const float* d_target3, float* d_loss_sum, int64_t n, void* stream);
 

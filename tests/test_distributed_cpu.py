@@ -114,7 +114,15 @@ def _worker(rank, world, port, out_dir, case):
             r = D.ShardedRenderer(torch, FakeEngine(), ray_fn, dist, tile=128)
             frame = r.render_frame(W * H, "cpu")
             assert (frame is None) == (rank != 0)
+
+            def tiled_ray_fn(tile, first_tile, stride, count, o, d):      # all tiles of the rank in one call
+                i = torch.arange(count)
+                ray_fn_at = ((first_tile + (i // tile) * stride) * tile + i % tile).float()
+                o.copy_(torch.stack([ray_fn_at, ray_fn_at * 2, ray_fn_at * 3], dim=1))
+                d.copy_(torch.stack([ray_fn_at % W, ray_fn_at // W, torch.ones_like(ray_fn_at)], dim=1))
+            frame2 = D.ShardedRenderer(torch, FakeEngine(), None, dist, tile=128, tiled_ray_fn=tiled_ray_fn).render_frame(W * H, "cpu")
             if rank == 0:
+                assert torch.equal(frame, frame2)
                 np.save(os.path.join(out_dir, "frame.npy"), frame.numpy())
             np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([r.local_pixels(W * H)]))
     finally:

@@ -371,3 +371,30 @@ def test_occupancy_kernels(cuda, nb, orc):
     got3 = smp3.cpu().numpy()
     same = got3[:, 3].copy().view(np.int32) == ref3[:, 3].copy().view(np.int32)
     assert same.mean() > 0.999 and np.allclose(got3[same, :3], ref3[same, :3], atol=2e-6)
+
+
+def test_generated_rays_plain_and_tiled(cuda, nb):
+    """nb_generate_rays against the pinhole formula, and nb_generate_rays_tiled (all tiles of a rank in one launch)
+    against nb_generate_rays per tile: the same bits, ragged last tile included."""
+    import importlib
+    torch = cuda
+    syn = importlib.import_module("3dmaker_b200.synthetic"); D = importlib.import_module("3dmaker_b200.distributed")
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    W, H, tile, world = 50, 37, 128, 3                       # 1850 pixels: 15 tiles, the last one 58 pixels
+    focal = syn.focal_from_fov(W, 50.0)
+    c2w = np.ascontiguousarray(syn.orbit_c2w(25.0, 10.0, 1.5), np.float32)
+    cp = c2w.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+    o = torch.zeros((W * H, 3), device="cuda"); d = torch.zeros((W * H, 3), device="cuda")
+    nb.check(lib.nb_generate_rays(W, H, focal, cp, 0, W * H, P(o), P(d), st), "nb_generate_rays")
+    torch.cuda.synchronize()
+    wo, wd = syn.frame_rays(torch, c2w, W, H, 50.0)
+    assert torch.allclose(o, wo, atol=1e-6) and torch.allclose(d, wd, atol=1e-5)
+    for rank in range(world):
+        tiles = D.pixel_tiles(W * H, rank, world, tile)
+        total = sum(c for _, c in tiles)
+        to = torch.full((total, 3), -7.0, device="cuda"); td = torch.full((total, 3), -7.0, device="cuda")
+        nb.check(lib.nb_generate_rays_tiled(W, H, focal, cp, tile, rank, world, total, P(to), P(td), st), "nb_generate_rays_tiled")
+        torch.cuda.synchronize()
+        idx = torch.cat([torch.arange(f, f + c, device="cuda") for f, c in tiles])
+        assert torch.equal(to, o[idx]) and torch.equal(td, d[idx])
+    assert lib.nb_generate_rays_tiled(W, H, focal, cp, tile, 14, 1, 59, P(o), P(d), st) != 0     # one pixel past the frame
