@@ -150,9 +150,10 @@ class ShardedRenderer:
     def local_pixels(self, num_pixels):
         return sum(c for _, c in pixel_tiles(num_pixels, self.rank, self.world, self.tile))
 
-    def render_local(self, num_pixels, device):
-        """Renders this rank's tiles into one [local_pixels, 3] tensor (tile order): the rays of all its tiles are
-        generated into one buffer and rendered by ONE engine call, so the engine batches samples across tiles."""
+    def render_local(self, num_pixels, device, rows=0):
+        """Renders this rank's tiles into one [max(local_pixels, rows), 3] tensor (tile order, zeros behind the local
+        pixels): the rays of all its tiles are generated into one buffer and rendered by ONE engine call, so the engine
+        batches samples across tiles."""
         torch = self.torch
         tiles = pixel_tiles(num_pixels, self.rank, self.world, self.tile)
         total = sum(c for _, c in tiles)
@@ -168,7 +169,7 @@ class ShardedRenderer:
             for first, count in merge_runs(tiles):
                 self.ray_fn(first, count, o[at:at + count], d[at:at + count])
                 at += count
-        out = torch.zeros((max(1, total), 3), dtype=torch.float32, device=device)
+        out = torch.zeros((max(1, total, rows), 3), dtype=torch.float32, device=device)
         if total > 0:
             self.engine.render(o[:total], d[:total], out[:total])
         return out, tiles
@@ -176,18 +177,17 @@ class ShardedRenderer:
     def render_frame(self, num_pixels, device):
         """Returns the [num_pixels, 3] frame on rank 0 (None elsewhere)."""
         torch = self.torch
-        local, tiles = self.render_local(num_pixels, device)
+        num_tiles = (num_pixels + self.tile - 1) // self.tile
+        max_tiles = (num_tiles + self.world - 1) // self.world
+        # with several ranks the local block is rendered straight into the equal-size block the gather sends
+        local, tiles = self.render_local(num_pixels, device, rows=max_tiles * self.tile if self.world > 1 else 0)
         if self.world == 1:
             frame = torch.empty((num_pixels, 3), dtype=torch.float32, device=device)
             self._place(frame, local, tiles)
             return frame
         # equal-size gather: pad every rank's block to the largest one; rank 0 receives into one [world, tiles, tile, 3]
         # buffer and un-deals the tiles with ONE strided copy (tile j of rank r is tile j * world + r of the frame)
-        num_tiles = (num_pixels + self.tile - 1) // self.tile
-        max_tiles = (num_tiles + self.world - 1) // self.world
-        n_local = sum(c for _, c in tiles)
-        padded = torch.zeros((max_tiles * self.tile, 3), dtype=torch.float32, device=device)
-        padded[:n_local] = local[:n_local]
+        padded = local[:max_tiles * self.tile]
         if self.rank == 0:
             buf = torch.empty((self.world, max_tiles, self.tile, 3), dtype=torch.float32, device=device)
             self.dist.gather(padded, [buf[r].view(max_tiles * self.tile, 3) for r in range(self.world)], dst=0)
