@@ -200,7 +200,9 @@ _SIGNATURES = {
     "nb_composite_infer": (c_int, [c_int64, ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                    c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), c_void_p]),
     "nb_composite_round": (c_int, [ctypes.c_uint32, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, ctypes.c_uint32, c_void_p,
-                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), c_void_p]),
+                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_float), ctypes.c_uint32,
+                                   ctypes.POINTER(SceneDesc), c_void_p, c_void_p, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p]),
     "nb_composite_train": (c_int, [c_int64, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, ctypes.POINTER(c_float), c_void_p]),
     "nb_color_grad": (c_int, [c_int64, ctypes.c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -96,4 +96,19 @@ __device__ __forceinline__ float4 ld_nc_f4(const float* p) {
     return v;
 }
 
+__device__ __forceinline__ float contract_axis(float v) {
+    return fabsf(v) <= 1.0f ? v : (2.0f - 1.0f / fabsf(v)) * copysignf(1.0f, v);
+}
+
+// World position -> the unit cube the hash grid is defined on: [-1, 1] of the inner box maps linearly, everything
+// outside is folded into (1, 2) per axis, then (c + 2) / 4.  modules/NeRF/processRays.cu:21-46.
+__device__ __forceinline__ float3 contract_pos(float3 pos, float3 aabb_min, float3 aabb_max) {
+    const float ex = aabb_max.x - aabb_min.x, ey = aabb_max.y - aabb_min.y, ez = aabb_max.z - aabb_min.z;
+    const float rx = (pos.x - aabb_min.x) / ex, ry = (pos.y - aabb_min.y) / ey, rz = (pos.z - aabb_min.z) / ez;
+    const float cx = contract_axis(rx * 2.0f - 1.0f), cy = contract_axis(ry * 2.0f - 1.0f), cz = contract_axis(rz * 2.0f - 1.0f);
+    return make_float3(fmaxf(0.0f, fminf((cx + 2.0f) * 0.25f, 1.0f)), fmaxf(0.0f, fminf((cy + 2.0f) * 0.25f, 1.0f)),
+                       fmaxf(0.0f, fminf((cz + 2.0f) * 0.25f, 1.0f)));
+}
+
+
 }  // namespace nb

@@ -129,64 +129,99 @@ __global__ void __launch_bounds__(256) composite_infer_kernel(const uint32_t num
 // dropped below 1e-4 are not evaluated any further (the samples the reference's loop never reaches contribute
 // nothing to it either).  State per ray between rounds: transmittance and (r, g, b, depth) composited so far.
 // ---------------------------------------------------------------------------------------------------------
+// When next_width > 0 the kernel also copies out the NEXT round (samples [round_begin + round_width, ... + next_width)) of
+// the rays that are still visible after this one: a block's eight rays take one range of the next round's counter and
+// each warp writes its ray's ids and contracted positions there - what round_emit_kernel does in a launch of its own.
 __global__ void __launch_bounds__(256) composite_round_kernel(const uint32_t ray_begin, const uint32_t ray_count,
-                                                              const uint32_t* __restrict__ num_steps, const uint32_t* __restrict__ round_off,
+                                                              const uint32_t* __restrict__ num_steps, uint32_t* __restrict__ round_off,
                                                               const float* __restrict__ rows, const uint32_t row_stride,
                                                               const uint32_t round_begin, const uint32_t round_width,
                                                               const float* __restrict__ sigma_in, const float* __restrict__ rgb_in,
                                                               const int rgb_stride, float* __restrict__ transmittance,
                                                               float4* __restrict__ composited, float* __restrict__ final_rgb,
-                                                              float* __restrict__ final_depth, float3 bg) {
-    const uint32_t local = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+                                                              float* __restrict__ final_depth, float3 bg, const uint32_t next_width,
+                                                              const float3 aabb_min, const float3 aabb_max, const float3* __restrict__ rays_o,
+                                                              const float3* __restrict__ rays_d, const uint32_t capacity,
+                                                              uint32_t* __restrict__ next_counter, unsigned long long* __restrict__ emitted_total,
+                                                              uint32_t* __restrict__ ray_idx_out, float4* __restrict__ pos_out) {
+    __shared__ uint32_t s_next[8], s_base;
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t local = blockIdx.x * 8 + warp;
     const int lane = threadIdx.x & 31;
-    if (local >= ray_count) return;
+    const bool in_range = local < ray_count;
     const uint32_t r = ray_begin + local;
-    const uint32_t n = num_steps[r];
-    float T = round_begin == 0 ? 1.0f : transmittance[r];
-    if (!(T >= 1e-4f && n > round_begin)) {  // the predicate round_emit_kernel planned this round with
-        if (round_begin == 0 && lane == 0) {
-            final_rgb[r * 3 + 0] = bg.x; final_rgb[r * 3 + 1] = bg.y; final_rgb[r * 3 + 2] = bg.z;
-            if (final_depth != nullptr) final_depth[r] = 0.0f;
-        }
-        return;
+    const uint32_t n = in_range ? num_steps[r] : 0u;
+    float T = 0.0f;
+    if (in_range) T = round_begin == 0 ? 1.0f : transmittance[r];
+    const bool active = in_range && T >= 1e-4f && n > round_begin;  // the predicate this round was planned with
+    if (in_range && !active && round_begin == 0 && lane == 0) {
+        final_rgb[r * 3 + 0] = bg.x; final_rgb[r * 3 + 1] = bg.y; final_rgb[r * 3 + 2] = bg.z;
+        if (final_depth != nullptr) final_depth[r] = 0.0f;
     }
-    const uint32_t count = min(n - round_begin, round_width);
-    const uint32_t first = round_off[r];
     const float* row = rows + (size_t)r * row_stride;
-    float cr = 0.f, cg = 0.f, cb = 0.f, depth = 0.f;
-    for (uint32_t w0 = 0; w0 < count; w0 += 32) {
-        const uint32_t i = w0 + lane;
-        const bool valid = i < count;
-        float alpha = 0.f, t = 0.f;
-        if (valid) {
-            const uint32_t k = round_begin + i;  // index of the sample in its ray
-            t = row[k];
-            float dt = (k + 1 < n) ? row[k + 1] - t : 1e-3f;
-            if (dt < 0.0f) dt = 0.0f;
-            alpha = 1.0f - expf(-sigma_in[first + i] * dt);
+    if (active) {
+        const uint32_t count = min(n - round_begin, round_width);
+        const uint32_t first = round_off[r];
+        float cr = 0.f, cg = 0.f, cb = 0.f, depth = 0.f;
+        for (uint32_t w0 = 0; w0 < count; w0 += 32) {
+            const uint32_t i = w0 + lane;
+            const bool valid = i < count;
+            float alpha = 0.f, t = 0.f;
+            if (valid) {
+                const uint32_t k = round_begin + i;  // index of the sample in its ray
+                t = row[k];
+                float dt = (k + 1 < n) ? row[k + 1] - t : 1e-3f;
+                if (dt < 0.0f) dt = 0.0f;
+                alpha = 1.0f - expf(-sigma_in[first + i] * dt);
+            }
+            const float incl = warp_incl_prod(1.0f - alpha, lane);
+            const float T_before = T * from_lane_below(incl, lane, 1.0f);
+            const bool live = valid && T_before >= 1e-4f;
+            if (live) {
+                const float w = alpha * T_before;
+                const float* c = rgb_in + (size_t)(first + i) * rgb_stride;
+                cr += w * c[0]; cg += w * c[1]; cb += w * c[2];
+                depth += w * t;
+            }
+            const unsigned live_mask = __ballot_sync(FULL, live);
+            const int last = 31 - __clz((int)live_mask);
+            T = __shfl_sync(FULL, T * incl, last);
+            if (live_mask != __ballot_sync(FULL, valid) || T < 1e-4f) break;
         }
-        const float incl = warp_incl_prod(1.0f - alpha, lane);
-        const float T_before = T * from_lane_below(incl, lane, 1.0f);
-        const bool live = valid && T_before >= 1e-4f;
-        if (live) {
-            const float w = alpha * T_before;
-            const float* c = rgb_in + (size_t)(first + i) * rgb_stride;
-            cr += w * c[0]; cg += w * c[1]; cb += w * c[2];
-            depth += w * t;
+        cr = warp_sum(cr); cg = warp_sum(cg); cb = warp_sum(cb); depth = warp_sum(depth);
+        if (lane == 0) {
+            float4 acc = round_begin == 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : composited[r];
+            acc.x += cr; acc.y += cg; acc.z += cb; acc.w += depth;
+            composited[r] = acc;
+            transmittance[r] = T;
+            final_rgb[r * 3 + 0] = acc.x + T * bg.x; final_rgb[r * 3 + 1] = acc.y + T * bg.y; final_rgb[r * 3 + 2] = acc.z + T * bg.z;
+            if (final_depth != nullptr) final_depth[r] = acc.w;
         }
-        const unsigned live_mask = __ballot_sync(FULL, live);
-        const int last = 31 - __clz((int)live_mask);
-        T = __shfl_sync(FULL, T * incl, last);
-        if (live_mask != __ballot_sync(FULL, valid) || T < 1e-4f) break;
     }
-    cr = warp_sum(cr); cg = warp_sum(cg); cb = warp_sum(cb); depth = warp_sum(depth);
-    if (lane == 0) {
-        float4 acc = round_begin == 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : composited[r];
-        acc.x += cr; acc.y += cg; acc.z += cb; acc.w += depth;
-        composited[r] = acc;
-        transmittance[r] = T;
-        final_rgb[r * 3 + 0] = acc.x + T * bg.x; final_rgb[r * 3 + 1] = acc.y + T * bg.y; final_rgb[r * 3 + 2] = acc.z + T * bg.z;
-        if (final_depth != nullptr) final_depth[r] = acc.w;
+    if (next_width == 0) return;  // the same for the whole grid
+    const uint32_t next_begin = round_begin + round_width;
+    const uint32_t c_next = (active && T >= 1e-4f && n > next_begin) ? min(n - next_begin, next_width) : 0u;
+    if (lane == 0) s_next[warp] = c_next;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) total += s_next[w];
+        s_base = total ? atomicAdd(next_counter, total) : 0u;
+        if (total && emitted_total != nullptr) atomicAdd(emitted_total, (unsigned long long)total);
+    }
+    __syncthreads();
+    if (c_next == 0) return;
+    uint32_t dst = s_base;
+    for (uint32_t w = 0; w < warp; w++) dst += s_next[w];
+    if (dst + c_next > capacity) return;  // cannot happen when the caller's bound holds; never write past the arrays
+    if (lane == 0) round_off[r] = dst;
+    const float3 o = rays_o[r], d = rays_d[r];
+    for (uint32_t k = lane; k < c_next; k += 32) {
+        const float t = row[next_begin + k];
+        ray_idx_out[dst + k] = r;
+        const float3 p = contract_pos(make_float3(o.x + t * d.x, o.y + t * d.y, o.z + t * d.z), aabb_min, aabb_max);
+        st_cs_v4(&pos_out[dst + k], make_uint4(__float_as_uint(p.x), __float_as_uint(p.y), __float_as_uint(p.z), 0u));
     }
 }
 
@@ -427,20 +462,35 @@ extern "C" int nb_color_grad(int64_t num_rays, uint32_t sample_base, const uint3
     return NB_OK;
 }
 
-extern "C" int nb_composite_round(uint32_t ray_begin, uint32_t ray_count, const uint32_t* d_num_steps, const uint32_t* d_round_offsets,
+extern "C" int nb_composite_round(uint32_t ray_begin, uint32_t ray_count, const uint32_t* d_num_steps, uint32_t* d_round_offsets,
                                   const float* d_t_rows, uint32_t round_begin, uint32_t round_width, const float* d_sigma, const float* d_rgb,
                                   int rgb_stride, float* d_transmittance, float* d_composited4, float* d_final_rgb, float* d_final_depth,
-                                  const float* bg_color3, void* stream) {
+                                  const float* bg_color3, uint32_t next_width, const nb_scene_desc* scene, const float* d_rays_o,
+                                  const float* d_rays_d, uint32_t capacity, uint32_t* d_next_counter, uint64_t* d_emitted_total,
+                                  uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream) {
     if (!d_num_steps || !d_round_offsets || !d_t_rows || !d_sigma || !d_rgb || !d_transmittance || !d_composited4 || !d_final_rgb ||
         !bg_color3 || rgb_stride < 3 || round_width == 0)
         return nb_set_error(NB_ERR_INVALID, "nb_composite_round: null pointer, empty round or rgb stride < 3");
     if (reinterpret_cast<uintptr_t>(d_composited4) & 15u)
         return nb_set_error(NB_ERR_INVALID, "nb_composite_round: the composited state must be 16-byte aligned");
     if (ray_count > 0x3ffffffu) return nb_set_error(NB_ERR_INVALID, "nb_composite_round: too many rays");
+    float3 lo = make_float3(0.f, 0.f, 0.f), hi = make_float3(1.f, 1.f, 1.f);
+    if (next_width > 0) {
+        if (!scene || !d_rays_o || !d_rays_d || !d_next_counter || !d_ray_idx_out || !d_pos4_out)
+            return nb_set_error(NB_ERR_INVALID, "nb_composite_round: the next round's copy-out needs the scene, the rays, a counter and the sample arrays");
+        if (reinterpret_cast<uintptr_t>(d_pos4_out) & 15u)
+            return nb_set_error(NB_ERR_INVALID, "nb_composite_round: positions must be 16-byte aligned");
+        if ((uint64_t)round_begin + round_width >= (uint64_t)nb_march_row_stride())
+            return nb_set_error(NB_ERR_INVALID, "nb_composite_round: the next round must lie inside a row");
+        lo = make_float3(scene->aabb_min[0], scene->aabb_min[1], scene->aabb_min[2]);
+        hi = make_float3(scene->aabb_max[0], scene->aabb_max[1], scene->aabb_max[2]);
+    }
     if (ray_count == 0) return NB_OK;
     composite_round_kernel<<<warp_grid(ray_count), 256, 0, (cudaStream_t)stream>>>(
         ray_begin, ray_count, d_num_steps, d_round_offsets, d_t_rows, (uint32_t)nb_march_row_stride(), round_begin, round_width, d_sigma, d_rgb,
-        rgb_stride, d_transmittance, (float4*)d_composited4, d_final_rgb, d_final_depth, make_float3(bg_color3[0], bg_color3[1], bg_color3[2]));
+        rgb_stride, d_transmittance, (float4*)d_composited4, d_final_rgb, d_final_depth, make_float3(bg_color3[0], bg_color3[1], bg_color3[2]),
+        next_width, lo, hi, (const float3*)d_rays_o, (const float3*)d_rays_d, capacity, d_next_counter, (unsigned long long*)d_emitted_total,
+        d_ray_idx_out, (float4*)d_pos4_out);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

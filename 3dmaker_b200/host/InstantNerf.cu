@@ -519,27 +519,76 @@ void InstantNerf::renderChunkRounds(const WalkSet& w, const float* chunk_o, cons
         }
     }
     int slot = kRoundCounters;  // forces the first clear
-    auto launchRange = [&](int r, uint32_t begin, uint32_t end, uint64_t bound) {
-        if (r > 0 && bound == 0) return;  // nobody reaches the round; round 0 still writes the background
-        if (slot == kRoundCounters) {
+    auto takeCounters = [&](int count) -> uint32_t* {
+        if (slot + count > kRoundCounters) {
             throw_on_cuda(cudaMemsetAsync(d_round_counters.as<uint32_t>(), 0, kRoundCounters * sizeof(uint32_t), stream), "round counters");
             slot = 0;
         }
-        uint32_t* counter = d_round_counters.as<uint32_t>() + slot++;
+        uint32_t* c = d_round_counters.as<uint32_t>() + slot;
+        slot += count;
+        return c;
+    };
+    auto blockBound = [&](uint32_t b, int r) { return (uint64_t)m_roundRays[(size_t)b * kRounds + r] * kWidth[r]; };
+    auto fieldOn = [&](uint64_t bound, const uint32_t* counter) {
+        throw_on_error(nb_field_forward_counted(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()), chunk_d,
+                                                d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()),
+                                                m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()), (int64_t)bound, counter,
+                                                m_opts.densityBias, d_sigma.as<float>(), d_color_out.as<float>(), 4, stream), "field inference");
+    };
+    // The usual case: every 1024-ray block fits the sample arrays in every round.  Then the chunk is cut into ray ranges
+    // that fit in EVERY round and each range runs all its rounds in a row, the compositing kernel of a round copying the
+    // next round's samples out as it goes: two launches per round.
+    bool everyBlockFits = true;
+    for (uint32_t b = 0; b < numBlocks && everyBlockFits; b++)
+        for (int r = 0; r < kRounds; r++) everyBlockFits = everyBlockFits && blockBound(b, r) <= capacity;
+    if (everyBlockFits) {
+        uint32_t b0 = 0;
+        while (b0 < numBlocks) {
+            uint64_t sum[kRounds] = {0, 0, 0, 0, 0, 0, 0};
+            uint32_t b1 = b0;
+            while (b1 < numBlocks) {
+                bool ok = true;
+                for (int r = 0; r < kRounds; r++) ok = ok && sum[r] + blockBound(b1, r) <= capacity;
+                if (!ok) break;
+                for (int r = 0; r < kRounds; r++) sum[r] += blockBound(b1, r);
+                b1++;
+            }
+            const uint32_t begin = b0 * BLOCK, end = std::min(chunkRays, b1 * BLOCK);
+            int last = 0;
+            for (int r = 0; r < kRounds; r++) if (sum[r] > 0) last = r;
+            uint32_t* counters = takeCounters(last + 1);
+            throw_on_error(nb_march_round_emit(&sc, chunk_o, chunk_d, begin, end - begin, w.num_steps.as<uint32_t>(), d_transmittance.as<float>(),
+                                               kBegin[0], kWidth[0], w.rows.as<float>(), capacity, counters, d_render_samples.as<uint64_t>(),
+                                               d_round_off.as<uint32_t>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
+                           "march: round");
+            for (int r = 0; r <= last; r++) {
+                if (sum[r] > 0) fieldOn(sum[r], counters + r);
+                const bool more = r < last;
+                throw_on_error(nb_composite_round(begin, end - begin, w.num_steps.as<uint32_t>(), d_round_off.as<uint32_t>(), w.rows.as<float>(),
+                                                  kBegin[r], kWidth[r], d_sigma.as<float>(), d_color_out.as<float>(), 4, d_transmittance.as<float>(),
+                                                  d_composited.as<float>(), rgb_dst, d_render_depth.as<float>(), bg, more ? kWidth[r + 1] : 0u, &sc,
+                                                  chunk_o, chunk_d, capacity, more ? counters + r + 1 : nullptr,
+                                                  d_render_samples.as<uint64_t>(), d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream),
+                               "compositing");
+            }
+            b0 = b1;
+        }
+        return;
+    }
+    // Otherwise (sample arrays smaller than one round of 1024 rays): round by round, ranges cut per round, each with a
+    // copy-out launch of its own.
+    auto launchRange = [&](int r, uint32_t begin, uint32_t end, uint64_t bound) {
+        if (r > 0 && bound == 0) return;  // nobody reaches the round; round 0 still writes the background
+        uint32_t* counter = takeCounters(1);
         throw_on_error(nb_march_round_emit(&sc, chunk_o, chunk_d, begin, end - begin, w.num_steps.as<uint32_t>(), d_transmittance.as<float>(),
                                            kBegin[r], kWidth[r], w.rows.as<float>(), capacity, counter, d_render_samples.as<uint64_t>(),
                                            d_round_off.as<uint32_t>(),
                                            d_ray_indices.as<uint32_t>(), d_positions.as<float>(), stream), "march: round");
-        if (bound > 0) {
-            throw_on_error(nb_field_forward_counted(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()),
-                                                    chunk_d, d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()),
-                                                    m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()), m_arena.W(cn->biasOffset()),
-                                                    (int64_t)bound, counter, m_opts.densityBias, d_sigma.as<float>(), d_color_out.as<float>(), 4,
-                                                    stream), "field inference");
-        }
+        if (bound > 0) fieldOn(bound, counter);
         throw_on_error(nb_composite_round(begin, end - begin, w.num_steps.as<uint32_t>(), d_round_off.as<uint32_t>(), w.rows.as<float>(), kBegin[r],
                                           kWidth[r], d_sigma.as<float>(), d_color_out.as<float>(), 4, d_transmittance.as<float>(),
-                                          d_composited.as<float>(), rgb_dst, d_render_depth.as<float>(), bg, stream), "compositing");
+                                          d_composited.as<float>(), rgb_dst, d_render_depth.as<float>(), bg, 0u, nullptr, nullptr, nullptr, 0u,
+                                          nullptr, nullptr, nullptr, nullptr, stream), "compositing");
     };
     for (int r = 0; r < kRounds; r++) {
         if (r > 0 && reach[r] == 0) break;  // round 0 always runs: it writes the background of rays without samples

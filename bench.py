@@ -688,6 +688,8 @@ def run_render(args, rank, world, local_rank):
         eng.ref.lib().ref_nerf_set_memory_mode(eng.h, 1)
     else:
         eng.set_memory_mode(True)
+        if args.render_rounds:
+            eng.set_render_rounds(True)
     W, H = 1920, 1080
     focal = syn.focal_from_fov(W, 50.0)
     pose = {}
@@ -766,6 +768,7 @@ def main():
     ap.add_argument("--dp", default="sharded", choices=["sharded", "allreduce", "sliced"],
                     help="N > 1: how the gradient is exchanged (sharded: reduce-scatter + Adam on a slice + all-gather of fp16 parameters; "
                          "allreduce: one allreduce + one full Adam; sliced: both pipelined over 4 slices)")
+    ap.add_argument("--render-rounds", action="store_true", help="render workload: render in rounds of samples per ray (A/B; off by default)")
     ap.add_argument("--plain-buffers", action="store_true", help="N > 1: keep the gradient in ordinary device memory instead of memory "
                     "registered with the communicator (A/B)")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")

@@ -343,11 +343,18 @@ int nb_composite_infer(int64_t num_rays, uint32_t base, uint32_t rays_done, cons
  * continues from d_transmittance / d_composited4 (r, g, b, depth per ray; not read when round_begin == 0), stops a ray
  * for good once its transmittance is below 1e-4 exactly where render_rays_kernel (compositing.cu:5-78) leaves its loop,
  * and writes colour (+ transmittance x background) and depth so far into d_final_rgb / d_final_depth (nullable) at the
- * ray's place in the chunk.  Round 0 writes every ray of the range (background for rays without samples). */
-int nb_composite_round(uint32_t ray_begin, uint32_t ray_count, const uint32_t* d_num_steps, const uint32_t* d_round_offsets,
+ * ray's place in the chunk.  Round 0 writes every ray of the range (background for rays without samples).
+ * next_width > 0: the same launch also does nb_march_round_emit's work for the round that follows
+ * ([round_begin + round_width, ... + next_width)) for the rays that are still visible, into d_ray_idx_out / d_pos4_out
+ * (free by then: this round's field kernel has read them), *d_next_counter (zero before the call) and d_round_offsets;
+ * then scene, rays, capacity and the arrays are needed, otherwise they may be NULL / 0.  All ray ranges of one round share
+ * the sample arrays, so with next_width > 0 a chunk is processed range by range (all rounds of a range, then the next). */
+int nb_composite_round(uint32_t ray_begin, uint32_t ray_count, const uint32_t* d_num_steps, uint32_t* d_round_offsets,
                        const float* d_t_rows, uint32_t round_begin, uint32_t round_width, const float* d_sigma, const float* d_rgb,
                        int rgb_stride, float* d_transmittance, float* d_composited4, float* d_final_rgb, float* d_final_depth,
-                       const float* bg_color3, void* stream);
+                       const float* bg_color3, uint32_t next_width, const nb_scene_desc* scene, const float* d_rays_o,
+                       const float* d_rays_d, uint32_t capacity, uint32_t* d_next_counter, uint64_t* d_emitted_total,
+                       uint32_t* d_ray_idx_out, float* d_pos4_out, void* stream);
 
 /* Replaces render_rays_distortion_kernel via launchVolumeRendering with d_dw_out != NULL
  * (modules/NeRF/compositing.cu:84-213).  d_depth_prior / d_sigma_prior may be NULL (depth supervision off). */

@@ -237,10 +237,11 @@ def test_compositing_and_color_grad(cuda, nb, orc, R):
     assert torch.equal(grad_b, grad[base:]) and torch.equal(dsig_b, dsig[base:]) and torch.equal(rgb_i, rgb2[k:])
 
 
-@pytest.mark.parametrize("capacity_rays", [None, 700])
-def test_rendering_in_rounds_equals_the_single_pass(cuda, nb, orc, capacity_rays):
+@pytest.mark.parametrize("capacity_rays,fused", [(None, False), (700, False), (None, True), (700, True)])
+def test_rendering_in_rounds_equals_the_single_pass(cuda, nb, orc, capacity_rays, fused):
     """nb_march_round_emit + nb_composite_round over the rounds 16, 16, 32, ... against nb_composite_infer on the same
-    rays: same colour and depth to fp32 rounding, and rays that turned opaque are not emitted again."""
+    rays: same colour and depth to fp32 rounding, and rays that turned opaque are not emitted again.  fused: the
+    compositing launch of a round copies the next round out itself (range by range instead of round by round)."""
     torch = cuda
     up = Uploader(torch, nb)
     lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
@@ -270,41 +271,63 @@ def test_rendering_in_rounds_equals_the_single_pass(cuda, nb, orc, capacity_rays
     got = torch.full((R, 3), -1.0, dtype=f32, device="cuda"); got_depth = torch.full((R,), -1.0, dtype=f32, device="cuda")
     sig_all, col_all, off_all = torch.from_numpy(sigma).cuda(), torch.from_numpy(col).cuda(), torch.from_numpy(off.astype(np.int64)).cuda()
     total = torch.zeros(1, dtype=torch.int64, device="cuda")
-    begin, emitted, reached = 0, 0, 0
-    for width in (16, 16, 32, 64, 128, 256, 512):
-        step = R if capacity_rays is None else capacity_rays
+    widths = (16, 16, 32, 64, 128, 256, 512)
+    begins = (0, 16, 32, 64, 128, 256, 512)
+    step = R if capacity_rays is None else capacity_rays
+    stats = {"emitted": 0, "reached": 0}
+
+    def field(r0, rc, begin, width, m):
+        """sigma and colour of the m samples in the arrays, looked up by (ray, sample index in the ray); checks the copy-out"""
+        reach = np.clip(counts[r0:r0 + rc].astype(np.int64) - begin, 0, width)
+        assert m <= reach.sum()
+        stats["emitted"] += m; stats["reached"] += int(reach.sum())
+        ray = ridx[:m].long()
+        assert m == 0 or (int(ray.min()) >= r0 and int(ray.max()) < r0 + rc)
+        k = begin + torch.arange(m, device="cuda") - roff.long()[ray]
+        assert m == 0 or (int(k.min()) >= begin and int(k.max()) < begin + width)
+        src = off_all[ray] + k
+        if m:
+            tt = rows[ray, k]
+            p_want = orc.contract_pos((o[ray] + tt[:, None] * d[ray]).cpu().numpy(), (-0.5,) * 3, (0.5,) * 3)
+            assert np.allclose(pos[:m, :3].cpu().numpy(), p_want, atol=2e-6)
+            return sig_all[src].contiguous(), col_all[src].contiguous()
+        return torch.zeros(1, device="cuda"), torch.zeros((1, 8), device="cuda")
+
+    def emit(r0, rc, begin, width, counter):
+        nb.check(lib.nb_march_round_emit(ctypes.byref(sc), P(o), P(d), r0, rc, d_cnt, P(T), begin, width, P(rows), cap, P(counter), P(total), P(roff),
+                                         P(ridx), P(pos), st), "nb_march_round_emit")
+        torch.cuda.synchronize()
+
+    def composite(r0, rc, begin, width, s_round, c_round, next_width=0, next_counter=None):
+        nb.check(lib.nb_composite_round(r0, rc, d_cnt, P(roff), P(rows), begin, width, P(s_round), P(c_round), 8, P(T), P(acc), P(got), P(got_depth),
+                                        bg, next_width, ctypes.byref(sc) if next_width else None, P(o) if next_width else None,
+                                        P(d) if next_width else None, cap if next_width else 0, P(next_counter) if next_width else None,
+                                        P(total) if next_width else None, P(ridx) if next_width else None, P(pos) if next_width else None, st),
+                 "nb_composite_round")
+        torch.cuda.synchronize()
+
+    if not fused:
+        for begin, width in zip(begins, widths):
+            for r0 in range(0, R, step):
+                rc = min(step, R - r0)
+                counter = torch.zeros(1, dtype=i32, device="cuda")
+                emit(r0, rc, begin, width, counter)
+                s_round, c_round = field(r0, rc, begin, width, int(counter.item()))
+                composite(r0, rc, begin, width, s_round, c_round)
+    else:
         for r0 in range(0, R, step):
             rc = min(step, R - r0)
-            counter = torch.zeros(1, dtype=i32, device="cuda")
-            nb.check(lib.nb_march_round_emit(ctypes.byref(sc), P(o), P(d), r0, rc, d_cnt, P(T), begin, width, P(rows), cap, P(counter), P(total), P(roff),
-                                             P(ridx), P(pos), st), "nb_march_round_emit")
-            torch.cuda.synchronize()
-            m = int(counter.item())
-            reach = np.clip(counts[r0:r0 + rc].astype(np.int64) - begin, 0, width)
-            assert m <= reach.sum()
-            emitted += m; reached += int(reach.sum())
-            # the field's part: sigma and colour of the emitted samples, looked up by (ray, sample index in the ray)
-            ray = ridx[:m].long()
-            assert m == 0 or (int(ray.min()) >= r0 and int(ray.max()) < r0 + rc)
-            k = begin + torch.arange(m, device="cuda") - roff.long()[ray]
-            assert m == 0 or (int(k.min()) >= begin and int(k.max()) < begin + width)
-            src = off_all[ray] + k
-            s_round = sig_all[src].contiguous() if m else torch.zeros(1, device="cuda")
-            c_round = col_all[src].contiguous() if m else torch.zeros((1, 8), device="cuda")
-            # positions are those of the row entries
-            tt = rows[ray, k]
-            if m:
-                p_want = orc.contract_pos((o[ray] + tt[:, None] * d[ray]).cpu().numpy(), (-0.5,) * 3, (0.5,) * 3)
-                assert np.allclose(pos[:m, :3].cpu().numpy(), p_want, atol=2e-6)
-            nb.check(lib.nb_composite_round(r0, rc, d_cnt, P(roff), P(rows), begin, width, P(s_round), P(c_round), 8, P(T), P(acc), P(got),
-                                            P(got_depth), bg, st), "nb_composite_round")
-            torch.cuda.synchronize()
-        begin += width
+            counters = torch.zeros(len(widths) + 1, dtype=i32, device="cuda")
+            emit(r0, rc, 0, widths[0], counters[0:1])
+            for j, (begin, width) in enumerate(zip(begins, widths)):
+                s_round, c_round = field(r0, rc, begin, width, int(counters[j].item()))
+                nxt = widths[j + 1] if j + 1 < len(widths) else 0
+                composite(r0, rc, begin, width, s_round, c_round, nxt, counters[j + 1:j + 2] if nxt else None)
     assert float((got - want).abs().max()) <= 1e-5
     assert torch.allclose(got_depth, want_depth, rtol=1e-5, atol=1e-5)
-    assert int(total.item()) == emitted
-    assert emitted < reached                                       # opaque rays dropped out before their last round
-    assert emitted >= int(np.minimum(counts, 16).sum())            # ... but every ray took part in the first
+    assert int(total.item()) == stats["emitted"]
+    assert stats["emitted"] < stats["reached"]                         # opaque rays dropped out before their last round
+    assert stats["emitted"] >= int(np.minimum(counts, 16).sum())       # ... but every ray took part in the first
 
 
 def test_occupancy_kernels(cuda, nb, orc):
