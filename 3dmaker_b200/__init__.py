@@ -230,6 +230,7 @@ _SIGNATURES = {
     "nb_nerf_last_render_samples": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint64)]),
     "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_steps_per_call": (c_int, [c_void_p, c_int]),
+    "nb_nerf_set_hit_counts_capacity": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_set_grad_buffer": (c_int, [c_void_p, c_void_p, c_int64]),
     "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),

@@ -22,7 +22,9 @@
 // scatter warpgroup, registers split by setmaxnreg; measured at 2^20 unordered samples it is slower, 0.654 against
 // 0.630 ms - the reductions' own rate binds by then - and on ray-ordered samples faster, 0.234 against 0.282 ms, where
 // the register kernel's 0.214 ms is what gets used anyway.)
-// Every wait - MMA barrier, hand-over full / empty - is bounded.
+// Every wait - MMA barrier, hand-over full / empty - is bounded in TIME (the global timer, one second); a CTA whose wait
+// runs out drops its accumulated weight gradients, raises an error flag in mapped host memory that the next
+// nb_field_backward call (and nb_field_backward_tc_status) reports, waits for its MMAs in flight and leaves.
 #include <atomic>
 #include <type_traits>
 
@@ -39,6 +41,7 @@ constexpr int ROWS = 128;      // rows of a tile = TMEM lanes = threads of the C
 constexpr int SCATTER_GROUPS = 1;  // warpgroups that only scatter; a row's levels are dealt round-robin to them
 constexpr int THREADS = 128 * (1 + SCATTER_GROUPS);  // warps 0-3: GEMM chain (thread = row); the rest: gradient scatter
 constexpr int CHAIN_THREADS = 128;
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;   // one second: the longest any wait inside the kernel lasts
 
 // ---- shared-memory map (bytes); every tile is [rows][cols] fp16 in core-matrix order --------------------------
 __host__ __device__ constexpr uint32_t tile_bytes(int rows, int cols) { return (uint32_t)rows * cols * 2; }
@@ -98,16 +101,33 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// Waits for the phase with the given parity; gives up after a bounded number of polls (false).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar_addr, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(bar_addr), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for the phase with the given parity, for at most limit_ns nanoseconds of the global timer (false when the time
+// ran out, or when *give_up - a flag another warp of the CTA raises - became non-zero).  limit_ns == 0 does not wait at
+// all: one non-blocking test decides.  That setting exists for the test of the give-up path.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns, volatile int* give_up = nullptr) {
     const uint32_t a = smem_u32(bar);
-    for (int it = 0; it < (1 << 22); it++) {
+    if (mbar_test(a, parity)) return true;
+    if (limit_ns == 0) return false;
+    const uint64_t t0 = global_ns();
+    for (;;) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
                      : "=r"(ok) : "r"(a), "r"(parity) : "memory");
         if (ok) return true;
+        if (give_up != nullptr && *give_up != 0) return false;
+        if (global_ns() - t0 > limit_ns) return false;
     }
-    return false;
 }
 
 // 32 consecutive columns of this thread's TMEM lane
@@ -278,6 +298,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
     const uint32_t tmem = tmem_base_s;
     const int64_t ntiles = (a.n + ROWS - 1) / ROWS;
     bool ok = true;
+    uint32_t phase_out = 0;   // chain warps: commits awaited or given up on so far
 
     if (warp >= 4) {
         // ================= scatter warpgroup: thread = row of the tile handed over =====================================
@@ -287,7 +308,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
             int it = 0;
             for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, it++) {
                 const int buf = it & 1, use = it >> 1;
-                const bool got = __all_sync(0xffffffffu, mbar_wait(&x_full[buf], use & 1));
+                const bool got = __all_sync(0xffffffffu, mbar_wait(&x_full[buf], use & 1, WAIT_LIMIT_NS, abort_flag));
                 if (!got) { ok = false; break; }   // the chain gave up (or never came): leave, every wait here is bounded
                 const uint32_t* x = reinterpret_cast<const uint32_t*>(smem + OFF_X) + buf * 16 * ROWS;
                 uint32_t pk[16];
@@ -316,7 +337,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
 
         // wait for the MMAs committed last; uniform verdict over the warpgroup
         auto await = [&]() -> bool {
-            if (!mbar_wait(&mbar, phase & 1)) *abort_flag = 1;
+            if (!mbar_wait(&mbar, phase & 1, a.wait_ns)) *abort_flag = 1;
             phase++;
             chain_barrier();
             tc_fence_after();
@@ -529,7 +550,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
                     // hand the tile's gradients to the scatter warps: buffer `it & 1`, free again once they have read it
                     const int buf = it & 1, use = it >> 1;
                     bool free_now = true;
-                    if (use > 0) free_now = mbar_wait(&x_empty[buf], (use - 1) & 1);
+                    if (use > 0) free_now = mbar_wait(&x_empty[buf], (use - 1) & 1, a.wait_ns);
                     if (free_now) {
                         uint32_t* x = reinterpret_cast<uint32_t*>(smem + OFF_X) + buf * 16 * ROWS;
 #pragma unroll
@@ -586,8 +607,15 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
             if (lane < 8) red_add(a.dbc + 128 + lane, db_c2);
             if (lane < 16) red_add(a.dbd + 64 + lane, db_d1);
         }
+        phase_out = phase;
     }
-    if (!ok && lane == 0 && a.error_flag != nullptr) atomicExch(a.error_flag, 1);
+    if (!ok && lane == 0 && a.error_flag != nullptr) atomicExch_system(a.error_flag, 1);
+    if (!ok && warp < 4 && phase_out > 0) {
+        // A chain that gave up may still have MMAs in flight that write tensor memory: before the columns are handed
+        // back, wait (bounded, the full limit whatever the tuning says) for the last commit.
+        mbar_wait(&mbar, (phase_out - 1) & 1, WAIT_LIMIT_NS);
+        tc_fence_after();
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -598,22 +626,41 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
 
 namespace nb {
 
-std::atomic<int> g_backward_tc{2};   // nb_set_tuning("backward_tc", ...)
-static __device__ int g_tc_error_flag;
+std::atomic<int> g_backward_tc{2};        // nb_set_tuning("backward_tc", ...)
+std::atomic<int> g_backward_tc_wait_us{1000000};   // nb_set_tuning("backward_tc_wait_us", ...): the chain's wait limit
+
+// The error flag lives in mapped, portable host memory: the kernel raises it with a system-scope atomic, the host
+// reads it without a CUDA call.  One flag per process, allocated on the first launch.
+static std::atomic<int*> g_tc_error_flag{nullptr};
+
+static int* tc_error_flag() {
+    int* p = g_tc_error_flag.load(std::memory_order_acquire);
+    if (p != nullptr) return p;
+    int* fresh = nullptr;
+    if (cudaHostAlloc((void**)&fresh, 64, cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess || fresh == nullptr) return nullptr;
+    *fresh = 0;
+    int* expected = nullptr;
+    if (!g_tc_error_flag.compare_exchange_strong(expected, fresh)) { cudaFreeHost(fresh); return expected; }
+    return fresh;
+}
+
+// Non-zero when a wait of the tensor-memory backward kernel has run out since the flag was last cleared.
+int field_backward_tc_failed() {
+    int* p = g_tc_error_flag.load(std::memory_order_acquire);
+    return p != nullptr && *reinterpret_cast<volatile int*>(p) != 0;
+}
 
 // Host side: launched by nb_field_backward when the tensor-memory path is selected.
 int launch_field_backward_tc(const GridParams& gp, const tc::BackwardArgs& args_in, cudaStream_t st) {
     tc::BackwardArgs args = args_in;
-    static int* flag_addr[64] = {};
-    int dev = 0;
-    NB_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return nb_set_error(NB_ERR_LIMIT, "field backward: device index beyond 63");
-    if (flag_addr[dev] == nullptr) NB_CUDA(cudaGetSymbolAddress((void**)&flag_addr[dev], g_tc_error_flag));
-    args.error_flag = flag_addr[dev];
+    args.error_flag = tc_error_flag();
+    if (args.error_flag == nullptr) return nb_set_error(NB_ERR_CUDA, "field backward: no mapped host memory for the error flag");
+    const int wait_us = g_backward_tc_wait_us.load();
+    args.wait_ns = wait_us <= 0 ? 0ull : (uint64_t)wait_us * 1000ull;
     auto kern = tc::field_backward_tc_kernel;
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES));
     const int64_t ntiles = (args.n + tc::ROWS - 1) / tc::ROWS;
-    int64_t grid = (int64_t)nb_num_sms() * 2;   // two CTAs per SM: 91 KB of shared memory and 256 tensor-memory columns each
+    int64_t grid = (int64_t)nb_num_sms() * 2;   // two CTAs per SM: 107 KB of shared memory and 256 tensor-memory columns each
     if (grid > ntiles) grid = ntiles;
     kern<<<(unsigned)grid, tc::THREADS, tc::SMEM_BYTES, st>>>(gp, args);
     NB_CHECK_LAUNCH();
@@ -623,16 +670,13 @@ int launch_field_backward_tc(const GridParams& gp, const tc::BackwardArgs& args_
 
 }  // namespace nb
 
-// 0 when no wait of the tensor-memory backward kernel has run out on the current device since the last call (the flag is
-// cleared); synchronises the device.
+// NB_OK when no wait of the tensor-memory backward kernel has run out since the last call; otherwise NB_ERR_CUDA, and
+// the flag is cleared.  Synchronises the device first, so that it speaks for every launch enqueued so far.
 extern "C" int nb_field_backward_tc_status(void) {
-    int v = 0;
     NB_CUDA(cudaDeviceSynchronize());
-    NB_CUDA(cudaMemcpyFromSymbol(&v, nb::g_tc_error_flag, sizeof(int)));
-    if (v != 0) {
-        int zero = 0;
-        NB_CUDA(cudaMemcpyToSymbol(nb::g_tc_error_flag, &zero, sizeof(int)));
-        return nb_set_error(NB_ERR_CUDA, "field backward (tensor memory): a bounded wait on the MMA barrier ran out");
+    if (nb::field_backward_tc_failed()) {
+        *reinterpret_cast<volatile int*>(nb::g_tc_error_flag.load()) = 0;
+        return nb_set_error(NB_ERR_CUDA, "field backward (tensor memory): a bounded wait inside the kernel ran out; the gradients of that launch are incomplete");
     }
     return NB_OK;
 }

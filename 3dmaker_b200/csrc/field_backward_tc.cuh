@@ -27,12 +27,15 @@ struct BackwardArgs {
     const float* pos4;        // scatter
     float* table_grads;
     int scatter_begin;
-    int* error_flag;          // set when a wait ran out
+    int* error_flag;          // mapped host memory; set when a wait ran out
+    uint64_t wait_ns;         // limit of the chain's waits (0: give up at once when a barrier is not ready - test only)
 };
 
 }  // namespace tc
 
 extern std::atomic<int> g_backward_tc;
+extern std::atomic<int> g_backward_tc_wait_us;
+int field_backward_tc_failed();
 int launch_field_backward_tc(const GridParams& gp, const tc::BackwardArgs& args, cudaStream_t st);
 
 }  // namespace nb

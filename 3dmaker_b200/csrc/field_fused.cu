@@ -583,6 +583,9 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
         misaligned(d_color_w_h, 16) || misaligned(d_grad_density_w, 8) || misaligned(d_grad_color_w, 8) || misaligned(d_density_b, 8) ||
         misaligned(d_color_b, 8))
         return nb_set_error(NB_ERR_INVALID, "nb_field_backward: misaligned device pointer");
+    if (nb::field_backward_tc_failed())
+        return nb_set_error(NB_ERR_CUDA, "nb_field_backward: a bounded wait of an earlier tensor-memory launch ran out (its gradients are "
+                                         "incomplete); nb_field_backward_tc_status() clears the condition");
     if (n == 0) return NB_OK;
     nb::FieldIO io{};
     io.dirs3 = d_dirs3; io.ray_idx = d_ray_indices; io.ray_idx_offset = ray_index_offset;
@@ -607,7 +610,11 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
         gio.denc_cols = 4 * shared_levels;   // only what the shared-memory scatter kernel below reads
     }
     const int tc_mode = nb::g_backward_tc.load();
-    if (tc_mode == 1 || (tc_mode == 2 && d_ray_indices == nullptr)) {
+    // The tensor-memory kernel adds its weight gradients with 16-byte reductions; the register kernel needs 8 bytes only.
+    const bool grads_16 = !misaligned(d_grad_density_w, 16) && !misaligned(d_grad_color_w, 16);
+    if (tc_mode == 1 && !grads_16)
+        return nb_set_error(NB_ERR_INVALID, "nb_field_backward: the tensor-memory kernel needs 16-byte aligned weight gradients");
+    if (tc_mode == 1 || (tc_mode == 2 && d_ray_indices == nullptr && grads_16)) {
         // tensor-memory formulation (field_backward_tc.cu): same inputs, outputs and rounding points
         nb::tc::BackwardArgs ta{};
         ta.enc = gio.enc; ta.dcolor = gio.dcolor; ta.dsigma = gio.dsigma; ta.dirs3 = io.dirs3; ta.ray_idx = io.ray_idx;

@@ -278,17 +278,19 @@ extern "C" int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size,
 // nb_grid_setup_noalloc: the same set-up without any allocation.
 //
 // Some host programs may not allocate device memory at the point where they configure a grid: a renderer
-// plug-in that was handed a fixed memory budget by its host application, a process whose allocator is
-// locked while a CUDA graph is being recorded, or a real-time loop that forbids cudaMalloc because it
-// synchronises the whole device.  For them the 32-float scratch that nb_grid_setup allocates and frees lives
-// in the library image instead: every GPU that loads the library holds these 128 bytes (one 256-byte aligned slot) until exit.
+// plug-in that was handed a fixed memory budget by its host application, or a real-time loop that forbids
+// cudaMalloc / cudaFree because they synchronise the whole device.  For them the 32-float scratch that
+// nb_grid_setup allocates and frees lives in the library image instead: every GPU that loads the library holds
+// these 128 bytes (at a 256-byte aligned address) until the process exits.
+// Like nb_grid_setup the call reads the scales back to the host and waits for the stream before it returns.
 // ---------------------------------------------------------------------------------------------------
 static __device__ __align__(256) float g_static_level_scales[2 * NB_MAX_LEVELS];
 
 // Device address of g_static_level_scales on each device, looked up on the first call made with that
 // device current.  In host code the array's name is only a handle for cudaGetSymbolAddress, never a pointer
-// a kernel could use.
-static float* g_static_level_scales_addr[64] = {nullptr};
+// a kernel could use.  Threads may race to fill an entry; they all store the same address.  The addresses
+// belong to the device's context: after cudaDeviceReset they are stale and the library must be reloaded.
+static std::atomic<float*> g_static_level_scales_addr[64];
 
 extern "C" int nb_grid_setup_noalloc(nb_grid_desc* desc, int num_levels, int table_size, int base_resolution, float growth,
                                      void* stream) {
@@ -313,13 +315,12 @@ extern "C" int nb_grid_setup_noalloc(nb_grid_desc* desc, int num_levels, int tab
     int dev = -1;
     NB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return nb_set_error(NB_ERR_LIMIT, "nb_grid_setup_noalloc: device ordinal beyond 63");
-    if (g_static_level_scales_addr[dev] == nullptr) {
-        float* p = nullptr;
-        NB_CUDA(cudaGetSymbolAddress((void**)&p, g_static_level_scales));
-        if (p == nullptr) return nb_set_error(NB_ERR_CUDA, "nb_grid_setup_noalloc: cudaGetSymbolAddress returned a null address");
-        g_static_level_scales_addr[dev] = p;
+    float* d_scales = g_static_level_scales_addr[dev].load(std::memory_order_acquire);
+    if (d_scales == nullptr) {
+        NB_CUDA(cudaGetSymbolAddress((void**)&d_scales, g_static_level_scales));
+        if (d_scales == nullptr) return nb_set_error(NB_ERR_CUDA, "nb_grid_setup_noalloc: cudaGetSymbolAddress returned a null address");
+        g_static_level_scales_addr[dev].store(d_scales, std::memory_order_release);
     }
-    float* d_scales = g_static_level_scales_addr[dev];
     cudaStream_t st = (cudaStream_t)stream;
     // the kernel writes entries [0, num_levels) and only those are read back, so nothing has to start at zero
     level_scales_kernel<<<1, 32, 0, st>>>(base_resolution, growth, std::log2(growth), num_levels, d_scales);
@@ -398,6 +399,7 @@ extern "C" int nb_set_tuning(const char* key, int value) {
     std::string k(key);
     if (k == "scatter_run_merge") g_run_merge = value;
     else if (k == "backward_tc") g_backward_tc = value;
+    else if (k == "backward_tc_wait_us") g_backward_tc_wait_us = value;
     else if (k == "scatter_smem_levels") g_scatter_tuning.smem_levels = value;
     else if (k == "pair_ops") g_pair_ops = value;
     else if (k == "scatter_level_begin") g_scatter_tuning.level_begin = value;

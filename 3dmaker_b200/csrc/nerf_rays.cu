@@ -26,6 +26,9 @@ extern std::atomic<uint64_t> g_launch_count;
 
 constexpr uint32_t MAX_HITS = 1024;  // per-ray sample cap, modules/NeRF/InstantNerf.h:24
 constexpr int MAX_MIP_LEVELS = 8;
+// Hard bound on the advances of one ray.  A ray crosses at most 3 x 128 finest voxels per cascade plus its 1024 samples;
+// 65536 is far beyond any walk that makes progress and only ends one that does not.
+constexpr uint32_t MAX_WALK_ADVANCES = 1u << 16;
 
 struct Scene {
     uint3 res;
@@ -138,7 +141,8 @@ __device__ __forceinline__ uint32_t walk_ray(const Scene& sc, float3 o, float3 d
     uint32_t count = 0;
     float t = t_begin;
     bool in_solid = false;
-    while (t < t_end && count < MAX_HITS) {
+    uint32_t advances = 0;
+    while (t < t_end && count < MAX_HITS && advances++ < MAX_WALK_ADVANCES) {
         const float3 pos = make_float3(o.x + t * d.x, o.y + t * d.y, o.z + t * d.z);
         const int cascade = get_cascade(pos, sc.aabb_min, sc.aabb_max, sc.num_cascades);
         const float cs = exp2f((float)cascade);
@@ -171,7 +175,12 @@ __device__ __forceinline__ uint32_t walk_ray(const Scene& sc, float3 o, float3 d
                 count++;
             }
         }
-        t = fmaxf(t + 1e-5f, p.exit_t + 1e-6f);
+        // The reference advances with exactly this expression (processRays.cu:235,733,925).  From t = 256 on the 1e-5 is
+        // below half an ulp and is rounded away, and a voxel face computed a rounding error behind t (or an exit of -inf
+        // from a -0.0 direction component) then leaves t where it was: the reference's loop would never end.  Where the
+        // expression makes progress its value is kept bit for bit; where it does not, t moves to the next float.
+        const float next = fmaxf(t + 1e-5f, p.exit_t + 1e-6f);
+        t = next > t ? next : nextafterf(t, INFINITY);
     }
     return count;
 }

@@ -311,6 +311,9 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
     const uint32_t budget = (uint32_t)m_opts.batchSize;
     uint32_t raysDone = 0;
     int i = 0;
+    auto recordHits = [&](uint32_t hits) {
+        if (hitCounts != nullptr && (m_hitCountsCapacity == 0 || (uint32_t)i < m_hitCountsCapacity)) hitCounts[i] = hits;
+    };
     // The reference walks the rays left in the chunk again for every optimizer step (InstantNerf.cu:386-407).  The
     // walk only depends on the rays and the occupancy bits, so one walk serves every step until the bits change
     // (every 16th step) or the walked window runs out while rays remain beyond it.
@@ -321,7 +324,7 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
     // runs the remaining steps with no samples (it still joins the exchange and applies the common update).
     while (m_stepsPerCall > 0 ? i < m_stepsPerCall : raysDone < numRays) {
         if (raysDone >= numRays) {
-            if (hitCounts != nullptr) hitCounts[i] = 0;
+            recordHits(0);
             m_lastTotalHits = 0;
             if (m_trainSteps % 16 == 0) {
                 timed(stream, m_times.occupancy, [&]() {
@@ -356,6 +359,9 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
         const uint32_t sampleBase = m_walk[0].h_offsets[begin];
         if (currentChunkRays == 0) {
             std::fprintf(stderr, "Error: Batch size is too small to fit even a single ray! Increase batchSize.\n");
+            // With a fixed number of steps per call every rank must still reach each gradient exchange: leaving here would
+            // strand the other ranks in their collective.  The ray that does not fit is dropped and the loop goes on.
+            if (m_stepsPerCall > 0) { raysDone++; m_lastRaysConsumed = raysDone; continue; }
             return;
         }
         const float* chunk_o = reinterpret_cast<const float*>(d_rays_o + raysDone);
@@ -372,7 +378,7 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                                                 stream), "march: compact");
             });
         }
-        if (hitCounts != nullptr) hitCounts[i] = totalHits;
+        recordHits(totalHits);
         m_lastTotalHits = totalHits;
         m_lastStepFirstRay = begin;
         m_lastSampleBase = sampleBase;

@@ -136,6 +136,8 @@ public:
     // k = 0 restores the reference's loop (as many steps as the rays need).
     void setStepsPerCall(int k) { m_stepsPerCall = k > 0 ? k : 0; }
     void setSingleStep(bool on) { m_stepsPerCall = on ? 1 : 0; }
+    // Entries the caller's hitCounts array holds (0 = unbounded, as the reference writes it): steps beyond it are not recorded.
+    void setHitCountsCapacity(uint32_t n) { m_hitCountsCapacity = n; }
     uint32_t lastRaysConsumed() const { return m_lastRaysConsumed; }
     const NerfPhaseTimes& phaseTimes() const { return m_times; }
     // Buffers of the last step, for parity tests (valid until the next call).
@@ -217,4 +219,5 @@ private:
     uint32_t m_lastTotalHits = 0;
     uint32_t m_lastRaysConsumed = 0;
     int m_stepsPerCall = 0;
+    uint32_t m_hitCountsCapacity = 0;
 };

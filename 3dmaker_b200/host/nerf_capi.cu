@@ -103,6 +103,12 @@ extern "C" int nb_nerf_set_steps_per_call(nb_nerf* h, int steps) {
     return NB_OK;
 }
 
+extern "C" int nb_nerf_set_hit_counts_capacity(nb_nerf* h, uint32_t capacity) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    h->impl.setHitCountsCapacity(capacity);
+    return NB_OK;
+}
+
 extern "C" int nb_nerf_set_fused_field(nb_nerf* h, int on) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     return h->impl.setFusedField(on != 0) ? 1 : 0;

@@ -33,6 +33,7 @@ class InstantNerf:
         self._cb = None
         self.steps = ctypes.c_int(0)
         self._hits = np.zeros(4096, np.uint32)      # samples of every optimizer step of the last train_rays() call
+        nb.check(self.lib.nb_nerf_set_hit_counts_capacity(self.h, self._hits.size), "nb_nerf_set_hit_counts_capacity")
 
     def close(self):
         if self.h:

@@ -84,12 +84,15 @@ int nb_grid_setup(nb_grid_desc* desc, int num_levels, int table_size, int base_r
  * whose launchers recompute the geometry inside every kernel).  Think of a plug-in running inside a
  * host application's fixed memory budget, or a loop that cannot afford the device-wide synchronisation
  * of cudaMalloc/cudaFree.  Same inputs, same results as nb_grid_setup; the 32-float scratch the set-up
- * kernel writes is a static device array inside the library (256 bytes per GPU, held until the process
- * exits) instead of a cudaMalloc'd buffer, and no cudaMalloc, cudaFree or other allocating call is made.
+ * kernel writes is a static device array inside the library (128 bytes per GPU at a 256-byte aligned
+ * address, held until the process exits) instead of a cudaMalloc'd buffer, and no cudaMalloc, cudaFree
+ * or other allocating call is made.  Like nb_grid_setup it copies the scales back to the host and waits
+ * for the stream (cudaStreamSynchronize) before returning.
  * Limits and rules:
  *   - num_levels > 16 (NB_MAX_LEVELS) is rejected with NB_ERR_LIMIT;
  *   - the first call on each device (with that device current) looks up the array's device address;
- *     make that first call before starting any stream capture;
+ *     make that first call before any stream capture begins.  The address belongs to the device's
+ *     context and does not survive cudaDeviceReset;
  *   - all calls on one GPU share the array, which keeps the previous call's values (each call overwrites
  *     exactly the entries it reads back, so nothing needs clearing); two calls that overlap on the GPU
  *     (different streams or threads) race on it - serialise them. */
@@ -222,8 +225,15 @@ int nb_field_forward_counted(const nb_grid_desc* grid, const nb_mlp_desc* densit
  * accumulators, 2 (default) picks by the sample order the call implies: d_ray_indices == NULL means explicit,
  * unordered samples, where the scatter's reductions are the long pole and the tensor-memory kernel (its scatter on
  * warps of their own) is faster (0.63 against 0.74 ms at 2^20 samples); ray-ordered samples from the marcher come with
- * ray indices, merge into few reductions, and the register kernel is the faster one there (0.21 against 0.23 ms at 2^18).  nb_field_backward_tc_status() synchronises the device and reports (NB_ERR_CUDA) whether a bounded
- * wait of the tensor-memory kernel ever ran out; it clears the flag. */
+ * ray indices, merge into few reductions, and the register kernel is the faster one there (0.21 against 0.23 ms at 2^18).
+ * The tensor-memory kernel adds its weight gradients with 16-byte reductions: with weight-gradient pointers that are only
+ * 8-byte aligned mode 2 uses the register kernel and mode 1 returns NB_ERR_INVALID.
+ * Every wait inside the tensor-memory kernel is bounded by the GPU's global timer (one second;
+ * nb_set_tuning("backward_tc_wait_us", v) changes the limit of the MMA and hand-over waits, v = 0 makes a wait give up
+ * as soon as its barrier is not ready, which is how the give-up path is tested).  A CTA whose wait runs out drops its
+ * weight gradients and raises a flag in mapped host memory; from then on nb_field_backward returns NB_ERR_CUDA until
+ * nb_field_backward_tc_status() - which synchronises the device, reports the condition (NB_ERR_CUDA) and clears it - has
+ * been called. */
 int nb_field_backward_tc_status(void);
 int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
                       const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h, const float* d_density_b,
@@ -466,6 +476,9 @@ int nb_nerf_set_single_step(nb_nerf* h, int on);
  * reference's loop).  A rank whose rays are used up before the last step takes the remaining steps with no samples
  * of its own: it still calls fn and applies the update. */
 int nb_nerf_set_steps_per_call(nb_nerf* h, int steps);
+/* Size of the hit_counts array passed to nb_nerf_train_rays (one entry per optimizer step of the call; the reference's
+ * trainWithRaysHit writes it unbounded, InstantNerf.cu:429): steps at or beyond `capacity` are not recorded.  0 = unbounded. */
+int nb_nerf_set_hit_counts_capacity(nb_nerf* h, uint32_t capacity);
 /* Switches between nb_field_forward / nb_field_backward (default when nb_field_supported) and the reference's
  * kernel-by-kernel sequence; returns 1 when the fused kernels are in effect afterwards, 0 otherwise.  Results agree
  * to the fp32 summation order of the weight gradients.  No counterpart in the reference. */

@@ -526,7 +526,9 @@ static uint32_t march_one(const float* o, const float* d, const float* d_inv, fl
     float current_t = t_min;
     int level = levels - 1;
     uint32_t total_mip = mipmap_offset(res, levels);
-    while (current_t < t_max_ray && hit_count < ORC_MAX_HITS) {
+    /* advances of the ray; bounded like the product's walk (see below) */
+    uint32_t advances = 0;
+    while (current_t < t_max_ray && hit_count < ORC_MAX_HITS && advances < (1u << 16)) {
         float pos[3] = {fmaf(current_t, d[0], o[0]), fmaf(current_t, d[1], o[1]), fmaf(current_t, d[2], o[2])};
         int cascade = get_cascade(pos, aabb_min, aabb_max, num_cascades);
         float cs = exp2f((float)cascade);
@@ -570,7 +572,14 @@ static uint32_t march_one(const float* o, const float* d, const float* d_inv, fl
                 }
             }
         }
-        current_t = fmaxf(current_t + 1e-5f, next_t + 1e-6f);
+        /* The reference's advance (processRays.cu:733,925).  From t = 256 on, 1e-5 is rounded away and a voxel face a
+         * rounding error behind t leaves t unchanged: the reference would loop forever.  Where the expression makes
+         * progress it is kept bit for bit; otherwise t moves to the next float, and the advances are bounded. */
+        {
+            float nt = fmaxf(current_t + 1e-5f, next_t + 1e-6f);
+            current_t = nt > current_t ? nt : nextafterf(current_t, INFINITY);
+        }
+        advances++;
         level = levels - 1;
     }
     return hit_count;

@@ -46,3 +46,20 @@ def test_missing_library_is_a_loud_error(monkeypatch):
         assert "no CPU or PyTorch fallback" in str(e)
     else:
         raise AssertionError("load() must raise when the CUDA library is missing")
+
+
+def test_forced_tensor_memory_backward_rejects_8_byte_aligned_weight_gradients():
+    """Argument validation only (it returns before any CUDA call): the tensor-memory backward adds its weight gradients
+    with 16-byte reductions, so forcing it with gradient pointers that are only 8-byte aligned is an error, not a fault."""
+    nb = importlib.import_module("3dmaker_b200")
+    lib = nb.load()
+    density, color = nb.mlp_desc(32, 64, 16, 2, 0), nb.mlp_desc(32, 64, 8, 3, 1)
+    A = ctypes.c_void_p(0x10000)             # any 16-byte aligned non-null address: never dereferenced
+    G8 = ctypes.c_void_p(0x20008)            # 8- but not 16-byte aligned
+    assert lib.nb_set_tuning(b"backward_tc", 1) == 0
+    try:
+        rc = lib.nb_field_backward(ctypes.byref(density), ctypes.byref(color), A, A, None, 0, A, A, A, A, 128, A, None, G8, A, G8, A, A,
+                                   None, None, None, None)
+        assert rc == 1 and b"16-byte aligned weight gradients" in lib.nb_last_error()
+    finally:
+        lib.nb_set_tuning(b"backward_tc", 2)

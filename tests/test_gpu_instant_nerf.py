@@ -222,3 +222,25 @@ def test_gradient_arena_in_caller_memory(cuda, nb):
     assert seen[-1][0] != buf.data_ptr() and seen[-1][2] > 0
     assert float(buf[total:].min().item()) == 3.0
     eng.close()
+
+
+def test_fixed_steps_per_call_survive_a_ray_that_does_not_fit_the_batch(cuda, nb):
+    """Data parallelism fixes the number of optimizer steps (gradient exchanges) per call.  A sample batch too small for
+    one of the rays must not make this rank leave the loop early - the other ranks would wait in their collective for
+    ever: the ray is dropped, every exchange still happens, and the per-step hit counts stay inside their array."""
+    torch = cuda
+    nm, syn = _mods()
+    opts = nm.default_options(grid_resolution=(64,) * 3, aabb_min=(-.5,) * 3, aabb_max=(.5,) * 3, levels_mipmap=3, hash_table_size=1 << 15,
+                              color_hidden_dim=64, color_num_layers=3, batch_size=16, ray_chunk_size=1 << 10, density_bias=1.0)
+    eng = nm.InstantNerf(torch, opts)
+    calls = []
+    eng.set_grad_sync(lambda g: calls.append(1))
+    eng.set_steps_per_call(5)
+    scene, poses = syn.SoftSphereScene(), syn.sphere_cameras(20)
+    o, d = syn.random_training_rays(torch, poses, 1 << 10, 200, 200, 50.0, seed=1)
+    # rays through the sphere carry more than 16 samples on a 64^3 grid, rays past it none
+    steps = eng.train_rays(o, d, syn.ground_truth(torch, scene, o, d, (1.0, 1.0, 1.0)))
+    torch.cuda.synchronize()
+    assert steps == 5 and len(calls) == 5
+    assert torch.isfinite(eng.arena_tensor("w")).all()
+    eng.close()

@@ -1,5 +1,6 @@
 """One full field-training step (encode + both MLPs fwd/bwd + scatter + Adam) through the C ABI, compared
 stage by stage with the same step restated from oracle calls."""
+import ctypes
 import importlib
 
 import numpy as np
@@ -228,3 +229,71 @@ def test_tensor_memory_backward_agrees_with_the_register_formulation(cuda, nb, n
         for off, cnt in ((model.off_dw, model.density.weight_count), (model.off_db, model.density.bias_count),
                          (model.off_cw, model.color.weight_count), (model.off_cb, model.color.bias_count)):
             assert rel_err(b[off:off + cnt], a[off:off + cnt]) <= 2e-3, (name, off)
+
+
+def test_tensor_memory_backward_wait_that_runs_out_is_reported_and_recoverable(cuda, nb):
+    """With the wait limit set to 0 a chain warp gives up as soon as its MMA barrier is not ready: the kernel must return
+    (nothing hangs, nothing faults), the condition must surface - nb_field_backward refuses to go on, the status call
+    reports and clears it - and the next launch with the normal limit must work and give the register kernel's gradients."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    lib = nb.load()
+    L, T, n = 16, 1 << 15, 5000
+    model = pl.FieldModel(torch, L, T, 16, 1.3819, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    pos, dirs, tgt = _inputs(n, 17)
+    tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=True)
+    tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+    try:
+        nb.check(lib.nb_set_tuning(b"backward_tc", 0), "nb_set_tuning")
+        model.g.zero_(); tr.forward_backward(n); torch.cuda.synchronize()
+        want = model.g.cpu().numpy().copy()
+        nb.check(lib.nb_set_tuning(b"backward_tc", 1), "nb_set_tuning")
+        nb.check(lib.nb_set_tuning(b"backward_tc_wait_us", 0), "nb_set_tuning")
+        model.g.zero_(); tr.forward_backward(n); torch.cuda.synchronize()          # the launch itself succeeds and returns
+        with pytest.raises(nb.NerfB200Error):                                       # ... but the next call is refused
+            tr.forward_backward(n)
+        assert lib.nb_field_backward_tc_status() == 3                               # NB_ERR_CUDA, and cleared
+        assert b"ran out" in lib.nb_last_error()
+        assert lib.nb_field_backward_tc_status() == 0
+        nb.check(lib.nb_set_tuning(b"backward_tc_wait_us", 1000000), "nb_set_tuning")
+        model.g.zero_(); tr.forward_backward(n)
+        nb.check(lib.nb_field_backward_tc_status(), "status after recovery")
+        got = model.g.cpu().numpy()
+        assert rel_err(got[:model.hash_count], want[:model.hash_count]) <= 2e-3
+        assert rel_err(got[model.off_cw:model.off_cw + model.color.weight_count], want[model.off_cw:model.off_cw + model.color.weight_count]) <= 2e-3
+    finally:
+        lib.nb_set_tuning(b"backward_tc_wait_us", 1000000)
+        lib.nb_set_tuning(b"backward_tc", 2)
+        lib.nb_field_backward_tc_status()
+        model.g.zero_()
+
+
+def test_field_backward_with_8_byte_aligned_weight_gradients_uses_the_register_kernel(cuda, nb):
+    """Weight-gradient pointers that are 8- but not 16-byte aligned: the default mode must not pick the tensor-memory
+    kernel (16-byte reductions); the register kernel runs and the gradients equal the aligned call's."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    lib, P = nb.load(), nb.ptr
+    L, T, n = 16, 1 << 14, 3000
+    model = pl.FieldModel(torch, L, T, 16, 1.3819, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    pos, dirs, tgt = _inputs(n, 19)
+    tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=False)
+    tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+    model.g.zero_(); tr.forward_backward(n); torch.cuda.synchronize()
+    m = model
+    dense = m.total - m.hash_count
+    want = m.g[m.hash_count:].cpu().numpy().copy()
+    shifted = torch.zeros(dense + 8, dtype=torch.float32, device="cuda")
+    base = shifted[2:]                                                    # 8 bytes past a 16-byte boundary
+    assert base.data_ptr() % 16 == 8
+    off = lambda o: ctypes.c_void_p(base.data_ptr() + (o - m.hash_count) * 4)
+    nb.check(lib.nb_field_backward(ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw),
+                                   m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, P(tr.c_grad), None, off(m.off_dw),
+                                   off(m.off_db), off(m.off_cw), off(m.off_cb), P(tr.d_enc), None, None, None, nb.stream_ptr()), "nb_field_backward")
+    torch.cuda.synchronize()
+    assert rel_err(base[:dense].cpu().numpy(), want) <= 2e-3
+    model.g.zero_()

@@ -95,6 +95,29 @@ def test_march_properties(orc, cascades, spv):
     assert orc.march_count(o, d, d_inv, nears, fars, np.zeros_like(bits), res, amin, amax, cascades, levels, spv).sum() == 0
 
 
+def test_march_ends_on_far_rays_and_signed_zero_directions(orc):
+    """8 cascades on a +-1 box reach t of several hundred, where the advance's +1e-5 is below half an ulp, and a
+    direction component of -0.0 gives an exit distance of -inf on that axis: the walk must still end (the advance
+    moves to the next float when its expression stalls, and the advances are bounded)."""
+    res, levels, cascades = (16, 16, 16), 3, 8
+    S = orc.pyramid_cells(res, levels)
+    bits = np.zeros(cascades * S // 8, np.uint8)                       # empty space only: every advance is a skip
+    rng = np.random.default_rng(11)
+    n = 256
+    o = rng.uniform(-120, 120, size=(n, 3)).astype(np.float32)
+    d = rng.normal(size=(n, 3)); d = (d / np.linalg.norm(d, axis=1, keepdims=True)).astype(np.float32)
+    d[:64, 0] = np.float32(-0.0); d[64:96, 1] = np.float32(0.0)        # axis-aligned planes, both zero signs
+    amin, amax = [-1.0] * 3, [1.0] * 3
+    d_inv, nears, fars = orc.ray_aabb(o, d, amin, amax, cascades)
+    assert fars.max() > 256.0
+    cnt = orc.march_count(o, d, d_inv, nears, fars, bits, res, amin, amax, cascades, levels, 1)
+    assert cnt.sum() == 0
+    # the same rays through a fully set grid are cut by the per-ray cap, not by the advance bound
+    full = np.full_like(bits, 0xff)
+    cnt = orc.march_count(o, d, d_inv, nears, fars, full, res, amin, amax, cascades, levels, 1)
+    assert cnt.max() <= 1024 and cnt.sum() > 0
+
+
 def test_cutoff_rule(orc):
     cnt = np.array([5, 0, 7, 3, 0, 9, 4], np.uint32)
     off = orc.exclusive_sum(cnt)
