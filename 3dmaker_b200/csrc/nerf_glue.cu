@@ -135,9 +135,37 @@ __global__ void __launch_bounds__(256) mse_rays_kernel(const float* __restrict__
     }
 }
 
+// Frame assembly of pixel-sharded rendering: pixel p of the frame belongs to tile p / tile, which rank (tile index %
+// ranks) rendered as its (tile index / ranks)-th tile; blocks holds every rank's tiles back to back, rows_per_rank
+// pixels per rank.  One float per thread (3 per pixel), coalesced on the frame side and within a tile on the block side.
+__global__ void __launch_bounds__(256) undeal_tiles_kernel(const float* __restrict__ blocks, int ranks, int64_t rows_per_rank, int64_t tile,
+                                                           int64_t num_pixels, float* __restrict__ frame) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_pixels * 3) return;
+    const int64_t p = i / 3, c = i - 3 * p;
+    const int64_t t = p / tile, within = p - t * tile;
+    const int64_t rank = t % ranks, slot = t / ranks;
+    frame[i] = blocks[(rank * rows_per_rank + slot * tile + within) * 3 + c];
+}
+
 }  // namespace nb
 
 using namespace nb;
+
+extern "C" int nb_undeal_tiles(const float* d_blocks, int ranks, int64_t rows_per_rank, int64_t tile, int64_t num_pixels, float* d_frame,
+                               void* stream) {
+    if (!d_blocks || !d_frame || ranks <= 0 || tile <= 0 || num_pixels < 0 || rows_per_rank < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_undeal_tiles: null pointer or bad tiling");
+    const int64_t tiles = (num_pixels + tile - 1) / tile;
+    if (((tiles + ranks - 1) / ranks) * tile > rows_per_rank)
+        return nb_set_error(NB_ERR_INVALID, "nb_undeal_tiles: rows_per_rank is smaller than a rank's share of the frame");
+    if (num_pixels == 0) return NB_OK;
+    undeal_tiles_kernel<<<(unsigned)((num_pixels * 3 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_blocks, ranks, rows_per_rank, tile, num_pixels,
+                                                                                                    d_frame);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
 
 extern "C" int nb_generate_rays(int width, int height, float focal, const float* c2w_3x4, int64_t first_pixel, int64_t count, float* d_rays_o,
                                 float* d_rays_d, void* stream) {

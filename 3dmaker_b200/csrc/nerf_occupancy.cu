@@ -89,20 +89,20 @@ __global__ void __launch_bounds__(256) update_tmp_grid_kernel(const float4* __re
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= N) return;
     int cell_idx = __float_as_int(samples[idx].w);
-    float densityValue = density_out[(size_t)idx * 16];
-    float sigma = expf(fminf(densityValue - densityBias, 8.0f));
+    const float logit = density_out[(size_t)idx * 16];   // first output of the density network
+    const float sigma = expf(fminf(logit - densityBias, 8.0f));
     atomicMax(reinterpret_cast<int*>(&tmpGrid[cell_idx]), __float_as_int(sigma));
 }
 
 // Decay + max into the master grid, and the block's partial sum of the NEW master values (fp64).
 __global__ void __launch_bounds__(256) update_master_grid_kernel(const float* __restrict__ tmpGrid, float* __restrict__ masterGrid,
-                                                                 float decayValue, int N, double* __restrict__ partial) {
+                                                                 float decay, int N, double* __restrict__ partial) {
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     float val = 0.0f;
     if (idx < N) {
-        float prevVal = masterGrid[idx];
-        float crrDensity = tmpGrid[idx];
-        val = (prevVal < 0.f) ? prevVal : fmaxf(prevVal * decayValue, crrDensity);
+        const float kept = masterGrid[idx];     // a negative entry marks a cell that is never updated
+        const float fresh = tmpGrid[idx];       // this update's per-cell maximum of sigma
+        val = (kept < 0.f) ? kept : fmaxf(kept * decay, fresh);
         masterGrid[idx] = val;
     }
     double s = (double)val;

@@ -138,8 +138,12 @@ class ShardedRenderer:
     a pixel run into [count, 3] slices (nb_generate_rays on a GPU).  No collective touches the data path except the
     final gather."""
 
-    def __init__(self, torch, engine, ray_fn, dist=None, tile=4096, tiled_ray_fn=None):
+    def __init__(self, torch, engine, ray_fn, dist=None, tile=4096, tiled_ray_fn=None, undeal_fn=None):
         self.torch, self.engine, self.ray_fn, self.dist, self.tile = torch, engine, ray_fn, dist, tile
+        # optional undeal_fn(blocks, ranks, rows_per_rank, tile, num_pixels, frame_out): frame assembly on rank 0 in one
+        # launch (nb_undeal_tiles)
+        self.undeal_fn = undeal_fn
+        self._local = self._gathered = self._frame = None
         # optional tiled_ray_fn(tile, first_tile, tile_stride, count, rays_o_out, rays_d_out): all tiles of this rank in one
         # call (nb_generate_rays_tiled); without it ray_fn runs once per run of consecutive pixels
         self.tiled_ray_fn = tiled_ray_fn
@@ -151,9 +155,9 @@ class ShardedRenderer:
         return sum(c for _, c in pixel_tiles(num_pixels, self.rank, self.world, self.tile))
 
     def render_local(self, num_pixels, device, rows=0):
-        """Renders this rank's tiles into one [max(local_pixels, rows), 3] tensor (tile order, zeros behind the local
-        pixels): the rays of all its tiles are generated into one buffer and rendered by ONE engine call, so the engine
-        batches samples across tiles."""
+        """Renders this rank's tiles into one [max(local_pixels, rows), 3] tensor (tile order; rows behind the local pixels
+        are padding and never read): the rays of all its tiles are generated into one buffer and rendered by ONE engine
+        call, so the engine batches samples across tiles.  The buffers are kept between frames."""
         torch = self.torch
         tiles = pixel_tiles(num_pixels, self.rank, self.world, self.tile)
         total = sum(c for _, c in tiles)
@@ -169,40 +173,40 @@ class ShardedRenderer:
             for first, count in merge_runs(tiles):
                 self.ray_fn(first, count, o[at:at + count], d[at:at + count])
                 at += count
-        out = torch.zeros((max(1, total, rows), 3), dtype=torch.float32, device=device)
+        need = max(1, total, rows)
+        if self._local is None or self._local.shape[0] < need:
+            self._local = torch.zeros((need, 3), dtype=torch.float32, device=device)
+        out = self._local[:need]
         if total > 0:
             self.engine.render(o[:total], d[:total], out[:total])
         return out, tiles
 
     def render_frame(self, num_pixels, device):
-        """Returns the [num_pixels, 3] frame on rank 0 (None elsewhere)."""
+        """Returns the [num_pixels, 3] frame on rank 0 (None elsewhere).  The tensor is reused by the next call."""
         torch = self.torch
         num_tiles = (num_pixels + self.tile - 1) // self.tile
         max_tiles = (num_tiles + self.world - 1) // self.world
+        rows = max_tiles * self.tile
         # with several ranks the local block is rendered straight into the equal-size block the gather sends
-        local, tiles = self.render_local(num_pixels, device, rows=max_tiles * self.tile if self.world > 1 else 0)
+        local, tiles = self.render_local(num_pixels, device, rows=rows if self.world > 1 else 0)
         if self.world == 1:
-            frame = torch.empty((num_pixels, 3), dtype=torch.float32, device=device)
-            self._place(frame, local, tiles)
-            return frame
-        # equal-size gather: pad every rank's block to the largest one; rank 0 receives into one [world, tiles, tile, 3]
-        # buffer and un-deals the tiles with ONE strided copy (tile j of rank r is tile j * world + r of the frame)
-        padded = local[:max_tiles * self.tile]
+            return local[:num_pixels]            # one rank holds every tile in frame order: the block IS the frame
+        # equal-size gather: every rank's block padded to the largest one; rank 0 receives all blocks into one buffer and
+        # un-deals the tiles into the frame with one launch (tile j of rank r is tile j * world + r of the frame)
+        padded = local[:rows]
         if self.rank == 0:
-            buf = torch.empty((self.world, max_tiles, self.tile, 3), dtype=torch.float32, device=device)
-            self.dist.gather(padded, [buf[r].view(max_tiles * self.tile, 3) for r in range(self.world)], dst=0)
-            frame = torch.empty((max_tiles, self.world, self.tile, 3), dtype=torch.float32, device=device)
-            frame.copy_(buf.permute(1, 0, 2, 3))
-            return frame.view(-1, 3)[:num_pixels]
+            if self._gathered is None or self._gathered.shape[1] != rows or self._frame.shape[0] != num_pixels:
+                self._gathered = torch.empty((self.world, rows, 3), dtype=torch.float32, device=device)
+                self._frame = torch.empty((num_pixels, 3), dtype=torch.float32, device=device)
+            buf = self._gathered
+            self.dist.gather(padded, [buf[r] for r in range(self.world)], dst=0)
+            if self.undeal_fn is not None:
+                self.undeal_fn(buf, self.world, rows, self.tile, num_pixels, self._frame)
+            else:   # no device kernel at hand (CPU ranks in the tests): the same permutation with a strided copy
+                self._frame.copy_(buf.view(self.world, max_tiles, self.tile, 3).permute(1, 0, 2, 3).reshape(-1, 3)[:num_pixels])
+            return self._frame
         self.dist.gather(padded, None, dst=0)
         return None
-
-    @staticmethod
-    def _place(frame, block, tiles):
-        at = 0
-        for first, count in merge_runs(tiles):
-            frame[first:first + count] = block[at:at + count]
-            at += count
 
 
 def gathered_bytes(num_pixels, world, tile=4096):

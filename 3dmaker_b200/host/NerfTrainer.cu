@@ -142,10 +142,22 @@ Image INerfTrainer::renderTrainView(int index, int width, int height) {
     return img;
 }
 
+// Learning rate of the step about to run: half a cosine from maxLR down to minLR over the anneal span (annealSteps, or
+// the whole run when that is 0), minLR from there on.  Schedule of the reference's currentLR (NerfTrainer.cu:131-135).
+namespace {
+struct CosineDecay {
+    float high, low;
+    int span;
+    float at(int step) const {
+        const float x = (span > 0 && step < span) ? (float)step / (float)span : 1.0f;
+        return low + (high - low) * 0.5f * (1.0f + cosf(kPI * x));
+    }
+};
+}  // namespace
+
 float INerfTrainer::currentLR() const {
-    int anneal = (m_config.annealSteps > 0) ? m_config.annealSteps : std::max(1, m_targetSteps);
-    float progress = fminf((float)m_globalStep / (float)anneal, 1.0f);
-    return m_config.minLR + 0.5f * (m_config.maxLR - m_config.minLR) * (1.0f + cosf(kPI * progress));
+    const CosineDecay lr{m_config.maxLR, m_config.minLR, m_config.annealSteps > 0 ? m_config.annealSteps : std::max(1, m_targetSteps)};
+    return lr.at(m_globalStep);
 }
 
 float INerfTrainer::trainOneChunk(bool computeLoss) {
@@ -160,15 +172,22 @@ float INerfTrainer::trainOneChunk(bool computeLoss) {
     if (m_randomBg) bg = make_float3(m_dist(m_rng), m_dist(m_rng), m_dist(m_rng));  // random-background augmentation
     m_nerf->setBgColor(bg);
 
-    m_source(m_rayCursor, (uint32_t)chunkSize, m_epochSeed, bg, m_d_rays_o.as<float3>(), m_d_rays_d.as<float3>(), m_d_rgb_true.as<float>(), 0);
+    // Data parallel: the chunk is the GLOBAL ray batch of these steps; this rank fetches and trains its contiguous share.
+    uint32_t first = m_rayCursor;
+    const uint32_t globalChunk = (uint32_t)chunkSize;
+    if (m_dpWorld > 1) {
+        first += (uint32_t)((uint64_t)globalChunk * m_dpRank / m_dpWorld);
+        chunkSize = (int)((uint64_t)globalChunk * (m_dpRank + 1) / m_dpWorld - (uint64_t)globalChunk * m_dpRank / m_dpWorld);
+    }
+    m_source(first, (uint32_t)chunkSize, m_epochSeed, bg, m_d_rays_o.as<float3>(), m_d_rays_d.as<float3>(), m_d_rgb_true.as<float>(), 0);
     if (computeLoss) throw_on_error(nb_zero_async(m_d_loss.as<float>(), sizeof(float), 0), "loss reset");
 
     const bool priors = m_hasImageSet && m_imageSet.num_records > 0;
     m_nerf->trainWithRaysHit(m_d_rays_o.as<float3>(), m_d_rays_d.as<float3>(), priors ? m_d_prior_depth.as<float>() : nullptr,
                              priors ? m_d_prior_sigma.as<float>() : nullptr, m_d_rgb_true.as<float>(), (uint32_t)chunkSize,
                              m_globalStep, nullptr, computeLoss ? m_d_chunkRgb.as<float>() : nullptr, 0);
-    m_rayCursor += chunkSize;
-    m_raysSeen += chunkSize;
+    m_rayCursor += globalChunk;
+    m_raysSeen += globalChunk;
     if (!computeLoss) return -1.0f;
     throw_on_error(nb_mse_rays(m_d_chunkRgb.as<float>(), m_d_rgb_true.as<float>(), m_d_loss.as<float>(), chunkSize, 0), "chunk MSE");
     float h_loss = 0.0f;
@@ -176,120 +195,164 @@ float INerfTrainer::trainOneChunk(bool computeLoss) {
     return h_loss / std::max(1, chunkSize);
 }
 
+void INerfTrainer::setDataParallel(InstantNerf::GradSync sync, uint32_t rank, uint32_t world, int stepsPerChunk) {
+    if (world == 0 || rank >= world) throw std::runtime_error("setDataParallel: rank must be below the number of ranks");
+    buildModel();
+    m_dpRank = rank; m_dpWorld = world;
+    m_nerf->setGlobalRayScale(world);
+    m_nerf->setGradSync(world > 1 ? std::move(sync) : InstantNerf::GradSync());
+    // the same number of optimizer steps, hence gradient exchanges, per chunk on every rank
+    m_nerf->setStepsPerCall(world > 1 ? std::max(1, stepsPerChunk) : 0);
+}
+
+// ---- run bookkeeping ---------------------------------------------------------------------------------------------
+// The C handle API counts optimizer steps inside the engine (trainWithRaysHit advances m_globalStep through its
+// reference argument); what the facade adds is the target, the ray cursor, the pace estimate and the loss history.
+
 void INerfTrainer::beginTraining(int totalSteps) {
-    m_targetSteps = std::max(1, totalSteps);
-    m_globalStep = 0;
-    m_rayCursor = 0;
+    m_lossHistory.clear();
     m_raysSeen = 0.0;
     m_emaMsPerStep = 0.0;
-    m_lossHistory.clear();
+    m_rayCursor = 0;
+    m_globalStep = 0;
+    m_targetSteps = totalSteps < 1 ? 1 : totalSteps;
 }
+
+// Blends a new ms-per-step measurement into the running pace: 30 % new, 70 % history (the weights of the reference's
+// progress estimate, NerfTrainer.cu:208-211); the first measurement is taken as it is.
+static double blendPace(double pace, double measuredMs) { return pace > 0.0 ? pace + 0.30 * (measuredMs - pace) : measuredMs; }
 
 TrainStats INerfTrainer::trainSteps(int nSteps) {
-    TrainStats s;
-    if (!m_nerf || !m_source || m_total_rays == 0) return s;
+    TrainStats report;
+    if (m_nerf == nullptr || !m_source || m_total_rays == 0) return report;
     if (m_targetSteps == 0) beginTraining(20000);
-    int target = std::min(m_globalStep + std::max(1, nSteps), m_targetSteps);
-    int startStep = m_globalStep;
-    auto t0 = std::chrono::high_resolution_clock::now();
-    float mse = -1.0f;
-    bool first = true;
-    while (m_globalStep < target) {
-        float chunkMse = trainOneChunk(first);
-        if (chunkMse > 0.0f) mse = chunkMse;
-        first = false;
+
+    using Clock = std::chrono::steady_clock;
+    const int stopAt = std::min(m_targetSteps, m_globalStep + std::max(nSteps, 1));
+    const int before = m_globalStep;
+    const Clock::time_point began = Clock::now();
+    // only the first chunk of a tick pays for the MSE read-back (NerfTrainer.cu:173-178)
+    float tickMse = -1.0f;
+    for (bool measure = true; m_globalStep < stopAt; measure = false) {
+        const float v = trainOneChunk(measure);
+        if (v > 0.0f) tickMse = v;
     }
     throw_on_cuda(cudaDeviceSynchronize(), "trainSteps");
-    auto t1 = std::chrono::high_resolution_clock::now();
-    int stepsDone = m_globalStep - startStep;
-    if (stepsDone > 0) {
-        double msPerStep = std::chrono::duration<double, std::milli>(t1 - t0).count() / stepsDone;
-        m_emaMsPerStep = (m_emaMsPerStep > 0.0) ? (0.70 * m_emaMsPerStep + 0.30 * msPerStep) : msPerStep;
-    }
-    if (mse > 0.0f) m_lossHistory.push_back(mse);
-    int remaining = std::max(0, m_targetSteps - m_globalStep);
-    s.step = m_globalStep;
-    s.targetSteps = m_targetSteps;
-    s.loss = (mse > 0.0f) ? mse : (m_lossHistory.empty() ? 0.0f : m_lossHistory.back());
-    s.psnr = (s.loss > 0.0f) ? -10.0f * log10f(fmaxf(s.loss, 1e-8f)) : 0.0f;
-    s.lr = currentLR();
-    s.epochs = epochs();
-    s.msPerStep = (float)m_emaMsPerStep;
-    s.etaSeconds = (float)(m_emaMsPerStep * remaining / 1000.0);
-    return s;
+    const double elapsedMs = std::chrono::duration<double, std::milli>(Clock::now() - began).count();
+    if (m_globalStep > before) m_emaMsPerStep = blendPace(m_emaMsPerStep, elapsedMs / (m_globalStep - before));
+    if (tickMse > 0.0f) m_lossHistory.push_back(tickMse);
+
+    report.loss = tickMse > 0.0f ? tickMse : (m_lossHistory.empty() ? 0.0f : m_lossHistory.back());
+    report.psnr = report.loss > 0.0f ? -10.0f * log10f(fmaxf(report.loss, 1e-8f)) : 0.0f;
+    report.step = m_globalStep;
+    report.targetSteps = m_targetSteps;
+    report.lr = currentLR();
+    report.epochs = epochs();
+    report.msPerStep = (float)m_emaMsPerStep;
+    report.etaSeconds = (float)(m_emaMsPerStep * 1e-3 * std::max(m_targetSteps - m_globalStep, 0));
+    return report;
 }
 
-void INerfTrainer::train(int maxSteps, int maxEpochs) {
-    (void)maxEpochs;
-    if (!m_nerf || !m_source || m_total_rays == 0) {
+void INerfTrainer::train(int maxSteps, int /*maxEpochs*/) {
+    if (m_nerf == nullptr || !m_source || m_total_rays == 0) {
         std::cerr << "[INerfTrainer] train() called before a ray source was set." << std::endl;
         return;
     }
     beginTraining(maxSteps);
-    int tick = std::max(1, maxSteps / 100);
-    while (!isTrainingDone()) {
-        TrainStats s = trainSteps(tick);
-        std::printf("\r%d/%d steps | epoch %.2f | %.2f ms/step | ETA %.0f s | PSNR %.1f   ", s.step, s.targetSteps, s.epochs, s.msPerStep,
-                    s.etaSeconds, s.psnr);
+    // a hundred progress lines per run
+    for (const int stride = std::max(maxSteps / 100, 1); !isTrainingDone();) {
+        const TrainStats r = trainSteps(stride);
+        std::printf("\r%d/%d steps | epoch %.2f | %.2f ms/step | ETA %.0f s | PSNR %.1f   ", r.step, r.targetSteps, r.epochs, r.msPerStep,
+                    r.etaSeconds, r.psnr);
         std::fflush(stdout);
     }
     std::printf("\n");
 }
 
-static const char kSceneMagic[4] = {'S', 'C', 'N', '1'};
-static const std::streamoff kSceneFooterBytes = 4 + 8 * (std::streamoff)sizeof(float);
+// ---- scene footer ------------------------------------------------------------------------------------------------
+// 36 bytes behind the .inerf payload: "SCN1", then centre xyz, up xyz, scale, horizontal field of view (radians), all
+// fp32 - the record the reference appends and looks for at the end of the file (NerfTrainer.cu:266-300).
+namespace {
+struct SceneFooter {
+    char tag[4];
+    float centre[3], up[3], scale, fovX;
+};
+static_assert(sizeof(SceneFooter) == 36, "the scene footer is 36 bytes on disk");
+const char kFooterTag[4] = {'S', 'C', 'N', '1'};
+
+bool readFooter(const std::string& path, SceneFooter& f) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) return false;
+    in.seekg(0, std::ios::end);
+    const std::streamoff bytes = in.tellg();
+    if (bytes < (std::streamoff)sizeof(SceneFooter)) return false;
+    in.seekg(bytes - (std::streamoff)sizeof(SceneFooter));
+    in.read(reinterpret_cast<char*>(&f), sizeof(SceneFooter));
+    return bool(in) && std::equal(f.tag, f.tag + 4, kFooterTag);
+}
+}  // namespace
 
 void INerfTrainer::save(const std::string& path) {
-    if (!m_nerf) return;
+    if (m_nerf == nullptr) return;
     m_nerf->save(path);
+    SceneFooter f;
+    std::copy(kFooterTag, kFooterTag + 4, f.tag);
+    f.centre[0] = m_sceneCenter.x; f.centre[1] = m_sceneCenter.y; f.centre[2] = m_sceneCenter.z;
+    f.up[0] = m_sceneUp.x; f.up[1] = m_sceneUp.y; f.up[2] = m_sceneUp.z;
+    f.scale = m_sceneScale;
+    f.fovX = m_cameraAngleX;
     std::ofstream out(path, std::ios::binary | std::ios::app);
-    if (!out) return;
-    float buf[8] = {m_sceneCenter.x, m_sceneCenter.y, m_sceneCenter.z, m_sceneUp.x, m_sceneUp.y, m_sceneUp.z, m_sceneScale, m_cameraAngleX};
-    out.write(kSceneMagic, 4);
-    out.write(reinterpret_cast<const char*>(buf), sizeof(buf));
+    if (out) out.write(reinterpret_cast<const char*>(&f), sizeof(SceneFooter));
 }
 
 void INerfTrainer::load(const std::string& path) {
     buildModel();
     m_nerf->load(path);
     m_masterConfig = m_nerf->options();
-    std::ifstream in(path, std::ios::binary | std::ios::ate);
-    if (!in) return;
-    std::streamoff size = in.tellg();
-    if (size < kSceneFooterBytes) return;
-    in.seekg(size - kSceneFooterBytes, std::ios::beg);
-    char magic[4];
-    in.read(magic, 4);
-    if (std::string(magic, 4) != std::string(kSceneMagic, 4)) return;
-    float buf[8];
-    in.read(reinterpret_cast<char*>(buf), sizeof(buf));
-    m_sceneCenter = {buf[0], buf[1], buf[2]};
-    m_sceneUp = {buf[3], buf[4], buf[5]};
-    m_sceneScale = buf[6];
-    m_cameraAngleX = buf[7];
+    SceneFooter f;
+    if (!readFooter(path, f)) return;   // a bare .inerf file: keep the current scene frame
+    m_sceneCenter = {f.centre[0], f.centre[1], f.centre[2]};
+    m_sceneUp = {f.up[0], f.up[1], f.up[2]};
+    m_sceneScale = f.scale;
+    m_cameraAngleX = f.fovX;
 }
 
-static inline float3 cross3(float3 a, float3 b) { return make_float3(a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x); }
-static inline float3 normalize3(float3 v) {
-    float l = sqrtf(v.x * v.x + v.y * v.y + v.z * v.z);
-    return l > 0 ? make_float3(v.x / l, v.y / l, v.z / l) : v;
+// ---- orbit camera ------------------------------------------------------------------------------------------------
+namespace {
+struct V3 {
+    float v[3];
+    float operator[](int i) const { return v[i]; }
+};
+V3 cross(const V3& a, const V3& b) { return {{a[1] * b[2] - a[2] * b[1], a[2] * b[0] - a[0] * b[2], a[0] * b[1] - a[1] * b[0]}}; }
+V3 unit(const V3& a) {
+    const float len = sqrtf(a[0] * a[0] + a[1] * a[1] + a[2] * a[2]);
+    return len > 0.0f ? V3{{a[0] / len, a[1] / len, a[2] / len}} : a;
 }
+V3 mix2(float s, const V3& a, float t, const V3& b) { return {{s * a[0] + t * b[0], s * a[1] + t * b[1], s * a[2] + t * b[2]}}; }
+}  // namespace
 
+// Camera on a sphere of `radius` around the scene centre, looking at it: azimuth turns in the plane perpendicular to the
+// scene's up vector, elevation lifts towards it.  Row-major 3x4 with columns right, up, backward, eye - the matrix
+// renderOrbit of the reference builds (NerfTrainer.cu:330-366).
 void INerfTrainer::orbitCamera(float azimuthDeg, float elevationDeg, float radius, float c2w[12]) const {
-    float3 center = make_float3(m_sceneCenter.x, m_sceneCenter.y, m_sceneCenter.z);
-    float3 up = normalize3(make_float3(m_sceneUp.x, m_sceneUp.y, m_sceneUp.z));
-    float3 ref = (fabsf(up.y) < 0.9f) ? make_float3(0, 1, 0) : make_float3(1, 0, 0);
-    float3 a = normalize3(cross3(up, ref));
-    float3 b = cross3(up, a);
-    float az = azimuthDeg * kPI / 180.0f, el = elevationDeg * kPI / 180.0f;
-    float3 planar = make_float3(cosf(az) * a.x + sinf(az) * b.x, cosf(az) * a.y + sinf(az) * b.y, cosf(az) * a.z + sinf(az) * b.z);
-    float3 dir = make_float3(cosf(el) * planar.x + sinf(el) * up.x, cosf(el) * planar.y + sinf(el) * up.y, cosf(el) * planar.z + sinf(el) * up.z);
-    float3 eye = make_float3(center.x + radius * dir.x, center.y + radius * dir.y, center.z + radius * dir.z);
-    float3 f = normalize3(make_float3(center.x - eye.x, center.y - eye.y, center.z - eye.z));
-    float3 r = normalize3(cross3(f, up));
-    float3 u = cross3(r, f);
-    const float m[12] = {r.x, u.x, -f.x, eye.x, r.y, u.y, -f.y, eye.y, r.z, u.z, -f.z, eye.z};
-    for (int i = 0; i < 12; i++) c2w[i] = m[i];
+    const V3 centre{{m_sceneCenter.x, m_sceneCenter.y, m_sceneCenter.z}};
+    const V3 up = unit(V3{{m_sceneUp.x, m_sceneUp.y, m_sceneUp.z}});
+    // two unit vectors spanning the horizontal plane; the helper axis avoids one parallel to up
+    const V3 helper = fabsf(up[1]) < 0.9f ? V3{{0.f, 1.f, 0.f}} : V3{{1.f, 0.f, 0.f}};
+    const V3 e0 = unit(cross(up, helper));
+    const V3 e1 = cross(up, e0);
+    const float az = azimuthDeg * (kPI / 180.0f), el = elevationDeg * (kPI / 180.0f);
+    const V3 outward = mix2(cosf(el), mix2(cosf(az), e0, sinf(az), e1), sinf(el), up);
+    const V3 eye = mix2(1.0f, centre, radius, outward);
+    const V3 forward = unit(mix2(1.0f, centre, -1.0f, eye));
+    const V3 right = unit(cross(forward, up));
+    const V3 camUp = cross(right, forward);
+    for (int row = 0; row < 3; row++) {
+        c2w[4 * row + 0] = right[row];
+        c2w[4 * row + 1] = camUp[row];
+        c2w[4 * row + 2] = -forward[row];
+        c2w[4 * row + 3] = eye[row];
+    }
 }
 
 void INerfTrainer::renderPixels(const float c2w[12], float focal, int width, int height, int64_t firstPixel, int64_t count, float* d_rgb_out,

@@ -72,6 +72,13 @@ public:
     float validate();
     // Frame `index` of the image set re-rendered from its own pose (NerfTrainer.cu:368-376).
     Image renderTrainView(int index, int width = 0, int height = 0);
+    // Data-parallel training (no counterpart in the reference, which is single-GPU): one process per GPU, each with its own
+    // INerfTrainer on the same ray source.  A chunk of the ray source becomes the GLOBAL batch: rank r fetches and trains
+    // rays [r * chunk / world, (r + 1) * chunk / world) of it, loss gradients are normalised by the global ray count, every
+    // rank takes exactly stepsPerChunk optimizer steps per chunk, and `sync` (e.g. ncclAllReduce(sum) in place on the
+    // caller's communicator and the given stream) runs on the flat gradient arena between backward and Adam of each.
+    // world == 1 restores single-process training.  Call after init() and before training.
+    void setDataParallel(InstantNerf::GradSync sync, uint32_t rank, uint32_t world, int stepsPerChunk = 1);
     // Lets a caller override what init() derives (AABB, network sizes, ...) before the model is built.
     NerfOptions& options() { return m_masterConfig; }
 
@@ -115,6 +122,7 @@ private:
     nb::DeviceMem m_d_prior_depth, m_d_prior_sigma;
     bool m_randomBg = true;
     uint32_t m_total_rays = 0;
+    uint32_t m_dpRank = 0, m_dpWorld = 1;
 
     Vec3 m_sceneCenter = {0.0f, 0.0f, 0.0f};
     Vec3 m_sceneUp = {0.0f, 1.0f, 0.0f};

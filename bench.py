@@ -704,7 +704,11 @@ def run_render(args, rank, world, local_rank):
         nb.check(lib.nb_generate_rays_tiled(W, H, focal, c2w.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), tile, first_tile, stride, count,
                                             nb.ptr(o), nb.ptr(d), nb.stream_ptr()), "nb_generate_rays_tiled")
 
-    r = D.ShardedRenderer(torch, eng, ray_fn, dist if (world > 1 and not reference) else None, tile=1 << 14, tiled_ray_fn=tiled_ray_fn)
+    def undeal_fn(blocks, ranks, rows, tile, num_pixels, frame):
+        nb.check(lib.nb_undeal_tiles(nb.ptr(blocks), ranks, rows, tile, num_pixels, nb.ptr(frame), nb.stream_ptr()), "nb_undeal_tiles")
+
+    r = D.ShardedRenderer(torch, eng, ray_fn, dist if (world > 1 and not reference) else None, tile=1 << 14, tiled_ray_fn=tiled_ray_fn,
+                          undeal_fn=undeal_fn)
     nranks = 1 if reference else world
 
     def frame(k):

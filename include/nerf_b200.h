@@ -181,6 +181,11 @@ int nb_generate_rays(int width, int height, float focal, const float* c2w_3x4, i
  * tiles a rank of a pixel-sharded frame renders (distributed.pixel_tiles); only the last tile may be cut short by count. */
 int nb_generate_rays_tiled(int width, int height, float focal, const float* c2w_3x4, int64_t tile, int64_t first_tile, int64_t tile_stride,
                            int64_t count, float* d_rays_o, float* d_rays_d, void* stream);
+/* Inverse of that deal, for the rank that assembles a pixel-sharded frame (no counterpart in the reference, which renders
+ * on one GPU): d_blocks holds `ranks` blocks of rows_per_rank pixels (3 floats each), block r = the tiles r, r + ranks,
+ * r + 2 ranks, ... of the frame one after the other as rank r rendered them; d_frame receives the num_pixels x 3 frame. */
+int nb_undeal_tiles(const float* d_blocks, int ranks, int64_t rows_per_rank, int64_t tile, int64_t num_pixels, float* d_frame,
+                    void* stream);
 /* Replaces mse_kernel (modules/NeRF/NerfTrainer.cu:15-23): ADDS sum over rays of mean((pred - target)^2) to *d_loss_sum. */
 int nb_mse_rays(const float* d_pred3, const float* d_target3, float* d_loss_sum, int64_t n, void* stream);
 

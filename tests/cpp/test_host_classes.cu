@@ -3,6 +3,7 @@
 // exit code is the number of failures so a test runner can rely on it.
 #include <cmath>
 #include <cstdio>
+#include <utility>
 #include <vector>
 
 #include "../../3dmaker_b200/host/NerfTrainer.h"
@@ -199,11 +200,48 @@ static void test_trainer_image_set() {
     std::printf("[SUCCESS?] INerfTrainer image set, %d failures so far\n", g_fail);
 }
 
+// The facade's data-parallel entry seen from one rank of two: the ray source is asked for this rank's half of every
+// chunk, the exchange callback runs exactly stepsPerChunk times per chunk on the whole gradient arena, and the cursor
+// advances by the global chunk.
+static void test_trainer_data_parallel_contract() {
+    INerfTrainer trainer;
+    NerfConfig cfg;
+    cfg.batchSize = 1 << 14; cfg.renderBatchSize = 1 << 14; cfg.lambdaDist = 0.0f;
+    trainer.init(cfg);
+    NerfOptions& o = trainer.options();
+    o.gridResolution = make_uint3(32, 32, 32); o.levelsMipmap = 3; o.hashTableSize = 1 << 14;
+    o.aabbMin = make_float3(-0.5f, -0.5f, -0.5f); o.aabbMax = make_float3(0.5f, 0.5f, 0.5f);
+    const int W = 128, H = 128;                      // 16384 rays = four chunks of batchSize / 4
+    float c2w[12];
+    trainer.orbitCamera(30.0f, 10.0f, 1.5f, c2w);
+    const float focal = 0.5f * W / std::tan(0.5f * 50.0f * 3.14159265f / 180.0f);
+    std::vector<std::pair<uint32_t, uint32_t>> asked;
+    auto source = [&](uint32_t cursor, uint32_t count, uint32_t, float3, float3* d_o, float3* d_d, float* d_rgb, cudaStream_t s) {
+        asked.push_back({cursor, count});
+        nb_generate_rays(W, H, focal, c2w, cursor, count, (float*)d_o, (float*)d_d, s);
+        cudaMemsetAsync(d_rgb, 0, (size_t)count * 3 * sizeof(float), s);
+    };
+    int exchanges = 0;
+    int64_t seenCount = 0;
+    EXPECT_THROW(trainer.setDataParallel([](float*, int64_t, cudaStream_t) {}, 2, 2));
+    EXPECT_NO_THROW(trainer.setDataParallel([&](float* g, int64_t count, cudaStream_t) { exchanges += (g != nullptr); seenCount = count; },
+                                            /*rank=*/1, /*world=*/2, /*stepsPerChunk=*/3));
+    EXPECT_NO_THROW(trainer.setRaySource(source, W * H, Vec3{0, 1, 0}, false));
+    trainer.beginTraining(6);
+    TrainStats st = trainer.trainSteps(6);
+    const uint32_t chunk = (uint32_t)o.rayChunkSize;
+    CHECK(st.step == 6 && exchanges == 6);
+    CHECK(seenCount == trainer.engine()->arena().total);
+    CHECK(asked.size() == 2 && asked[0].first == chunk / 2 && asked[0].second == chunk / 2 && asked[1].first == chunk + chunk / 2);
+    std::printf("[SUCCESS?] INerfTrainer data-parallel contract, %d failures so far\n", g_fail);
+}
+
 int main() {
     test_tinymlp_modes();
     test_hashgrid_modes();
     test_trainer_facade();
     test_trainer_image_set();
+    test_trainer_data_parallel_contract();
     std::printf(g_fail == 0 ? "[SUCCESS] all host-class checks passed\n" : "[FAILED] %d checks failed\n", g_fail);
     return g_fail;
 }

@@ -1,5 +1,7 @@
 """Generates tests/golden/reference_vectors.npz: outputs of the REFERENCE's own CUDA code (its sources compiled where
-they lie into oracle/_ref/libref3dmaker.so by oracle/build_ref.py) on small seeded inputs.
+they lie into oracle/_ref/libref3dmaker.so by oracle/build_ref.py) on small seeded inputs - reference output only.
+A second file, tests/golden/device_level_scales.npz, holds what is NOT reference output: the per-level grid
+resolutions as this library's set-up kernel evaluates them on the device (the reference never materialises them).
 
 Run on a machine with a CUDA GPU, from the repository root, after the reference build exists:
 
@@ -68,7 +70,7 @@ def main():
     P, st = nb.ptr, nb.stream_ptr()
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     inp = golden_inputs()
-    out = {}
+    out, aux = {}, {}
     V = lambda p, cnt, dt=np.float32: nm.view_tensor(torch, p, cnt, dt).cpu().numpy().copy()
 
     # ---- field forward + backward, both growth factors ----------------------------------------------------
@@ -96,13 +98,13 @@ def main():
                 out["field_%s_dW_%d_%d" % (tag, net, l)] = V(lib.ref_field_layer_grads(rf, net, l, 0), ki * ko)
                 out["field_%s_db_%d_%d" % (tag, net, l)] = V(lib.ref_field_layer_grads(rf, net, l, 1), ko)
         lib.ref_field_destroy(rf)
-        # aux (NOT a reference output): the per-level resolutions as evaluated on the device by this library's set-up
-        # kernel with the reference's expressions.  The reference never materialises them; that the two agree is what
-        # tests/test_gpu_vs_reference.py checks.  Stored so the CPU test indexes the same cells as the GPU did.
+        # NOT a reference output, hence a file of its own: the per-level resolutions as evaluated on the device by this
+        # library's set-up kernel with the reference's expressions.  The reference never materialises them; that the two
+        # agree is what tests/test_gpu_vs_reference.py checks.  Stored so the CPU test indexes the same cells as the GPU did.
         gd = nb.grid_setup(f["L"], f["T"], f["base"], b)
-        out["aux_%s_scales" % tag] = np.array(list(gd.scales)[:f["L"]], np.float32)
-        out["aux_%s_scatter_scales" % tag] = np.array(list(gd.scatter_scales)[:f["L"]], np.float32)
-        out["aux_%s_dense_level_start" % tag] = np.array([gd.dense_level_start], np.int32)
+        aux["%s_scales" % tag] = np.array(list(gd.scales)[:f["L"]], np.float32)
+        aux["%s_scatter_scales" % tag] = np.array(list(gd.scatter_scales)[:f["L"]], np.float32)
+        aux["%s_dense_level_start" % tag] = np.array([gd.dense_level_start], np.int32)
 
     # ---- ray / box, march, compaction ------------------------------------------------------------------------
     m = MARCH
@@ -159,11 +161,14 @@ def main():
 
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
-    print("wrote %s (%d arrays, %.0f KB)" % (path, len(out), os.path.getsize(path) / 1024))
+    aux_path = os.path.join(HERE, "device_level_scales.npz")
+    np.savez_compressed(aux_path, **aux)
+    print("wrote %s (%d arrays, %.0f KB) and %s" % (path, len(out), os.path.getsize(path) / 1024, aux_path))
     if len(sys.argv) > 1:                      # optional second copy, e.g. into a folder that is collected from the GPU machine
         import shutil
         os.makedirs(sys.argv[1], exist_ok=True)
         shutil.copy(path, os.path.join(sys.argv[1], "reference_vectors.npz"))
+        shutil.copy(aux_path, os.path.join(sys.argv[1], "device_level_scales.npz"))
 
 
 if __name__ == "__main__":

@@ -17,6 +17,7 @@ from helpers import ABS_RGB, REL_MLP, half_bits, half_vals, rel_err  # noqa: E40
 from oracle_pipeline import OracleField  # noqa: E402
 
 PATH = os.path.join(HERE, "golden", "reference_vectors.npz")
+AUX_PATH = os.path.join(HERE, "golden", "device_level_scales.npz")   # not reference output: see make_golden.py
 
 
 @pytest.fixture(scope="module")
@@ -36,8 +37,9 @@ def inputs():
 def test_field_step_against_reference_outputs(orc, golden, inputs, tag, b):
     inp, f, _ = inputs
     fi = inp["field"]
-    scales, sscales = golden["aux_%s_scales" % tag], golden["aux_%s_scatter_scales" % tag]
-    dls = int(golden["aux_%s_dense_level_start" % tag][0])
+    aux = np.load(AUX_PATH)
+    scales, sscales = aux["%s_scales" % tag], aux["%s_scatter_scales" % tag]
+    dls = int(aux["%s_dense_level_start" % tag][0])
     assert dls == orc.dense_level_start(f["T"], f["base"], b, f["L"])
     assert np.allclose(orc.level_scales(f["base"], b, f["L"]), scales, rtol=2e-6)
     field = OracleField(f["L"], f["T"], f["base"], b, scales, dls, f["density"], f["color"], fi["table"], fi["dens"][0], fi["dens"][1],

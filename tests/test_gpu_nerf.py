@@ -6,6 +6,7 @@ The march kernels use the device's approximate division / log2 / exp2 (the refer
 voxel face within that error may gain or lose a sample: counts are compared per ray with a small allowance
 (MARCH_MISMATCH), everything downstream is compared on the rays whose counts agree."""
 import ctypes
+import importlib
 
 import numpy as np
 import pytest
@@ -421,3 +422,26 @@ def test_generated_rays_plain_and_tiled(cuda, nb):
         idx = torch.cat([torch.arange(f, f + c, device="cuda") for f, c in tiles])
         assert torch.equal(to, o[idx]) and torch.equal(td, d[idx])
     assert lib.nb_generate_rays_tiled(W, H, focal, cp, tile, 14, 1, 59, P(o), P(d), st) != 0     # one pixel past the frame
+
+
+@pytest.mark.parametrize("world,tile,num_pixels", [(1, 64, 1000), (3, 64, 1000), (8, 16384, 1920 * 1080), (4, 128, 128 * 8 + 5)])
+def test_undeal_tiles_rebuilds_the_frame(cuda, nb, world, tile, num_pixels):
+    """nb_undeal_tiles: the blocks the ranks of a pixel-sharded frame send (tiles dealt round-robin, padded to equal
+    size) back into frame order - bit for bit the strided copy it replaces."""
+    torch = cuda
+    lib, P = nb.load(), nb.ptr
+    D = importlib.import_module("3dmaker_b200.distributed")
+    num_tiles = (num_pixels + tile - 1) // tile
+    rows = (num_tiles + world - 1) // world * tile
+    frame_true = torch.rand((num_pixels, 3), device="cuda")
+    blocks = torch.full((world, rows, 3), -7.0, device="cuda")
+    for r in range(world):
+        at = 0
+        for first, count in D.pixel_tiles(num_pixels, r, world, tile):
+            blocks[r, at:at + count] = frame_true[first:first + count]
+            at += tile
+    frame = torch.zeros((num_pixels, 3), device="cuda")
+    nb.check(lib.nb_undeal_tiles(P(blocks), world, rows, tile, num_pixels, P(frame), nb.stream_ptr()), "nb_undeal_tiles")
+    torch.cuda.synchronize()
+    assert torch.equal(frame, frame_true)
+    assert lib.nb_undeal_tiles(P(blocks), world, rows - 1, tile, num_pixels, P(frame), nb.stream_ptr()) == 1   # block too small
