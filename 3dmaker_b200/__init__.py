@@ -137,6 +137,7 @@ class StepView(ctypes.Structure):
 
 
 GRAD_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
+PARAM_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
 
 
 class NerfB200Error(RuntimeError):
@@ -231,6 +232,7 @@ _SIGNATURES = {
     "nb_nerf_last_render_samples": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint64)]),
     "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_steps_per_call": (c_int, [c_void_p, c_int]),
+    "nb_nerf_set_optimizer_shard": (c_int, [c_void_p, ctypes.c_uint32, ctypes.c_uint32, PARAM_SYNC_FN, c_void_p]),
     "nb_nerf_set_hit_counts_capacity": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_set_grad_buffer": (c_int, [c_void_p, c_void_p, c_int64]),

@@ -77,11 +77,21 @@ class DataParallelTrainer:
     """Wraps a scene engine so that train_rays() takes the GLOBAL ray batch.
 
     engine needs: set_global_ray_scale(int), set_steps_per_call(int), set_grad_sync(fn), train_rays(o, d, rgb) -> total
-    optimizer steps so far, rays_consumed(), arena_tensor(name).  dist is torch.distributed (already initialised) or
-    None for a single process.  registered_gradient (NCCL on GPUs): the engine's gradient arena is moved into
-    CollectiveBuffers memory (engine.set_grad_buffer)."""
+    optimizer steps so far, rays_consumed(), arena_tensor(name), arena(); for exchange="sharded" also
+    set_optimizer_shard(rank, world, fn).  dist is torch.distributed (already initialised) or None for a single process.
+    registered_gradient (NCCL on GPUs): the engine's gradient arena is moved into CollectiveBuffers memory
+    (engine.set_grad_buffer).
 
-    def __init__(self, torch, engine, dist=None, steps_per_call=1, registered_gradient=False):
+    exchange: how the ranks' gradients meet the optimizer.
+      "allreduce"  one SUM all-reduce of the flat gradient arena, every rank runs Adam on everything (replicated state);
+      "sharded"    reduce-scatter of the hash-table gradient in place, Adam on this rank's 1/N slice of the table (and
+                   on the small dense tail, which is all-reduced), all-gather of the updated fp16 slices: 3/4 of the
+                   all-reduce's bytes on the wire and 1/N of the optimizer's memory traffic - the part of a step that
+                   does not shrink with the number of ranks when the batch is split (2^22-entry levels: 4.6 GB per
+                   Adam launch).  The fp32 master copy and the moments of a slice live on its owner; gather_master()
+                   collects the master copy (before saving)."""
+
+    def __init__(self, torch, engine, dist=None, steps_per_call=1, registered_gradient=False, exchange="allreduce"):
         self.torch, self.engine, self.dist = torch, engine, dist
         self.steps_per_call = steps_per_call
         self.rank = dist.get_rank() if dist is not None else 0
@@ -89,6 +99,10 @@ class DataParallelTrainer:
         self._steps_seen = 0
         self.sync_calls = 0
         self.buffers = None
+        if exchange not in ("allreduce", "sharded"):
+            raise ValueError("unknown exchange %r" % (exchange,))
+        self.exchange = exchange
+        self._bytes = {"gradient_out_per_step": 0, "parameters_out_per_step": 0}
         if self.world > 1:
             if registered_gradient and hasattr(engine, "set_grad_buffer"):
                 # the gradient arena moves into memory registered with the communicator
@@ -96,8 +110,21 @@ class DataParallelTrainer:
                 count = (engine.arena().total + 3) // 4 * 4
                 engine.set_grad_buffer(self.buffers.zeros(count, torch.float32))
                 self.buffers.register()
-            engine.set_grad_sync(self._allreduce)
-            # the same number of optimizer steps, hence allreduces, per call on every rank, whatever the local sample
+            a = engine.arena()
+            self._hash, self._total = int(a.sparse_count), int(a.total)
+            if exchange == "sharded":
+                if self._hash % (4 * self.world) != 0:
+                    raise ValueError("the hash table (%d elements) does not split into %d aligned slices" % (self._hash, self.world))
+                self._shard = self._hash // self.world
+                engine.set_optimizer_shard(self.rank, self.world, self._allgather_params)
+                engine.set_grad_sync(self._reduce_scatter)
+                wire = (self.world - 1) / self.world
+                self._bytes = {"gradient_out_per_step": int(self._hash * 4 * wire + (self._total - self._hash) * 4 * 2 * wire),
+                               "parameters_out_per_step": int(self._hash * 2 * wire)}
+            else:
+                engine.set_grad_sync(self._allreduce)
+                self._bytes = {"gradient_out_per_step": int(self._total * 4 * 2 * (self.world - 1) / self.world), "parameters_out_per_step": 0}
+            # the same number of optimizer steps, hence exchanges, per call on every rank, whatever the local sample
             # counts are (steps_per_call > 1 lets one occupancy walk of a large ray shard serve several steps)
             engine.set_steps_per_call(steps_per_call)
         # with equal shards (num_rays a multiple of world) local_rays * world is exactly the global ray count
@@ -106,6 +133,35 @@ class DataParallelTrainer:
     def _allreduce(self, grad):
         self.sync_calls += 1
         self.dist.all_reduce(grad, op=self.dist.ReduceOp.SUM)
+
+    def _reduce_scatter(self, grad):
+        self.sync_calls += 1
+        lo = self.rank * self._shard
+        self.dist.reduce_scatter_tensor(grad[lo:lo + self._shard], grad[:self._hash], op=self.dist.ReduceOp.SUM)   # in place
+        self.dist.all_reduce(grad[self._hash:self._total], op=self.dist.ReduceOp.SUM)
+
+    def _allgather_params(self, w_h):
+        lo = self.rank * self._shard
+        self.dist.all_gather_into_tensor(w_h[:self._hash], w_h[lo:lo + self._shard])                                # in place
+
+    def gather_master(self):
+        """After sharded steps: every rank receives the fp32 master copy of every table slice (call before saving)."""
+        if self.world > 1 and self.exchange == "sharded":
+            w = self.engine.arena_tensor("w")
+            lo = self.rank * self._shard
+            self.dist.all_gather_into_tensor(w[:self._hash], w[lo:lo + self._shard])
+
+    def exchange_stats(self):
+        """Bytes this rank sends per optimizer step (ring accounting: (N - 1) / N of a buffer per reduce-scatter or
+        all-gather, twice that per all-reduce)."""
+        return dict(self._bytes, mode=self.exchange, ranks=self.world)
+
+    def close(self):
+        """Detaches the callbacks from the engine (they hold references to this object)."""
+        if self.world > 1:
+            if self.exchange == "sharded" and hasattr(self.engine, "set_optimizer_shard"):
+                self.engine.set_optimizer_shard(0, 1, None)
+            self.engine.set_grad_sync(None)
 
     def train_rays(self, rays_o, rays_d, rgb_true):
         """steps_per_call optimizer steps on the global batch (which must split evenly over the ranks); returns the
@@ -121,9 +177,10 @@ class DataParallelTrainer:
         return self.engine.rays_consumed() if self.world > 1 else count
 
     def replicas_in_sync(self):
-        """True when every rank holds bit-identical parameters: compares the 64-bit sum of the raw parameter bits."""
-        w = self.engine.arena_tensor("w")
-        s = w.view(self.torch.int32).to(self.torch.int64).sum().reshape(1)
+        """True when every rank holds bit-identical parameters: compares the 64-bit sum of the raw bits of the fp16 copy
+        the forward reads (with the sharded optimizer the fp32 master copy of a slice is current on its owner only)."""
+        w = self.engine.arena_tensor("w_h" if self.exchange == "sharded" else "w")
+        s = w.view(self.torch.int16 if self.exchange == "sharded" else self.torch.int32).to(self.torch.int64).sum().reshape(1)
         if self.world == 1:
             return True
         t = self.torch.stack([s[0], -s[0]])

@@ -476,14 +476,31 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
     }
 }
 
+void InstantNerf::setOptimizerShard(uint32_t rank, uint32_t world, ParamSync sync) {
+    if (world <= 1) { m_shardRank = 0; m_shardWorld = 1; m_paramSync = ParamSync(); return; }
+    if (rank >= world) throw std::runtime_error("setOptimizerShard: rank must be below the number of ranks");
+    if (m_arena.sparse_count % (4 * (int64_t)world) != 0) throw std::runtime_error("setOptimizerShard: the hash table does not split into 16-byte aligned slices");
+    m_shardRank = rank; m_shardWorld = world; m_paramSync = std::move(sync);
+}
+
 void InstantNerf::optimizerStep(cudaStream_t stream) {
     timed(stream, m_times.optimizer, [&]() {
         if (m_optSteps < 50000) m_optSteps++;
         float bc1 = 1.0f - std::pow(m_opts.beta1, (float)m_optSteps);
         float bc2 = 1.0f - std::pow(m_opts.beta2, (float)m_optSteps);
-        throw_on_error(nb_adam_step(m_arena.W(0), m_arena.Wh(0), m_arena.G(0), m_arena.M(0), m_arena.V(0), m_arena.sparse_count, m_arena.total,
-                                    m_opts.learningRate, m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),
-                       "optimizer");
+        auto adam = [&](int64_t off, int64_t sparse, int64_t count, const char* what) {
+            throw_on_error(nb_adam_step(m_arena.W(off), m_arena.Wh(off), m_arena.G(off), m_arena.M(off), m_arena.V(off), sparse, count,
+                                        m_opts.learningRate, m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),
+                           what);
+        };
+        if (m_shardWorld <= 1) { adam(0, m_arena.sparse_count, m_arena.total, "optimizer"); return; }
+        const int64_t H = m_arena.sparse_count, shard = H / m_shardWorld, lo = (int64_t)m_shardRank * shard, hi = lo + shard;
+        adam(lo, shard, shard, "optimizer (table slice)");
+        adam(H, 0, m_arena.total - H, "optimizer (networks)");
+        // the other slices still hold this rank's own unreduced gradient
+        if (lo > 0) throw_on_error(nb_zero_async(m_arena.G(0), lo * (int64_t)sizeof(float), stream), "optimizer: clear");
+        if (hi < H) throw_on_error(nb_zero_async(m_arena.G(hi), (H - hi) * (int64_t)sizeof(float), stream), "optimizer: clear");
+        if (m_paramSync) m_paramSync(m_arena.Wh(0), H, stream);
     });
 }
 

@@ -108,6 +108,14 @@ public:
     // Called on the gradient arena between backward and the optimizer of every step (data-parallel all-reduce).
     using GradSync = std::function<void(float* d_grads, int64_t count, cudaStream_t stream)>;
     void setGradSync(GradSync fn) { m_gradSync = std::move(fn); }
+    // Data parallelism with the hash table's optimizer state used shard-wise: of the table's `sparse_count` elements this
+    // rank updates slice [rank, rank + 1) * sparse_count / world only (the gradient-sync callback is expected to leave
+    // the SUMMED gradient of that slice there, e.g. by a reduce-scatter in place), every rank updates the small dense tail
+    // (network weights), the rest of the table gradient is cleared, and `sync` then runs on the fp16 parameter copy - an
+    // all-gather of the slices, so that every rank's forward reads identical parameters.  The fp32 master copy, m and v of a
+    // slice are current on its owner only.  world <= 1 restores the whole-arena update.
+    using ParamSync = std::function<void(half* d_params_h, int64_t sparse_count, cudaStream_t stream)>;
+    void setOptimizerShard(uint32_t rank, uint32_t world, ParamSync sync);
     // Loss gradients are normalised by numRays * scale (the global ray count when ranks split a batch).
     void setGlobalRayScale(uint32_t scale) { m_rayScale = scale ? scale : 1u; }
     // One kernel each way for the whole field (encode + both networks) instead of the reference's kernel sequence;
@@ -169,6 +177,8 @@ private:
     TinyMLP* m_colorMLP = nullptr;
     TinyMLPHashGrid* m_densityMLP = nullptr;
     GradSync m_gradSync;
+    ParamSync m_paramSync;
+    uint32_t m_shardRank = 0, m_shardWorld = 1;
     uint32_t m_rayScale = 1;
     bool m_fused = false;
     bool m_renderRounds = false;

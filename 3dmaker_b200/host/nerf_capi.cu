@@ -103,6 +103,12 @@ extern "C" int nb_nerf_set_steps_per_call(nb_nerf* h, int steps) {
     return NB_OK;
 }
 
+extern "C" int nb_nerf_set_optimizer_shard(nb_nerf* h, uint32_t rank, uint32_t world, nb_param_sync_fn fn, void* user) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    if (world > 1 && !fn) return nb_set_error(NB_ERR_INVALID, "nb_nerf_set_optimizer_shard: a parameter-sync callback is required");
+    NB_GUARD(h->impl.setOptimizerShard(rank, world, [fn, user](half* p, int64_t count, cudaStream_t st) { fn(user, p, count, st); }))
+}
+
 extern "C" int nb_nerf_set_hit_counts_capacity(nb_nerf* h, uint32_t capacity) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     h->impl.setHitCountsCapacity(capacity);

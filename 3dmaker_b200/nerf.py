@@ -119,6 +119,21 @@ class InstantNerf:
         self._cb = nb.GRAD_SYNC_FN(trampoline)
         nb.check(self.lib.nb_nerf_set_grad_sync(self.h, self._cb, None))
 
+    def set_optimizer_shard(self, rank, world, fn):
+        """Sharded optimizer (see nb_nerf_set_optimizer_shard): this rank updates slice `rank` of `world` of the hash table;
+        fn(w_h) runs after every update with a float16 view of the whole parameter arena and all-gathers the table slices.
+        world <= 1 switches back."""
+        if world <= 1 or fn is None:
+            self._param_cb = None
+            nb.check(self.lib.nb_nerf_set_optimizer_shard(self.h, 0, 1, nb.PARAM_SYNC_FN(0), None), "nb_nerf_set_optimizer_shard")
+            return
+        w_h = self.arena_tensor("w_h")
+
+        def trampoline(user, ptr, count, stream):
+            fn(w_h)
+        self._param_cb = nb.PARAM_SYNC_FN(trampoline)
+        nb.check(self.lib.nb_nerf_set_optimizer_shard(self.h, rank, world, self._param_cb, None), "nb_nerf_set_optimizer_shard")
+
     def set_grad_buffer(self, tensor):
         """Moves the gradient arena into `tensor` (float32, CUDA, at least arena().total elements; the engine zeroes it and
         this object keeps it alive) - e.g. memory registered with the communicator so that the all-reduce of

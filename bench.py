@@ -31,6 +31,12 @@ COLOR = (32, 64, 8, 3)
 HYPER = dict(lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0)
 METRIC = "train samples/s (encode+MLP fwd/bwd+Adam)"
 WORKLOAD = "cfg2+encode+Adam: 2^20 samples/GPU, L16 F2 T2^19 b1.447, density 32-64-16, colour 32-64-64-3, MSE, Adam"
+L2_NOTE = "inputs and activations of one step (>1 GB) exceed the 126 MB L2; two input batches alternate"
+
+
+def common_config(world):
+    """The `config` object of the line: identical in both arms (what ran it goes under `notes`)."""
+    return {"workload": WORKLOAD, "per_gpu_batch": BATCH, "l2": L2_NOTE, "parallelism": "dp%d" % world}
 
 
 def load_peaks():
@@ -208,33 +214,74 @@ def run_reference_cuda(args, rank, world, local_rank):
     torch.cuda.synchronize()
     clocks = sampler.stop(mark0, sampler.mark())
     ms = e0.elapsed_time(e1) / args.steps
-    own = tuple(torch.empty_like(t) for t in dev[0])
+    # e2e, harnessed exactly like ours: the copy of batch k + 1 runs on a copy stream into the input set the running step
+    # does not use, and the 4 bytes read back per step (one colour value: the reference's step leaves no loss scalar on
+    # the device) travel to pinned memory asynchronously and are read by the host one step late
+    slots = [tuple(torch.empty_like(t) for t in dev[0]) for _ in range(2)]
+    copy_stream = torch.cuda.Stream()
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    free = [torch.cuda.Event(), torch.cuda.Event()]
     probe = nm_view(torch, lib.ref_field_color_out(rf), 1)
+    probe_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    probe_done = [torch.cuda.Event(), torch.cuda.Event()]
+    cur = torch.cuda.current_stream()
+
+    def prefetch(k, src):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(free[k])
+            for dst, a in zip(slots[k], src):
+                dst.copy_(a, non_blocking=True)
+            ready[k].record(copy_stream)
+
+    def e2e_loop(count):
+        """`count` steps; slot 0 holds the first batch already (primed outside the timed region, as in the other arm),
+        every step copies the next batch in and reads the value of the step before."""
+        reads = 0
+        for i in range(count):
+            k = i % 2
+            prefetch(1 - k, host[(i + 1) % 2])
+            cur.wait_event(ready[k])
+            step(slots[k])
+            free[k].record(cur)
+            probe_host[k].copy_(probe, non_blocking=True)
+            probe_done[k].record(cur)
+            if i > 0:
+                probe_done[1 - k].synchronize(); float(probe_host[1 - k].item()); reads += 1
+        probe_done[(count - 1) % 2].synchronize(); float(probe_host[(count - 1) % 2].item()); reads += 1
+        return reads
+
+    prefetch(0, host[0])
+    e2e_loop(2)
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        for dst, src in zip(own, host[i % 2]):
-            dst.copy_(src, non_blocking=True)
-        step(own)
-        probe.cpu()
+    reads = e2e_loop(args.steps)
     e1.record()
     torch.cuda.synchronize()
+    assert reads == args.steps
     e2e_ms = e0.elapsed_time(e1) / args.steps
     h2d = sum(a.numel() * a.element_size() for a in host[0])
     value = world * BATCH / (ms / 1000.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH,
-                   "reference": "reference CUDA classes/kernels recompiled for sm_100a (oracle/_ref); single-GPU code, value = %d ideal replicas" % world},
+        "config": common_config(world),
+        "notes": {"reference": "reference CUDA classes/kernels recompiled for sm_100a (oracle/_ref); single-GPU code, value = %d ideal replicas" % world,
+                  "e2e": "copy stream + loss read one step late, the same harness as the other arm"},
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 0, "kind": "reference",
                          "sample": "full 2^20-sample step on the GPU: the reference has no CPU implementation of this path"},
         "e2e": {"value": world * BATCH / (e2e_ms / 1000.0), "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4},
         "gpu_launches": 0, "clocks": clocks,
     }
-    print(json.dumps(line))
     lib.ref_field_destroy(rf)
+    del dev, slots
+    torch.cuda.empty_cache()
+    if not args.no_extras:
+        # the reference is single-GPU: its render and config-5 numbers are one GPU's, whatever --gpus says
+        line.update(run_extras(args, 0, 1, local_rank))
+    print(json.dumps(line))
+    return
 
 
 def nm_view(torch, ptr, count):
@@ -267,7 +314,7 @@ def run_reference(args, rank, world=1, local_rank=0):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "sample_per_step": sample},
+        "data": "synthetic", "config": common_config(args.gpus), "notes": {"sample_per_step": sample},
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port",
                          "sample": "%d samples per step of the 2^20-sample workload, full T=2^19 table and Adam over it" % sample},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -483,9 +530,9 @@ def run_ours(args, rank, world, local_rank):
         line = {
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "l2": "inputs and activations of one step (>1 GB) exceed the 126 MB L2; two input batches alternate",
-                       "parallelism": "dp%d" % world if world == 1 else "dp%d/%s" % (world, args.dp), "field_kernels": ("fused+scatter" if tr.fused_scatter else "fused") if tr.fused else "sequence",
-                       "tuning": args.tune},
+            "config": common_config(world),
+            "notes": {"exchange": None if world == 1 else args.dp, "field_kernels": ("fused+scatter" if tr.fused_scatter else "fused") if tr.fused else "sequence",
+                      "tuning": args.tune},
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "last_loss": loss},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernel_ms": kt,
@@ -495,6 +542,16 @@ def run_ours(args, rank, world, local_rank):
             v, dt = cpu_baseline(sample)
             line["cpu_baseline"] = {"value": v, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": "one step on %d samples (%.1f s) of the 2^20-sample workload, full T=2^19 table" % (sample, dt)}
+    # ---- the rest of the metric (render Mrays/s) and config 5, on the same ranks ----------------------------------
+    del tr, model, dev, own
+    if buffers is not None:
+        del buffers
+    torch.cuda.empty_cache()
+    if not args.no_extras:
+        extras = run_extras(args, rank, world, local_rank)
+        if rank == 0:
+            line.update(extras)
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -515,10 +572,13 @@ RENDER_WORKLOAD = "cfg4: 1920x1080 orbit frames of the cfg3 model after %d train
 
 
 # config 5: 32 seeded soft spheres in a box of scale 4, 3 cascades of 128^3, T = 2^22 per level, 300 cameras 1280x720,
-# 2^21 samples per step over all ranks (2^18 per rank at 8 GPUs; the per-rank batch stays 2^18 at every N: weak scaling)
+# 2^21 samples per optimizer step over ALL ranks, split evenly (strong scaling): a rank's sample batch is 2^21 / N and
+# it gets 524288 / N rays per call, about six optimizer steps' worth
+SCENE5_GLOBAL_BATCH = 1 << 21
+SCENE5_GLOBAL_RAYS = 1 << 19
 SCENE5_OPTS = dict(SCENE_OPTS, hash_table_size=1 << 22, num_cascades=3)
 SCENE5_WORKLOAD = ("cfg5: 32 soft spheres in a scale-4 box, 300 cameras 1280x720, 128^3 occupancy x3 cascades, L16 F2 T2^22, "
-                   "batch 2^18 samples per GPU, ray chunk 65536, distortion loss, Adam")
+                   "2^21 samples per optimizer step over all GPUs (2^21/N per GPU), 2^19 rays per call over all GPUs, distortion loss, Adam")
 
 
 class _RefEngine:
@@ -568,36 +628,44 @@ def _scene_batches(torch, syn, count, rays, seed0, config=3):
     return out
 
 
-def run_scene(args, rank, world, local_rank):
+def run_scene(args, rank, world, local_rank, embedded=False):
     """Full training step (march + field + compositing + loss + backward + scatter + Adam) on the analytic scene.
-    --gpus N: the global ray batch is N x 65536 rays, data-parallel with one gradient allreduce per step."""
+    scene (config 3): every rank trains 65536 rays per call, one gradient allreduce per optimizer step (weak scaling).
+    scene5 (config 5): 2^21 samples per optimizer step and 2^19 rays per call over ALL ranks (strong scaling).
+    embedded: called from the default run - the process group exists already, the line is returned, not printed."""
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
     reference = args.impl == "reference"
     if reference and rank != 0:
-        return
-    if world > 1 and not reference:
+        return None
+    if world > 1 and not reference and not embedded:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     nb = importlib.import_module("3dmaker_b200")
     nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
     D = importlib.import_module("3dmaker_b200.distributed")
     cfg5 = args.workload == "scene5"
-    opts = nm.default_options(**(SCENE5_OPTS if cfg5 else SCENE_OPTS))
-    rays = 1 << 16
+    nranks = 1 if reference else world
+    if cfg5:
+        rays = SCENE5_GLOBAL_RAYS // nranks
+        opts = nm.default_options(**dict(SCENE5_OPTS, batch_size=SCENE5_GLOBAL_BATCH // nranks, ray_chunk_size=rays))
+    else:
+        rays = 1 << 16
+        opts = nm.default_options(**SCENE_OPTS)
     if reference:
         from oracle import ref_cuda as ref
         if not ref.available():
-            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref3dmaker.so not built (no reference tree at build time)"}))
-            return
-        eng, trainer, nranks = _RefEngine(torch, opts), None, 1
+            line = {"impl": "reference", "unavailable": "oracle/_ref/libref3dmaker.so not built (no reference tree at build time)"}
+            if not embedded:
+                print(json.dumps(line))
+            return line
+        eng, trainer = _RefEngine(torch, opts), None
     else:
         eng = nm.InstantNerf(torch, opts)
-        # data parallel: every rank gets 65536 rays per call and takes DP_STEPS optimizer steps on them (one occupancy
-        # walk per call); the sphere scene yields about 7 steps' worth of samples per 65536 rays
-        trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None, steps_per_call=6, registered_gradient=not args.plain_buffers)
-        nranks = world
-    batches = _scene_batches(torch, syn, 8, rays * nranks, 9000, config=5 if cfg5 else 3)
+        # data parallel: every rank takes DP_STEPS optimizer steps on its rays of a call (one occupancy walk per call)
+        trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None, steps_per_call=6, registered_gradient=not args.plain_buffers,
+                                        exchange=args.exchange)
+    batches = _scene_batches(torch, syn, 4 if cfg5 else 8, rays * nranks, 9000, config=5 if cfg5 else 3)
 
     used = [0]
 
@@ -632,27 +700,36 @@ def run_scene(args, rank, world, local_rank):
         t = torch.cat([tm, ts])
     ms, total, rays_used = float(t[0].item()), float(t[1].item()), float(t[2].item())
     opt_steps = (eng.steps if reference else eng.steps.value) - steps_before
+    line = None
+    in_sync = None
+    if trainer is not None and world > 1:
+        in_sync = bool(trainer.replicas_in_sync())
     if rank == 0:
         line = {"metric": "train samples/s (full NeRF step)", "value": total / (ms / 1000.0), "unit": "samples/s", "n_gpus": nranks,
-                "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": SCENE5_WORKLOAD if cfg5 else SCENE_WORKLOAD, "rays_per_step_per_gpu": rays, "optimizer_steps": opt_steps,
+                "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "strong" if cfg5 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": SCENE5_WORKLOAD if cfg5 else SCENE_WORKLOAD, "rays_per_call_per_gpu": rays, "optimizer_steps": opt_steps,
                            "samples_per_call": total / args.steps, "rays_per_s": rays_used / (ms / 1000.0),
+                           "samples_per_optimizer_step": total / max(opt_steps, 1),
                            "ms_per_optimizer_step": ms / max(opt_steps, 1)}}
         if reference:
             line["impl"] = "reference"
         elif trainer is not None:
-            line["config"]["replicas_in_sync"] = None
-        print(json.dumps(line))
-    if trainer is not None and world > 1:
-        ok = trainer.replicas_in_sync()
-        if rank == 0:
-            print(json.dumps({"replicas_in_sync": bool(ok)}))
+            line["config"]["replicas_in_sync"] = in_sync
+            line["config"]["exchange"] = trainer.exchange if world > 1 else None
+            if world > 1:
+                line["config"]["exchange_stats"] = trainer.exchange_stats()
+        if not embedded:
+            print(json.dumps(line))
+    if trainer is not None and world > 1 and not embedded:
         dist.barrier(); dist.destroy_process_group()
+    if trainer is not None:
+        trainer.close()
     eng.close()
+    return line
 
 
-def run_render(args, rank, world, local_rank):
+def run_render(args, rank, world, local_rank, embedded=False):
     """Frames of the trained scene along an orbit, pixels sharded over the ranks, one gather per frame."""
     import ctypes
     import torch
@@ -660,8 +737,8 @@ def run_render(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     reference = args.impl == "reference"
     if reference and rank != 0:
-        return
-    if world > 1 and not reference:
+        return None
+    if world > 1 and not reference and not embedded:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     nb = importlib.import_module("3dmaker_b200")
     nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
@@ -672,8 +749,10 @@ def run_render(args, rank, world, local_rank):
     if reference:
         from oracle import ref_cuda as ref
         if not ref.available():
-            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref3dmaker.so not built (no reference tree at build time)"}))
-            return
+            line = {"impl": "reference", "unavailable": "oracle/_ref/libref3dmaker.so not built (no reference tree at build time)"}
+            if not embedded:
+                print(json.dumps(line))
+            return line
         eng = _RefEngine(torch, opts)
     else:
         eng = nm.InstantNerf(torch, opts)
@@ -715,6 +794,7 @@ def run_render(args, rank, world, local_rank):
         pose["c2w"] = syn.orbit_c2w(3.0 * k, 20.0, 1.5)
         return r.render_frame(W * H, "cuda")
 
+    frames = args.render_frames if embedded else args.steps
     for k in range(max(args.warmup, 3)):
         img = frame(k)
     torch.cuda.synchronize()
@@ -722,35 +802,71 @@ def run_render(args, rank, world, local_rank):
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for k in range(args.steps):
+    for k in range(frames):
         img = frame(10 + k)
     e1.record()
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
     if nranks > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
+    ms = float(t.item()) / frames
+    line = None
     if rank == 0:
         frame_samples = None if reference else eng.last_render_samples() * nranks   # this rank's share of the last frame, scaled
+        frame_mean = float(img.mean().item())
         scene = syn.SoftSphereScene()
         o, d = syn.frame_rays(torch, pose["c2w"], W // 4, H // 4, 50.0)
         gt = syn.ground_truth(torch, scene, o, d, (1.0, 1.0, 1.0))
         small = torch.zeros_like(gt)
         eng.render(o, d, small)
         torch.cuda.synchronize()
-        line = {"metric": "render Mrays/s", "value": W * H / (ms / 1000.0) / 1e6, "unit": "Mrays/s", "n_gpus": nranks, "steps": args.steps,
+        line = {"metric": "render Mrays/s", "value": W * H / (ms / 1000.0) / 1e6, "unit": "Mrays/s", "n_gpus": nranks, "steps": frames,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": RENDER_WORKLOAD % train_steps, "frame": [W, H], "tile_pixels": 1 << 14,
                            "gather_bytes_per_frame": D.gathered_bytes(W * H, nranks, 1 << 14),
-                           "psnr_quarter_res_db": float(syn.psnr(torch, small, gt)), "frame_mean": float(img.mean().item()),
+                           "psnr_quarter_res_db": float(syn.psnr(torch, small, gt)), "frame_mean": frame_mean,
                            "field_samples_per_frame": frame_samples}}
         if reference:
             line["impl"] = "reference"
-        print(json.dumps(line))
-    if nranks > 1:
+        if not embedded:
+            print(json.dumps(line))
+    if nranks > 1 and not embedded:
         dist.barrier(); dist.destroy_process_group()
     eng.close()
+    return line
+
+
+def run_extras(args, rank, world, local_rank):
+    """The other half of the metric and the multi-GPU configuration, measured in the same process (and process group)
+    as the headline line: `render` = 1920x1080 orbit frames of the config-3 model, pixels sharded over the ranks
+    (config 4, Mrays/s); `scene5` = the full training step of config 5 (T = 2^22, 3 cascades, 2^21 samples per
+    optimizer step split over the ranks: strong scaling).  Returns {"render": {...}, "scene5": {...}} on rank 0."""
+    import copy
+    import torch
+    out = {}
+    for key, workload, fn in (("render", "render", run_render), ("scene5", "scene5", run_scene)):
+        a = copy.copy(args)
+        a.workload = workload
+        a.warmup, a.steps, a.scene_warm = 3, args.extra_steps, args.extra_scene_warm
+        try:
+            line = fn(a, rank, world, local_rank, embedded=True)
+        except Exception as e:            # an extra must never cost the headline line
+            if world > 1:
+                raise                     # ... but ranks of a collective job have to fail together
+            line = {"error": "%s: %s" % (type(e).__name__, e)}
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        if rank == 0 and line is not None:
+            if "metric" in line:
+                out[key] = {"value": line["value"], "unit": line["unit"], "metric": line["metric"], "n_gpus": line["n_gpus"],
+                            "ms_per_step": line["ms_per_step"], "scaling": line["scaling"], "steps": line["steps"], "warmup": line["warmup"],
+                            "workload": line["config"]["workload"], "detail": {k: v for k, v in line["config"].items() if k != "workload"}}
+                if key == "render":
+                    out[key]["ms_per_frame"] = line["ms_per_step"]
+            else:
+                out[key] = line
+    return out
 
 
 def main():
@@ -767,6 +883,14 @@ def main():
     ap.add_argument("--scene-warm", type=int, default=272, help="scene workload: untimed train_rays calls before the timed ones")
     ap.add_argument("--render-train-steps", type=int, default=400, help="render workload: optimizer steps the model is trained for first")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="field workload: leave the `render` and `scene5` keys out of the line")
+    ap.add_argument("--extra-steps", type=int, default=10, help="timed train_rays calls of the embedded scene5 measurement")
+    ap.add_argument("--extra-scene-warm", type=int, default=48, help="untimed train_rays calls of the embedded scene5 measurement "
+                    "(six optimizer steps each: past the 256 steps of whole-grid occupancy updates)")
+    ap.add_argument("--render-frames", type=int, default=12, help="timed frames of the embedded render measurement")
+    ap.add_argument("--exchange", default="sharded", choices=["allreduce", "sharded"],
+                    help="scene workloads at N > 1: all-reduce + replicated Adam, or reduce-scatter + Adam on a table slice + all-gather of fp16 "
+                         "parameters inside the engine")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
     ap.add_argument("--dp", default="sharded", choices=["sharded", "allreduce", "sliced"],

@@ -473,6 +473,14 @@ int nb_nerf_set_memory_mode(nb_nerf* h, int memory_mode);
  * num_rays * scale, and fn runs on the gradient arena between backward and the optimizer of every step. */
 int nb_nerf_set_global_ray_scale(nb_nerf* h, uint32_t scale);
 int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user);
+/* Sharded optimizer for data parallelism (no counterpart in the reference): this rank applies Adam to slice
+ * [rank, rank + 1) * sparse_count / world of the hash table only - nb_grad_sync_fn is expected to leave the summed
+ * gradient of that slice in place (reduce-scatter) and the summed gradient of the dense tail (network weights) - clears
+ * the rest of the table gradient and then calls fn on the fp16 parameter copy, where the caller all-gathers the slices.
+ * Adam's launch and the bytes on the wire shrink; the fp32 master copy and the moments of a slice are current on its
+ * owner only.  world <= 1 switches back.  sparse_count must be a multiple of 4 x world. */
+typedef void (*nb_param_sync_fn)(void* user, void* d_params_h, int64_t sparse_count, void* stream);
+int nb_nerf_set_optimizer_shard(nb_nerf* h, uint32_t rank, uint32_t world, nb_param_sync_fn fn, void* user);
 /* on != 0: nb_nerf_train_rays runs exactly one optimizer step (one fn call) per call; rays that do not fit the sample
  * batch are left untrained (nb_nerf_step_view.rays_consumed says how many were used) instead of starting a second
  * step, so that every rank of a data-parallel job issues the same number of gradient exchanges. */

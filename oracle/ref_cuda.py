@@ -22,6 +22,11 @@ _SIG = {
     "ref_field_forward": (None, [V, V, V, I, F, V]),
     "ref_field_forward_backward": (None, [V, V, V, V, I, F, F, V]),
     "ref_field_train_step": (None, [V, V, V, V, I, F, F, F, F, F, F, V]),
+    "ref_field_grid_activation": (V, [V, I]),
+    "ref_field_step": (None, [V, F, F, F, F, F, V]),
+    "ref_nerf_save": (I, [V, ctypes.c_char_p]),
+    "ref_nerf_load": (I, [V, ctypes.c_char_p]),
+    "ref_volume_rendering_priors": (None, [U, V, V, V, V, V, V, V, V, V, V, V, V, V, F, F, V, V]),
     "ref_nerf_create": (V, [V, I]),
     "ref_nerf_options_size": (I, []),
     "ref_nerf_destroy": (None, [V]),

@@ -94,6 +94,13 @@ float* ref_field_layer_grads(void* h, int net, int layer, int what) {
     cudaMemcpy(&p, arr + layer, sizeof(float*), cudaMemcpyDeviceToHost);
     return p;
 }
+// Saved activation `index` of the grid network after a forward: 0 = the encoded features [n][32] fp16
+// (networkFusionHashtable.cu:553-569), 1.. = hidden layers.
+void* ref_field_grid_activation(void* h, int index) {
+    half* p = nullptr;
+    cudaMemcpy(&p, ((RefField*)h)->density->d_activations + index, sizeof(half*), cudaMemcpyDeviceToHost);
+    return p;
+}
 float* ref_field_density_out(void* h) { return ((RefField*)h)->d_density_out; }
 float* ref_field_color_out(void* h) { return ((RefField*)h)->d_color_out; }
 void* ref_field_color_in(void* h) { return ((RefField*)h)->d_color_in; }
@@ -120,6 +127,14 @@ void ref_field_train_step(void* h, const float* d_pos4, const float* d_dirs3, co
     f->color->backward(f->d_color_dx, n, stream);
     compute_density_grad<<<(n + 255) / 256, 256, 0, stream>>>(n, f->d_zero_dsigma, f->d_color_dx, f->d_density_grad);
     f->density->backward(f->d_density_grad, n, stream);
+    f->color->step(lr, beta1, beta2, eps, lossScale, stream);
+    f->density->step(lr, beta1, beta2, eps, lossScale, stream);
+}
+
+// The optimizer alone, on whatever the gradient buffers hold (tests write a known gradient there first):
+// TinyMLP::step and TinyMLPHashGrid::step (TinyMLP.cu:379-404, TinyMLPHashGrid.cu:379-392).
+void ref_field_step(void* h, float lossScale, float lr, float beta1, float beta2, float eps, cudaStream_t stream) {
+    RefField* f = (RefField*)h;
     f->color->step(lr, beta1, beta2, eps, lossScale, stream);
     f->density->step(lr, beta1, beta2, eps, lossScale, stream);
 }
@@ -185,6 +200,15 @@ int ref_nerf_train(void* h, const float* d_rays_o, const float* d_rays_d, const 
 void ref_nerf_render(void* h, const float* d_rays_o, const float* d_rays_d, unsigned numRays, float* d_rgb_out, cudaStream_t stream) {
     ((InstantNerf*)h)->renderImageHit((const float3*)d_rays_o, (const float3*)d_rays_d, numRays, d_rgb_out, stream);
 }
+// InstantNerf::save / load, the .inerf file (InstantNerf.cu:1206-1352).  0 on success, 1 when the reference threw.
+int ref_nerf_save(void* h, const char* path) {
+    try { ((InstantNerf*)h)->save(path); } catch (const std::exception& e) { std::fprintf(stderr, "ref_nerf_save: %s\n", e.what()); return 1; }
+    return 0;
+}
+int ref_nerf_load(void* h, const char* path) {
+    try { ((InstantNerf*)h)->load(path); } catch (const std::exception& e) { std::fprintf(stderr, "ref_nerf_load: %s\n", e.what()); return 1; }
+    return 0;
+}
 void ref_nerf_set_memory_mode(void* h, int mode) { ((InstantNerf*)h)->setMemoryMode(mode == 1 ? INFERENCE : TRAINING); }
 
 // scratch buffers of the last step, by name index (parity tests)
@@ -238,6 +262,15 @@ void ref_volume_rendering(unsigned numRays, const unsigned* offsets, const unsig
                           float lambdaDepth, const float* bg3, unsigned base, unsigned raysDone, cudaStream_t stream) {
     launchVolumeRendering(numRays, offsets, steps, t, sigma, nullptr, nullptr, rgb3, rgbTrue, outRgb, outDepth, phi, dw, wsum, lambdaDist, lambdaDepth,
                           make_float3(bg3[0], bg3[1], bg3[2]), base, raysDone, stream);
+}
+
+// The same launcher with per-ray depth priors (depth < 0 = no prior for that ray), compositing.cu:108-111,157-159,183-189.
+void ref_volume_rendering_priors(unsigned numRays, const unsigned* offsets, const unsigned* steps, const float* t, const float* sigma,
+                                 const float* depthPrior, const float* sigmaPrior, const float* rgb3, const float* rgbTrue, float* outRgb,
+                                 float* outDepth, float* phi, float* dw, float* wsum, float lambdaDist, float lambdaDepth, const float* bg3,
+                                 cudaStream_t stream) {
+    launchVolumeRendering(numRays, offsets, steps, t, sigma, depthPrior, sigmaPrior, rgb3, rgbTrue, outRgb, outDepth, phi, dw, wsum, lambdaDist,
+                          lambdaDepth, make_float3(bg3[0], bg3[1], bg3[2]), 0, 0, stream);
 }
 
 void ref_color_grad(unsigned numRays, const unsigned* steps, const unsigned* offsets, const float* t, const float* densityOut16, const float* colorOut3,

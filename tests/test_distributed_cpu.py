@@ -19,10 +19,22 @@ class FakeEngine:
     by (local rays x global scale) the way the scene engine normalises by the global ray count, summed over rays,
     handed to the sync hook, then applied with plain SGD.  max_rays mimics the sample batch that bounds one step."""
 
+    SPARSE = 16     # the first 16 of the 18 parameters play the hash table (updated shard-wise by the sharded optimizer)
+
     def __init__(self, max_rays=1 << 30):
         self.w = torch.linspace(-0.5, 0.5, 18, dtype=torch.float32)
+        self.w_h = self.w.half()          # the copy the "forward" reads, as in the real engine
         self.g = torch.zeros(18, dtype=torch.float32)
         self.scale, self.sync, self.single, self.steps, self.max_rays, self.consumed = 1, None, 0, 0, max_rays, 0
+        self.shard, self.param_sync = None, None
+
+    def arena(self):
+        class View:
+            sparse_count, total = FakeEngine.SPARSE, 18
+        return View()
+
+    def set_optimizer_shard(self, rank, world, fn):
+        self.shard, self.param_sync = ((rank, world), fn) if world > 1 and fn is not None else (None, None)
 
     def set_global_ray_scale(self, s):
         self.scale = s
@@ -37,18 +49,27 @@ class FakeEngine:
         return self.consumed
 
     def arena_tensor(self, name):
-        return {"w": self.w, "g": self.g}[name]
+        return {"w": self.w, "g": self.g, "w_h": self.w_h}[name]
 
     def train_rays(self, o, d, rgb):
         n, done, taken = o.shape[0], 0, 0
         while (taken < self.single) if self.single else (done < n):
             k = min(self.max_rays, n - done)
             x = torch.cat([o[done:done + k], d[done:done + k]], dim=1)
-            err = x @ self.w.view(3, 6).t() - rgb[done:done + k]
+            err = x @ self.w_h.float().view(3, 6).t() - rgb[done:done + k]
             self.g += (2.0 * err.t() @ x / (n * self.scale)).reshape(-1)
             if self.sync is not None:
                 self.sync(self.g)
-            self.w -= 0.1 * self.g
+            if self.shard is None:
+                self.w -= 0.1 * self.g
+                self.w_h.copy_(self.w.half())
+            else:                          # this rank's slice of the table and the dense tail; then the slices are gathered
+                (r, world), H = self.shard, FakeEngine.SPARSE
+                lo, hi = r * H // world, (r + 1) * H // world
+                for a, b in ((lo, hi), (H, 18)):
+                    self.w[a:b] -= 0.1 * self.g[a:b]
+                    self.w_h[a:b] = self.w[a:b].half()
+                self.param_sync(self.w_h)
             self.g.zero_()
             self.steps += 1
             done += k
@@ -84,6 +105,27 @@ def _worker(rank, world, port, out_dir, case):
                 used.append(tr.train_rays(o, d, c))
             np.save(os.path.join(out_dir, "w%d.npy" % rank), eng.w.numpy())
             np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([tr.sync_calls, eng.steps, int(tr.replicas_in_sync())] + used))
+        elif case == "sharded":
+            # reduce-scatter + slice update + all-gather of the fp16 copy, with uneven per-rank sample batches
+            eng = FakeEngine(max_rays=20 if rank == 1 else 1 << 30)
+            tr = D.DataParallelTrainer(torch, eng, dist, steps_per_call=2, exchange="sharded")
+            for c in range(4):
+                tr.train_rays(*_batch(64, 40 + c))
+            in_sync = int(tr.replicas_in_sync())
+            stale = eng.w.clone()
+            tr.gather_master()
+            np.save(os.path.join(out_dir, "w%d.npy" % rank), eng.w.numpy())
+            np.save(os.path.join(out_dir, "wh%d.npy" % rank), eng.w_h.float().numpy())
+            np.save(os.path.join(out_dir, "stale%d.npy" % rank), stale.numpy())
+            np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([tr.sync_calls, eng.steps, in_sync]))
+            tr.close()
+            assert eng.sync is None and eng.shard is None
+        elif case == "sharded_vs_allreduce":
+            eng = FakeEngine(max_rays=20 if rank == 1 else 1 << 30)
+            tr = D.DataParallelTrainer(torch, eng, dist, steps_per_call=2, exchange="allreduce")
+            for c in range(4):
+                tr.train_rays(*_batch(64, 40 + c))
+            np.save(os.path.join(out_dir, "ar_w%d.npy" % rank), eng.w.numpy())
         elif case == "overflow":
             # rank 1's sample batch holds only 20 of its 32 rays: it still takes ONE step and ONE exchange
             eng = FakeEngine(max_rays=20 if rank == 1 else 1 << 30)
@@ -176,6 +218,26 @@ def test_fixed_number_of_steps_per_call_keeps_ranks_in_lock_step(tmp_path):
     m0, m1 = np.load(tmp_path / "meta0.npy"), np.load(tmp_path / "meta1.npy")
     assert list(m0) == [6, 6, 1, 32, 32] and list(m1) == [6, 6, 1, 32, 32]
     assert np.array_equal(np.load(tmp_path / "w0.npy"), np.load(tmp_path / "w1.npy"))
+
+
+def test_sharded_optimizer_equals_the_allreduce_exchange(tmp_path):
+    """Reduce-scatter, update of the own table slice, all-gather of the fp16 copy: every rank ends with the parameters the
+    all-reduce + full update gives; before gather_master() a rank's master copy of the OTHER slice is stale, after it
+    every rank holds all of it."""
+    _run("sharded", tmp_path)
+    _run("sharded_vs_allreduce", tmp_path)
+    w0, w1 = np.load(tmp_path / "w0.npy"), np.load(tmp_path / "w1.npy")
+    assert np.array_equal(w0, w1)
+    assert np.array_equal(np.load(tmp_path / "wh0.npy"), np.load(tmp_path / "wh1.npy"))
+    assert np.allclose(w0, np.load(tmp_path / "ar_w0.npy"), rtol=1e-5, atol=1e-6)
+    assert np.array_equal(np.load(tmp_path / "wh0.npy"), w0.astype(np.float16).astype(np.float32))
+    s0, s1 = np.load(tmp_path / "stale0.npy"), np.load(tmp_path / "stale1.npy")
+    assert np.array_equal(s0[:8], w0[:8]) and not np.array_equal(s0[8:16], w0[8:16])      # rank 0 owns the first half
+    assert np.array_equal(s1[8:16], w0[8:16]) and not np.array_equal(s1[:8], w0[:8])
+    assert np.array_equal(s0[16:], w0[16:]) and np.array_equal(s1[16:], w0[16:])            # the dense tail is replicated
+    for r in range(2):
+        meta = np.load(tmp_path / ("meta%d.npy" % r))
+        assert list(meta) == [8, 8, 1]
 
 
 def test_replica_drift_is_detected(tmp_path):
