@@ -166,6 +166,14 @@ _SIGNATURES = {
     "nb_field_forward_counted": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float,
                                          c_void_p, c_void_p, c_int, c_void_p]),
+    "nb_sample_order_scratch_bytes": (c_int64, []),
+    "nb_sample_order": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "nb_field_forward_ordered": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_int, c_void_p]),
+    "nb_field_backward_ordered": (c_int, [ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_void_p]),
     "nb_field_backward": (c_int, [ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_void_p]),
@@ -215,6 +223,7 @@ _SIGNATURES = {
     "nb_occ_update_master_grid": (c_int, [c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "nb_occ_update_bitfield": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "nb_occ_extract_active": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_unpack_samples": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "nb_undeal_tiles": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nb_nerf_default_options": (c_int, [ctypes.POINTER(NerfOptions)]),
     "nb_nerf_create": (c_void_p, [ctypes.POINTER(NerfOptions), c_int]),

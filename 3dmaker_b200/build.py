@@ -74,10 +74,14 @@ def build(force=False, verbose=False):
             for log in ex.map(lambda j: _compile(j[0], j[1], verbose), jobs):
                 logs.append(log)
     if jobs or not os.path.exists(LIB):
-        cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+        # link beside the target and rename: whoever reads the library (a copy of the tree, a running process) never sees
+        # a half-written file
+        tmp = LIB + ".linking"
+        cmd = [_nvcc(), "-shared", "-o", tmp] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+        os.replace(tmp, LIB)
     if verbose:
         print("\n".join(logs))
     return LIB

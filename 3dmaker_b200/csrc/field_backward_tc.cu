@@ -64,7 +64,8 @@ constexpr uint32_t OFF_C = OFF_B + tile_bytes(ROWS, 64);          // colour hidd
 constexpr uint32_t OFF_Z = OFF_C + tile_bytes(ROWS, 64);          // 16-wide gradients: colour output, then density output [128][16]
 constexpr uint32_t OFF_BIAS = OFF_Z + tile_bytes(ROWS, 16);       // fp32 biases: density 64 + 16, colour 64 + 64 + 8
 constexpr uint32_t OFF_X = OFF_BIAS + (64 + 16 + 64 + 64 + 8) * 4;   // hand-over: 2 buffers x [16 levels][128 rows] fp16 pairs
-constexpr uint32_t SMEM_BYTES = OFF_X + 2 * 16 * ROWS * 4;
+constexpr int GROUP_TILES = 1;        // consecutive tiles a CTA takes at a time
+constexpr uint32_t SMEM_BYTES = OFF_X + 2 * 16 * ROWS * 4;   // 107 KB: two CTAs per SM (measured: at 111 KB only one is resident)
 
 // ---- tensor-memory map (32-bit columns) ----------------------------------------------------------------------
 constexpr uint32_t COL_WORK = 0;      // result of the current layer GEMM, up to 64 columns, 128 lanes
@@ -119,14 +120,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
     const uint32_t a = smem_u32(bar);
     if (mbar_test(a, parity)) return true;
     if (limit_ns == 0) return false;
-    const uint64_t t0 = global_ns();
-    for (;;) {
+    // the timer is looked at once in 256 failed polls (a poll itself waits a while in hardware): the common case, a
+    // barrier that completes within a few polls, never reads it
+    uint64_t t0 = 0;
+    for (uint32_t polls = 1;; polls++) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
                      : "=r"(ok) : "r"(a), "r"(parity) : "memory");
         if (ok) return true;
         if (give_up != nullptr && *give_up != 0) return false;
-        if (global_ns() - t0 > limit_ns) return false;
+        if ((polls & 255u) == 0u) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) return false;
+        }
     }
 }
 
@@ -297,6 +304,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
     const int64_t ntiles = (a.n + ROWS - 1) / ROWS;
+    const int64_t ngroups = (ntiles + GROUP_TILES - 1) / GROUP_TILES;   // a CTA takes whole groups of consecutive tiles
     bool ok = true;
     uint32_t phase_out = 0;   // chain warps: commits awaited or given up on so far
 
@@ -306,24 +314,29 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
         if (a.table_grads != nullptr) {
             const int r = (tid - CHAIN_THREADS) & (ROWS - 1), group = (tid - CHAIN_THREADS) >> 7;
             int it = 0;
-            for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, it++) {
-                const int buf = it & 1, use = it >> 1;
-                const bool got = __all_sync(0xffffffffu, mbar_wait(&x_full[buf], use & 1, WAIT_LIMIT_NS, abort_flag));
-                if (!got) { ok = false; break; }   // the chain gave up (or never came): leave, every wait here is bounded
-                const uint32_t* x = reinterpret_cast<const uint32_t*>(smem + OFF_X) + buf * 16 * ROWS;
-                uint32_t pk[16];
+            for (int64_t grp = blockIdx.x; grp < ngroups && ok; grp += gridDim.x) {
+                for (int tl = 0; tl < GROUP_TILES; tl++) {
+                    const int64_t tile = grp * GROUP_TILES + tl;
+                    if (tile >= ntiles) break;
+                    const int buf = it & 1, use = it >> 1;
+                    const bool got = __all_sync(0xffffffffu, mbar_wait(&x_full[buf], use & 1, WAIT_LIMIT_NS, abort_flag));
+                    if (!got) { ok = false; break; }   // the chain gave up (or never came): leave, every wait here is bounded
+                    const uint32_t* x = reinterpret_cast<const uint32_t*>(smem + OFF_X) + buf * 16 * ROWS;
+                    uint32_t pk[16];
 #pragma unroll
-                for (int l = 0; l < 16; l++) pk[l] = x[l * ROWS + r];
-                mbar_arrive(&x_empty[buf]);
-                const int64_t row = tile * ROWS + r;
-                const bool has = row < a.n;
-                float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (has) p = ld_nc_f4(a.pos4 + row * 4);
-                // a warp is 32 consecutive samples working on one level at a time
+                    for (int l = 0; l < 16; l++) pk[l] = x[l * ROWS + r];
+                    mbar_arrive(&x_empty[buf]);
+                    it++;
+                    const int64_t row = tile * ROWS + r;
+                    const bool has = row < a.n;
+                    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (has) p = ld_nc_f4(a.pos4 + (a.perm ? (int64_t)a.perm[row] : row) * 4);
+                    // a warp is 32 consecutive rows working on one level at a time
 #pragma unroll
-                for (int l = 0; l < 16; l++)
-                    if (l >= a.scatter_begin && (l % SCATTER_GROUPS) == group)
-                        scatter_level_warp(gp, l, p.x, p.y, p.z, unpack_half2(pk[l]), has, a.table_grads, lane);
+                    for (int l = 0; l < 16; l++)
+                        if (l >= a.scatter_begin && (l % SCATTER_GROUPS) == group)
+                            scatter_level_warp(gp, l, p.x, p.y, p.z, unpack_half2(pk[l]), has, a.table_grads, lane);
+                }
             }
         }
     } else {
@@ -344,23 +357,26 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
             return *abort_flag == 0;
         };
 
-        for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, it++) {
+        for (int64_t tile_seq = (int64_t)blockIdx.x * GROUP_TILES; tile_seq < ntiles && ok; it++,
+                     tile_seq = ((tile_seq % GROUP_TILES) == GROUP_TILES - 1) ? tile_seq - (GROUP_TILES - 1) + (int64_t)gridDim.x * GROUP_TILES : tile_seq + 1) {
+            const int64_t tile = tile_seq;
             const int64_t row_base = tile * ROWS;
             const int64_t row = row_base + tid;
             const bool has = row < a.n;
+            const int64_t smp = has ? (a.perm ? (int64_t)a.perm[row] : row) : 0;   // the sample in this row
             // ---- stage 0: encoding tile and colour gradient (zero rows past n; gradient columns 8..15 zero) -------------
             for (int c = tid; c < ROWS * 4; c += CHAIN_THREADS) {
                 const int r = c >> 2, c8 = c & 3;
                 const bool v = row_base + r < a.n;
                 cp_async16(smem + OFF_E + core_off(r, c8 * 8, 32), v ? (const void*)(a.enc + (row_base + r) * 32 + c8 * 8) : (const void*)a.enc, v);
             }
-            cp_async16(smem + OFF_Z + core_off(tid, 0, 16), has ? (const void*)(a.dcolor + row * 8) : (const void*)a.dcolor, has);
+            cp_async16(smem + OFF_Z + core_off(tid, 0, 16), has ? (const void*)(a.dcolor + smp * 8) : (const void*)a.dcolor, has);
             *reinterpret_cast<uint4*>(smem + OFF_Z + core_off(tid, 8, 16)) = make_uint4(0u, 0u, 0u, 0u);
             cp_async_commit();
             // direction of this row's ray, for the SH half of the colour input
             float sh[16];
             {
-                int64_t r = has ? row : a.n - 1;
+                int64_t r = has ? smp : (a.perm ? (int64_t)a.perm[a.n - 1] : a.n - 1);
                 int64_t ray = a.ray_idx ? (int64_t)a.ray_idx[r + a.ray_idx_offset] : r;
                 const float* dp = a.dirs3 + 3 * ray;
                 sh16(dp[0], dp[1], dp[2], sh);
@@ -491,7 +507,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
                 float v[16];
                 tmem_ld16(lane_base + COL_WORK, v);
                 // compute_density_grad (modules/NeRF/otherKernels.cu:497-562): fp16 gradient, + dL/dsigma on logit 0, clamp, NaN -> 0
-                const float ds = (has && a.dsigma != nullptr) ? a.dsigma[row] : 0.f;
+                const float ds = (has && a.dsigma != nullptr) ? a.dsigma[smp] : 0.f;
 #pragma unroll
                 for (int i = 0; i < 16; i++) v[i] = clamp_half_range(__half2float(__float2half_rn(v[i])) + (i == 0 ? ds : 0.f));
                 store_chunk(smem + OFF_Z, tid, 0, 16, v);
@@ -541,7 +557,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
 #pragma unroll
                 for (int l = 0; l < 16; l++) pk[l] = pack_half2(v[2 * l], v[2 * l + 1]);
                 if (has && a.denc_cols > 0) {
-                    uint2* dst = reinterpret_cast<uint2*>(a.denc + row * a.denc_cols);
+                    uint2* dst = reinterpret_cast<uint2*>(a.denc + smp * a.denc_cols);
 #pragma unroll
                     for (int q = 0; q < 8; q++)
                         if (4 * q < a.denc_cols) dst[q] = make_uint2(pk[2 * q], pk[2 * q + 1]);
@@ -660,8 +676,12 @@ int launch_field_backward_tc(const GridParams& gp, const tc::BackwardArgs& args_
     auto kern = tc::field_backward_tc_kernel;
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES));
     const int64_t ntiles = (args.n + tc::ROWS - 1) / tc::ROWS;
-    int64_t grid = (int64_t)nb_num_sms() * 2;   // two CTAs per SM: 107 KB of shared memory and 256 tensor-memory columns each
-    if (grid > ntiles) grid = ntiles;
+    // Two CTAs per SM: 107 KB of shared memory, 128 registers x 256 threads and 256 tensor-memory columns each.  The grid is
+    // sized by that count, not by cudaOccupancyMaxActiveBlocksPerMultiprocessor, which answers 1 for this kernel although
+    // two CTAs are resident (measured: 0.60 ms with 296 CTAs, 0.91 ms with the 148 the query suggests).
+    int64_t grid = (int64_t)nb_num_sms() * 2;
+    const int64_t ngroups = (ntiles + tc::GROUP_TILES - 1) / tc::GROUP_TILES;
+    if (grid > ngroups) grid = ngroups;
     kern<<<(unsigned)grid, tc::THREADS, tc::SMEM_BYTES, st>>>(gp, args);
     NB_CHECK_LAUNCH();
     g_launch_count++;

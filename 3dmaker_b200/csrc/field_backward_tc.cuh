@@ -27,6 +27,7 @@ struct BackwardArgs {
     const float* pos4;        // scatter
     float* table_grads;
     int scatter_begin;
+    const uint32_t* perm;     // nullable: row r of the tile order is sample perm[r] (enc is in row order, everything else by sample)
     int* error_flag;          // mapped host memory; set when a wait ran out
     uint64_t wait_ns;         // limit of the chain's waits (0: give up at once when a barrier is not ready - test only)
 };
@@ -35,6 +36,9 @@ struct BackwardArgs {
 
 extern std::atomic<int> g_backward_tc;
 extern std::atomic<int> g_backward_tc_wait_us;
+extern std::atomic<int> g_forward_staged;
+extern std::atomic<int> g_forward_stage_levels;
+extern std::atomic<int> g_forward_persistent;
 int field_backward_tc_failed();
 int launch_field_backward_tc(const GridParams& gp, const tc::BackwardArgs& args, cudaStream_t st);
 

@@ -14,6 +14,7 @@
 //
 // Arithmetic is the same as in the unfused kernels (same fp16 rounding points), so the two paths agree to the
 // last bit of every fp16 intermediate; only the fp32 summation order of dW differs.
+#include <algorithm>
 #include <atomic>
 
 #include "hashgrid_core.cuh"
@@ -70,8 +71,9 @@ struct FieldIO {
 // Colour-network input fragments of the warp's 16 rows from the density output fragments (16 logits) and the
 // ray directions: k chunk 0 = clamped logits, k chunk 1 = SH.  Also hands back sigma / raw logit of the rows
 // (valid in lanes with t == 0).
+// perm (nullable): row r of the tile order is sample perm[r].
 __device__ __forceinline__ void build_color_input(const float (&dout)[2][4], const FieldIO& io, int64_t row0, int lane, uint32_t (&a)[2][4],
-                                                  float& raw0, float& raw1) {
+                                                  float& raw0, float& raw1, const uint32_t* __restrict__ perm = nullptr) {
     const int g = lane >> 2, t = lane & 3;
     raw0 = dout[0][0]; raw1 = dout[0][2];  // column 0 of rows g and g+8 (lanes with t == 0)
     a[0][0] = pack_half2(sanitize_logit_f(dout[0][0]), sanitize_logit_f(dout[0][1]));
@@ -83,6 +85,7 @@ __device__ __forceinline__ void build_color_input(const float (&dout)[2][4], con
     for (int h = 0; h < 2; h++) {
         int64_t r = row0 + g + 8 * h;
         if (r >= io.n) r = io.n - 1;
+        if (perm != nullptr) r = (int64_t)perm[r];
         int64_t ray = io.ray_idx ? (int64_t)io.ray_idx[r + io.ray_idx_offset] : r;
         const float* dp = io.dirs3 + 3 * ray;
         sh_quad(dp[0], dp[1], dp[2], t, lo0, lo1, hi0, hi1);
@@ -163,6 +166,176 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid
     forward_layers<CS, 0, 1, false>(ca, cx);
 }
 
+
+
+// ---------------------------------------------------------------------------------------------
+// forward with the coarse levels staged in shared memory
+// ---------------------------------------------------------------------------------------------
+// Same arithmetic and outputs as field_forward_kernel.  Differences: CTAs are persistent and walk over groups of
+// FWD_GROUP_TILES consecutive tiles; per group the levels whose corner boxes fit are copied into shared memory once and
+// gathered from there; the weights are staged once per CTA; rows may be visited through a permutation (perm[row] =
+// sample), in which case the saved encoding is in ROW order (the backward visits the same rows) and every per-sample
+// output lands at its sample's place.
+constexpr int FWD_GROUP_TILES = 4;
+constexpr int FWD_STAGE_CAP = 6144;   // entries of 4 bytes
+constexpr int FWD_STAGE_LEVELS = 8;   // never look further than this many levels
+
+template <class DS, class CS>
+struct FieldStagedSmem {
+    static constexpr int ENC_STRIDE = DS::K0 + 8;
+    static constexpr size_t bytes() {
+        return FieldSmem<DS, CS>::fwd_bytes() + (size_t)FWD_STAGE_CAP * 4 + sizeof(StagePlan) + 32;
+    }
+};
+
+template <class DS, class CS>
+__global__ void __launch_bounds__(CTA_THREADS) field_forward_staged_kernel(const __grid_constant__ GridParams gp, FieldIO io,
+                                                                           const uint32_t* __restrict__ perm, __half* __restrict__ enc_save,
+                                                                           float* __restrict__ sigma_out, float* __restrict__ logit_out,
+                                                                           float* __restrict__ rgb_out, int rgb_stride, int stage_levels) {
+    static_assert(DS::OUT == 16 && CS::K0 == 32 && CS::OUT == 8, "the colour network takes 16 density features and 16 SH coefficients");
+    using FS = FieldSmem<DS, CS>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half* sWd = reinterpret_cast<__half*>(smem_raw);
+    __half* sWc = sWd + DS::SW_TOTAL;
+    float* sBd = reinterpret_cast<float*>(sWc + CS::SW_TOTAL);
+    float* sBc = sBd + DS::B_TOTAL;
+    __half* tile = reinterpret_cast<__half*>(sBc + CS::B_TOTAL);
+    uint32_t* s_tab = reinterpret_cast<uint32_t*>(tile + TILE_ROWS * FS::ENC_STRIDE);
+    StagePlan& plan = *reinterpret_cast<StagePlan*>(s_tab + FWD_STAGE_CAP);
+    float* s_box = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&plan) + sizeof(StagePlan));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+
+    if (io.count != nullptr) {
+        const int64_t counted = (int64_t)__ldg(io.count);
+        if (counted < io.n) io.n = counted;
+    }
+    const int64_t group_rows = (int64_t)FWD_GROUP_TILES * TILE_ROWS;
+    const int64_t groups = (io.n + group_rows - 1) / group_rows;
+    if ((int64_t)blockIdx.x >= groups) return;
+    load_weights_to_smem<DS>(io.Wd, io.bd, sWd, sBd, tid);
+    load_weights_to_smem<CS>(io.Wc, io.bc, sWc, sBc, tid);
+    cp_async_commit();
+    cp_async_wait_all();
+
+    for (int64_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+        const int64_t group_base = grp * group_rows;
+        // ---- which levels come from shared memory for this group, and their boxes ---------------------------------
+        int staged = 0;
+        if (stage_levels > 0) {
+            plan_stage<false, CTA_THREADS>(gp, io.pos4, perm, group_base, (int)group_rows, io.n, FWD_STAGE_CAP, stage_levels, s_box, plan, tid,
+                                           [] { __syncthreads(); });
+            staged = plan.count;
+        }
+        for (int l = 0; l < staged; l++) {
+            const uint32_t* tl = io.table2 + (size_t)l * gp.T;
+            const int N_l = __float2int_rd(gp.scales[l]);
+            const bool dense = l < gp.dls;
+            const int w = plan.w[l], wh = plan.wh[l], cnt = plan.whd[l], base = plan.base[l];
+            const int ox = plan.ox[l], oy = plan.oy[l], oz = plan.oz[l];
+            for (int e = tid; e < cnt; e += CTA_THREADS) {
+                const int lz = e / wh, rem = e - lz * wh, ly = rem / w, lx = rem - ly * w;
+                s_tab[base + e] = __ldg(tl + level_index(ox + lx, oy + ly, oz + lz, N_l, dense, gp.T));
+            }
+        }
+        __syncthreads();
+
+        for (int tl_i = 0; tl_i < FWD_GROUP_TILES; tl_i++) {
+            const int64_t row_base = group_base + (int64_t)tl_i * TILE_ROWS;
+            if (row_base >= io.n) break;
+            // ---- encode: thread = (row, every other level), so staged and gathered levels split evenly over the halves ---
+            {
+                const int r = tid & (TILE_ROWS - 1), hsel = tid >> 7;
+                const int64_t row = row_base + r;
+                if (row < io.n) {
+                    const int64_t smp = perm ? (int64_t)perm[row] : row;
+                    const float4 p = ld_nc_f4(io.pos4 + smp * 4);
+                    for (int li = hsel; li < gp.L; li += 4) {
+                        // two levels at a time keeps 16 gathers in flight
+                        const int la = li, lb = li + 2;
+                        const bool has_b = lb < gp.L;
+                        CornerBox ba, bb;
+                        corner_box<false>(p.x, p.y, p.z, gp.scales[la], ba);
+                        corner_box<false>(p.x, p.y, p.z, gp.scales[has_b ? lb : la], bb);
+                        uint32_t fa[8], fb[8];
+                        int loc[8];
+                        if (la < staged && staged_corners(plan, la, ba, loc)) {
+#pragma unroll
+                            for (int k = 0; k < 8; k++) fa[k] = s_tab[loc[k]];
+                        } else {
+                            Corners c;
+                            corners_from_box(ba, la < gp.dls, gp.T, c);
+                            gather_corners(io.table2 + (size_t)la * gp.T, c, gp.pair_ops != 0, fa);
+                        }
+                        if (has_b) {
+                            if (lb < staged && staged_corners(plan, lb, bb, loc)) {
+#pragma unroll
+                                for (int k = 0; k < 8; k++) fb[k] = s_tab[loc[k]];
+                            } else {
+                                Corners c;
+                                corners_from_box(bb, lb < gp.dls, gp.T, c);
+                                gather_corners(io.table2 + (size_t)lb * gp.T, c, gp.pair_ops != 0, fb);
+                            }
+                        }
+                        Corners wa, wb;
+                        wa.wx1 = ba.wx1; wa.wy1 = ba.wy1; wa.wz1 = ba.wz1;
+                        wb.wx1 = bb.wx1; wb.wy1 = bb.wy1; wb.wz1 = bb.wz1;
+                        float ka[8], kb[8];
+                        corner_weights(wa, ka);
+                        corner_weights(wb, kb);
+                        *reinterpret_cast<uint32_t*>(&tile[r * FS::ENC_STRIDE + 2 * la]) = blend(fa, ka);
+                        if (has_b) *reinterpret_cast<uint32_t*>(&tile[r * FS::ENC_STRIDE + 2 * lb]) = blend(fb, kb);
+                    }
+                } else {
+                    for (int l = hsel; l < gp.L; l += 2) *reinterpret_cast<uint32_t*>(&tile[r * FS::ENC_STRIDE + 2 * l]) = 0u;
+                }
+            }
+            __syncthreads();
+            if (enc_save != nullptr) store_enc_tile<FS::ENC_STRIDE>(tile, enc_save, gp.L, row_base, io.n, tid);
+
+            const int64_t row0 = row_base + warp * 16;
+            if (row0 < io.n) {
+                uint32_t a[DS::K0 / 16][4];
+#pragma unroll
+                for (int kc = 0; kc < DS::K0 / 16; kc++) {
+                    int q = lane >> 3, r = lane & 7;
+                    ldmatrix_x4(a[kc], &tile[(warp * 16 + r + (q & 1) * 8) * FS::ENC_STRIDE + 16 * kc + (q >> 1) * 8]);
+                }
+                FwdCtx dx{};
+                dx.sW = sWd; dx.sBias = sBd; dx.row0 = row0; dx.n = io.n; dx.lane = lane;
+                float dout[2][4];
+                forward_layers<DS, 0, 0, true>(a, dx, dout);
+                uint32_t ca[2][4];
+                float raw0, raw1;
+                build_color_input(dout, io, row0, lane, ca, raw0, raw1, perm);
+                const int64_t r0 = row0 + g, r1 = r0 + 8;
+                const int64_t s0 = (r0 < io.n) ? (perm ? (int64_t)perm[r0] : r0) : -1;
+                const int64_t s1 = (r1 < io.n) ? (perm ? (int64_t)perm[r1] : r1) : -1;
+                if (t == 0) {
+                    if (s0 >= 0) {
+                        if (logit_out) logit_out[s0] = raw0;
+                        if (sigma_out) sigma_out[s0] = expf(fminf(sanitize_logit_f(raw0) - io.density_bias, 8.0f));
+                    }
+                    if (s1 >= 0) {
+                        if (logit_out) logit_out[s1] = raw1;
+                        if (sigma_out) sigma_out[s1] = expf(fminf(sanitize_logit_f(raw1) - io.density_bias, 8.0f));
+                    }
+                }
+                FwdCtx cx{};
+                cx.sW = sWc; cx.sBias = sBc; cx.row0 = row0; cx.n = io.n; cx.lane = lane;
+                float fin[1][4];
+                forward_layers<CS, 0, 1, true>(ca, cx, fin);
+                // lane t holds columns 2t, 2t + 1 of rows g and g + 8: rgb and the padding column(s)
+                const int col = 2 * t;
+                if (col < (rgb_stride < 8 ? 4 : 8)) {
+                    if (s0 >= 0) *reinterpret_cast<float2*>(&rgb_out[s0 * rgb_stride + col]) = make_float2(fin[0][0], fin[0][1]);
+                    if (s1 >= 0) *reinterpret_cast<float2*>(&rgb_out[s1 * rgb_stride + col]) = make_float2(fin[0][2], fin[0][3]);
+                }
+            }
+            __syncthreads();   // the next tile's encode overwrites the tile
+        }
+    }
+}
 
 // ---------------------------------------------------------------------------------------------
 // backward
@@ -517,11 +690,17 @@ extern "C" int nb_field_supported(const nb_grid_desc* grid, const nb_mlp_desc* d
            color->output_activation == 1;
 }
 
+namespace nb {
+std::atomic<int> g_forward_staged{2};   // nb_set_tuning("forward_staged", ...): 0 never, 1 always, 2 when the call brings a sample order
+std::atomic<int> g_forward_stage_levels{FWD_STAGE_LEVELS};   // "forward_stage_levels": leading levels the ordered forward may stage (0: none)
+std::atomic<int> g_forward_persistent{1};                     // "forward_persistent": 0 = one CTA per tile group
+}
+
 static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
                                 const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
                                 const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
                                 int64_t n, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
-                                int rgb_stride, const uint32_t* d_count, void* stream) {
+                                int rgb_stride, const uint32_t* d_count, void* stream, const uint32_t* d_perm = nullptr) {
     if (!grid || !density || !color || !d_pos4 || !d_table_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b ||
         !d_rgb || n < 0)
         return nb_set_error(NB_ERR_INVALID, "nb_field_forward: null pointer or negative count");
@@ -537,12 +716,32 @@ static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* densi
     io.ray_idx_offset = ray_index_offset;
     io.Wd = (const __half*)d_density_w_h; io.bd = d_density_b; io.Wc = (const __half*)d_color_w_h; io.bc = d_color_b;
     io.n = n; io.density_bias = density_bias; io.count = d_count;
+    nb::GridParams gp = nb::make_params(grid);
+    if (misaligned(d_table_h, 8)) gp.pair_ops = 0;
+    const int staged_mode = nb::g_forward_staged.load();
+    if (d_perm != nullptr || staged_mode == 1) {
+        if (staged_mode == 0) return nb_set_error(NB_ERR_INVALID, "nb_field_forward_ordered: the staged forward is switched off (forward_staged = 0)");
+        auto kern = nb::field_forward_staged_kernel<DensityNet, ColorNet>;
+        const size_t smem = nb::FieldStagedSmem<DensityNet, ColorNet>::bytes();
+        NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int per_sm = 0;
+        NB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, nb::CTA_THREADS, smem));
+        if (per_sm < 1) per_sm = 1;
+        const int64_t group_rows = (int64_t)nb::FWD_GROUP_TILES * nb::TILE_ROWS;
+        const int64_t groups = (n + group_rows - 1) / group_rows;
+        int64_t grid_dim = (int64_t)nb_num_sms() * per_sm;
+        if (grid_dim > groups || nb::g_forward_persistent.load() == 0) grid_dim = groups;
+        const int stage_levels = std::max(0, std::min(nb::g_forward_stage_levels.load(), (int)nb::FWD_STAGE_LEVELS));
+        kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, d_perm, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb,
+                                                                                  rgb_stride, stage_levels);
+        NB_CHECK_LAUNCH();
+        nb::g_launch_count++;
+        return NB_OK;
+    }
     auto kern = nb::field_forward_kernel<DensityNet, ColorNet>;
     size_t smem = nb::FieldSmem<DensityNet, ColorNet>::fwd_bytes();
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
-    nb::GridParams gp = nb::make_params(grid);
-    if (misaligned(d_table_h, 8)) gp.pair_ops = 0;
     kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride);
     NB_CHECK_LAUNCH();
     nb::g_launch_count++;
@@ -558,6 +757,16 @@ extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* den
                               d_color_w_h, d_color_b, n, density_bias, d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride, nullptr, stream);
 }
 
+extern "C" int nb_field_forward_ordered(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                                        const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                                        const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
+                                        int64_t n, const uint32_t* d_order, float density_bias, void* d_enc_save_h, float* d_sigma,
+                                        float* d_logit0, float* d_rgb, int rgb_stride, void* stream) {
+    if (!d_order) return nb_set_error(NB_ERR_INVALID, "nb_field_forward_ordered: null sample order");
+    return field_forward_impl(grid, density, color, d_pos4, d_table_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b,
+                              d_color_w_h, d_color_b, n, density_bias, d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride, nullptr, stream, d_order);
+}
+
 extern "C" int nb_field_forward_counted(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
                                         const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices,
                                         int64_t ray_index_offset, const void* d_density_w_h, const float* d_density_b,
@@ -568,12 +777,12 @@ extern "C" int nb_field_forward_counted(const nb_grid_desc* grid, const nb_mlp_d
                               d_color_w_h, d_color_b, n_max, density_bias, nullptr, d_sigma, nullptr, d_rgb, rgb_stride, d_count, stream);
 }
 
-extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
-                                 const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
-                                 const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
-                                 const void* d_dcolor_h, const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b,
-                                 float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h, const nb_grid_desc* grid,
-                                 const float* d_pos4, float* d_table_grads, void* stream) {
+static int field_backward_impl(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
+                               const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
+                               const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
+                               const void* d_dcolor_h, const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b,
+                               float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h, const nb_grid_desc* grid,
+                               const float* d_pos4, float* d_table_grads, void* stream, const uint32_t* d_perm) {
     if (!density || !color || !d_enc_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b || !d_dcolor_h ||
         !d_grad_density_w || !d_grad_density_b || !d_grad_color_w || !d_grad_color_b || !d_denc_h || n < 0)
         return nb_set_error(NB_ERR_INVALID, "nb_field_backward: null pointer or negative count");
@@ -609,11 +818,12 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
         gio.pos4 = d_pos4; gio.table_grads = d_table_grads; gio.scatter_begin = shared_levels;
         gio.denc_cols = 4 * shared_levels;   // only what the shared-memory scatter kernel below reads
     }
-    const int tc_mode = nb::g_backward_tc.load();
+    const int tc_mode = d_perm != nullptr ? 1 : nb::g_backward_tc.load();
     // The tensor-memory kernel adds its weight gradients with 16-byte reductions; the register kernel needs 8 bytes only.
     const bool grads_16 = !misaligned(d_grad_density_w, 16) && !misaligned(d_grad_color_w, 16);
     if (tc_mode == 1 && !grads_16)
         return nb_set_error(NB_ERR_INVALID, "nb_field_backward: the tensor-memory kernel needs 16-byte aligned weight gradients");
+    if (d_perm != nullptr && scatter && misaligned(d_pos4, 16)) return nb_set_error(NB_ERR_INVALID, "nb_field_backward_ordered: misaligned positions");
     if (tc_mode == 1 || (tc_mode == 2 && d_ray_indices == nullptr && grads_16)) {
         // tensor-memory formulation (field_backward_tc.cu): same inputs, outputs and rounding points
         nb::tc::BackwardArgs ta{};
@@ -621,6 +831,7 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
         ta.ray_idx_offset = io.ray_idx_offset; ta.Wd = io.Wd; ta.Wc = io.Wc; ta.bd = io.bd; ta.bc = io.bc; ta.n = n;
         ta.dWd = gio.dWd; ta.dbd = gio.dbd; ta.dWc = gio.dWc; ta.dbc = gio.dbc; ta.denc = gio.denc; ta.denc_cols = gio.denc_cols;
         ta.pos4 = gio.pos4; ta.table_grads = gio.table_grads; ta.scatter_begin = gio.scatter_begin;
+        ta.perm = d_perm;
         int rc = nb::launch_field_backward_tc(gp, ta, (cudaStream_t)stream);
         if (rc != NB_OK) return rc;
         if (scatter && shared_levels > 0)
@@ -642,4 +853,27 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
     if (scatter && shared_levels > 0)
         return nb::scatter_launch(gp, d_pos4, (const __half*)d_denc_h, 4 * shared_levels, n, d_table_grads, 0, shared_levels, (cudaStream_t)stream);
     return NB_OK;
+}
+
+extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
+                                 const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
+                                 const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
+                                 const void* d_dcolor_h, const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b,
+                                 float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h, const nb_grid_desc* grid,
+                                 const float* d_pos4, float* d_table_grads, void* stream) {
+    return field_backward_impl(density, color, d_enc_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b, d_color_w_h, d_color_b, n,
+                               d_dcolor_h, d_dsigma, d_grad_density_w, d_grad_density_b, d_grad_color_w, d_grad_color_b, d_denc_h, grid, d_pos4,
+                               d_table_grads, stream, nullptr);
+}
+
+extern "C" int nb_field_backward_ordered(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
+                                         const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
+                                         const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
+                                         const uint32_t* d_order, const void* d_dcolor_h, const float* d_dsigma, float* d_grad_density_w,
+                                         float* d_grad_density_b, float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h,
+                                         const nb_grid_desc* grid, const float* d_pos4, float* d_table_grads, void* stream) {
+    if (!d_order) return nb_set_error(NB_ERR_INVALID, "nb_field_backward_ordered: null sample order");
+    return field_backward_impl(density, color, d_enc_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b, d_color_w_h, d_color_b, n,
+                               d_dcolor_h, d_dsigma, d_grad_density_w, d_grad_density_b, d_grad_color_w, d_grad_color_b, d_denc_h, grid, d_pos4,
+                               d_table_grads, stream, d_order);
 }

@@ -79,6 +79,13 @@ __global__ void __launch_bounds__(CTA_THREADS) grid_mlp_forward_kernel(const __g
 
     const int64_t row_base = (int64_t)blockIdx.x * TILE_ROWS;
     encode_tile<S::TILE_STRIDE>(gp, pos4, table2, row_base, n, tile, tid);
+    if constexpr (S::K0V < S::K0) {
+        // fewer levels than the 16-wide k chunk: the columns behind the encoding are zero
+        for (int c = tid; c < TILE_ROWS * (S::K0 - S::K0V) / 2; c += CTA_THREADS) {
+            const int r = c / ((S::K0 - S::K0V) / 2), c2 = c % ((S::K0 - S::K0V) / 2);
+            *reinterpret_cast<uint32_t*>(&tile[r * S::TILE_STRIDE + S::K0V + 2 * c2]) = 0u;
+        }
+    }
     cp_async_wait_all();
     __syncthreads();
     if (SAVE && save_enc != nullptr) {
@@ -391,6 +398,9 @@ extern "C" int nb_grid_mlp_forward(const nb_grid_desc* desc, const nb_mlp_desc* 
     X(32, 64, 16, 1)
     X(16, 16, 16, 2)
 #undef X
+    // four levels: 8 encoded features, run as a 16-wide input whose upper half is zero (forward only)
+    if (mlp->input_dim == 8 && mlp->hidden_dim == 64 && mlp->output_dim == 16 && mlp->num_layers == 2)
+        return launch_grid_mlp<MlpShape<16, 64, 16, 2, 8>>(gp, d_pos4, d_table_h, d_weights_h, d_biases, n, d_out, d_save_enc_h, d_save_acts_h, st);
     return nb_set_error(NB_ERR_UNSUPPORTED, "nb_grid_mlp_forward: no kernel built for this (levels, hidden, output, layers) shape");
 }
 
@@ -400,6 +410,9 @@ extern "C" int nb_set_tuning(const char* key, int value) {
     if (k == "scatter_run_merge") g_run_merge = value;
     else if (k == "backward_tc") g_backward_tc = value;
     else if (k == "backward_tc_wait_us") g_backward_tc_wait_us = value;
+    else if (k == "forward_staged") g_forward_staged = value;
+    else if (k == "forward_stage_levels") g_forward_stage_levels = value;
+    else if (k == "forward_persistent") g_forward_persistent = value;
     else if (k == "scatter_smem_levels") g_scatter_tuning.smem_levels = value;
     else if (k == "pair_ops") g_pair_ops = value;
     else if (k == "scatter_level_begin") g_scatter_tuning.level_begin = value;

@@ -170,10 +170,7 @@ __device__ __forceinline__ void reduce_corners(const Corners& c, const float (&v
 // Scattered positions (most lanes in different cells) take the direct path.
 // sink(c, v) adds v[2k], v[2k+1] to corner k's entry.
 template <class Sink>
-__device__ __forceinline__ void scatter_level_runs(const GridParams& gp, int level, float px, float py, float pz, float2 g, bool active, int lane,
-                                                   Sink&& sink) {
-    Corners c;
-    corners_of<true>(px, py, pz, gp.sscales[level], level < gp.dls, gp.T, c);
+__device__ __forceinline__ void scatter_runs(const GridParams& gp, const Corners& c, float2 g, bool active, int lane, Sink&& sink) {
     float w[8];
     corner_weights(c, w);
     active = active && (g.x != 0.f || g.y != 0.f);
@@ -203,11 +200,134 @@ __device__ __forceinline__ void scatter_level_runs(const GridParams& gp, int lev
     if (head && active) sink(c, v);
 }
 
+template <class Sink>
+__device__ __forceinline__ void scatter_level_runs(const GridParams& gp, int level, float px, float py, float pz, float2 g, bool active, int lane,
+                                                   Sink&& sink) {
+    Corners c;
+    corners_of<true>(px, py, pz, gp.sscales[level], level < gp.dls, gp.T, c);
+    scatter_runs(gp, c, g, active, lane, sink);
+}
+
 __device__ __forceinline__ void scatter_level_warp(const GridParams& gp, int level, float px, float py, float pz, float2 g, bool active,
                                                    float* __restrict__ grads, int lane) {
     float* base = grads + (size_t)level * gp.T * 2;
     const bool pair_ops = gp.pair_ops != 0;
     scatter_level_runs(gp, level, px, py, pz, g, active, lane, [&](const Corners& c, const float (&v)[16]) { reduce_corners(c, v, pair_ops, base); });
+}
+
+// ---- coarse levels from shared memory ------------------------------------------------------------------------------
+// When the samples a CTA works on lie close together, the corners they touch on a coarse level form a small box of the
+// level's grid.  The CTA then copies that box into shared memory once (forward) or accumulates into it and adds it to the
+// table gradient once (backward) instead of going to L2 eight times per sample and level.  Which levels are staged is
+// decided per group of tiles from the bounding box of the group's positions: levels 0, 1, ... as long as their boxes fit
+// the capacity.  Works for any sample order; nb_sample_order makes the boxes small.
+struct StagePlan {
+    int count;                                  // levels [0, count) are staged
+    int ox[NB_MAX_LEVELS], oy[NB_MAX_LEVELS], oz[NB_MAX_LEVELS];   // lowest corner of the box, in corner coordinates
+    int w[NB_MAX_LEVELS], wh[NB_MAX_LEVELS], whd[NB_MAX_LEVELS];   // extent in x, x * y, x * y * z (= entries)
+    int h[NB_MAX_LEVELS], d[NB_MAX_LEVELS];                        // extent in y and z
+    int base[NB_MAX_LEVELS];                    // first entry of the level in the staging array
+};
+
+// Low / high corner coordinates and interpolation weights of a point on one level (the arithmetic of corners_of).
+struct CornerBox {
+    int x0, y0, z0, x1, y1, z1, N_l;
+    float wx1, wy1, wz1;
+};
+
+template <bool BWD_CLAMP>
+__device__ __forceinline__ void corner_box(float px, float py, float pz, float scale, CornerBox& b) {
+    const int N_l = __float2int_rd(scale);
+    const float x_l = px * scale, y_l = py * scale, z_l = pz * scale;
+    const int hi = BWD_CLAMP ? N_l - 1 : N_l;
+    b.N_l = N_l;
+    b.x0 = max(0, min(__float2int_rd(x_l), hi)); b.y0 = max(0, min(__float2int_rd(y_l), hi)); b.z0 = max(0, min(__float2int_rd(z_l), hi));
+    b.x1 = min(b.x0 + 1, N_l); b.y1 = min(b.y0 + 1, N_l); b.z1 = min(b.z0 + 1, N_l);
+    b.wx1 = 1.0f - x_l + floorf(x_l);
+    b.wy1 = 1.0f - y_l + floorf(y_l);
+    b.wz1 = 1.0f - z_l + floorf(z_l);
+}
+
+// Entry index of corner (x, y, z) inside its level.
+__device__ __forceinline__ uint32_t level_index(int x, int y, int z, int N_l, bool dense, int T) {
+    return dense ? dense_index(x, y, z, N_l) : hash_coords(x, y, z, T);
+}
+
+__device__ __forceinline__ void corners_from_box(const CornerBox& b, bool dense, int T, Corners& c) {
+    c.wx1 = b.wx1; c.wy1 = b.wy1; c.wz1 = b.wz1;
+    c.cell = (b.N_l < 1024) ? ((uint32_t)b.x0 | ((uint32_t)b.y0 << 10) | ((uint32_t)b.z0 << 20)) : 0xffffffffu;
+#pragma unroll
+    for (int k = 0; k < 8; k++) c.idx[k] = level_index((k & 1) ? b.x1 : b.x0, (k & 2) ? b.y1 : b.y0, (k & 4) ? b.z1 : b.z0, b.N_l, dense, T);
+}
+
+// True when all 8 corners of the point lie inside the staged box of the level; loc[k] = their places in the staging array.
+__device__ __forceinline__ bool staged_corners(const StagePlan& pl, int level, const CornerBox& b, int (&loc)[8]) {
+    const int lx0 = b.x0 - pl.ox[level], ly0 = b.y0 - pl.oy[level], lz0 = b.z0 - pl.oz[level];
+    const int lx1 = b.x1 - pl.ox[level], ly1 = b.y1 - pl.oy[level], lz1 = b.z1 - pl.oz[level];
+    const int w = pl.w[level], wh = pl.wh[level], h = pl.h[level], d = pl.d[level];
+    if (lx0 < 0 || ly0 < 0 || lz0 < 0 || lx1 >= w || ly1 >= h || lz1 >= d) return false;
+#pragma unroll
+    for (int k = 0; k < 8; k++) loc[k] = pl.base[level] + ((k & 1) ? lx1 : lx0) + ((k & 2) ? ly1 : ly0) * w + ((k & 4) ? lz1 : lz0) * wh;
+    return true;
+}
+
+// Block-wide: bounding box of the positions of rows [row_first, row_first + rows) (through perm when given), then the
+// staging plan of levels 0, 1, ... while their boxes fit `capacity` entries.  s_box: 6 floats of shared memory.
+// All THREADS threads of the group must call (tid = 0 .. THREADS - 1, whole warps); `barrier()` synchronises exactly
+// them; ends with a barrier.  BWD_CLAMP selects the backward's clamp and resolutions.
+template <bool BWD_CLAMP, int THREADS, class Barrier>
+__device__ __forceinline__ void plan_stage(const GridParams& gp, const float* __restrict__ pos4, const uint32_t* __restrict__ perm,
+                                           int64_t row_first, int rows, int64_t n, int capacity, int max_levels, float* s_box, StagePlan& pl,
+                                           int tid, Barrier&& barrier) {
+    float lo[3] = {INFINITY, INFINITY, INFINITY}, hi[3] = {-INFINITY, -INFINITY, -INFINITY};
+    for (int r = tid; r < rows; r += THREADS) {
+        const int64_t row = row_first + r;
+        if (row < n) {
+            const int64_t s = perm ? (int64_t)perm[row] : row;
+            const float4 p = ld_nc_f4(pos4 + s * 4);
+            lo[0] = fminf(lo[0], p.x); lo[1] = fminf(lo[1], p.y); lo[2] = fminf(lo[2], p.z);
+            hi[0] = fmaxf(hi[0], p.x); hi[1] = fmaxf(hi[1], p.y); hi[2] = fmaxf(hi[2], p.z);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 3; a++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            lo[a] = fminf(lo[a], __shfl_xor_sync(0xffffffffu, lo[a], o));
+            hi[a] = fmaxf(hi[a], __shfl_xor_sync(0xffffffffu, hi[a], o));
+        }
+    if (tid < 6) s_box[tid] = tid < 3 ? INFINITY : -INFINITY;
+    barrier();
+    if ((tid & 31) == 0) {
+        // float min / max through the integer atomics: order-preserving for non-negative values, and a box that comes out
+        // too large (negative or non-finite coordinates) only means fewer levels are staged
+#pragma unroll
+        for (int a = 0; a < 3; a++) {
+            atomicMin(reinterpret_cast<int*>(&s_box[a]), __float_as_int(fmaxf(lo[a], 0.0f)));
+            atomicMax(reinterpret_cast<int*>(&s_box[3 + a]), __float_as_int(fmaxf(hi[a], 0.0f)));
+        }
+    }
+    barrier();
+    if (tid < gp.L && tid < max_levels) {
+        const int l = tid;
+        const float scale = BWD_CLAMP ? gp.sscales[l] : gp.scales[l];
+        CornerBox a, b;
+        corner_box<BWD_CLAMP>(s_box[0], s_box[1], s_box[2], scale, a);
+        corner_box<BWD_CLAMP>(s_box[3], s_box[4], s_box[5], scale, b);
+        pl.ox[l] = a.x0; pl.oy[l] = a.y0; pl.oz[l] = a.z0;
+        const int w = b.x1 - a.x0 + 1, h = b.y1 - a.y0 + 1, d = b.z1 - a.z0 + 1;
+        const bool sane = w > 0 && h > 0 && d > 0 && w <= 1024 && h <= 1024 && d <= 1024;
+        pl.w[l] = sane ? w : 1; pl.wh[l] = sane ? w * h : 1; pl.h[l] = sane ? h : 1; pl.d[l] = sane ? d : 1;
+        pl.whd[l] = (sane && (int64_t)w * h * d <= capacity) ? w * h * d : capacity + 1;
+    }
+    barrier();
+    if (tid == 0) {
+        int used = 0, count = 0;
+        const int top = min(gp.L, max_levels);
+        while (count < top && used + pl.whd[count] <= capacity) { pl.base[count] = used; used += pl.whd[count]; count++; }
+        pl.count = count;
+    }
+    barrier();
 }
 
 // Host side of the stand-alone scatter (hashgrid.cu): levels [level_begin, level_end) from a gradient matrix whose

@@ -342,6 +342,7 @@ static int launch_backward(const void* dL, const void* W, const void* act0, cons
     X(64, 64, 64, 4)     \
     X(32, 32, 32, 2)     \
     X(16, 16, 16, 2)     \
+    X(16, 32, 16, 3)     \
     X(32, 64, 16, 1)
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -17,19 +17,23 @@ namespace nb {
 constexpr int TILE_ROWS = 128;  // batch rows per CTA tile (8 warps x 16 rows)
 constexpr int CTA_THREADS = 256;
 
-template <int K0_, int H_, int OUT_, int NL_>
+// K0V: input columns that exist in global memory (weights of layer 0 are [out][K0V], the input rows K0V wide); the
+// kernels work on K0 >= K0V columns, the extra ones zero.  Only the forward kernels accept K0V != K0.
+template <int K0_, int H_, int OUT_, int NL_, int K0V_ = K0_>
 struct MlpShape {
-    static constexpr int K0 = K0_, H = H_, OUT = OUT_, NL = NL_;
+    static constexpr int K0 = K0_, H = H_, OUT = OUT_, NL = NL_, K0V = K0V_;
     static_assert(K0 % 16 == 0 && H % 16 == 0 && OUT % 8 == 0, "dims must fit m16n8k16 tiles");
+    static_assert(K0V % 8 == 0 && K0V > 0 && K0V <= K0, "valid input columns come in 16-byte chunks");
     static_assert(NL >= 1 && NL <= NB_MAX_LAYERS, "layer count");
     __host__ __device__ static constexpr int in_dim(int l) { return l == 0 ? K0 : H; }
+    __host__ __device__ static constexpr int in_dim_global(int l) { return l == 0 ? K0V : H; }
     __host__ __device__ static constexpr int out_dim(int l) { return l == NL - 1 ? OUT : H; }
     // rows of layer l in the shared copy: the last layer is padded to 16 rows of zeros when OUT == 8 so
     // a 16-deep k chunk over the output dimension (backward) never reads past the layer
     __host__ __device__ static constexpr int out_rows_padded(int l) { return out_dim(l) < 16 ? 16 : out_dim(l); }
     __host__ __device__ static constexpr int w_off(int l) {
         int o = 0;
-        for (int i = 0; i < l; i++) o += in_dim(i) * out_dim(i);
+        for (int i = 0; i < l; i++) o += in_dim_global(i) * out_dim(i);
         return o;
     }
     __host__ __device__ static constexpr int b_off(int l) {
@@ -52,11 +56,12 @@ struct MlpShape {
 template <class S, int L>
 __device__ __forceinline__ void load_layer_weights(const __half* __restrict__ W, __half* sW, int tid) {
     if constexpr (L < S::NL) {
-        constexpr int K = S::in_dim(L), N = S::out_dim(L), NP = S::out_rows_padded(L);
+        constexpr int K = S::in_dim(L), KG = S::in_dim_global(L), N = S::out_dim(L), NP = S::out_rows_padded(L);
         constexpr int CPR = K / 8;  // 16-byte chunks per row
         for (int c = tid; c < NP * CPR; c += CTA_THREADS) {
             int r = c / CPR, c8 = c % CPR;
-            cp_async16(&sW[S::sw_off(L) + r * (K + 8) + c8 * 8], &W[S::w_off(L) + r * K + c8 * 8], r < N);
+            const bool valid = r < N && c8 * 8 < KG;   // rows past the layer and columns past the real input are zero
+            cp_async16(&sW[S::sw_off(L) + r * (K + 8) + c8 * 8], valid ? &W[S::w_off(L) + r * KG + c8 * 8] : W, valid);
         }
         load_layer_weights<S, L + 1>(W, sW, tid);
     }

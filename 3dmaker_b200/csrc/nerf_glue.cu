@@ -135,6 +135,19 @@ __global__ void __launch_bounds__(256) mse_rays_kernel(const float* __restrict__
     }
 }
 
+// Samples as they travel from the host - position float3, target colour three halves - into the layouts the field
+// kernels read: position float4 (w = 0), target eight halves (3 valid, 5 zero).  One thread per sample.
+__global__ void __launch_bounds__(256) unpack_samples_kernel(const float* __restrict__ pos3, const __half* __restrict__ tgt3, int64_t n,
+                                                             float4* __restrict__ pos4, uint4* __restrict__ tgt8) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (pos4 != nullptr) pos4[i] = make_float4(pos3[3 * i], pos3[3 * i + 1], pos3[3 * i + 2], 0.0f);
+    if (tgt8 != nullptr) {
+        const unsigned short* t = reinterpret_cast<const unsigned short*>(tgt3) + 3 * i;
+        tgt8[i] = make_uint4((uint32_t)t[0] | ((uint32_t)t[1] << 16), (uint32_t)t[2], 0u, 0u);
+    }
+}
+
 // Frame assembly of pixel-sharded rendering: pixel p of the frame belongs to tile p / tile, which rank (tile index %
 // ranks) rendered as its (tile index / ranks)-th tile; blocks holds every rank's tiles back to back, rows_per_rank
 // pixels per rank.  One float per thread (3 per pixel), coalesced on the frame side and within a tile on the block side.
@@ -162,6 +175,20 @@ extern "C" int nb_undeal_tiles(const float* d_blocks, int ranks, int64_t rows_pe
     if (num_pixels == 0) return NB_OK;
     undeal_tiles_kernel<<<(unsigned)((num_pixels * 3 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_blocks, ranks, rows_per_rank, tile, num_pixels,
                                                                                                     d_frame);
+    NB_CHECK_LAUNCH();
+    g_launch_count++;
+    return NB_OK;
+}
+
+extern "C" int nb_unpack_samples(const float* d_pos3, const void* d_target3_h, int64_t n, float* d_pos4, void* d_target8_h, void* stream) {
+    if (n < 0 || (d_pos4 != nullptr && d_pos3 == nullptr) || (d_target8_h != nullptr && d_target3_h == nullptr))
+        return nb_set_error(NB_ERR_INVALID, "nb_unpack_samples: an output without its input, or a negative count");
+    if ((reinterpret_cast<uintptr_t>(d_pos4) & 15u) || (reinterpret_cast<uintptr_t>(d_target8_h) & 15u) || (reinterpret_cast<uintptr_t>(d_target3_h) & 1u) ||
+        (reinterpret_cast<uintptr_t>(d_pos3) & 3u))
+        return nb_set_error(NB_ERR_INVALID, "nb_unpack_samples: misaligned device pointer");
+    if (n == 0 || (d_pos4 == nullptr && d_target8_h == nullptr)) return NB_OK;
+    unpack_samples_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_pos3, (const __half*)d_target3_h, n, (float4*)d_pos4,
+                                                                                         (uint4*)d_target8_h);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

@@ -12,13 +12,28 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdio>
 #include <functional>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
 #include "TinyMLPHashGrid.h"
 
 #define MAX_HITS 1024  // per-ray sample cap
+
+// Programs written against the reference's InstantNerf.h use this macro for their own CUDA calls; as there
+// (modules/NeRF/InstantNerf.h:13-22) a failed call prints where it happened and throws std::runtime_error.
+#ifndef CUDA_CHECK
+#define CUDA_CHECK(call)                                                                                  \
+    do {                                                                                                  \
+        cudaError_t nb_cuda_check_status_ = (call);                                                       \
+        if (nb_cuda_check_status_ != cudaSuccess) {                                                       \
+            std::fprintf(stderr, "CUDA error at %s:%d: %s\n", __FILE__, __LINE__, cudaGetErrorString(nb_cuda_check_status_)); \
+            throw std::runtime_error(cudaGetErrorString(nb_cuda_check_status_));                          \
+        }                                                                                                 \
+    } while (0)
+#endif
 
 enum MemoryMode { TRAINING, INFERENCE };
 

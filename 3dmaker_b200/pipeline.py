@@ -85,10 +85,14 @@ class SampleTrainer:
     """One optimizer step on explicit samples (position, view direction, target colour):
     the 'encode + MLP fwd/bwd + Adam' step of the benchmark.  Buffers are sized once for max_batch."""
 
-    def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0, fused=None, fused_scatter=None):
+    def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0, fused=None, fused_scatter=None,
+                 ordered=None):
         """fused=None picks the two-kernel field path (nb_field_forward / nb_field_backward) when it is built for
         the model's shapes, else the kernel-by-kernel sequence; True / False force one of them.  fused_scatter
-        (default: on with the fused path) lets the backward kernel scatter the table gradient itself."""
+        (default: on with the fused path) lets the backward kernel scatter the table gradient itself.  ordered
+        (default: off) sorts the samples of every step by brick first (nb_sample_order) and runs the field kernels in
+        that order (nb_field_forward_ordered / nb_field_backward_ordered); measured on uniformly scattered samples it
+        does not pay - the eleven hashed levels, whose entries have no locality in any order, set the pace."""
         torch = model.torch
         self.model, self.torch, self.lib = model, torch, model.lib
         self.max_batch = max_batch
@@ -98,6 +102,7 @@ class SampleTrainer:
             raise nb.NerfB200Error("the fused field kernels are not built for these network shapes")
         self.fused = supported if fused is None else bool(fused)
         self.fused_scatter = self.fused if fused_scatter is None else (bool(fused_scatter) and self.fused)
+        self.ordered = False if ordered is None else (bool(ordered) and self.fused)
         n, dev = max_batch, "cuda"
         d, c = model.density, model.color
         f16, f32 = torch.float16, torch.float32
@@ -110,6 +115,9 @@ class SampleTrainer:
         self.c_grad = torch.zeros((n, 8), dtype=f16, device=dev)
         self.d_enc = torch.zeros((n, d.input_dim), dtype=f16, device=dev)
         self.loss = torch.zeros(1, dtype=f32, device=dev)
+        if self.ordered:
+            self.order = torch.zeros(n, dtype=torch.int32, device=dev)
+            self.order_scratch = torch.zeros(int(self.lib.nb_sample_order_scratch_bytes()) // 4, dtype=torch.int32, device=dev)
         if self.fused:
             self.logit0 = torch.zeros(n, dtype=f32, device=dev)
         else:
@@ -128,7 +136,24 @@ class SampleTrainer:
         if n > self.max_batch:
             raise nb.NerfB200Error("batch exceeds max_batch")
         nb.check(lib.nb_zero_async(P(self.loss), 4, st), "nb_zero_async")
-        if self.fused:
+        if self.fused and self.ordered:
+            gs = ctypes.byref(m.grid) if self.fused_scatter else None
+            nb.check(lib.nb_sample_order(P(self.pos), n, P(self.order), P(self.order_scratch), st), "nb_sample_order")
+            nb.check(lib.nb_field_forward_ordered(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(self.pos), m.ptr("w_h", 0),
+                                                  P(self.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
+                                                  m.ptr("w", m.off_cb), n, P(self.order), self.density_bias, P(self.enc), P(self.sigma),
+                                                  P(self.logit0), P(self.c_out), 8, st), "nb_field_forward_ordered")
+            nb.check(lib.nb_mse_loss_grad(P(self.c_out), P(self.target), P(self.c_grad), P(self.loss), n, 8, 3, self.loss_scale, 1, st),
+                     "nb_mse_loss_grad")
+            nb.check(lib.nb_field_backward_ordered(ctypes.byref(m.density), ctypes.byref(m.color), P(self.enc), P(self.dirs), None, 0,
+                                                   m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
+                                                   P(self.order), P(self.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db),
+                                                   m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(self.d_enc), gs,
+                                                   P(self.pos) if self.fused_scatter else None, m.ptr("g", 0) if self.fused_scatter else None, st),
+                     "nb_field_backward_ordered")
+            if self.fused_scatter:
+                return
+        elif self.fused:
             nb.check(lib.nb_field_forward(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(self.pos), m.ptr("w_h", 0),
                                           P(self.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
                                           m.ptr("w", m.off_cb), n, self.density_bias, P(self.enc), P(self.sigma), P(self.logit0),
@@ -160,6 +185,15 @@ class SampleTrainer:
                                          m.ptr("g", m.off_dw), m.ptr("g", m.off_db), P(self.d_enc), st), "nb_mlp_backward(density)")
         nb.check(lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(self.pos), P(self.d_enc), n, m.ptr("g", 0), st),
                  "nb_hash_scatter_backward")
+
+    def encoded(self, n):
+        """The encoded features the last forward saved, in SAMPLE order (the ordered kernels keep them in the order they
+        visited the samples).  For tests; allocates."""
+        if not (self.fused and self.ordered):
+            return self.enc[:n]
+        out = self.torch.empty_like(self.enc[:n])
+        out[self.order[:n].long()] = self.enc[:n]
+        return out
 
     def optimizer_step(self, stream=None):
         """Fused Adam over the whole arena; bias corrections as TinyMLPHashGrid::step (step counter capped at 50000)."""
@@ -251,8 +285,12 @@ class SampleTrainer:
     # ---- pipelined host input: the copy of the next batch overlaps the step on the current one -----------------
     def prefetch(self, pos4, dirs3, target_h8):
         """Enqueues the host->device copy of one batch (pinned tensors) on a copy stream into the input slot that
-        the running step is not using.  Pair every call with one step_prefetched()."""
+        the running step is not using.  Pair every call with one step_prefetched().  The batch comes either in the
+        kernels' own layouts (positions [n, 4] float32, targets [n, 8] float16: 44 bytes per sample with the directions) or
+        compact (positions [n, 3], targets [n, 3]: 30 bytes), in which case nb_unpack_samples widens it on the device,
+        on the copy stream."""
         torch = self.torch
+        compact = pos4.shape[1] == 3
         if not hasattr(self, "_slots"):
             self._copy_stream = torch.cuda.Stream()
             self._slots = [(self.pos, self.dirs, self.target),
@@ -265,7 +303,17 @@ class SampleTrainer:
         with torch.cuda.stream(self._copy_stream):
             self._copy_stream.wait_event(self._free[k])      # the step that last read this slot has finished
             p, d, t = self._slots[k]
-            p[:n].copy_(pos4, non_blocking=True); d[:n].copy_(dirs3, non_blocking=True); t[:n].copy_(target_h8, non_blocking=True)
+            d[:n].copy_(dirs3, non_blocking=True)
+            if compact:
+                if not hasattr(self, "_compact"):
+                    self._compact = [(torch.empty((self.max_batch, 3), dtype=torch.float32, device=p.device),
+                                      torch.empty((self.max_batch, 3), dtype=torch.float16, device=p.device)) for _ in range(2)]
+                p3, t3 = self._compact[k]
+                p3[:n].copy_(pos4, non_blocking=True); t3[:n].copy_(target_h8, non_blocking=True)
+                nb.check(self.lib.nb_unpack_samples(nb.ptr(p3), nb.ptr(t3), n, nb.ptr(p), nb.ptr(t), nb.stream_ptr(self._copy_stream)),
+                         "nb_unpack_samples")
+            else:
+                p[:n].copy_(pos4, non_blocking=True); t[:n].copy_(target_h8, non_blocking=True)
             self._ready[k].record(self._copy_stream)
         self._queued.append((k, n))
         self._next = 1 - k

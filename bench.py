@@ -329,7 +329,28 @@ def time_kernels(torch, tr, n, iters=5):
     nb = importlib.import_module("3dmaker_b200")
     m, lib, P = tr.model, tr.lib, nb.ptr
     st = nb.stream_ptr()
-    if tr.fused:
+    if tr.fused and tr.ordered:
+        # the step as it runs: brick order of the samples, then the two field kernels in that order
+        calls = {
+            "sample_order": lambda: lib.nb_sample_order(P(tr.pos), n, P(tr.order), P(tr.order_scratch), st),
+            "field_forward": lambda: lib.nb_field_forward_ordered(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(tr.pos),
+                                                                  m.ptr("w_h", 0), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db),
+                                                                  m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, P(tr.order), tr.density_bias,
+                                                                  P(tr.enc), P(tr.sigma), P(tr.logit0), P(tr.c_out), 8, st),
+            "mse_loss_grad": lambda: lib.nb_mse_loss_grad(P(tr.c_out), P(tr.target), P(tr.c_grad), P(tr.loss), n, 8, 3, tr.loss_scale, 1, st),
+            "field_backward": lambda: lib.nb_field_backward_ordered(ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0,
+                                                                    m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
+                                                                    m.ptr("w", m.off_cb), n, P(tr.order), P(tr.c_grad), None, m.ptr("g", m.off_dw),
+                                                                    m.ptr("g", m.off_db), m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc),
+                                                                    None, None, None, st),
+            "scatter_backward": lambda: lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(tr.pos), P(tr.d_enc), n, m.ptr("g", 0), st),
+        }
+        if tr.fused_scatter:
+            calls["field_backward_scatter"] = lambda: lib.nb_field_backward_ordered(
+                ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db),
+                m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, P(tr.order), P(tr.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db),
+                m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc), ctypes.byref(m.grid), P(tr.pos), m.ptr("g", 0), st)
+    elif tr.fused:
         calls = {
             "field_forward": lambda: lib.nb_field_forward(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(tr.pos),
                                                           m.ptr("w_h", 0), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db),
@@ -397,6 +418,29 @@ ALGO_BYTES = {"grid_mlp_forward": 592.0, "field_forward": 644.0, "scatter_backwa
 NCU_TRAFFIC = {"field_forward": 120.3e6, "field_backward_scatter": 192.9e6}
 
 
+def bind_to_gpu_numa_node(torch, local_rank):
+    """Several ranks on one host: keeps this process (and so the pinned staging buffers it allocates next: first touch)
+    on the NUMA node its GPU hangs off, so that eight ranks do not pull their input through one socket.  Best effort;
+    returns the node or None."""
+    try:
+        p = torch.cuda.get_device_properties(local_rank)
+        bus = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % bus).read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -424,15 +468,17 @@ def run_ours(args, rank, world, local_rank):
         buffers.register()
     table, dW, db, cW, cb = init_params()
     model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
-    tr = pl.SampleTrainer(model, BATCH, fused=False if args.unfused else None, fused_scatter=False if args.separate_scatter else None, **HYPER)
+    tr = pl.SampleTrainer(model, BATCH, fused=False if args.unfused else None, fused_scatter=False if args.separate_scatter else None,
+                          ordered=True if args.ordered else None, **HYPER)
 
-    # two distinct seeded batches per rank, pinned on the host and resident on the device
+    # two distinct seeded batches per rank: resident on the device in the kernels' layouts (`value`), and pinned on the
+    # host in the compact layout they travel in (`e2e`: position float3, direction float3, target three halves = 30 B)
+    numa_node = bind_to_gpu_numa_node(torch, local_rank) if world > 1 else None
     host, dev = [], []
     for k in range(2):
         pos, dirs, tgt = make_batch(BATCH, 1000 + 10 * rank + k)
-        hp = tuple(torch.from_numpy(a).pin_memory() for a in (pos, dirs, tgt))
-        host.append(hp)
-        dev.append(tuple(t.cuda() for t in hp))
+        dev.append(tuple(torch.from_numpy(a).cuda() for a in (pos, dirs, tgt)))
+        host.append(tuple(torch.from_numpy(np.ascontiguousarray(a)).pin_memory() for a in (pos[:, :3], dirs, tgt[:, :3])))
     own = (tr.pos, tr.dirs, tr.target)
 
     grad_sync = None
@@ -531,8 +577,10 @@ def run_ours(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": common_config(world),
-            "notes": {"exchange": None if world == 1 else args.dp, "field_kernels": ("fused+scatter" if tr.fused_scatter else "fused") if tr.fused else "sequence",
-                      "tuning": args.tune},
+            "notes": {"exchange": None if world == 1 else args.dp,
+                      "field_kernels": (("fused+scatter" if tr.fused_scatter else "fused") + ("+ordered" if tr.ordered else "")) if tr.fused else "sequence",
+                      "tuning": args.tune, "host_batch_layout": "pos float3 + dir float3 + target half3 (30 B/sample), widened on the device",
+                      "numa_node": numa_node},
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "last_loss": loss},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernel_ms": kt,
@@ -899,6 +947,7 @@ def main():
     ap.add_argument("--render-rounds", action="store_true", help="render workload: render in rounds of samples per ray (A/B; off by default)")
     ap.add_argument("--plain-buffers", action="store_true", help="N > 1: keep the gradient in ordinary device memory instead of memory "
                     "registered with the communicator (A/B)")
+    ap.add_argument("--ordered", action="store_true", help="sort every batch by brick and run the field kernels in that order (A/B; off by default)")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")
     args = ap.parse_args()

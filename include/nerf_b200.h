@@ -171,6 +171,11 @@ int nb_sh_gather(const float* d_dirs3, const uint32_t* d_ray_indices, int64_t of
  * d_density_grad_h fp16 [n][16], clamped to +-65504, NaN -> 0. */
 int nb_density_grad(int64_t n, const float* d_tmp_dsigma, const void* d_color_dx_h, void* d_density_grad_h, void* stream);
 
+/* Samples in their compact host layout - position float3, target colour three halves: 18 bytes where the kernels' own
+ * layouts take 32 - into position float4 (w = 0) and target eight halves (channels 3..7 zero), the job of the
+ * reference's hg_pad kernels and fusedPadAndCastKernel (TinyMLPHashGrid.cu:11-34, TinyMLP.cu:23-45).  Either pair may
+ * be NULL.  Lets a training loop that feeds samples from the host move 30 instead of 44 bytes per sample over PCIe. */
+int nb_unpack_samples(const float* d_pos3, const void* d_target3_h, int64_t n, float* d_pos4, void* d_target8_h, void* stream);
 /* Replaces generate_custom_rays_kernel (modules/NeRF/NerfTrainer.cu:25-47): pinhole rays of pixels
  * [first_pixel, first_pixel + count) of a width x height frame; c2w_3x4 is a HOST pointer to the row-major 3x4
  * camera-to-world matrix.  The pixel range is what pixel-sharded rendering splits across ranks. */
@@ -215,6 +220,41 @@ int nb_field_forward_counted(const nb_grid_desc* grid, const nb_mlp_desc* densit
                              const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
                              int64_t n_max, const uint32_t* d_count, float density_bias, float* d_sigma, float* d_rgb, int rgb_stride,
                              void* stream);
+
+/* ---- samples in spatial order ---------------------------------------------------------------------------------
+ * The reference keeps a Morton ordering of the samples in its legacy march (morton keys from the sample position and a
+ * radix sort, modules/NeRF/processRays.cu:70-81,412-448); its field kernels take samples in whatever order they come.
+ * Here the order is an input of the field kernels: neighbouring samples share their corners on the coarser levels, and a
+ * CTA that works on neighbours keeps those corners' boxes in shared memory instead of going to L2 for each of them.
+ *
+ * nb_sample_order: d_order[k] = the k-th sample when the samples are listed brick by brick, the 16^3 bricks of the unit
+ * cube in Morton order (a counting sort over 12-bit keys; samples of one brick in no particular order).  d_scratch:
+ * nb_sample_order_scratch_bytes() bytes, 16-byte aligned.  Positions outside [0, 1] count for the nearest brick. */
+int64_t nb_sample_order_scratch_bytes(void);
+int nb_sample_order(const float* d_pos4, int64_t n, uint32_t* d_order, void* d_scratch, void* stream);
+
+/* nb_field_forward visiting the samples in the order d_order (any permutation of 0 .. n-1; nb_sample_order's makes it
+ * fast): persistent CTAs take groups of four consecutive 128-row tiles, copy the boxes of the leading levels that the
+ * group's positions span into shared memory (as many levels as fit 24 KB) and gather those levels from there.  Results
+ * are identical to nb_field_forward's, sample by sample: d_sigma, d_logit0 and d_rgb are indexed by SAMPLE; only
+ * d_enc_save_h is in ROW order (row k = sample d_order[k]), which is what nb_field_backward_ordered expects.
+ * nb_set_tuning("forward_staged", 1) makes nb_field_forward itself use this kernel (rows = samples); 0 switches it off. */
+int nb_field_forward_ordered(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                             const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                             const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
+                             const uint32_t* d_order, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
+                             int rgb_stride, void* stream);
+
+/* nb_field_backward for the same order: d_enc_h in ROW order as nb_field_forward_ordered saved it, d_dcolor_h, d_dsigma,
+ * d_pos4 and d_denc_h by SAMPLE.  Always the tensor-memory kernel; its scatter warps visit the rows in the given order, so
+ * that the reductions of neighbouring samples on the coarser levels meet in the same L2 sectors.  Gradients agree with
+ * nb_field_backward's to fp32 summation order. */
+int nb_field_backward_ordered(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,
+                              const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h, const float* d_density_b,
+                              const void* d_color_w_h, const float* d_color_b, int64_t n, const uint32_t* d_order, const void* d_dcolor_h,
+                              const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b, float* d_grad_color_w,
+                              float* d_grad_color_b, void* d_denc_h, const nb_grid_desc* grid, const float* d_pos4, float* d_table_grads,
+                              void* stream);
 
 /* Gradients of both networks, of the encoding and (optionally) of the hash table from the colour gradient.  Replaces
  * TinyMLP::backward (colour) -> compute_density_grad -> TinyMLPHashGrid::backward (modules/NeRF/InstantNerf.cu:506-561).

@@ -75,11 +75,58 @@ def build(ref_root, verbose=True):
     return OUT
 
 
+# The reference's own test programs, compiled UNMODIFIED against this repository's host classes instead of the
+# reference's: (program name, module, path inside the module, the headers it reaches through "../").
+COMPAT_TESTS = [("ref_testModes", "TinyMLP", os.path.join("tests_kernels", "testModes.cu"), ["TinyMLP.h", "TinyMLPHashGrid.h"]),
+                ("ref_test_loading", "NeRF", os.path.join("test_kernels", "test_loading.cu"), ["InstantNerf.h"])]
+
+
+def build_compat_tests(ref_root, verbose=True):
+    """Source compatibility of 3dmaker_b200/host/*.h, shown with the reference's own programs: each test source is
+    reached through a symbolic link placed in a scratch tree under oracle/_ref/compat/ whose parent directory holds
+    one-line headers forwarding to this repository's classes, so the program's `#include "../TinyMLP.h"` finds OUR
+    header; nothing of the reference is copied or edited.  The programs link against libnerf_b200.so (built first) and
+    are run on the GPU by tests/test_gpu_host_classes.py."""
+    repo = os.path.dirname(HERE)
+    host = os.path.join(repo, "3dmaker_b200", "host")
+    libdir = os.path.join(repo, "3dmaker_b200")
+    if not os.path.exists(os.path.join(libdir, "libnerf_b200.so")):
+        return []
+    built = []
+    for exe, module, rel, headers in COMPAT_TESTS:
+        src = os.path.join(ref_root, "modules", module, rel)
+        if not os.path.exists(src):
+            continue
+        mod_dir = os.path.join(OUT, "compat", module)
+        link = os.path.join(mod_dir, rel)
+        os.makedirs(os.path.dirname(link), exist_ok=True)
+        if os.path.islink(link) or os.path.exists(link):
+            os.remove(link)
+        os.symlink(src, link)
+        for h in headers:
+            with open(os.path.join(mod_dir, h), "w") as f:
+                f.write('#include "%s"\n' % os.path.join(host, h))
+        out = os.path.join(OUT, exe)
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O2", "-w", link, "-o", out, "-I", os.path.join(repo, "include"),
+               "-L", libdir, "-lnerf_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../3dmaker_b200"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("the reference's %s does not compile against 3dmaker_b200/host:\n%s" % (rel, r.stderr[-3000:]))
+        built.append(out)
+    # the scratch tree held only links and forwarding headers; the programs are what travels
+    shutil.rmtree(os.path.join(OUT, "compat"), ignore_errors=True)
+    if verbose:
+        print("compatibility programs:", ", ".join(os.path.basename(b) for b in built))
+    return built
+
+
 def build_if_reference_present(ref_root=None):
     """Called by __graft_entry__.build(): a no-op where the reference tree is absent (the GPU box)."""
     ref_root = ref_root or os.environ.get("REFERENCE_ROOT")
     if ref_root and all(os.path.isdir(d) for d in _dirs(ref_root)):
-        return build(ref_root, verbose=False)
+        out = build(ref_root, verbose=False)
+        build_compat_tests(ref_root, verbose=False)
+        return out
     return None
 
 
@@ -88,3 +135,4 @@ if __name__ == "__main__":
     if not root:
         raise SystemExit("usage: python oracle/build_ref.py <reference tree>   (or set REFERENCE_ROOT)")
     build(root)
+    build_compat_tests(root)

@@ -24,6 +24,7 @@ _SIG = {
     "ref_field_train_step": (None, [V, V, V, V, I, F, F, F, F, F, F, V]),
     "ref_field_grid_activation": (V, [V, I]),
     "ref_field_step": (None, [V, F, F, F, F, F, V]),
+    "ref_nerf_set_learning_rate": (None, [V, F]),
     "ref_nerf_save": (I, [V, ctypes.c_char_p]),
     "ref_nerf_load": (I, [V, ctypes.c_char_p]),
     "ref_volume_rendering_priors": (None, [U, V, V, V, V, V, V, V, V, V, V, V, V, V, F, F, V, V]),

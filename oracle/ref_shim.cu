@@ -209,6 +209,7 @@ int ref_nerf_load(void* h, const char* path) {
     try { ((InstantNerf*)h)->load(path); } catch (const std::exception& e) { std::fprintf(stderr, "ref_nerf_load: %s\n", e.what()); return 1; }
     return 0;
 }
+void ref_nerf_set_learning_rate(void* h, float lr) { ((InstantNerf*)h)->setLearningRate(lr); }
 void ref_nerf_set_memory_mode(void* h, int mode) { ((InstantNerf*)h)->setMemoryMode(mode == 1 ? INFERENCE : TRAINING); }
 
 // scratch buffers of the last step, by name index (parity tests)

@@ -1,11 +1,13 @@
 """Generates tests/golden/psnr_runs.json: PSNR of this engine and of the reference's InstantNerf (oracle/_ref build)
 after a fixed number of optimizer steps on the analytic soft-sphere scene, several paired runs.
 
-    python tests/golden/make_psnr_runs.py [--runs 16] [--steps 2000] [--out DIR]
+    python tests/golden/make_psnr_runs.py [--runs 16] [--steps 2000] [--schedule cosine|constant] [--out DIR]
 
 Protocol (the single-GPU training configuration of the benchmark: 100 cameras 800x800, 128^3 occupancy grid with one
-cascade, T = 2^19, growth 1.3819, batch 2^18 samples, 65536-ray chunks, Adam lr 1e-2 constant, beta = (0.9, 0.99),
-eps 1e-15, distortion weight 0.1, loss scale 128, white background): run k draws its training rays from seeds
+cascade, T = 2^19, growth 1.3819, batch 2^18 samples, 65536-ray chunks, Adam beta = (0.9, 0.99), eps 1e-15, distortion
+weight 0.1, loss scale 128, white background; learning rate 1e-2 annealed to 1e-3 over the run by the half cosine of
+the reference's own trainer, INerfTrainer::currentLR, NerfTrainer.cu:131-135, set before every call - or held at 1e-2
+with --schedule constant, where either engine ends anywhere within several dB): run k draws its training rays from seeds
 10000 k + call index, the SAME rays go to both engines call by call, both start from the parameters their
 constructors draw from std::mt19937(42) (identical, checked), training stops at the first call boundary at or past
 `steps` optimizer steps, and the PSNR is the mean over four held-out 200x200 views against the analytic ground truth.
@@ -14,6 +16,7 @@ import argparse
 import ctypes
 import importlib
 import json
+import math
 import os
 import sys
 import time
@@ -38,6 +41,8 @@ def main():
     ap.add_argument("--runs", type=int, default=16)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--lambda-dist", type=float, default=OPTIONS["lambda_dist"])
+    ap.add_argument("--schedule", default="cosine", choices=["cosine", "constant"])
+    ap.add_argument("--name", default="psnr_runs.json", help="file name of the fixture")
     ap.add_argument("--out", default=None, help="also copy the file into this directory")
     args = ap.parse_args()
     import torch
@@ -61,12 +66,21 @@ def main():
         eng = nm.InstantNerf(torch, opts)
         rh = lib.ref_nerf_create(ctypes.byref(opts), 0)
         ref_steps, call = 0, 0
+
+        def lr_at(step):
+            if args.schedule == "constant":
+                return 1e-2
+            x = min(step / float(args.steps), 1.0)
+            return 1e-3 + 0.5 * (1e-2 - 1e-3) * (1.0 + math.cos(math.pi * x))
+
         while eng.steps.value < args.steps or ref_steps < args.steps:
             o, d = syn.random_training_rays(torch, poses, R, 800, 800, 50.0, seed=10000 * k + call)
             tgt = syn.ground_truth(torch, scene, o, d, bg)
             if eng.steps.value < args.steps:
+                eng.set_learning_rate(lr_at(eng.steps.value))
                 eng.train_rays(o, d, tgt)
             if ref_steps < args.steps:
+                lib.ref_nerf_set_learning_rate(rh, lr_at(ref_steps))
                 ref_steps += lib.ref_nerf_train(rh, nb.ptr(o), nb.ptr(d), nb.ptr(depth), nb.ptr(sig), nb.ptr(tgt), R, None, None, st)
             call += 1
         torch.cuda.synchronize()
@@ -84,16 +98,16 @@ def main():
               flush=True)
         eng.close()
         lib.ref_nerf_destroy(rh)
-    doc = {"protocol": {"steps": args.steps, "views": list(VIEWS), "view_size": [200, 200], "rays_per_call": R,
+    doc = {"protocol": {"steps": args.steps, "schedule": args.schedule, "views": list(VIEWS), "view_size": [200, 200], "rays_per_call": R,
                         "options": {k: (list(v) if isinstance(v, tuple) else v) for k, v in dict(OPTIONS, lambda_dist=args.lambda_dist).items()},
                         "device": torch.cuda.get_device_name(0)},
            "runs": runs}
-    path = os.path.join(HERE, "psnr_runs.json")
+    path = os.path.join(HERE, args.name)
     with open(path, "w") as f:
         json.dump(doc, f, indent=1)
     if args.out:
         os.makedirs(args.out, exist_ok=True)
-        with open(os.path.join(args.out, "psnr_runs.json"), "w") as f:
+        with open(os.path.join(args.out, args.name), "w") as f:
             json.dump(doc, f, indent=1)
     d = np.array([r["ours_db"] - r["reference_db"] for r in runs])
     print("paired difference ours - reference: mean %.3f dB, sd %.3f, n %d" % (d.mean(), d.std(ddof=1) if len(d) > 1 else 0.0, len(d)))

@@ -24,3 +24,22 @@ def test_cpp_host_classes(cuda, tmp_path):
     print(r.stdout[-3000:])
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
     assert "[SUCCESS] all host-class checks passed" in r.stdout
+
+
+@pytest.mark.parametrize("program,needle", [("ref_testModes", "passed"), ("ref_test_loading", "All tests passed!")])
+def test_reference_test_programs_run_against_these_classes(cuda, tmp_path, program, needle):
+    """The reference's own tests_kernels/testModes.cu (mode switching: training methods throw in inference mode) and
+    test_kernels/test_loading.cu (train, save, load into a fresh engine, render), compiled UNMODIFIED against
+    3dmaker_b200/host/*.h by oracle/build_ref.py and linked to libnerf_b200.so: the classes are a source-level drop-in."""
+    exe = os.path.join(ROOT, "oracle", "_ref", program)
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/%s not built (the reference tree was absent at build time)" % program)
+    env = dict(os.environ, LD_LIBRARY_PATH=os.path.join(ROOT, "3dmaker_b200") + os.pathsep + os.environ.get("LD_LIBRARY_PATH", ""))
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600, cwd=str(tmp_path), env=env)
+    print(r.stdout[-2000:])
+    assert needle.lower() in r.stdout.lower(), r.stdout[-2000:] + r.stderr[-2000:]
+    # test_loading.cu hands trainWithRaysHit a ONE-entry hitCounts vector for a call that takes many optimizer steps; the
+    # engine writes one entry per step, as the reference's does (InstantNerf.cu:430-432), so the program's own heap is
+    # damaged and glibc may abort it when the vector is freed - after every check has passed and been printed.
+    own_heap_bug = program == "ref_test_loading" and r.returncode == -6 and "free()" in r.stderr
+    assert r.returncode == 0 or own_heap_bug, r.stdout[-2000:] + r.stderr[-2000:]

@@ -44,7 +44,7 @@ def test_sample_training_step_matches_oracle(cuda, nb, orc, n, fused):
     sscales = np.array(list(model.grid.scatter_scales)[:L], np.float32)
     ref = OracleField(L, T, 16, 1.447, scales, model.grid.dense_level_start, (32, 64, 16, 2), (32, 64, 8, 3), table, dW, db, cW, cb, sscales)
     r = ref.forward_backward(pos, dirs, tgt, 128.0)
-    assert np.array_equal(dev_half_bits(tr.enc), r["enc"])
+    assert np.array_equal(dev_half_bits(tr.encoded(n)), r["enc"])
     if fused:
         assert rel_err(tr.logit0.cpu().numpy(), r["d_out"][:, 0]) <= REL_MLP
     else:
@@ -113,7 +113,8 @@ def test_fused_field_kernels_agree_with_the_kernel_sequence(cuda, nb, n):
     model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
     pos, dirs, tgt = _inputs(n, 11)
     out = {}
-    modes = {"sequence": dict(fused=False), "fused": dict(fused=True, fused_scatter=False), "fused+scatter": dict(fused=True, fused_scatter=True)}
+    modes = {"sequence": dict(fused=False), "fused": dict(fused=True, fused_scatter=False),
+             "fused+scatter": dict(fused=True, fused_scatter=True, ordered=False)}
     # the bit-for-bit claims hold for the mma.sync backward, which accumulates in the sequence's order; the tensor-memory
     # backward (the default) has its own test below
     nb.check(nb.load().nb_set_tuning(b"backward_tc", 0), "nb_set_tuning")
@@ -123,7 +124,7 @@ def test_fused_field_kernels_agree_with_the_kernel_sequence(cuda, nb, n):
         model.g.zero_()
         tr.forward_backward(n)
         torch.cuda.synchronize()
-        out[name] = dict(enc=dev_half_bits(tr.enc), sigma=tr.sigma.cpu().numpy(), c_out=tr.c_out.cpu().numpy()[:, :3].copy(),
+        out[name] = dict(enc=dev_half_bits(tr.encoded(n)), sigma=tr.sigma.cpu().numpy(), c_out=tr.c_out.cpu().numpy()[:, :3].copy(),
                          logit=(tr.logit0 if tr.fused else tr.d_out[:, 0]).cpu().numpy(), d_enc=dev_half_bits(tr.d_enc), g=model.g.cpu().numpy().copy(),
                          loss=tr.loss.item())
     model.g.zero_()
@@ -211,7 +212,7 @@ def test_tensor_memory_backward_agrees_with_the_register_formulation(cuda, nb, n
     try:
         for name, tcflag, fs in (("regs", 0, False), ("tc", 1, False), ("regs+scatter", 0, True), ("tc+scatter", 1, True)):
             nb.check(lib.nb_set_tuning(b"backward_tc", tcflag), "nb_set_tuning")
-            tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=fs)
+            tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=fs, ordered=False)
             tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
             model.g.zero_()
             tr.forward_backward(n)
@@ -243,7 +244,7 @@ def test_tensor_memory_backward_wait_that_runs_out_is_reported_and_recoverable(c
     model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
     model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
     pos, dirs, tgt = _inputs(n, 17)
-    tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=True)
+    tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=True, ordered=False)
     tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
     try:
         nb.check(lib.nb_set_tuning(b"backward_tc", 0), "nb_set_tuning")
@@ -297,3 +298,143 @@ def test_field_backward_with_8_byte_aligned_weight_gradients_uses_the_register_k
     torch.cuda.synchronize()
     assert rel_err(base[:dense].cpu().numpy(), want) <= 2e-3
     model.g.zero_()
+
+
+def _brick_keys(pos):
+    """12-bit Morton key of the 16^3 brick of every position (numpy restatement of the ordering's key)."""
+    q = np.clip(np.floor(pos[:, :3] * np.float32(16.0)).astype(np.int64), 0, 15)
+    spread = lambda v: (v & 1) | ((v & 2) << 2) | ((v & 4) << 4) | ((v & 8) << 6)
+    return spread(q[:, 0]) | (spread(q[:, 1]) << 1) | (spread(q[:, 2]) << 2)
+
+
+@pytest.mark.parametrize("n", [1, 255, 2048, 2049, 100000])
+def test_sample_order_is_a_permutation_sorted_by_brick(cuda, nb, n):
+    torch = cuda
+    lib, P = nb.load(), nb.ptr
+    pos = make_positions(n, 31)
+    pos[: min(n, 4), :3] = np.array([[0, 0, 0], [1, 1, 1], [-3.0, 0.5, 2.0], [0.999999, 0.0625, 0.5]], np.float32)[: min(n, 4)]
+    d_pos = torch.from_numpy(pos).cuda()
+    order = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(int(lib.nb_sample_order_scratch_bytes()) // 4, dtype=torch.int32, device="cuda")
+    for _ in range(2):                                   # the scratch is reused call after call
+        nb.check(lib.nb_sample_order(P(d_pos), n, P(order), P(scratch), nb.stream_ptr()), "nb_sample_order")
+    torch.cuda.synchronize()
+    o = order.cpu().numpy().astype(np.int64)
+    assert np.array_equal(np.sort(o), np.arange(n))      # every sample exactly once
+    keys = _brick_keys(pos)[o]
+    assert np.all(np.diff(keys) >= 0)                    # brick after brick, in Morton order
+
+
+@pytest.mark.parametrize("order_kind", ["bricks", "random", "identity"])
+@pytest.mark.parametrize("n", [1, 127, 513, 5000, 70000])
+def test_ordered_field_kernels_agree_with_the_unordered_ones(cuda, nb, n, order_kind):
+    """nb_field_forward_ordered / nb_field_backward_ordered against nb_field_forward / nb_field_backward on the same
+    inputs: the forward's outputs are identical bit for bit whatever the order (levels staged in shared memory hold the
+    same table entries), the saved encoding is the same rows permuted, and every gradient agrees to fp32 summation
+    order - with the brick order (boxes small, many levels staged), a random permutation (boxes cover the whole grid,
+    nothing or little staged) and the identity."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    lib, P = nb.load(), nb.ptr
+    L, T = 16, 1 << 15
+    model = pl.FieldModel(torch, L, T, 16, 1.447, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    pos, dirs, tgt = _inputs(n, 23)
+    if n > 8:
+        pos[:4, :3] = [[0, 0, 0], [1, 1, 1], [1.0, 0.0, 0.999999], [0.5, 0.5, 0.5]]
+    out = {}
+    try:
+        nb.check(lib.nb_set_tuning(b"backward_tc", 1), "nb_set_tuning")
+        for name in ("plain", "ordered"):
+            tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=True, ordered=(name == "ordered"))
+            tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+            model.g.zero_()
+            if name == "ordered" and order_kind != "bricks":
+                # drive the two ordered entry points with an order of our own
+                rng = np.random.default_rng(5)
+                o = rng.permutation(n) if order_kind == "random" else np.arange(n)
+                tr.order.copy_(torch.from_numpy(o.astype(np.int32)))
+                st, m = nb.stream_ptr(), model
+                nb.check(lib.nb_zero_async(P(tr.loss), 4, st))
+                nb.check(lib.nb_field_forward_ordered(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(tr.pos), m.ptr("w_h", 0),
+                                                      P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
+                                                      m.ptr("w", m.off_cb), n, P(tr.order), tr.density_bias, P(tr.enc), P(tr.sigma), P(tr.logit0),
+                                                      P(tr.c_out), 8, st), "nb_field_forward_ordered")
+                nb.check(lib.nb_mse_loss_grad(P(tr.c_out), P(tr.target), P(tr.c_grad), P(tr.loss), n, 8, 3, tr.loss_scale, 1, st))
+                nb.check(lib.nb_field_backward_ordered(ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0,
+                                                       m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
+                                                       P(tr.order), P(tr.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db), m.ptr("g", m.off_cw),
+                                                       m.ptr("g", m.off_cb), P(tr.d_enc), ctypes.byref(m.grid), P(tr.pos), m.ptr("g", 0), st),
+                         "nb_field_backward_ordered")
+            else:
+                tr.forward_backward(n)
+            nb.check(lib.nb_field_backward_tc_status(), "tensor-memory backward status")
+            out[name] = dict(enc=dev_half_bits(tr.encoded(n)), sigma=tr.sigma.cpu().numpy(), logit=tr.logit0.cpu().numpy(),
+                             c_out=tr.c_out.cpu().numpy().copy(), g=model.g.cpu().numpy().copy(), loss=tr.loss.item())
+    finally:
+        nb.check(lib.nb_set_tuning(b"backward_tc", 2), "nb_set_tuning")
+        model.g.zero_()
+    a, b = out["plain"], out["ordered"]
+    for k in ("enc", "sigma", "logit", "c_out"):
+        assert np.array_equal(a[k], b[k]), k
+    assert abs(a["loss"] - b["loss"]) <= 1e-5 * abs(a["loss"])
+    H = model.hash_count
+    assert rel_err(b["g"][:H], a["g"][:H]) <= 2e-3
+    assert np.mean((a["g"][:H] != 0) != (b["g"][:H] != 0)) < 1e-4
+    for off, cnt in ((model.off_dw, model.density.weight_count), (model.off_db, model.density.bias_count),
+                     (model.off_cw, model.color.weight_count), (model.off_cb, model.color.bias_count)):
+        assert rel_err(b["g"][off:off + cnt], a["g"][off:off + cnt]) <= 2e-3, off
+
+
+def test_ordered_backward_without_the_fused_scatter_writes_the_encoding_gradient_by_sample(cuda, nb):
+    """d_table_grads == NULL: dL/d(encoding) comes back as a matrix indexed by SAMPLE, ready for nb_hash_scatter_backward."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    lib = nb.load()
+    L, T, n = 16, 1 << 15, 3000
+    model = pl.FieldModel(torch, L, T, 16, 1.447, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    pos, dirs, tgt = _inputs(n, 29)
+    res = {}
+    try:
+        nb.check(lib.nb_set_tuning(b"backward_tc", 1), "nb_set_tuning")
+        for name, ordered in (("plain", False), ("ordered", True)):
+            tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, fused_scatter=False, ordered=ordered)
+            tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+            model.g.zero_()
+            tr.forward_backward(n)
+            torch.cuda.synchronize()
+            res[name] = (half_vals(dev_half_bits(tr.d_enc)), model.g.cpu().numpy().copy())
+    finally:
+        nb.check(lib.nb_set_tuning(b"backward_tc", 2), "nb_set_tuning")
+        model.g.zero_()
+    assert rel_err(res["ordered"][0], res["plain"][0]) <= 2e-3
+    assert rel_err(res["ordered"][1][:model.hash_count], res["plain"][1][:model.hash_count]) <= 2e-3
+
+
+def test_compact_host_batches_train_like_full_layout_ones(cuda, nb):
+    """prefetch() with the compact host layout (position float3, target three halves: 30 bytes per sample instead of
+    44) widens the batch on the device with nb_unpack_samples; the step's inputs, and so its loss, are bit-identical."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    L, T, n = 16, 1 << 14, 3000
+    pos, dirs, tgt = _inputs(n, 37)
+    losses = {}
+    for layout in ("full", "compact"):
+        model = pl.FieldModel(torch, L, T, 16, 1.447, 64, 2, 64, 3)
+        model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+        model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+        tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, ordered=False)
+        nb.check(nb.load().nb_set_tuning(b"backward_tc", 0), "nb_set_tuning")      # one summation order for both runs is not needed: only the loss is compared
+        P = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+        t16 = tgt.view(np.float16)
+        batch = (P(pos), P(dirs), P(t16)) if layout == "full" else (P(pos[:, :3]), P(dirs), P(t16[:, :3]))
+        tr.prefetch(*batch)
+        losses[layout] = tr.step_prefetched(lag=False)
+        if layout == "compact":
+            assert torch.equal(tr.pos[:n].cpu(), torch.from_numpy(pos)) and torch.equal(tr.target[:n].cpu().view(torch.int16), torch.from_numpy(tgt.view(np.int16)))
+    nb.check(nb.load().nb_set_tuning(b"backward_tc", 2), "nb_set_tuning")
+    # the loss is one atomic sum over the batch: equal up to its summation order
+    assert abs(losses["full"] - losses["compact"]) <= 1e-6 * losses["full"] and losses["full"] > 0

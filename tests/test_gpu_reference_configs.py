@@ -107,7 +107,7 @@ def test_field_step_at_the_benchmark_shape_against_reference(cuda, nb, ref):
     lib.ref_field_forward_backward(rf, nb.ptr(tr.pos), nb.ptr(tr.dirs), nb.ptr(d_t3), n, 1.0, 128.0, st)
     torch.cuda.synchronize()
     r_enc = _view(torch, lib.ref_field_grid_activation(rf, 0), n * 32, np.float16).view(n, 32)
-    assert torch.equal(tr.enc.view(torch.int16), r_enc.view(torch.int16)), "encoded features differ from the reference's"
+    assert torch.equal(tr.encoded(n).view(torch.int16), r_enc.view(torch.int16)), "encoded features differ from the reference's"
     r_dout = _view(torch, lib.ref_field_density_out(rf), n * 16).view(n, 16)
     r_cout = _view(torch, lib.ref_field_color_out(rf), n * 3).view(n, 3)
     assert float((tr.c_out[:, :3] - r_cout).abs().max().item()) <= 1e-2
