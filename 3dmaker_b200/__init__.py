@@ -138,6 +138,7 @@ class StepView(ctypes.Structure):
 
 GRAD_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
 PARAM_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
+BARRIER_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p)
 
 
 class NerfB200Error(RuntimeError):
@@ -180,6 +181,13 @@ _SIGNATURES = {
     "nb_mlp_forward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "nb_mlp_backward": (c_int, [ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                 c_void_p, c_void_p, c_void_p]),
+    "nb_adam_step_peer": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int, c_int64, c_int64,
+                                  c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_void_p]),
+    "nb_ipc_export": (c_int, [c_void_p, c_void_p]),
+    "nb_ipc_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "nb_ipc_close": (c_int, [c_void_p]),
+    "nb_device_alloc": (c_int, [c_int64, ctypes.POINTER(c_void_p)]),
+    "nb_device_free": (c_int, [c_void_p]),
     "nb_mse_loss_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_int, c_void_p]),
     "nb_adam_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_float,
                              c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]),
@@ -242,6 +250,8 @@ _SIGNATURES = {
     "nb_nerf_set_single_step": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_steps_per_call": (c_int, [c_void_p, c_int]),
     "nb_nerf_set_optimizer_shard": (c_int, [c_void_p, ctypes.c_uint32, ctypes.c_uint32, PARAM_SYNC_FN, c_void_p]),
+    "nb_nerf_set_peer_exchange": (c_int, [c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), BARRIER_FN,
+                                          c_void_p]),
     "nb_nerf_set_hit_counts_capacity": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_set_grad_buffer": (c_int, [c_void_p, c_void_p, c_int64]),

@@ -73,6 +73,37 @@ class CollectiveBuffers:
         return self.registered
 
 
+class PeerMemory:
+    """Addresses of every rank's copy of an array, for kernels that read and write peer memory (nb_adam_step_peer):
+    each rank exports its allocation (cudaIpcGetMemHandle through nb_ipc_export - the address must be the start of a
+    cudaMalloc allocation), the handles travel through the process group, every rank opens the others'.  pointers[r] is
+    rank r's array as THIS process addresses it.  One node only; needs peer access between the GPUs (NVLink)."""
+
+    def __init__(self, nb, dist, base_ptr):
+        import ctypes
+        self.nb, self.lib = nb, nb.load()
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        handle = ctypes.create_string_buffer(64)
+        nb.check(self.lib.nb_ipc_export(ctypes.c_void_p(int(base_ptr)), handle), "nb_ipc_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw)
+        self.pointers, self._opened = [], []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.pointers.append(int(base_ptr))
+                continue
+            p = ctypes.c_void_p()
+            nb.check(self.lib.nb_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p)), "nb_ipc_open")
+            self.pointers.append(int(p.value))
+            self._opened.append(int(p.value))
+
+    def close(self):
+        import ctypes
+        for p in self._opened:
+            self.lib.nb_ipc_close(ctypes.c_void_p(p))
+        self._opened = []
+
+
 class DataParallelTrainer:
     """Wraps a scene engine so that train_rays() takes the GLOBAL ray batch.
 
@@ -89,7 +120,11 @@ class DataParallelTrainer:
                    all-reduce's bytes on the wire and 1/N of the optimizer's memory traffic - the part of a step that
                    does not shrink with the number of ranks when the batch is split (2^22-entry levels: 4.6 GB per
                    Adam launch).  The fp32 master copy and the moments of a slice live on its owner; gather_master()
-                   collects the master copy (before saving)."""
+                   collects the master copy (before saving);
+      "peer"       the same three stages as ONE kernel per rank (nb_adam_step_peer): the slice's gradients are loaded
+                   from every rank's memory over NVLink, the updated fp16 slice is stored into every rank's forward
+                   copy, a one-element all-reduce before and after keeps the ranks together.  GPUs of one node only;
+                   the engine's arenas must be its own allocations (no registered_gradient)."""
 
     def __init__(self, torch, engine, dist=None, steps_per_call=1, registered_gradient=False, exchange="allreduce"):
         self.torch, self.engine, self.dist = torch, engine, dist
@@ -99,11 +134,14 @@ class DataParallelTrainer:
         self._steps_seen = 0
         self.sync_calls = 0
         self.buffers = None
-        if exchange not in ("allreduce", "sharded"):
+        self._peer_g = self._peer_w = None
+        if exchange not in ("allreduce", "sharded", "peer"):
             raise ValueError("unknown exchange %r" % (exchange,))
         self.exchange = exchange
         self._bytes = {"gradient_out_per_step": 0, "parameters_out_per_step": 0}
         if self.world > 1:
+            if exchange == "peer":
+                registered_gradient = False      # the kernel reads the engine's own allocation through an IPC mapping
             if registered_gradient and hasattr(engine, "set_grad_buffer"):
                 # the gradient arena moves into memory registered with the communicator
                 self.buffers = CollectiveBuffers(torch, dist, "cuda:%d" % torch.cuda.current_device())
@@ -120,6 +158,22 @@ class DataParallelTrainer:
                 engine.set_grad_sync(self._reduce_scatter)
                 wire = (self.world - 1) / self.world
                 self._bytes = {"gradient_out_per_step": int(self._hash * 4 * wire + (self._total - self._hash) * 4 * 2 * wire),
+                               "parameters_out_per_step": int(self._hash * 2 * wire)}
+            elif exchange == "peer":
+                if self._hash % (4 * self.world) != 0:
+                    raise ValueError("the hash table (%d elements) does not split into %d aligned slices" % (self._hash, self.world))
+                self._shard = self._hash // self.world
+                import importlib
+                nbm = importlib.import_module("3dmaker_b200")
+                self._peer_g = PeerMemory(nbm, dist, a.g)
+                self._peer_w = PeerMemory(nbm, dist, a.w_h)
+                self._token = torch.zeros(1, dtype=torch.float32, device="cuda:%d" % torch.cuda.current_device())
+                engine.set_grad_sync(None)
+                engine.set_peer_exchange(self.rank, self.world, self._peer_g.pointers, self._peer_w.pointers, self._barrier)
+                wire = (self.world - 1) / self.world
+                # what crosses NVLink per step: the other ranks read (N - 1) / N of this gradient table, this rank stores its
+                # fp16 slice into N - 1 peers, and everybody reads everybody's dense tail
+                self._bytes = {"gradient_out_per_step": int(self._hash * 4 * wire + (self._total - self._hash) * 4 * (self.world - 1)),
                                "parameters_out_per_step": int(self._hash * 2 * wire)}
             else:
                 engine.set_grad_sync(self._allreduce)
@@ -140,13 +194,17 @@ class DataParallelTrainer:
         self.dist.reduce_scatter_tensor(grad[lo:lo + self._shard], grad[:self._hash], op=self.dist.ReduceOp.SUM)   # in place
         self.dist.all_reduce(grad[self._hash:self._total], op=self.dist.ReduceOp.SUM)
 
+    def _barrier(self):
+        self.sync_calls += 1
+        self.dist.all_reduce(self._token, op=self.dist.ReduceOp.SUM)
+
     def _allgather_params(self, w_h):
         lo = self.rank * self._shard
         self.dist.all_gather_into_tensor(w_h[:self._hash], w_h[lo:lo + self._shard])                                # in place
 
     def gather_master(self):
         """After sharded steps: every rank receives the fp32 master copy of every table slice (call before saving)."""
-        if self.world > 1 and self.exchange == "sharded":
+        if self.world > 1 and self.exchange in ("sharded", "peer"):
             w = self.engine.arena_tensor("w")
             lo = self.rank * self._shard
             self.dist.all_gather_into_tensor(w[:self._hash], w[lo:lo + self._shard])
@@ -161,6 +219,11 @@ class DataParallelTrainer:
         if self.world > 1:
             if self.exchange == "sharded" and hasattr(self.engine, "set_optimizer_shard"):
                 self.engine.set_optimizer_shard(0, 1, None)
+            if self.exchange == "peer":
+                self.torch.cuda.synchronize()
+                self.dist.barrier()              # nobody unmaps memory a peer's kernel may still be using
+                self.engine.set_peer_exchange(0, 1, None, None, None)
+                self._peer_g.close(); self._peer_w.close()
             self.engine.set_grad_sync(None)
 
     def train_rays(self, rays_o, rays_d, rgb_true):
@@ -179,8 +242,9 @@ class DataParallelTrainer:
     def replicas_in_sync(self):
         """True when every rank holds bit-identical parameters: compares the 64-bit sum of the raw bits of the fp16 copy
         the forward reads (with the sharded optimizer the fp32 master copy of a slice is current on its owner only)."""
-        w = self.engine.arena_tensor("w_h" if self.exchange == "sharded" else "w")
-        s = w.view(self.torch.int16 if self.exchange == "sharded" else self.torch.int32).to(self.torch.int64).sum().reshape(1)
+        owner_only = self.exchange in ("sharded", "peer")
+        w = self.engine.arena_tensor("w_h" if owner_only else "w")
+        s = w.view(self.torch.int16 if owner_only else self.torch.int32).to(self.torch.int64).sum().reshape(1)
         if self.world == 1:
             return True
         t = self.torch.stack([s[0], -s[0]])

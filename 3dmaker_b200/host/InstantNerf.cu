@@ -483,11 +483,33 @@ void InstantNerf::setOptimizerShard(uint32_t rank, uint32_t world, ParamSync syn
     m_shardRank = rank; m_shardWorld = world; m_paramSync = std::move(sync);
 }
 
+void InstantNerf::setPeerExchange(uint32_t rank, uint32_t world, const std::vector<const float*>& peerGrads, const std::vector<void*>& peerParamsH,
+                                  RankBarrier barrier) {
+    if (world <= 1) { m_peerGrads.clear(); m_peerParamsH.clear(); m_rankBarrier = RankBarrier(); m_shardRank = 0; m_shardWorld = 1; return; }
+    if (rank >= world || peerGrads.size() != world || peerParamsH.size() != world || !barrier)
+        throw std::runtime_error("setPeerExchange: one gradient and one parameter pointer per rank and a barrier are required");
+    if (m_arena.sparse_count % (4 * (int64_t)world) != 0) throw std::runtime_error("setPeerExchange: the hash table does not split into 16-byte aligned slices");
+    if (peerGrads[rank] != m_arena.G(0) || peerParamsH[rank] != (void*)m_arena.Wh(0))
+        throw std::runtime_error("setPeerExchange: this rank's own entries must be its own arenas");
+    m_peerGrads = peerGrads; m_peerParamsH = peerParamsH; m_rankBarrier = std::move(barrier);
+    m_shardRank = rank; m_shardWorld = world;
+    m_paramSync = ParamSync();
+}
+
 void InstantNerf::optimizerStep(cudaStream_t stream) {
     timed(stream, m_times.optimizer, [&]() {
         if (m_optSteps < 50000) m_optSteps++;
         float bc1 = 1.0f - std::pow(m_opts.beta1, (float)m_optSteps);
         float bc2 = 1.0f - std::pow(m_opts.beta2, (float)m_optSteps);
+        if (!m_peerGrads.empty()) {
+            m_rankBarrier(stream);     // every rank's backward has finished: the gradients may be read
+            throw_on_error(nb_adam_step_peer(m_arena.W(0), m_arena.M(0), m_arena.V(0), m_peerGrads.data(), m_peerParamsH.data(), (int)m_shardRank,
+                                             (int)m_shardWorld, m_arena.sparse_count, m_arena.total, m_opts.learningRate, m_opts.beta1, m_opts.beta2,
+                                             m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, stream), "optimizer (peer)");
+            m_rankBarrier(stream);     // every rank has stored its slice everywhere and read what it needed of this gradient
+            throw_on_error(nb_zero_async(m_arena.G(0), m_arena.total * (int64_t)sizeof(float), stream), "optimizer: clear");
+            return;
+        }
         auto adam = [&](int64_t off, int64_t sparse, int64_t count, const char* what) {
             throw_on_error(nb_adam_step(m_arena.W(off), m_arena.Wh(off), m_arena.G(off), m_arena.M(off), m_arena.V(off), sparse, count,
                                         m_opts.learningRate, m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),

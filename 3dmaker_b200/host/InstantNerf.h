@@ -131,6 +131,14 @@ public:
     // slice are current on its owner only.  world <= 1 restores the whole-arena update.
     using ParamSync = std::function<void(half* d_params_h, int64_t sparse_count, cudaStream_t stream)>;
     void setOptimizerShard(uint32_t rank, uint32_t world, ParamSync sync);
+    // Data parallelism with ONE kernel for reduce-scatter + optimizer + all-gather (nb_adam_step_peer): peerGrads[r] /
+    // peerParamsH[r] are rank r's gradient arena and fp16 parameter arena as THIS process can address them (entry `rank`:
+    // this engine's own), `barrier` meets all ranks on the given stream.  Per step: barrier, the kernel on this rank's
+    // slice of the table, barrier, this rank's gradient arena cleared.  The gradient-sync callback is not used in this
+    // mode.  world <= 1 switches back.
+    using RankBarrier = std::function<void(cudaStream_t stream)>;
+    void setPeerExchange(uint32_t rank, uint32_t world, const std::vector<const float*>& peerGrads, const std::vector<void*>& peerParamsH,
+                         RankBarrier barrier);
     // Loss gradients are normalised by numRays * scale (the global ray count when ranks split a batch).
     void setGlobalRayScale(uint32_t scale) { m_rayScale = scale ? scale : 1u; }
     // One kernel each way for the whole field (encode + both networks) instead of the reference's kernel sequence;
@@ -193,6 +201,9 @@ private:
     TinyMLPHashGrid* m_densityMLP = nullptr;
     GradSync m_gradSync;
     ParamSync m_paramSync;
+    RankBarrier m_rankBarrier;
+    std::vector<const float*> m_peerGrads;
+    std::vector<void*> m_peerParamsH;
     uint32_t m_shardRank = 0, m_shardWorld = 1;
     uint32_t m_rayScale = 1;
     bool m_fused = false;

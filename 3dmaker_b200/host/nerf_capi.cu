@@ -109,6 +109,16 @@ extern "C" int nb_nerf_set_optimizer_shard(nb_nerf* h, uint32_t rank, uint32_t w
     NB_GUARD(h->impl.setOptimizerShard(rank, world, [fn, user](half* p, int64_t count, cudaStream_t st) { fn(user, p, count, st); }))
 }
 
+extern "C" int nb_nerf_set_peer_exchange(nb_nerf* h, uint32_t rank, uint32_t world, const float* const* peer_grads, void* const* peer_w_h,
+                                         nb_barrier_fn fn, void* user) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    if (world > 1 && (!peer_grads || !peer_w_h || !fn)) return nb_set_error(NB_ERR_INVALID, "nb_nerf_set_peer_exchange: peer pointers and a barrier are required");
+    std::vector<const float*> g;
+    std::vector<void*> p;
+    for (uint32_t r = 0; world > 1 && r < world; r++) { g.push_back(peer_grads[r]); p.push_back(peer_w_h[r]); }
+    NB_GUARD(h->impl.setPeerExchange(rank, world, g, p, [fn, user](cudaStream_t st) { fn(user, st); }))
+}
+
 extern "C" int nb_nerf_set_hit_counts_capacity(nb_nerf* h, uint32_t capacity) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     h->impl.setHitCountsCapacity(capacity);

@@ -134,6 +134,21 @@ class InstantNerf:
         self._param_cb = nb.PARAM_SYNC_FN(trampoline)
         nb.check(self.lib.nb_nerf_set_optimizer_shard(self.h, rank, world, self._param_cb, None), "nb_nerf_set_optimizer_shard")
 
+    def set_peer_exchange(self, rank, world, grad_ptrs, param_ptrs, barrier):
+        """Optimizer tail through nb_adam_step_peer (see nb_nerf_set_peer_exchange): grad_ptrs / param_ptrs are lists of
+        `world` device addresses (ints), barrier() meets all ranks on the current stream.  world <= 1 switches back."""
+        if world <= 1:
+            nb.check(self.lib.nb_nerf_set_peer_exchange(self.h, 0, 1, None, None, nb.BARRIER_FN(0), None), "nb_nerf_set_peer_exchange")
+            self._barrier_cb = None
+            return
+        G = (ctypes.c_void_p * world)(*[int(p) for p in grad_ptrs])
+        W = (ctypes.c_void_p * world)(*[int(p) for p in param_ptrs])
+
+        def trampoline(user, stream):
+            barrier()
+        self._barrier_cb = nb.BARRIER_FN(trampoline)
+        nb.check(self.lib.nb_nerf_set_peer_exchange(self.h, rank, world, G, W, self._barrier_cb, None), "nb_nerf_set_peer_exchange")
+
     def set_grad_buffer(self, tensor):
         """Moves the gradient arena into `tensor` (float32, CUDA, at least arena().total elements; the engine zeroes it and
         this object keeps it alive) - e.g. memory registered with the communicator so that the all-reduce of

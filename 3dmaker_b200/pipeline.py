@@ -27,7 +27,9 @@ class FieldModel:
     """Parameters of hash grid + density network + colour network in one arena, with Adam state."""
 
     def __init__(self, torch, num_levels=16, table_size=1 << 19, base_resolution=16, growth=1.3819, density_hidden=64,
-                 density_layers=2, color_hidden=64, color_layers=3, training=True, stream=None, grad_alloc=None):
+                 density_layers=2, color_hidden=64, color_layers=3, training=True, stream=None, grad_alloc=None, exportable=False):
+        """exportable: the gradient and the fp16 parameter copy are cudaMalloc allocations of their own (nb_device_alloc)
+        instead of torch tensors, so that other ranks can map them (distributed.PeerMemory) for nb_adam_step_peer."""
         self.torch = torch
         self.lib = nb.load()
         self.grid = nb.grid_setup(num_levels, table_size, base_resolution, growth, stream)
@@ -43,14 +45,33 @@ class FieldModel:
         self.total = _pad4(o)
         dev = "cuda"
         self.w = torch.zeros(self.total, dtype=torch.float32, device=dev)
-        self.w_h = torch.zeros(self.total, dtype=torch.float16, device=dev)
+        self._own = []          # base addresses of nb_device_alloc allocations, freed with the model
+        self.w_h = self._exportable(self.total, np.float16) if exportable else torch.zeros(self.total, dtype=torch.float16, device=dev)
         self.training = training
         if training:
             # grad_alloc(count, dtype): where the gradient lives, e.g. distributed.CollectiveBuffers.zeros for data parallelism
-            self.g = grad_alloc(self.total, torch.float32) if grad_alloc is not None else torch.zeros(self.total, dtype=torch.float32, device=dev)
+            if exportable:
+                self.g = self._exportable(self.total, np.float32)
+            else:
+                self.g = grad_alloc(self.total, torch.float32) if grad_alloc is not None else torch.zeros(self.total, dtype=torch.float32, device=dev)
             self.m = torch.zeros(self.total, dtype=torch.float32, device=dev)
             self.v = torch.zeros(self.total, dtype=torch.float32, device=dev)
         self.step_count = 0
+
+    def _exportable(self, count, dtype):
+        nm = importlib.import_module("3dmaker_b200.nerf")
+        ptr = ctypes.c_void_p()
+        nb.check(self.lib.nb_device_alloc(count * np.dtype(dtype).itemsize, ctypes.byref(ptr)), "nb_device_alloc")
+        self._own.append(ptr.value)
+        return nm.view_tensor(self.torch, ptr.value, count, dtype)
+
+    def __del__(self):
+        try:
+            for p in getattr(self, "_own", []):
+                self.lib.nb_device_free(ctypes.c_void_p(p))
+            self._own = []
+        except Exception:
+            pass
 
     # ---- parameter I/O (host numpy <-> arena), mirrors loadHashgrid / loadWeights of the reference classes
     def load_hashgrid(self, table_f32):
@@ -238,6 +259,40 @@ class SampleTrainer:
             nb.check(self.lib.nb_zero_async(m.ptr("g", hi), (H - hi) * 4, nb.stream_ptr(stream)), "nb_zero_async")
         dist.all_gather_into_tensor(m.w_h[:H], m.w_h[lo:hi])                        # in place as well
 
+    def optimizer_step_peer(self, dist, stream=None):
+        """Data-parallel tail of a step as one kernel per rank (nb_adam_step_peer): the model must be `exportable`.  The
+        first call maps the other ranks' gradient and fp16 parameter arrays (distributed.PeerMemory).  Per step: a
+        one-element all-reduce as barrier, the kernel, the barrier again, then this rank's gradient is cleared."""
+        m = self.model
+        if not hasattr(self, "_peers"):
+            D = importlib.import_module("3dmaker_b200.distributed")
+            if not m._own:
+                raise nb.NerfB200Error("optimizer_step_peer needs FieldModel(exportable=True)")
+            self._peers = (D.PeerMemory(nb, dist, m.g.data_ptr()), D.PeerMemory(nb, dist, m.w_h.data_ptr()))
+            self._token = self.torch.zeros(1, dtype=self.torch.float32, device=m.g.device)
+            world = dist.get_world_size()
+            self._peer_arrays = ((ctypes.c_void_p * world)(*self._peers[0].pointers), (ctypes.c_void_p * world)(*self._peers[1].pointers))
+        world, rank = dist.get_world_size(), dist.get_rank()
+        if m.step_count < 50000:
+            m.step_count += 1
+        bc1 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta1), np.float32(m.step_count)))
+        bc2 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta2), np.float32(m.step_count)))
+        dist.all_reduce(self._token)
+        nb.check(self.lib.nb_adam_step_peer(m.ptr("w", 0), m.ptr("m", 0), m.ptr("v", 0), self._peer_arrays[0], self._peer_arrays[1], rank, world,
+                                            m.hash_count, m.total, self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2),
+                                            1.0 / self.loss_scale, nb.stream_ptr(stream)), "nb_adam_step_peer")
+        dist.all_reduce(self._token)
+        nb.check(self.lib.nb_zero_async(m.ptr("g", 0), m.total * 4, nb.stream_ptr(stream)), "nb_zero_async")
+
+    def close_peers(self, dist):
+        """Unmaps the other ranks' arrays (after a barrier: nobody's kernel may still be using them)."""
+        if hasattr(self, "_peers"):
+            self.torch.cuda.synchronize()
+            dist.barrier()
+            for p in self._peers:
+                p.close()
+            del self._peers
+
     def gather_master(self, dist):
         """After sharded steps: brings the fp32 master table of every slice to every rank (e.g. before saving)."""
         m = self.model
@@ -273,7 +328,10 @@ class SampleTrainer:
         self.forward_backward(n, stream)
         if grad_sync is not None and hasattr(grad_sync, "all_reduce"):
             # a torch.distributed module: sharded optimizer (default) or the pipelined allreduce + Adam
-            if getattr(self, "dp_mode", "sharded") == "sharded":
+            mode = getattr(self, "dp_mode", "sharded")
+            if mode == "peer":
+                self.optimizer_step_peer(grad_sync, stream=stream)
+            elif mode == "sharded":
                 self.optimizer_step_sharded(grad_sync, stream=stream)
             else:
                 self.optimizer_step_synced(grad_sync, stream=stream)

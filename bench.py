@@ -463,7 +463,7 @@ def run_ours(args, rank, world, local_rank):
         D = importlib.import_module("3dmaker_b200.distributed")
         buffers = D.CollectiveBuffers(torch, dist, "cuda:%d" % local_rank)
     model = pl.FieldModel(torch, L, T, BASE, GROWTH, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3],
-                          grad_alloc=buffers.zeros if buffers is not None else None)
+                          grad_alloc=buffers.zeros if buffers is not None else None, exportable=(world > 1 and args.dp == "peer"))
     if buffers is not None:
         buffers.register()
     table, dW, db, cW, cb = init_params()
@@ -591,6 +591,8 @@ def run_ours(args, rank, world, local_rank):
             line["cpu_baseline"] = {"value": v, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": "one step on %d samples (%.1f s) of the 2^20-sample workload, full T=2^19 table" % (sample, dt)}
     # ---- the rest of the metric (render Mrays/s) and config 5, on the same ranks ----------------------------------
+    if world > 1 and args.dp == "peer":
+        tr.close_peers(dist)
     del tr, model, dev, own
     if buffers is not None:
         del buffers
@@ -936,14 +938,15 @@ def main():
     ap.add_argument("--extra-scene-warm", type=int, default=48, help="untimed train_rays calls of the embedded scene5 measurement "
                     "(six optimizer steps each: past the 256 steps of whole-grid occupancy updates)")
     ap.add_argument("--render-frames", type=int, default=12, help="timed frames of the embedded render measurement")
-    ap.add_argument("--exchange", default="sharded", choices=["allreduce", "sharded"],
-                    help="scene workloads at N > 1: all-reduce + replicated Adam, or reduce-scatter + Adam on a table slice + all-gather of fp16 "
-                         "parameters inside the engine")
+    ap.add_argument("--exchange", default="peer", choices=["allreduce", "sharded", "peer"],
+                    help="scene workloads at N > 1: all-reduce + replicated Adam; reduce-scatter + Adam on a table slice + all-gather of fp16 "
+                         "parameters; or the same three stages as one kernel over peer memory (default)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
-    ap.add_argument("--dp", default="sharded", choices=["sharded", "allreduce", "sliced"],
-                    help="N > 1: how the gradient is exchanged (sharded: reduce-scatter + Adam on a slice + all-gather of fp16 parameters; "
-                         "allreduce: one allreduce + one full Adam; sliced: both pipelined over 4 slices)")
+    ap.add_argument("--dp", default="peer", choices=["peer", "sharded", "allreduce", "sliced"],
+                    help="N > 1: how the gradient is exchanged (peer: one kernel per rank that sums the ranks' gradients of its table slice "
+                         "from peer memory, applies Adam and stores the fp16 slice into every rank; sharded: reduce-scatter + Adam on a slice + "
+                         "all-gather of fp16 parameters; allreduce: one allreduce + one full Adam; sliced: both pipelined over 4 slices)")
     ap.add_argument("--render-rounds", action="store_true", help="render workload: render in rounds of samples per ray (A/B; off by default)")
     ap.add_argument("--plain-buffers", action="store_true", help="N > 1: keep the gradient in ordinary device memory instead of memory "
                     "registered with the communicator (A/B)")

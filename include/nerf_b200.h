@@ -158,6 +158,28 @@ int nb_adam_step(float* d_w, void* d_w_h, float* d_g, float* d_m, float* d_v, in
                  float lr, float beta1, float beta2, float eps, float bias_correction1, float bias_correction2,
                  float inv_loss_scale, int zero_dense_grads, void* stream);
 
+/* Data-parallel tail of a step as ONE kernel over peer memory (no counterpart in the reference, which is single-GPU):
+ * this rank's slice [rank, rank + 1) * sparse_count / world of the hash table gets the SUM of all ranks' gradients -
+ * loaded straight from the ranks' gradient arenas, peer_grads[r] (HOST array of `world` device pointers, entry `rank`
+ * this rank's own) -, the sparse Adam rule of nb_adam_step on this rank's d_w / d_m / d_v, and the updated fp16 groups are
+ * stored into EVERY rank's forward copy, peer_w_h[r].  The dense tail [sparse_count, total_count) is summed and updated
+ * by every rank for itself.  Replaces reduce-scatter + optimizer + all-gather.  The caller provides what the kernel
+ * does not: a barrier across the ranks before the launch (gradients complete) and after it (parameters delivered,
+ * gradients read), after which each rank clears its own gradient arena; peer pointers come from nb_ipc_open or
+ * cudaDeviceEnablePeerAccess.  At most 8 ranks; sparse_count a multiple of 4 x world.  The fp32 master copy and the
+ * moments of a slice are current on its owner only. */
+int nb_adam_step_peer(float* d_w, float* d_m, float* d_v, const float* const* peer_grads, void* const* peer_w_h, int rank, int world,
+                      int64_t sparse_count, int64_t total_count, float lr, float beta1, float beta2, float eps, float bias_correction1,
+                      float bias_correction2, float inv_loss_scale, void* stream);
+/* cudaIpcGetMemHandle / cudaIpcOpenMemHandle (lazy peer access) / cudaIpcCloseMemHandle: handle64 is the 64-byte
+ * cudaIpcMemHandle_t; d_base must be the start of a cudaMalloc allocation (nb_device_alloc's, or the arenas of
+ * nb_nerf_get_arena).  nb_device_alloc returns zeroed memory. */
+int nb_ipc_export(void* d_base, void* handle64);
+int nb_ipc_open(const void* handle64, void** d_ptr_out);
+int nb_ipc_close(void* d_ptr);
+int nb_device_alloc(int64_t bytes, void** d_ptr_out);
+int nb_device_free(void* d_ptr);
+
 /* ---- NeRF glue between the two networks ------------------------------------------------------ */
 
 /* Replaces compute_SH_gather (modules/NeRF/otherKernels.cu:156-273).  d_dirs3: float3 per ray;
@@ -521,6 +543,14 @@ int nb_nerf_set_grad_sync(nb_nerf* h, nb_grad_sync_fn fn, void* user);
  * owner only.  world <= 1 switches back.  sparse_count must be a multiple of 4 x world. */
 typedef void (*nb_param_sync_fn)(void* user, void* d_params_h, int64_t sparse_count, void* stream);
 int nb_nerf_set_optimizer_shard(nb_nerf* h, uint32_t rank, uint32_t world, nb_param_sync_fn fn, void* user);
+/* Data parallelism through nb_adam_step_peer (no counterpart in the reference): peer_grads[r] / peer_w_h[r] = rank r's
+ * gradient arena and fp16 parameter arena (nb_nerf_get_arena's g and w_h) as this process addresses them - its own for
+ * r == rank, nb_ipc_open'ed for the others; fn must meet all ranks on the stream it is given (e.g. a one-element
+ * all-reduce).  Every optimizer step then runs: fn, the kernel, fn, clearing of this rank's gradient.  nb_grad_sync_fn is
+ * not called in this mode.  world <= 1 switches back. */
+typedef void (*nb_barrier_fn)(void* user, void* stream);
+int nb_nerf_set_peer_exchange(nb_nerf* h, uint32_t rank, uint32_t world, const float* const* peer_grads, void* const* peer_w_h,
+                              nb_barrier_fn fn, void* user);
 /* on != 0: nb_nerf_train_rays runs exactly one optimizer step (one fn call) per call; rays that do not fit the sample
  * batch are left untrained (nb_nerf_step_view.rays_consumed says how many were used) instead of starting a second
  * step, so that every rank of a data-parallel job issues the same number of gradient exchanges. */

@@ -438,3 +438,48 @@ def test_compact_host_batches_train_like_full_layout_ones(cuda, nb):
     nb.check(nb.load().nb_set_tuning(b"backward_tc", 2), "nb_set_tuning")
     # the loss is one atomic sum over the batch: equal up to its summation order
     assert abs(losses["full"] - losses["compact"]) <= 1e-6 * losses["full"] and losses["full"] > 0
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_peer_optimizer_kernel_equals_reduce_then_adam(cuda, nb, world):
+    """nb_adam_step_peer with the ranks played by separate buffers on ONE device (the kernel never waits for another rank,
+    so the ranks' launches simply run one after the other): every rank's fp16 parameters end up equal to what one Adam
+    launch on the summed gradient gives, each slice's master copy and moments are right on its owner, the dense tail on
+    everybody; untouched entries keep parameters and moments."""
+    torch = cuda
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    H, total = 1 << 16, (1 << 16) + 1024
+    rng = np.random.default_rng(8)
+    w0 = rng.uniform(-0.1, 0.1, total).astype(np.float32)
+    grads = []
+    for r in range(world):
+        g = np.zeros(total, np.float32)
+        g[:H] = (rng.normal(0, 3, H) * (rng.random(H) < 0.2)).astype(np.float32)
+        g[H:] = rng.normal(0, 5, total - H).astype(np.float32)
+        grads.append(g)
+    hyper = (1e-2, 0.9, 0.99, 1e-15, 0.1, 0.01, 1.0 / 128.0)
+    dev = lambda a: torch.from_numpy(a.copy()).cuda()
+    # reference: one launch on the sum (added in rank order, as the kernel adds)
+    gsum = grads[0].copy()
+    for r in range(1, world):
+        gsum += grads[r]
+    ref = dict(w=dev(w0), h=dev(w0).half(), g=dev(gsum), m=torch.zeros(total, device="cuda"), v=torch.zeros(total, device="cuda"))
+    nb.check(lib.nb_adam_step(P(ref["w"]), P(ref["h"]), P(ref["g"]), P(ref["m"]), P(ref["v"]), H, total, *hyper, 1, st), "nb_adam_step")
+    ranks = [dict(w=dev(w0), h=dev(w0).half(), g=dev(grads[r]), m=torch.zeros(total, device="cuda"), v=torch.zeros(total, device="cuda"))
+             for r in range(world)]
+    G = (ctypes.c_void_p * world)(*[t["g"].data_ptr() for t in ranks])
+    W = (ctypes.c_void_p * world)(*[t["h"].data_ptr() for t in ranks])
+    for r in range(world):
+        nb.check(lib.nb_adam_step_peer(P(ranks[r]["w"]), P(ranks[r]["m"]), P(ranks[r]["v"]), G, W, r, world, H, total, *hyper, st), "nb_adam_step_peer")
+    torch.cuda.synchronize()
+    shard = H // world
+    for r in range(world):
+        assert torch.equal(ranks[r]["h"], ref["h"]), "rank %d: fp16 parameters differ" % r
+        lo, hi = r * shard, (r + 1) * shard
+        for k in ("w", "m", "v"):
+            assert torch.equal(ranks[r][k][lo:hi], ref[k][lo:hi]), (r, k)
+            assert torch.equal(ranks[r][k][H:], ref[k][H:]), (r, k, "dense tail")
+        untouched = torch.from_numpy(gsum[:H] == 0).cuda()
+        assert torch.equal(ranks[r]["h"][:H][untouched], dev(w0).half()[:H][untouched])
+        assert torch.equal(ranks[r]["g"], dev(grads[r]))            # the kernel leaves the gradients alone: the caller clears them
+    assert lib.nb_adam_step_peer(P(ranks[0]["w"]), P(ranks[0]["m"]), P(ranks[0]["v"]), G, W, 0, 9, H, total, *hyper, st) == 4     # NB_ERR_LIMIT
