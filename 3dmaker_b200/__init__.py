@@ -231,6 +231,7 @@ _SIGNATURES = {
     "nb_occ_update_master_grid": (c_int, [c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "nb_occ_update_bitfield": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "nb_occ_extract_active": (c_int, [ctypes.POINTER(SceneDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_probe_random_access": (c_int, [c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "nb_unpack_samples": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "nb_undeal_tiles": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nb_nerf_default_options": (c_int, [ctypes.POINTER(NerfOptions)]),

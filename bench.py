@@ -441,6 +441,33 @@ def bind_to_gpu_numa_node(torch, local_rank):
         return None
 
 
+# L1TEX lane requests of one field_forward launch and L2 reduction requests of one backward launch at 2^20 samples, from the
+# ncu captures summarised in profiles/field_step_kernels_2p20_ncu.md
+NCU_REQUESTS = {"field_forward": 105.0e6, "field_backward_scatter": 92.0e6}
+
+
+def random_access_rates(torch, nb):
+    """What the memory system gives a kernel that does nothing but scattered accesses to an L2-resident table the size
+    of ours (nb_probe_random_access): 4-byte gathers from 2^23 entries (the 32 MiB fp16 table), 8-byte fp32-pair
+    reductions into 2^23 entries (the 64 MiB gradient table).  G operations per second, best of 3."""
+    lib = nb.load()
+    table = torch.zeros(1 << 24, dtype=torch.float32, device="cuda")
+    blocks, per_thread = 148 * 16, 128
+    out = {}
+    for name, kind in (("gather_gops", 0), ("reduction_gops", 1)):
+        nb.check(lib.nb_probe_random_access(kind, 23, blocks, per_thread, nb.ptr(table), nb.stream_ptr()), "nb_probe_random_access")
+        best = None
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            nb.check(lib.nb_probe_random_access(kind, 23, blocks, per_thread, nb.ptr(table), nb.stream_ptr()), "nb_probe_random_access")
+            b.record(); b.synchronize()
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+        out[name] = blocks * 256 * per_thread / best / 1e6
+    return out
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -573,6 +600,19 @@ def run_ours(args, rank, world, local_rank):
                             "its fp32 gradient (64 MiB) are L2-resident, so the kernel is bound by L2 reductions and the L1TEX request "
                             "rate, not by HBM: DRAM traffic per launch (ncu) is far below the algorithmic bytes"
                             % (ALGO_BYTES[dom], kt[dom])}
+        # the roof these kernels actually run under: scattered accesses to L2-resident tables
+        rates = random_access_rates(torch, nb)
+        scale = BATCH / float(1 << 20)
+        fwd_rate = NCU_REQUESTS["field_forward"] * scale / (kt["field_forward"] / 1000.0) / 1e9 if "field_forward" in kt else None
+        bwd_key = "field_backward_scatter" if "field_backward_scatter" in kt else None
+        bwd_rate = NCU_REQUESTS["field_backward_scatter"] * scale / (kt[bwd_key] / 1000.0) / 1e9 if bwd_key else None
+        roofline["l2_random_access"] = {
+            "probe": rates, "unit": "G operations/s",
+            "field_forward": None if fwd_rate is None else {"gather_requests_gops": fwd_rate, "frac_of_probe": fwd_rate / rates["gather_gops"]},
+            "field_backward_scatter": None if bwd_rate is None else {"reduction_requests_gops": bwd_rate,
+                                                                      "frac_of_probe": bwd_rate / rates["reduction_gops"]},
+            "note": "request counts per launch from ncu (profiles/field_step_kernels_2p20_ncu.md); probe = nb_probe_random_access on "
+                    "tables of the same size, a kernel that does nothing else"}
         line = {
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",

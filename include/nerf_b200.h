@@ -66,6 +66,11 @@ int nb_built_arch(void);
 /* Number of kernel launches this library has issued since load (bench accounting). */
 uint64_t nb_launch_count(void);
 
+/* Measurement aid (no counterpart in the reference): `blocks` x 256 threads x per_thread scattered accesses to seeded
+ * random entries of d_table and nothing else - kind 0: 4-byte gathers from 2^entries_log2 4-byte entries; kind 1: 8-byte
+ * fp32-pair reductions into 2^entries_log2 8-byte entries (the gradient scatter's operation; it adds to the table).  The
+ * rates it reaches are the ceilings bench.py reports the hash-grid gathers and the gradient scatter against. */
+int nb_probe_random_access(int kind, int entries_log2, int blocks, int per_thread, void* d_table, void* stream);
 /* cudaMemsetAsync(d_ptr, 0, bytes) on the caller's stream (the reference's classes call
  * cudaMemsetAsync directly, e.g. TinyMLPHashGrid.cu:312). */
 int nb_zero_async(void* d_ptr, int64_t bytes, void* stream);

@@ -483,3 +483,20 @@ def test_peer_optimizer_kernel_equals_reduce_then_adam(cuda, nb, world):
         assert torch.equal(ranks[r]["h"][:H][untouched], dev(w0).half()[:H][untouched])
         assert torch.equal(ranks[r]["g"], dev(grads[r]))            # the kernel leaves the gradients alone: the caller clears them
     assert lib.nb_adam_step_peer(P(ranks[0]["w"]), P(ranks[0]["m"]), P(ranks[0]["v"]), G, W, 0, 9, H, total, *hyper, st) == 4     # NB_ERR_LIMIT
+
+
+def test_random_access_probe_counts_its_operations(cuda, nb):
+    """nb_probe_random_access: the reduction kind adds (1, 2) to an entry per operation, so the table's sums give the
+    operation count back; the gather kind leaves the table alone."""
+    torch = cuda
+    lib, P = nb.load(), nb.ptr
+    table = torch.zeros((1 << 12, 2), dtype=torch.float32, device="cuda")
+    nb.check(lib.nb_probe_random_access(1, 12, 8, 16, P(table), nb.stream_ptr()), "nb_probe_random_access")
+    torch.cuda.synchronize()
+    ops = 8 * 256 * 16
+    assert float(table[:, 0].sum().item()) == ops and float(table[:, 1].sum().item()) == 2 * ops
+    before = table.clone()
+    nb.check(lib.nb_probe_random_access(0, 13, 8, 16, P(table), nb.stream_ptr()), "nb_probe_random_access")
+    torch.cuda.synchronize()
+    assert torch.equal(table, before)
+    assert lib.nb_probe_random_access(2, 12, 8, 16, P(table), nb.stream_ptr()) == 1
