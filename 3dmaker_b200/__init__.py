@@ -159,6 +159,7 @@ _SIGNATURES = {
                                     c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_hash_scatter_backward": (c_int, [ctypes.POINTER(GridDesc), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "nb_set_tuning": (c_int, [ctypes.c_char_p, c_int]),
+    "nb_get_tuning": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_int)]),
     "nb_field_backward_tc_status": (c_int, []),
     "nb_field_supported": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc)]),
     "nb_field_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
@@ -296,6 +297,28 @@ def check(status, what=""):
     if status != 0:
         msg = load().nb_last_error().decode("utf-8", "replace")
         raise NerfB200Error("%s failed with status %d: %s" % (what or "libnerf_b200 call", status, msg))
+
+
+def get_tuning(key):
+    v = c_int(0)
+    check(load().nb_get_tuning(key.encode(), ctypes.byref(v)), "nb_get_tuning(%s)" % key)
+    return v.value
+
+
+def set_grad_table_half(on, scale_log2=None):
+    """Process-wide: the hash part of every gradient arena becomes one __half2 per entry (see nb_set_tuning in
+    include/nerf_b200.h).  Call it before the first backward, never between a backward and its optimizer step."""
+    if scale_log2 is not None:
+        check(load().nb_set_tuning(b"grad_table_scale_log2", int(scale_log2)), "nb_set_tuning(grad_table_scale_log2)")
+    check(load().nb_set_tuning(b"grad_table_half", 1 if on else 0), "nb_set_tuning(grad_table_half)")
+
+
+def grad_table_half():
+    return get_tuning("grad_table_half") != 0
+
+
+def grad_table_scale():
+    return float(1 << get_tuning("grad_table_scale_log2")) if grad_table_half() else 1.0
 
 
 def ptr(t):

@@ -82,6 +82,13 @@ __device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+// fp16 pair reductions (the half-precision gradient table): one entry, or two entries in an aligned 8-byte slot pair.
+__device__ __forceinline__ void red_add_h2(uint32_t* addr, uint32_t v) {
+    asm volatile("red.global.add.noftz.f16x2 [%0], %1;\n" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_h2x2(uint32_t* addr, uint32_t lo, uint32_t hi) {
+    asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1, %2};\n" ::"l"(addr), "r"(lo), "r"(hi) : "memory");
+}
 __device__ __forceinline__ void red_add(float* addr, float a) {
     asm volatile("red.global.add.f32 [%0], %1;\n" ::"l"(addr), "f"(a) : "memory");
 }

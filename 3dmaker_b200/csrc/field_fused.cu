@@ -813,7 +813,7 @@ static int field_backward_impl(const nb_mlp_desc* density, const nb_mlp_desc* co
         if (misaligned(d_pos4, 16) || misaligned(d_table_grads, 8))
             return nb_set_error(NB_ERR_INVALID, "nb_field_backward: misaligned positions or table gradient");
         gp = nb::make_params(grid);
-        if (misaligned(d_table_grads, 16)) gp.pair_ops = 0;
+        if (misaligned(d_table_grads, 16) && !gp.grad_half) gp.pair_ops = 0;   // the fp32 pair is a 16-byte reduction, the fp16 pair 8 bytes
         shared_levels = nb::scatter_shared_levels(gp, n);
         gio.pos4 = d_pos4; gio.table_grads = d_table_grads; gio.scatter_begin = shared_levels;
         gio.denc_cols = 4 * shared_levels;   // only what the shared-memory scatter kernel below reads

@@ -111,6 +111,10 @@ struct ScatterTuning {
 static ScatterTuning g_scatter_tuning;
 std::atomic<int> g_pair_ops{1};
 std::atomic<int> g_run_merge{20};
+// Half-precision gradient table (opt-in): the hash part of a gradient arena holds one __half2 per entry in its first
+// half instead of two floats; scatter kernels multiply by 2^scale_log2 before rounding and the optimizer divides again.
+std::atomic<int> g_grad_table_half{0};
+std::atomic<int> g_grad_table_scale_log2{7};
 
 // Gradient scatter, one thread per (sample, level), level = level_base + blockIdx.y so that all CTAs resident at one
 // time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector reduction.
@@ -164,6 +168,14 @@ __global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant
         });
     }
     __syncthreads();
+    if (gp.grad_half) {
+        uint32_t* base = reinterpret_cast<uint32_t*>(grads) + (size_t)level * gp.T;
+        for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+            float2 v = acc[c];
+            if (v.x != 0.f || v.y != 0.f) red_add_h2(base + c, pack_half2(v.x * gp.grad_scale, v.y * gp.grad_scale));
+        }
+        return;
+    }
     float* base = grads + (size_t)level * gp.T * 2;
     for (int c = threadIdx.x; c < cells; c += blockDim.x) {
         float2 v = acc[c];
@@ -415,9 +427,26 @@ extern "C" int nb_set_tuning(const char* key, int value) {
     else if (k == "forward_persistent") g_forward_persistent = value;
     else if (k == "scatter_smem_levels") g_scatter_tuning.smem_levels = value;
     else if (k == "pair_ops") g_pair_ops = value;
+    else if (k == "grad_table_half") g_grad_table_half = value != 0;
+    else if (k == "grad_table_scale_log2") {
+        if (value < 0 || value > 24) return nb_set_error(NB_ERR_INVALID, "nb_set_tuning: grad_table_scale_log2 must be 0..24");
+        g_grad_table_scale_log2 = value;
+    }
     else if (k == "scatter_level_begin") g_scatter_tuning.level_begin = value;
     else if (k == "scatter_level_end") g_scatter_tuning.level_end = value;
     else return nb_set_error(NB_ERR_INVALID, "nb_set_tuning: unknown key");
+    return NB_OK;
+}
+
+extern "C" int nb_get_tuning(const char* key, int* value) {
+    if (!key || !value) return nb_set_error(NB_ERR_INVALID, "nb_get_tuning: null pointer");
+    std::string k(key);
+    if (k == "grad_table_half") *value = g_grad_table_half.load();
+    else if (k == "grad_table_scale_log2") *value = g_grad_table_scale_log2.load();
+    else if (k == "pair_ops") *value = g_pair_ops.load();
+    else if (k == "scatter_run_merge") *value = g_run_merge.load();
+    else if (k == "backward_tc") *value = g_backward_tc.load();
+    else return nb_set_error(NB_ERR_INVALID, "nb_get_tuning: unknown key");
     return NB_OK;
 }
 
@@ -431,6 +460,6 @@ extern "C" int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d
         return nb_set_error(NB_ERR_INVALID, "nb_hash_scatter_backward: misaligned device pointer");
     if (n == 0) return NB_OK;
     GridParams gp = make_params(desc);
-    if (reinterpret_cast<uintptr_t>(d_table_grads) & 15u) gp.pair_ops = 0;
+    if ((reinterpret_cast<uintptr_t>(d_table_grads) & 15u) && !gp.grad_half) gp.pair_ops = 0;
     return scatter_launch(gp, d_pos4, (const __half*)d_denc_h, 2 * gp.L, n, d_table_grads, 0, gp.L, (cudaStream_t)stream);
 }

@@ -11,12 +11,17 @@ namespace nb {
 
 extern std::atomic<int> g_pair_ops;   // nb_set_tuning("pair_ops", ...)
 extern std::atomic<int> g_run_merge;  // nb_set_tuning("scatter_run_merge", ...)
+extern std::atomic<int> g_grad_table_half;        // nb_set_tuning("grad_table_half", ...)
+extern std::atomic<int> g_grad_table_scale_log2;  // nb_set_tuning("grad_table_scale_log2", ...)
+inline float grad_table_scale() { return g_grad_table_half.load() ? (float)(1u << g_grad_table_scale_log2.load()) : 1.0f; }
 
 struct GridParams {
     int L, T, dls;
     int run_merge; // > 0: the gradient scatter sums runs of consecutive samples in one cell before reducing, in warps that
                    // have at most this many runs (merging costs about 300 instructions per warp and level)
     int pair_ops;  // non-zero: the two x-neighbours of a corner pair that share an aligned slot pair move as one access
+    int grad_half; // non-zero: the table gradient is one __half2 per entry (4 bytes), every contribution multiplied by
+    float grad_scale;  // grad_scale before it is rounded to fp16; zero: two floats per entry, unscaled
     float scales[NB_MAX_LEVELS];   // forward (encode) resolutions
     float sscales[NB_MAX_LEVELS];  // resolutions of the gradient scatter
 };
@@ -24,6 +29,7 @@ struct GridParams {
 inline GridParams make_params(const nb_grid_desc* d) {
     GridParams p;
     p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start; p.pair_ops = g_pair_ops.load(); p.run_merge = g_run_merge.load();
+    p.grad_half = g_grad_table_half.load() != 0; p.grad_scale = grad_table_scale();
     for (int i = 0; i < NB_MAX_LEVELS; i++) { p.scales[i] = d->scales[i]; p.sscales[i] = d->scatter_scales[i]; }
     return p;
 }
@@ -159,6 +165,22 @@ __device__ __forceinline__ void reduce_corners(const Corners& c, const float (&v
     }
 }
 
+// The same into the half-precision table (one 4-byte entry per corner), contributions scaled before rounding.
+__device__ __forceinline__ void reduce_corners_half(const Corners& c, const float (&v)[16], bool pair_ops, float s, uint32_t* __restrict__ base) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t a = c.idx[2 * j], b = c.idx[2 * j + 1];
+        const uint32_t va = pack_half2(v[4 * j] * s, v[4 * j + 1] * s), vb = pack_half2(v[4 * j + 2] * s, v[4 * j + 3] * s);
+        if (pair_ops && ((a ^ b) == 1u)) {
+            const bool a_hi = (a & 1u) != 0;
+            red_add_h2x2(base + (a & ~1u), a_hi ? vb : va, a_hi ? va : vb);
+        } else {
+            red_add_h2(base + a, va);
+            red_add_h2(base + b, vb);
+        }
+    }
+}
+
 // Adds the gradient of one level (feature pair g) of the warp's 32 samples to the fp32 table gradient: 8 corner
 // entries per sample.  Backward clamp and scatter resolution as hashTableScatter_Backward
 // (networkFusionBackwardHashtable.cu:797-900).  ALL 32 LANES MUST CALL; lanes without a sample pass active = false.
@@ -210,8 +232,15 @@ __device__ __forceinline__ void scatter_level_runs(const GridParams& gp, int lev
 
 __device__ __forceinline__ void scatter_level_warp(const GridParams& gp, int level, float px, float py, float pz, float2 g, bool active,
                                                    float* __restrict__ grads, int lane) {
-    float* base = grads + (size_t)level * gp.T * 2;
     const bool pair_ops = gp.pair_ops != 0;
+    if (gp.grad_half) {
+        uint32_t* base = reinterpret_cast<uint32_t*>(grads) + (size_t)level * gp.T;
+        const float s = gp.grad_scale;
+        scatter_level_runs(gp, level, px, py, pz, g, active, lane,
+                           [&](const Corners& c, const float (&v)[16]) { reduce_corners_half(c, v, pair_ops, s, base); });
+        return;
+    }
+    float* base = grads + (size_t)level * gp.T * 2;
     scatter_level_runs(gp, level, px, py, pz, g, active, lane, [&](const Corners& c, const float (&v)[16]) { reduce_corners(c, v, pair_ops, base); });
 }
 

@@ -15,12 +15,36 @@
 namespace nb {
 
 extern std::atomic<uint64_t> g_launch_count;
+extern std::atomic<int> g_grad_table_half;        // hashgrid.cu: the hash part of a gradient arena is __half2 per entry
+extern std::atomic<int> g_grad_table_scale_log2;
 
 __device__ __forceinline__ float finite_or_zero(float x) { return isfinite(x) ? x : 0.0f; }
 
 struct AdamHyper {
     float lr, beta1, beta2, eps, bc1, bc2, inv_loss_scale;
 };
+
+// Four consecutive gradients of the hash part.  fp32 table: element 4i of the arena.  Half-precision table: the hash
+// part's gradients are packed as fp16 at the start of the arena (8 bytes per group of four), scaled by the factor the
+// scatter applied; the caller folds that factor into inv_loss_scale.
+template <bool GRAD_HALF>
+__device__ __forceinline__ float4 load_hash_grad4(const void* g, int64_t i) {
+    if constexpr (GRAD_HALF) {
+        uint2 raw;
+        asm volatile("ld.global.cs.v2.u32 {%0,%1}, [%2];\n" : "=r"(raw.x), "=r"(raw.y) : "l"(reinterpret_cast<const uint2*>(g) + i));
+        const float2 a = unpack_half2(raw.x), b = unpack_half2(raw.y);
+        return make_float4(a.x, a.y, b.x, b.y);
+    } else {
+        float4 v;
+        asm volatile("ld.global.cs.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(reinterpret_cast<const float4*>(g) + i));
+        return v;
+    }
+}
+template <bool GRAD_HALF>
+__device__ __forceinline__ void clear_hash_grad4(void* g, int64_t i) {
+    if constexpr (GRAD_HALF) reinterpret_cast<uint2*>(g)[i] = make_uint2(0u, 0u);
+    else reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
 
 // optimizerKernel.cu:142-166
 __device__ __forceinline__ bool adam_sparse(float g_raw, float& m, float& v, float& w, const AdamHyper& h) {
@@ -55,25 +79,29 @@ __device__ __forceinline__ void adam_dense(float g_raw, float& m, float& v, floa
 }
 
 // Four consecutive parameters per thread (16-byte loads).  sparse4 / total4 are counts of such groups.
+template <bool GRAD_HALF>
 __global__ void __launch_bounds__(256) adam_arena_kernel(float4* __restrict__ w, uint2* __restrict__ w_h, float4* __restrict__ g,
                                                          float4* __restrict__ m, float4* __restrict__ v, int64_t sparse4,
-                                                         int64_t total4, AdamHyper h, int zero_dense) {
+                                                         int64_t total4, AdamHyper h, AdamHyper h_hash, int zero_dense) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
-        float4 gv = g[i];
         if (i < sparse4) {
+            float4 gv;
+            if constexpr (GRAD_HALF) gv = load_hash_grad4<true>(g, i);
+            else gv = g[i];
             if (gv.x == 0.f && gv.y == 0.f && gv.z == 0.f && gv.w == 0.f) continue;  // untouched group: 16 bytes read, nothing else
             float4 mv = m[i], vv = v[i], wv = w[i];
             uint2 hv = w_h[i];
             __half2 h01 = *reinterpret_cast<__half2*>(&hv.x), h23 = *reinterpret_cast<__half2*>(&hv.y);
-            if (adam_sparse(gv.x, mv.x, vv.x, wv.x, h)) h01 = __halves2half2(__float2half(wv.x), __high2half(h01));
-            if (adam_sparse(gv.y, mv.y, vv.y, wv.y, h)) h01 = __halves2half2(__low2half(h01), __float2half(wv.y));
-            if (adam_sparse(gv.z, mv.z, vv.z, wv.z, h)) h23 = __halves2half2(__float2half(wv.z), __high2half(h23));
-            if (adam_sparse(gv.w, mv.w, vv.w, wv.w, h)) h23 = __halves2half2(__low2half(h23), __float2half(wv.w));
+            if (adam_sparse(gv.x, mv.x, vv.x, wv.x, h_hash)) h01 = __halves2half2(__float2half(wv.x), __high2half(h01));
+            if (adam_sparse(gv.y, mv.y, vv.y, wv.y, h_hash)) h01 = __halves2half2(__low2half(h01), __float2half(wv.y));
+            if (adam_sparse(gv.z, mv.z, vv.z, wv.z, h_hash)) h23 = __halves2half2(__float2half(wv.z), __high2half(h23));
+            if (adam_sparse(gv.w, mv.w, vv.w, wv.w, h_hash)) h23 = __halves2half2(__low2half(h23), __float2half(wv.w));
             m[i] = mv; v[i] = vv; w[i] = wv;
             hv.x = *reinterpret_cast<uint32_t*>(&h01); hv.y = *reinterpret_cast<uint32_t*>(&h23);
             w_h[i] = hv;
-            g[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            clear_hash_grad4<GRAD_HALF>(g, i);
         } else {
+            const float4 gv = g[i];
             float4 mv = m[i], vv = v[i], wv = w[i];
             adam_dense(gv.x, mv.x, vv.x, wv.x, h);
             adam_dense(gv.y, mv.y, vv.y, wv.y, h);
@@ -111,26 +139,27 @@ __device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
     return v;
 }
 
+template <bool GRAD_HALF>
 __global__ void __launch_bounds__(256) adam_peer_kernel(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v, PeerArenas peers,
                                                         int rank, int world, int64_t lo4, int64_t hi4, int64_t sparse4, int64_t total4,
-                                                        AdamHyper h) {
+                                                        AdamHyper h, AdamHyper h_hash) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     // this rank's slice of the hash table
     for (int64_t i = lo4 + first; i < hi4; i += stride) {
-        float4 gv = ld_stream_f4(peers.g[0] + i);
+        float4 gv = load_hash_grad4<GRAD_HALF>(peers.g[0], i);
         for (int r = 1; r < world; r++) {
-            const float4 o = ld_stream_f4(peers.g[r] + i);
+            const float4 o = load_hash_grad4<GRAD_HALF>(peers.g[r], i);
             gv.x += o.x; gv.y += o.y; gv.z += o.z; gv.w += o.w;
         }
         if (gv.x == 0.f && gv.y == 0.f && gv.z == 0.f && gv.w == 0.f) continue;
         float4 mv = m[i], vv = v[i], wv = w[i];
         uint2 hv = peers.w_h[rank][i];
         __half2 h01 = *reinterpret_cast<__half2*>(&hv.x), h23 = *reinterpret_cast<__half2*>(&hv.y);
-        if (adam_sparse(gv.x, mv.x, vv.x, wv.x, h)) h01 = __halves2half2(__float2half(wv.x), __high2half(h01));
-        if (adam_sparse(gv.y, mv.y, vv.y, wv.y, h)) h01 = __halves2half2(__low2half(h01), __float2half(wv.y));
-        if (adam_sparse(gv.z, mv.z, vv.z, wv.z, h)) h23 = __halves2half2(__float2half(wv.z), __high2half(h23));
-        if (adam_sparse(gv.w, mv.w, vv.w, wv.w, h)) h23 = __halves2half2(__low2half(h23), __float2half(wv.w));
+        if (adam_sparse(gv.x, mv.x, vv.x, wv.x, h_hash)) h01 = __halves2half2(__float2half(wv.x), __high2half(h01));
+        if (adam_sparse(gv.y, mv.y, vv.y, wv.y, h_hash)) h01 = __halves2half2(__low2half(h01), __float2half(wv.y));
+        if (adam_sparse(gv.z, mv.z, vv.z, wv.z, h_hash)) h23 = __halves2half2(__float2half(wv.z), __high2half(h23));
+        if (adam_sparse(gv.w, mv.w, vv.w, wv.w, h_hash)) h23 = __halves2half2(__low2half(h23), __float2half(wv.w));
         m[i] = mv; v[i] = vv; w[i] = wv;
         hv.x = *reinterpret_cast<uint32_t*>(&h01); hv.y = *reinterpret_cast<uint32_t*>(&h23);
         for (int r = 0; r < world; r++) peers.w_h[r][i] = hv;
@@ -208,8 +237,15 @@ extern "C" int nb_adam_step(float* d_w, void* d_w_h, float* d_g, float* d_m, flo
     int64_t blocks = (total4 + 255) / 256;
     int64_t cap = (int64_t)nb_num_sms() * 32;
     if (blocks > cap) blocks = cap;
-    adam_arena_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float4*)d_w, (uint2*)d_w_h, (float4*)d_g, (float4*)d_m,
-                                                                          (float4*)d_v, sparse_count / 4, total4, h, zero_dense_grads);
+    const bool grad_half = g_grad_table_half.load() != 0;
+    AdamHyper h_hash = h;
+    if (grad_half) h_hash.inv_loss_scale = inv_loss_scale / (float)(1u << g_grad_table_scale_log2.load());
+    if (grad_half)
+        adam_arena_kernel<true><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float4*)d_w, (uint2*)d_w_h, (float4*)d_g, (float4*)d_m,
+                                                                                    (float4*)d_v, sparse_count / 4, total4, h, h_hash, zero_dense_grads);
+    else
+        adam_arena_kernel<false><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float4*)d_w, (uint2*)d_w_h, (float4*)d_g, (float4*)d_m,
+                                                                                     (float4*)d_v, sparse_count / 4, total4, h, h_hash, zero_dense_grads);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;
@@ -240,8 +276,15 @@ extern "C" int nb_adam_step_peer(float* d_w, float* d_m, float* d_v, const float
     int64_t blocks = (work + 255) / 256;
     const int64_t cap = (int64_t)nb_num_sms() * 8;   // enough loads in flight to cover the latency of the peer reads
     if (blocks > cap) blocks = cap;
-    adam_peer_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float4*)d_w, (float4*)d_m, (float4*)d_v, peers, rank, world, lo4, hi4,
-                                                                         sparse_count / 4, total_count / 4, h);
+    const bool grad_half = g_grad_table_half.load() != 0;
+    AdamHyper h_hash = h;
+    if (grad_half) h_hash.inv_loss_scale = inv_loss_scale / (float)(1u << g_grad_table_scale_log2.load());
+    if (grad_half)
+        adam_peer_kernel<true><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float4*)d_w, (float4*)d_m, (float4*)d_v, peers, rank, world, lo4,
+                                                                                   hi4, sparse_count / 4, total_count / 4, h, h_hash);
+    else
+        adam_peer_kernel<false><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float4*)d_w, (float4*)d_m, (float4*)d_v, peers, rank, world, lo4,
+                                                                                    hi4, sparse_count / 4, total_count / 4, h, h_hash);
     NB_CHECK_LAUNCH();
     g_launch_count++;
     return NB_OK;

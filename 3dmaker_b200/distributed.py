@@ -73,6 +73,17 @@ class CollectiveBuffers:
         return self.registered
 
 
+def _grad_table_half():
+    """Whether the CUDA library keeps the table gradient in half precision (False when the library is not built: the
+    host-side logic of this module is also exercised without it)."""
+    import importlib
+    nbm = importlib.import_module("3dmaker_b200")
+    try:
+        return nbm.grad_table_half()
+    except nbm.NerfB200Error:
+        return False
+
+
 class PeerMemory:
     """Addresses of every rank's copy of an array, for kernels that read and write peer memory (nb_adam_step_peer):
     each rank exports its allocation (cudaIpcGetMemHandle through nb_ipc_export - the address must be the start of a
@@ -137,6 +148,8 @@ class DataParallelTrainer:
         self._peer_g = self._peer_w = None
         if exchange not in ("allreduce", "sharded", "peer"):
             raise ValueError("unknown exchange %r" % (exchange,))
+        if exchange != "peer" and dist is not None and dist.get_world_size() > 1 and _grad_table_half():
+            raise ValueError("the half-precision gradient table needs exchange='peer' (the others treat the gradient arena as one fp32 array)")
         self.exchange = exchange
         self._bytes = {"gradient_out_per_step": 0, "parameters_out_per_step": 0}
         if self.world > 1:

@@ -510,6 +510,10 @@ void InstantNerf::optimizerStep(cudaStream_t stream) {
             throw_on_error(nb_zero_async(m_arena.G(0), m_arena.total * (int64_t)sizeof(float), stream), "optimizer: clear");
             return;
         }
+        int grad_half = 0;
+        nb_get_tuning("grad_table_half", &grad_half);
+        if (grad_half && (m_gradSync || m_shardWorld > 1))
+            throw std::runtime_error("optimizer: the half-precision gradient table cannot be exchanged as one fp32 array; use setPeerExchange");
         auto adam = [&](int64_t off, int64_t sparse, int64_t count, const char* what) {
             throw_on_error(nb_adam_step(m_arena.W(off), m_arena.Wh(off), m_arena.G(off), m_arena.M(off), m_arena.V(off), sparse, count,
                                         m_opts.learningRate, m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),

@@ -101,6 +101,22 @@ class FieldModel:
         t = getattr(self, which)
         return ctypes.c_void_p(t.data_ptr() + off * t.element_size())
 
+    # ---- the table gradient in the precision the library currently keeps it in (nb.set_grad_table_half) ------------
+    def hash_grad(self):
+        """The hash part of the gradient as the library wrote it: fp32 [hash_count], or with the half-precision table
+        fp16 [hash_count] packed at the start of the same memory and scaled by nb.grad_table_scale()."""
+        if nb.grad_table_half():
+            return self.g[:self.hash_count].view(self.torch.float16)[:self.hash_count]
+        return self.g[:self.hash_count]
+
+    def hash_grad_f32(self):
+        """The table gradient as fp32 values without the half-precision table's extra scale (a copy)."""
+        return self.hash_grad().float() / nb.grad_table_scale()
+
+    def hash_grad_ptr(self, off):
+        t = self.hash_grad()
+        return ctypes.c_void_p(t.data_ptr() + off * t.element_size())
+
 
 class SampleTrainer:
     """One optimizer step on explicit samples (position, view direction, target colour):
@@ -246,17 +262,19 @@ class SampleTrainer:
         bc1 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta1), np.float32(m.step_count)))
         bc2 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta2), np.float32(m.step_count)))
         hyper = (self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2), 1.0 / self.loss_scale, 1, nb.stream_ptr(stream))
-        dist.reduce_scatter_tensor(m.g[lo:hi], m.g[:H], op=dist.ReduceOp.SUM)      # in place: the output is this rank's slice
+        gh = m.hash_grad()                                                      # fp32, or fp16 with the half-precision table
+        dist.reduce_scatter_tensor(gh[lo:hi], gh, op=dist.ReduceOp.SUM)         # in place: the output is this rank's slice
         dist.all_reduce(m.g[H:], op=dist.ReduceOp.SUM)
-        nb.check(self.lib.nb_adam_step(m.ptr("w", lo), m.ptr("w_h", lo), m.ptr("g", lo), m.ptr("m", lo), m.ptr("v", lo), shard, shard, *hyper),
+        nb.check(self.lib.nb_adam_step(m.ptr("w", lo), m.ptr("w_h", lo), m.hash_grad_ptr(lo), m.ptr("m", lo), m.ptr("v", lo), shard, shard, *hyper),
                  "nb_adam_step(table slice)")
         nb.check(self.lib.nb_adam_step(m.ptr("w", H), m.ptr("w_h", H), m.ptr("g", H), m.ptr("m", H), m.ptr("v", H), 0, m.total - H, *hyper),
                  "nb_adam_step(networks)")
         # the other slices still hold this rank's unreduced gradient: clear them for the next step's accumulation
+        gb = gh.element_size()
         if lo > 0:
-            nb.check(self.lib.nb_zero_async(m.ptr("g", 0), lo * 4, nb.stream_ptr(stream)), "nb_zero_async")
+            nb.check(self.lib.nb_zero_async(m.hash_grad_ptr(0), lo * gb, nb.stream_ptr(stream)), "nb_zero_async")
         if hi < H:
-            nb.check(self.lib.nb_zero_async(m.ptr("g", hi), (H - hi) * 4, nb.stream_ptr(stream)), "nb_zero_async")
+            nb.check(self.lib.nb_zero_async(m.hash_grad_ptr(hi), (H - hi) * gb, nb.stream_ptr(stream)), "nb_zero_async")
         dist.all_gather_into_tensor(m.w_h[:H], m.w_h[lo:hi])                        # in place as well
 
     def optimizer_step_peer(self, dist, stream=None):
@@ -305,6 +323,8 @@ class SampleTrainer:
         the arena - the allreduce of slice c+1 (NCCL's stream) runs while Adam updates slice c, so only the first
         exchange and the last update are exposed.  Same result as one allreduce followed by optimizer_step()."""
         m = self.model
+        if nb.grad_table_half():
+            raise nb.NerfB200Error("the half-precision gradient table cannot be all-reduced as one fp32 array: use dp_mode 'peer' or 'sharded'")
         if m.step_count < 50000:
             m.step_count += 1
         bc1 = np.float32(1.0) - np.float32(np.power(np.float32(self.beta1), np.float32(m.step_count)))
@@ -337,6 +357,8 @@ class SampleTrainer:
                 self.optimizer_step_synced(grad_sync, stream=stream)
             return
         if grad_sync is not None:
+            if nb.grad_table_half():
+                raise nb.NerfB200Error("the half-precision gradient table cannot be exchanged as one fp32 array: use dp_mode 'peer' or 'sharded'")
             grad_sync(self.model.g)
         self.optimizer_step(stream)
 

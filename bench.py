@@ -483,6 +483,8 @@ def run_ours(args, rank, world, local_rank):
     for kv in args.tune:
         k, v = kv.split("=")
         nb.check(nb.load().nb_set_tuning(k.encode(), int(v)), "nb_set_tuning")
+    if args.grad_half:
+        nb.set_grad_table_half(True, args.grad_scale_log2)
 
     buffers = None
     if world > 1 and args.dp == "allreduce" and not args.plain_buffers:
@@ -619,7 +621,8 @@ def run_ours(args, rank, world, local_rank):
             "config": common_config(world),
             "notes": {"exchange": None if world == 1 else args.dp,
                       "field_kernels": (("fused+scatter" if tr.fused_scatter else "fused") + ("+ordered" if tr.ordered else "")) if tr.fused else "sequence",
-                      "tuning": args.tune, "host_batch_layout": "pos float3 + dir float3 + target half3 (30 B/sample), widened on the device",
+                      "tuning": args.tune, "grad_table": ("fp16 x 2^%d (opt-in A/B)" % args.grad_scale_log2) if args.grad_half else "fp32",
+                      "host_batch_layout": "pos float3 + dir float3 + target half3 (30 B/sample), widened on the device",
                       "numa_node": numa_node},
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "last_loss": loss},
@@ -736,6 +739,8 @@ def run_scene(args, rank, world, local_rank, embedded=False):
     D = importlib.import_module("3dmaker_b200.distributed")
     cfg5 = args.workload == "scene5"
     nranks = 1 if reference else world
+    if args.grad_half and not reference:
+        nb.set_grad_table_half(True, args.grad_scale_log2)
     if cfg5:
         rays = SCENE5_GLOBAL_RAYS // nranks
         opts = nm.default_options(**dict(SCENE5_OPTS, batch_size=SCENE5_GLOBAL_BATCH // nranks, ray_chunk_size=rays))
@@ -807,6 +812,8 @@ def run_scene(args, rank, world, local_rank, embedded=False):
         elif trainer is not None:
             line["config"]["replicas_in_sync"] = in_sync
             line["config"]["exchange"] = trainer.exchange if world > 1 else None
+            if args.grad_half:
+                line["config"]["grad_table"] = "fp16 x 2^%d (opt-in A/B)" % args.grad_scale_log2
             if world > 1:
                 line["config"]["exchange_stats"] = trainer.exchange_stats()
         if not embedded:
@@ -990,6 +997,8 @@ def main():
     ap.add_argument("--render-rounds", action="store_true", help="render workload: render in rounds of samples per ray (A/B; off by default)")
     ap.add_argument("--plain-buffers", action="store_true", help="N > 1: keep the gradient in ordinary device memory instead of memory "
                     "registered with the communicator (A/B)")
+    ap.add_argument("--grad-half", action="store_true", help="keep the table gradient in half precision (A/B; off by default: the reference keeps fp32)")
+    ap.add_argument("--grad-scale-log2", type=int, default=7, help="with --grad-half: contributions are multiplied by 2^this before they are rounded to fp16")
     ap.add_argument("--ordered", action="store_true", help="sort every batch by brick and run the field kernels in that order (A/B; off by default)")
     ap.add_argument("--unfused", action="store_true", help="run the kernel-by-kernel sequence instead of the two field kernels (A/B)")
     ap.add_argument("--reference-cpu", action="store_true", help="reference arm: time the CPU port even when the CUDA build exists")

@@ -131,8 +131,28 @@ int nb_hash_scatter_backward(const nb_grid_desc* desc, const float* d_pos4, cons
  * warp before the reduction, in warps with at most this many runs; default 20, 0 = never), "scatter_smem_levels" (dense levels below it that fit shared memory are
  * accumulated per CTA; default 2), "scatter_level_begin" / "scatter_level_end" (restrict the scatter to a level range),
  * "pair_ops" (x-neighbour corners that share an aligned slot pair are gathered with one 8-byte load and scattered with
- * one 16-byte reduction; default 1).  Results do not depend on these beyond fp32 summation order of the scatter. */
+ * one 16-byte reduction; default 1).  Results do not depend on these beyond fp32 summation order of the scatter.
+ * Further keys, described where they act: "backward_tc", "backward_tc_wait_us" (nb_field_backward), "forward_staged",
+ * "forward_stage_levels", "forward_persistent" (nb_field_forward_ordered).
+ *
+ * "grad_table_half" (default 0) switches the TABLE GRADIENT to half precision, process-wide; the reference keeps fp32
+ * only (TinyMLPHashGrid.h:119).  With it on, the hash part of every gradient array handed to this library -
+ * d_table_grads of nb_hash_scatter_backward / nb_field_backward, the first sparse_count elements of d_g of nb_adam_step
+ * and of the peer arrays of nb_adam_step_peer - is ONE __half2 PER ENTRY (4 bytes, entry e of level l at element
+ * l * T + e) packed at the start of the array, instead of two floats; the array keeps its fp32 size and everything
+ * behind the hash part (network weights and biases) keeps its fp32 place and type.  The scatter multiplies every
+ * contribution by 2^"grad_table_scale_log2" (default 7, 0..24) before rounding it to fp16 (on top of the loss scale the
+ * activations' gradients already carry) and adds it with red.global.add.noftz.f16x2 (x-neighbour corners in one 8-byte
+ * vector reduction); levels accumulated in shared memory are rounded once per CTA.  The optimizer divides by the same
+ * factor.  An entry whose fp16 sum overflows reads as non-finite and is treated like any non-finite gradient: it
+ * counts as zero (optimizerKernel.cu:145-150 does the same for its fp32 gradients).  Set both keys before the first
+ * backward and leave them alone between a backward and the optimizer step that consumes it.  Not available with
+ * gradient exchanges that treat the arena as one fp32 array (all-reduce, reduce-scatter): nb_adam_step_peer reads the
+ * half-precision slices of every rank itself. */
 int nb_set_tuning(const char* key, int value);
+/* Current value of a switch ("grad_table_half", "grad_table_scale_log2", "pair_ops", "scatter_run_merge",
+ * "backward_tc"); NB_ERR_INVALID for any other key. */
+int nb_get_tuning(const char* key, int* value);
 
 /* ---- fused MLP ---------------------------------------------------------------------------- */
 
