@@ -250,6 +250,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
+template <bool GRAD_HALF>
 __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __grid_constant__ GridParams gp, const BackwardArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(8) uint64_t mbar;         // MMAs of the current stage done
@@ -335,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, 2) field_backward_tc_kernel(const __g
 #pragma unroll
                     for (int l = 0; l < 16; l++)
                         if (l >= a.scatter_begin && (l % SCATTER_GROUPS) == group)
-                            scatter_level_warp(gp, l, p.x, p.y, p.z, unpack_half2(pk[l]), has, a.table_grads, lane);
+                            scatter_level_warp<GRAD_HALF>(gp, l, p.x, p.y, p.z, unpack_half2(pk[l]), has, a.table_grads, lane);
                 }
             }
         }
@@ -673,7 +674,7 @@ int launch_field_backward_tc(const GridParams& gp, const tc::BackwardArgs& args_
     if (args.error_flag == nullptr) return nb_set_error(NB_ERR_CUDA, "field backward: no mapped host memory for the error flag");
     const int wait_us = g_backward_tc_wait_us.load();
     args.wait_ns = wait_us <= 0 ? 0ull : (uint64_t)wait_us * 1000ull;
-    auto kern = tc::field_backward_tc_kernel;
+    auto kern = gp.grad_half ? tc::field_backward_tc_kernel<true> : tc::field_backward_tc_kernel<false>;
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES));
     const int64_t ntiles = (args.n + tc::ROWS - 1) / tc::ROWS;
     // Two CTAs per SM: 107 KB of shared memory, 128 registers x 256 threads and 256 tensor-memory columns each.  The grid is

@@ -492,7 +492,7 @@ struct FieldBwd {
     }
 };
 
-template <class DS, class CS>
+template <class DS, class CS, bool GRAD_HALF>
 __global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(const __grid_constant__ GridParams gp, FieldIO io, FieldGradIO gio) {
     using FB = FieldBwd<DS, CS>;
     constexpr int H = FB::H, IS = FB::IS, HS = FB::HS;
@@ -650,7 +650,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(const __
                 if (has) p = ld_nc_f4(gio.pos4 + row * 4);
                 for (int level = gio.scatter_begin + hsel; level < gp.L; level += 2) {
                     const float2 gq = __half22float2(*reinterpret_cast<const __half2*>(&sDZ[r * HS + 2 * level]));
-                    scatter_level_warp(gp, level, p.x, p.y, p.z, gq, has, gio.table_grads, lane);
+                    scatter_level_warp<GRAD_HALF>(gp, level, p.x, p.y, p.z, gq, has, gio.table_grads, lane);
                 }
             }
             __syncthreads();
@@ -838,7 +838,7 @@ static int field_backward_impl(const nb_mlp_desc* density, const nb_mlp_desc* co
             return nb::scatter_launch(gp, d_pos4, (const __half*)d_denc_h, 4 * shared_levels, n, d_table_grads, 0, shared_levels, (cudaStream_t)stream);
         return NB_OK;
     }
-    auto kern = nb::field_backward_kernel<DensityNet, ColorNet>;
+    auto kern = (scatter && gp.grad_half) ? nb::field_backward_kernel<DensityNet, ColorNet, true> : nb::field_backward_kernel<DensityNet, ColorNet, false>;
     size_t smem = nb::FieldBwd<DensityNet, ColorNet>::smem_bytes();
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int per_sm = 0;

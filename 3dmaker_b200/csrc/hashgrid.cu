@@ -118,6 +118,7 @@ std::atomic<int> g_grad_table_scale_log2{7};
 
 // Gradient scatter, one thread per (sample, level), level = level_base + blockIdx.y so that all CTAs resident at one
 // time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector reduction.
+template <bool GRAD_HALF>
 __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
                                                                const __half* __restrict__ dEnc, int denc_stride, int64_t n,
                                                                float* __restrict__ grads, int level_base) {
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
         p = ld_nc_f4(pos4 + i * 4);
         g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
     }
-    scatter_level_warp(gp, level, p.x, p.y, p.z, g, has, grads, threadIdx.x & 31);
+    scatter_level_warp<GRAD_HALF>(gp, level, p.x, p.y, p.z, g, has, grads, threadIdx.x & 31);
 }
 
 // Coarse dense levels whose whole grid fits shared memory: every CTA accumulates its share of the samples into a
@@ -249,7 +250,8 @@ int scatter_launch(const GridParams& gp, const float* d_pos4, const __half* d_de
     }
     if (le > smem_end) {
         dim3 grid((unsigned)((n + 255) / 256), le - smem_end, 1);
-        scatter_backward_kernel<<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end);
+        if (gp.grad_half) scatter_backward_kernel<true><<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end);
+        else scatter_backward_kernel<false><<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end);
         NB_CHECK_LAUNCH();
         g_launch_count++;
     }

@@ -230,18 +230,21 @@ __device__ __forceinline__ void scatter_level_runs(const GridParams& gp, int lev
     scatter_runs(gp, c, g, active, lane, sink);
 }
 
+// GRAD_HALF is a compile-time choice (kernels exist in both forms and the launchers pick by gp.grad_half): the scatter
+// is unrolled over 16 levels inside the field kernels and a run-time branch here doubles that code.
+template <bool GRAD_HALF = false>
 __device__ __forceinline__ void scatter_level_warp(const GridParams& gp, int level, float px, float py, float pz, float2 g, bool active,
                                                    float* __restrict__ grads, int lane) {
     const bool pair_ops = gp.pair_ops != 0;
-    if (gp.grad_half) {
+    if constexpr (GRAD_HALF) {
         uint32_t* base = reinterpret_cast<uint32_t*>(grads) + (size_t)level * gp.T;
         const float s = gp.grad_scale;
         scatter_level_runs(gp, level, px, py, pz, g, active, lane,
                            [&](const Corners& c, const float (&v)[16]) { reduce_corners_half(c, v, pair_ops, s, base); });
-        return;
+    } else {
+        float* base = grads + (size_t)level * gp.T * 2;
+        scatter_level_runs(gp, level, px, py, pz, g, active, lane, [&](const Corners& c, const float (&v)[16]) { reduce_corners(c, v, pair_ops, base); });
     }
-    float* base = grads + (size_t)level * gp.T * 2;
-    scatter_level_runs(gp, level, px, py, pz, g, active, lane, [&](const Corners& c, const float (&v)[16]) { reduce_corners(c, v, pair_ops, base); });
 }
 
 // ---- coarse levels from shared memory ------------------------------------------------------------------------------
