@@ -186,7 +186,8 @@ class DataParallelTrainer:
                 wire = (self.world - 1) / self.world
                 # what crosses NVLink per step: the other ranks read (N - 1) / N of this gradient table, this rank stores its
                 # fp16 slice into N - 1 peers, and everybody reads everybody's dense tail
-                self._bytes = {"gradient_out_per_step": int(self._hash * 4 * wire + (self._total - self._hash) * 4 * (self.world - 1)),
+                gbytes = 2 if _grad_table_half() else 4
+                self._bytes = {"gradient_out_per_step": int(self._hash * gbytes * wire + (self._total - self._hash) * 4 * (self.world - 1)),
                                "parameters_out_per_step": int(self._hash * 2 * wire)}
             else:
                 engine.set_grad_sync(self._allreduce)
