@@ -170,6 +170,9 @@ _SIGNATURES = {
                                          c_void_p, c_void_p, c_int, c_void_p]),
     "nb_sample_order_scratch_bytes": (c_int64, []),
     "nb_sample_order": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "nb_field_forward_mse": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                             c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "nb_field_forward_ordered": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_int, c_void_p]),

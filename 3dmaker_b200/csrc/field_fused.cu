@@ -102,10 +102,20 @@ struct FieldSmem {
     }
 };
 
-template <class DS, class CS>
+// MSE loss against per-sample target colours, taken in the forward's epilogue (the arithmetic of mse_loss_grad_kernel,
+// optim.cu, on the colour the kernel has in registers): grad[n][8] fp16 = dL/d(colour pre-activation) x loss scale,
+// total += sum of squared differences.
+struct FieldLossIO {
+    const __half* target;   // [n][8] fp16, columns >= 3 ignored
+    __half* grad;           // [n][8] fp16
+    float* total;           // nullable
+    float grad_scale;       // 2 / (n * 3) * loss scale
+};
+
+template <class DS, class CS, bool WITH_LOSS>
 __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid_constant__ GridParams gp, FieldIO io, __half* __restrict__ enc_save,
                                                                     float* __restrict__ sigma_out, float* __restrict__ logit_out,
-                                                                    float* __restrict__ rgb_out, int rgb_stride) {
+                                                                    float* __restrict__ rgb_out, int rgb_stride, FieldLossIO lio) {
     static_assert(DS::OUT == 16 && CS::K0 == 32, "the colour network takes 16 density features and 16 SH coefficients");
     using FS = FieldSmem<DS, CS>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -132,38 +142,78 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid
     if (enc_save != nullptr) store_enc_tile<FS::ENC_STRIDE>(tile, enc_save, gp.L, row_base, io.n, tid);
 
     const int64_t row0 = row_base + warp * 16;
-    if (row0 >= io.n) return;
-    // density network, output kept in registers
-    uint32_t a[DS::K0 / 16][4];
+    if constexpr (!WITH_LOSS) {
+        if (row0 >= io.n) return;
+    }
+    float sq = 0.f;   // WITH_LOSS: this thread's share of the squared differences
+    if (!WITH_LOSS || row0 < io.n) {
+        // density network, output kept in registers
+        uint32_t a[DS::K0 / 16][4];
 #pragma unroll
-    for (int kc = 0; kc < DS::K0 / 16; kc++) {
-        int q = lane >> 3, r = lane & 7;
-        ldmatrix_x4(a[kc], &tile[(warp * 16 + r + (q & 1) * 8) * FS::ENC_STRIDE + 16 * kc + (q >> 1) * 8]);
-    }
-    FwdCtx dx{};
-    dx.sW = sWd; dx.sBias = sBd; dx.row0 = row0; dx.n = io.n; dx.lane = lane;
-    float dout[2][4];
-    forward_layers<DS, 0, 0, true>(a, dx, dout);
-    // clamp, sigma, SH -> colour input fragments
-    uint32_t ca[2][4];
-    float raw0, raw1;
-    build_color_input(dout, io, row0, lane, ca, raw0, raw1);
-    if (t == 0) {
-        int64_t r0 = row0 + g, r1 = r0 + 8;
-        if (r0 < io.n) {
-            if (logit_out) logit_out[r0] = raw0;
-            if (sigma_out) sigma_out[r0] = expf(fminf(sanitize_logit_f(raw0) - io.density_bias, 8.0f));
+        for (int kc = 0; kc < DS::K0 / 16; kc++) {
+            int q = lane >> 3, r = lane & 7;
+            ldmatrix_x4(a[kc], &tile[(warp * 16 + r + (q & 1) * 8) * FS::ENC_STRIDE + 16 * kc + (q >> 1) * 8]);
         }
-        if (r1 < io.n) {
-            if (logit_out) logit_out[r1] = raw1;
-            if (sigma_out) sigma_out[r1] = expf(fminf(sanitize_logit_f(raw1) - io.density_bias, 8.0f));
+        FwdCtx dx{};
+        dx.sW = sWd; dx.sBias = sBd; dx.row0 = row0; dx.n = io.n; dx.lane = lane;
+        float dout[2][4];
+        forward_layers<DS, 0, 0, true>(a, dx, dout);
+        // clamp, sigma, SH -> colour input fragments
+        uint32_t ca[2][4];
+        float raw0, raw1;
+        build_color_input(dout, io, row0, lane, ca, raw0, raw1);
+        if (t == 0) {
+            int64_t r0 = row0 + g, r1 = r0 + 8;
+            if (r0 < io.n) {
+                if (logit_out) logit_out[r0] = raw0;
+                if (sigma_out) sigma_out[r0] = expf(fminf(sanitize_logit_f(raw0) - io.density_bias, 8.0f));
+            }
+            if (r1 < io.n) {
+                if (logit_out) logit_out[r1] = raw1;
+                if (sigma_out) sigma_out[r1] = expf(fminf(sanitize_logit_f(raw1) - io.density_bias, 8.0f));
+            }
+        }
+        // colour network, sigmoid output, rgb (+ the padding column) written rgb_stride floats apart
+        FwdCtx cx{};
+        cx.sW = sWc; cx.sBias = sBc; cx.row0 = row0; cx.n = io.n; cx.lane = lane;
+        cx.out = rgb_out; cx.out_stride = rgb_stride; cx.out_valid = rgb_stride < 8 ? 4 : 8;
+        if constexpr (!WITH_LOSS) {
+            forward_layers<CS, 0, 1, false>(ca, cx);
+        } else {
+            float fin[1][4];
+            forward_layers<CS, 0, 1, true>(ca, cx, fin);
+            const int col = 2 * t;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int64_t r = row0 + g + 8 * h;
+                if (r >= io.n) continue;
+                const float px = fin[0][2 * h], py = fin[0][2 * h + 1];
+                if (col < cx.out_valid) *reinterpret_cast<float2*>(&rgb_out[r * rgb_stride + col]) = make_float2(px, py);
+                const float2 tg = __half22float2(*reinterpret_cast<const __half2*>(&lio.target[r * 8 + col]));
+                const float dxv = (col < 3) ? (px - tg.x) : 0.0f;
+                const float dyv = (col + 1 < 3) ? (py - tg.y) : 0.0f;
+                sq += (dxv * dxv) + (dyv * dyv);
+                float gx = dxv * lio.grad_scale, gy = dyv * lio.grad_scale;
+                gx *= px * (1.0f - px);
+                gy *= py * (1.0f - py);
+                *reinterpret_cast<__half2*>(&lio.grad[r * 8 + col]) = __floats2half2_rn(gx, gy);
+            }
         }
     }
-    // colour network, sigmoid output, rgb (+ the padding column) written rgb_stride floats apart
-    FwdCtx cx{};
-    cx.sW = sWc; cx.sBias = sBc; cx.row0 = row0; cx.n = io.n; cx.lane = lane;
-    cx.out = rgb_out; cx.out_stride = rgb_stride; cx.out_valid = rgb_stride < 8 ? 4 : 8;
-    forward_layers<CS, 0, 1, false>(ca, cx);
+    if constexpr (WITH_LOSS) {
+        // one addition per CTA to the total; the tile is free by now, its first words carry the warps' sums
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_down_sync(0xffffffffu, sq, o);
+        __syncthreads();
+        float* warp_sums = reinterpret_cast<float*>(tile);
+        if (lane == 0) warp_sums[warp] = sq;
+        __syncthreads();
+        if (tid == 0 && lio.total != nullptr) {
+            float total = 0.f;
+            for (int k = 0; k < CTA_THREADS / 32; k++) total += warp_sums[k];
+            atomicAdd(lio.total, total);
+        }
+    }
 }
 
 
@@ -700,7 +750,8 @@ static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* densi
                                 const void* d_table_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
                                 const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
                                 int64_t n, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
-                                int rgb_stride, const uint32_t* d_count, void* stream, const uint32_t* d_perm = nullptr) {
+                                int rgb_stride, const uint32_t* d_count, void* stream, const uint32_t* d_perm = nullptr,
+                                const nb::FieldLossIO* loss = nullptr) {
     if (!grid || !density || !color || !d_pos4 || !d_table_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b ||
         !d_rgb || n < 0)
         return nb_set_error(NB_ERR_INVALID, "nb_field_forward: null pointer or negative count");
@@ -719,6 +770,17 @@ static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* densi
     nb::GridParams gp = nb::make_params(grid);
     if (misaligned(d_table_h, 8)) gp.pair_ops = 0;
     const int staged_mode = nb::g_forward_staged.load();
+    if (loss != nullptr) {
+        auto kern = nb::field_forward_kernel<DensityNet, ColorNet, true>;
+        size_t smem = nb::FieldSmem<DensityNet, ColorNet>::fwd_bytes();
+        NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
+        kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride,
+                                                                                  *loss);
+        NB_CHECK_LAUNCH();
+        nb::g_launch_count++;
+        return NB_OK;
+    }
     if (d_perm != nullptr || staged_mode == 1) {
         if (staged_mode == 0) return nb_set_error(NB_ERR_INVALID, "nb_field_forward_ordered: the staged forward is switched off (forward_staged = 0)");
         auto kern = nb::field_forward_staged_kernel<DensityNet, ColorNet>;
@@ -738,11 +800,12 @@ static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* densi
         nb::g_launch_count++;
         return NB_OK;
     }
-    auto kern = nb::field_forward_kernel<DensityNet, ColorNet>;
+    auto kern = nb::field_forward_kernel<DensityNet, ColorNet, false>;
     size_t smem = nb::FieldSmem<DensityNet, ColorNet>::fwd_bytes();
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
-    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride);
+    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride,
+                                                                              nb::FieldLossIO{});
     NB_CHECK_LAUNCH();
     nb::g_launch_count++;
     return NB_OK;
@@ -755,6 +818,20 @@ extern "C" int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* den
                                 int rgb_stride, void* stream) {
     return field_forward_impl(grid, density, color, d_pos4, d_table_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b,
                               d_color_w_h, d_color_b, n, density_bias, d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride, nullptr, stream);
+}
+
+extern "C" int nb_field_forward_mse(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                                    const void* d_table_h, const float* d_dirs3, const void* d_density_w_h, const float* d_density_b,
+                                    const void* d_color_w_h, const float* d_color_b, int64_t n, float density_bias, void* d_enc_save_h,
+                                    float* d_sigma, float* d_logit0, float* d_rgb, int rgb_stride, const void* d_target_h, void* d_dcolor_h,
+                                    float* d_total_loss, float loss_scale, void* stream) {
+    if (!d_target_h || !d_dcolor_h) return nb_set_error(NB_ERR_INVALID, "nb_field_forward_mse: null target or gradient");
+    if (misaligned(d_target_h, 4) || misaligned(d_dcolor_h, 4)) return nb_set_error(NB_ERR_INVALID, "nb_field_forward_mse: misaligned target or gradient");
+    nb::FieldLossIO lio{};
+    lio.target = (const __half*)d_target_h; lio.grad = (__half*)d_dcolor_h; lio.total = d_total_loss;
+    lio.grad_scale = n > 0 ? (2.0f / (float)(n * 3)) * loss_scale : 0.0f;   // as nb_mse_loss_grad with valid_dim 3
+    return field_forward_impl(grid, density, color, d_pos4, d_table_h, d_dirs3, nullptr, 0, d_density_w_h, d_density_b, d_color_w_h, d_color_b, n,
+                              density_bias, d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride, nullptr, stream, nullptr, &lio);
 }
 
 extern "C" int nb_field_forward_ordered(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,

@@ -123,13 +123,15 @@ class SampleTrainer:
     the 'encode + MLP fwd/bwd + Adam' step of the benchmark.  Buffers are sized once for max_batch."""
 
     def __init__(self, model, max_batch, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-15, loss_scale=128.0, density_bias=0.0, fused=None, fused_scatter=None,
-                 ordered=None):
+                 ordered=None, fused_loss=None):
         """fused=None picks the two-kernel field path (nb_field_forward / nb_field_backward) when it is built for
         the model's shapes, else the kernel-by-kernel sequence; True / False force one of them.  fused_scatter
         (default: on with the fused path) lets the backward kernel scatter the table gradient itself.  ordered
         (default: off) sorts the samples of every step by brick first (nb_sample_order) and runs the field kernels in
         that order (nb_field_forward_ordered / nb_field_backward_ordered); measured on uniformly scattered samples it
-        does not pay - the eleven hashed levels, whose entries have no locality in any order, set the pace."""
+        does not pay - the eleven hashed levels, whose entries have no locality in any order, set the pace.  fused_loss
+        (default: on with the fused, unordered path) takes the MSE loss and its gradient in the forward kernel's epilogue
+        (nb_field_forward_mse) instead of a launch of its own."""
         torch = model.torch
         self.model, self.torch, self.lib = model, torch, model.lib
         self.max_batch = max_batch
@@ -140,6 +142,7 @@ class SampleTrainer:
         self.fused = supported if fused is None else bool(fused)
         self.fused_scatter = self.fused if fused_scatter is None else (bool(fused_scatter) and self.fused)
         self.ordered = False if ordered is None else (bool(ordered) and self.fused)
+        self.fused_loss = (self.fused and not self.ordered) if fused_loss is None else (bool(fused_loss) and self.fused and not self.ordered)
         n, dev = max_batch, "cuda"
         d, c = model.density, model.color
         f16, f32 = torch.float16, torch.float32
@@ -191,12 +194,19 @@ class SampleTrainer:
             if self.fused_scatter:
                 return
         elif self.fused:
-            nb.check(lib.nb_field_forward(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(self.pos), m.ptr("w_h", 0),
-                                          P(self.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
-                                          m.ptr("w", m.off_cb), n, self.density_bias, P(self.enc), P(self.sigma), P(self.logit0),
-                                          P(self.c_out), 8, st), "nb_field_forward")
-            nb.check(lib.nb_mse_loss_grad(P(self.c_out), P(self.target), P(self.c_grad), P(self.loss), n, 8, 3, self.loss_scale, 1, st),
-                     "nb_mse_loss_grad")
+            if self.fused_loss:
+                nb.check(lib.nb_field_forward_mse(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(self.pos), m.ptr("w_h", 0),
+                                                  P(self.dirs), m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
+                                                  m.ptr("w", m.off_cb), n, self.density_bias, P(self.enc), P(self.sigma), P(self.logit0),
+                                                  P(self.c_out), 8, P(self.target), P(self.c_grad), P(self.loss), self.loss_scale, st),
+                         "nb_field_forward_mse")
+            else:
+                nb.check(lib.nb_field_forward(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(self.pos), m.ptr("w_h", 0),
+                                              P(self.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw),
+                                              m.ptr("w", m.off_cb), n, self.density_bias, P(self.enc), P(self.sigma), P(self.logit0),
+                                              P(self.c_out), 8, st), "nb_field_forward")
+                nb.check(lib.nb_mse_loss_grad(P(self.c_out), P(self.target), P(self.c_grad), P(self.loss), n, 8, 3, self.loss_scale, 1, st),
+                         "nb_mse_loss_grad")
             nb.check(lib.nb_field_backward(ctypes.byref(m.density), ctypes.byref(m.color), P(self.enc), P(self.dirs), None, 0,
                                            m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n,
                                            P(self.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db), m.ptr("g", m.off_cw),

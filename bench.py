@@ -352,7 +352,14 @@ def time_kernels(torch, tr, n, iters=5):
                 m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, P(tr.order), P(tr.c_grad), None, m.ptr("g", m.off_dw), m.ptr("g", m.off_db),
                 m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc), ctypes.byref(m.grid), P(tr.pos), m.ptr("g", 0), st)
     elif tr.fused:
-        calls = {
+        calls = {}
+        if tr.fused_loss:
+            # the step's forward: loss and colour gradient taken in its epilogue
+            calls["field_forward_mse"] = lambda: lib.nb_field_forward_mse(
+                ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(tr.pos), m.ptr("w_h", 0), P(tr.dirs), m.ptr("w_h", m.off_dw),
+                m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, tr.density_bias, P(tr.enc), P(tr.sigma), P(tr.logit0),
+                P(tr.c_out), 8, P(tr.target), P(tr.c_grad), P(tr.loss), tr.loss_scale, st)
+        calls.update({
             "field_forward": lambda: lib.nb_field_forward(ctypes.byref(m.grid), ctypes.byref(m.density), ctypes.byref(m.color), P(tr.pos),
                                                           m.ptr("w_h", 0), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db),
                                                           m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb), n, tr.density_bias, P(tr.enc),
@@ -364,7 +371,7 @@ def time_kernels(torch, tr, n, iters=5):
                                                             m.ptr("g", m.off_db), m.ptr("g", m.off_cw), m.ptr("g", m.off_cb), P(tr.d_enc),
                                                             None, None, None, st),
             "scatter_backward": lambda: lib.nb_hash_scatter_backward(ctypes.byref(m.grid), P(tr.pos), P(tr.d_enc), n, m.ptr("g", 0), st),
-        }
+        })
         if tr.fused_scatter:
             calls["field_backward_scatter"] = lambda: lib.nb_field_backward(
                 ctypes.byref(m.density), ctypes.byref(m.color), P(tr.enc), P(tr.dirs), None, 0, m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db),
@@ -499,7 +506,7 @@ def run_ours(args, rank, world, local_rank):
     table, dW, db, cW, cb = init_params()
     model.load_hashgrid(table); model.load_density_weights(dW, db); model.load_color_weights(cW, cb)
     tr = pl.SampleTrainer(model, BATCH, fused=False if args.unfused else None, fused_scatter=False if args.separate_scatter else None,
-                          ordered=True if args.ordered else None, **HYPER)
+                          ordered=True if args.ordered else None, fused_loss=False if args.separate_loss else None, **HYPER)
 
     # two distinct seeded batches per rank: resident on the device in the kernels' layouts (`value`), and pinned on the
     # host in the compact layout they travel in (`e2e`: position float3, direction float3, target three halves = 30 B)
@@ -621,7 +628,7 @@ def run_ours(args, rank, world, local_rank):
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": common_config(world),
             "notes": {"exchange": None if world == 1 else args.dp,
-                      "field_kernels": (("fused+scatter" if tr.fused_scatter else "fused") + ("+ordered" if tr.ordered else "")) if tr.fused else "sequence",
+                      "field_kernels": (("fused+scatter" if tr.fused_scatter else "fused") + ("+ordered" if tr.ordered else "") + ("+loss" if tr.fused_loss else "")) if tr.fused else "sequence",
                       "tuning": args.tune, "grad_table": ("fp16 x 2^%d (opt-in A/B)" % args.grad_scale_log2) if args.grad_half else "fp32",
                       "host_batch_layout": "pos float3 + dir float3 + target half3 (30 B/sample), widened on the device",
                       "numa_node": numa_node},
@@ -997,6 +1004,7 @@ def main():
                     help="scene workloads at N > 1: all-reduce + replicated Adam; reduce-scatter + Adam on a table slice + all-gather of fp16 "
                          "parameters; or the same three stages as one kernel over peer memory (default)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
+    ap.add_argument("--separate-loss", action="store_true", help="keep the MSE loss a launch of its own instead of the forward's epilogue (A/B)")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
     ap.add_argument("--dp", default="peer", choices=["peer", "sharded", "allreduce", "sliced"],
                     help="N > 1: how the gradient is exchanged (peer: one kernel per rank that sums the ranks' gradients of its table slice "

@@ -259,6 +259,17 @@ int nb_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const
                      const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
                      float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb, int rgb_stride,
                      void* stream);
+/* nb_field_forward for explicit samples (direction i belongs to sample i) followed by nb_mse_loss_grad on its colour
+ * output (valid_dim 3, padded_dim 8, sigmoid derivative folded in), in one launch: the loss is taken in the forward's
+ * epilogue from the colour it still has in registers.  Replaces TinyMLP::forward -> launchMSELossGrad
+ * (modules/TinyMLP/optimizerKernel.cu:169-224, 380-400) for the field.  d_target_h fp16 [n][8], d_dcolor_h fp16 [n][8]
+ * (what nb_field_backward takes), *d_total_loss (nullable) is ADDED the sum of squared differences. */
+int nb_field_forward_mse(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,
+                         const void* d_table_h, const float* d_dirs3, const void* d_density_w_h, const float* d_density_b,
+                         const void* d_color_w_h, const float* d_color_b, int64_t n, float density_bias, void* d_enc_save_h,
+                         float* d_sigma, float* d_logit0, float* d_rgb, int rgb_stride, const void* d_target_h, void* d_dcolor_h,
+                         float* d_total_loss, float loss_scale, void* stream);
+
 
 /* nb_field_forward for rendering when the sample count is known only on the device: the launch covers n_max samples
  * and tiles at or behind *d_count (read when the kernel runs; at most n_max) leave at once. */

@@ -500,3 +500,36 @@ def test_random_access_probe_counts_its_operations(cuda, nb):
     torch.cuda.synchronize()
     assert torch.equal(table, before)
     assert lib.nb_probe_random_access(2, 12, 8, 16, P(table), nb.stream_ptr()) == 1
+
+
+@pytest.mark.parametrize("n", [1, 127, 128, 129, 5000, 70000])
+def test_forward_with_the_loss_in_its_epilogue_equals_forward_then_loss_kernel(cuda, nb, n):
+    """nb_field_forward_mse against nb_field_forward + nb_mse_loss_grad: same colours, sigma, saved encoding (bit for
+    bit: the same code ran), the same fp16 colour gradient (the same expression on the same fp32 colour; the compiler may
+    contract it differently in the two kernels, so a last-bit difference in a few values is allowed) and the same loss
+    up to summation order."""
+    torch = cuda
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    L, T = 16, 1 << 15
+    model = pl.FieldModel(torch, L, T, 16, 1.3819, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    pos, dirs, tgt = _inputs(n, 17)
+    got = {}
+    for fused_loss in (False, True):
+        tr = pl.SampleTrainer(model, n, loss_scale=128.0, density_bias=1.0, fused=True, ordered=False, fused_loss=fused_loss)
+        assert tr.fused_loss == fused_loss
+        tr.pos.copy_(torch.from_numpy(pos)); tr.dirs.copy_(torch.from_numpy(dirs)); tr.target.copy_(torch.from_numpy(tgt.view(np.float16)))
+        tr.c_grad.fill_(7.0)
+        model.g.zero_()
+        tr.forward_backward(n)
+        torch.cuda.synchronize()
+        got[fused_loss] = dict(rgb=tr.c_out[:n].cpu().numpy().copy(), sigma=tr.sigma[:n].cpu().numpy().copy(), enc=dev_half_bits(tr.enc[:n]).copy(),
+                               grad=half_vals(dev_half_bits(tr.c_grad[:n])).copy(), loss=float(tr.loss.item()), g=model.g.cpu().numpy().copy())
+    model.g.zero_()
+    a, b = got[False], got[True]
+    assert np.array_equal(a["rgb"], b["rgb"]) and np.array_equal(a["sigma"], b["sigma"]) and np.array_equal(a["enc"], b["enc"])
+    assert np.all(b["grad"][:, 3:] == 0)
+    assert np.mean(a["grad"] != b["grad"]) < 1e-3 and rel_err(b["grad"], a["grad"]) <= 1e-3
+    assert abs(a["loss"] - b["loss"]) <= 1e-5 * max(a["loss"], 1e-30)
+    assert rel_err(b["g"], a["g"]) <= 2e-3
