@@ -139,6 +139,7 @@ class StepView(ctypes.Structure):
 GRAD_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
 PARAM_SYNC_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_int64, c_void_p)
 BARRIER_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p)
+BLOCK_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p, c_void_p, c_int64, c_void_p)
 
 
 class NerfB200Error(RuntimeError):
@@ -170,6 +171,13 @@ _SIGNATURES = {
                                          c_void_p, c_void_p, c_int, c_void_p]),
     "nb_sample_order_scratch_bytes": (c_int64, []),
     "nb_sample_order": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "nb_part_stamp_count": (c_int, [c_void_p, c_int64, c_int64, c_void_p]),
+    "nb_part_encode": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nb_part_field_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_int, c_int64, c_void_p, c_void_p,
+                              c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_int, c_void_p]),
+    "nb_part_pack_denc": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
+    "nb_part_scatter": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_field_forward_mse": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
@@ -259,6 +267,8 @@ _SIGNATURES = {
                                           c_void_p]),
     "nb_nerf_set_hit_counts_capacity": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
+    "nb_nerf_set_level_partition": (c_int, [c_void_p, ctypes.c_uint32, ctypes.c_uint32, BLOCK_FN, BLOCK_FN, GRAD_SYNC_FN, c_void_p]),
+    "nb_nerf_sync_levels": (c_int, [c_void_p, c_int, c_void_p]),
     "nb_nerf_set_grad_buffer": (c_int, [c_void_p, c_void_p, c_int64]),
     "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),
     "nb_nerf_load_params": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

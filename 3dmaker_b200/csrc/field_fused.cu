@@ -112,10 +112,31 @@ struct FieldLossIO {
     float grad_scale;       // 2 / (n * 3) * loss scale
 };
 
-template <class DS, class CS, bool WITH_LOSS>
+// The encoding of this rank's samples as the level owners delivered it (level_partition.cu): piece q holds the levels
+// q, q + ranks, ... of every sample, level-major, `cap` samples per level.
+struct FieldPiecesIO {
+    const uint32_t* pieces;
+    int ranks;
+    int64_t cap;
+};
+
+// tile[r][2l .. 2l+1] = level l of row row_base + r, taken from the pieces (zero behind the last sample)
+template <int TILE_STRIDE>
+__device__ __forceinline__ void load_pieces_tile(const FieldPiecesIO& pio, int L, int64_t row_base, int64_t n, __half* tile, int tid) {
+    const int own = L / pio.ranks;
+    for (int idx = tid; idx < L * TILE_ROWS; idx += CTA_THREADS) {
+        const int l = idx / TILE_ROWS, r = idx - l * TILE_ROWS;
+        const int64_t row = row_base + r;
+        const uint32_t v = row < n ? __ldg(pio.pieces + ((int64_t)(l % pio.ranks) * own + l / pio.ranks) * pio.cap + row) : 0u;
+        *reinterpret_cast<uint32_t*>(&tile[r * TILE_STRIDE + 2 * l]) = v;
+    }
+}
+
+template <class DS, class CS, bool WITH_LOSS, bool FROM_PIECES = false>
 __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid_constant__ GridParams gp, FieldIO io, __half* __restrict__ enc_save,
                                                                     float* __restrict__ sigma_out, float* __restrict__ logit_out,
-                                                                    float* __restrict__ rgb_out, int rgb_stride, FieldLossIO lio) {
+                                                                    float* __restrict__ rgb_out, int rgb_stride, FieldLossIO lio,
+                                                                    FieldPiecesIO pio) {
     static_assert(DS::OUT == 16 && CS::K0 == 32, "the colour network takes 16 density features and 16 SH coefficients");
     using FS = FieldSmem<DS, CS>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -136,7 +157,8 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_kernel(const __grid
     load_weights_to_smem<DS>(io.Wd, io.bd, sWd, sBd, tid);
     load_weights_to_smem<CS>(io.Wc, io.bc, sWc, sBc, tid);
     cp_async_commit();
-    encode_tile<FS::ENC_STRIDE>(gp, io.pos4, io.table2, row_base, io.n, tile, tid);
+    if constexpr (FROM_PIECES) load_pieces_tile<FS::ENC_STRIDE>(pio, gp.L, row_base, io.n, tile, tid);
+    else encode_tile<FS::ENC_STRIDE>(gp, io.pos4, io.table2, row_base, io.n, tile, tid);
     cp_async_wait_all();
     __syncthreads();
     if (enc_save != nullptr) store_enc_tile<FS::ENC_STRIDE>(tile, enc_save, gp.L, row_base, io.n, tid);
@@ -278,7 +300,7 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_staged_kernel(const
             staged = plan.count;
         }
         for (int l = 0; l < staged; l++) {
-            const uint32_t* tl = io.table2 + (size_t)l * gp.T;
+            const uint32_t* tl = io.table2 + (size_t)l * gp.ls;
             const int N_l = __float2int_rd(gp.scales[l]);
             const bool dense = l < gp.dls;
             const int w = plan.w[l], wh = plan.wh[l], cnt = plan.whd[l], base = plan.base[l];
@@ -315,7 +337,7 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_staged_kernel(const
                         } else {
                             Corners c;
                             corners_from_box(ba, la < gp.dls, gp.T, c);
-                            gather_corners(io.table2 + (size_t)la * gp.T, c, gp.pair_ops != 0, fa);
+                            gather_corners(io.table2 + (size_t)la * gp.ls, c, gp.pair_ops != 0, fa);
                         }
                         if (has_b) {
                             if (lb < staged && staged_corners(plan, lb, bb, loc)) {
@@ -324,7 +346,7 @@ __global__ void __launch_bounds__(CTA_THREADS) field_forward_staged_kernel(const
                             } else {
                                 Corners c;
                                 corners_from_box(bb, lb < gp.dls, gp.T, c);
-                                gather_corners(io.table2 + (size_t)lb * gp.T, c, gp.pair_ops != 0, fb);
+                                gather_corners(io.table2 + (size_t)lb * gp.ls, c, gp.pair_ops != 0, fb);
                             }
                         }
                         Corners wa, wb;
@@ -776,7 +798,7 @@ static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* densi
         NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
         kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride,
-                                                                                  *loss);
+                                                                                  *loss, nb::FieldPiecesIO{});
         NB_CHECK_LAUNCH();
         nb::g_launch_count++;
         return NB_OK;
@@ -805,7 +827,7 @@ static int field_forward_impl(const nb_grid_desc* grid, const nb_mlp_desc* densi
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
     kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride,
-                                                                              nb::FieldLossIO{});
+                                                                              nb::FieldLossIO{}, nb::FieldPiecesIO{});
     NB_CHECK_LAUNCH();
     nb::g_launch_count++;
     return NB_OK;
@@ -832,6 +854,38 @@ extern "C" int nb_field_forward_mse(const nb_grid_desc* grid, const nb_mlp_desc*
     lio.grad_scale = n > 0 ? (2.0f / (float)(n * 3)) * loss_scale : 0.0f;   // as nb_mse_loss_grad with valid_dim 3
     return field_forward_impl(grid, density, color, d_pos4, d_table_h, d_dirs3, nullptr, 0, d_density_w_h, d_density_b, d_color_w_h, d_color_b, n,
                               density_bias, d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride, nullptr, stream, nullptr, &lio);
+}
+
+extern "C" int nb_part_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, int ranks, int64_t capacity,
+                                     const void* d_pieces_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                                     const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
+                                     int64_t n, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
+                                     int rgb_stride, void* stream) {
+    if (!grid || !density || !color || !d_pieces_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b || !d_rgb || n < 0)
+        return nb_set_error(NB_ERR_INVALID, "nb_part_field_forward: null pointer or negative count");
+    if (!nb_field_supported(grid, density, color))
+        return nb_set_error(NB_ERR_UNSUPPORTED, "nb_part_field_forward: built for 16 levels, density 32-64-16 and colour 32-64-64-8 (sigmoid)");
+    if (ranks < 1 || grid->num_levels % ranks != 0 || capacity < n) return nb_set_error(NB_ERR_INVALID, "nb_part_field_forward: ranks must divide the levels, capacity >= n");
+    if (rgb_stride != 4 && rgb_stride != 8) return nb_set_error(NB_ERR_INVALID, "nb_part_field_forward: rgb_stride must be 4 or 8");
+    if (misaligned(d_pieces_h, 4) || misaligned(d_density_w_h, 16) || misaligned(d_color_w_h, 16) || misaligned(d_enc_save_h, 16) || misaligned(d_rgb, 8) ||
+        misaligned(d_density_b, 8) || misaligned(d_color_b, 8))
+        return nb_set_error(NB_ERR_INVALID, "nb_part_field_forward: misaligned device pointer");
+    if (n == 0) return NB_OK;
+    nb::FieldIO io{};
+    io.dirs3 = d_dirs3; io.ray_idx = d_ray_indices; io.ray_idx_offset = ray_index_offset;
+    io.Wd = (const __half*)d_density_w_h; io.bd = d_density_b; io.Wc = (const __half*)d_color_w_h; io.bc = d_color_b;
+    io.n = n; io.density_bias = density_bias;
+    nb::GridParams gp = nb::make_params(grid);
+    nb::FieldPiecesIO pio{reinterpret_cast<const uint32_t*>(d_pieces_h), ranks, capacity};
+    auto kern = nb::field_forward_kernel<DensityNet, ColorNet, false, true>;
+    size_t smem = nb::FieldSmem<DensityNet, ColorNet>::fwd_bytes();
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t grid_dim = (n + nb::TILE_ROWS - 1) / nb::TILE_ROWS;
+    kern<<<(unsigned)grid_dim, nb::CTA_THREADS, smem, (cudaStream_t)stream>>>(gp, io, (__half*)d_enc_save_h, d_sigma, d_logit0, d_rgb, rgb_stride,
+                                                                              nb::FieldLossIO{}, pio);
+    NB_CHECK_LAUNCH();
+    nb::g_launch_count++;
+    return NB_OK;
 }
 
 extern "C" int nb_field_forward_ordered(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, const float* d_pos4,

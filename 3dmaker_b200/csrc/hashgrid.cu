@@ -116,21 +116,46 @@ std::atomic<int> g_run_merge{20};
 std::atomic<int> g_grad_table_half{0};
 std::atomic<int> g_grad_table_scale_log2{7};
 
+// Where a scatter kernel finds sample i's position and the gradient of its encoding on a level.
+// RowsDenc: the samples of one batch, gradients row-major ([n][denc_stride] halves, level l at columns 2l, 2l + 1).
+struct RowsDenc {
+    const float* pos4; const __half* denc; int stride; int64_t n;
+    __device__ __forceinline__ int64_t rows() const { return n; }
+    __device__ __forceinline__ bool fetch(int64_t i, int level, float4& p, float2& g) const {
+        if (i >= n) return false;
+        p = ld_nc_f4(pos4 + i * 4);
+        g = __half22float2(*reinterpret_cast<const __half2*>(&denc[i * stride + 2 * level]));
+        return true;
+    }
+};
+// PiecesDenc: the samples of ALL ranks of a level-partitioned grid (level_partition.cu): rank q's slot of the gathered
+// positions holds `cap` positions and its sample count in element `cap`; the gradients of the owner's level k for rank q's
+// samples are the contiguous run pieces[(q * own + k) * cap ...].
+struct PiecesDenc {
+    const float* pos_all; const uint32_t* pieces; int ranks, own; int64_t cap;
+    __device__ __forceinline__ int64_t rows() const { return (int64_t)ranks * cap; }
+    __device__ __forceinline__ bool fetch(int64_t i, int level, float4& p, float2& g) const {
+        const int q = (int)(i / cap);
+        const int64_t j = i - (int64_t)q * cap;
+        if (q >= ranks) return false;
+        const float* slot = pos_all + (int64_t)q * (cap + 1) * 4;
+        if (j >= (int64_t)__float_as_uint(__ldg(slot + cap * 4))) return false;
+        p = ld_nc_f4(slot + j * 4);
+        g = unpack_half2(__ldg(pieces + ((int64_t)q * own + level) * cap + j));
+        return true;
+    }
+};
+
 // Gradient scatter, one thread per (sample, level), level = level_base + blockIdx.y so that all CTAs resident at one
 // time work on the same 2T-float slice of the gradient table.  A feature pair is one 8-byte vector reduction.
-template <bool GRAD_HALF>
-__global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
-                                                               const __half* __restrict__ dEnc, int denc_stride, int64_t n,
-                                                               float* __restrict__ grads, int level_base) {
+template <bool GRAD_HALF, class Fetch>
+__global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_constant__ GridParams gp, const Fetch in, float* __restrict__ grads,
+                                                               int level_base) {
     const int level = level_base + blockIdx.y;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool has = i < n;
     float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
     float2 g = make_float2(0.f, 0.f);
-    if (has) {
-        p = ld_nc_f4(pos4 + i * 4);
-        g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
-    }
+    const bool has = in.fetch(i, level, p, g);
     scatter_level_warp<GRAD_HALF>(gp, level, p.x, p.y, p.z, g, has, grads, threadIdx.x & 31);
 }
 
@@ -139,9 +164,9 @@ __global__ void __launch_bounds__(256) scatter_backward_kernel(const __grid_cons
 // heavily contended coarse entries see (#CTAs) global reductions instead of (#samples x 8).  Runs of consecutive
 // samples in one cell are merged in the warp first (scatter_level_runs): on these levels a ray spends ten or more
 // samples per cell, and same-address shared-memory atomics serialise.
-__global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant__ GridParams gp, const float* __restrict__ pos4,
-                                                           const __half* __restrict__ dEnc, int denc_stride, int64_t n,
-                                                           float* __restrict__ grads, int level_base) {
+template <class Fetch>
+__global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant__ GridParams gp, const Fetch in, float* __restrict__ grads,
+                                                           int level_base) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* acc = reinterpret_cast<float2*>(smem_raw);
     const int level = level_base + blockIdx.y;
@@ -151,15 +176,12 @@ __global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant
     for (int c = threadIdx.x; c < cells; c += blockDim.x) acc[c] = make_float2(0.f, 0.f);
     __syncthreads();
     const int lane = threadIdx.x & 31;
+    const int64_t n = in.rows();
     for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x; i0 < n; i0 += (int64_t)gridDim.x * blockDim.x) {
         const int64_t i = i0 + threadIdx.x;
-        const bool has = i < n;
         float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
         float2 g = make_float2(0.f, 0.f);
-        if (has) {
-            p = ld_nc_f4(pos4 + i * 4);
-            g = __half22float2(*reinterpret_cast<const __half2*>(&dEnc[i * denc_stride + 2 * level]));
-        }
+        const bool has = in.fetch(i, level, p, g);
         scatter_level_runs(gp, level, p.x, p.y, p.z, g, has, lane, [&](const Corners& c, const float (&v)[16]) {
 #pragma unroll
             for (int k = 0; k < 8; k++) {
@@ -170,14 +192,14 @@ __global__ void __launch_bounds__(256) scatter_smem_kernel(const __grid_constant
     }
     __syncthreads();
     if (gp.grad_half) {
-        uint32_t* base = reinterpret_cast<uint32_t*>(grads) + (size_t)level * gp.T;
+        uint32_t* base = reinterpret_cast<uint32_t*>(grads) + (size_t)level * gp.ls;
         for (int c = threadIdx.x; c < cells; c += blockDim.x) {
             float2 v = acc[c];
             if (v.x != 0.f || v.y != 0.f) red_add_h2(base + c, pack_half2(v.x * gp.grad_scale, v.y * gp.grad_scale));
         }
         return;
     }
-    float* base = grads + (size_t)level * gp.T * 2;
+    float* base = grads + (size_t)level * gp.ls * 2;
     for (int c = threadIdx.x; c < cells; c += blockDim.x) {
         float2 v = acc[c];
         if (v.x != 0.f || v.y != 0.f) red_add_v2(base + (size_t)c * 2, v.x, v.y);
@@ -228,34 +250,48 @@ int scatter_shared_levels(const GridParams& gp, int64_t n) {
     return k;
 }
 
-int scatter_launch(const GridParams& gp, const float* d_pos4, const __half* d_denc, int denc_stride, int64_t n, float* d_table_grads,
-                   int level_begin, int level_end, cudaStream_t st) {
+// Launches the scatter of levels [level_begin, level_end) over in.rows() samples; n_hint = how many of them are real
+// (decides whether the shared-memory kernel is worth its fixed cost).
+template <class Fetch>
+static int scatter_launch_from(const GridParams& gp, const Fetch& in, int64_t rows, int64_t n_hint, float* d_table_grads, int level_begin,
+                               int level_end, cudaStream_t st) {
     const ScatterTuning tn = g_scatter_tuning;
     const int lb = std::max(level_begin, std::max(0, tn.level_begin)), le = std::min(level_end, std::min(gp.L, tn.level_end));
-    if (le <= lb) return NB_OK;
-    const int smem_end = std::max(lb, std::min(le, scatter_shared_levels(gp, n)));
+    if (le <= lb || rows <= 0) return NB_OK;
+    const int smem_end = std::max(lb, std::min(le, scatter_shared_levels(gp, n_hint)));
     if (smem_end > lb) {
         size_t smem_bytes = 0;
         for (int l = lb; l < smem_end; l++) {
             int N_l = (int)std::floor(gp.sscales[l]);
             smem_bytes = std::max(smem_bytes, (size_t)(N_l + 1) * (N_l + 1) * (N_l + 1) * sizeof(float2));
         }
-        NB_CUDA(cudaFuncSetAttribute(scatter_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+        NB_CUDA(cudaFuncSetAttribute(scatter_smem_kernel<Fetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         int per_level = std::max(1, nb_num_sms() * 2 / (smem_end - lb));
-        int64_t need = (n + 255) / 256;
+        int64_t need = (rows + 255) / 256;
         dim3 grid((unsigned)std::min<int64_t>(per_level, need), smem_end - lb, 1);
-        scatter_smem_kernel<<<grid, 256, smem_bytes, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, lb);
+        scatter_smem_kernel<Fetch><<<grid, 256, smem_bytes, st>>>(gp, in, d_table_grads, lb);
         NB_CHECK_LAUNCH();
         g_launch_count++;
     }
     if (le > smem_end) {
-        dim3 grid((unsigned)((n + 255) / 256), le - smem_end, 1);
-        if (gp.grad_half) scatter_backward_kernel<true><<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end);
-        else scatter_backward_kernel<false><<<grid, 256, 0, st>>>(gp, d_pos4, d_denc, denc_stride, n, d_table_grads, smem_end);
+        dim3 grid((unsigned)((rows + 255) / 256), le - smem_end, 1);
+        if (gp.grad_half) scatter_backward_kernel<true, Fetch><<<grid, 256, 0, st>>>(gp, in, d_table_grads, smem_end);
+        else scatter_backward_kernel<false, Fetch><<<grid, 256, 0, st>>>(gp, in, d_table_grads, smem_end);
         NB_CHECK_LAUNCH();
         g_launch_count++;
     }
     return NB_OK;
+}
+
+int scatter_launch(const GridParams& gp, const float* d_pos4, const __half* d_denc, int denc_stride, int64_t n, float* d_table_grads,
+                   int level_begin, int level_end, cudaStream_t st) {
+    return scatter_launch_from(gp, RowsDenc{d_pos4, d_denc, denc_stride, n}, n, n, d_table_grads, level_begin, level_end, st);
+}
+
+int scatter_launch_pieces(const GridParams& view, const float* d_pos_all, const uint32_t* d_pieces, int ranks, int own, int64_t cap,
+                          float* d_table_grads_view, cudaStream_t st) {
+    return scatter_launch_from(view, PiecesDenc{d_pos_all, d_pieces, ranks, own, cap}, (int64_t)ranks * cap, (int64_t)ranks * cap, d_table_grads_view, 0,
+                               view.L, st);
 }
 
 }  // namespace nb

@@ -17,6 +17,8 @@ inline float grad_table_scale() { return g_grad_table_half.load() ? (float)(1u <
 
 struct GridParams {
     int L, T, dls;
+    int ls;        // entries between the starts of consecutive levels in the table and its gradient: T for a whole grid,
+                   // ranks * T for the view of the levels one rank owns (level_view)
     int run_merge; // > 0: the gradient scatter sums runs of consecutive samples in one cell before reducing, in warps that
                    // have at most this many runs (merging costs about 300 instructions per warp and level)
     int pair_ops;  // non-zero: the two x-neighbours of a corner pair that share an aligned slot pair move as one access
@@ -28,9 +30,26 @@ struct GridParams {
 
 inline GridParams make_params(const nb_grid_desc* d) {
     GridParams p;
-    p.L = d->num_levels; p.T = d->table_size; p.dls = d->dense_level_start; p.pair_ops = g_pair_ops.load(); p.run_merge = g_run_merge.load();
+    p.L = d->num_levels; p.T = d->table_size; p.ls = d->table_size; p.dls = d->dense_level_start; p.pair_ops = g_pair_ops.load(); p.run_merge = g_run_merge.load();
     p.grad_half = g_grad_table_half.load() != 0; p.grad_scale = grad_table_scale();
     for (int i = 0; i < NB_MAX_LEVELS; i++) { p.scales[i] = d->scales[i]; p.sscales[i] = d->scatter_scales[i]; }
+    return p;
+}
+
+// The grid as the owner of levels rank, rank + ranks, rank + 2 ranks, ... sees it: those levels renumbered 0, 1, ...,
+// resolutions picked accordingly, consecutive levels ranks * T entries apart.  Pointers into the table or its gradient
+// that go with this view start at level `rank` (first_level_offset entries into the array).  Dense levels stay a prefix
+// because resolutions grow with the level.
+inline GridParams level_view(const GridParams& whole, int rank, int ranks) {
+    GridParams p = whole;
+    p.L = whole.L / ranks;
+    p.ls = whole.T * ranks;
+    p.dls = 0;
+    for (int k = 0; k < p.L; k++) {
+        const int l = rank + k * ranks;
+        p.scales[k] = whole.scales[l]; p.sscales[k] = whole.sscales[l];
+        if (l < whole.dls) p.dls = k + 1;
+    }
     return p;
 }
 
@@ -131,8 +150,8 @@ __device__ __forceinline__ void encode_tile(const GridParams& gp, const float* _
             Corners ca, cb;
             corners_of<false>(p.x, p.y, p.z, gp.scales[la], la < gp.dls, gp.T, ca);
             corners_of<false>(p.x, p.y, p.z, gp.scales[has_b ? lb : la], (has_b ? lb : la) < gp.dls, gp.T, cb);
-            const uint32_t* ta = table2 + (size_t)la * gp.T;
-            const uint32_t* tb = table2 + (size_t)(has_b ? lb : la) * gp.T;
+            const uint32_t* ta = table2 + (size_t)la * gp.ls;
+            const uint32_t* tb = table2 + (size_t)(has_b ? lb : la) * gp.ls;
             uint32_t fa[8], fb[8];
             gather_corners(ta, ca, gp.pair_ops != 0, fa);
             gather_corners(tb, cb, gp.pair_ops != 0, fb);
@@ -237,12 +256,12 @@ __device__ __forceinline__ void scatter_level_warp(const GridParams& gp, int lev
                                                    float* __restrict__ grads, int lane) {
     const bool pair_ops = gp.pair_ops != 0;
     if constexpr (GRAD_HALF) {
-        uint32_t* base = reinterpret_cast<uint32_t*>(grads) + (size_t)level * gp.T;
+        uint32_t* base = reinterpret_cast<uint32_t*>(grads) + (size_t)level * gp.ls;
         const float s = gp.grad_scale;
         scatter_level_runs(gp, level, px, py, pz, g, active, lane,
                            [&](const Corners& c, const float (&v)[16]) { reduce_corners_half(c, v, pair_ops, s, base); });
     } else {
-        float* base = grads + (size_t)level * gp.T * 2;
+        float* base = grads + (size_t)level * gp.ls * 2;
         scatter_level_runs(gp, level, px, py, pz, g, active, lane, [&](const Corners& c, const float (&v)[16]) { reduce_corners(c, v, pair_ops, base); });
     }
 }
@@ -368,6 +387,10 @@ __device__ __forceinline__ void plan_stage(const GridParams& gp, const float* __
 int scatter_shared_levels(const GridParams& gp, int64_t n);
 int scatter_launch(const GridParams& gp, const float* d_pos4, const __half* d_denc, int denc_stride, int64_t n, float* d_table_grads,
                    int level_begin, int level_end, cudaStream_t st);
+// The same for the owner of some levels of a level-partitioned grid (level_partition.cu): `view` = level_view of the
+// grid, samples of all ranks from the gathered position slots, gradients from the received pieces.
+int scatter_launch_pieces(const GridParams& view, const float* d_pos_all, const uint32_t* d_pieces, int ranks, int own, int64_t cap,
+                          float* d_table_grads_view, cudaStream_t st);
 
 // Coalesced write of the encoded tile (128 x 2L halves) to global memory.
 template <int TILE_STRIDE>

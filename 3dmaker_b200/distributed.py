@@ -135,7 +135,13 @@ class DataParallelTrainer:
       "peer"       the same three stages as ONE kernel per rank (nb_adam_step_peer): the slice's gradients are loaded
                    from every rank's memory over NVLink, the updated fp16 slice is stored into every rank's forward
                    copy, a one-element all-reduce before and after keeps the ranks together.  GPUs of one node only;
-                   the engine's arenas must be its own allocations (no registered_gradient)."""
+                   the engine's arenas must be its own allocations (no registered_gradient);
+      "levels"     the table is not replicated at all: rank r OWNS levels r, r + N, ... (engine.set_level_partition).  Per
+                   step one all-gather of the ranks' sample positions, one all-to-all of encodings, one all-to-all of
+                   their gradients (128 bytes per sample in all) and an all-reduce of the networks' few thousand gradients;
+                   no table gradient and no table parameter crosses the wire.  For tables that outweigh a step's samples
+                   (T = 2^22: 805 MB of table traffic per step and rank against 34-270 MB of encodings).  The levels a
+                   rank does not own go stale between occupancy updates: sync() before rendering, saving or comparing."""
 
     def __init__(self, torch, engine, dist=None, steps_per_call=1, registered_gradient=False, exchange="allreduce"):
         self.torch, self.engine, self.dist = torch, engine, dist
@@ -146,15 +152,15 @@ class DataParallelTrainer:
         self.sync_calls = 0
         self.buffers = None
         self._peer_g = self._peer_w = None
-        if exchange not in ("allreduce", "sharded", "peer"):
+        if exchange not in ("allreduce", "sharded", "peer", "levels"):
             raise ValueError("unknown exchange %r" % (exchange,))
-        if exchange != "peer" and dist is not None and dist.get_world_size() > 1 and _grad_table_half():
+        if exchange not in ("peer", "levels") and dist is not None and dist.get_world_size() > 1 and _grad_table_half():
             raise ValueError("the half-precision gradient table needs exchange='peer' (the others treat the gradient arena as one fp32 array)")
         self.exchange = exchange
         self._bytes = {"gradient_out_per_step": 0, "parameters_out_per_step": 0}
         if self.world > 1:
-            if exchange == "peer":
-                registered_gradient = False      # the kernel reads the engine's own allocation through an IPC mapping
+            if exchange in ("peer", "levels"):
+                registered_gradient = False      # peer: the kernel reads the engine's own allocation; levels: no table gradient travels
             if registered_gradient and hasattr(engine, "set_grad_buffer"):
                 # the gradient arena moves into memory registered with the communicator
                 self.buffers = CollectiveBuffers(torch, dist, "cuda:%d" % torch.cuda.current_device())
@@ -189,6 +195,11 @@ class DataParallelTrainer:
                 gbytes = 2 if _grad_table_half() else 4
                 self._bytes = {"gradient_out_per_step": int(self._hash * gbytes * wire + (self._total - self._hash) * 4 * (self.world - 1)),
                                "parameters_out_per_step": int(self._hash * 2 * wire)}
+            elif exchange == "levels":
+                engine.set_grad_sync(None)
+                engine.set_level_partition(self.rank, self.world, self._gather_blocks, self._exchange_blocks, self._allreduce)
+                self._bytes = {"gradient_out_per_step": int((self._total - self._hash) * 4 * 2 * (self.world - 1) / self.world),
+                               "parameters_out_per_step": 0, "per_sample_out": 16 * (self.world - 1) + int(2 * 64 * (self.world - 1) / self.world)}
             else:
                 engine.set_grad_sync(self._allreduce)
                 self._bytes = {"gradient_out_per_step": int(self._total * 4 * 2 * (self.world - 1) / self.world), "parameters_out_per_step": 0}
@@ -208,6 +219,19 @@ class DataParallelTrainer:
         self.dist.reduce_scatter_tensor(grad[lo:lo + self._shard], grad[:self._hash], op=self.dist.ReduceOp.SUM)   # in place
         self.dist.all_reduce(grad[self._hash:self._total], op=self.dist.ReduceOp.SUM)
 
+    def _gather_blocks(self, send, recv):
+        self.sync_calls += 1
+        self.dist.all_gather_into_tensor(recv, send)
+
+    def _exchange_blocks(self, send, recv):
+        self.sync_calls += 1
+        self.dist.all_to_all_single(recv, send)
+
+    def sync(self, master=False):
+        """exchange="levels": every rank's copy of the table is made whole again (all ranks call it)."""
+        if self.world > 1 and self.exchange == "levels":
+            self.engine.sync_levels(master)
+
     def _barrier(self):
         self.sync_calls += 1
         self.dist.all_reduce(self._token, op=self.dist.ReduceOp.SUM)
@@ -222,6 +246,8 @@ class DataParallelTrainer:
             w = self.engine.arena_tensor("w")
             lo = self.rank * self._shard
             self.dist.all_gather_into_tensor(w[:self._hash], w[lo:lo + self._shard])
+        if self.world > 1 and self.exchange == "levels":
+            self.sync(master=True)
 
     def exchange_stats(self):
         """Bytes this rank sends per optimizer step (ring accounting: (N - 1) / N of a buffer per reduce-scatter or
@@ -238,6 +264,8 @@ class DataParallelTrainer:
                 self.dist.barrier()              # nobody unmaps memory a peer's kernel may still be using
                 self.engine.set_peer_exchange(0, 1, None, None, None)
                 self._peer_g.close(); self._peer_w.close()
+            if self.exchange == "levels":
+                self.engine.set_level_partition(0, 1, None, None, None)
             self.engine.set_grad_sync(None)
 
     def train_rays(self, rays_o, rays_d, rgb_true):
@@ -256,7 +284,8 @@ class DataParallelTrainer:
     def replicas_in_sync(self):
         """True when every rank holds bit-identical parameters: compares the 64-bit sum of the raw bits of the fp16 copy
         the forward reads (with the sharded optimizer the fp32 master copy of a slice is current on its owner only)."""
-        owner_only = self.exchange in ("sharded", "peer")
+        owner_only = self.exchange in ("sharded", "peer", "levels")
+        self.sync()                       # exchange="levels": make the table whole first (a collective: every rank is here)
         w = self.engine.arena_tensor("w_h" if owner_only else "w")
         s = w.view(self.torch.int16 if owner_only else self.torch.int32).to(self.torch.int64).sum().reshape(1)
         if self.world == 1:

@@ -162,7 +162,8 @@ void InstantNerf::initRenderBuffers() {
     d_render_rgb.allocate(R * 3 * sizeof(float)); d_render_depth.allocate(R * sizeof(float)); d_phi.allocate(R * 3 * sizeof(float));
     d_weight_sum.allocate(R * sizeof(float));
 
-    d_positions.allocate(B * 4 * sizeof(float)); d_ray_indices.allocate(B * sizeof(uint32_t)); d_t_sorted.allocate(B * sizeof(float));
+    d_positions.allocate((B + 1) * 4 * sizeof(float));   // + the slot's count element of a level-partitioned step
+    d_ray_indices.allocate(B * sizeof(uint32_t)); d_t_sorted.allocate(B * sizeof(float));
     d_positions2.allocate(B * 4 * sizeof(float)); d_ray_indices2.allocate(B * sizeof(uint32_t)); d_t_sorted2.allocate(B * sizeof(float));
     d_sigma2.allocate(B * sizeof(float)); d_color_out2.allocate(B * 4 * sizeof(float));
     d_density_out.allocate(std::max(B, (size_t)G + 16) * 16 * sizeof(float));
@@ -388,6 +389,7 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
         // It only reads the parameters, which do not change before the optimizer below; the walk above used the old bits,
         // as the reference's march of this step does, and the next step walks again.
         if (m_trainSteps % 16 == 0) {
+            if (m_partWorld > 1) syncLevels(stream);     // the density queries of the update read every level
             timed(stream, m_times.occupancy, [&]() {
                 if (m_trainSteps < 256) earlyOccupancyGridUpdate(stream);
                 else lateOccupancyGridUpdate(stream);
@@ -396,7 +398,9 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
         }
 
         const int logitStride = m_fused ? 1 : 16, colorStride = m_fused ? 4 : 8;
-        if (n > 0 && m_fused) {
+        if (m_partWorld > 1) {
+            timed(stream, m_times.densityFwd, [&]() { partitionedForward(chunk_d, n, colorStride, stream); });
+        } else if (n > 0 && m_fused) {
             timed(stream, m_times.densityFwd, [&]() {
                 throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()), chunk_d,
                                                 d_ray_indices.as<uint32_t>(), 0, m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()),
@@ -436,7 +440,9 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                                              d_dw.as<float>(), d_weight_sum.as<float>(), d_color_grad.as<half>(), 8, d_tmpsigma.as<float>(),
                                              m_opts.lossScale, m_opts.densityBias, numRays * m_rayScale, stream), "loss gradients");
             });
-            if (m_fused) {
+            if (m_partWorld > 1) {
+                // below, outside this block: every rank takes part in the exchange whether or not it has samples
+            } else if (m_fused) {
                 timed(stream, m_times.colorBwd, [&]() {
                     throw_on_error(nb_field_backward(&dn->desc(), &cn->desc(), d_enc.as<half>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
                                                      m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
@@ -465,6 +471,7 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                 });
             }
         }
+        if (m_partWorld > 1) timed(stream, m_times.colorBwd, [&]() { partitionedBackward(chunk_d, n, stream); });
         if (m_gradSync) m_gradSync(m_arena.G(0), m_arena.total, stream);
         optimizerStep(stream);
         trainStepCount++;
@@ -496,6 +503,80 @@ void InstantNerf::setPeerExchange(uint32_t rank, uint32_t world, const std::vect
     m_paramSync = ParamSync();
 }
 
+void InstantNerf::setLevelPartition(uint32_t rank, uint32_t world, BlockGather gather, BlockExchange exchange, GradSync reduce) {
+    if (world <= 1) {
+        m_partRank = 0; m_partWorld = 1; m_partGather = BlockGather(); m_partExchange = BlockExchange(); m_partReduce = GradSync();
+        d_pos_all.release(); d_pieces_send.release(); d_pieces_recv.release();
+        return;
+    }
+    const int levels = m_densityMLP->grid().num_levels;
+    if (rank >= world || levels % (int)world != 0) throw std::runtime_error("setLevelPartition: rank below world, world a divisor of the number of levels");
+    if (!gather || !exchange || !reduce) throw std::runtime_error("setLevelPartition: the three collectives are required");
+    if (!m_fused) throw std::runtime_error("setLevelPartition: needs the fused field kernels");
+    if (m_shardWorld > 1 || !m_peerGrads.empty()) throw std::runtime_error("setLevelPartition: not together with a replicated-table exchange");
+    if (m_arena.sparse_count != (int64_t)levels * m_densityMLP->grid().table_size * 2) throw std::runtime_error("setLevelPartition: unexpected table layout");
+    const size_t B = (size_t)m_opts.batchSize;
+    d_pos_all.allocate((size_t)world * (B + 1) * 4 * sizeof(float));
+    d_pieces_send.allocate((size_t)levels * B * sizeof(uint32_t));
+    d_pieces_recv.allocate((size_t)levels * B * sizeof(uint32_t));
+    m_partRank = rank; m_partWorld = world;
+    m_partGather = std::move(gather); m_partExchange = std::move(exchange); m_partReduce = std::move(reduce);
+}
+
+// Owned levels -> every rank, level block by level block: levels k * world ... (k + 1) * world - 1 are contiguous in the
+// arena and this rank's level is block `rank` of them, which is the in-place form of an all-gather.
+void InstantNerf::syncLevels(cudaStream_t stream, bool master) {
+    if (m_partWorld <= 1) return;
+    const int levels = m_densityMLP->grid().num_levels;
+    const int64_t level = m_arena.sparse_count / levels;
+    for (int k = 0; k < levels / (int)m_partWorld; k++) {
+        const int64_t block = (int64_t)k * m_partWorld * level, mine = block + (int64_t)m_partRank * level;
+        m_partGather(m_arena.Wh(mine), m_arena.Wh(block), level * (int64_t)sizeof(half), stream);
+        if (master) m_partGather(m_arena.W(mine), m_arena.W(block), level * (int64_t)sizeof(float), stream);
+    }
+}
+
+// Forward of a level-partitioned step: positions to everybody, the owned levels encoded for everybody's samples, pieces
+// to the samples' ranks, networks from the received pieces.  Runs on every rank in every step, with or without samples.
+void InstantNerf::partitionedForward(const float* chunk_d, int64_t n, int colorStride, cudaStream_t stream) {
+    TinyMLPHashGrid* dn = m_densityMLP;
+    TinyMLP* cn = m_colorMLP;
+    const int64_t B = (int64_t)m_opts.batchSize;
+    const int world = (int)m_partWorld, rank = (int)m_partRank;
+    throw_on_error(nb_part_stamp_count(d_positions.as<float>(), B, n, stream), "partition: count");
+    m_partGather(d_positions.as<float>(), d_pos_all.as<float>(), (B + 1) * 4 * (int64_t)sizeof(float), stream);
+    throw_on_error(nb_part_encode(&dn->grid(), world, rank, B, d_pos_all.as<float>(), m_arena.Wh(dn->hashOffset()), d_pieces_send.as<void>(), stream),
+                   "partition: encode");
+    const int64_t piece = (int64_t)(dn->grid().num_levels / world) * B * (int64_t)sizeof(uint32_t);
+    m_partExchange(d_pieces_send.as<void>(), d_pieces_recv.as<void>(), piece, stream);
+    if (n > 0)
+        throw_on_error(nb_part_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), world, B, d_pieces_recv.as<void>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
+                                             m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
+                                             m_arena.W(cn->biasOffset()), n, m_opts.densityBias, d_enc.as<half>(), d_sigma.as<float>(),
+                                             d_density_out.as<float>(), d_color_out.as<float>(), colorStride, stream), "partition: field forward");
+}
+
+// Backward: the networks' gradients and dL/d(encoding) of this rank's samples, the latter packed by owner, exchanged, and
+// scattered by every owner into its levels for everybody's samples (positions still in d_pos_all from the forward).
+void InstantNerf::partitionedBackward(const float* chunk_d, int64_t n, cudaStream_t stream) {
+    TinyMLPHashGrid* dn = m_densityMLP;
+    TinyMLP* cn = m_colorMLP;
+    const int64_t B = (int64_t)m_opts.batchSize;
+    const int world = (int)m_partWorld, rank = (int)m_partRank;
+    if (n > 0) {
+        throw_on_error(nb_field_backward(&dn->desc(), &cn->desc(), d_enc.as<half>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
+                                         m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
+                                         m_arena.W(cn->biasOffset()), n, d_color_grad.as<half>(), d_tmpsigma.as<float>(),
+                                         m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()), m_arena.G(cn->weightOffset()),
+                                         m_arena.G(cn->biasOffset()), d_denc.as<half>(), nullptr, nullptr, nullptr, stream), "partition: field backward");
+    }
+    throw_on_error(nb_part_pack_denc(&dn->grid(), world, B, d_denc.as<half>(), n, d_pieces_send.as<void>(), stream), "partition: pack");
+    const int64_t piece = (int64_t)(dn->grid().num_levels / world) * B * (int64_t)sizeof(uint32_t);
+    m_partExchange(d_pieces_send.as<void>(), d_pieces_recv.as<void>(), piece, stream);
+    throw_on_error(nb_part_scatter(&dn->grid(), world, rank, B, d_pos_all.as<float>(), d_pieces_recv.as<void>(), m_arena.G(dn->hashOffset()), stream),
+                   "partition: scatter");
+}
+
 void InstantNerf::optimizerStep(cudaStream_t stream) {
     timed(stream, m_times.optimizer, [&]() {
         if (m_optSteps < 50000) m_optSteps++;
@@ -508,6 +589,25 @@ void InstantNerf::optimizerStep(cudaStream_t stream) {
                                              m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, stream), "optimizer (peer)");
             m_rankBarrier(stream);     // every rank has stored its slice everywhere and read what it needed of this gradient
             throw_on_error(nb_zero_async(m_arena.G(0), m_arena.total * (int64_t)sizeof(float), stream), "optimizer: clear");
+            return;
+        }
+        if (m_partWorld > 1) {
+            // owned levels of the table, then the networks on the gradient summed over the ranks
+            const int64_t H = m_arena.sparse_count, level = H / m_densityMLP->grid().num_levels;
+            if (m_partReduce) m_partReduce(m_arena.G(H), m_arena.total - H, stream);
+            int grad_half_part = 0;
+            nb_get_tuning("grad_table_half", &grad_half_part);
+            for (int64_t l = m_partRank; l < m_densityMLP->grid().num_levels; l += m_partWorld) {
+                const int64_t off = l * level;
+                // with the half-precision table the level's gradient sits at half the byte offset
+                float* g = grad_half_part ? reinterpret_cast<float*>(reinterpret_cast<half*>(m_arena.G(0)) + off) : m_arena.G(off);
+                throw_on_error(nb_adam_step(m_arena.W(off), m_arena.Wh(off), g, m_arena.M(off), m_arena.V(off), level, level, m_opts.learningRate,
+                                            m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),
+                               "optimizer (owned level)");
+            }
+            throw_on_error(nb_adam_step(m_arena.W(H), m_arena.Wh(H), m_arena.G(H), m_arena.M(H), m_arena.V(H), 0, m_arena.total - H, m_opts.learningRate,
+                                        m_opts.beta1, m_opts.beta2, m_opts.epsilon, bc1, bc2, 1.0f / m_opts.lossScale, 1, stream),
+                           "optimizer (networks)");
             return;
         }
         int grad_half = 0;

@@ -139,6 +139,21 @@ public:
     using RankBarrier = std::function<void(cudaStream_t stream)>;
     void setPeerExchange(uint32_t rank, uint32_t world, const std::vector<const float*>& peerGrads, const std::vector<void*>& peerParamsH,
                          RankBarrier barrier);
+    // Data parallelism with the table PARTITIONED BY LEVEL instead of replicated (csrc/level_partition.cu): rank r of
+    // `world` owns levels r, r + world, ...; per step the ranks exchange sample positions (one all-gather), encodings (one
+    // all-to-all) and encoding gradients (one all-to-all back), 128 bytes per sample in all, and nothing of the table;
+    // every rank updates its own levels and, after `reduce` has summed the small dense tail of the gradient arena over the
+    // ranks, the network weights.  Needs the fused field kernels; world must divide the number of levels.
+    //   gather(send, recv, bytes, stream):   recv = the ranks' `bytes`-sized blocks one after the other (all-gather)
+    //   exchange(send, recv, bytes, stream): block q of send goes to rank q, block r of recv comes from rank r (all-to-all)
+    // Between steps the levels a rank does not own go stale in its copy of the table; syncLevels() brings every rank's
+    // copy up to date (fp16 forward copy; with `master` also the fp32 copy) and runs by itself before occupancy updates.
+    // Call it before rendering, saving or comparing replicas.  world <= 1 switches back.
+    using BlockGather = std::function<void(const void* d_send, void* d_recv, int64_t bytes, cudaStream_t stream)>;
+    using BlockExchange = std::function<void(const void* d_send, void* d_recv, int64_t bytes, cudaStream_t stream)>;
+    void setLevelPartition(uint32_t rank, uint32_t world, BlockGather gather, BlockExchange exchange, GradSync reduce);
+    void syncLevels(cudaStream_t stream, bool master = false);
+    bool levelPartitioned() const { return m_partWorld > 1; }
     // Loss gradients are normalised by numRays * scale (the global ray count when ranks split a batch).
     void setGlobalRayScale(uint32_t scale) { m_rayScale = scale ? scale : 1u; }
     // One kernel each way for the whole field (encode + both networks) instead of the reference's kernel sequence;
@@ -205,6 +220,14 @@ private:
     std::vector<const float*> m_peerGrads;
     std::vector<void*> m_peerParamsH;
     uint32_t m_shardRank = 0, m_shardWorld = 1;
+    // level partition: position slots of all ranks, pieces to send and received
+    uint32_t m_partRank = 0, m_partWorld = 1;
+    BlockGather m_partGather;
+    BlockExchange m_partExchange;
+    GradSync m_partReduce;
+    nb::DeviceMem d_pos_all, d_pieces_send, d_pieces_recv;
+    void partitionedForward(const float* chunk_d, int64_t n, int colorStride, cudaStream_t stream);
+    void partitionedBackward(const float* chunk_d, int64_t n, cudaStream_t stream);
     uint32_t m_rayScale = 1;
     bool m_fused = false;
     bool m_renderRounds = false;

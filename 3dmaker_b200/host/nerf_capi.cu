@@ -119,6 +119,22 @@ extern "C" int nb_nerf_set_peer_exchange(nb_nerf* h, uint32_t rank, uint32_t wor
     NB_GUARD(h->impl.setPeerExchange(rank, world, g, p, [fn, user](cudaStream_t st) { fn(user, st); }))
 }
 
+extern "C" int nb_nerf_set_level_partition(nb_nerf* h, uint32_t rank, uint32_t world, nb_block_fn gather, nb_block_fn exchange, nb_grad_sync_fn reduce,
+                                           void* user) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    if (world > 1 && (!gather || !exchange || !reduce)) return nb_set_error(NB_ERR_INVALID, "nb_nerf_set_level_partition: the three collectives are required");
+    if (world <= 1) { NB_GUARD(h->impl.setLevelPartition(0, 1, nullptr, nullptr, nullptr)) }
+    NB_GUARD(h->impl.setLevelPartition(
+        rank, world, [gather, user](const void* s, void* r, int64_t bytes, cudaStream_t st) { gather(user, s, r, bytes, st); },
+        [exchange, user](const void* s, void* r, int64_t bytes, cudaStream_t st) { exchange(user, s, r, bytes, st); },
+        [reduce, user](float* g, int64_t count, cudaStream_t st) { reduce(user, g, count, st); }))
+}
+
+extern "C" int nb_nerf_sync_levels(nb_nerf* h, int master, void* stream) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    NB_GUARD(h->impl.syncLevels((cudaStream_t)stream, master != 0))
+}
+
 extern "C" int nb_nerf_set_hit_counts_capacity(nb_nerf* h, uint32_t capacity) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     h->impl.setHitCountsCapacity(capacity);

@@ -149,6 +149,38 @@ class InstantNerf:
         self._barrier_cb = nb.BARRIER_FN(trampoline)
         nb.check(self.lib.nb_nerf_set_peer_exchange(self.h, rank, world, G, W, self._barrier_cb, None), "nb_nerf_set_peer_exchange")
 
+    def set_level_partition(self, rank, world, gather, exchange, reduce):
+        """Table partitioned by level over the ranks (see nb_nerf_set_level_partition).  The three collectives get torch
+        views of the engine's buffers: gather(send_u8, recv_u8) - all-gather of equal blocks; exchange(send_u8, recv_u8) -
+        all-to-all of equal blocks; reduce(grad_f32) - SUM over the ranks.  world <= 1 switches back."""
+        if world <= 1:
+            nb.check(self.lib.nb_nerf_set_level_partition(self.h, 0, 1, nb.BLOCK_FN(0), nb.BLOCK_FN(0), nb.GRAD_SYNC_FN(0), None),
+                     "nb_nerf_set_level_partition")
+            self._part_cbs = None
+            return
+        views = {}
+
+        def view(ptr, count, dtype):
+            key = (int(ptr), int(count), np.dtype(dtype).str)
+            if key not in views:
+                views[key] = view_tensor(self.torch, int(ptr), int(count), dtype)
+            return views[key]
+
+        def gather_cb(user, send, recv, nbytes, stream):
+            gather(view(send, nbytes, np.uint8), view(recv, nbytes * world, np.uint8))
+
+        def exchange_cb(user, send, recv, nbytes, stream):
+            exchange(view(send, nbytes * world, np.uint8), view(recv, nbytes * world, np.uint8))
+
+        def reduce_cb(user, ptr, count, stream):
+            reduce(view(ptr, count, np.float32))
+        self._part_cbs = (nb.BLOCK_FN(gather_cb), nb.BLOCK_FN(exchange_cb), nb.GRAD_SYNC_FN(reduce_cb))
+        nb.check(self.lib.nb_nerf_set_level_partition(self.h, rank, world, *self._part_cbs, None), "nb_nerf_set_level_partition")
+
+    def sync_levels(self, master=False, stream=None):
+        """Level-partitioned training: brings the levels this rank does not own up to date (all ranks must call it)."""
+        nb.check(self.lib.nb_nerf_sync_levels(self.h, 1 if master else 0, nb.stream_ptr(stream)), "nb_nerf_sync_levels")
+
     def set_grad_buffer(self, tensor):
         """Moves the gradient arena into `tensor` (float32, CUDA, at least arena().total elements; the engine zeroes it and
         this object keeps it alive) - e.g. memory registered with the communicator so that the all-reduce of

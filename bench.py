@@ -1000,7 +1000,7 @@ def main():
     ap.add_argument("--extra-scene-warm", type=int, default=48, help="untimed train_rays calls of the embedded scene5 measurement "
                     "(six optimizer steps each: past the 256 steps of whole-grid occupancy updates)")
     ap.add_argument("--render-frames", type=int, default=12, help="timed frames of the embedded render measurement")
-    ap.add_argument("--exchange", default="peer", choices=["allreduce", "sharded", "peer"],
+    ap.add_argument("--exchange", default="peer", choices=["allreduce", "sharded", "peer", "levels"],
                     help="scene workloads at N > 1: all-reduce + replicated Adam; reduce-scatter + Adam on a table slice + all-gather of fp16 "
                          "parameters; or the same three stages as one kernel over peer memory (default)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")

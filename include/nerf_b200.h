@@ -154,6 +154,35 @@ int nb_set_tuning(const char* key, int value);
  * "backward_tc"); NB_ERR_INVALID for any other key. */
 int nb_get_tuning(const char* key, int* value);
 
+/* ---- level-partitioned grid (no counterpart in the reference, which trains on one GPU) --------------------------
+ *
+ * Data-parallel training in which rank r of R OWNS levels r, r + R, r + 2R, ... of the table instead of holding a
+ * replica of all levels: the ranks exchange positions, encodings and encoding gradients (128 bytes per sample and step)
+ * and nothing of the table.  R must divide the number of levels.  The collectives are the caller's; these entry points
+ * define the layouts they move:
+ *   position slots  float4 [R][capacity + 1]: slot q = rank q's sample positions, element `capacity` = its sample
+ *                   count (uint32 bits in .x; nb_part_stamp_count writes it).  One all-gather of a rank's slot fills it.
+ *   pieces          half2 [R][levels / R][capacity]: piece q, owned level k, sample j.  After nb_part_encode piece q
+ *                   holds THIS rank's levels for rank q's samples; one all-to-all of whole pieces later piece q holds the
+ *                   levels OWNED BY rank q for this rank's samples, which is what nb_part_field_forward reads.  The
+ *                   backward exchange runs the other way: nb_part_pack_denc, all-to-all, nb_part_scatter.
+ * Results equal those of the replicated path sample by sample (the encoding bit for bit; gradients up to summation order). */
+int nb_part_stamp_count(float* d_pos_slot, int64_t capacity, int64_t n, void* stream);
+int nb_part_encode(const nb_grid_desc* grid, int ranks, int rank, int64_t capacity, const float* d_pos_all, const void* d_table_h,
+                   void* d_pieces_h, void* stream);
+/* nb_field_forward with the encoding taken from the received pieces (d_enc_save_h row-major [n][32] as before). */
+int nb_part_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, const nb_mlp_desc* color, int ranks, int64_t capacity,
+                          const void* d_pieces_h, const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset,
+                          const void* d_density_w_h, const float* d_density_b, const void* d_color_w_h, const float* d_color_b,
+                          int64_t n, float density_bias, void* d_enc_save_h, float* d_sigma, float* d_logit0, float* d_rgb,
+                          int rgb_stride, void* stream);
+/* d_denc_h fp16 [n][2 levels] as nb_field_backward (without a table gradient) writes it -> pieces for the owners. */
+int nb_part_pack_denc(const nb_grid_desc* grid, int ranks, int64_t capacity, const void* d_denc_h, int64_t n, void* d_pieces_h, void* stream);
+/* The owner's levels of d_table_grads (the WHOLE gradient array, standard layout) receive the gradients of all ranks'
+ * samples: hashTableScatter_Backward (networkFusionBackwardHashtable.cu:783-910) restricted to the owned levels. */
+int nb_part_scatter(const nb_grid_desc* grid, int ranks, int rank, int64_t capacity, const float* d_pos_all, const void* d_pieces_h,
+                    float* d_table_grads, void* stream);
+
 /* ---- fused MLP ---------------------------------------------------------------------------- */
 
 /* Replaces launchNetworkFusionKernel / launchNetworkFusionGradKernel (TinyMLP.h:172-206). */
@@ -587,6 +616,21 @@ int nb_nerf_set_optimizer_shard(nb_nerf* h, uint32_t rank, uint32_t world, nb_pa
 typedef void (*nb_barrier_fn)(void* user, void* stream);
 int nb_nerf_set_peer_exchange(nb_nerf* h, uint32_t rank, uint32_t world, const float* const* peer_grads, void* const* peer_w_h,
                               nb_barrier_fn fn, void* user);
+/* Data parallelism with the table partitioned by level instead of replicated (see "level-partitioned grid" above): rank
+ * `rank` of `world` owns levels rank, rank + world, ...  Per optimizer step the engine calls
+ *   gather(user, send, recv, bytes, stream)    once: recv = every rank's `bytes`-sized block, rank order (an all-gather;
+ *                                               send may be the rank's own block inside recv: the in-place form);
+ *   exchange(user, send, recv, bytes, stream)  twice: block q of send to rank q, block r of recv from rank r (all-to-all);
+ *   reduce(user, d_grads, count, stream)       once: SUM over the ranks of the networks' gradients (a few thousand floats);
+ * and `gather` again, per block of `world` levels, before every occupancy update and in nb_nerf_sync_levels, which
+ * brings the levels a rank does not own up to date in its copy of the table (fp16 forward copy; master != 0: the fp32
+ * copy as well) - call it before rendering, saving or comparing replicas.  world must divide the number of levels; the
+ * fused field kernels are required; not together with nb_nerf_set_optimizer_shard / nb_nerf_set_peer_exchange /
+ * nb_nerf_set_grad_sync.  world <= 1 switches back. */
+typedef void (*nb_block_fn)(void* user, const void* d_send, void* d_recv, int64_t bytes, void* stream);
+int nb_nerf_set_level_partition(nb_nerf* h, uint32_t rank, uint32_t world, nb_block_fn gather, nb_block_fn exchange, nb_grad_sync_fn reduce,
+                                void* user);
+int nb_nerf_sync_levels(nb_nerf* h, int master, void* stream);
 /* on != 0: nb_nerf_train_rays runs exactly one optimizer step (one fn call) per call; rays that do not fit the sample
  * batch are left untrained (nb_nerf_step_view.rays_consumed says how many were used) instead of starting a second
  * step, so that every rank of a data-parallel job issues the same number of gradient exchanges. */

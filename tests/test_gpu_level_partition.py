@@ -1,0 +1,255 @@
+"""Level-partitioned grid (nb_part_*): R ranks played by separate buffers on ONE device, the collectives between them
+replaced by tensor copies.  Yardstick: the replicated path (nb_field_forward / nb_field_backward /
+nb_hash_scatter_backward) on each rank's samples, which is pinned against the reference elsewhere."""
+import ctypes
+import importlib
+
+import numpy as np
+import pytest
+
+from helpers import dev_half_bits, half_bits, make_mlp, make_positions, make_table, rel_err
+
+pytestmark = pytest.mark.gpu
+
+L, T = 16, 1 << 15
+
+
+def _rank_inputs(n, seed):
+    rng = np.random.default_rng(seed)
+    pos = make_positions(n, seed)
+    d = rng.normal(size=(n, 3)).astype(np.float32)
+    d /= np.linalg.norm(d, axis=1, keepdims=True)
+    tgt = np.zeros((n, 8), np.float32)
+    tgt[:, :3] = rng.random((n, 3), dtype=np.float32)
+    return pos, d, half_bits(tgt).view(np.float16)
+
+
+@pytest.mark.parametrize("half_table", [False, True])
+@pytest.mark.parametrize("ranks,counts", [(1, [5000]), (2, [4097, 1]), (4, [3000, 0, 4096, 17]), (8, [900, 1024, 5, 777, 1000, 128, 129, 640])])
+def test_level_partition_equals_the_replicated_path(cuda, nb, ranks, counts, half_table):
+    torch = cuda
+    if half_table and ranks not in (2, 8):
+        pytest.skip("the half-precision table is exercised with 2 and 8 ranks")
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    model = pl.FieldModel(torch, L, T, 16, 1.3819, 64, 2, 64, 3)
+    model.load_hashgrid(make_table(L, T, seed=3, amp=0.3))
+    model.load_density_weights(*make_mlp(32, 64, 16, 2, seed=4, bias_amp=0.05)); model.load_color_weights(*make_mlp(32, 64, 8, 3, seed=5, bias_amp=0.05))
+    m, G, D, C = model, ctypes.byref(model.grid), ctypes.byref(model.density), ctypes.byref(model.color)
+    cap, own = 4100, L // ranks
+    f16, f32 = torch.float16, torch.float32
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    ins = [_rank_inputs(max(c, 1), 40 + q) for q, c in enumerate(counts)]
+    try:
+        nb.set_grad_table_half(half_table, 7)
+        # ---- 1. position slots, counts stamped, "all-gathered"
+        pos_all = torch.full((ranks, cap + 1, 4), 0.5, dtype=f32, device="cuda")
+        for q, c in enumerate(counts):
+            pos_all[q, :c].copy_(dev(ins[q][0][:c]))
+            nb.check(lib.nb_part_stamp_count(ctypes.c_void_p(pos_all[q].data_ptr()), cap, c, st), "nb_part_stamp_count")
+        # ---- 2. every owner encodes its levels for everybody's samples; 3. "all-to-all" of whole pieces
+        send = []
+        for r in range(ranks):
+            pieces = torch.full((ranks, own, cap), 0x7e007e00, dtype=torch.int32, device="cuda")     # NaNs where nothing is written
+            nb.check(lib.nb_part_encode(G, ranks, r, cap, P(pos_all), m.ptr("w_h", 0), P(pieces), st), "nb_part_encode")
+            send.append(pieces)
+        recv = [torch.stack([send[r][q] for r in range(ranks)]).contiguous() for q in range(ranks)]
+        # ---- 4. networks from the pieces against the replicated forward
+        fwd = []
+        for q, c in enumerate(counts):
+            n = c
+            pos, dirs, tgt = (dev(a[:max(n, 1)]) for a in ins[q])
+            o = {k: dict(enc=torch.zeros((max(n, 1), 32), dtype=f16, device="cuda"), sigma=torch.zeros(max(n, 1), device="cuda"),
+                         logit=torch.zeros(max(n, 1), device="cuda"), rgb=torch.zeros((max(n, 1), 8), device="cuda")) for k in ("whole", "part")}
+            w = (m.ptr("w_h", m.off_dw), m.ptr("w", m.off_db), m.ptr("w_h", m.off_cw), m.ptr("w", m.off_cb))
+            nb.check(lib.nb_field_forward(G, D, C, P(pos), m.ptr("w_h", 0), P(dirs), None, 0, *w, n, 1.0, P(o["whole"]["enc"]), P(o["whole"]["sigma"]),
+                                          P(o["whole"]["logit"]), P(o["whole"]["rgb"]), 8, st), "nb_field_forward")
+            nb.check(lib.nb_part_field_forward(G, D, C, ranks, cap, P(recv[q]), P(dirs), None, 0, *w, n, 1.0, P(o["part"]["enc"]), P(o["part"]["sigma"]),
+                                               P(o["part"]["logit"]), P(o["part"]["rgb"]), 8, st), "nb_part_field_forward")
+            torch.cuda.synchronize()
+            for k in ("enc", "sigma", "logit", "rgb"):
+                assert torch.equal(o["whole"][k].view(torch.int16 if k == "enc" else torch.int32), o["part"][k].view(torch.int16 if k == "enc" else torch.int32)), (q, k)
+            fwd.append((pos, dirs, tgt, o["whole"], w))
+        # ---- 5. backward per rank, gradients of the encoding packed and "sent" to the owners
+        g_whole = torch.zeros(m.total, dtype=f32, device="cuda")          # the replicated path: everything into one gradient arena
+        dsend = []
+        for q, c in enumerate(counts):
+            n = c
+            pos, dirs, tgt, o, w = fwd[q]
+            dcol = torch.zeros((max(n, 1), 8), dtype=f16, device="cuda")
+            loss = torch.zeros(1, device="cuda")
+            denc = torch.zeros((max(n, 1), 32), dtype=f16, device="cuda")
+            if n > 0:
+                nb.check(lib.nb_mse_loss_grad(P(o["rgb"]), P(tgt), P(dcol), P(loss), n, 8, 3, 128.0, 1, st), "nb_mse_loss_grad")
+            scratch = torch.zeros(m.total, dtype=f32, device="cuda")
+            nb.check(lib.nb_field_backward(D, C, P(o["enc"]), P(dirs), None, 0, *w, n, P(dcol), None, ctypes.c_void_p(scratch.data_ptr() + 4 * m.off_dw),
+                                           ctypes.c_void_p(scratch.data_ptr() + 4 * m.off_db), ctypes.c_void_p(scratch.data_ptr() + 4 * m.off_cw),
+                                           ctypes.c_void_p(scratch.data_ptr() + 4 * m.off_cb), P(denc), None, None, None, st), "nb_field_backward")
+            if n > 0:
+                nb.check(lib.nb_hash_scatter_backward(G, P(pos), P(denc), n, P(g_whole), st), "nb_hash_scatter_backward")
+            pieces = torch.zeros((ranks, own, cap), dtype=torch.int32, device="cuda")
+            nb.check(lib.nb_part_pack_denc(G, ranks, cap, P(denc), n, P(pieces), st), "nb_part_pack_denc")
+            dsend.append(pieces)
+        drecv = [torch.stack([dsend[q][r] for q in range(ranks)]).contiguous() for r in range(ranks)]
+        # ---- 6. every owner scatters its levels for everybody's samples
+        H = m.hash_count
+        g_sum = torch.zeros(H, dtype=f32, device="cuda")
+        for r in range(ranks):
+            g_r = torch.zeros(m.total, dtype=f32, device="cuda")
+            nb.check(lib.nb_part_scatter(G, ranks, r, cap, P(pos_all), P(drecv[r]), P(g_r), st), "nb_part_scatter")
+            torch.cuda.synchronize()
+            table = (g_r[:H].view(f16)[:H].float() / nb.grad_table_scale() if half_table else g_r[:H]).reshape(L, T * 2)
+            for l in range(L):
+                if l % ranks != r:
+                    assert float(table[l].abs().max().item()) == 0.0, "rank %d wrote level %d, which it does not own" % (r, l)
+            g_sum += table.reshape(-1)
+        torch.cuda.synchronize()
+        ref = (g_whole[:H].view(f16)[:H].float() / nb.grad_table_scale() if half_table else g_whole[:H]).reshape(L, T * 2).cpu().numpy()
+        got = g_sum.reshape(L, T * 2).cpu().numpy()
+    finally:
+        nb.set_grad_table_half(False, 7)
+    assert np.abs(ref).max() > 0
+    for l in range(L):
+        tol = 1e-2 if half_table else 2e-3
+        assert np.abs(got[l] - ref[l]).max() <= tol * np.abs(ref[l]).max() + 1e-12, l
+
+
+def test_level_partition_rejects_rank_counts_that_do_not_divide_the_levels(cuda, nb):
+    torch = cuda
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    grid = nb.grid_setup(16, 1 << 14, 16, 1.3819)
+    a = torch.zeros(1 << 16, dtype=torch.float32, device="cuda")
+    assert lib.nb_part_encode(ctypes.byref(grid), 3, 0, 128, P(a), P(a), P(a), st) == 2          # NB_ERR_UNSUPPORTED
+    assert lib.nb_part_encode(ctypes.byref(grid), 4, 4, 128, P(a), P(a), P(a), st) == 1          # NB_ERR_INVALID: rank outside [0, ranks)
+    assert lib.nb_part_stamp_count(P(a), 128, 129, st) == 1
+
+
+class _ThreadDist:
+    """torch.distributed's few calls for `world` threads of ONE process on ONE device: every collective is a host
+    rendezvous plus tensor copies, so no kernel ever waits for another rank's kernel."""
+
+    class ReduceOp:
+        SUM, MAX = "sum", "max"
+
+    class _Shared:
+        def __init__(self, torch, world):
+            import threading
+            self.torch, self.world = torch, world
+            self.barrier = threading.Barrier(world)
+            self.slots = [None] * world
+
+    def __init__(self, shared, rank):
+        self.s, self.rank = shared, rank
+
+    def get_rank(self):
+        return self.rank
+
+    def get_world_size(self):
+        return self.s.world
+
+    def _meet(self, tensor):
+        self.s.torch.cuda.synchronize()
+        self.s.slots[self.rank] = tensor
+        self.s.barrier.wait()
+        return list(self.s.slots)
+
+    def _leave(self):
+        self.s.torch.cuda.synchronize()
+        self.s.barrier.wait()
+
+    def all_gather_into_tensor(self, recv, send):
+        n = send.numel()
+        staged = [t.clone() for t in self._meet(send)]          # the in-place form overlaps send and recv
+        self._leave()
+        for q, t in enumerate(staged):
+            recv[q * n:(q + 1) * n].copy_(t)
+        self._leave()
+
+    def all_to_all_single(self, recv, send):
+        n = send.numel() // self.s.world
+        sends = self._meet(send)
+        for q, t in enumerate(sends):
+            recv[q * n:(q + 1) * n].copy_(t[self.rank * n:(self.rank + 1) * n])
+        self._leave()
+
+    def all_reduce(self, tensor, op="sum"):
+        parts = [t.clone() for t in self._meet(tensor)]
+        self._leave()
+        total = parts[0]
+        for t in parts[1:]:
+            total = total + t if op == "sum" else self.s.torch.maximum(total, t)
+        tensor.copy_(total)
+        self._leave()
+
+    def barrier(self):
+        self.s.barrier.wait()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_level_partitioned_engine_trains_like_one_engine_on_all_rays(cuda, nb, world):
+    """`world` scene engines on one device, one thread each, table partitioned by level, against ONE engine given all the
+    rays: the same optimizer steps (every rank's rays fit its batch), so after 6 steps the parameters agree up to the
+    summation order of the gradients - compared through the loss of the next step and the fp16 tables themselves - and
+    all ranks hold the same table after sync_levels."""
+    import threading
+    torch = cuda
+    nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
+    D = importlib.import_module("3dmaker_b200.distributed")
+    rays_global, steps = 1 << 12, 6
+    base = dict(grid_resolution=(64,) * 3, aabb_min=(-.5,) * 3, aabb_max=(.5,) * 3, levels_mipmap=3, hash_table_size=1 << 15, growth_factor=1.3819,
+                color_hidden_dim=64, color_num_layers=3, lambda_dist=0.01, lambda_depth=0.0, learning_rate=1e-2, beta2=0.99, epsilon=1e-15,
+                loss_scale=128.0, density_bias=1.0, bg_color=(1.0, 1.0, 1.0))
+    scene = syn.SoftSphereScene(); poses = syn.sphere_cameras(20); bg = (1.0, 1.0, 1.0)
+    batches = []
+    for i in range(steps):
+        o, d = syn.random_training_rays(torch, poses, rays_global, 200, 200, 50.0, seed=900 + i)
+        batches.append((o, d, syn.ground_truth(torch, scene, o, d, bg)))
+    # ---- one engine, all rays (batch large enough for every ray: one optimizer step per call)
+    one = nm.InstantNerf(torch, nm.default_options(**dict(base, batch_size=1 << 20, render_batch_size=1 << 18, ray_chunk_size=rays_global)))
+    one.set_single_step(True)
+    for o, d, t in batches:
+        one.train_rays(o, d, t)
+        assert one.rays_consumed() == rays_global
+    torch.cuda.synchronize()
+    ref_w = one.arena_tensor("w_h").clone()
+    H = int(one.arena().sparse_count)
+    # ---- `world` engines, one thread each
+    shared = _ThreadDist._Shared(torch, world)
+    out, errors = [None] * world, []
+
+    def run(rank):
+        try:
+            torch.cuda.set_device(0)
+            eng = nm.InstantNerf(torch, nm.default_options(**dict(base, batch_size=(1 << 20) // world, render_batch_size=1 << 18,
+                                                                  ray_chunk_size=rays_global // world)))
+            tr = D.DataParallelTrainer(torch, eng, _ThreadDist(shared, rank), steps_per_call=1, exchange="levels")
+            for o, d, t in batches:
+                assert tr.train_rays(o, d, t) == rays_global // world
+            in_sync = tr.replicas_in_sync()
+            torch.cuda.synchronize()
+            out[rank] = (eng.arena_tensor("w_h").clone(), in_sync, tr.sync_calls)
+            tr.close(); eng.close()
+        except BaseException as e:          # a thread that dies would leave the others at the barrier
+            errors.append(e)
+            shared.barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    assert not errors, errors
+    one.close()
+    for r in range(world):
+        w, in_sync, calls = out[r]
+        assert in_sync
+        assert torch.equal(w.view(torch.int16), out[0][0].view(torch.int16)), "rank %d holds a different table after sync_levels" % r
+    got = out[0][0].float().cpu().numpy()
+    ref = ref_w.float().cpu().numpy()
+    moved = np.abs(ref[:H] - got[:H])
+    # Adam's first steps move every touched entry by about the learning rate whatever the gradient's size, so entries
+    # whose tiny gradient differs in sign or vanishes on one side differ by a step or two: bound their share and the rest
+    print("table entries further than 2e-3 apart after %d steps: %.2e; networks rel %.2e" % (steps, float(np.mean(moved > 2e-3)), rel_err(got[H:], ref[H:])))
+    assert np.mean(moved > 2e-3) < 5e-2, float(np.mean(moved > 2e-3))
+    assert np.mean(moved == 0) > 0.5
+    assert rel_err(got[H:], ref[H:]) <= 5e-2
