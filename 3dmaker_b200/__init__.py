@@ -268,6 +268,7 @@ _SIGNATURES = {
     "nb_nerf_set_hit_counts_capacity": (c_int, [c_void_p, ctypes.c_uint32]),
     "nb_nerf_set_grad_sync": (c_int, [c_void_p, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_set_level_partition": (c_int, [c_void_p, ctypes.c_uint32, ctypes.c_uint32, BLOCK_FN, BLOCK_FN, GRAD_SYNC_FN, c_void_p]),
+    "nb_nerf_set_occupancy_shard": (c_int, [c_void_p, ctypes.c_uint32, ctypes.c_uint32, GRAD_SYNC_FN, c_void_p]),
     "nb_nerf_sync_levels": (c_int, [c_void_p, c_int, c_void_p]),
     "nb_nerf_set_grad_buffer": (c_int, [c_void_p, c_void_p, c_int64]),
     "nb_nerf_get_arena": (c_int, [c_void_p, ctypes.POINTER(ArenaView)]),

@@ -143,7 +143,7 @@ class DataParallelTrainer:
                    (T = 2^22: 805 MB of table traffic per step and rank against 34-270 MB of encodings).  The levels a
                    rank does not own go stale between occupancy updates: sync() before rendering, saving or comparing."""
 
-    def __init__(self, torch, engine, dist=None, steps_per_call=1, registered_gradient=False, exchange="allreduce"):
+    def __init__(self, torch, engine, dist=None, steps_per_call=1, registered_gradient=False, exchange="allreduce", shard_occupancy=True):
         self.torch, self.engine, self.dist = torch, engine, dist
         self.steps_per_call = steps_per_call
         self.rank = dist.get_rank() if dist is not None else 0
@@ -203,6 +203,10 @@ class DataParallelTrainer:
             else:
                 engine.set_grad_sync(self._allreduce)
                 self._bytes = {"gradient_out_per_step": int(self._total * 4 * 2 * (self.world - 1) / self.world), "parameters_out_per_step": 0}
+            # occupancy updates: every rank evaluates its share of the density queries, the per-cell maxima are merged
+            self._occupancy_sharded = hasattr(engine, "set_occupancy_shard") and shard_occupancy
+            if self._occupancy_sharded:
+                engine.set_occupancy_shard(self.rank, self.world, self._allreduce_max)
             # the same number of optimizer steps, hence exchanges, per call on every rank, whatever the local sample
             # counts are (steps_per_call > 1 lets one occupancy walk of a large ray shard serve several steps)
             engine.set_steps_per_call(steps_per_call)
@@ -218,6 +222,10 @@ class DataParallelTrainer:
         lo = self.rank * self._shard
         self.dist.reduce_scatter_tensor(grad[lo:lo + self._shard], grad[:self._hash], op=self.dist.ReduceOp.SUM)   # in place
         self.dist.all_reduce(grad[self._hash:self._total], op=self.dist.ReduceOp.SUM)
+
+    def _allreduce_max(self, t):
+        self.sync_calls += 1
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
 
     def _gather_blocks(self, send, recv):
         self.sync_calls += 1
@@ -266,6 +274,8 @@ class DataParallelTrainer:
                 self._peer_g.close(); self._peer_w.close()
             if self.exchange == "levels":
                 self.engine.set_level_partition(0, 1, None, None, None)
+            if getattr(self, "_occupancy_sharded", False):
+                self.engine.set_occupancy_shard(0, 1, None)
             self.engine.set_grad_sync(None)
 
     def train_rays(self, rays_o, rays_d, rgb_true):

@@ -212,17 +212,38 @@ void InstantNerf::earlyOccupancyGridUpdate(cudaStream_t stream) {
     const int G = m_opts.gridResolution.x * m_opts.gridResolution.y * m_opts.gridResolution.z;
     const int N = m_opts.numCascades * G;
     nb_scene_desc sc = scene();
-    TinyMLPHashGrid* d = m_densityMLP;
     throw_on_error(nb_zero_async(d_tmp_grid.as<float>(), (int64_t)N * sizeof(float), stream), "occupancy: clear");
     for (int c = 0; c < m_opts.numCascades; ++c) {
         throw_on_error(nb_occ_sample_cells(&sc, d_occ_samples.as<float>(), G, G, c * G, (uint64_t)m_trainSteps + (uint64_t)c, stream),
                        "occupancy: sample");
-        throw_on_error(nb_grid_mlp_forward(&d->grid(), &d->desc(), d_occ_samples.as<float>(), m_arena.Wh(d->hashOffset()), m_arena.Wh(d->weightOffset()),
-                                           m_arena.W(d->biasOffset()), G, d_density_out.as<float>(), nullptr, nullptr, stream), "occupancy: density");
-        throw_on_error(nb_occ_update_tmp_grid(d_occ_samples.as<float>(), d_density_out.as<float>(), d_tmp_grid.as<float>(), m_opts.densityBias, G, stream),
-                       "occupancy: cell maximum");
+        occupancyDensity(G, stream);
     }
+    if (m_occWorld > 1) m_occReduceMax(d_tmp_grid.as<float>(), (int64_t)N, stream);
     finishOccupancyUpdate(stream);
+}
+
+// Density of the sampled points [0, count) of d_occ_samples and the per-cell maximum; with the update split over ranks
+// only this rank's contiguous share of the points (16-point granules keep every pointer aligned).
+void InstantNerf::occupancyDensity(int count, cudaStream_t stream) {
+    TinyMLPHashGrid* d = m_densityMLP;
+    int lo = 0, hi = count;
+    if (m_occWorld > 1) {
+        const int64_t granules = ((int64_t)count + 15) / 16;
+        lo = (int)std::min<int64_t>(count, granules * m_occRank / m_occWorld * 16);
+        hi = (int)std::min<int64_t>(count, granules * (m_occRank + 1) / m_occWorld * 16);
+    }
+    if (hi <= lo) return;
+    const float* samples = d_occ_samples.as<float>() + (size_t)lo * 4;
+    float* out = d_density_out.as<float>() + (size_t)lo * 16;
+    throw_on_error(nb_grid_mlp_forward(&d->grid(), &d->desc(), samples, m_arena.Wh(d->hashOffset()), m_arena.Wh(d->weightOffset()),
+                                       m_arena.W(d->biasOffset()), hi - lo, out, nullptr, nullptr, stream), "occupancy: density");
+    throw_on_error(nb_occ_update_tmp_grid(samples, out, d_tmp_grid.as<float>(), m_opts.densityBias, hi - lo, stream), "occupancy: cell maximum");
+}
+
+void InstantNerf::setOccupancyShard(uint32_t rank, uint32_t world, GradSync reduceMax) {
+    if (world <= 1) { m_occRank = 0; m_occWorld = 1; m_occReduceMax = GradSync(); return; }
+    if (rank >= world || !reduceMax) throw std::runtime_error("setOccupancyShard: rank below world and a MAX all-reduce are required");
+    m_occRank = rank; m_occWorld = world; m_occReduceMax = std::move(reduceMax);
 }
 
 // Half a grid's worth of samples, half of them inside currently occupied cells.  InstantNerf.cu:1009-1106.
@@ -230,7 +251,6 @@ void InstantNerf::lateOccupancyGridUpdate(cudaStream_t stream) {
     const int G = m_opts.gridResolution.x * m_opts.gridResolution.y * m_opts.gridResolution.z;
     const int N = m_opts.numCascades * G;
     nb_scene_desc sc = scene();
-    TinyMLPHashGrid* d = m_densityMLP;
     throw_on_error(nb_zero_async(d_tmp_grid.as<float>(), (int64_t)N * sizeof(float), stream), "occupancy: clear");
     throw_on_error(nb_occ_extract_active(&sc, d_occupancyGrid.as<uint8_t>(), d_active_cells.as<int>(), d_num_active.as<int>(), stream),
                    "occupancy: active cells");
@@ -244,13 +264,9 @@ void InstantNerf::lateOccupancyGridUpdate(cudaStream_t stream) {
                                               stream), "occupancy: sample occupied");
         throw_on_error(nb_occ_sample_cells(&sc, d_occ_samples.as<float>() + (size_t)occPerChunk * 4, uniPerChunk, N, 0, seedBase + 1ULL, stream),
                        "occupancy: sample uniform");
-        const int chunkCount = occPerChunk + uniPerChunk;
-        throw_on_error(nb_grid_mlp_forward(&d->grid(), &d->desc(), d_occ_samples.as<float>(), m_arena.Wh(d->hashOffset()), m_arena.Wh(d->weightOffset()),
-                                           m_arena.W(d->biasOffset()), chunkCount, d_density_out.as<float>(), nullptr, nullptr, stream),
-                       "occupancy: density");
-        throw_on_error(nb_occ_update_tmp_grid(d_occ_samples.as<float>(), d_density_out.as<float>(), d_tmp_grid.as<float>(), m_opts.densityBias, chunkCount,
-                                              stream), "occupancy: cell maximum");
+        occupancyDensity(occPerChunk + uniPerChunk, stream);
     }
+    if (m_occWorld > 1) m_occReduceMax(d_tmp_grid.as<float>(), (int64_t)N, stream);
     finishOccupancyUpdate(stream);
 }
 
@@ -399,7 +415,7 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
 
         const int logitStride = m_fused ? 1 : 16, colorStride = m_fused ? 4 : 8;
         if (m_partWorld > 1) {
-            timed(stream, m_times.densityFwd, [&]() { partitionedForward(chunk_d, n, colorStride, stream); });
+            partitionedForward(chunk_d, n, colorStride, stream);
         } else if (n > 0 && m_fused) {
             timed(stream, m_times.densityFwd, [&]() {
                 throw_on_error(nb_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), d_positions.as<float>(), m_arena.Wh(dn->hashOffset()), chunk_d,
@@ -471,7 +487,7 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
                 });
             }
         }
-        if (m_partWorld > 1) timed(stream, m_times.colorBwd, [&]() { partitionedBackward(chunk_d, n, stream); });
+        if (m_partWorld > 1) partitionedBackward(chunk_d, n, stream);
         if (m_gradSync) m_gradSync(m_arena.G(0), m_arena.total, stream);
         optimizerStep(stream);
         trainStepCount++;
@@ -543,17 +559,24 @@ void InstantNerf::partitionedForward(const float* chunk_d, int64_t n, int colorS
     TinyMLP* cn = m_colorMLP;
     const int64_t B = (int64_t)m_opts.batchSize;
     const int world = (int)m_partWorld, rank = (int)m_partRank;
-    throw_on_error(nb_part_stamp_count(d_positions.as<float>(), B, n, stream), "partition: count");
-    m_partGather(d_positions.as<float>(), d_pos_all.as<float>(), (B + 1) * 4 * (int64_t)sizeof(float), stream);
-    throw_on_error(nb_part_encode(&dn->grid(), world, rank, B, d_pos_all.as<float>(), m_arena.Wh(dn->hashOffset()), d_pieces_send.as<void>(), stream),
-                   "partition: encode");
+    // phase times in this mode: shGather = positions to everybody, colorFwd = encoding of the owned levels, densityGrad =
+    // the two exchanges of pieces, densityFwd / colorBwd = the networks, densityBwd = packing, scatter = the owners' scatter
+    timed(stream, m_times.shGather, [&]() {
+        throw_on_error(nb_part_stamp_count(d_positions.as<float>(), B, n, stream), "partition: count");
+        m_partGather(d_positions.as<float>(), d_pos_all.as<float>(), (B + 1) * 4 * (int64_t)sizeof(float), stream);
+    });
+    timed(stream, m_times.colorFwd, [&]() {
+        throw_on_error(nb_part_encode(&dn->grid(), world, rank, B, d_pos_all.as<float>(), m_arena.Wh(dn->hashOffset()), d_pieces_send.as<void>(), stream),
+                       "partition: encode");
+    });
     const int64_t piece = (int64_t)(dn->grid().num_levels / world) * B * (int64_t)sizeof(uint32_t);
-    m_partExchange(d_pieces_send.as<void>(), d_pieces_recv.as<void>(), piece, stream);
-    if (n > 0)
+    timed(stream, m_times.densityGrad, [&]() { m_partExchange(d_pieces_send.as<void>(), d_pieces_recv.as<void>(), piece, stream); });
+    if (n > 0) timed(stream, m_times.densityFwd, [&]() {
         throw_on_error(nb_part_field_forward(&dn->grid(), &dn->desc(), &cn->desc(), world, B, d_pieces_recv.as<void>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
                                              m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
                                              m_arena.W(cn->biasOffset()), n, m_opts.densityBias, d_enc.as<half>(), d_sigma.as<float>(),
                                              d_density_out.as<float>(), d_color_out.as<float>(), colorStride, stream), "partition: field forward");
+    });
 }
 
 // Backward: the networks' gradients and dL/d(encoding) of this rank's samples, the latter packed by owner, exchanged, and
@@ -563,18 +586,22 @@ void InstantNerf::partitionedBackward(const float* chunk_d, int64_t n, cudaStrea
     TinyMLP* cn = m_colorMLP;
     const int64_t B = (int64_t)m_opts.batchSize;
     const int world = (int)m_partWorld, rank = (int)m_partRank;
-    if (n > 0) {
+    if (n > 0) timed(stream, m_times.colorBwd, [&]() {
         throw_on_error(nb_field_backward(&dn->desc(), &cn->desc(), d_enc.as<half>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
                                          m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
                                          m_arena.W(cn->biasOffset()), n, d_color_grad.as<half>(), d_tmpsigma.as<float>(),
                                          m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()), m_arena.G(cn->weightOffset()),
                                          m_arena.G(cn->biasOffset()), d_denc.as<half>(), nullptr, nullptr, nullptr, stream), "partition: field backward");
-    }
-    throw_on_error(nb_part_pack_denc(&dn->grid(), world, B, d_denc.as<half>(), n, d_pieces_send.as<void>(), stream), "partition: pack");
+    });
+    timed(stream, m_times.densityBwd, [&]() {
+        throw_on_error(nb_part_pack_denc(&dn->grid(), world, B, d_denc.as<half>(), n, d_pieces_send.as<void>(), stream), "partition: pack");
+    });
     const int64_t piece = (int64_t)(dn->grid().num_levels / world) * B * (int64_t)sizeof(uint32_t);
-    m_partExchange(d_pieces_send.as<void>(), d_pieces_recv.as<void>(), piece, stream);
-    throw_on_error(nb_part_scatter(&dn->grid(), world, rank, B, d_pos_all.as<float>(), d_pieces_recv.as<void>(), m_arena.G(dn->hashOffset()), stream),
-                   "partition: scatter");
+    timed(stream, m_times.densityGrad, [&]() { m_partExchange(d_pieces_send.as<void>(), d_pieces_recv.as<void>(), piece, stream); });
+    timed(stream, m_times.scatter, [&]() {
+        throw_on_error(nb_part_scatter(&dn->grid(), world, rank, B, d_pos_all.as<float>(), d_pieces_recv.as<void>(), m_arena.G(dn->hashOffset()), stream),
+                       "partition: scatter");
+    });
 }
 
 void InstantNerf::optimizerStep(cudaStream_t stream) {

@@ -149,6 +149,11 @@ public:
     // Between steps the levels a rank does not own go stale in its copy of the table; syncLevels() brings every rank's
     // copy up to date (fp16 forward copy; with `master` also the fp32 copy) and runs by itself before occupancy updates.
     // Call it before rendering, saving or comparing replicas.  world <= 1 switches back.
+    // Data parallelism: the density queries of an occupancy update (the only heavy part of it) are split over the ranks -
+    // rank r evaluates slice r of every batch of sampled cells - and `reduceMax` (an all-reduce with MAX over the ranks)
+    // runs on the per-cell maxima before they are folded into the grid.  A maximum does not depend on the order, so
+    // every rank ends with the bits a single GPU computes.  world <= 1 switches back.
+    void setOccupancyShard(uint32_t rank, uint32_t world, GradSync reduceMax);
     using BlockGather = std::function<void(const void* d_send, void* d_recv, int64_t bytes, cudaStream_t stream)>;
     using BlockExchange = std::function<void(const void* d_send, void* d_recv, int64_t bytes, cudaStream_t stream)>;
     void setLevelPartition(uint32_t rank, uint32_t world, BlockGather gather, BlockExchange exchange, GradSync reduce);
@@ -226,6 +231,9 @@ private:
     BlockExchange m_partExchange;
     GradSync m_partReduce;
     nb::DeviceMem d_pos_all, d_pieces_send, d_pieces_recv;
+    uint32_t m_occRank = 0, m_occWorld = 1;
+    GradSync m_occReduceMax;
+    void occupancyDensity(int count, cudaStream_t stream);   // density + per-cell maximum of d_occ_samples[0, count), this rank's slice
     void partitionedForward(const float* chunk_d, int64_t n, int colorStride, cudaStream_t stream);
     void partitionedBackward(const float* chunk_d, int64_t n, cudaStream_t stream);
     uint32_t m_rayScale = 1;

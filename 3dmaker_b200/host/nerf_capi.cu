@@ -130,6 +130,13 @@ extern "C" int nb_nerf_set_level_partition(nb_nerf* h, uint32_t rank, uint32_t w
         [reduce, user](float* g, int64_t count, cudaStream_t st) { reduce(user, g, count, st); }))
 }
 
+extern "C" int nb_nerf_set_occupancy_shard(nb_nerf* h, uint32_t rank, uint32_t world, nb_grad_sync_fn reduce_max, void* user) {
+    if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
+    if (world <= 1) { NB_GUARD(h->impl.setOccupancyShard(0, 1, nullptr)) }
+    if (!reduce_max) return nb_set_error(NB_ERR_INVALID, "nb_nerf_set_occupancy_shard: a MAX all-reduce is required");
+    NB_GUARD(h->impl.setOccupancyShard(rank, world, [reduce_max, user](float* g, int64_t count, cudaStream_t st) { reduce_max(user, g, count, st); }))
+}
+
 extern "C" int nb_nerf_sync_levels(nb_nerf* h, int master, void* stream) {
     if (!h) return nb_set_error(NB_ERR_INVALID, "null handle");
     NB_GUARD(h->impl.syncLevels((cudaStream_t)stream, master != 0))

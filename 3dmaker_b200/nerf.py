@@ -177,6 +177,23 @@ class InstantNerf:
         self._part_cbs = (nb.BLOCK_FN(gather_cb), nb.BLOCK_FN(exchange_cb), nb.GRAD_SYNC_FN(reduce_cb))
         nb.check(self.lib.nb_nerf_set_level_partition(self.h, rank, world, *self._part_cbs, None), "nb_nerf_set_level_partition")
 
+    def set_occupancy_shard(self, rank, world, reduce_max):
+        """Occupancy updates split over the ranks (see nb_nerf_set_occupancy_shard): reduce_max(tensor_f32) must be an
+        all-reduce with MAX over the ranks.  world <= 1 switches back."""
+        if world <= 1 or reduce_max is None:
+            nb.check(self.lib.nb_nerf_set_occupancy_shard(self.h, 0, 1, nb.GRAD_SYNC_FN(0), None), "nb_nerf_set_occupancy_shard")
+            self._occ_cb = None
+            return
+        views = {}
+
+        def trampoline(user, ptr, count, stream):
+            key = (int(ptr), int(count))
+            if key not in views:
+                views[key] = view_tensor(self.torch, int(ptr), int(count), np.float32)
+            reduce_max(views[key])
+        self._occ_cb = nb.GRAD_SYNC_FN(trampoline)
+        nb.check(self.lib.nb_nerf_set_occupancy_shard(self.h, rank, world, self._occ_cb, None), "nb_nerf_set_occupancy_shard")
+
     def sync_levels(self, master=False, stream=None):
         """Level-partitioned training: brings the levels this rank does not own up to date (all ranks must call it)."""
         nb.check(self.lib.nb_nerf_sync_levels(self.h, 1 if master else 0, nb.stream_ptr(stream)), "nb_nerf_sync_levels")

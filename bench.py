@@ -769,8 +769,11 @@ def run_scene(args, rank, world, local_rank, embedded=False):
     else:
         eng = nm.InstantNerf(torch, opts)
         # data parallel: every rank takes DP_STEPS optimizer steps on its rays of a call (one occupancy walk per call)
-        trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None, steps_per_call=6, registered_gradient=not args.plain_buffers,
-                                        exchange=args.exchange)
+        # config 3: 65536 rays per rank and call hold 6-7 batches of 2^18 samples; config 5: a rank's share of the 2^19 rays
+        # holds 17 batches of its share of the 2^21 samples at every N.  Rays walked but not trained on are wasted march time.
+        trainer = D.DataParallelTrainer(torch, eng, dist if world > 1 else None, steps_per_call=16 if cfg5 else 6,
+                                        registered_gradient=not args.plain_buffers,
+                                        exchange=args.exchange or ("levels" if cfg5 else "peer"))
     batches = _scene_batches(torch, syn, 4 if cfg5 else 8, rays * nranks, 9000, config=5 if cfg5 else 3)
 
     used = [0]
@@ -790,6 +793,9 @@ def run_scene(args, rank, world, local_rank, embedded=False):
     torch.cuda.synchronize()
     if world > 1 and not reference:
         dist.barrier()
+    if args.phases and not reference:
+        eng.set_profiling(True)      # every phase is waited for: the per-phase times add up, the step gets slower
+        p0, s0 = eng.phase_times()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     samples = 0
     steps_before = eng.steps if reference else eng.steps.value
@@ -825,14 +831,17 @@ def run_scene(args, rank, world, local_rank, embedded=False):
             line["config"]["exchange"] = trainer.exchange if world > 1 else None
             if args.grad_half:
                 line["config"]["grad_table"] = "fp16 x 2^%d (opt-in A/B)" % args.grad_scale_log2
+            if args.phases:
+                p1, s1 = eng.phase_times()
+                line["config"]["phase_ms_per_optimizer_step"] = {k: round((p1[k] - p0[k]) / max(s1 - s0, 1), 4) for k in p1}
             if world > 1:
                 line["config"]["exchange_stats"] = trainer.exchange_stats()
         if not embedded:
             print(json.dumps(line))
+    if trainer is not None:
+        trainer.close()          # peer exchange: meets the other ranks before it unmaps their memory
     if trainer is not None and world > 1 and not embedded:
         dist.barrier(); dist.destroy_process_group()
-    if trainer is not None:
-        trainer.close()
     eng.close()
     return line
 
@@ -1000,9 +1009,11 @@ def main():
     ap.add_argument("--extra-scene-warm", type=int, default=48, help="untimed train_rays calls of the embedded scene5 measurement "
                     "(six optimizer steps each: past the 256 steps of whole-grid occupancy updates)")
     ap.add_argument("--render-frames", type=int, default=12, help="timed frames of the embedded render measurement")
-    ap.add_argument("--exchange", default="peer", choices=["allreduce", "sharded", "peer", "levels"],
+    ap.add_argument("--exchange", default=None, choices=["allreduce", "sharded", "peer", "levels"],
                     help="scene workloads at N > 1: all-reduce + replicated Adam; reduce-scatter + Adam on a table slice + all-gather of fp16 "
-                         "parameters; or the same three stages as one kernel over peer memory (default)")
+                         "parameters; the same three stages as one kernel over peer memory (default for config 3); or the table "
+                         "partitioned by level, encodings exchanged instead of the table (default for config 5, whose table outweighs "
+                         "a step's samples)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="nb_set_tuning switch for A/B runs, e.g. pair_ops=0")
     ap.add_argument("--separate-loss", action="store_true", help="keep the MSE loss a launch of its own instead of the forward's epilogue (A/B)")
     ap.add_argument("--separate-scatter", action="store_true", help="keep the gradient scatter a launch of its own (A/B)")
@@ -1013,6 +1024,8 @@ def main():
     ap.add_argument("--render-rounds", action="store_true", help="render workload: render in rounds of samples per ray (A/B; off by default)")
     ap.add_argument("--plain-buffers", action="store_true", help="N > 1: keep the gradient in ordinary device memory instead of memory "
                     "registered with the communicator (A/B)")
+    ap.add_argument("--phases", action="store_true", help="scene workloads: per-phase device times of the engine (waits after every phase: "
+                                                          "the line's throughput is NOT a benchmark value then)")
     ap.add_argument("--grad-half", action="store_true", help="keep the table gradient in half precision (A/B; off by default: the reference keeps fp32)")
     ap.add_argument("--grad-scale-log2", type=int, default=7, help="with --grad-half: contributions are multiplied by 2^this before they are rounded to fp16")
     ap.add_argument("--ordered", action="store_true", help="sort every batch by brick and run the field kernels in that order (A/B; off by default)")

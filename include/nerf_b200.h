@@ -627,6 +627,11 @@ int nb_nerf_set_peer_exchange(nb_nerf* h, uint32_t rank, uint32_t world, const f
  * copy as well) - call it before rendering, saving or comparing replicas.  world must divide the number of levels; the
  * fused field kernels are required; not together with nb_nerf_set_optimizer_shard / nb_nerf_set_peer_exchange /
  * nb_nerf_set_grad_sync.  world <= 1 switches back. */
+/* Data parallelism: rank `rank` evaluates only its share of the density queries of every occupancy update
+ * (InstantNerf.cu:1009-1204 evaluates all of them on its one GPU) and reduce_max - an all-reduce with MAX over the ranks,
+ * on `count` floats - merges the per-cell maxima before they are folded into the grid; the resulting bits are those of a
+ * single GPU.  world <= 1 switches back. */
+int nb_nerf_set_occupancy_shard(nb_nerf* h, uint32_t rank, uint32_t world, nb_grad_sync_fn reduce_max, void* user);
 typedef void (*nb_block_fn)(void* user, const void* d_send, void* d_recv, int64_t bytes, void* stream);
 int nb_nerf_set_level_partition(nb_nerf* h, uint32_t rank, uint32_t world, nb_block_fn gather, nb_block_fn exchange, nb_grad_sync_fn reduce,
                                 void* user);
