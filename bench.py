@@ -423,7 +423,7 @@ def time_kernels(torch, tr, n, iters=5):
 ALGO_BYTES = {"grid_mlp_forward": 592.0, "field_forward": 644.0, "scatter_backward": 1104.0, "field_backward_scatter": 1132.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at 2^20 samples, from the ncu capture summarised in
 # profiles/field_step_kernels_2p20_ncu.md (same workload, same sizes)
-NCU_TRAFFIC = {"field_forward": 120.3e6, "field_backward_scatter": 192.9e6}
+NCU_TRAFFIC = {"field_forward": 159.7e6, "field_backward_scatter": 190.9e6 + 33.7e6}   # backward kernel + the levels 0-1 kernel
 
 
 def bind_to_gpu_numa_node(torch, local_rank):

@@ -185,7 +185,7 @@ class _ThreadDist:
         self.s.barrier.wait()
 
 
-@pytest.mark.parametrize("world,exchange", [(2, "levels"), (4, "levels"), (2, "allreduce")])
+@pytest.mark.parametrize("world,exchange", [(2, "levels"), (4, "levels"), (8, "levels"), (2, "allreduce")])
 def test_level_partitioned_engine_trains_like_one_engine_on_all_rays(cuda, nb, world, exchange):
     """`world` scene engines on one device, one thread each, table partitioned by level (or, for comparison, replicated with
     an all-reduce of the gradient; either way the occupancy updates are split over the ranks), against ONE engine given all the

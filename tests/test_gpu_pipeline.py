@@ -440,7 +440,7 @@ def test_compact_host_batches_train_like_full_layout_ones(cuda, nb):
     assert abs(losses["full"] - losses["compact"]) <= 1e-6 * losses["full"] and losses["full"] > 0
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_peer_optimizer_kernel_equals_reduce_then_adam(cuda, nb, world):
     """nb_adam_step_peer with the ranks played by separate buffers on ONE device (the kernel never waits for another rank,
     so the ranks' launches simply run one after the other): every rank's fp16 parameters end up equal to what one Adam
