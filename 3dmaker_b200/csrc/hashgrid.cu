@@ -265,7 +265,9 @@ static int scatter_launch_from(const GridParams& gp, const Fetch& in, int64_t ro
             int N_l = (int)std::floor(gp.sscales[l]);
             smem_bytes = std::max(smem_bytes, (size_t)(N_l + 1) * (N_l + 1) * (N_l + 1) * sizeof(float2));
         }
-        NB_CUDA(cudaFuncSetAttribute(scatter_smem_kernel<Fetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+        // always the cap, not this launch's size: the attribute belongs to the function, and two host threads launching
+        // levels of different size would otherwise lower it under each other's feet
+        NB_CUDA(cudaFuncSetAttribute(scatter_smem_kernel<Fetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCATTER_SMEM_CAP));
         int per_level = std::max(1, nb_num_sms() * 2 / (smem_end - lb));
         int64_t need = (rows + 255) / 256;
         dim3 grid((unsigned)std::min<int64_t>(per_level, need), smem_end - lb, 1);
