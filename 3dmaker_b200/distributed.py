@@ -141,7 +141,8 @@ class DataParallelTrainer:
                    their gradients (128 bytes per sample in all) and an all-reduce of the networks' few thousand gradients;
                    no table gradient and no table parameter crosses the wire.  For tables that outweigh a step's samples
                    (T = 2^22: 805 MB of table traffic per step and rank against 34-270 MB of encodings).  The levels a
-                   rank does not own go stale between occupancy updates: sync() before rendering, saving or comparing."""
+                   rank does not own go stale between occupancy updates: sync() before rendering, saving or comparing
+                   (close() does it, fp32 master copy included; the Adam moments of a level stay with its owner)."""
 
     def __init__(self, torch, engine, dist=None, steps_per_call=1, registered_gradient=False, exchange="allreduce", shard_occupancy=True):
         self.torch, self.engine, self.dist = torch, engine, dist
@@ -273,6 +274,8 @@ class DataParallelTrainer:
                 self.engine.set_peer_exchange(0, 1, None, None, None)
                 self._peer_g.close(); self._peer_w.close()
             if self.exchange == "levels":
+                self.engine.sync_levels(True)    # every rank leaves with the whole table, fp32 master included (all ranks close)
+                self.torch.cuda.synchronize()
                 self.engine.set_level_partition(0, 1, None, None, None)
             if getattr(self, "_occupancy_sharded", False):
                 self.engine.set_occupancy_shard(0, 1, None)
