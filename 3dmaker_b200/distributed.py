@@ -275,7 +275,8 @@ class DataParallelTrainer:
                 self._peer_g.close(); self._peer_w.close()
             if self.exchange == "levels":
                 self.engine.sync_levels(True)    # every rank leaves with the whole table, fp32 master included (all ranks close)
-                self.torch.cuda.synchronize()
+                if self.torch.cuda.is_available():
+                    self.torch.cuda.synchronize()
                 self.engine.set_level_partition(0, 1, None, None, None)
             if getattr(self, "_occupancy_sharded", False):
                 self.engine.set_occupancy_shard(0, 1, None)

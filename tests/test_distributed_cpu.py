@@ -27,6 +27,7 @@ class FakeEngine:
         self.g = torch.zeros(18, dtype=torch.float32)
         self.scale, self.sync, self.single, self.steps, self.max_rays, self.consumed = 1, None, 0, 0, max_rays, 0
         self.shard, self.param_sync = None, None
+        self.part = None
 
     def arena(self):
         class View:
@@ -35,6 +36,56 @@ class FakeEngine:
 
     def set_optimizer_shard(self, rank, world, fn):
         self.shard, self.param_sync = ((rank, world), fn) if world > 1 and fn is not None else (None, None)
+
+    def set_level_partition(self, rank, world, gather, exchange, reduce):
+        self.part = (rank, world, gather, exchange, reduce) if world > 1 else None
+
+    def sync_levels(self, master=False):
+        """Owned table parameters to every rank (the real engine all-gathers whole levels)."""
+        rank, world, gather, _, _ = self.part
+        for arr in ([self.w_h, self.w] if master else [self.w_h]):
+            mine = arr[rank:FakeEngine.SPARSE:world].contiguous()
+            everybody = torch.zeros(world * mine.numel(), dtype=arr.dtype)
+            gather(mine, everybody)
+            for q in range(world):
+                arr[q:FakeEngine.SPARSE:world] = everybody[q * mine.numel():(q + 1) * mine.numel()]
+
+    def _partitioned_step(self, x, target, n_global):
+        """The level partition's protocol on the linear field: table parameter j belongs to rank j % world.  Inputs of
+        all ranks are gathered, every owner computes ITS parameters' share of every rank's prediction, the shares travel
+        to the samples' ranks (all-to-all), the errors travel back (all-to-all), every owner forms the gradient of its
+        parameters from all ranks' samples; the two dense parameters are reduced and updated by everybody."""
+        rank, world, gather, exchange, reduce = self.part
+        k, cap = x.shape[0], 64                                       # cap: fixed slot size, as the engine's batch capacity
+        slot = torch.zeros((cap + 1, 6)); slot[:k] = x; slot[cap, 0] = k
+        slots = torch.zeros((world, cap + 1, 6))
+        gather(slot.view(-1), slots.view(-1))
+        W = self.w_h.float().view(3, 6)
+        own = torch.zeros(18, dtype=torch.bool); own[rank:FakeEngine.SPARSE:world] = True
+        dense = torch.zeros(18, dtype=torch.bool); dense[FakeEngine.SPARSE:] = True
+        W_own = torch.where(own.view(3, 6), W, torch.zeros_like(W))
+        send = torch.stack([slots[q, :cap] @ W_own.t() for q in range(world)])          # [world][cap][3]: piece q for rank q
+        recv = torch.zeros_like(send)
+        exchange(send.view(-1), recv.view(-1))
+        W_dense = torch.where(dense.view(3, 6), W, torch.zeros_like(W))
+        pred = recv.sum(0)[:k] + x @ W_dense.t()
+        err = torch.zeros((cap, 3)); err[:k] = pred - target
+        back = torch.stack([err] * world)                                                # every owner needs this rank's errors
+        got = torch.zeros_like(back)
+        exchange(back.view(-1), got.view(-1))
+        g = torch.zeros(3, 6)
+        for q in range(world):
+            cnt = int(slots[q, cap, 0].item())
+            g += 2.0 * got[q, :cnt].t() @ slots[q, :cnt] / n_global
+        self.g += torch.where(own, g.reshape(-1), torch.zeros(18))
+        g_dense = (2.0 * err[:k].t() @ x / n_global).reshape(-1)
+        tail = g_dense[FakeEngine.SPARSE:].clone()
+        reduce(tail)
+        self.g[FakeEngine.SPARSE:] += tail
+        upd = own | dense
+        self.w[upd] -= 0.1 * self.g[upd]
+        self.w_h[upd] = self.w[upd].half()
+        self.g.zero_()
 
     def set_global_ray_scale(self, s):
         self.scale = s
@@ -56,6 +107,10 @@ class FakeEngine:
         while (taken < self.single) if self.single else (done < n):
             k = min(self.max_rays, n - done)
             x = torch.cat([o[done:done + k], d[done:done + k]], dim=1)
+            if self.part is not None:
+                self._partitioned_step(x, rgb[done:done + k], n * self.scale)
+                self.steps += 1; done += k; taken += 1; self.consumed = done
+                continue
             err = x @ self.w_h.float().view(3, 6).t() - rgb[done:done + k]
             self.g += (2.0 * err.t() @ x / (n * self.scale)).reshape(-1)
             if self.sync is not None:
@@ -126,6 +181,20 @@ def _worker(rank, world, port, out_dir, case):
             for c in range(4):
                 tr.train_rays(*_batch(64, 40 + c))
             np.save(os.path.join(out_dir, "ar_w%d.npy" % rank), eng.w.numpy())
+        elif case == "levels":
+            # table partitioned over the ranks: positions gathered, shares exchanged, errors exchanged back, dense tail reduced
+            eng = FakeEngine(max_rays=20 if rank == 1 else 1 << 30)
+            tr = D.DataParallelTrainer(torch, eng, dist, steps_per_call=2, exchange="levels")
+            for c in range(4):
+                tr.train_rays(*_batch(64, 40 + c))
+            stale = eng.w_h.clone()
+            in_sync = int(tr.replicas_in_sync())            # makes the table whole first
+            tr.gather_master()
+            np.save(os.path.join(out_dir, "lv_w%d.npy" % rank), eng.w.numpy())
+            np.save(os.path.join(out_dir, "lv_stale%d.npy" % rank), stale.float().numpy())
+            np.save(os.path.join(out_dir, "meta%d.npy" % rank), np.array([eng.steps, in_sync]))
+            tr.close()
+            assert eng.part is None
         elif case == "overflow":
             # rank 1's sample batch holds only 20 of its 32 rays: it still takes ONE step and ONE exchange
             eng = FakeEngine(max_rays=20 if rank == 1 else 1 << 30)
@@ -238,6 +307,22 @@ def test_sharded_optimizer_equals_the_allreduce_exchange(tmp_path):
     for r in range(2):
         meta = np.load(tmp_path / ("meta%d.npy" % r))
         assert list(meta) == [8, 8, 1]
+
+
+def test_level_partition_equals_the_allreduce_exchange(tmp_path):
+    """exchange="levels" through gloo: the three collectives deliver the right blocks (the fake engine runs the engine's
+    protocol on a linear field), every rank ends with the parameters the all-reduce exchange gives, and before the table
+    is made whole a rank's copy of the parameters it does not own is stale."""
+    _run("levels", tmp_path)
+    _run("sharded_vs_allreduce", tmp_path)
+    w0, w1 = np.load(tmp_path / "lv_w0.npy"), np.load(tmp_path / "lv_w1.npy")
+    assert np.array_equal(w0, w1)
+    assert np.allclose(w0, np.load(tmp_path / "ar_w0.npy"), rtol=1e-4, atol=1e-5)
+    s0 = np.load(tmp_path / "lv_stale0.npy")
+    half = w0.astype(np.float16).astype(np.float32)
+    assert np.array_equal(s0[0:16:2], half[0:16:2]) and not np.array_equal(s0[1:16:2], half[1:16:2])   # rank 0 owns the even ones
+    for r in range(2):
+        assert list(np.load(tmp_path / ("meta%d.npy" % r))) == [8, 1]
 
 
 def test_replica_drift_is_detected(tmp_path):
