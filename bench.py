@@ -990,13 +990,100 @@ def run_extras(args, rank, world, local_rank):
     return out
 
 
+def run_partition_kernels(args):
+    """The kernels of the level-partitioned step on ONE GPU, at config-5 sizes: this device plays rank 0 of `--ranks`
+    (it owns levels 0, R, 2R, ...), the other ranks' samples are random positions in their slots, the exchanges are
+    skipped (their buffers are simply there).  Per-kernel CUDA-event times next to the replicated path's fused kernels
+    on the same number of own samples.  Not a throughput claim for the multi-GPU step: it times what one rank computes."""
+    import ctypes
+    import torch
+    torch.cuda.set_device(0)
+    nb = importlib.import_module("3dmaker_b200")
+    pl = importlib.import_module("3dmaker_b200.pipeline")
+    from helpers import make_mlp
+    lib, P, st = nb.load(), nb.ptr, nb.stream_ptr()
+    R, Tp = args.ranks, 1 << 22
+    cap = SCENE5_GLOBAL_BATCH // R
+    own = L // R
+    model = pl.FieldModel(torch, L, Tp, BASE, 1.3819, DENSITY[1], DENSITY[3], COLOR[1], COLOR[3])
+    model.w[:model.hash_count].uniform_(-1e-4, 1e-4)
+    model.w_h[:model.hash_count].copy_(model.w[:model.hash_count].half())
+    model.load_density_weights(*make_mlp(*DENSITY, seed=1)); model.load_color_weights(*make_mlp(*COLOR, seed=1))
+    G, D, C = ctypes.byref(model.grid), ctypes.byref(model.density), ctypes.byref(model.color)
+    g = torch.Generator(device="cuda"); g.manual_seed(5)
+    pos_all = torch.rand((R, cap + 1, 4), generator=g, device="cuda")
+    for q in range(R):
+        nb.check(lib.nb_part_stamp_count(ctypes.c_void_p(pos_all[q].data_ptr()), cap, cap, st), "nb_part_stamp_count")
+    pos = pos_all[0, :cap].contiguous()
+    dirs = torch.nn.functional.normalize(torch.randn((cap, 3), generator=g, device="cuda"), dim=1).contiguous()
+    pieces = torch.zeros((R, own, cap), dtype=torch.int32, device="cuda")
+    pieces2 = torch.zeros_like(pieces)
+    enc = torch.zeros((cap, 32), dtype=torch.float16, device="cuda")
+    denc = torch.zeros((cap, 32), dtype=torch.float16, device="cuda")
+    sigma, logit = torch.zeros(cap, device="cuda"), torch.zeros(cap, device="cuda")
+    rgb = torch.zeros((cap, 4), device="cuda")
+    dcol = (torch.randn((cap, 8), generator=g, device="cuda") * 1e-3).half()
+    w = (model.ptr("w_h", model.off_dw), model.ptr("w", model.off_db), model.ptr("w_h", model.off_cw), model.ptr("w", model.off_cb))
+    gw = (model.ptr("g", model.off_dw), model.ptr("g", model.off_db), model.ptr("g", model.off_cw), model.ptr("g", model.off_cb))
+    level = model.hash_count // L
+    hyper = (1e-2, 0.9, 0.99, 1e-15, 0.1, 0.01, 1.0 / 128.0, 1, st)
+
+    def owned_adam():
+        rc = 0
+        for l in range(0, L, R):
+            off = l * level
+            rc |= lib.nb_adam_step(model.ptr("w", off), model.ptr("w_h", off), model.ptr("g", off), model.ptr("m", off), model.ptr("v", off), level, level, *hyper)
+        return rc
+
+    calls = [
+        ("part_encode (own levels, all ranks' samples)", lambda: lib.nb_part_encode(G, R, 0, cap, P(pos_all), model.ptr("w_h", 0), P(pieces), st),
+         R * cap * own * (16.0 / own + 8 * 4 + 4)),
+        ("part_field_forward (networks from pieces)", lambda: lib.nb_part_field_forward(G, D, C, R, cap, P(pieces), P(dirs), None, 0, *w, cap, 1.0, P(enc), P(sigma),
+                                                                                       P(logit), P(rgb), 4, st), cap * (64.0 + 12 + 64 + 24)),
+        ("field_backward (no table gradient)", lambda: lib.nb_field_backward(D, C, P(enc), P(dirs), None, 0, *w, cap, P(dcol), None, *gw, P(denc), None, None, None, st),
+         cap * (64.0 + 12 + 16 + 64)),
+        ("part_pack_denc", lambda: lib.nb_part_pack_denc(G, R, cap, P(denc), cap, P(pieces2), st), cap * 128.0),
+        ("part_scatter (own levels, all ranks' samples)", lambda: lib.nb_part_scatter(G, R, 0, cap, P(pos_all), P(pieces2), model.ptr("g", 0), st),
+         R * cap * own * (16.0 / own + 4 + 8 * 8)),
+        ("adam on the owned levels", owned_adam, None),
+        ("replicated: field_forward on the own samples", lambda: lib.nb_field_forward(G, D, C, P(pos), model.ptr("w_h", 0), P(dirs), None, 0, *w, cap, 1.0, P(enc), P(sigma),
+                                                                                       P(logit), P(rgb), 4, st), cap * ALGO_BYTES["field_forward"]),
+        ("replicated: field_backward with the scatter", lambda: lib.nb_field_backward(D, C, P(enc), P(dirs), None, 0, *w, cap, P(dcol), None, *gw, P(denc), G, P(pos),
+                                                                                       model.ptr("g", 0), st), cap * ALGO_BYTES["field_backward_scatter"]),
+        ("replicated: adam on the whole arena", lambda: lib.nb_adam_step(model.ptr("w", 0), model.ptr("w_h", 0), model.ptr("g", 0), model.ptr("m", 0), model.ptr("v", 0),
+                                                                        model.hash_count, model.total, *hyper), None),
+    ]
+    peak, peak_source = load_peaks()
+    out = {}
+    for name, fn, nbytes in calls:
+        ts = []
+        for i in range(args.warmup + args.steps):
+            if "adam" in name:
+                model.g[:model.hash_count].uniform_(-1e-3, 1e-3)          # every entry touched, as a config-5 step leaves it
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            nb.check(fn(), name)
+            b.record(); b.synchronize()
+            if i >= args.warmup:
+                ts.append(a.elapsed_time(b))
+        ms = float(np.median(ts))
+        out[name] = {"ms": round(ms, 4)}
+        if nbytes:
+            out[name]["algorithmic_GBs"] = round(nbytes / ms / 1e6, 1)
+            if peak:
+                out[name]["frac_of_%s_hbm" % peak_source] = round(nbytes / ms / 1e6 / peak, 3)
+    print(json.dumps({"metric": "kernel ms of one rank's share of a level-partitioned step", "n_gpus": 1, "ranks_played": R, "dtype": "f16",
+                      "data": "synthetic", "config": {"workload": "cfg5 grid (L16 F2 T2^22 b1.3819), 2^21 / ranks samples per rank, uniformly scattered",
+                                                       "samples_per_rank": cap, "owned_levels": own}, "kernel_ms": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="field", choices=["field", "scene", "scene5", "render"],
+    ap.add_argument("--workload", default="field", choices=["field", "scene", "scene5", "render", "partition"],
                     help="field: the headline step on explicit samples (default, the driver's line); scene / scene5: full NeRF training step on the "
                          "analytic scene of config 3 / config 5; render: 1920x1080 orbit frames, pixels sharded over the ranks")
     ap.add_argument("--batch-log2", type=int, default=20, help="field workload: log2 of the samples per GPU and step (20 = the benchmark's; "
@@ -1024,6 +1111,7 @@ def main():
     ap.add_argument("--render-rounds", action="store_true", help="render workload: render in rounds of samples per ray (A/B; off by default)")
     ap.add_argument("--plain-buffers", action="store_true", help="N > 1: keep the gradient in ordinary device memory instead of memory "
                     "registered with the communicator (A/B)")
+    ap.add_argument("--ranks", type=int, default=8, help="partition workload: how many ranks the one device pretends to be one of")
     ap.add_argument("--phases", action="store_true", help="scene workloads: per-phase device times of the engine (waits after every phase: "
                                                           "the line's throughput is NOT a benchmark value then)")
     ap.add_argument("--grad-half", action="store_true", help="keep the table gradient in half precision (A/B; off by default: the reference keeps fp32)")
@@ -1039,7 +1127,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload in ("scene", "scene5"):
+    if args.workload == "partition":
+        run_partition_kernels(args)
+    elif args.workload in ("scene", "scene5"):
         run_scene(args, rank, world, local_rank)
     elif args.workload == "render":
         run_render(args, rank, world, local_rank)
