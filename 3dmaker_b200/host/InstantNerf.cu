@@ -344,10 +344,16 @@ void InstantNerf::trainWithRaysHit(const float3* d_rays_o, const float3* d_rays_
             recordHits(0);
             m_lastTotalHits = 0;
             if (m_trainSteps % 16 == 0) {
+                if (m_partWorld > 1) syncLevels(stream);
                 timed(stream, m_times.occupancy, [&]() {
                     if (m_trainSteps < 256) earlyOccupancyGridUpdate(stream);
                     else lateOccupancyGridUpdate(stream);
                 });
+            }
+            if (m_partWorld > 1) {
+                // no samples of its own, but this rank's levels are needed for everybody else's: it joins every exchange
+                partitionedForward(nullptr, 0, m_fused ? 4 : 8, stream);
+                partitionedBackward(nullptr, 0, stream);
             }
             if (m_gradSync) m_gradSync(m_arena.G(0), m_arena.total, stream);
             optimizerStep(stream);

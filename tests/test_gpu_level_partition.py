@@ -185,13 +185,15 @@ class _ThreadDist:
         self.s.barrier.wait()
 
 
-@pytest.mark.parametrize("world,exchange", [(2, "levels"), (4, "levels"), (8, "levels"), (2, "allreduce")])
-def test_level_partitioned_engine_trains_like_one_engine_on_all_rays(cuda, nb, world, exchange):
+@pytest.mark.parametrize("world,exchange,per_call", [(2, "levels", 1), (4, "levels", 1), (8, "levels", 1), (2, "allreduce", 1), (2, "levels", 2)])
+def test_level_partitioned_engine_trains_like_one_engine_on_all_rays(cuda, nb, world, exchange, per_call):
     """`world` scene engines on one device, one thread each, table partitioned by level (or, for comparison, replicated with
     an all-reduce of the gradient; either way the occupancy updates are split over the ranks), against ONE engine given all the
     rays: the same optimizer steps (every rank's rays fit its batch), so after 6 steps the parameters agree up to the
     summation order of the gradients - compared through the loss of the next step and the fp16 tables themselves - and
-    all ranks hold the same table after sync_levels."""
+    all ranks hold the same table after sync_levels.  per_call = 2: every call takes a second optimizer step for which no
+    rank has rays left - the ranks still meet in every exchange of that step (their levels would be needed by a rank
+    that had samples) and the optimizer runs on what momentum is left, exactly as one engine told to take two steps."""
     import threading
     torch = cuda
     nm = importlib.import_module("3dmaker_b200.nerf"); syn = importlib.import_module("3dmaker_b200.synthetic")
@@ -207,7 +209,7 @@ def test_level_partitioned_engine_trains_like_one_engine_on_all_rays(cuda, nb, w
         batches.append((o, d, syn.ground_truth(torch, scene, o, d, bg)))
     # ---- one engine, all rays (batch large enough for every ray: one optimizer step per call)
     one = nm.InstantNerf(torch, nm.default_options(**dict(base, batch_size=1 << 20, render_batch_size=1 << 18, ray_chunk_size=rays_global)))
-    one.set_single_step(True)
+    one.set_steps_per_call(per_call)
     for o, d, t in batches:
         one.train_rays(o, d, t)
         assert one.rays_consumed() == rays_global
@@ -224,7 +226,7 @@ def test_level_partitioned_engine_trains_like_one_engine_on_all_rays(cuda, nb, w
             torch.cuda.set_device(0)
             eng = nm.InstantNerf(torch, nm.default_options(**dict(base, batch_size=(1 << 20) // world, render_batch_size=1 << 18,
                                                                   ray_chunk_size=rays_global // world)))
-            tr = D.DataParallelTrainer(torch, eng, _ThreadDist(shared, rank), steps_per_call=1, exchange=exchange)
+            tr = D.DataParallelTrainer(torch, eng, _ThreadDist(shared, rank), steps_per_call=per_call, exchange=exchange)
             for o, d, t in batches:
                 assert tr.train_rays(o, d, t) == rays_global // world
             in_sync = tr.replicas_in_sync()
