@@ -176,6 +176,8 @@ _SIGNATURES = {
     "nb_part_field_forward": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_int, c_int64, c_void_p, c_void_p,
                               c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_int, c_void_p]),
+    "nb_part_field_backward": (c_int, [ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_part_pack_denc": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     "nb_part_scatter": (c_int, [ctypes.POINTER(GridDesc), c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nb_field_forward_mse": (c_int, [ctypes.POINTER(GridDesc), ctypes.POINTER(MlpDesc), ctypes.POINTER(MlpDesc), c_void_p, c_void_p, c_void_p,

@@ -542,6 +542,11 @@ struct FieldGradIO {
     const float* pos4;
     float* table_grads;
     int scatter_begin;
+    // level-partitioned step (level_partition.cu): dL/d(encoding) goes straight into the pieces for the levels' owners,
+    // level l of sample i at pieces[((l % piece_ranks) * (L / piece_ranks) + l / piece_ranks) * piece_cap + i]
+    uint32_t* pieces;
+    int piece_ranks;
+    int64_t piece_cap;
 };
 
 template <class DS, class CS>
@@ -709,6 +714,17 @@ __global__ void __launch_bounds__(CTA_THREADS, 2) field_backward_kernel(const __
                         uint2 v = *reinterpret_cast<const uint2*>(&sDZ[(16 * warp + r) * HS + c4 * 4]);
                         *reinterpret_cast<uint2*>(&gio.denc[gr * gio.denc_cols + c4 * 4]) = v;
                     }
+                }
+            }
+            if (gio.pieces != nullptr) {
+                // the warp's 16 rows, level by level: 64 contiguous bytes per level in the owner's piece
+                const int own = (DS::K0 / 2) / gio.piece_ranks;
+                for (int ch = lane; ch < 16 * (DS::K0 / 2); ch += 32) {
+                    const int l = ch >> 4, r = ch & 15;
+                    const int64_t gr = row0 + r;
+                    if (gr < io.n)
+                        gio.pieces[((int64_t)(l % gio.piece_ranks) * own + l / gio.piece_ranks) * gio.piece_cap + gr] =
+                            *reinterpret_cast<const uint32_t*>(&sDZ[(16 * warp + r) * HS + 2 * l]);
                 }
             }
             if (gio.table_grads != nullptr) {
@@ -913,9 +929,10 @@ static int field_backward_impl(const nb_mlp_desc* density, const nb_mlp_desc* co
                                const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n,
                                const void* d_dcolor_h, const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b,
                                float* d_grad_color_w, float* d_grad_color_b, void* d_denc_h, const nb_grid_desc* grid,
-                               const float* d_pos4, float* d_table_grads, void* stream, const uint32_t* d_perm) {
+                               const float* d_pos4, float* d_table_grads, void* stream, const uint32_t* d_perm,
+                               uint32_t* d_pieces = nullptr, int piece_ranks = 0, int64_t piece_cap = 0) {
     if (!density || !color || !d_enc_h || !d_dirs3 || !d_density_w_h || !d_density_b || !d_color_w_h || !d_color_b || !d_dcolor_h ||
-        !d_grad_density_w || !d_grad_density_b || !d_grad_color_w || !d_grad_color_b || !d_denc_h || n < 0)
+        !d_grad_density_w || !d_grad_density_b || !d_grad_color_w || !d_grad_color_b || (!d_denc_h && !d_pieces) || n < 0)
         return nb_set_error(NB_ERR_INVALID, "nb_field_backward: null pointer or negative count");
     if (!is_shape(density, 32, 64, 16, 2) || !is_shape(color, 32, 64, 8, 3))
         return nb_set_error(NB_ERR_UNSUPPORTED, "nb_field_backward: built for density 32-64-16 and colour 32-64-64-8");
@@ -935,6 +952,7 @@ static int field_backward_impl(const nb_mlp_desc* density, const nb_mlp_desc* co
     gio.enc = (const __half*)d_enc_h; gio.dcolor = (const __half*)d_dcolor_h; gio.dsigma = d_dsigma;
     gio.dWd = d_grad_density_w; gio.dbd = d_grad_density_b; gio.dWc = d_grad_color_w; gio.dbc = d_grad_color_b;
     gio.denc = (__half*)d_denc_h; gio.denc_cols = 32;
+    if (d_pieces != nullptr) { gio.denc = nullptr; gio.denc_cols = 0; gio.pieces = d_pieces; gio.piece_ranks = piece_ranks; gio.piece_cap = piece_cap; }
     nb::GridParams gp{};
     int shared_levels = 0;
     const bool scatter = d_table_grads != nullptr;
@@ -949,7 +967,8 @@ static int field_backward_impl(const nb_mlp_desc* density, const nb_mlp_desc* co
         gio.pos4 = d_pos4; gio.table_grads = d_table_grads; gio.scatter_begin = shared_levels;
         gio.denc_cols = 4 * shared_levels;   // only what the shared-memory scatter kernel below reads
     }
-    const int tc_mode = d_perm != nullptr ? 1 : nb::g_backward_tc.load();
+    // pieces are written by the register kernel only (it is also the faster one on the ray-ordered samples of the engine)
+    const int tc_mode = d_pieces != nullptr ? 0 : (d_perm != nullptr ? 1 : nb::g_backward_tc.load());
     // The tensor-memory kernel adds its weight gradients with 16-byte reductions; the register kernel needs 8 bytes only.
     const bool grads_16 = !misaligned(d_grad_density_w, 16) && !misaligned(d_grad_color_w, 16);
     if (tc_mode == 1 && !grads_16)
@@ -995,6 +1014,18 @@ extern "C" int nb_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* 
     return field_backward_impl(density, color, d_enc_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b, d_color_w_h, d_color_b, n,
                                d_dcolor_h, d_dsigma, d_grad_density_w, d_grad_density_b, d_grad_color_w, d_grad_color_b, d_denc_h, grid, d_pos4,
                                d_table_grads, stream, nullptr);
+}
+
+extern "C" int nb_part_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, int ranks, int64_t capacity, const void* d_enc_h,
+                                      const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
+                                      const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n, const void* d_dcolor_h,
+                                      const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b, float* d_grad_color_w,
+                                      float* d_grad_color_b, void* d_pieces_h, void* stream) {
+    if (!d_pieces_h || ranks < 1 || 16 % ranks != 0 || capacity < n || misaligned(d_pieces_h, 4))
+        return nb_set_error(NB_ERR_INVALID, "nb_part_field_backward: pieces required, ranks must divide the 16 levels, capacity >= n");
+    return field_backward_impl(density, color, d_enc_h, d_dirs3, d_ray_indices, ray_index_offset, d_density_w_h, d_density_b, d_color_w_h, d_color_b, n,
+                               d_dcolor_h, d_dsigma, d_grad_density_w, d_grad_density_b, d_grad_color_w, d_grad_color_b, nullptr, nullptr, nullptr,
+                               nullptr, stream, nullptr, reinterpret_cast<uint32_t*>(d_pieces_h), ranks, capacity);
 }
 
 extern "C" int nb_field_backward_ordered(const nb_mlp_desc* density, const nb_mlp_desc* color, const void* d_enc_h, const float* d_dirs3,

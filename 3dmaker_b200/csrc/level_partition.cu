@@ -10,8 +10,9 @@
 //      destination rank;
 //   3. all-to-all of the pieces: every rank now holds all 16 levels' features of its own samples;
 //   4. nb_part_field_forward: the networks, exactly as nb_field_forward, reading the encoding from the pieces;
-//      compositing, loss, nb_field_backward (without a table gradient: it writes dL/d(encoding));
-//   5. nb_part_pack_denc + all-to-all back: the owner receives the gradient of its levels for all ranks' samples;
+//      compositing, loss, the networks' backward (no table gradient here);
+//   5. dL/d(encoding) by owner (nb_part_field_backward writes the pieces itself; nb_part_pack_denc makes them from a
+//      row-major matrix) + all-to-all back: the owner receives the gradient of its levels for all ranks' samples;
 //   6. nb_part_scatter: the owner adds them to ITS levels of the table gradient (the scatter kernels of hashgrid.cu on the
 //      level view); the optimizer then updates owned levels only - no gradient or parameter exchange for the table at all.
 // The collectives are the caller's (NCCL through the host); the kernels here only define the buffer layouts:

@@ -566,7 +566,7 @@ void InstantNerf::partitionedForward(const float* chunk_d, int64_t n, int colorS
     const int64_t B = (int64_t)m_opts.batchSize;
     const int world = (int)m_partWorld, rank = (int)m_partRank;
     // phase times in this mode: shGather = positions to everybody, colorFwd = encoding of the owned levels, densityGrad =
-    // the two exchanges of pieces, densityFwd / colorBwd = the networks, densityBwd = packing, scatter = the owners' scatter
+    // the two exchanges of pieces, densityFwd / colorBwd = the networks, scatter = the owners' scatter
     timed(stream, m_times.shGather, [&]() {
         throw_on_error(nb_part_stamp_count(d_positions.as<float>(), B, n, stream), "partition: count");
         m_partGather(d_positions.as<float>(), d_pos_all.as<float>(), (B + 1) * 4 * (int64_t)sizeof(float), stream);
@@ -592,15 +592,13 @@ void InstantNerf::partitionedBackward(const float* chunk_d, int64_t n, cudaStrea
     TinyMLP* cn = m_colorMLP;
     const int64_t B = (int64_t)m_opts.batchSize;
     const int world = (int)m_partWorld, rank = (int)m_partRank;
+    // the backward writes dL/d(encoding) straight into the pieces (rows behind n stay as they are: receivers go by the count)
     if (n > 0) timed(stream, m_times.colorBwd, [&]() {
-        throw_on_error(nb_field_backward(&dn->desc(), &cn->desc(), d_enc.as<half>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
-                                         m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
-                                         m_arena.W(cn->biasOffset()), n, d_color_grad.as<half>(), d_tmpsigma.as<float>(),
-                                         m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()), m_arena.G(cn->weightOffset()),
-                                         m_arena.G(cn->biasOffset()), d_denc.as<half>(), nullptr, nullptr, nullptr, stream), "partition: field backward");
-    });
-    timed(stream, m_times.densityBwd, [&]() {
-        throw_on_error(nb_part_pack_denc(&dn->grid(), world, B, d_denc.as<half>(), n, d_pieces_send.as<void>(), stream), "partition: pack");
+        throw_on_error(nb_part_field_backward(&dn->desc(), &cn->desc(), world, B, d_enc.as<half>(), chunk_d, d_ray_indices.as<uint32_t>(), 0,
+                                              m_arena.Wh(dn->weightOffset()), m_arena.W(dn->biasOffset()), m_arena.Wh(cn->weightOffset()),
+                                              m_arena.W(cn->biasOffset()), n, d_color_grad.as<half>(), d_tmpsigma.as<float>(),
+                                              m_arena.G(dn->weightOffset()), m_arena.G(dn->biasOffset()), m_arena.G(cn->weightOffset()),
+                                              m_arena.G(cn->biasOffset()), d_pieces_send.as<void>(), stream), "partition: field backward");
     });
     const int64_t piece = (int64_t)(dn->grid().num_levels / world) * B * (int64_t)sizeof(uint32_t);
     timed(stream, m_times.densityGrad, [&]() { m_partExchange(d_pieces_send.as<void>(), d_pieces_recv.as<void>(), piece, stream); });

@@ -178,6 +178,13 @@ int nb_part_field_forward(const nb_grid_desc* grid, const nb_mlp_desc* density, 
                           int rgb_stride, void* stream);
 /* d_denc_h fp16 [n][2 levels] as nb_field_backward (without a table gradient) writes it -> pieces for the owners. */
 int nb_part_pack_denc(const nb_grid_desc* grid, int ranks, int64_t capacity, const void* d_denc_h, int64_t n, void* d_pieces_h, void* stream);
+/* nb_field_backward without a table gradient whose dL/d(encoding) goes straight into the pieces (no row-major copy, no
+ * nb_part_pack_denc); always the register formulation of the kernel. */
+int nb_part_field_backward(const nb_mlp_desc* density, const nb_mlp_desc* color, int ranks, int64_t capacity, const void* d_enc_h,
+                           const float* d_dirs3, const uint32_t* d_ray_indices, int64_t ray_index_offset, const void* d_density_w_h,
+                           const float* d_density_b, const void* d_color_w_h, const float* d_color_b, int64_t n, const void* d_dcolor_h,
+                           const float* d_dsigma, float* d_grad_density_w, float* d_grad_density_b, float* d_grad_color_w,
+                           float* d_grad_color_b, void* d_pieces_h, void* stream);
 /* The owner's levels of d_table_grads (the WHOLE gradient array, standard layout) receive the gradients of all ranks'
  * samples: hashTableScatter_Backward (networkFusionBackwardHashtable.cu:783-910) restricted to the owned levels. */
 int nb_part_scatter(const nb_grid_desc* grid, int ranks, int rank, int64_t capacity, const float* d_pos_all, const void* d_pieces_h,

@@ -90,6 +90,21 @@ def test_level_partition_equals_the_replicated_path(cuda, nb, ranks, counts, hal
             pieces = torch.zeros((ranks, own, cap), dtype=torch.int32, device="cuda")
             nb.check(lib.nb_part_pack_denc(G, ranks, cap, P(denc), n, P(pieces), st), "nb_part_pack_denc")
             dsend.append(pieces)
+            # the backward that writes the pieces itself (register kernel) against backward + pack: same rounding points,
+            # fp32 sums in another order, so an fp16 value may differ in its last bit here and there
+            direct = torch.zeros_like(pieces)
+            scratch2 = torch.zeros(m.total, dtype=f32, device="cuda")
+            nb.check(lib.nb_part_field_backward(D, C, ranks, cap, P(o["enc"]), P(dirs), None, 0, *w, n, P(dcol), None,
+                                                ctypes.c_void_p(scratch2.data_ptr() + 4 * m.off_dw), ctypes.c_void_p(scratch2.data_ptr() + 4 * m.off_db),
+                                                ctypes.c_void_p(scratch2.data_ptr() + 4 * m.off_cw), ctypes.c_void_p(scratch2.data_ptr() + 4 * m.off_cb),
+                                                P(direct), st), "nb_part_field_backward")
+            torch.cuda.synchronize()
+            if n > 0:
+                a = pieces[:, :, :n].contiguous().view(f16).float().cpu().numpy()
+                b = direct[:, :, :n].contiguous().view(f16).float().cpu().numpy()
+                assert rel_err(b, a) <= 2e-3 and np.mean(a != b) < 2e-2
+                assert rel_err(scratch2.cpu().numpy(), scratch.cpu().numpy()) <= 2e-3
+            assert n >= cap or float(direct[:, :, n:].abs().max().item()) == 0          # nothing is written behind the last sample
         drecv = [torch.stack([dsend[q][r] for q in range(ranks)]).contiguous() for r in range(ranks)]
         # ---- 6. every owner scatters its levels for everybody's samples
         H = m.hash_count
